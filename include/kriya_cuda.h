@@ -1,0 +1,218 @@
+/*
+ * C ABI of libkriya_cuda: the B200 (sm_100a) backend for KriyaRT's paged KV-cache hot path.
+ *
+ * These entry points are what a `kriya-backend-cuda` crate binds in place of the attention /
+ * KV dispatch sites of `MetalExecutor` (crates/kriya-backend-metal/src/encoder.rs, "enc:").
+ * Each declaration cites the reference interface it replaces.  There is no CPU fallback: every
+ * compute entry point launches CUDA kernels on the context's device or returns an error code.
+ *
+ * Conventions
+ *   - All functions return 0 on success or a negative kriya_cuda_status; the message of the most
+ *     recent failure on a context is available from kriya_cuda_last_error().
+ *   - A context is single-threaded and non-re-entrant, like `&mut self` on the reference executor
+ *     (enc:4756, crates/kriya-server/src/runtime.rs:19-27).
+ *   - Pointers named *_dev are device pointers on the context's device; *_host are host pointers.
+ *     Activations and the cache are 16-bit (bf16 or fp16 bit patterns, chosen at create time);
+ *     plan arrays are int32; positions are uint32; partial softmax states are fp32.
+ *   - Work is enqueued on the context's stream; host-pointer variants and kriya_cuda_sync()
+ *     wait for completion, everything else returns as soon as the launch is queued.
+ *   - The step path allocates nothing: pool, plan buffers, work list and scratch are sized at
+ *     create time (enc:7,1957-2035) and an over-capacity plan is rejected with
+ *     KRIYA_CUDA_INVALID_INPUT (enc:2159-2218).
+ */
+#ifndef KRIYA_CUDA_H
+#define KRIYA_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#include "kriya_kv.h" /* kriya_cta_work_tile */
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct kriya_cuda_ctx kriya_cuda_ctx;
+
+/* MetalError (enc:32-54) as status codes. */
+typedef enum kriya_cuda_status {
+    KRIYA_CUDA_OK = 0,
+    KRIYA_CUDA_DEVICE_INIT_FAILED = -1, /* DeviceInitFailed */
+    KRIYA_CUDA_INVALID_INPUT = -2,      /* InvalidExecutionInput */
+    KRIYA_CUDA_EXECUTION_ERROR = -3,    /* ExecutionError: a CUDA call failed or a kernel reported a bad index / timeout */
+    KRIYA_CUDA_UNSUPPORTED = -4,        /* UnsupportedProductionConfiguration: shape the kernels are not built for */
+    KRIYA_CUDA_TIMEOUT = -5             /* kriya_cuda_sync() gave up waiting */
+} kriya_cuda_status;
+
+enum { KRIYA_DTYPE_BF16 = 0, KRIYA_DTYPE_FP16 = 1 };
+
+/* RopeKvWriteParams, 48 bytes, byte-identical to enc:159-174 / paged_gqa_and_deltanet.metal:72-85. */
+typedef struct kriya_rope_kv_write_params {
+    uint32_t num_q_heads;
+    uint32_t num_kv_heads;
+    uint32_t head_dim;
+    uint32_t rotary_dim;
+    uint32_t block_size_tokens;
+    uint32_t apply_qk_norm;
+    float rms_eps;
+    float rope_theta;
+    uint32_t max_seq_len;
+    uint32_t has_table;
+    uint32_t _pad0;
+    uint32_t _pad1;
+} kriya_rope_kv_write_params;
+
+/* BsrGqaParams, 32 bytes, byte-identical to enc:176-187 / paged_gqa_and_deltanet.metal:60-69. */
+typedef struct kriya_bsr_gqa_params {
+    uint32_t num_q_heads;
+    uint32_t num_kv_heads;
+    uint32_t head_dim;
+    uint32_t block_size_tokens;
+    uint32_t max_split_k_tiles;
+    uint32_t max_query_tokens;
+    float sm_scale;
+    float logit_softcap;
+} kriya_bsr_gqa_params;
+
+/* What `MetalExecutor::new(desc, shader_dir, ckpt, num_kv_blocks, block_size_tokens)` (enc:1680-1696)
+ * derives from the model descriptor for this path, plus capacities.  Zero capacities pick defaults
+ * derived from num_kv_blocks (the reference's fixed 1024 / 16384 / 4096 entries, enc:1964-1967, are
+ * too small for long contexts). */
+typedef struct kriya_cuda_config {
+    int32_t device;              /* CUDA device ordinal */
+    uint32_t num_layers;         /* layers sharing the pool; layer l starts at l * layer stride (enc:2061) */
+    uint32_t num_kv_blocks;      /* physical blocks per layer */
+    uint32_t block_size_tokens;  /* tokens per block (kernels are built for 16) */
+    uint32_t num_q_heads;
+    uint32_t num_kv_heads;
+    uint32_t head_dim;           /* 64 or 128 */
+    uint32_t dtype;              /* KRIYA_DTYPE_* storage of activations and cache */
+    uint32_t rotary_dim;         /* 0 -> head_dim (enc:1929-1933) */
+    float rope_theta;
+    uint32_t rope_max_seq_len;   /* rows of the fp32 cos/sin table; 0 -> 4096 (enc:1939) */
+    uint32_t max_batch_rows;     /* plan rows (sequences) per step; 0 -> 1024 */
+    uint32_t max_page_indices;   /* page_indices entries per plan; 0 -> max(16384, num_kv_blocks) */
+    uint32_t max_tiles;          /* cta_work_tiles entries per plan; 0 -> 4096 */
+    uint32_t max_query_tokens;   /* tokens per append / prefill call; 0 -> 8192 */
+} kriya_cuda_config;
+
+/* ---- context ------------------------------------------------------------------------------- */
+
+/* MetalExecutor::new / new_internal (enc:1680-1696,1740-2035): selects the device, allocates the K
+ * and V pools for all layers, the RoPE cos/sin table (enc:1939-1955), plan buffers and scratch. */
+int32_t kriya_cuda_ctx_create(const kriya_cuda_config* cfg, kriya_cuda_ctx** out_ctx);
+void kriya_cuda_ctx_destroy(kriya_cuda_ctx* ctx);
+/* Message of the last failure on `ctx`; with ctx == NULL, of the last failed kriya_cuda_ctx_create on
+ * this thread.  The string stays valid until the next call on the same context / thread. */
+const char* kriya_cuda_last_error(const kriya_cuda_ctx* ctx);
+/* MetalExecutor::layer_kv_byte_offset (enc:2059-2063). */
+uint64_t kriya_cuda_layer_kv_byte_offset(const kriya_cuda_ctx* ctx, uint32_t layer);
+/* Device base pointers of one layer's K and V pools, laid out [num_kv_blocks][block][Hkv][D] 16-bit
+ * (kv_cache_k_buf / kv_cache_v_buf + layer offset, enc:1890-1894,4969-4970).  For tests and for hosts
+ * that fill the cache themselves. */
+int32_t kriya_cuda_kv_pool_ptrs(kriya_cuda_ctx* ctx, uint32_t layer, void** out_k_dev, void** out_v_dev);
+/* The CUDA stream (cudaStream_t) all work of this context is queued on. */
+void* kriya_cuda_stream(kriya_cuda_ctx* ctx);
+/* wait_for_gpu (enc:2070-2109): waits until queued work has finished, polling; timeout_ms == 0 waits
+ * without limit.  Also surfaces errors reported by kernels (bad block index, bounded wait expired). */
+int32_t kriya_cuda_sync(kriya_cuda_ctx* ctx, uint32_t timeout_ms);
+
+/* ---- per-step plan ("plan once, run per layer", crates/kriya-kv/src/bsr_paged.rs:299-301) -------- */
+
+/* The copy of tokens/positions/indptr/indices/last_len/tiles into the executor's buffers
+ * (enc:4803-4846) preceded by validate_batch_inputs (enc:2159-2218).  All pointers are host memory
+ * and may be dropped when the call returns.  Besides capacities this checks what the kernels rely on:
+ * indptr monotone from 0, 0 <= page_indices < num_kv_blocks, 1 <= last_page_len <= block size, tiles
+ * inside their row.  The plan stays current for every following append / decode / prefill call on
+ * any layer until the next upload.  `seq_positions` has one entry per row for decode, one per token
+ * for prefill (n_positions says how many). */
+int32_t kriya_cuda_plan_upload(kriya_cuda_ctx* ctx, const int32_t* page_indptr_host, size_t indptr_len,
+                               const int32_t* page_indices_host, size_t indices_len,
+                               const int32_t* last_page_len_host, size_t last_len_len,
+                               const kriya_cta_work_tile* tiles_host, size_t tiles_len,
+                               const uint32_t* seq_positions_host, size_t n_positions);
+
+/* ---- the hot path ----------------------------------------------------------------------------- */
+
+/* fused_qknorm_rope_and_kv_append (paged_gqa_and_deltanet.metal:115-226; dispatch enc:4945-4983 and
+ * enc:4218-4256).  Row r of q/k/v is token r of the current plan: q is rotated in place, K is rotated
+ * into slot (page_indices[indptr[r+1]-1], last_page_len[r]-1) of `layer`, V is copied bit for bit.
+ * Uses the context's cos/sin table when params->has_table != 0 and the position is inside it,
+ * otherwise pow/cos/sin on the device.  q_norm_w / k_norm_w may be NULL when apply_qk_norm == 0. */
+int32_t kriya_cuda_rope_kv_append(kriya_cuda_ctx* ctx, uint32_t layer, void* q_inout_dev, const void* k_in_dev,
+                                  const void* v_in_dev, const void* q_norm_w_dev, const void* k_norm_w_dev,
+                                  uint32_t num_tokens, const kriya_rope_kv_write_params* params);
+
+/* Chunked-prefill append: the same kernel for a chunk of `num_tokens` tokens of ONE sequence whose
+ * block table is row 0 of the current plan; token i lands at absolute position prefix_tokens + i.
+ * Replaces the per-token BSR rows of build_parallel_prefill_layout (bsr_paged.rs:607-667), which grow
+ * as O(tokens x blocks), by (table, prefix, count).  Positions for RoPE are prefix_tokens + i. */
+int32_t kriya_cuda_rope_kv_append_chunk(kriya_cuda_ctx* ctx, uint32_t layer, void* q_inout_dev, const void* k_in_dev,
+                                        const void* v_in_dev, const void* q_norm_w_dev, const void* k_norm_w_dev,
+                                        uint32_t prefix_tokens, uint32_t num_tokens,
+                                        const kriya_rope_kv_write_params* params);
+
+/* bsr_paged_gqa_decode_stage1 + bsr_paged_gqa_split_k_reduce (paged_gqa_and_deltanet.metal:242-495,
+ * 1474-1525; dispatch enc:4986-5053) behind one call.  For every row r of the current plan, query
+ * heads q[r] attend over all blocks of the row (last block limited to last_page_len[r]); out[r] gets
+ * the normalised result in the storage dtype.  The query heads of one KV head are processed together
+ * so each cached K/V element is read once; long rows are split along the KV axis by the library's own
+ * balanced work list and merged by the last work item to finish (the caller's cta_work_tiles are
+ * validated but do not constrain the split).  q and out are [rows][Hq][D]. */
+int32_t kriya_cuda_paged_gqa_decode(kriya_cuda_ctx* ctx, uint32_t layer, const void* q_dev, void* out_dev,
+                                    const kriya_bsr_gqa_params* params);
+
+/* Decode restricted to a block range of every row, returning the un-normalised softmax state instead
+ * of the output: m [rows][Hq] (running maximum, natural-log units, -inf for an empty range),
+ * l [rows][Hq] and o [rows][Hq][D], all fp32.  Row r covers logical blocks
+ * [blk_begin_host[r], blk_end_host[r]) (NULL: the whole row).  This is the per-GPU half of splitting
+ * one long sequence along the KV axis; kriya_cuda_merge_states() finishes it.  The reference has no
+ * multi-GPU path; the state is the (max, sum, output) triple of its split-K design
+ * (paged_gqa_and_deltanet.metal:328-342). */
+int32_t kriya_cuda_paged_gqa_decode_partial(kriya_cuda_ctx* ctx, uint32_t layer, const void* q_dev,
+                                            const uint32_t* blk_begin_host, const uint32_t* blk_end_host,
+                                            float* out_m_dev, float* out_l_dev, float* out_o_dev,
+                                            const kriya_bsr_gqa_params* params);
+
+/* Merge `parts` partial states laid out [parts][rows*Hq] (m, l) and [parts][rows*Hq][D] (o), e.g.
+ * gathered from all ranks, into the normalised 16-bit output [rows*Hq][D]: the split-K reduce
+ * (paged_gqa_and_deltanet.metal:1493-1524) on (m, l, o). */
+int32_t kriya_cuda_merge_states(kriya_cuda_ctx* ctx, const float* m_dev, const float* l_dev, const float* o_dev,
+                                uint32_t parts, uint32_t rows_times_heads, void* out_dev);
+
+/* bsr_paged_gqa_prefill_stage1 / _bq8 / bsr_paged_gqa_tiled_mma_prefill
+ * (paged_gqa_and_deltanet.metal:508-847,851-1192,1206-1468; selection and dispatch enc:4262-4311).
+ * Causal attention of a chunk of `num_tokens` queries of ONE sequence (row 0 of the current plan is
+ * its block table, already holding the chunk's K/V) at absolute positions prefix_tokens + i over
+ * cache positions 0..=prefix_tokens + i.  q and out are [num_tokens][Hq][D]. */
+int32_t kriya_cuda_paged_gqa_prefill(kriya_cuda_ctx* ctx, uint32_t layer, const void* q_dev, void* out_dev,
+                                     uint32_t prefix_tokens, uint32_t num_tokens, const kriya_bsr_gqa_params* params);
+
+/* Copy-on-write block copy: for every (src, dst) pair, in order, block dst := block src in every
+ * layer, K and V.  Consumes the pairs produced by append_token_slot (bsr_paged.rs:412-420) and
+ * collected in ScheduledIterationBatch.cow_block_copies (crates/kriya-scheduler/src/orca_engine.rs:
+ * 267-278,359); the reference backend ships no consumer.  `pairs_host` is [n_pairs][2] uint32. */
+int32_t kriya_cuda_kv_block_copy(kriya_cuda_ctx* ctx, const uint32_t* pairs_host, uint32_t n_pairs);
+
+/* commit_speculative_kv (enc:3591-3664): row `node` of a staging buffer [nodes][Hkv*D] is copied bit
+ * for bit into (block, slot) of `layer`'s K and V pools.  `triples_host` is [n][3] = (node, block, slot). */
+int32_t kriya_cuda_kv_slot_write(kriya_cuda_ctx* ctx, uint32_t layer, const void* stage_k_dev, const void* stage_v_dev,
+                                 const uint32_t* triples_host, uint32_t n);
+
+/* ---- host-buffer step (end-to-end form) --------------------------------------------------------- */
+
+/* One decode layer with HOST activations: copies q/k/v [rows][..] to the device, runs append then
+ * decode on `layer` with the current plan, copies out [rows][Hq][D] back and waits.  This is the shape
+ * of a forward_and_sample_batch call (enc:4756-4773) reduced to its attention ops: host inputs in,
+ * host result out. */
+int32_t kriya_cuda_decode_layer_host(kriya_cuda_ctx* ctx, uint32_t layer, const void* q_host, const void* k_host,
+                                     const void* v_host, void* out_host, uint32_t rows,
+                                     const kriya_rope_kv_write_params* rope, const kriya_bsr_gqa_params* gqa);
+
+/* Number of kernels this library has launched on `ctx` since creation (for launch accounting). */
+uint64_t kriya_cuda_launch_count(const kriya_cuda_ctx* ctx);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KRIYA_CUDA_H */

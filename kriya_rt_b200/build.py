@@ -1,0 +1,109 @@
+"""In-tree build of the native libraries (no build system beyond nvcc / g++ / gcc).
+
+    python -m kriya_rt_b200.build            # CUDA library + host bookkeeping library
+    python -m kriya_rt_b200.build --oracle   # also the C oracle used by tests and the CPU baseline
+
+Outputs (git-ignored, they travel with the tree):
+    kriya_rt_b200/lib/libkriya_cuda.so   sm_100a kernels + C ABI (include/kriya_cuda.h)
+    kriya_rt_b200/lib/libkriya_kv.so     host bookkeeping C ABI (include/kriya_kv.h)
+    oracle/libkriya_oracle.so            CPU oracle (test infrastructure)
+"""
+from __future__ import annotations
+
+import argparse
+import os
+import shutil
+import subprocess
+import sys
+from concurrent.futures import ThreadPoolExecutor
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent.parent
+CSRC = ROOT / "kriya_rt_b200" / "csrc"
+LIB = ROOT / "kriya_rt_b200" / "lib"
+INCLUDE = ROOT / "include"
+OBJ = ROOT / "build" / "obj"
+
+CUDA_SOURCES = ["kriya_ctx.cu", "kriya_append.cu", "kriya_decode.cu", "kriya_copy.cu", "kriya_prefill.cu"]
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+    "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr", "-Xptxas", "-v",
+]
+
+
+def _nvcc() -> str:
+    exe = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(exe):
+        raise RuntimeError("nvcc not found: the CUDA library cannot be built")
+    return exe
+
+
+def _newer(target: Path, deps) -> bool:
+    if not target.exists():
+        return False
+    t = target.stat().st_mtime
+    return all(Path(d).stat().st_mtime <= t for d in deps)
+
+
+def _run(cmd, log: Path | None = None) -> None:
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if log is not None:
+        log.write_text(" ".join(map(str, cmd)) + "\n" + res.stdout + res.stderr)
+    if res.returncode != 0:
+        sys.stderr.write(res.stdout + res.stderr)
+        raise RuntimeError("build step failed: " + " ".join(map(str, cmd)))
+
+
+def build_cuda(force: bool = False) -> Path:
+    LIB.mkdir(parents=True, exist_ok=True)
+    OBJ.mkdir(parents=True, exist_ok=True)
+    headers = list(CSRC.glob("*.h")) + list(CSRC.glob("*.cuh")) + list(INCLUDE.glob("*.h"))
+    sources = [s for s in CUDA_SOURCES if (CSRC / s).exists()]
+    out = LIB / "libkriya_cuda.so"
+    objs = [OBJ / (Path(s).stem + ".o") for s in sources]
+
+    def compile_one(pair):
+        src, obj = pair
+        if not force and _newer(obj, [CSRC / src] + headers):
+            return
+        _run([_nvcc(), *NVCC_FLAGS, "-I", str(INCLUDE), "-I", str(CSRC), "-c", str(CSRC / src), "-o", str(obj)],
+             log=OBJ / (Path(src).stem + ".ptxas.log"))
+
+    with ThreadPoolExecutor(max_workers=min(8, len(sources))) as pool:
+        list(pool.map(compile_one, zip(sources, objs)))
+    if force or not _newer(out, objs):
+        _run([_nvcc(), "-shared", "-o", str(out), *map(str, objs), "-lcudart"])
+    return out
+
+
+def build_kv(force: bool = False) -> Path:
+    LIB.mkdir(parents=True, exist_ok=True)
+    out = LIB / "libkriya_kv.so"
+    src = CSRC / "kriya_kv.cpp"
+    if force or not _newer(out, [src, INCLUDE / "kriya_kv.h"]):
+        _run(["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-Wall", "-I", str(INCLUDE), str(src), "-o", str(out)])
+    return out
+
+
+def build_oracle(force: bool = False) -> Path:
+    out = ROOT / "oracle" / "libkriya_oracle.so"
+    src = ROOT / "oracle" / "kriya_oracle.c"
+    if force or not _newer(out, [src]):
+        _run(["gcc", "-O3", "-march=native", "-ffp-contract=off", "-fopenmp", "-fPIC", "-shared", "-Wall",
+              str(src), "-o", str(out), "-lm"])
+    return out
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--force", action="store_true")
+    ap.add_argument("--oracle", action="store_true")
+    args = ap.parse_args()
+    print(build_kv(args.force))
+    print(build_cuda(args.force))
+    if args.oracle:
+        print(build_oracle(args.force))
+
+
+if __name__ == "__main__":
+    main()

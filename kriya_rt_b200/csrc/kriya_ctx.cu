@@ -1,0 +1,686 @@
+// Context, plan upload and the C ABI of libkriya_cuda (see include/kriya_cuda.h).
+//
+// The context plays the part of MetalExecutor for this path
+// (crates/kriya-backend-metal/src/encoder.rs:1740-2035): it owns the KV pools of all layers, the RoPE
+// cos/sin table, the per-step plan buffers and all scratch, allocated once.  Nothing on the step path
+// allocates.
+#include <math.h>
+#include <string.h>
+
+#include <algorithm>
+#include <chrono>
+#include <string>
+#include <thread>
+#include <vector>
+
+#include "kriya_internal.h"
+
+namespace {
+
+thread_local std::string g_create_error;
+
+inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+#define KRIYA_CUDA_TRY(ctx, expr)                                                                          \
+    do {                                                                                                   \
+        cudaError_t _e = (expr);                                                                           \
+        if (_e != cudaSuccess)                                                                             \
+            return (ctx)->fail(KRIYA_CUDA_EXECUTION_ERROR, std::string(#expr) + ": " + cudaGetErrorString(_e)); \
+    } while (0)
+
+void destroy(kriya_cuda_ctx* c) {
+    if (!c) return;
+    cudaSetDevice(c->cfg.device);
+    if (c->stream) cudaStreamSynchronize(c->stream);
+    if (c->copy_stream) cudaStreamSynchronize(c->copy_stream);
+    cudaFree(c->pool_k);
+    cudaFree(c->pool_v);
+    cudaFree(c->rope_table);
+    cudaFree(c->d_plan);
+    cudaFree(c->part_o);
+    cudaFree(c->part_ml);
+    cudaFree(c->part_counter);
+    cudaFree(c->d_status);
+    cudaFree(c->d_act);
+    cudaFree(c->d_pairs);
+    for (int i = 0; i < 2; ++i) {
+        if (c->h_plan[i]) cudaFreeHost(c->h_plan[i]);
+        if (c->h_plan_free[i]) cudaEventDestroy(c->h_plan_free[i]);
+    }
+    if (c->h_status) cudaFreeHost(c->h_status);
+    if (c->h_act) cudaFreeHost(c->h_act);
+    if (c->h_pairs) cudaFreeHost(c->h_pairs);
+    if (c->h_pairs_free) cudaEventDestroy(c->h_pairs_free);
+    if (c->stream) cudaStreamDestroy(c->stream);
+    if (c->copy_stream) cudaStreamDestroy(c->copy_stream);
+    delete c;
+}
+
+// Splits every plan row into near-equal contiguous block ranges so that about `target` work items of
+// similar size exist, largest first.  `begin`/`end` (optional) restrict each row to a block range.
+uint32_t build_work(const int32_t* indptr, uint32_t rows, const uint32_t* begin, const uint32_t* end, uint32_t target,
+                    uint32_t min_chunk, KriyaDecodeWork* out, uint32_t cap) {
+    uint64_t total = 0;
+    for (uint32_t r = 0; r < rows; ++r) {
+        const uint32_t nb = uint32_t(indptr[r + 1] - indptr[r]);
+        const uint32_t b = begin ? std::min(begin[r], nb) : 0u;
+        const uint32_t e = end ? std::min(end[r], nb) : nb;
+        total += e > b ? e - b : 0u;
+    }
+    uint32_t chunk = uint32_t((total + target - 1) / std::max(target, 1u));
+    chunk = std::max(chunk, min_chunk);
+    uint32_t n = 0, slot = 0;
+    for (uint32_t r = 0; r < rows; ++r) {
+        const uint32_t nb = uint32_t(indptr[r + 1] - indptr[r]);
+        const uint32_t b = begin ? std::min(begin[r], nb) : 0u;
+        const uint32_t e = end ? std::min(end[r], nb) : nb;
+        const uint32_t len = e > b ? e - b : 0u;
+        const uint32_t parts = std::max(1u, (len + chunk - 1) / chunk);
+        const uint32_t size = (len + parts - 1) / parts;
+        if (n + parts > cap) return UINT32_MAX;
+        for (uint32_t k = 0; k < parts; ++k) {
+            KriyaDecodeWork w{};
+            w.req = r;
+            w.blk_begin = b + std::min(k * size, len);
+            w.blk_end = b + std::min((k + 1) * size, len);
+            w.slot = slot + k;
+            w.first_slot = slot;
+            w.n_parts = parts;
+            out[n++] = w;
+        }
+        slot += parts;
+    }
+    std::stable_sort(out, out + n, [](const KriyaDecodeWork& x, const KriyaDecodeWork& y) {
+        return (x.blk_end - x.blk_begin) > (y.blk_end - y.blk_begin);
+    });
+    return n;
+}
+
+int32_t check_layer(kriya_cuda_ctx* c, uint32_t layer) {
+    if (layer >= c->cfg.num_layers)
+        return c->fail(KRIYA_CUDA_INVALID_INPUT, "layer " + std::to_string(layer) + " out of range (context has " +
+                                                     std::to_string(c->cfg.num_layers) + ")");
+    return KRIYA_CUDA_OK;
+}
+
+int32_t check_gqa(kriya_cuda_ctx* c, const kriya_bsr_gqa_params* p) {
+    if (!p) return c->fail(KRIYA_CUDA_INVALID_INPUT, "params must not be null");
+    if (p->num_q_heads != c->cfg.num_q_heads || p->num_kv_heads != c->cfg.num_kv_heads ||
+        p->head_dim != c->cfg.head_dim || p->block_size_tokens != c->cfg.block_size_tokens)
+        return c->fail(KRIYA_CUDA_INVALID_INPUT, "BsrGqaParams shape differs from the context's configuration");
+    return KRIYA_CUDA_OK;
+}
+
+int32_t check_rope(kriya_cuda_ctx* c, const kriya_rope_kv_write_params* p) {
+    if (!p) return c->fail(KRIYA_CUDA_INVALID_INPUT, "params must not be null");
+    if (p->num_q_heads != c->cfg.num_q_heads || p->num_kv_heads != c->cfg.num_kv_heads ||
+        p->head_dim != c->cfg.head_dim || p->block_size_tokens != c->cfg.block_size_tokens)
+        return c->fail(KRIYA_CUDA_INVALID_INPUT, "RopeKvWriteParams shape differs from the context's configuration");
+    if (p->rotary_dim > p->head_dim || (p->rotary_dim & 1u))
+        return c->fail(KRIYA_CUDA_INVALID_INPUT, "rotary_dim must be even and <= head_dim");
+    return KRIYA_CUDA_OK;
+}
+
+// The table is only usable when it was built for the same theta / rotary_dim the call asks for.
+const float* table_for(const kriya_cuda_ctx* c, const kriya_rope_kv_write_params* p) {
+    if (!p->has_table || !c->rope_table) return nullptr;
+    if (p->rotary_dim != c->rope_rotary_dim || p->rope_theta != c->cfg.rope_theta) return nullptr;
+    if (p->max_seq_len > c->cfg.rope_max_seq_len) return nullptr;
+    return c->rope_table;
+}
+
+int32_t launch_append(kriya_cuda_ctx* c, uint32_t layer, void* q, const void* k, const void* v, const void* qw,
+                      const void* kw, uint32_t num_tokens, uint32_t chunk_mode, uint32_t prefix,
+                      const kriya_rope_kv_write_params* p) {
+    KriyaAppendArgs a{};
+    a.q_inout = q;
+    a.k_in = k;
+    a.v_in = v;
+    a.q_norm_w = qw;
+    a.k_norm_w = kw;
+    a.cache_k = c->layer_k(layer);
+    a.cache_v = c->layer_v(layer);
+    a.indptr = c->plan_dev<int32_t>(c->off_indptr);
+    a.indices = c->plan_dev<int32_t>(c->off_indices);
+    a.last_len = c->plan_dev<int32_t>(c->off_last_len);
+    a.positions = c->plan_dev<uint32_t>(c->off_positions);
+    a.table = table_for(c, p);
+    a.status = c->d_status;
+    a.num_tokens = num_tokens;
+    a.num_blocks = c->cfg.num_kv_blocks;
+    a.chunk_mode = chunk_mode;
+    a.prefix_tokens = prefix;
+    a.p = *p;
+    KRIYA_CUDA_TRY(c, kriya_launch_append(a, c->cfg.dtype, c->stream));
+    c->launches += 1;
+    return KRIYA_CUDA_OK;
+}
+
+int32_t launch_decode(kriya_cuda_ctx* c, uint32_t layer, const void* q, void* out, float* sm, float* sl, float* so,
+                      size_t work_off, uint32_t n_work, const kriya_bsr_gqa_params* p) {
+    KriyaDecodeArgs a{};
+    a.q = q;
+    a.cache_k = c->layer_k(layer);
+    a.cache_v = c->layer_v(layer);
+    a.indptr = c->plan_dev<int32_t>(c->off_indptr);
+    a.indices = c->plan_dev<int32_t>(c->off_indices);
+    a.last_len = c->plan_dev<int32_t>(c->off_last_len);
+    a.work = c->plan_dev<KriyaDecodeWork>(work_off);
+    a.out = out;
+    a.part_o = c->part_o;
+    a.part_ml = c->part_ml;
+    a.counters = c->part_counter;
+    a.state_m = sm;
+    a.state_l = sl;
+    a.state_o = so;
+    a.status = c->d_status;
+    a.n_work = n_work;
+    a.num_blocks = c->cfg.num_kv_blocks;
+    a.num_q_heads = c->cfg.num_q_heads;
+    a.num_kv_heads = c->cfg.num_kv_heads;
+    a.sm_scale = p->sm_scale;
+    a.logit_softcap = p->logit_softcap;
+    KRIYA_CUDA_TRY(c, kriya_launch_decode(a, c->cfg.head_dim, c->cfg.block_size_tokens, c->cfg.dtype,
+                                          c->max_smem_optin, c->stream));
+    c->launches += 1;
+    return KRIYA_CUDA_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t kriya_cuda_ctx_create(const kriya_cuda_config* cfg_in, kriya_cuda_ctx** out_ctx) {
+    auto bad = [&](int32_t code, const std::string& msg) {
+        g_create_error = msg;
+        return code;
+    };
+    if (!cfg_in || !out_ctx) return bad(KRIYA_CUDA_INVALID_INPUT, "config and out_ctx must not be null");
+    *out_ctx = nullptr;
+    kriya_cuda_config cfg = *cfg_in;
+    if (cfg.num_layers == 0 || cfg.num_kv_blocks == 0 || cfg.block_size_tokens == 0 || cfg.num_q_heads == 0 ||
+        cfg.num_kv_heads == 0 || cfg.head_dim == 0)
+        return bad(KRIYA_CUDA_INVALID_INPUT, "layers, blocks, block size, heads and head_dim must be non-zero");
+    if (cfg.num_q_heads % cfg.num_kv_heads != 0)
+        return bad(KRIYA_CUDA_INVALID_INPUT, "num_q_heads must be a multiple of num_kv_heads");
+    if (cfg.dtype != KRIYA_DTYPE_BF16 && cfg.dtype != KRIYA_DTYPE_FP16)
+        return bad(KRIYA_CUDA_INVALID_INPUT, "dtype must be KRIYA_DTYPE_BF16 or KRIYA_DTYPE_FP16");
+    if ((cfg.head_dim * 2u) % 16u != 0)
+        return bad(KRIYA_CUDA_UNSUPPORTED, "head_dim must make head rows a multiple of 16 bytes");
+    if (cfg.rotary_dim == 0) cfg.rotary_dim = cfg.head_dim;  // enc:1929-1933
+    if (cfg.rope_theta == 0.0f) cfg.rope_theta = 10000.0f;
+    if (cfg.rope_max_seq_len == 0) cfg.rope_max_seq_len = 4096;  // enc:1939
+    if (cfg.max_batch_rows == 0) cfg.max_batch_rows = 1024;
+    if (cfg.max_page_indices == 0) cfg.max_page_indices = std::max(16384u, cfg.num_kv_blocks);
+    if (cfg.max_tiles == 0) cfg.max_tiles = 4096;
+    if (cfg.max_query_tokens == 0) cfg.max_query_tokens = 8192;
+
+    int ndev = 0;
+    cudaError_t e = cudaGetDeviceCount(&ndev);
+    if (e != cudaSuccess || ndev == 0)
+        return bad(KRIYA_CUDA_DEVICE_INIT_FAILED,
+                   std::string("no CUDA device available: ") + (e != cudaSuccess ? cudaGetErrorString(e) : "count is 0"));
+    if (cfg.device < 0 || cfg.device >= ndev)
+        return bad(KRIYA_CUDA_DEVICE_INIT_FAILED, "device ordinal " + std::to_string(cfg.device) + " out of range");
+    if ((e = cudaSetDevice(cfg.device)) != cudaSuccess)
+        return bad(KRIYA_CUDA_DEVICE_INIT_FAILED, std::string("cudaSetDevice: ") + cudaGetErrorString(e));
+    cudaDeviceProp prop{};
+    if ((e = cudaGetDeviceProperties(&prop, cfg.device)) != cudaSuccess)
+        return bad(KRIYA_CUDA_DEVICE_INIT_FAILED, std::string("cudaGetDeviceProperties: ") + cudaGetErrorString(e));
+    if (prop.major != 10)
+        return bad(KRIYA_CUDA_DEVICE_INIT_FAILED, "this library holds sm_100a code only; device is sm_" +
+                                                      std::to_string(prop.major) + std::to_string(prop.minor));
+
+    auto* c = new kriya_cuda_ctx();
+    c->cfg = cfg;
+    c->sm_count = prop.multiProcessorCount;
+    c->max_smem_optin = int(prop.sharedMemPerBlockOptin);
+    c->block_bytes = size_t(cfg.block_size_tokens) * cfg.num_kv_heads * cfg.head_dim * 2;
+    c->layer_stride_bytes = align_up(size_t(cfg.num_kv_blocks) * c->block_bytes, 256);  // enc:1890-1894
+    c->cap_rows = cfg.max_batch_rows;
+    c->cap_indices = cfg.max_page_indices;
+    c->cap_tiles = cfg.max_tiles;
+    c->cap_tokens = std::max(cfg.max_query_tokens, cfg.max_batch_rows);
+    c->cap_work = c->cap_rows + 8u * uint32_t(c->sm_count);
+    c->cap_pairs = std::max(4096u, c->cap_rows);
+
+    auto fail_create = [&](const char* what, cudaError_t err) {
+        g_create_error = std::string(what) + ": " + cudaGetErrorString(err);
+        destroy(c);
+        return int32_t(KRIYA_CUDA_DEVICE_INIT_FAILED);
+    };
+#define CREATE_TRY(expr)                                     \
+    do {                                                     \
+        cudaError_t _e = (expr);                             \
+        if (_e != cudaSuccess) return fail_create(#expr, _e); \
+    } while (0)
+
+    CREATE_TRY(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
+    CREATE_TRY(cudaStreamCreateWithFlags(&c->copy_stream, cudaStreamNonBlocking));
+    const size_t pool_bytes = c->layer_stride_bytes * cfg.num_layers;
+    CREATE_TRY(cudaMalloc(&c->pool_k, pool_bytes));
+    CREATE_TRY(cudaMalloc(&c->pool_v, pool_bytes));
+    CREATE_TRY(cudaMemsetAsync(c->pool_k, 0, pool_bytes, c->stream));
+    CREATE_TRY(cudaMemsetAsync(c->pool_v, 0, pool_bytes, c->stream));
+
+    // RoPE table, enc:1939-1955: f32 cos/sin of pos * theta^-(2i/rot)
+    {
+        const uint32_t half_rot = std::max(cfg.rotary_dim / 2u, 1u);
+        std::vector<float> inv_freq(half_rot);
+        for (uint32_t i = 0; i < half_rot; ++i) {
+            const float freq_exp = (2.0f * float(i)) / float(cfg.rotary_dim);
+            inv_freq[i] = powf(cfg.rope_theta, -freq_exp);
+        }
+        std::vector<float> table(size_t(cfg.rope_max_seq_len) * half_rot * 2);
+        for (uint32_t pos = 0; pos < cfg.rope_max_seq_len; ++pos)
+            for (uint32_t i = 0; i < half_rot; ++i) {
+                const float angle = float(pos) * inv_freq[i];
+                table[(size_t(pos) * half_rot + i) * 2 + 0] = cosf(angle);
+                table[(size_t(pos) * half_rot + i) * 2 + 1] = sinf(angle);
+            }
+        CREATE_TRY(cudaMalloc(&c->rope_table, table.size() * sizeof(float)));
+        CREATE_TRY(cudaMemcpy(c->rope_table, table.data(), table.size() * sizeof(float), cudaMemcpyHostToDevice));
+        c->rope_rotary_dim = cfg.rotary_dim;
+    }
+
+    // plan image: small arrays first, the page-index array last so one copy of the used prefix suffices
+    size_t off = 0;
+    c->off_indptr = off;
+    off = align_up(off + (size_t(c->cap_rows) + 1) * 4, 256);
+    c->off_last_len = off;
+    off = align_up(off + size_t(c->cap_rows) * 4, 256);
+    c->off_positions = off;
+    off = align_up(off + size_t(c->cap_tokens) * 4, 256);
+    c->off_work = off;
+    off = align_up(off + size_t(c->cap_work) * sizeof(KriyaDecodeWork), 256);
+    c->off_range = off;  // second work list, used by the block-range (partial state) decode
+    off = align_up(off + size_t(c->cap_work) * sizeof(KriyaDecodeWork), 256);
+    c->off_tiles = off;
+    off = align_up(off + size_t(c->cap_tiles) * sizeof(kriya_cta_work_tile), 256);
+    c->off_indices = off;
+    off = align_up(off + size_t(c->cap_indices) * 4, 256);
+    c->plan_bytes = off;
+    CREATE_TRY(cudaMalloc(&c->d_plan, c->plan_bytes));
+    CREATE_TRY(cudaMemsetAsync(c->d_plan, 0, c->plan_bytes, c->stream));
+    for (int i = 0; i < 2; ++i) {
+        CREATE_TRY(cudaMallocHost(&c->h_plan[i], c->plan_bytes));
+        memset(c->h_plan[i], 0, c->plan_bytes);
+        CREATE_TRY(cudaEventCreateWithFlags(&c->h_plan_free[i], cudaEventDisableTiming));
+    }
+
+    const size_t rows_hq = size_t(c->cap_work) * cfg.num_q_heads;
+    CREATE_TRY(cudaMalloc(&c->part_o, rows_hq * cfg.head_dim * sizeof(float)));
+    CREATE_TRY(cudaMalloc(&c->part_ml, rows_hq * 2 * sizeof(float)));
+    CREATE_TRY(cudaMalloc(&c->part_counter, size_t(c->cap_rows) * sizeof(uint32_t)));
+    CREATE_TRY(cudaMemsetAsync(c->part_counter, 0, size_t(c->cap_rows) * sizeof(uint32_t), c->stream));
+    CREATE_TRY(cudaMalloc(&c->d_status, 256));
+    CREATE_TRY(cudaMemsetAsync(c->d_status, 0, 256, c->stream));
+    CREATE_TRY(cudaMallocHost(&c->h_status, 256));
+    *c->h_status = 0;
+
+    // staging for host-buffer calls: q, k, v in and out, for up to cap_tokens rows
+    c->act_bytes = size_t(c->cap_tokens) * (2 * cfg.num_q_heads + 2 * cfg.num_kv_heads) * cfg.head_dim * 2;
+    CREATE_TRY(cudaMalloc(&c->d_act, c->act_bytes));
+    CREATE_TRY(cudaMallocHost(&c->h_act, c->act_bytes));
+    CREATE_TRY(cudaMalloc(&c->d_pairs, size_t(c->cap_pairs) * 3 * sizeof(uint32_t)));
+    CREATE_TRY(cudaMallocHost(&c->h_pairs, size_t(c->cap_pairs) * 3 * sizeof(uint32_t)));
+    CREATE_TRY(cudaEventCreateWithFlags(&c->h_pairs_free, cudaEventDisableTiming));
+    CREATE_TRY(cudaStreamSynchronize(c->stream));
+#undef CREATE_TRY
+    *out_ctx = c;
+    return KRIYA_CUDA_OK;
+}
+
+void kriya_cuda_ctx_destroy(kriya_cuda_ctx* ctx) { destroy(ctx); }
+
+const char* kriya_cuda_last_error(const kriya_cuda_ctx* ctx) {
+    return ctx ? ctx->last_error.c_str() : g_create_error.c_str();
+}
+
+uint64_t kriya_cuda_layer_kv_byte_offset(const kriya_cuda_ctx* ctx, uint32_t layer) {
+    return ctx ? uint64_t(layer) * ctx->layer_stride_bytes : 0;
+}
+
+int32_t kriya_cuda_kv_pool_ptrs(kriya_cuda_ctx* ctx, uint32_t layer, void** out_k_dev, void** out_v_dev) {
+    if (!ctx) return KRIYA_CUDA_INVALID_INPUT;
+    if (int32_t rc = check_layer(ctx, layer)) return rc;
+    if (out_k_dev) *out_k_dev = ctx->layer_k(layer);
+    if (out_v_dev) *out_v_dev = ctx->layer_v(layer);
+    return KRIYA_CUDA_OK;
+}
+
+void* kriya_cuda_stream(kriya_cuda_ctx* ctx) { return ctx ? static_cast<void*>(ctx->stream) : nullptr; }
+
+uint64_t kriya_cuda_launch_count(const kriya_cuda_ctx* ctx) { return ctx ? ctx->launches : 0; }
+
+int32_t kriya_cuda_sync(kriya_cuda_ctx* ctx, uint32_t timeout_ms) {
+    if (!ctx) return KRIYA_CUDA_INVALID_INPUT;
+    cudaSetDevice(ctx->cfg.device);
+    KRIYA_CUDA_TRY(ctx, cudaMemcpyAsync(ctx->h_status, ctx->d_status, sizeof(uint32_t), cudaMemcpyDeviceToHost,
+                                        ctx->stream));
+    if (timeout_ms == 0) {
+        KRIYA_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    } else {
+        const auto t0 = std::chrono::steady_clock::now();
+        for (;;) {
+            const cudaError_t q = cudaStreamQuery(ctx->stream);
+            if (q == cudaSuccess) break;
+            if (q != cudaErrorNotReady)
+                return ctx->fail(KRIYA_CUDA_EXECUTION_ERROR, std::string("stream query: ") + cudaGetErrorString(q));
+            const auto ms = std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::steady_clock::now() - t0);
+            if (ms.count() > int64_t(timeout_ms))
+                return ctx->fail(KRIYA_CUDA_TIMEOUT, "queued work did not finish within " + std::to_string(timeout_ms) + " ms");
+            std::this_thread::yield();
+        }
+    }
+    const uint32_t st = *ctx->h_status;
+    if (st != KRIYA_DEV_OK) {
+        cudaMemsetAsync(ctx->d_status, 0, sizeof(uint32_t), ctx->stream);
+        *ctx->h_status = 0;
+        const char* what = st == KRIYA_DEV_BAD_BLOCK_INDEX ? "a page index outside the pool reached a kernel"
+                           : st == KRIYA_DEV_WAIT_EXPIRED  ? "a bounded wait inside a kernel expired"
+                           : st == KRIYA_DEV_BAD_SLOT      ? "a slot index outside its block reached a kernel"
+                                                           : "unknown kernel status";
+        return ctx->fail(KRIYA_CUDA_EXECUTION_ERROR, what);
+    }
+    return KRIYA_CUDA_OK;
+}
+
+int32_t kriya_cuda_plan_upload(kriya_cuda_ctx* c, const int32_t* indptr, size_t indptr_len, const int32_t* indices,
+                               size_t indices_len, const int32_t* last_len, size_t last_len_len,
+                               const kriya_cta_work_tile* tiles, size_t tiles_len, const uint32_t* positions,
+                               size_t n_positions) {
+    if (!c) return KRIYA_CUDA_INVALID_INPUT;
+    c->plan_valid = false;
+    auto invalid = [&](const std::string& m) { return c->fail(KRIYA_CUDA_INVALID_INPUT, m); };
+    // validate_batch_inputs, enc:2159-2218
+    if (!indptr || indptr_len < 2) return invalid("page_indptr must hold at least one row");
+    const size_t rows = indptr_len - 1;
+    if (!last_len || last_len_len != rows)
+        return invalid("last_page_len has " + std::to_string(last_len_len) + " entries but page_indptr describes " +
+                       std::to_string(rows) + " rows");
+    if (indices_len > 0 && !indices) return invalid("page_indices must not be null");
+    if (tiles_len > 0 && !tiles) return invalid("cta_work_tiles must not be null");
+    if (n_positions > 0 && !positions) return invalid("seq_positions must not be null");
+    auto over = [&](const char* name, size_t len, size_t cap) {
+        return invalid(std::string(name) + " has " + std::to_string(len) + " entries but its GPU buffer holds " +
+                       std::to_string(cap));
+    };
+    if (rows > c->cap_rows) return over("page_indptr", indptr_len, size_t(c->cap_rows) + 1);
+    if (indices_len > c->cap_indices) return over("page_indices", indices_len, c->cap_indices);
+    if (tiles_len > c->cap_tiles) return over("cta_work_tiles", tiles_len, c->cap_tiles);
+    if (n_positions > c->cap_tokens) return over("seq_positions", n_positions, c->cap_tokens);
+    // what the kernels rely on
+    if (indptr[0] != 0) return invalid("page_indptr must start at 0");
+    for (size_t r = 0; r < rows; ++r) {
+        if (indptr[r + 1] < indptr[r]) return invalid("page_indptr must be non-decreasing (row " + std::to_string(r) + ")");
+        if (last_len[r] < 1 || uint32_t(last_len[r]) > c->cfg.block_size_tokens)
+            return invalid("last_page_len[" + std::to_string(r) + "] = " + std::to_string(last_len[r]) +
+                           " outside 1..=" + std::to_string(c->cfg.block_size_tokens));
+        if (indptr[r + 1] == indptr[r]) return invalid("row " + std::to_string(r) + " has no KV blocks");
+    }
+    if (size_t(indptr[rows]) != indices_len)
+        return invalid("page_indptr ends at " + std::to_string(indptr[rows]) + " but page_indices has " +
+                       std::to_string(indices_len) + " entries");
+    for (size_t i = 0; i < indices_len; ++i)
+        if (indices[i] < 0 || uint32_t(indices[i]) >= c->cfg.num_kv_blocks)
+            return invalid("page_indices[" + std::to_string(i) + "] = " + std::to_string(indices[i]) +
+                           " outside the pool of " + std::to_string(c->cfg.num_kv_blocks) + " blocks");
+    for (size_t t = 0; t < tiles_len; ++t) {
+        const kriya_cta_work_tile& w = tiles[t];
+        if (w.request_idx >= rows) return invalid("cta_work_tiles[" + std::to_string(t) + "].request_idx out of range");
+        const uint32_t nb = uint32_t(indptr[w.request_idx + 1] - indptr[w.request_idx]);
+        if (w.kv_block_start > nb || w.kv_block_count > nb - w.kv_block_start)
+            return invalid("cta_work_tiles[" + std::to_string(t) + "] reaches outside its row");
+    }
+
+    cudaSetDevice(c->cfg.device);
+    const int cur = c->h_plan_cur;
+    c->h_plan_cur ^= 1;
+    KRIYA_CUDA_TRY(c, cudaEventSynchronize(c->h_plan_free[cur]));  // the copy that last read this buffer is done
+    uint8_t* h = c->h_plan[cur];
+    memcpy(h + c->off_indptr, indptr, indptr_len * 4);
+    memcpy(h + c->off_last_len, last_len, rows * 4);
+    if (n_positions) memcpy(h + c->off_positions, positions, n_positions * 4);
+    if (tiles_len) memcpy(h + c->off_tiles, tiles, tiles_len * sizeof(kriya_cta_work_tile));
+    if (indices_len) memcpy(h + c->off_indices, indices, indices_len * 4);
+    auto* work = reinterpret_cast<KriyaDecodeWork*>(h + c->off_work);
+    const uint32_t n_work =
+        build_work(indptr, uint32_t(rows), nullptr, nullptr, 2u * uint32_t(c->sm_count), 2u, work, c->cap_work);
+    if (n_work == UINT32_MAX) return invalid("plan needs more decode work items than the context holds");
+    const size_t used = c->off_indices + indices_len * 4;
+    KRIYA_CUDA_TRY(c, cudaMemcpyAsync(c->d_plan, h, used, cudaMemcpyHostToDevice, c->stream));
+    KRIYA_CUDA_TRY(c, cudaEventRecord(c->h_plan_free[cur], c->stream));
+
+    c->n_rows = uint32_t(rows);
+    c->n_indices = uint32_t(indices_len);
+    c->n_tiles = uint32_t(tiles_len);
+    c->n_positions = uint32_t(n_positions);
+    c->n_work = n_work;
+    c->row0_blocks = uint32_t(indptr[1] - indptr[0]);
+    c->row0_last_len = uint32_t(last_len[0]);
+    c->h_plan_last = h;
+    uint64_t tokens = 0;
+    for (size_t r = 0; r < rows; ++r)
+        tokens += uint64_t(indptr[r + 1] - indptr[r] - 1) * c->cfg.block_size_tokens + uint32_t(last_len[r]);
+    c->total_row_tokens = tokens;
+    c->plan_valid = true;
+    return KRIYA_CUDA_OK;
+}
+
+int32_t kriya_cuda_rope_kv_append(kriya_cuda_ctx* c, uint32_t layer, void* q, const void* k, const void* v,
+                                  const void* qw, const void* kw, uint32_t num_tokens,
+                                  const kriya_rope_kv_write_params* p) {
+    if (!c) return KRIYA_CUDA_INVALID_INPUT;
+    if (int32_t rc = check_layer(c, layer)) return rc;
+    if (int32_t rc = check_rope(c, p)) return rc;
+    if (!c->plan_valid) return c->fail(KRIYA_CUDA_INVALID_INPUT, "no plan uploaded");
+    if (num_tokens == 0) return c->fail(KRIYA_CUDA_INVALID_INPUT, "input_tokens must not be empty");  // enc:2165-2169
+    if (!q || !k || !v) return c->fail(KRIYA_CUDA_INVALID_INPUT, "q, k and v must not be null");
+    if (p->apply_qk_norm && (!qw || !kw)) return c->fail(KRIYA_CUDA_INVALID_INPUT, "apply_qk_norm needs both norm weights");
+    if (num_tokens > c->n_rows)
+        return c->fail(KRIYA_CUDA_INVALID_INPUT, "append of " + std::to_string(num_tokens) + " tokens but the plan has " +
+                                                     std::to_string(c->n_rows) + " rows");
+    if (num_tokens != c->n_positions)  // enc:2170-2176
+        return c->fail(KRIYA_CUDA_INVALID_INPUT, "input_tokens has " + std::to_string(num_tokens) +
+                                                     " entries but seq_positions has " + std::to_string(c->n_positions));
+    cudaSetDevice(c->cfg.device);
+    return launch_append(c, layer, q, k, v, qw, kw, num_tokens, 0, 0, p);
+}
+
+int32_t kriya_cuda_rope_kv_append_chunk(kriya_cuda_ctx* c, uint32_t layer, void* q, const void* k, const void* v,
+                                        const void* qw, const void* kw, uint32_t prefix_tokens, uint32_t num_tokens,
+                                        const kriya_rope_kv_write_params* p) {
+    if (!c) return KRIYA_CUDA_INVALID_INPUT;
+    if (int32_t rc = check_layer(c, layer)) return rc;
+    if (int32_t rc = check_rope(c, p)) return rc;
+    if (!c->plan_valid) return c->fail(KRIYA_CUDA_INVALID_INPUT, "no plan uploaded");
+    if (num_tokens == 0) return c->fail(KRIYA_CUDA_INVALID_INPUT, "input_tokens must not be empty");
+    if (!q || !k || !v) return c->fail(KRIYA_CUDA_INVALID_INPUT, "q, k and v must not be null");
+    if (p->apply_qk_norm && (!qw || !kw)) return c->fail(KRIYA_CUDA_INVALID_INPUT, "apply_qk_norm needs both norm weights");
+    if (num_tokens > c->cap_tokens) return c->fail(KRIYA_CUDA_INVALID_INPUT, "chunk exceeds max_query_tokens");
+    const uint64_t end = uint64_t(prefix_tokens) + num_tokens;
+    if (end > uint64_t(c->row0_blocks) * c->cfg.block_size_tokens)
+        return c->fail(KRIYA_CUDA_INVALID_INPUT, "chunk ends at token " + std::to_string(end) + " but row 0 of the plan holds " +
+                                                     std::to_string(c->row0_blocks) + " blocks");
+    cudaSetDevice(c->cfg.device);
+    return launch_append(c, layer, q, k, v, qw, kw, num_tokens, 1, prefix_tokens, p);
+}
+
+int32_t kriya_cuda_paged_gqa_decode(kriya_cuda_ctx* c, uint32_t layer, const void* q, void* out,
+                                    const kriya_bsr_gqa_params* p) {
+    if (!c) return KRIYA_CUDA_INVALID_INPUT;
+    if (int32_t rc = check_layer(c, layer)) return rc;
+    if (int32_t rc = check_gqa(c, p)) return rc;
+    if (!c->plan_valid) return c->fail(KRIYA_CUDA_INVALID_INPUT, "no plan uploaded");
+    if (!q || !out) return c->fail(KRIYA_CUDA_INVALID_INPUT, "q and out must not be null");
+    if (!kriya_decode_supported(c->cfg.head_dim, c->cfg.num_q_heads / c->cfg.num_kv_heads, c->cfg.num_kv_heads,
+                                c->cfg.block_size_tokens))
+        return c->fail(KRIYA_CUDA_UNSUPPORTED,
+                       "decode kernels cover head_dim 64/128, group size 1..8, up to 8 KV heads, 16-token blocks");
+    cudaSetDevice(c->cfg.device);
+    return launch_decode(c, layer, q, out, nullptr, nullptr, nullptr, c->off_work, c->n_work, p);
+}
+
+int32_t kriya_cuda_paged_gqa_decode_partial(kriya_cuda_ctx* c, uint32_t layer, const void* q, const uint32_t* blk_begin,
+                                            const uint32_t* blk_end, float* out_m, float* out_l, float* out_o,
+                                            const kriya_bsr_gqa_params* p) {
+    if (!c) return KRIYA_CUDA_INVALID_INPUT;
+    if (int32_t rc = check_layer(c, layer)) return rc;
+    if (int32_t rc = check_gqa(c, p)) return rc;
+    if (!c->plan_valid) return c->fail(KRIYA_CUDA_INVALID_INPUT, "no plan uploaded");
+    if (!q || !out_m || !out_l || !out_o) return c->fail(KRIYA_CUDA_INVALID_INPUT, "q and state outputs must not be null");
+    if (!kriya_decode_supported(c->cfg.head_dim, c->cfg.num_q_heads / c->cfg.num_kv_heads, c->cfg.num_kv_heads,
+                                c->cfg.block_size_tokens))
+        return c->fail(KRIYA_CUDA_UNSUPPORTED,
+                       "decode kernels cover head_dim 64/128, group size 1..8, up to 8 KV heads, 16-token blocks");
+    cudaSetDevice(c->cfg.device);
+    // work list for the requested ranges, staged behind the plan's own list
+    KRIYA_CUDA_TRY(c, cudaEventSynchronize(c->h_pairs_free));
+    const int32_t* indptr = reinterpret_cast<const int32_t*>(c->h_plan_last + c->off_indptr);
+    auto* work = reinterpret_cast<KriyaDecodeWork*>(c->h_plan_last + c->off_range);
+    const uint32_t n_work =
+        build_work(indptr, c->n_rows, blk_begin, blk_end, 2u * uint32_t(c->sm_count), 2u, work, c->cap_work);
+    if (n_work == UINT32_MAX) return c->fail(KRIYA_CUDA_INVALID_INPUT, "ranges need more work items than the context holds");
+    KRIYA_CUDA_TRY(c, cudaMemcpyAsync(c->d_plan + c->off_range, work, size_t(n_work) * sizeof(KriyaDecodeWork),
+                                      cudaMemcpyHostToDevice, c->stream));
+    KRIYA_CUDA_TRY(c, cudaEventRecord(c->h_pairs_free, c->stream));
+    return launch_decode(c, layer, q, nullptr, out_m, out_l, out_o, c->off_range, n_work, p);
+}
+
+int32_t kriya_cuda_merge_states(kriya_cuda_ctx* c, const float* m, const float* l, const float* o, uint32_t parts,
+                                uint32_t rows_times_heads, void* out) {
+    if (!c) return KRIYA_CUDA_INVALID_INPUT;
+    if (!m || !l || !o || !out || parts == 0) return c->fail(KRIYA_CUDA_INVALID_INPUT, "merge needs states, an output and parts >= 1");
+    cudaSetDevice(c->cfg.device);
+    KRIYA_CUDA_TRY(c, kriya_launch_merge_states(m, l, o, parts, rows_times_heads, c->cfg.head_dim, out, c->cfg.dtype, c->stream));
+    c->launches += 1;
+    return KRIYA_CUDA_OK;
+}
+
+int32_t kriya_cuda_paged_gqa_prefill(kriya_cuda_ctx* c, uint32_t layer, const void* q, void* out, uint32_t prefix_tokens,
+                                     uint32_t num_tokens, const kriya_bsr_gqa_params* p) {
+    if (!c) return KRIYA_CUDA_INVALID_INPUT;
+    if (int32_t rc = check_layer(c, layer)) return rc;
+    if (int32_t rc = check_gqa(c, p)) return rc;
+    if (!c->plan_valid) return c->fail(KRIYA_CUDA_INVALID_INPUT, "no plan uploaded");
+    if (!q || !out) return c->fail(KRIYA_CUDA_INVALID_INPUT, "q and out must not be null");
+    if (num_tokens == 0) return c->fail(KRIYA_CUDA_INVALID_INPUT, "input_tokens must not be empty");
+    if (num_tokens > c->cap_tokens) return c->fail(KRIYA_CUDA_INVALID_INPUT, "chunk exceeds max_query_tokens");
+    const uint64_t end = uint64_t(prefix_tokens) + num_tokens;
+    if (end > uint64_t(c->row0_blocks) * c->cfg.block_size_tokens)
+        return c->fail(KRIYA_CUDA_INVALID_INPUT, "chunk ends at token " + std::to_string(end) + " but row 0 of the plan holds " +
+                                                     std::to_string(c->row0_blocks) + " blocks");
+    if (!kriya_prefill_supported(c->cfg.head_dim, c->cfg.num_q_heads / c->cfg.num_kv_heads, c->cfg.block_size_tokens,
+                                 c->cfg.dtype))
+        return c->fail(KRIYA_CUDA_UNSUPPORTED, "prefill kernels cover head_dim 64/128 and 16-token blocks");
+    cudaSetDevice(c->cfg.device);
+    KriyaPrefillArgs a{};
+    a.q = q;
+    a.cache_k = c->layer_k(layer);
+    a.cache_v = c->layer_v(layer);
+    a.table = c->plan_dev<int32_t>(c->off_indices);
+    a.out = out;
+    a.status = c->d_status;
+    a.num_tokens = num_tokens;
+    a.prefix_tokens = prefix_tokens;
+    a.num_blocks = c->cfg.num_kv_blocks;
+    a.num_q_heads = c->cfg.num_q_heads;
+    a.num_kv_heads = c->cfg.num_kv_heads;
+    a.sm_scale = p->sm_scale;
+    a.logit_softcap = p->logit_softcap;
+    KRIYA_CUDA_TRY(c, kriya_launch_prefill(a, c->cfg.head_dim, c->cfg.block_size_tokens, c->cfg.dtype, c->max_smem_optin,
+                                           c->stream));
+    c->launches += 1;
+    return KRIYA_CUDA_OK;
+}
+
+int32_t kriya_cuda_kv_block_copy(kriya_cuda_ctx* c, const uint32_t* pairs, uint32_t n_pairs) {
+    if (!c) return KRIYA_CUDA_INVALID_INPUT;
+    if (n_pairs == 0) return KRIYA_CUDA_OK;
+    if (!pairs) return c->fail(KRIYA_CUDA_INVALID_INPUT, "pairs must not be null");
+    if (n_pairs > c->cap_pairs) return c->fail(KRIYA_CUDA_INVALID_INPUT, "more copy pairs than the context holds");
+    for (uint32_t i = 0; i < 2 * n_pairs; ++i)
+        if (pairs[i] >= c->cfg.num_kv_blocks)
+            return c->fail(KRIYA_CUDA_INVALID_INPUT, "copy pair " + std::to_string(i / 2) + " names block " +
+                                                         std::to_string(pairs[i]) + " outside the pool");
+    cudaSetDevice(c->cfg.device);
+    KRIYA_CUDA_TRY(c, cudaEventSynchronize(c->h_pairs_free));
+    memcpy(c->h_pairs, pairs, size_t(n_pairs) * 2 * sizeof(uint32_t));
+    KRIYA_CUDA_TRY(c, cudaMemcpyAsync(c->d_pairs, c->h_pairs, size_t(n_pairs) * 2 * sizeof(uint32_t),
+                                      cudaMemcpyHostToDevice, c->stream));
+    KRIYA_CUDA_TRY(c, cudaEventRecord(c->h_pairs_free, c->stream));
+    // Pairs apply in order.  A launch copies its pairs concurrently, so a batch ends where a pair reads or
+    // rewrites a block an earlier pair of the batch wrote.
+    uint32_t start = 0;
+    std::vector<uint32_t> written;
+    for (uint32_t i = 0; i <= n_pairs; ++i) {
+        bool cut = i == n_pairs;
+        if (!cut) {
+            const uint32_t src = pairs[2 * i], dst = pairs[2 * i + 1];
+            for (uint32_t wv : written)
+                if (wv == src || wv == dst) {
+                    cut = true;
+                    break;
+                }
+        }
+        if (cut && i > start) {
+            KRIYA_CUDA_TRY(c, kriya_launch_block_copy(c->pool_k, c->pool_v, c->layer_stride_bytes, c->cfg.num_layers,
+                                                      c->block_bytes, c->d_pairs + 2 * size_t(start), i - start,
+                                                      c->sm_count, c->stream));
+            c->launches += 1;
+            start = i;
+            written.clear();
+        }
+        if (i < n_pairs) written.push_back(pairs[2 * i + 1]);
+    }
+    return KRIYA_CUDA_OK;
+}
+
+int32_t kriya_cuda_kv_slot_write(kriya_cuda_ctx* c, uint32_t layer, const void* stage_k, const void* stage_v,
+                                 const uint32_t* triples, uint32_t n) {
+    if (!c) return KRIYA_CUDA_INVALID_INPUT;
+    if (int32_t rc = check_layer(c, layer)) return rc;
+    if (n == 0) return KRIYA_CUDA_OK;
+    if (!stage_k || !stage_v || !triples) return c->fail(KRIYA_CUDA_INVALID_INPUT, "staging buffers and triples must not be null");
+    if (n > c->cap_pairs) return c->fail(KRIYA_CUDA_INVALID_INPUT, "more slot writes than the context holds");
+    for (uint32_t i = 0; i < n; ++i)
+        if (triples[3 * i + 1] >= c->cfg.num_kv_blocks || triples[3 * i + 2] >= c->cfg.block_size_tokens)
+            return c->fail(KRIYA_CUDA_INVALID_INPUT, "slot write " + std::to_string(i) + " is outside the pool");
+    cudaSetDevice(c->cfg.device);
+    KRIYA_CUDA_TRY(c, cudaEventSynchronize(c->h_pairs_free));
+    memcpy(c->h_pairs, triples, size_t(n) * 3 * sizeof(uint32_t));
+    KRIYA_CUDA_TRY(c, cudaMemcpyAsync(c->d_pairs, c->h_pairs, size_t(n) * 3 * sizeof(uint32_t), cudaMemcpyHostToDevice,
+                                      c->stream));
+    KRIYA_CUDA_TRY(c, cudaEventRecord(c->h_pairs_free, c->stream));
+    KRIYA_CUDA_TRY(c, kriya_launch_slot_write(c->layer_k(layer), c->layer_v(layer), stage_k, stage_v,
+                                              size_t(c->cfg.num_kv_heads) * c->cfg.head_dim * 2, c->cfg.block_size_tokens,
+                                              c->d_pairs, n, c->cfg.num_kv_blocks, c->d_status, c->stream));
+    c->launches += 1;
+    return KRIYA_CUDA_OK;
+}
+
+int32_t kriya_cuda_decode_layer_host(kriya_cuda_ctx* c, uint32_t layer, const void* q_host, const void* k_host,
+                                     const void* v_host, void* out_host, uint32_t rows,
+                                     const kriya_rope_kv_write_params* rope, const kriya_bsr_gqa_params* gqa) {
+    if (!c) return KRIYA_CUDA_INVALID_INPUT;
+    if (!q_host || !k_host || !v_host || !out_host) return c->fail(KRIYA_CUDA_INVALID_INPUT, "host buffers must not be null");
+    if (!c->plan_valid) return c->fail(KRIYA_CUDA_INVALID_INPUT, "no plan uploaded");
+    if (rows == 0 || rows != c->n_rows) return c->fail(KRIYA_CUDA_INVALID_INPUT, "rows must equal the plan's row count");
+    cudaSetDevice(c->cfg.device);
+    const size_t qb = size_t(rows) * c->cfg.num_q_heads * c->cfg.head_dim * 2;
+    const size_t kb = size_t(rows) * c->cfg.num_kv_heads * c->cfg.head_dim * 2;
+    uint8_t* dq = c->d_act;
+    uint8_t* dk = dq + qb;
+    uint8_t* dv = dk + kb;
+    uint8_t* dout = dv + kb;
+    KRIYA_CUDA_TRY(c, cudaMemcpyAsync(dq, q_host, qb, cudaMemcpyHostToDevice, c->stream));
+    KRIYA_CUDA_TRY(c, cudaMemcpyAsync(dk, k_host, kb, cudaMemcpyHostToDevice, c->stream));
+    KRIYA_CUDA_TRY(c, cudaMemcpyAsync(dv, v_host, kb, cudaMemcpyHostToDevice, c->stream));
+    if (int32_t rc = kriya_cuda_rope_kv_append(c, layer, dq, dk, dv, nullptr, nullptr, rows, rope)) return rc;
+    if (int32_t rc = kriya_cuda_paged_gqa_decode(c, layer, dq, dout, gqa)) return rc;
+    KRIYA_CUDA_TRY(c, cudaMemcpyAsync(out_host, dout, qb, cudaMemcpyDeviceToHost, c->stream));
+    return kriya_cuda_sync(c, 0);
+}
+
+}  // extern "C"

@@ -1,0 +1,178 @@
+// Internal declarations shared by the translation units of libkriya_cuda.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+
+#include "kriya_cuda.h"
+
+// One unit of decode work: logical blocks [blk_begin, blk_end) of plan row `req`.
+// `slot` is the index of this unit's partial state in the scratch arrays; the units of one row
+// occupy slots [first_slot, first_slot + n_parts).
+struct KriyaDecodeWork {
+    uint32_t req;
+    uint32_t blk_begin;
+    uint32_t blk_end;
+    uint32_t slot;
+    uint32_t first_slot;
+    uint32_t n_parts;
+    uint32_t _pad0;
+    uint32_t _pad1;
+};
+static_assert(sizeof(KriyaDecodeWork) == 32, "work item is 32 bytes");
+
+// Device status word values written by kernels instead of trapping.
+enum : uint32_t {
+    KRIYA_DEV_OK = 0,
+    KRIYA_DEV_BAD_BLOCK_INDEX = 1,  // a page index outside the pool reached a kernel
+    KRIYA_DEV_WAIT_EXPIRED = 2,     // a bounded mbarrier wait gave up
+    KRIYA_DEV_BAD_SLOT = 3          // append slot outside its block
+};
+
+struct kriya_cuda_ctx {
+    kriya_cuda_config cfg{};
+    cudaStream_t stream = nullptr;
+    cudaStream_t copy_stream = nullptr;
+    int sm_count = 0;
+    int max_smem_optin = 0;
+
+    // KV pools, all layers: layer l at l * layer_stride_bytes
+    uint8_t* pool_k = nullptr;
+    uint8_t* pool_v = nullptr;
+    size_t layer_stride_bytes = 0;
+    size_t block_bytes = 0;  // block_size * Hkv * D * 2
+
+    float* rope_table = nullptr;  // [rope_max_seq_len][rotary_dim/2][2]
+    uint32_t rope_rotary_dim = 0;
+
+    // plan: one pinned host staging area, one device image, sub-arrays at fixed offsets
+    uint8_t* h_plan[2] = {nullptr, nullptr};
+    cudaEvent_t h_plan_free[2] = {nullptr, nullptr};
+    int h_plan_cur = 0;
+    uint8_t* d_plan = nullptr;
+    size_t plan_bytes = 0;
+    size_t off_indptr = 0, off_indices = 0, off_last_len = 0, off_tiles = 0, off_positions = 0, off_work = 0,
+           off_range = 0;
+    uint32_t cap_rows = 0, cap_indices = 0, cap_tiles = 0, cap_tokens = 0, cap_work = 0;
+    // current plan (host copy of the sizes and of what later calls need)
+    bool plan_valid = false;
+    uint32_t n_rows = 0, n_indices = 0, n_tiles = 0, n_positions = 0, n_work = 0;
+    uint32_t row0_blocks = 0, row0_last_len = 0;
+    uint64_t total_row_tokens = 0;
+    uint8_t* h_plan_last = nullptr;  // staging buffer holding the current plan (for partial-range rebuilds)
+
+    // split-KV scratch
+    float* part_o = nullptr;        // [cap_work][Hq][D]
+    float* part_ml = nullptr;       // [cap_work][Hq][2]
+    uint32_t* part_counter = nullptr;  // [cap_rows * head_groups]
+    uint32_t* d_status = nullptr;   // device status word
+    uint32_t* h_status = nullptr;   // pinned mirror
+
+    // staging for host-buffer entry points
+    uint8_t* h_act = nullptr;  // pinned
+    uint8_t* d_act = nullptr;
+    size_t act_bytes = 0;
+    uint32_t* d_pairs = nullptr;  // copy pairs / slot triples
+    uint32_t* h_pairs = nullptr;
+    uint32_t cap_pairs = 0;
+    cudaEvent_t h_pairs_free = nullptr;
+
+    uint64_t launches = 0;
+    std::string last_error;
+
+    int32_t fail(int32_t code, const std::string& msg) {
+        last_error = msg;
+        return code;
+    }
+    template <typename T>
+    T* plan_dev(size_t off) const {
+        return reinterpret_cast<T*>(d_plan + off);
+    }
+    uint8_t* layer_k(uint32_t layer) const { return pool_k + size_t(layer) * layer_stride_bytes; }
+    uint8_t* layer_v(uint32_t layer) const { return pool_v + size_t(layer) * layer_stride_bytes; }
+};
+
+// ---- kernel launchers (one per translation unit) ---------------------------------------------
+
+struct KriyaAppendArgs {
+    void* q_inout;
+    const void* k_in;
+    const void* v_in;
+    const void* q_norm_w;
+    const void* k_norm_w;
+    void* cache_k;
+    void* cache_v;
+    const int32_t* indptr;
+    const int32_t* indices;
+    const int32_t* last_len;
+    const uint32_t* positions;
+    const float* table;  // may be null
+    uint32_t* status;
+    uint32_t num_tokens;
+    uint32_t num_blocks;
+    // chunk mode: token i of row 0 at absolute position prefix + i (plan rows are not per token)
+    uint32_t chunk_mode;
+    uint32_t prefix_tokens;
+    kriya_rope_kv_write_params p;
+};
+cudaError_t kriya_launch_append(const KriyaAppendArgs& a, uint32_t dtype, cudaStream_t s);
+
+struct KriyaDecodeArgs {
+    const void* q;          // [rows][Hq][D]
+    const void* cache_k;    // layer base
+    const void* cache_v;
+    const int32_t* indptr;
+    const int32_t* indices;
+    const int32_t* last_len;
+    const KriyaDecodeWork* work;
+    void* out;              // [rows][Hq][D] 16-bit (normal mode)
+    float* part_o;          // scratch
+    float* part_ml;
+    uint32_t* counters;
+    // partial mode: write merged (m, l, o) per row instead of the normalised output
+    float* state_m;
+    float* state_l;
+    float* state_o;
+    uint32_t* status;
+    uint32_t n_work;
+    uint32_t num_blocks;
+    uint32_t num_q_heads;
+    uint32_t num_kv_heads;
+    float sm_scale;
+    float logit_softcap;
+};
+// Returns cudaErrorInvalidValue for shapes the kernels are not instantiated for.
+cudaError_t kriya_launch_decode(const KriyaDecodeArgs& a, uint32_t head_dim, uint32_t block_size, uint32_t dtype,
+                                int max_smem_optin, cudaStream_t s);
+bool kriya_decode_supported(uint32_t head_dim, uint32_t group, uint32_t num_kv_heads, uint32_t block_size);
+
+cudaError_t kriya_launch_merge_states(const float* m, const float* l, const float* o, uint32_t parts, uint32_t rows,
+                                      uint32_t D, void* out, uint32_t dtype, cudaStream_t s);
+
+cudaError_t kriya_launch_block_copy(uint8_t* pool_k, uint8_t* pool_v, size_t layer_stride_bytes, uint32_t num_layers,
+                                    size_t block_bytes, const uint32_t* pairs_dev, uint32_t n_pairs, int sm_count,
+                                    cudaStream_t s);
+cudaError_t kriya_launch_slot_write(uint8_t* cache_k, uint8_t* cache_v, const void* stage_k, const void* stage_v,
+                                    size_t row_bytes, uint32_t block_size, const uint32_t* triples_dev, uint32_t n,
+                                    uint32_t num_blocks, uint32_t* status, cudaStream_t s);
+
+struct KriyaPrefillArgs {
+    const void* q;        // [T][Hq][D]
+    const void* cache_k;  // layer base
+    const void* cache_v;
+    const int32_t* table; // row 0 of the plan
+    void* out;            // [T][Hq][D]
+    uint32_t* status;
+    uint32_t num_tokens;
+    uint32_t prefix_tokens;
+    uint32_t num_blocks;
+    uint32_t num_q_heads;
+    uint32_t num_kv_heads;
+    float sm_scale;
+    float logit_softcap;
+};
+cudaError_t kriya_launch_prefill(const KriyaPrefillArgs& a, uint32_t head_dim, uint32_t block_size, uint32_t dtype,
+                                 int max_smem_optin, cudaStream_t s);
+bool kriya_prefill_supported(uint32_t head_dim, uint32_t group, uint32_t block_size, uint32_t dtype);

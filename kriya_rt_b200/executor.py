@@ -1,0 +1,173 @@
+"""Host-side mirror of the attention / KV ops of the reference executor over `libkriya_cuda.so`.
+
+`CudaExecutor` stands where `MetalExecutor` (crates/kriya-backend-metal/src/encoder.rs) stands in the
+reference: it owns the KV pool and the per-step plan buffers and exposes the ops of the hot path.
+Every method is one call through the C ABI of `include/kriya_cuda.h`; device arrays are passed as raw
+pointers (anything with `.data_ptr()` or an int), host arrays as numpy arrays.  There is no fallback:
+a missing library or a missing GPU raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional, Sequence
+
+import numpy as np
+
+from . import _native as N
+from ._native import BsrGqaParams, RopeKvWriteParams
+
+DTYPE_BF16, DTYPE_FP16 = 0, 1
+
+
+class CudaBackendError(RuntimeError):
+    """MetalError (encoder.rs:32-54) for this backend; `.code` is the kriya_cuda_status."""
+
+    def __init__(self, code: int, message: str):
+        super().__init__(f"[{code}] {message}")
+        self.code = code
+
+
+class InvalidExecutionInput(CudaBackendError):
+    pass
+
+
+def _ptr(x) -> Optional[int]:
+    if x is None:
+        return None
+    if hasattr(x, "data_ptr"):
+        return int(x.data_ptr())
+    if isinstance(x, np.ndarray):
+        return int(x.ctypes.data)
+    return int(x)
+
+
+class CudaExecutor:
+    def __init__(self, *, num_layers: int, num_kv_blocks: int, block_size_tokens: int, num_q_heads: int,
+                 num_kv_heads: int, head_dim: int, dtype: int = DTYPE_BF16, device: int = 0, rotary_dim: int = 0,
+                 rope_theta: float = 10000.0, rope_max_seq_len: int = 0, max_batch_rows: int = 0,
+                 max_page_indices: int = 0, max_tiles: int = 0, max_query_tokens: int = 0):
+        self._lib = N.cuda_lib()
+        self.cfg = N.CudaConfig(device, num_layers, num_kv_blocks, block_size_tokens, num_q_heads, num_kv_heads,
+                                head_dim, dtype, rotary_dim, rope_theta, rope_max_seq_len, max_batch_rows,
+                                max_page_indices, max_tiles, max_query_tokens)
+        h = C.c_void_p()
+        rc = self._lib.kriya_cuda_ctx_create(C.byref(self.cfg), C.byref(h))
+        if rc != 0:
+            raise self._error(rc, None)
+        self._h = h
+        self.num_layers, self.num_kv_blocks, self.block_size_tokens = num_layers, num_kv_blocks, block_size_tokens
+        self.num_q_heads, self.num_kv_heads, self.head_dim, self.dtype = num_q_heads, num_kv_heads, head_dim, dtype
+        self.rotary_dim = rotary_dim or head_dim
+        self.rope_theta = rope_theta
+        self.rope_max_seq_len = rope_max_seq_len or 4096
+
+    def close(self) -> None:
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            self._lib.kriya_cuda_ctx_destroy(h)
+
+    def __del__(self):
+        self.close()
+
+    def _error(self, rc: int, h) -> CudaBackendError:
+        msg = self._lib.kriya_cuda_last_error(h)
+        text = msg.decode() if msg else ""
+        return (InvalidExecutionInput if rc == -2 else CudaBackendError)(rc, text)
+
+    def _check(self, rc: int) -> None:
+        if rc != 0:
+            raise self._error(rc, self._h)
+
+    # ---- parameter blocks as the reference fills them (encoder.rs:4953-4966, 4990-4999) -------------
+    def rope_params(self, *, apply_qk_norm: bool = False, rms_eps: float = 1e-6, has_table: bool = True,
+                    rope_theta: Optional[float] = None, rotary_dim: Optional[int] = None) -> RopeKvWriteParams:
+        return RopeKvWriteParams(self.num_q_heads, self.num_kv_heads, self.head_dim,
+                                 self.rotary_dim if rotary_dim is None else rotary_dim, self.block_size_tokens,
+                                 int(apply_qk_norm), rms_eps, self.rope_theta if rope_theta is None else rope_theta,
+                                 self.rope_max_seq_len, int(has_table), 0, 0)
+
+    def gqa_params(self, *, max_query_tokens: int = 1, sm_scale: Optional[float] = None,
+                   logit_softcap: float = 0.0) -> BsrGqaParams:
+        scale = float(np.float32(1.0) / np.sqrt(np.float32(self.head_dim))) if sm_scale is None else sm_scale
+        return BsrGqaParams(self.num_q_heads, self.num_kv_heads, self.head_dim, self.block_size_tokens, 16,
+                            max_query_tokens, scale, logit_softcap)
+
+    # ---- context accessors -----------------------------------------------------------------------
+    def layer_kv_byte_offset(self, layer: int) -> int:
+        return int(self._lib.kriya_cuda_layer_kv_byte_offset(self._h, layer))
+
+    def kv_pool_ptrs(self, layer: int):
+        k, v = C.c_void_p(), C.c_void_p()
+        self._check(self._lib.kriya_cuda_kv_pool_ptrs(self._h, layer, C.byref(k), C.byref(v)))
+        return k.value, v.value
+
+    @property
+    def stream_ptr(self) -> int:
+        return int(self._lib.kriya_cuda_stream(self._h))
+
+    @property
+    def launch_count(self) -> int:
+        return int(self._lib.kriya_cuda_launch_count(self._h))
+
+    def sync(self, timeout_ms: int = 0) -> None:
+        self._check(self._lib.kriya_cuda_sync(self._h, timeout_ms))
+
+    # ---- plan ------------------------------------------------------------------------------------
+    def plan_upload(self, page_indptr, page_indices, last_page_len, cta_work_tiles=None, seq_positions=None) -> None:
+        indptr = np.ascontiguousarray(page_indptr, dtype=np.int32)
+        indices = np.ascontiguousarray(page_indices, dtype=np.int32)
+        last = np.ascontiguousarray(last_page_len, dtype=np.int32)
+        tiles = np.zeros((0, 4), np.uint32) if cta_work_tiles is None else np.ascontiguousarray(cta_work_tiles, np.uint32)
+        pos = np.zeros(0, np.uint32) if seq_positions is None else np.ascontiguousarray(seq_positions, np.uint32)
+        self._check(self._lib.kriya_cuda_plan_upload(
+            self._h, indptr.ctypes.data, indptr.size, indices.ctypes.data, indices.size, last.ctypes.data, last.size,
+            tiles.ctypes.data, tiles.shape[0], pos.ctypes.data, pos.size))
+
+    def upload_schedule_plan(self, plan, seq_positions=None) -> None:
+        """`plan` is a FlashInferSchedulePlan as the kv manager builds it."""
+        self.plan_upload(plan.page_indptr, plan.page_indices, plan.last_page_len, plan.cta_work_tiles, seq_positions)
+
+    # ---- ops -------------------------------------------------------------------------------------
+    def rope_kv_append(self, layer: int, q_inout, k_in, v_in, num_tokens: int, params: RopeKvWriteParams,
+                       q_norm_w=None, k_norm_w=None) -> None:
+        self._check(self._lib.kriya_cuda_rope_kv_append(self._h, layer, _ptr(q_inout), _ptr(k_in), _ptr(v_in),
+                                                        _ptr(q_norm_w), _ptr(k_norm_w), num_tokens, C.byref(params)))
+
+    def rope_kv_append_chunk(self, layer: int, q_inout, k_in, v_in, prefix_tokens: int, num_tokens: int,
+                             params: RopeKvWriteParams, q_norm_w=None, k_norm_w=None) -> None:
+        self._check(self._lib.kriya_cuda_rope_kv_append_chunk(
+            self._h, layer, _ptr(q_inout), _ptr(k_in), _ptr(v_in), _ptr(q_norm_w), _ptr(k_norm_w), prefix_tokens,
+            num_tokens, C.byref(params)))
+
+    def paged_gqa_decode(self, layer: int, q, out, params: BsrGqaParams) -> None:
+        self._check(self._lib.kriya_cuda_paged_gqa_decode(self._h, layer, _ptr(q), _ptr(out), C.byref(params)))
+
+    def paged_gqa_decode_partial(self, layer: int, q, blk_begin, blk_end, out_m, out_l, out_o,
+                                 params: BsrGqaParams) -> None:
+        b = None if blk_begin is None else np.ascontiguousarray(blk_begin, np.uint32)
+        e = None if blk_end is None else np.ascontiguousarray(blk_end, np.uint32)
+        self._check(self._lib.kriya_cuda_paged_gqa_decode_partial(
+            self._h, layer, _ptr(q), _ptr(b), _ptr(e), _ptr(out_m), _ptr(out_l), _ptr(out_o), C.byref(params)))
+
+    def merge_states(self, m, l, o, parts: int, rows_times_heads: int, out) -> None:
+        self._check(self._lib.kriya_cuda_merge_states(self._h, _ptr(m), _ptr(l), _ptr(o), parts, rows_times_heads,
+                                                      _ptr(out)))
+
+    def paged_gqa_prefill(self, layer: int, q, out, prefix_tokens: int, num_tokens: int, params: BsrGqaParams) -> None:
+        self._check(self._lib.kriya_cuda_paged_gqa_prefill(self._h, layer, _ptr(q), _ptr(out), prefix_tokens,
+                                                           num_tokens, C.byref(params)))
+
+    def kv_block_copy(self, pairs: Sequence) -> None:
+        arr = np.ascontiguousarray(pairs, dtype=np.uint32).reshape(-1, 2)
+        self._check(self._lib.kriya_cuda_kv_block_copy(self._h, arr.ctypes.data, arr.shape[0]))
+
+    def kv_slot_write(self, layer: int, stage_k, stage_v, triples: Sequence) -> None:
+        arr = np.ascontiguousarray(triples, dtype=np.uint32).reshape(-1, 3)
+        self._check(self._lib.kriya_cuda_kv_slot_write(self._h, layer, _ptr(stage_k), _ptr(stage_v), arr.ctypes.data,
+                                                       arr.shape[0]))
+
+    def decode_layer_host(self, layer: int, q_host: np.ndarray, k_host: np.ndarray, v_host: np.ndarray,
+                          out_host: np.ndarray, rope: RopeKvWriteParams, gqa: BsrGqaParams) -> None:
+        rows = q_host.shape[0]
+        self._check(self._lib.kriya_cuda_decode_layer_host(self._h, layer, _ptr(q_host), _ptr(k_host), _ptr(v_host),
+                                                           _ptr(out_host), rows, C.byref(rope), C.byref(gqa)))
