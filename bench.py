@@ -1,0 +1,399 @@
+"""Benchmark of the paged KV-cache decode path (append + paged GQA decode, every layer, per decode step).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (N=1): Qwen2.5-3B attention shape (16 query heads, 2 KV heads, head_dim 128, bf16 KV, 36 layers),
+batch 32, context lengths uniform in [512, 4096], 16-token blocks in a 16384-block pool per layer with seeded
+random block tables; Q/K/V activations N(0,1).  One "step" = one decode step: for each of the 36 layers the
+fused RoPE + KV append of 32 new tokens followed by paged GQA decode attention; contexts grow by one token
+per step.  Metric: decode tokens per second (batch / step time), with the KV-read bandwidth it implies.
+
+With N > 1 (one process per GPU under torch.distributed.run) every rank runs its own batch of 32 sequences
+over its own pool (sequences shard across GPUs, no data-path collective): weak scaling, value = all ranks'
+tokens over the slowest rank's time.
+
+`--impl reference` times the CPU restatement of the reference's path (oracle/, OpenMP over all host cores)
+on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+from kriya_rt_b200 import workloads as W  # noqa: E402
+
+METRIC = "paged_gqa_decode_tokens_per_s"
+UNIT = "tokens/s"
+SHAPE = W.QWEN25_3B
+BATCH = 32
+NUM_BLOCKS = 16384
+CTX_LO, CTX_HI = 512, 4096
+WORKLOAD = ("qwen2.5-3b attention decode: Hq16 Hkv2 D128 bf16, 36 layers, batch 32/GPU, ctx U[512,4096], "
+            "16-token blocks, 16384-block pool/layer, append+attention per layer per step")
+
+
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return json.loads(p.read_text()), "measured"
+        except Exception:
+            pass
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}, "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons during the timed region."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.lines = []
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._pump, daemon=True)
+        self.thread.start()
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()  # the exact process started above
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            pass
+        sm, mx, reasons = [], None, set()
+        for ln in self.lines:
+            parts = [p.strip() for p in ln.split(",")]
+            if len(parts) < 8:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx = float(parts[1])
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), parts[4:8]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def contexts_for_rank(rank: int) -> np.ndarray:
+    return W.config2_contexts(seed_tables=2002 + 17 * rank, batch=BATCH, lo=CTX_LO, hi=CTX_HI)
+
+
+# ---------------------------------------------------------------------------------------------------
+# CPU arm: the oracle port on a bounded sample
+# ---------------------------------------------------------------------------------------------------
+
+
+def cpu_sample(layers_in_sample: int, repeats: int, seed: int = 1002):
+    """Times `layers_in_sample` layers of one decode step (append + whole-row decode per layer) on the host
+    cores with the C oracle.  Returns (seconds per sample, cores, description)."""
+    from oracle import c_oracle as O
+
+    ctx = contexts_for_rank(0)
+    batch = W.make_decode_batch(SHAPE, ctx, NUM_BLOCKS, seed=2002)
+    rng = np.random.default_rng(seed)
+    Hq, Hkv, D = SHAPE.num_q_heads, SHAPE.num_kv_heads, SHAPE.head_dim
+    # only the blocks the tables name need real data; the pool is allocated once and shared by the layers
+    ck = np.zeros((NUM_BLOCKS, 16, Hkv, D), np.uint16)
+    cv = np.zeros((NUM_BLOCKS, 16, Hkv, D), np.uint16)
+    used = batch.page_indices
+    ck[used] = W.normal16(rng, (used.size, 16, Hkv, D), W.BF16)
+    cv[used] = W.normal16(rng, (used.size, 16, Hkv, D), W.BF16)
+    q = W.normal16(rng, (BATCH, Hq, D), W.BF16)
+    k = W.normal16(rng, (BATCH, Hkv, D), W.BF16)
+    v = W.normal16(rng, (BATCH, Hkv, D), W.BF16)
+    rp = O.RopeParams(Hq, Hkv, D, D, 16, 0, 1e-6, SHAPE.rope_theta, 8192, 1, 0, 0)
+    gp = O.GqaParams(Hq, Hkv, D, 16, 16, 1, float(np.float32(1.0) / np.sqrt(np.float32(D))), 0.0)
+    table = O.rope_table(8192, D, SHAPE.rope_theta)
+    cores = O.num_threads()
+
+    def one_sample():
+        for _ in range(layers_in_sample):
+            qq = q.copy()
+            O.rope_kv_append(qq, k, v, ck, cv, batch.page_indptr, batch.page_indices, batch.last_page_len,
+                             batch.positions, rp, W.BF16, table=table)
+            O.decode(qq, ck, cv, batch.page_indptr, batch.page_indices, batch.last_page_len, gp, W.BF16)
+
+    one_sample()  # warm caches / OpenMP pool
+    times = []
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        one_sample()
+        times.append(time.perf_counter() - t0)
+    desc = (f"{layers_in_sample} of {SHAPE.num_layers} layers of one decode step (batch {BATCH}, "
+            f"{batch.attended_tokens} attended tokens/layer), scaled by {SHAPE.num_layers}/{layers_in_sample}")
+    return float(np.median(times)), cores, desc
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    # size the sample from one layer so that warmup + steps stay within a few minutes
+    t1, cores, _ = cpu_sample(1, 1)
+    budget_s = 150.0
+    per_step_budget = budget_s / max(args.steps + args.warmup, 1)
+    layers = int(max(1, min(SHAPE.num_layers, per_step_budget / max(t1, 1e-6))))
+    from oracle import c_oracle as O  # noqa: F401
+
+    times = []
+    for i in range(args.warmup + args.steps):
+        t, cores, desc = cpu_sample(layers, 1, seed=1002 + i)
+        if i >= args.warmup:
+            times.append(t)
+    step_s = float(np.mean(times)) * SHAPE.num_layers / layers
+    value = BATCH / step_s
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": step_s * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "note": "CPU restatement of the reference path (the reference is Rust + Metal "
+                   "and cannot run here); rank 0 host cores only"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": desc},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+# ---------------------------------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------------------------------
+
+
+def run_gpu_arm(args):
+    import torch
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the CUDA path has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    from kriya_rt_b200.executor import CudaExecutor
+    from kriya_rt_b200.kv import PagedKvCacheManager
+
+    L, Hq, Hkv, D = SHAPE.num_layers, SHAPE.num_q_heads, SHAPE.num_kv_heads, SHAPE.head_dim
+    total_steps = args.warmup + args.steps
+    ex = CudaExecutor(num_layers=L, num_kv_blocks=NUM_BLOCKS, block_size_tokens=16, num_q_heads=Hq, num_kv_heads=Hkv,
+                      head_dim=D, dtype=W.BF16, device=local_rank, rope_theta=SHAPE.rope_theta, rope_max_seq_len=8192,
+                      max_batch_rows=64, max_page_indices=NUM_BLOCKS, max_tiles=4096, max_query_tokens=64)
+    stream = torch.cuda.ExternalStream(ex.stream_ptr, device=torch.device("cuda", local_rank))
+
+    # KV pool: N(0,1) in every block of every layer (bf16), generated on the device
+    gen = torch.Generator(device="cuda").manual_seed(1002 + rank)
+    for layer in range(L):
+        kview, vview = ex.layer_cache_views(layer)
+        for view in (kview, vview):
+            flat = view.view(-1)
+            chunk = 1 << 25
+            for s in range(0, flat.numel(), chunk):
+                n = min(chunk, flat.numel() - s)
+                flat[s:s + n] = torch.randn(n, device="cuda", generator=gen).to(torch.bfloat16).view(torch.int16)
+    # activations for all layers, resident in HBM (one buffer set reused every step)
+    q = torch.randn(L, BATCH, Hq, D, device="cuda", generator=gen).to(torch.bfloat16).view(torch.int16)
+    k = torch.randn(L, BATCH, Hkv, D, device="cuda", generator=gen).to(torch.bfloat16).view(torch.int16)
+    v = torch.randn(L, BATCH, Hkv, D, device="cuda", generator=gen).to(torch.bfloat16).view(torch.int16)
+    out = torch.zeros_like(q)
+    torch.cuda.synchronize()
+
+    ctx0 = contexts_for_rank(rank)
+    rp = ex.rope_params()
+    gp = ex.gqa_params()
+
+    # ---- leg 1: device-resident throughput (`value`) -------------------------------------------------
+    # Bookkeeping runs in the compiled manager exactly as a scheduler would drive it: one append_token_slot
+    # per sequence, then build_schedule_plan, every step.
+    def fresh_manager():
+        mgr = PagedKvCacheManager(NUM_BLOCKS, 0, 16)
+        rng = np.random.default_rng(2002 + 17 * rank)
+        # a seeded shuffle of the free list: allocate every block once in random order and free in that order
+        order = rng.permutation(NUM_BLOCKS)
+        ids = [mgr.gpu_allocator.allocate_block() for _ in range(NUM_BLOCKS)]
+        for b in order:
+            mgr.gpu_allocator.free_block(int(ids[b]))
+        for i, c in enumerate(ctx0):
+            mgr.allocate_sequence(i, (np.arange(int(c), dtype=np.uint32) + np.uint32(100000 * (i + 1))))
+        return mgr
+
+    seq_ids = list(range(BATCH))
+
+    def step_plan(mgr, t):
+        for s in seq_ids:
+            mgr.append_token_slot(s)
+        plan = mgr.build_schedule_plan(seq_ids, 8)
+        positions = (ctx0 + t).astype(np.uint32)
+        return plan, positions
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+
+    mgr = fresh_manager()
+    attended = []
+    ex.timing_enable(False)
+    for t in range(args.warmup):
+        plan, pos = step_plan(mgr, t)
+        ex.upload_schedule_plan(plan, pos)
+        ex.decode_step(q, k, v, out, BATCH, rp, gp)
+    ex.sync()
+    barrier()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    launches0 = ex.launch_count
+    ex.timing_enable(True)
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record(stream)
+    for t in range(args.warmup, total_steps):
+        plan, pos = step_plan(mgr, t)
+        attended.append(int((ctx0 + t + 1).sum()))
+        ex.upload_schedule_plan(plan, pos)
+        ex.decode_step(q, k, v, out, BATCH, rp, gp)
+    ev1.record(stream)
+    ex.sync()
+    torch.cuda.synchronize()
+    barrier()
+    clocks = sampler.stop()
+    elapsed_ms = ev0.elapsed_time(ev1)
+    n_dec, ms_dec = ex.timing_read(0)
+    n_app, ms_app = ex.timing_read(1)
+    ex.timing_enable(False)
+    gpu_launches = ex.launch_count - launches0
+
+    # ---- leg 2: end to end through host buffers ---------------------------------------------------------
+    qh = torch.empty(L, BATCH, Hq, D, dtype=torch.int16).pin_memory()
+    kh = torch.empty(L, BATCH, Hkv, D, dtype=torch.int16).pin_memory()
+    vh = torch.empty(L, BATCH, Hkv, D, dtype=torch.int16).pin_memory()
+    oh = torch.empty(L, BATCH, Hq, D, dtype=torch.int16).pin_memory()
+    qh.copy_(q.cpu()); kh.copy_(k.cpu()); vh.copy_(v.cpu())
+    mgr2 = fresh_manager()
+    e2e_steps = args.steps
+    plan_bytes = 0
+    for t in range(args.warmup):
+        plan, pos = step_plan(mgr2, t)
+        ex.upload_schedule_plan(plan, pos)
+        ex.decode_step_host(qh, kh, vh, oh, BATCH, rp, gp)
+    barrier()
+    t0 = time.perf_counter()
+    for t in range(args.warmup, args.warmup + e2e_steps):
+        plan, pos = step_plan(mgr2, t)
+        plan_bytes = 4 * (plan.page_indptr.size + plan.page_indices.size + plan.last_page_len.size + pos.size) + \
+            16 * plan.cta_work_tiles.shape[0]
+        ex.upload_schedule_plan(plan, pos)
+        ex.decode_step_host(qh, kh, vh, oh, BATCH, rp, gp)  # waits for the result
+    e2e_s = time.perf_counter() - t0
+    barrier()
+
+    # max over ranks
+    t_dev = torch.tensor([elapsed_ms, e2e_s * 1e3], device="cuda", dtype=torch.float64)
+    if dist is not None:
+        dist.all_reduce(t_dev, op=dist.ReduceOp.MAX)
+    elapsed_ms, e2e_ms = float(t_dev[0]), float(t_dev[1])
+    ms_per_step = elapsed_ms / args.steps
+    value = world * BATCH / (ms_per_step * 1e-3)
+    e2e_value = world * BATCH / (e2e_ms / e2e_steps * 1e-3)
+
+    # roofline of the dominant kernel (paged decode): algorithmic bytes per launch / mean launch time
+    kv_bytes_launch = float(np.mean(attended)) * SHAPE.kv_bytes_per_token  # K and V, each element once
+    qo_bytes = 2 * BATCH * Hq * D * 2
+    table_bytes = 4 * float(np.mean([(c + 15) // 16 for c in attended])) + 4 * (2 * BATCH + 1)
+    alg_bytes = kv_bytes_launch + qo_bytes + table_bytes
+    peaks, peak_kind = measured_peaks()
+    dec_us = ms_dec / max(n_dec, 1) * 1e3
+    achieved = alg_bytes / (dec_us * 1e-6) / 1e9 if n_dec else None
+    traffic = None
+    tfile = ROOT / "profiles" / "decode_traffic.json"
+    if tfile.exists():
+        try:
+            traffic = json.loads(tfile.read_text()).get("dram_bytes_per_attended_token", None)
+            traffic = traffic * float(np.mean(attended)) if traffic else None
+        except Exception:
+            traffic = None
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "l2": "inputs larger than L2: each step streams %.2f GB of KV" %
+                       (kv_bytes_launch * L / 1e9), "plan": "rebuilt on the host every step by the C++ manager and uploaded inside the timed region",
+                       "kv_read_gbs_whole_step": kv_bytes_launch * L / (ms_per_step * 1e-3) / 1e9,
+                       "append_us_per_launch": ms_app / max(n_app, 1) * 1e3, "decode_us_per_launch": dec_us},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": (achieved / peaks["hbm_gbs"]) if achieved else None, "traffic": traffic,
+                         "kernel": "decode_kernel", "algorithmic_bytes_per_launch": alg_bytes, "peak_source": peak_kind,
+                         "frac_of_nominal_8000": (achieved / 8000.0) if achieved else None},
+            "e2e": {"value": e2e_value, "unit": UNIT,
+                    "h2d_bytes_per_step": int(plan_bytes + qh.numel() * 2 + kh.numel() * 2 + vh.numel() * 2),
+                    "d2h_bytes_per_step": int(oh.numel() * 2 + 4)},
+            "gpu_launches": int(gpu_launches),
+            "clocks": clocks,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            t1, cores, _ = cpu_sample(1, 1)
+            layers = int(max(1, min(L, 15.0 / max(t1, 1e-6))))
+            ts, cores, desc = cpu_sample(layers, 1)
+            line["cpu_baseline"] = {"value": BATCH / (ts * L / layers), "unit": UNIT, "cores": cores, "kind": "port",
+                                    "sample": desc}
+        print(json.dumps(line))
+    ex.close()
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -209,6 +209,27 @@ int32_t kriya_cuda_decode_layer_host(kriya_cuda_ctx* ctx, uint32_t layer, const 
                                      const void* v_host, void* out_host, uint32_t rows,
                                      const kriya_rope_kv_write_params* rope, const kriya_bsr_gqa_params* gqa);
 
+/* One decode step over ALL layers with device activations: for layer l = 0..num_layers-1, append then
+ * decode with the current plan.  q/k/v/out hold the layers back to back: q and out [layers][rows][Hq][D],
+ * k and v [layers][rows][Hkv][D].  One host call per step instead of two per layer; the per-layer loop of
+ * forward_and_sample_impl (enc:4880-5053) reduced to its attention ops. */
+int32_t kriya_cuda_decode_step(kriya_cuda_ctx* ctx, void* q_inout_dev, const void* k_dev, const void* v_dev,
+                               void* out_dev, uint32_t rows, const kriya_rope_kv_write_params* rope,
+                               const kriya_bsr_gqa_params* gqa);
+
+/* The same step with HOST activations (pinned memory recommended): inputs are copied to the device, every
+ * layer runs, out is copied back and the call waits.  The first call (and any call with more rows than
+ * before) allocates the staging buffers; later calls allocate nothing. */
+int32_t kriya_cuda_decode_step_host(kriya_cuda_ctx* ctx, const void* q_host, const void* k_host, const void* v_host,
+                                    void* out_host, uint32_t rows, const kriya_rope_kv_write_params* rope,
+                                    const kriya_bsr_gqa_params* gqa);
+
+/* Per-kernel device timing.  While enabled, every decode (kind 0) and append (kind 1) launch is bracketed
+ * by CUDA events on the context's stream; kriya_cuda_timing_read() waits for the stream, adds up the
+ * finished brackets since the last read and returns launch count and total milliseconds per kind. */
+int32_t kriya_cuda_timing_enable(kriya_cuda_ctx* ctx, int32_t enable);
+int32_t kriya_cuda_timing_read(kriya_cuda_ctx* ctx, uint32_t kind, uint64_t* out_launches, double* out_total_ms);
+
 /* Number of kernels this library has launched on `ctx` since creation (for launch accounting). */
 uint64_t kriya_cuda_launch_count(const kriya_cuda_ctx* ctx);
 

@@ -1,12 +1,10 @@
 """In-tree build of the native libraries (no build system beyond nvcc / g++ / gcc).
 
     python -m kriya_rt_b200.build            # CUDA library + host bookkeeping library
-    python -m kriya_rt_b200.build --oracle   # also the C oracle used by tests and the CPU baseline
 
 Outputs (git-ignored, they travel with the tree):
     kriya_rt_b200/lib/libkriya_cuda.so   sm_100a kernels + C ABI (include/kriya_cuda.h)
     kriya_rt_b200/lib/libkriya_kv.so     host bookkeeping C ABI (include/kriya_kv.h)
-    oracle/libkriya_oracle.so            CPU oracle (test infrastructure)
 """
 from __future__ import annotations
 
@@ -72,7 +70,7 @@ def build_cuda(force: bool = False) -> Path:
     with ThreadPoolExecutor(max_workers=min(8, len(sources))) as pool:
         list(pool.map(compile_one, zip(sources, objs)))
     if force or not _newer(out, objs):
-        _run([_nvcc(), "-shared", "-o", str(out), *map(str, objs), "-lcudart"])
+        _run([_nvcc(), "-shared", "-o", str(out), *map(str, objs)])  # cudart is linked statically (nvcc default)
     return out
 
 
@@ -85,24 +83,12 @@ def build_kv(force: bool = False) -> Path:
     return out
 
 
-def build_oracle(force: bool = False) -> Path:
-    out = ROOT / "oracle" / "libkriya_oracle.so"
-    src = ROOT / "oracle" / "kriya_oracle.c"
-    if force or not _newer(out, [src]):
-        _run(["gcc", "-O3", "-march=native", "-ffp-contract=off", "-fopenmp", "-fPIC", "-shared", "-Wall",
-              str(src), "-o", str(out), "-lm"])
-    return out
-
-
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--force", action="store_true")
-    ap.add_argument("--oracle", action="store_true")
     args = ap.parse_args()
     print(build_kv(args.force))
     print(build_cuda(args.force))
-    if args.oracle:
-        print(build_oracle(args.force))
 
 
 if __name__ == "__main__":

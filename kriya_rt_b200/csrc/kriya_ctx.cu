@@ -43,6 +43,8 @@ void destroy(kriya_cuda_ctx* c) {
     cudaFree(c->d_status);
     cudaFree(c->d_act);
     cudaFree(c->d_pairs);
+    cudaFree(c->d_step);
+    for (cudaEvent_t e : c->ev_pool) cudaEventDestroy(e);
     for (int i = 0; i < 2; ++i) {
         if (c->h_plan[i]) cudaFreeHost(c->h_plan[i]);
         if (c->h_plan_free[i]) cudaEventDestroy(c->h_plan_free[i]);
@@ -129,6 +131,48 @@ const float* table_for(const kriya_cuda_ctx* c, const kriya_rope_kv_write_params
     return c->rope_table;
 }
 
+// Timing brackets: events come from a pool that grows while timing is on; closed brackets are summed by
+// timing_collect() once the stream has drained.
+struct TimingScope {
+    kriya_cuda_ctx* c;
+    uint32_t kind;
+    uint32_t start = 0, stop = 0;
+    bool on;
+    TimingScope(kriya_cuda_ctx* ctx, uint32_t k) : c(ctx), kind(k), on(ctx->timing) {
+        if (!on) return;
+        while (c->ev_next + 2 > c->ev_pool.size()) {
+            cudaEvent_t e;
+            if (cudaEventCreate(&e) != cudaSuccess) {
+                on = false;
+                return;
+            }
+            c->ev_pool.push_back(e);
+        }
+        start = uint32_t(c->ev_next++);
+        stop = uint32_t(c->ev_next++);
+        cudaEventRecord(c->ev_pool[start], c->stream);
+    }
+    ~TimingScope() {
+        if (!on) return;
+        cudaEventRecord(c->ev_pool[stop], c->stream);
+        c->ev_open[kind].emplace_back(start, stop);
+    }
+};
+
+void timing_collect(kriya_cuda_ctx* c) {
+    for (int k = 0; k < 2; ++k) {
+        for (auto& pr : c->ev_open[k]) {
+            float ms = 0.0f;
+            if (cudaEventElapsedTime(&ms, c->ev_pool[pr.first], c->ev_pool[pr.second]) == cudaSuccess) {
+                c->t_ms[k] += ms;
+                c->t_launches[k] += 1;
+            }
+        }
+        c->ev_open[k].clear();
+    }
+    c->ev_next = 0;
+}
+
 int32_t launch_append(kriya_cuda_ctx* c, uint32_t layer, void* q, const void* k, const void* v, const void* qw,
                       const void* kw, uint32_t num_tokens, uint32_t chunk_mode, uint32_t prefix,
                       const kriya_rope_kv_write_params* p) {
@@ -151,6 +195,7 @@ int32_t launch_append(kriya_cuda_ctx* c, uint32_t layer, void* q, const void* k,
     a.chunk_mode = chunk_mode;
     a.prefix_tokens = prefix;
     a.p = *p;
+    TimingScope ts(c, 1);
     KRIYA_CUDA_TRY(c, kriya_launch_append(a, c->cfg.dtype, c->stream));
     c->launches += 1;
     return KRIYA_CUDA_OK;
@@ -180,6 +225,7 @@ int32_t launch_decode(kriya_cuda_ctx* c, uint32_t layer, const void* q, void* ou
     a.num_kv_heads = c->cfg.num_kv_heads;
     a.sm_scale = p->sm_scale;
     a.logit_softcap = p->logit_softcap;
+    TimingScope ts(c, 0);
     KRIYA_CUDA_TRY(c, kriya_launch_decode(a, c->cfg.head_dim, c->cfg.block_size_tokens, c->cfg.dtype,
                                           c->max_smem_optin, c->stream));
     c->launches += 1;
@@ -681,6 +727,79 @@ int32_t kriya_cuda_decode_layer_host(kriya_cuda_ctx* c, uint32_t layer, const vo
     if (int32_t rc = kriya_cuda_paged_gqa_decode(c, layer, dq, dout, gqa)) return rc;
     KRIYA_CUDA_TRY(c, cudaMemcpyAsync(out_host, dout, qb, cudaMemcpyDeviceToHost, c->stream));
     return kriya_cuda_sync(c, 0);
+}
+
+int32_t kriya_cuda_decode_step(kriya_cuda_ctx* c, void* q, const void* k, const void* v, void* out, uint32_t rows,
+                               const kriya_rope_kv_write_params* rope, const kriya_bsr_gqa_params* gqa) {
+    if (!c) return KRIYA_CUDA_INVALID_INPUT;
+    if (!q || !k || !v || !out) return c->fail(KRIYA_CUDA_INVALID_INPUT, "q, k, v and out must not be null");
+    if (!c->plan_valid) return c->fail(KRIYA_CUDA_INVALID_INPUT, "no plan uploaded");
+    if (rows == 0 || rows != c->n_rows) return c->fail(KRIYA_CUDA_INVALID_INPUT, "rows must equal the plan's row count");
+    const size_t qb = size_t(rows) * c->cfg.num_q_heads * c->cfg.head_dim * 2;
+    const size_t kb = size_t(rows) * c->cfg.num_kv_heads * c->cfg.head_dim * 2;
+    for (uint32_t layer = 0; layer < c->cfg.num_layers; ++layer) {
+        uint8_t* ql = static_cast<uint8_t*>(q) + layer * qb;
+        const uint8_t* kl = static_cast<const uint8_t*>(k) + layer * kb;
+        const uint8_t* vl = static_cast<const uint8_t*>(v) + layer * kb;
+        uint8_t* ol = static_cast<uint8_t*>(out) + layer * qb;
+        if (int32_t rc = kriya_cuda_rope_kv_append(c, layer, ql, kl, vl, nullptr, nullptr, rows, rope)) return rc;
+        if (int32_t rc = kriya_cuda_paged_gqa_decode(c, layer, ql, ol, gqa)) return rc;
+    }
+    return KRIYA_CUDA_OK;
+}
+
+int32_t kriya_cuda_decode_step_host(kriya_cuda_ctx* c, const void* q_host, const void* k_host, const void* v_host,
+                                    void* out_host, uint32_t rows, const kriya_rope_kv_write_params* rope,
+                                    const kriya_bsr_gqa_params* gqa) {
+    if (!c) return KRIYA_CUDA_INVALID_INPUT;
+    if (!q_host || !k_host || !v_host || !out_host) return c->fail(KRIYA_CUDA_INVALID_INPUT, "host buffers must not be null");
+    if (!c->plan_valid) return c->fail(KRIYA_CUDA_INVALID_INPUT, "no plan uploaded");
+    if (rows == 0 || rows != c->n_rows) return c->fail(KRIYA_CUDA_INVALID_INPUT, "rows must equal the plan's row count");
+    cudaSetDevice(c->cfg.device);
+    const size_t L = c->cfg.num_layers;
+    const size_t qb = size_t(rows) * c->cfg.num_q_heads * c->cfg.head_dim * 2 * L;
+    const size_t kb = size_t(rows) * c->cfg.num_kv_heads * c->cfg.head_dim * 2 * L;
+    const size_t need = 2 * qb + 2 * kb;
+    if (need > c->step_bytes) {  // first call / larger batch only
+        KRIYA_CUDA_TRY(c, cudaStreamSynchronize(c->stream));
+        cudaFree(c->d_step);
+        c->d_step = nullptr;
+        c->step_bytes = 0;
+        KRIYA_CUDA_TRY(c, cudaMalloc(&c->d_step, need));
+        c->step_bytes = need;
+    }
+    uint8_t* dq = c->d_step;
+    uint8_t* dk = dq + qb;
+    uint8_t* dv = dk + kb;
+    uint8_t* dout = dv + kb;
+    KRIYA_CUDA_TRY(c, cudaMemcpyAsync(dq, q_host, qb, cudaMemcpyHostToDevice, c->stream));
+    KRIYA_CUDA_TRY(c, cudaMemcpyAsync(dk, k_host, kb, cudaMemcpyHostToDevice, c->stream));
+    KRIYA_CUDA_TRY(c, cudaMemcpyAsync(dv, v_host, kb, cudaMemcpyHostToDevice, c->stream));
+    if (int32_t rc = kriya_cuda_decode_step(c, dq, dk, dv, dout, rows, rope, gqa)) return rc;
+    KRIYA_CUDA_TRY(c, cudaMemcpyAsync(out_host, dout, qb, cudaMemcpyDeviceToHost, c->stream));
+    return kriya_cuda_sync(c, 0);
+}
+
+int32_t kriya_cuda_timing_enable(kriya_cuda_ctx* c, int32_t enable) {
+    if (!c) return KRIYA_CUDA_INVALID_INPUT;
+    cudaSetDevice(c->cfg.device);
+    KRIYA_CUDA_TRY(c, cudaStreamSynchronize(c->stream));
+    timing_collect(c);
+    c->timing = enable != 0;
+    return KRIYA_CUDA_OK;
+}
+
+int32_t kriya_cuda_timing_read(kriya_cuda_ctx* c, uint32_t kind, uint64_t* out_launches, double* out_total_ms) {
+    if (!c) return KRIYA_CUDA_INVALID_INPUT;
+    if (kind > 1) return c->fail(KRIYA_CUDA_INVALID_INPUT, "timing kind must be 0 (decode) or 1 (append)");
+    cudaSetDevice(c->cfg.device);
+    KRIYA_CUDA_TRY(c, cudaStreamSynchronize(c->stream));
+    timing_collect(c);
+    if (out_launches) *out_launches = c->t_launches[kind];
+    if (out_total_ms) *out_total_ms = c->t_ms[kind];
+    c->t_launches[kind] = 0;
+    c->t_ms[kind] = 0.0;
+    return KRIYA_CUDA_OK;
 }
 
 }  // extern "C"

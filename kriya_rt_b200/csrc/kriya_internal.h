@@ -5,6 +5,8 @@
 #include <stdint.h>
 
 #include <string>
+#include <utility>
+#include <vector>
 
 #include "kriya_cuda.h"
 
@@ -78,6 +80,18 @@ struct kriya_cuda_ctx {
     uint32_t* h_pairs = nullptr;
     uint32_t cap_pairs = 0;
     cudaEvent_t h_pairs_free = nullptr;
+
+    // staging for whole-step host calls (grown on demand by kriya_cuda_decode_step_host)
+    uint8_t* d_step = nullptr;
+    size_t step_bytes = 0;
+
+    // optional per-kernel timing: event pairs around decode (kind 0) and append (kind 1) launches
+    bool timing = false;
+    std::vector<cudaEvent_t> ev_pool;
+    std::vector<std::pair<uint32_t, uint32_t>> ev_open[2];  // indices into ev_pool: (start, stop)
+    size_t ev_next = 0;
+    uint64_t t_launches[2] = {0, 0};
+    double t_ms[2] = {0.0, 0.0};
 
     uint64_t launches = 0;
     std::string last_error;

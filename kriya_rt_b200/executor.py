@@ -101,6 +101,21 @@ class CudaExecutor:
         self._check(self._lib.kriya_cuda_kv_pool_ptrs(self._h, layer, C.byref(k), C.byref(v)))
         return k.value, v.value
 
+    def layer_cache_views(self, layer: int):
+        """Zero-copy torch views (int16 bit patterns) of one layer's K and V pools,
+        shaped [num_kv_blocks, block_size, Hkv, D].  For tests and for hosts that fill the cache themselves."""
+        import torch
+
+        k, v = self.kv_pool_ptrs(layer)
+        shape = (self.num_kv_blocks, self.block_size_tokens, self.num_kv_heads, self.head_dim)
+
+        class _Raw:
+            def __init__(self, ptr):
+                self.__cuda_array_interface__ = {"shape": shape, "typestr": "<i2", "data": (ptr, False), "version": 3}
+
+        dev = f"cuda:{self.cfg.device}"
+        return torch.as_tensor(_Raw(k), device=dev), torch.as_tensor(_Raw(v), device=dev)
+
     @property
     def stream_ptr(self) -> int:
         return int(self._lib.kriya_cuda_stream(self._h))
@@ -171,3 +186,23 @@ class CudaExecutor:
         rows = q_host.shape[0]
         self._check(self._lib.kriya_cuda_decode_layer_host(self._h, layer, _ptr(q_host), _ptr(k_host), _ptr(v_host),
                                                            _ptr(out_host), rows, C.byref(rope), C.byref(gqa)))
+
+    def decode_step(self, q_inout, k_in, v_in, out, rows: int, rope: RopeKvWriteParams, gqa: BsrGqaParams) -> None:
+        """All layers, device activations laid out [layers][rows][heads][D]."""
+        self._check(self._lib.kriya_cuda_decode_step(self._h, _ptr(q_inout), _ptr(k_in), _ptr(v_in), _ptr(out), rows,
+                                                     C.byref(rope), C.byref(gqa)))
+
+    def decode_step_host(self, q_host, k_host, v_host, out_host, rows: int, rope: RopeKvWriteParams,
+                         gqa: BsrGqaParams) -> None:
+        """All layers, host activations (numpy arrays or pinned torch CPU tensors); waits for the result."""
+        self._check(self._lib.kriya_cuda_decode_step_host(self._h, _ptr(q_host), _ptr(k_host), _ptr(v_host),
+                                                          _ptr(out_host), rows, C.byref(rope), C.byref(gqa)))
+
+    def timing_enable(self, enable: bool) -> None:
+        self._check(self._lib.kriya_cuda_timing_enable(self._h, int(enable)))
+
+    def timing_read(self, kind: int):
+        """(launches, total_ms) of decode (kind 0) or append (kind 1) kernels since the last read."""
+        n, ms = C.c_uint64(), C.c_double()
+        self._check(self._lib.kriya_cuda_timing_read(self._h, kind, C.byref(n), C.byref(ms)))
+        return n.value, ms.value

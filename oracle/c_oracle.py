@@ -30,11 +30,28 @@ class GqaParams(C.Structure):
                 ("max_query_tokens", C.c_uint32), ("sm_scale", C.c_float), ("logit_softcap", C.c_float)]
 
 
+def _cpu_stamp() -> str:
+    """The library is built with -march=native, so it is only valid on the CPU model it was built on."""
+    try:
+        for line in open("/proc/cpuinfo"):
+            if line.startswith("flags"):
+                import hashlib
+
+                return hashlib.sha1(line.encode()).hexdigest()
+    except OSError:
+        pass
+    return "unknown"
+
+
 def build(force: bool = False) -> Path:
-    """Compile the C oracle next to its source (gcc, OpenMP)."""
-    if force or not _SO.exists() or _SO.stat().st_mtime < _SRC.stat().st_mtime:
+    """Compile the C oracle next to its source (gcc, OpenMP); rebuilt when the source or the host CPU changed."""
+    stamp = _HERE / "libkriya_oracle.stamp"
+    cur = _cpu_stamp()
+    fresh = _SO.exists() and _SO.stat().st_mtime >= _SRC.stat().st_mtime and stamp.exists() and stamp.read_text() == cur
+    if force or not fresh:
         subprocess.run(["gcc", "-O3", "-march=native", "-ffp-contract=off", "-fopenmp", "-fPIC", "-shared", "-Wall",
                         str(_SRC), "-o", str(_SO), "-lm"], check=True)
+        stamp.write_text(cur)
     return _SO
 
 
@@ -44,11 +61,7 @@ _lib = None
 def lib() -> C.CDLL:
     global _lib
     if _lib is None:
-        try:
-            _lib = C.CDLL(str(build()))
-        except OSError:
-            # a library built with -march=native on another host may not load here: rebuild once
-            _lib = C.CDLL(str(build(force=True)))
+        _lib = C.CDLL(str(build()))
         _lib.ko_num_threads.restype = C.c_int
     return _lib
 

@@ -20,7 +20,9 @@ def _native_libs():
     from kriya_rt_b200 import build as B
 
     B.build_kv()
-    B.build_oracle()
+    from oracle import c_oracle
+
+    c_oracle.build()
     yield
 
 
