@@ -309,6 +309,15 @@ int32_t kriya_cuda_ctx_create(const kriya_cuda_config* cfg_in, kriya_cuda_ctx** 
     CREATE_TRY(cudaMemsetAsync(c->pool_k, 0, pool_bytes, c->stream));
     CREATE_TRY(cudaMemsetAsync(c->pool_v, 0, pool_bytes, c->stream));
 
+    // tensor maps for the prefill kernel's paged gather (rows of all layers back to back)
+    if (kriya_prefill_supported(cfg.head_dim, cfg.num_q_heads / cfg.num_kv_heads, cfg.block_size_tokens, cfg.dtype) &&
+        c->layer_stride_bytes % (size_t(cfg.num_kv_heads) * cfg.head_dim * 2) == 0 &&
+        (size_t(cfg.num_kv_heads) * cfg.head_dim * 2) % 16 == 0) {
+        const uint32_t row_elems = cfg.num_kv_heads * cfg.head_dim;
+        const uint64_t total_rows = pool_bytes / (size_t(row_elems) * 2);
+        c->tmaps_ok = kriya_prefill_encode_maps(c->pool_k, c->pool_v, total_rows, row_elems, c->tmap_k, c->tmap_v) == cudaSuccess;
+    }
+
     // RoPE table, enc:1939-1955: f32 cos/sin of pos * theta^-(2i/rot)
     {
         const uint32_t half_rot = std::max(cfg.rotary_dim / 2u, 1u);
@@ -618,14 +627,17 @@ int32_t kriya_cuda_paged_gqa_prefill(kriya_cuda_ctx* c, uint32_t layer, const vo
         return c->fail(KRIYA_CUDA_INVALID_INPUT, "chunk ends at token " + std::to_string(end) + " but row 0 of the plan holds " +
                                                      std::to_string(c->row0_blocks) + " blocks");
     if (!kriya_prefill_supported(c->cfg.head_dim, c->cfg.num_q_heads / c->cfg.num_kv_heads, c->cfg.block_size_tokens,
-                                 c->cfg.dtype))
+                                 c->cfg.dtype) || !c->tmaps_ok)
         return c->fail(KRIYA_CUDA_UNSUPPORTED, "prefill kernels cover head_dim 64/128 and 16-token blocks");
     cudaSetDevice(c->cfg.device);
     KriyaPrefillArgs a{};
     a.q = q;
     a.cache_k = c->layer_k(layer);
     a.cache_v = c->layer_v(layer);
+    a.layer_row0 = uint32_t(size_t(layer) * c->layer_stride_bytes / (size_t(c->cfg.num_kv_heads) * c->cfg.head_dim * 2));
     a.table = c->plan_dev<int32_t>(c->off_indices);
+    a.map_k = c->tmap_k;
+    a.map_v = c->tmap_v;
     a.out = out;
     a.status = c->d_status;
     a.num_tokens = num_tokens;

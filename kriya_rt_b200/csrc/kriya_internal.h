@@ -46,6 +46,11 @@ struct kriya_cuda_ctx {
     size_t layer_stride_bytes = 0;
     size_t block_bytes = 0;  // block_size * Hkv * D * 2
 
+    // TMA tensor maps over the K and V pools (128-byte opaque blobs), valid when tmaps_ok
+    alignas(64) unsigned char tmap_k[128];
+    alignas(64) unsigned char tmap_v[128];
+    bool tmaps_ok = false;
+
     float* rope_table = nullptr;  // [rope_max_seq_len][rotary_dim/2][2]
     uint32_t rope_rotary_dim = 0;
 
@@ -176,6 +181,8 @@ struct KriyaPrefillArgs {
     const void* q;        // [T][Hq][D]
     const void* cache_k;  // layer base
     const void* cache_v;
+    const void* map_k;    // CUtensorMap over the K pool (host copy)
+    const void* map_v;
     const int32_t* table; // row 0 of the plan
     void* out;            // [T][Hq][D]
     uint32_t* status;
@@ -184,9 +191,12 @@ struct KriyaPrefillArgs {
     uint32_t num_blocks;
     uint32_t num_q_heads;
     uint32_t num_kv_heads;
+    uint32_t layer_row0;  // first row of this layer inside the all-layer tensor map
     float sm_scale;
     float logit_softcap;
 };
 cudaError_t kriya_launch_prefill(const KriyaPrefillArgs& a, uint32_t head_dim, uint32_t block_size, uint32_t dtype,
                                  int max_smem_optin, cudaStream_t s);
 bool kriya_prefill_supported(uint32_t head_dim, uint32_t group, uint32_t block_size, uint32_t dtype);
+cudaError_t kriya_prefill_encode_maps(void* pool_k, void* pool_v, uint64_t total_rows, uint32_t row_elems,
+                                      void* out_map_k, void* out_map_v);

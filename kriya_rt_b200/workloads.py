@@ -66,6 +66,10 @@ class DecodeBatch:
     tiles: np.ndarray = field(default_factory=lambda: np.zeros((0, 4), np.uint32))
 
     @property
+    def cta_work_tiles(self) -> np.ndarray:  # same field name as FlashInferSchedulePlan
+        return self.tiles
+
+    @property
     def batch(self) -> int:
         return int(self.context.size)
 

@@ -1,0 +1,109 @@
+"""Chunked causal prefill on the GPU (tcgen05 kernel) through the C ABI, against the fp32 CPU oracle."""
+import numpy as np
+import pytest
+import torch
+
+from kriya_rt_b200 import workloads as W
+from kriya_rt_b200.kv import PagedKvCacheManager
+from oracle import c_oracle as O
+from gpu_util import TOL, dev16, fill_cache, host16, make_executor, oracle_gqa, oracle_rope, read_cache
+
+pytestmark = pytest.mark.gpu
+
+
+def chunked_prefill(shape, total, chunk, num_blocks=256, seed=0, poison=True, other_seq_tokens=100):
+    """Runs a whole prompt through append_chunk + prefill in chunks on the GPU and the same through the oracle.
+    Returns (gpu_out f32 [total,Hq,D], oracle_out f32, gpu cache, oracle cache)."""
+    Hq, Hkv, D, dt = shape.num_q_heads, shape.num_kv_heads, shape.head_dim, shape.dtype
+    mgr = PagedKvCacheManager(num_blocks, 0, 16)
+    if other_seq_tokens:
+        mgr.allocate_sequence(1, list(range(other_seq_tokens)))  # so the prompt's blocks are not 0..n
+    mgr.allocate_sequence(2, list(range(5000, 5000 + total)))
+    table, _ = mgr.sequence_table(2)
+    rng = np.random.default_rng(seed)
+    q = W.normal16(rng, (total, Hq, D), dt); k = W.normal16(rng, (total, Hkv, D), dt); v = W.normal16(rng, (total, Hkv, D), dt)
+    fillbits = (0x7FC1 if dt == W.BF16 else 0x7E01) if poison else 0
+    ck = np.full((num_blocks, 16, Hkv, D), fillbits, np.uint16)
+    cv = np.full((num_blocks, 16, Hkv, D), fillbits, np.uint16)
+    ex = make_executor(shape, num_blocks, max_query_tokens=max(chunk, 64))
+    fill_cache(ex, 0, ck, cv)
+    rp, gp = ex.rope_params(), ex.gqa_params(max_query_tokens=chunk)
+    outs = []
+    ok, ov = ck.copy(), cv.copy()
+    oouts = []
+    tab = O.rope_table(4096, D, shape.rope_theta)
+    for start in range(0, total, chunk):
+        n = min(chunk, total - start)
+        dq, dk, dv = dev16(q[start:start + n]), dev16(k[start:start + n]), dev16(v[start:start + n])
+        out = torch.zeros_like(dq)
+        torch.cuda.synchronize()
+        plan = mgr.build_prefix_schedule_plan(2, start + n, 8)
+        ex.upload_schedule_plan(plan)
+        ex.rope_kv_append_chunk(0, dq, dk, dv, start, n, rp)
+        ex.paged_gqa_prefill(0, dq, out, start, n, gp)
+        ex.sync()
+        outs.append(W.from_storage(host16(out), dt))
+        # oracle: per-token rows as the reference lays them out
+        rows = mgr.build_parallel_prefill_layout(2, start, n, 8)
+        oq = q[start:start + n].copy()
+        O.rope_kv_append(oq, k[start:start + n], v[start:start + n], ok, ov, rows.page_indptr, rows.page_indices,
+                         rows.last_page_len, np.arange(start, start + n), oracle_rope(rp), dt, table=tab)
+        assert np.array_equal(host16(dq), oq)
+        _, of = O.prefill_causal(oq, ok, ov, np.asarray(table, np.int32), start, oracle_gqa(ex), dt)
+        oouts.append(of)
+    gk, gv = read_cache(ex, 0)
+    ex.close()
+    return np.concatenate(outs), np.concatenate(oouts), (gk, gv), (ok, ov)
+
+
+@pytest.mark.parametrize("total,chunk", [(16, 16), (130, 130), (700, 256), (1024, 512), (300, 77)])
+def test_qwen15_shape_chunked_prefill(total, chunk):
+    shape = W.AttnShape("qwen1.5b", 12, 2, 128, W.BF16, rope_theta=1e6)
+    got, ref, (gk, gv), (ok, ov) = chunked_prefill(shape, total, chunk, seed=total)
+    assert np.isfinite(got).all()
+    assert np.abs(got - ref).max() <= TOL[W.BF16]
+    assert np.array_equal(gk, ok) and np.array_equal(gv, ov)  # the chunk's K/V landed bit-exactly
+
+
+@pytest.mark.parametrize("dtype", [W.FP16, W.BF16])
+def test_smollm_shape_head_dim_64(dtype):
+    shape = W.AttnShape("smol", 9, 3, 64, dtype)
+    got, ref, _, _ = chunked_prefill(shape, 333, 128, seed=7)
+    assert np.isfinite(got).all()
+    # P is rounded to the storage dtype before the P.V product, like the reference's tensor-core kernel
+    # (paged_gqa_and_deltanet.metal:1386 stores P as half; its test allows 0.05)
+    assert np.abs(got - ref).max() <= (4e-3 if dtype == W.FP16 else 1e-2)
+
+
+def test_reference_tiled_mma_prefill_case():
+    """test_shader_compile.rs:1696-1881: T=16, Hq=2, Hkv=1, D=64, closed-form inputs, K/V given (no RoPE), tol 0.05."""
+    T, Hq, Hkv, D = 16, 2, 1, 64
+    f = np.float32
+    q_f = np.array([(f(i % 17) - f(8.0)) * f(0.05) for i in range(T * Hq * D)], f)
+    k_f = np.array([(f(i % 13) - f(6.0)) * f(0.06) for i in range(16 * Hkv * D)], f)
+    v_f = np.array([(f(i % 11) - f(5.0)) * f(0.07) for i in range(16 * Hkv * D)], f)
+    q = W.to_storage(q_f.reshape(T, Hq, D), W.BF16)
+    ck = W.to_storage(k_f.reshape(1, 16, Hkv, D), W.BF16)
+    cv = W.to_storage(v_f.reshape(1, 16, Hkv, D), W.BF16)
+    expected = O.ref_test_causal_prefill(W.from_storage(q, W.BF16), W.from_storage(ck, W.BF16), W.from_storage(cv, W.BF16),
+                                         Hq, Hkv, D, float(f(1.0) / np.sqrt(f(D))))
+    shape = W.AttnShape("tsc", Hq, Hkv, D, W.BF16)
+    ex = make_executor(shape, 1)
+    fill_cache(ex, 0, ck, cv)
+    dq = dev16(q)
+    out = torch.zeros_like(dq)
+    torch.cuda.synchronize()
+    ex.plan_upload([0, 1], [0], [16])
+    ex.paged_gqa_prefill(0, dq, out, 0, T, ex.gqa_params(max_query_tokens=T))
+    ex.sync()
+    assert np.abs(W.from_storage(host16(out), W.BF16).ravel() - expected).max() < 0.05
+    ex.close()
+
+
+def test_prefill_last_row_equals_decode():
+    """Cross-check of the two attention kernels: the last query of a prefilled prompt sees exactly what a
+    decode step at that position sees."""
+    shape = W.AttnShape("x", 16, 2, 128, W.BF16)
+    total = 517
+    got, ref, (gk, gv), _ = chunked_prefill(shape, total, 517, seed=3, poison=False)
+    assert np.abs(got[-1] - ref[-1]).max() <= 1e-2
