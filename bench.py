@@ -380,6 +380,98 @@ def run_gpu_arm(args):
         dist.destroy_process_group()
 
 
+def run_kernel_case(args):
+    """A small single-kernel case for profiling under ncu: a few launches of one kernel, nothing else.
+    decode : Qwen2.5-3B shape, one layer, batch 32, contexts U[2048,8192] (about 170 MB of KV, larger than L2)
+    prefill: Qwen2.5-1.5B shape, one 2048-token prompt, last 512-token chunk (prefix 1536)
+    append : Qwen2.5-3B shape, 32 tokens;  copy: 64 pairs x 36 layers"""
+    import torch
+
+    from kriya_rt_b200.executor import CudaExecutor
+
+    case, reps = args.kernel_case, args.steps
+    torch.cuda.set_device(0)
+    gen = torch.Generator(device="cuda").manual_seed(7)
+
+    def fill(ex, layers):
+        for layer in range(layers):
+            for view in ex.layer_cache_views(layer):
+                view.view(-1).copy_(torch.randn(view.numel(), device="cuda", generator=gen).to(torch.bfloat16).view(torch.int16))
+
+    def rnd(*shape):
+        return torch.randn(*shape, device="cuda", generator=gen).to(torch.bfloat16).view(torch.int16)
+
+    if case in ("decode", "append"):
+        sh = SHAPE
+        ctx = W.config2_contexts(seed_tables=2002, batch=BATCH, lo=2048, hi=8192)
+        batch = W.make_decode_batch(sh, ctx, NUM_BLOCKS, seed=2002)
+        ex = CudaExecutor(num_layers=1, num_kv_blocks=NUM_BLOCKS, block_size_tokens=16, num_q_heads=16, num_kv_heads=2,
+                          head_dim=128, rope_theta=sh.rope_theta, rope_max_seq_len=16384, max_page_indices=NUM_BLOCKS)
+        fill(ex, 1)
+        q, k, v = rnd(BATCH, 16, 128), rnd(BATCH, 2, 128), rnd(BATCH, 2, 128)
+        out = torch.zeros_like(q)
+        torch.cuda.synchronize()
+        ex.upload_schedule_plan(batch, batch.positions)
+        rp, gp = ex.rope_params(), ex.gqa_params()
+        ex.timing_enable(True)
+        for _ in range(reps):
+            if case == "append":
+                ex.rope_kv_append(0, q, k, v, BATCH, rp)
+            else:
+                ex.paged_gqa_decode(0, q, out, gp)
+        n, ms = ex.timing_read(1 if case == "append" else 0)
+        kv_bytes = batch.kv_bytes_per_layer
+        print(json.dumps({"case": case, "launches": n, "us_per_launch": ms / max(n, 1) * 1e3,
+                          "kv_bytes_per_launch": kv_bytes, "attended_tokens": batch.attended_tokens,
+                          "kv_gbs": kv_bytes / (ms / max(n, 1) * 1e-3) / 1e9 if case == "decode" and n else None}))
+        ex.close()
+    elif case == "prefill":
+        sh = W.QWEN25_1P5B
+        total, chunk = 2048, 512
+        nb = 256
+        ex = CudaExecutor(num_layers=1, num_kv_blocks=nb, block_size_tokens=16, num_q_heads=12, num_kv_heads=2,
+                          head_dim=128, rope_theta=sh.rope_theta)
+        fill(ex, 1)
+        perm = np.random.default_rng(3).permutation(nb)[: total // 16].astype(np.int32)
+        ex.plan_upload([0, perm.size], perm, [16])
+        q = rnd(chunk, 12, 128)
+        out = torch.zeros_like(q)
+        torch.cuda.synchronize()
+        gp = ex.gqa_params(max_query_tokens=chunk)
+        stream = torch.cuda.ExternalStream(ex.stream_ptr)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ex.paged_gqa_prefill(0, q, out, total - chunk, chunk, gp)
+        ex.sync()
+        e0.record(stream)
+        for _ in range(reps):
+            ex.paged_gqa_prefill(0, q, out, total - chunk, chunk, gp)
+        e1.record(stream)
+        ex.sync()
+        us = e0.elapsed_time(e1) / reps * 1e3
+        flop = 4 * 12 * 128 * sum(total - chunk + i + 1 for i in range(chunk))
+        print(json.dumps({"case": case, "launches": reps, "us_per_launch": us, "flop_per_launch": flop,
+                          "tflops": flop / (us * 1e-6) / 1e12}))
+        ex.close()
+    elif case == "copy":
+        layers, nb = 36, 2048
+        ex = CudaExecutor(num_layers=layers, num_kv_blocks=nb, block_size_tokens=16, num_q_heads=16, num_kv_heads=2, head_dim=128)
+        pairs = np.stack([np.arange(64, dtype=np.uint32), np.arange(1000, 1064, dtype=np.uint32)], 1)
+        stream = torch.cuda.ExternalStream(ex.stream_ptr)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ex.kv_block_copy(pairs)
+        ex.sync()
+        e0.record(stream)
+        for _ in range(reps):
+            ex.kv_block_copy(pairs)
+        e1.record(stream)
+        ex.sync()
+        us = e0.elapsed_time(e1) / reps * 1e3
+        nbytes = 2 * 64 * layers * 2 * 8192
+        print(json.dumps({"case": case, "launches": reps, "us_per_launch": us, "bytes_moved": nbytes,
+                          "gbs": nbytes / (us * 1e-6) / 1e9}))
+        ex.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -387,7 +479,12 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--kernel-case", default=None, choices=["decode", "prefill", "append", "copy"],
+                    help="run a few launches of one kernel on a small case (for ncu), --steps = launches")
     args = ap.parse_args()
+    if args.kernel_case:
+        run_kernel_case(args)
+        return
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         run_reference_arm(args)
