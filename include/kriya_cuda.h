@@ -224,6 +224,11 @@ int32_t kriya_cuda_decode_step_host(kriya_cuda_ctx* ctx, const void* q_host, con
                                     void* out_host, uint32_t rows, const kriya_rope_kv_write_params* rope,
                                     const kriya_bsr_gqa_params* gqa);
 
+/* Chooses between the two decode kernels, which compute the same result: 0 = by shape (tensor-core kernel for
+ * head_dim 128, CUDA-core kernel otherwise), 1 = CUDA-core kernel, 2 = tensor-core kernel.  The reference picks
+ * kernels by shape in the same way (enc:4262-4281); this switch exists so that tests can hold both to the oracle. */
+int32_t kriya_cuda_set_decode_path(kriya_cuda_ctx* ctx, int32_t path);
+
 /* Per-kernel device timing.  While enabled, every decode (kind 0) and append (kind 1) launch is bracketed
  * by CUDA events on the context's stream; kriya_cuda_timing_read() waits for the stream, adds up the
  * finished brackets since the last read and returns launch count and total milliseconds per kind. */

@@ -98,6 +98,53 @@ uint32_t build_work(const int32_t* indptr, uint32_t rows, const uint32_t* begin,
     return n;
 }
 
+// Tensor-core decode work: every (row, KV head) is a run of 128-token tiles; the runs laid end to end are cut
+// into `ctas` equal contiguous pieces.  Returns the number of segment records, or UINT32_MAX when `cap` is too
+// small.  `ptr` receives ctas + 1 offsets into `out`.
+uint32_t build_tc_segments(const int32_t* indptr, uint32_t rows, uint32_t hkv, const uint32_t* begin, const uint32_t* end,
+                           uint32_t ctas, KriyaTcSeg* out, uint32_t cap, uint32_t* ptr) {
+    const uint32_t TP = 8;  // pages per tile
+    uint64_t total = 0;
+    for (uint32_t r = 0; r < rows; ++r) {
+        const uint32_t nb = uint32_t(indptr[r + 1] - indptr[r]);
+        const uint32_t b = begin ? std::min(begin[r], nb) : 0u;
+        const uint32_t e = end ? std::min(end[r], nb) : nb;
+        if (e > b) total += uint64_t((e + TP - 1) / TP - b / TP) * hkv;
+    }
+    uint32_t n = 0, slot = 0, cta = 0;
+    uint64_t unit = 0;  // index of the next tile in the stream
+    auto cta_end = [&](uint32_t c) { return total * (c + 1) / ctas; };  // first unit NOT owned by cta c
+    ptr[0] = 0;
+    for (uint32_t r = 0; r < rows; ++r) {
+        const uint32_t nb = uint32_t(indptr[r + 1] - indptr[r]);
+        const uint32_t b = begin ? std::min(begin[r], nb) : 0u;
+        const uint32_t e = end ? std::min(end[r], nb) : nb;
+        for (uint32_t h = 0; h < hkv; ++h) {
+            if (e <= b) {  // empty run: one zero-length record so that its output is still written
+                if (n + 1 > cap) return UINT32_MAX;
+                out[n++] = KriyaTcSeg{r, h, b, b, slot, slot, 1u, 0u};
+                slot += 1;
+                continue;
+            }
+            const uint32_t t0 = b / TP, t1 = (e + TP - 1) / TP;
+            const uint32_t first = n, first_slot = slot;
+            uint32_t t = t0;
+            while (t < t1) {
+                while (cta + 1 < ctas && unit >= cta_end(cta)) ptr[++cta] = n;
+                const uint64_t room = cta + 1 < ctas ? cta_end(cta) - unit : uint64_t(t1 - t);
+                const uint32_t take = uint32_t(std::min<uint64_t>(room, t1 - t));
+                if (n + 1 > cap) return UINT32_MAX;
+                out[n++] = KriyaTcSeg{r, h, std::max(b, t * TP), std::min(e, (t + take) * TP), slot++, first_slot, 0u, 0u};
+                t += take;
+                unit += take;
+            }
+            for (uint32_t i = first; i < n; ++i) out[i].n_parts = n - first;
+        }
+    }
+    while (cta < ctas) ptr[++cta] = n;
+    return n;
+}
+
 int32_t check_layer(kriya_cuda_ctx* c, uint32_t layer) {
     if (layer >= c->cfg.num_layers)
         return c->fail(KRIYA_CUDA_INVALID_INPUT, "layer " + std::to_string(layer) + " out of range (context has " +
@@ -201,8 +248,14 @@ int32_t launch_append(kriya_cuda_ctx* c, uint32_t layer, void* q, const void* k,
     return KRIYA_CUDA_OK;
 }
 
+bool use_tc_decode(const kriya_cuda_ctx* c) {
+    if (c->decode_path == 1) return false;
+    return c->tmaps_ok && kriya_decode_tc_supported(c->cfg.head_dim, c->cfg.num_q_heads / c->cfg.num_kv_heads,
+                                                    c->cfg.block_size_tokens);
+}
+
 int32_t launch_decode(kriya_cuda_ctx* c, uint32_t layer, const void* q, void* out, float* sm, float* sl, float* so,
-                      size_t work_off, uint32_t n_work, const kriya_bsr_gqa_params* p) {
+                      bool range_list, uint32_t n_work, const kriya_bsr_gqa_params* p) {
     KriyaDecodeArgs a{};
     a.q = q;
     a.cache_k = c->layer_k(layer);
@@ -210,7 +263,7 @@ int32_t launch_decode(kriya_cuda_ctx* c, uint32_t layer, const void* q, void* ou
     a.indptr = c->plan_dev<int32_t>(c->off_indptr);
     a.indices = c->plan_dev<int32_t>(c->off_indices);
     a.last_len = c->plan_dev<int32_t>(c->off_last_len);
-    a.work = c->plan_dev<KriyaDecodeWork>(work_off);
+    a.work = c->plan_dev<KriyaDecodeWork>(range_list ? c->off_range : c->off_work);
     a.out = out;
     a.part_o = c->part_o;
     a.part_ml = c->part_ml;
@@ -226,8 +279,17 @@ int32_t launch_decode(kriya_cuda_ctx* c, uint32_t layer, const void* q, void* ou
     a.sm_scale = p->sm_scale;
     a.logit_softcap = p->logit_softcap;
     TimingScope ts(c, 0);
-    KRIYA_CUDA_TRY(c, kriya_launch_decode(a, c->cfg.head_dim, c->cfg.block_size_tokens, c->cfg.dtype,
-                                          c->max_smem_optin, c->stream));
+    if (use_tc_decode(c)) {
+        const uint32_t layer_row0 =
+            uint32_t(size_t(layer) * c->layer_stride_bytes / (size_t(c->cfg.num_kv_heads) * c->cfg.head_dim * 2));
+        KRIYA_CUDA_TRY(c, kriya_launch_decode_tc(a, c->plan_dev<KriyaTcSeg>(range_list ? c->off_tcseg2 : c->off_tcseg),
+                                                 c->plan_dev<uint32_t>(range_list ? c->off_tcptr2 : c->off_tcptr),
+                                                 uint32_t(c->sm_count), c->tmap_k, c->tmap_v, layer_row0, c->cfg.dtype,
+                                                 c->max_smem_optin, c->stream));
+    } else {
+        KRIYA_CUDA_TRY(c, kriya_launch_decode(a, c->cfg.head_dim, c->cfg.block_size_tokens, c->cfg.dtype,
+                                              c->max_smem_optin, c->stream));
+    }
     c->launches += 1;
     return KRIYA_CUDA_OK;
 }
@@ -350,6 +412,15 @@ int32_t kriya_cuda_ctx_create(const kriya_cuda_config* cfg_in, kriya_cuda_ctx** 
     off = align_up(off + size_t(c->cap_work) * sizeof(KriyaDecodeWork), 256);
     c->off_range = off;  // second work list, used by the block-range (partial state) decode
     off = align_up(off + size_t(c->cap_work) * sizeof(KriyaDecodeWork), 256);
+    c->cap_seg = c->cap_rows * cfg.num_kv_heads + uint32_t(c->sm_count) + 8u;
+    c->off_tcptr = off;
+    off = align_up(off + (size_t(c->sm_count) + 1) * 4, 256);
+    c->off_tcseg = off;
+    off = align_up(off + size_t(c->cap_seg) * sizeof(KriyaTcSeg), 256);
+    c->off_tcptr2 = off;
+    off = align_up(off + (size_t(c->sm_count) + 1) * 4, 256);
+    c->off_tcseg2 = off;
+    off = align_up(off + size_t(c->cap_seg) * sizeof(KriyaTcSeg), 256);
     c->off_tiles = off;
     off = align_up(off + size_t(c->cap_tiles) * sizeof(kriya_cta_work_tile), 256);
     c->off_indices = off;
@@ -363,11 +434,12 @@ int32_t kriya_cuda_ctx_create(const kriya_cuda_config* cfg_in, kriya_cuda_ctx** 
         CREATE_TRY(cudaEventCreateWithFlags(&c->h_plan_free[i], cudaEventDisableTiming));
     }
 
-    const size_t rows_hq = size_t(c->cap_work) * cfg.num_q_heads;
+    const size_t rows_hq = size_t(std::max(c->cap_work, c->cap_seg)) * cfg.num_q_heads;
     CREATE_TRY(cudaMalloc(&c->part_o, rows_hq * cfg.head_dim * sizeof(float)));
     CREATE_TRY(cudaMalloc(&c->part_ml, rows_hq * 2 * sizeof(float)));
-    CREATE_TRY(cudaMalloc(&c->part_counter, size_t(c->cap_rows) * sizeof(uint32_t)));
-    CREATE_TRY(cudaMemsetAsync(c->part_counter, 0, size_t(c->cap_rows) * sizeof(uint32_t), c->stream));
+    const size_t n_counters = size_t(c->cap_rows) * cfg.num_kv_heads;
+    CREATE_TRY(cudaMalloc(&c->part_counter, n_counters * sizeof(uint32_t)));
+    CREATE_TRY(cudaMemsetAsync(c->part_counter, 0, n_counters * sizeof(uint32_t), c->stream));
     CREATE_TRY(cudaMalloc(&c->d_status, 256));
     CREATE_TRY(cudaMemsetAsync(c->d_status, 0, 256, c->stream));
     CREATE_TRY(cudaMallocHost(&c->h_status, 256));
@@ -503,6 +575,11 @@ int32_t kriya_cuda_plan_upload(kriya_cuda_ctx* c, const int32_t* indptr, size_t 
     const uint32_t n_work =
         build_work(indptr, uint32_t(rows), nullptr, nullptr, 2u * uint32_t(c->sm_count), 2u, work, c->cap_work);
     if (n_work == UINT32_MAX) return invalid("plan needs more decode work items than the context holds");
+    const uint32_t n_seg = build_tc_segments(indptr, uint32_t(rows), c->cfg.num_kv_heads, nullptr, nullptr, uint32_t(c->sm_count),
+                                             reinterpret_cast<KriyaTcSeg*>(h + c->off_tcseg), c->cap_seg,
+                                             reinterpret_cast<uint32_t*>(h + c->off_tcptr));
+    if (n_seg == UINT32_MAX) return invalid("plan needs more decode segments than the context holds");
+    c->n_seg = n_seg;
     const size_t used = c->off_indices + indices_len * 4;
     KRIYA_CUDA_TRY(c, cudaMemcpyAsync(c->d_plan, h, used, cudaMemcpyHostToDevice, c->stream));
     KRIYA_CUDA_TRY(c, cudaEventRecord(c->h_plan_free[cur], c->stream));
@@ -569,12 +646,12 @@ int32_t kriya_cuda_paged_gqa_decode(kriya_cuda_ctx* c, uint32_t layer, const voi
     if (int32_t rc = check_gqa(c, p)) return rc;
     if (!c->plan_valid) return c->fail(KRIYA_CUDA_INVALID_INPUT, "no plan uploaded");
     if (!q || !out) return c->fail(KRIYA_CUDA_INVALID_INPUT, "q and out must not be null");
-    if (!kriya_decode_supported(c->cfg.head_dim, c->cfg.num_q_heads / c->cfg.num_kv_heads, c->cfg.num_kv_heads,
-                                c->cfg.block_size_tokens))
+    if (!use_tc_decode(c) && !kriya_decode_supported(c->cfg.head_dim, c->cfg.num_q_heads / c->cfg.num_kv_heads,
+                                                     c->cfg.num_kv_heads, c->cfg.block_size_tokens))
         return c->fail(KRIYA_CUDA_UNSUPPORTED,
-                       "decode kernels cover head_dim 64/128, group size 1..8, up to 8 KV heads, 16-token blocks");
+                       "decode kernels cover head_dim 64/128, group size 1..8, 16-token blocks (head_dim 64: up to 8 KV heads)");
     cudaSetDevice(c->cfg.device);
-    return launch_decode(c, layer, q, out, nullptr, nullptr, nullptr, c->off_work, c->n_work, p);
+    return launch_decode(c, layer, q, out, nullptr, nullptr, nullptr, false, c->n_work, p);
 }
 
 int32_t kriya_cuda_paged_gqa_decode_partial(kriya_cuda_ctx* c, uint32_t layer, const void* q, const uint32_t* blk_begin,
@@ -585,10 +662,10 @@ int32_t kriya_cuda_paged_gqa_decode_partial(kriya_cuda_ctx* c, uint32_t layer, c
     if (int32_t rc = check_gqa(c, p)) return rc;
     if (!c->plan_valid) return c->fail(KRIYA_CUDA_INVALID_INPUT, "no plan uploaded");
     if (!q || !out_m || !out_l || !out_o) return c->fail(KRIYA_CUDA_INVALID_INPUT, "q and state outputs must not be null");
-    if (!kriya_decode_supported(c->cfg.head_dim, c->cfg.num_q_heads / c->cfg.num_kv_heads, c->cfg.num_kv_heads,
-                                c->cfg.block_size_tokens))
+    if (!use_tc_decode(c) && !kriya_decode_supported(c->cfg.head_dim, c->cfg.num_q_heads / c->cfg.num_kv_heads,
+                                                     c->cfg.num_kv_heads, c->cfg.block_size_tokens))
         return c->fail(KRIYA_CUDA_UNSUPPORTED,
-                       "decode kernels cover head_dim 64/128, group size 1..8, up to 8 KV heads, 16-token blocks");
+                       "decode kernels cover head_dim 64/128, group size 1..8, 16-token blocks (head_dim 64: up to 8 KV heads)");
     cudaSetDevice(c->cfg.device);
     // work list for the requested ranges, staged behind the plan's own list
     KRIYA_CUDA_TRY(c, cudaEventSynchronize(c->h_pairs_free));
@@ -599,8 +676,15 @@ int32_t kriya_cuda_paged_gqa_decode_partial(kriya_cuda_ctx* c, uint32_t layer, c
     if (n_work == UINT32_MAX) return c->fail(KRIYA_CUDA_INVALID_INPUT, "ranges need more work items than the context holds");
     KRIYA_CUDA_TRY(c, cudaMemcpyAsync(c->d_plan + c->off_range, work, size_t(n_work) * sizeof(KriyaDecodeWork),
                                       cudaMemcpyHostToDevice, c->stream));
+    auto* segs = reinterpret_cast<KriyaTcSeg*>(c->h_plan_last + c->off_tcseg2);
+    auto* sptr = reinterpret_cast<uint32_t*>(c->h_plan_last + c->off_tcptr2);
+    const uint32_t n_seg = build_tc_segments(indptr, c->n_rows, c->cfg.num_kv_heads, blk_begin, blk_end, uint32_t(c->sm_count),
+                                             segs, c->cap_seg, sptr);
+    if (n_seg == UINT32_MAX) return c->fail(KRIYA_CUDA_INVALID_INPUT, "ranges need more segments than the context holds");
+    KRIYA_CUDA_TRY(c, cudaMemcpyAsync(c->d_plan + c->off_tcptr2, sptr, c->off_tcseg2 - c->off_tcptr2 + size_t(n_seg) * sizeof(KriyaTcSeg),
+                                      cudaMemcpyHostToDevice, c->stream));
     KRIYA_CUDA_TRY(c, cudaEventRecord(c->h_pairs_free, c->stream));
-    return launch_decode(c, layer, q, nullptr, out_m, out_l, out_o, c->off_range, n_work, p);
+    return launch_decode(c, layer, q, nullptr, out_m, out_l, out_o, true, n_work, p);
 }
 
 int32_t kriya_cuda_merge_states(kriya_cuda_ctx* c, const float* m, const float* l, const float* o, uint32_t parts,
@@ -790,6 +874,16 @@ int32_t kriya_cuda_decode_step_host(kriya_cuda_ctx* c, const void* q_host, const
     if (int32_t rc = kriya_cuda_decode_step(c, dq, dk, dv, dout, rows, rope, gqa)) return rc;
     KRIYA_CUDA_TRY(c, cudaMemcpyAsync(out_host, dout, qb, cudaMemcpyDeviceToHost, c->stream));
     return kriya_cuda_sync(c, 0);
+}
+
+int32_t kriya_cuda_set_decode_path(kriya_cuda_ctx* c, int32_t path) {
+    if (!c) return KRIYA_CUDA_INVALID_INPUT;
+    if (path < 0 || path > 2) return c->fail(KRIYA_CUDA_INVALID_INPUT, "decode path must be 0 (auto), 1 (CUDA-core) or 2 (tensor-core)");
+    if (path == 2 && !(c->tmaps_ok && kriya_decode_tc_supported(c->cfg.head_dim, c->cfg.num_q_heads / c->cfg.num_kv_heads,
+                                                                 c->cfg.block_size_tokens)))
+        return c->fail(KRIYA_CUDA_UNSUPPORTED, "the tensor-core decode kernel covers head_dim 128, group size 1..8, 16-token blocks");
+    c->decode_path = path;
+    return KRIYA_CUDA_OK;
 }
 
 int32_t kriya_cuda_timing_enable(kriya_cuda_ctx* c, int32_t enable) {

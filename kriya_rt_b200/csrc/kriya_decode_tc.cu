@@ -1,0 +1,520 @@
+// Paged GQA decode attention on the tensor cores, head_dim 128 (the job of bsr_paged_gqa_decode_stage1 and
+// bsr_paged_gqa_split_k_reduce, kernels/metal/paged_gqa_and_deltanet.metal:242-495,1474-1525).
+//
+// Why tensor cores for a bandwidth-bound op: with G query heads packed per KV head the fp32 path needs
+// 2*G FMA per cached element; at G = 8 the instruction stream alone takes longer than the HBM transfer
+// (measured on the CUDA-core kernel).  Here the KV tile sits on the M axis of the MMA, so the arithmetic is
+// a handful of tiny tcgen05.mma per 64 KB of cache and the kernel is left with the HBM stream.
+//
+// Shape of the kernel (persistent, one CTA per SM, 192 threads)
+//   - Work: every (plan row, KV head) is a run of 128-token tiles (8 pages).  All runs laid end to end form
+//     one tile stream that the host cuts into equal contiguous pieces, one per CTA, so every SM streams the
+//     same number of bytes.  A run cut across CTAs leaves partial (m, l, o) states in scratch; the last
+//     piece to finish (atomic ticket, no waiting) merges them.
+//   - Warp 4 (producer) walks its piece: per tile it reads up to 8 page indices and issues TMA tensor loads
+//     of K and V ([16 tokens] x [64 d] boxes, 128-byte swizzle, no multicast) into a 3-stage shared-memory
+//     ring; it also stages the G query heads of each run as a 16-row MMA operand.
+//   - Warp 5 (one thread) issues tcgen05.mma:  S^T[128 tokens x 16] = K_tile . Q^T   (K-major operands) and
+//     O^T[128 d x 16] += V_tile^T . P^T  (V consumed in place as an MN-major operand), accumulators in TMEM.
+//     S^T of tile g+1 is issued before P.V of tile g so the softmax overlaps the tensor pipe.
+//   - Warps 0-3: thread t owns token t of the tile (TMEM lane t of S^T) and dimension t of the output (lane t
+//     of O^T).  Per tile: read 16 scores, mask tokens past the row end, column max by warp shuffles plus a
+//     4-warp exchange in shared memory, exp2, write P (storage dtype) into the swizzled operand tile, keep
+//     the running sum per lane, rescale O^T in TMEM only when a head's max moved by more than 2^8.
+//   - Every mbarrier wait is bounded; on expiry the kernel records a status word, abandons its piece,
+//     frees its TMEM and returns.
+//
+// HBM roofline: algorithmic bytes per launch = attended tokens * 2 * Hkv * D * 2 B; every K/V byte is read
+// from HBM once (one TMA load) and from shared memory once (one MMA operand read).
+#include <algorithm>
+
+#include "kriya_tc.cuh"
+
+namespace kriya {
+
+constexpr int kTcD = 128;
+constexpr int kTcTile = 128;          // tokens per tile
+constexpr int kTcPage = 16;
+constexpr int kTcPagesPerTile = kTcTile / kTcPage;
+constexpr int kTcStages = 3;
+constexpr int kTcThreads = 192;
+constexpr int kTcN = 16;              // MMA N: query heads of one KV head, zero padded
+constexpr float kTcLog2e = 1.4426950408889634f;
+constexpr float kTcRescale = 8.0f;
+constexpr uint32_t kTcPanel = 128 * 128;           // one 64-d panel of a 128-token tile
+constexpr uint32_t kTcKvBytes = 2 * kTcPanel;      // K (or V) tile, both panels: 32 KB
+constexpr uint32_t kTcQBytes = 2 * 16 * 128;       // 16 rows x 256 B as two panels: 4 KB
+constexpr uint32_t kTcPBytes = 2 * 16 * 128;       // [16 heads][128 tokens] as two 64-token panels: 4 KB
+constexpr uint32_t kTcTmemCols = 64;
+constexpr uint32_t kColS0 = 0, kColS1 = 16, kColO = 32;
+
+struct TcParams {
+    KriyaDecodeArgs a;
+    const KriyaTcSeg* segs;
+    const uint32_t* cta_seg_ptr;  // [grid + 1]
+    uint32_t layer_row0;
+};
+
+__device__ __forceinline__ void named_bar_sync_128() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+template <int G, typename T>
+__global__ void __launch_bounds__(kTcThreads, 1)
+decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, TcParams pp) {
+    constexpr uint32_t FMT = (T::kDtype == KRIYA_DTYPE_BF16) ? 1u : 0u;
+    constexpr uint32_t IDESC_S = make_idesc(FMT, 128, kTcN, 0, 0);  // A = K tile (K-major), B = Q (K-major)
+    constexpr uint32_t IDESC_O = make_idesc(FMT, 128, kTcN, 1, 0);  // A = V tile (MN-major), B = P (K-major)
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* sm = smem_raw + (base - smem_u32(smem_raw));
+    uint8_t* sK = sm;                                   // [stages][32 KB]
+    uint8_t* sV = sK + kTcStages * kTcKvBytes;          // [stages][32 KB]
+    uint8_t* sQ = sV + kTcStages * kTcKvBytes;          // [3][4 KB]
+    uint8_t* sP = sQ + 3 * kTcQBytes;                   // 4 KB
+    float* red = reinterpret_cast<float*>(sP + kTcPBytes);  // [4 warps][16]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(red + 64);
+    uint64_t* kv_full = bars;                     // [stages]
+    uint64_t* kv_empty = bars + kTcStages;        // [stages]
+    uint64_t* s_full = bars + 2 * kTcStages;      // [2]
+    uint64_t* p_ready = bars + 2 * kTcStages + 2; // 128 arrivals
+    uint64_t* pv_done = bars + 2 * kTcStages + 3;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kTcStages + 4);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+    uint32_t* ticket_s = tmem_slot + 2;
+
+    const KriyaDecodeArgs& a = pp.a;
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
+    const uint32_t seg_begin = pp.cta_seg_ptr[blockIdx.x], seg_end = pp.cta_seg_ptr[blockIdx.x + 1];
+    if (seg_begin == seg_end) return;  // whole CTA idle: nothing allocated yet
+
+    if (tid == 0) {
+        for (int s = 0; s < kTcStages; ++s) {
+            mbar_init(&kv_full[s], 1);
+            mbar_init(&kv_empty[s], 1);
+        }
+        mbar_init(&s_full[0], 1);
+        mbar_init(&s_full[1], 1);
+        mbar_init(p_ready, 128);
+        mbar_init(pv_done, 1);
+        *abort_flag = 0;
+        mbar_fence_init();
+    }
+    if (warp == 5) {
+        tmem_alloc(tmem_slot, kTcTmemCols);
+        tmem_relinquish();
+    }
+    // zero the K/V ring, the Q buffers and the P tile once: rows and pages that are never loaded must read as
+    // finite values, and the padding heads of Q and P must be zero
+    for (uint32_t i = tid; i < (2 * kTcStages * kTcKvBytes + 3 * kTcQBytes + kTcPBytes) / 16; i += kTcThreads)
+        reinterpret_cast<uint4*>(sK)[i] = make_uint4(0u, 0u, 0u, 0u);
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t Hq = a.num_q_heads, Hkv = a.num_kv_heads;
+
+    if (warp == 4) {
+        // ---- producer ---------------------------------------------------------------------------------
+        uint32_t g = 0;     // tiles issued by this CTA so far
+        uint32_t runs = 0;  // non-empty run pieces started so far (selects the Q buffer)
+        bool ok = true;
+        for (uint32_t si = seg_begin; si < seg_end && ok; ++si) {
+            const KriyaTcSeg seg = pp.segs[si];
+            const uint32_t t0 = seg.blk_lo / kTcPagesPerTile, t1 = (seg.blk_hi + kTcPagesPerTile - 1) / kTcPagesPerTile;
+            if (seg.blk_hi <= seg.blk_lo) continue;
+            const int32_t* table = a.indices + a.indptr[seg.req];
+            for (uint32_t t = t0; t < t1; ++t, ++g) {
+                if (*abort_flag) { ok = false; break; }
+                const uint32_t stage = g % kTcStages;
+                if (g >= kTcStages && !warp_wait(&kv_empty[stage], ((g / kTcStages) - 1u) & 1u)) {
+                    ok = false;
+                    break;
+                }
+                if (t == t0) {
+                    // The run's query heads as a 16-row K-major operand (rows >= G stay zero).  Staged after the
+                    // ring wait above: the buffer's previous user is three non-empty runs back, so all of its
+                    // S^T MMAs belong to tiles <= g - 3, which the wait has just shown to be complete.
+                    uint8_t* qb = sQ + (runs % 3u) * kTcQBytes;
+                    const uint16_t* qg = reinterpret_cast<const uint16_t*>(a.q) + (size_t(seg.req) * Hq + seg.kv_head * G) * kTcD;
+                    for (uint32_t i = lane; i < uint32_t(G) * 16u; i += 32u) {
+                        const uint32_t h = i >> 4, c = i & 15u;
+                        const uint4 val = *reinterpret_cast<const uint4*>(qg + h * kTcD + c * 8);
+                        *reinterpret_cast<uint4*>(qb + (c >> 3) * 2048u + h * 128u + (((c & 7u) ^ (h & 7u)) << 4)) = val;
+                    }
+                    fence_async_smem();
+                    __syncwarp();
+                    ++runs;
+                }
+                const uint32_t p_lo = max(t * kTcPagesPerTile, seg.blk_lo), p_hi = min((t + 1) * kTcPagesPerTile, seg.blk_hi);
+                const uint32_t npages = p_hi - p_lo;
+                const uint32_t my_page = p_lo + lane;
+                int32_t blk = 0;
+                if (lane < npages) {
+                    blk = table[my_page];
+                    if (uint32_t(blk) >= a.num_blocks) {
+                        atomicMax(a.status, uint32_t(KRIYA_DEV_BAD_BLOCK_INDEX));
+                        blk = 0;
+                    }
+                }
+                if (lane == 0) mbar_arrive_expect_tx(&kv_full[stage], npages * uint32_t(4 * kTcPage * 128));
+                __syncwarp();
+                if (lane < npages) {
+                    const int32_t y = int32_t(pp.layer_row0) + blk * kTcPage;
+                    const uint32_t row_off = (my_page - t * kTcPagesPerTile) * (kTcPage * 128);
+#pragma unroll
+                    for (int p = 0; p < 2; ++p) {
+                        const int32_t x = int32_t(seg.kv_head) * kTcD + p * 64;
+                        tma_load_2d(sK + stage * kTcKvBytes + p * kTcPanel + row_off, &map_k, x, y, &kv_full[stage]);
+                        tma_load_2d(sV + stage * kTcKvBytes + p * kTcPanel + row_off, &map_v, x, y, &kv_full[stage]);
+                    }
+                }
+            }
+        }
+        if (!ok && lane == 0) {
+            atomicMax(a.status, uint32_t(KRIYA_DEV_WAIT_EXPIRED));
+            *abort_flag = 1;
+        }
+    } else if (warp == 5) {
+        // ---- MMA issuer ---------------------------------------------------------------------------------
+        const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV), q_addr = smem_u32(sQ), p_addr = smem_u32(sP);
+        // (segment, tile) cursor for the look-ahead S^T issue
+        auto issue_s = [&](uint32_t gg, uint32_t qbuf) {
+            const uint32_t stage = gg % kTcStages;
+            const uint32_t d_tmem = tmem_base + ((gg & 1u) ? kColS1 : kColS0);
+#pragma unroll
+            for (int ks = 0; ks < kTcD / 16; ++ks) {
+                const uint32_t a_off = stage * kTcKvBytes + uint32_t(ks / 4) * kTcPanel + uint32_t(ks % 4) * 32u;
+                const uint32_t b_off = qbuf * kTcQBytes + uint32_t(ks / 4) * 2048u + uint32_t(ks % 4) * 32u;
+                umma_f16(d_tmem, smem_desc_sw128(k_addr + a_off, 16, 1024), smem_desc_sw128(q_addr + b_off, 16, 1024), IDESC_S,
+                         ks > 0 ? 1u : 0u);
+            }
+            umma_commit(&s_full[gg & 1u]);
+        };
+        // flatten the piece into (tile -> q buffer, first-of-run) on the fly with two cursors
+        uint32_t g = 0;
+        bool ok = true;
+        // look-ahead cursor
+        uint32_t la_si = seg_begin, la_t = 0, la_t1 = 0, la_g = 0, la_run = 0;
+        auto la_load = [&]() {
+            while (la_si < seg_end) {
+                const KriyaTcSeg s2 = pp.segs[la_si];
+                if (s2.blk_hi > s2.blk_lo) {
+                    la_t = s2.blk_lo / kTcPagesPerTile;
+                    la_t1 = (s2.blk_hi + kTcPagesPerTile - 1) / kTcPagesPerTile;
+                    return true;
+                }
+                ++la_si;
+            }
+            return false;
+        };
+        bool la_valid = la_load();
+        auto la_issue = [&]() -> bool {  // issue S^T for the look-ahead tile and advance the cursor
+            if (!la_valid) return true;
+            if (!warp_wait(&kv_full[la_g % kTcStages], (la_g / kTcStages) & 1u)) return false;
+            tc_fence_after();
+            if (lane == 0) issue_s(la_g, la_run % 3u);
+            __syncwarp();
+            ++la_g;
+            if (++la_t >= la_t1) {
+                ++la_si;
+                ++la_run;
+                la_valid = la_load();
+            }
+            return true;
+        };
+        ok = la_issue();  // S^T of the first tile
+        for (uint32_t si = seg_begin; si < seg_end && ok; ++si) {
+            const KriyaTcSeg seg = pp.segs[si];
+            if (seg.blk_hi <= seg.blk_lo) continue;
+            const uint32_t t0 = seg.blk_lo / kTcPagesPerTile, t1 = (seg.blk_hi + kTcPagesPerTile - 1) / kTcPagesPerTile;
+            for (uint32_t t = t0; t < t1 && ok; ++t, ++g) {
+                if (*abort_flag) { ok = false; break; }
+                ok = la_issue();  // S^T of tile g+1 (possibly of the next run) before P.V of tile g
+                if (!ok) break;
+                ok = warp_wait(p_ready, g & 1u);
+                if (!ok) break;
+                tc_fence_after();
+                if (lane == 0) {
+                    const uint32_t stage = g % kTcStages;
+#pragma unroll
+                    for (int ks = 0; ks < kTcTile / 16; ++ks) {
+                        const uint32_t a_off = stage * kTcKvBytes + uint32_t(ks) * (kTcPage * 128);
+                        const uint32_t b_off = uint32_t(ks / 4) * 2048u + uint32_t(ks % 4) * 32u;
+                        umma_f16(tmem_base + kColO, smem_desc_sw128(v_addr + a_off, kTcPanel, 1024),
+                                 smem_desc_sw128(p_addr + b_off, 16, 1024), IDESC_O, (t > t0 || ks > 0) ? 1u : 0u);
+                    }
+                    umma_commit(&kv_empty[stage]);
+                    umma_commit(pv_done);
+                }
+                __syncwarp();
+            }
+        }
+        if (!ok && lane == 0) {
+            atomicMax(a.status, uint32_t(KRIYA_DEV_WAIT_EXPIRED));
+            *abort_flag = 1;
+        }
+    } else {
+        // ---- softmax warps ----------------------------------------------------------------------------------
+        const uint32_t lane_addr = (warp * 32u) << 16;
+        const bool softcap = a.logit_softcap > 0.0f;
+        const float scale2 = softcap ? a.sm_scale : a.sm_scale * kTcLog2e;
+        const bool state_mode = a.state_o != nullptr;
+        uint32_t g = 0;
+        bool ok = true;
+        for (uint32_t si = seg_begin; si < seg_end && ok; ++si) {
+            const KriyaTcSeg seg = pp.segs[si];
+            const uint32_t req = seg.req;
+            const uint32_t nb = uint32_t(max(a.indptr[req + 1] - a.indptr[req], 0));
+            const uint32_t row_tokens = nb ? (nb - 1u) * kTcPage + uint32_t(max(a.last_len[req], 1)) : 0u;
+            const uint32_t tok_lo = seg.blk_lo * kTcPage, tok_hi = min(seg.blk_hi * kTcPage, row_tokens);
+            const uint32_t t0 = seg.blk_lo / kTcPagesPerTile, t1 = (seg.blk_hi + kTcPagesPerTile - 1) / kTcPagesPerTile;
+            const bool empty = seg.blk_hi <= seg.blk_lo;
+            float m_used[G], l_lane[G];
+#pragma unroll
+            for (int h = 0; h < G; ++h) {
+                m_used[h] = -INFINITY;
+                l_lane[h] = 0.0f;
+            }
+            for (uint32_t t = empty ? t1 : t0; t < t1; ++t, ++g) {
+                if (*abort_flag) { ok = false; break; }
+                ok = warp_wait(&s_full[g & 1u], (g >> 1) & 1u);
+                if (!ok) break;
+                tc_fence_after();
+                uint32_t r[16];
+                tmem_ld16(tmem_base + lane_addr + ((g & 1u) ? kColS1 : kColS0), r);
+                tmem_wait_ld();
+                const uint32_t tok = t * kTcTile + tid;
+                const bool valid = tok >= tok_lo && tok < tok_hi;
+                float s[G], mx[G];
+#pragma unroll
+                for (int h = 0; h < G; ++h) {
+                    float x = __uint_as_float(r[h]) * scale2;
+                    if (softcap) x = tanhf(fminf(fmaxf(x / a.logit_softcap, -15.0f), 15.0f)) * a.logit_softcap * kTcLog2e;
+                    s[h] = valid ? x : -INFINITY;
+                    mx[h] = s[h];
+                }
+#pragma unroll
+                for (int off = 16; off >= 1; off >>= 1)
+#pragma unroll
+                    for (int h = 0; h < G; ++h) mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xFFFFFFFFu, mx[h], off));
+                // `red` is free: its previous readers passed the second barrier of the previous tile
+                if (lane == 0) {
+#pragma unroll
+                    for (int h = 0; h < G; ++h) red[warp * 16 + h] = mx[h];
+                }
+                named_bar_sync_128();
+                bool need = false;
+                float alpha[G];
+#pragma unroll
+                for (int h = 0; h < G; ++h) {
+                    const float m_tile = fmaxf(fmaxf(red[h], red[16 + h]), fmaxf(red[32 + h], red[48 + h]));
+                    alpha[h] = 1.0f;
+                    if (m_tile > m_used[h] + kTcRescale || (m_used[h] == -INFINITY && m_tile > -INFINITY)) {
+                        alpha[h] = (m_used[h] == -INFINITY) ? 0.0f : exp2f(m_used[h] - m_tile);
+                        m_used[h] = m_tile;
+                        need = need || (t > t0);
+                    }
+                }
+                named_bar_sync_128();  // everyone has read `red`
+                // the previous P.V must be complete before P is overwritten or O^T rescaled
+                if (g > 0) {
+                    ok = warp_wait(pv_done, (g - 1u) & 1u);
+                    if (!ok) break;
+                    tc_fence_after();
+                }
+                if (need) {  // uniform across the 128 threads: every thread computed the same maxima
+                    uint32_t o[16];
+                    tmem_ld16(tmem_base + lane_addr + kColO, o);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int h = 0; h < G; ++h) o[h] = __float_as_uint(__uint_as_float(o[h]) * alpha[h]);
+                    tmem_st16(tmem_base + lane_addr + kColO, o);
+                    tmem_wait_st();
+                }
+                // probabilities of this token for the G heads -> P[h][token] (K-major, swizzled)
+                {
+                    const uint32_t tt = tid;  // token inside the tile
+                    const uint32_t panel = tt >> 6, col = tt & 63u;
+#pragma unroll
+                    for (int h = 0; h < G; ++h) {
+                        const float p = (s[h] == -INFINITY) ? 0.0f : fast_exp2(s[h] - m_used[h]);
+                        const uint16_t pb = T::store(p);
+                        l_lane[h] = l_lane[h] * alpha[h] + T::load(pb);
+                        *reinterpret_cast<uint16_t*>(sP + panel * 2048u + uint32_t(h) * 128u +
+                                                     ((((col >> 3) ^ (uint32_t(h) & 7u)) << 4) | ((col & 7u) << 1))) = pb;
+                    }
+                }
+                // a token outside the run (past the row end, outside the block range, or a page that was not
+                // loaded) must contribute nothing: its V row is cleared so that 0 * garbage cannot appear
+                if (!valid) {
+                    const uint32_t stage = g % kTcStages;
+#pragma unroll
+                    for (int p = 0; p < 2; ++p)
+#pragma unroll
+                        for (int c = 0; c < 8; ++c)
+                            *reinterpret_cast<uint4*>(sV + stage * kTcKvBytes + p * kTcPanel + tid * 128u + (c << 4)) =
+                                make_uint4(0u, 0u, 0u, 0u);
+                }
+                tc_fence_before();
+                fence_async_smem();
+                mbar_arrive(p_ready);
+            }
+            if (!ok) break;
+            // ---- end of the run piece: total l per head, then O^T / l or the partial state ----------------
+            float l_tot[G];
+#pragma unroll
+            for (int h = 0; h < G; ++h) l_tot[h] = l_lane[h];
+#pragma unroll
+            for (int off = 16; off >= 1; off >>= 1)
+#pragma unroll
+                for (int h = 0; h < G; ++h) l_tot[h] += __shfl_xor_sync(0xFFFFFFFFu, l_tot[h], off);
+            if (lane == 0) {
+#pragma unroll
+                for (int h = 0; h < G; ++h) red[warp * 16 + h] = l_tot[h];
+            }
+            named_bar_sync_128();
+#pragma unroll
+            for (int h = 0; h < G; ++h) l_tot[h] = (red[h] + red[16 + h]) + (red[32 + h] + red[48 + h]);
+            named_bar_sync_128();
+            uint32_t o[16];
+#pragma unroll
+            for (int h = 0; h < 16; ++h) o[h] = 0u;
+            if (!empty) {
+                ok = warp_wait(pv_done, (g - 1u) & 1u);
+                if (!ok) break;
+                tc_fence_after();
+                tmem_ld16(tmem_base + lane_addr + kColO, o);
+                tmem_wait_ld();
+                tc_fence_before();
+            }
+            const uint32_t d = tid;  // output dimension owned by this thread
+            const size_t row0 = size_t(req) * Hq + seg.kv_head * G;
+            if (seg.n_parts == 1u) {
+#pragma unroll
+                for (int h = 0; h < G; ++h) {
+                    const float ov = __uint_as_float(o[h]);
+                    if (state_mode) {
+                        a.state_o[(row0 + h) * kTcD + d] = ov;
+                        if (d == 0) {
+                            a.state_m[row0 + h] = m_used[h] / kTcLog2e;
+                            a.state_l[row0 + h] = l_tot[h];
+                        }
+                    } else {
+                        reinterpret_cast<uint16_t*>(a.out)[(row0 + h) * kTcD + d] = T::store(ov / fmaxf(l_tot[h], 1e-12f));
+                    }
+                }
+            } else {
+                const size_t prow = size_t(seg.slot) * G;
+#pragma unroll
+                for (int h = 0; h < G; ++h) {
+                    a.part_o[(prow + h) * kTcD + d] = __uint_as_float(o[h]);
+                    if (d == 0) {
+                        a.part_ml[(prow + h) * 2 + 0] = m_used[h];
+                        a.part_ml[(prow + h) * 2 + 1] = l_tot[h];
+                    }
+                }
+                __threadfence();
+                named_bar_sync_128();
+                if (tid == 0) *ticket_s = atomicAdd(&a.counters[req * Hkv + seg.kv_head], 1u);
+                named_bar_sync_128();
+                const bool last = *ticket_s == seg.n_parts - 1u;
+                named_bar_sync_128();  // ticket_s may be rewritten by the next run
+                if (last) {
+                    __threadfence();
+#pragma unroll
+                    for (int h = 0; h < G; ++h) {
+                        float M = -INFINITY;
+                        for (uint32_t s2 = 0; s2 < seg.n_parts; ++s2)
+                            M = fmaxf(M, __ldcg(&a.part_ml[(size_t(seg.first_slot + s2) * G + h) * 2]));
+                        float Ls = 0.0f, Os = 0.0f;
+                        for (uint32_t s2 = 0; s2 < seg.n_parts; ++s2) {
+                            const size_t pr = size_t(seg.first_slot + s2) * G + h;
+                            const float ms = __ldcg(&a.part_ml[pr * 2]);
+                            if (ms == -INFINITY) continue;
+                            const float sc = exp2f(ms - M);
+                            Ls = fmaf(sc, __ldcg(&a.part_ml[pr * 2 + 1]), Ls);
+                            Os = fmaf(sc, __ldcg(&a.part_o[pr * kTcD + d]), Os);
+                        }
+                        if (state_mode) {
+                            a.state_o[(row0 + h) * kTcD + d] = Os;
+                            if (d == 0) {
+                                a.state_m[row0 + h] = M / kTcLog2e;
+                                a.state_l[row0 + h] = Ls;
+                            }
+                        } else {
+                            reinterpret_cast<uint16_t*>(a.out)[(row0 + h) * kTcD + d] = T::store(Os / fmaxf(Ls, 1e-12f));
+                        }
+                    }
+                    if (tid == 0) a.counters[req * Hkv + seg.kv_head] = 0u;
+                }
+            }
+        }
+        if (!ok && lane == 0) {
+            atomicMax(a.status, uint32_t(KRIYA_DEV_WAIT_EXPIRED));
+            *abort_flag = 1;
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 5) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, kTcTmemCols);
+    }
+}
+
+template <int G, typename T>
+cudaError_t launch_tc_t(const TcParams& pp, const CUtensorMap& mk, const CUtensorMap& mv, uint32_t grid, int max_smem_optin,
+                        cudaStream_t s) {
+    const size_t smem = size_t(2 * kTcStages) * kTcKvBytes + 3 * kTcQBytes + kTcPBytes + 256 + 256 + 1024;
+    if (smem > size_t(max_smem_optin)) return cudaErrorInvalidValue;
+    auto kern = decode_tc_kernel<G, T>;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+        if (e != cudaSuccess) return e;
+        attr_set = true;
+    }
+    kern<<<grid, kTcThreads, smem, s>>>(mk, mv, pp);
+    return cudaGetLastError();
+}
+
+template <typename T>
+cudaError_t launch_tc_g(uint32_t group, const TcParams& pp, const CUtensorMap& mk, const CUtensorMap& mv, uint32_t grid,
+                        int max_smem_optin, cudaStream_t s) {
+    switch (group) {
+        case 1: return launch_tc_t<1, T>(pp, mk, mv, grid, max_smem_optin, s);
+        case 2: return launch_tc_t<2, T>(pp, mk, mv, grid, max_smem_optin, s);
+        case 3: return launch_tc_t<3, T>(pp, mk, mv, grid, max_smem_optin, s);
+        case 4: return launch_tc_t<4, T>(pp, mk, mv, grid, max_smem_optin, s);
+        case 5: return launch_tc_t<5, T>(pp, mk, mv, grid, max_smem_optin, s);
+        case 6: return launch_tc_t<6, T>(pp, mk, mv, grid, max_smem_optin, s);
+        case 7: return launch_tc_t<7, T>(pp, mk, mv, grid, max_smem_optin, s);
+        case 8: return launch_tc_t<8, T>(pp, mk, mv, grid, max_smem_optin, s);
+        default: return cudaErrorInvalidValue;
+    }
+}
+
+}  // namespace kriya
+
+bool kriya_decode_tc_supported(uint32_t head_dim, uint32_t group, uint32_t block_size) {
+    return head_dim == uint32_t(kriya::kTcD) && group >= 1 && group <= 8 && block_size == uint32_t(kriya::kTcPage);
+}
+
+cudaError_t kriya_launch_decode_tc(const KriyaDecodeArgs& a, const KriyaTcSeg* segs, const uint32_t* cta_seg_ptr, uint32_t grid,
+                                   const void* map_k, const void* map_v, uint32_t layer_row0, uint32_t dtype,
+                                   int max_smem_optin, cudaStream_t s) {
+    if (grid == 0) return cudaSuccess;
+    const uint32_t group = a.num_q_heads / a.num_kv_heads;
+    if (!kriya_decode_tc_supported(kriya::kTcD, group, kriya::kTcPage) || !map_k || !map_v) return cudaErrorInvalidValue;
+    kriya::TcParams pp;
+    pp.a = a;
+    pp.segs = segs;
+    pp.cta_seg_ptr = cta_seg_ptr;
+    pp.layer_row0 = layer_row0;
+    const CUtensorMap& mk = *static_cast<const CUtensorMap*>(map_k);
+    const CUtensorMap& mv = *static_cast<const CUtensorMap*>(map_v);
+    return dtype == KRIYA_DTYPE_FP16 ? kriya::launch_tc_g<kriya::Fp16>(group, pp, mk, mv, grid, max_smem_optin, s)
+                                     : kriya::launch_tc_g<kriya::Bf16>(group, pp, mk, mv, grid, max_smem_optin, s);
+}

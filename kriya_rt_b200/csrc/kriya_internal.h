@@ -25,6 +25,20 @@ struct KriyaDecodeWork {
 };
 static_assert(sizeof(KriyaDecodeWork) == 32, "work item is 32 bytes");
 
+// One piece of a (plan row, KV head) run for the tensor-core decode kernel: logical blocks [blk_lo, blk_hi).
+// Pieces of one run occupy scratch slots [first_slot, first_slot + n_parts).
+struct KriyaTcSeg {
+    uint32_t req;
+    uint32_t kv_head;
+    uint32_t blk_lo;
+    uint32_t blk_hi;
+    uint32_t slot;
+    uint32_t first_slot;
+    uint32_t n_parts;
+    uint32_t _pad;
+};
+static_assert(sizeof(KriyaTcSeg) == 32, "segment record is 32 bytes");
+
 // Device status word values written by kernels instead of trapping.
 enum : uint32_t {
     KRIYA_DEV_OK = 0,
@@ -61,7 +75,9 @@ struct kriya_cuda_ctx {
     uint8_t* d_plan = nullptr;
     size_t plan_bytes = 0;
     size_t off_indptr = 0, off_indices = 0, off_last_len = 0, off_tiles = 0, off_positions = 0, off_work = 0,
-           off_range = 0;
+           off_range = 0, off_tcseg = 0, off_tcptr = 0, off_tcseg2 = 0, off_tcptr2 = 0;
+    uint32_t cap_seg = 0, n_seg = 0;
+    int decode_path = 0;  // 0: pick per shape, 1: CUDA-core kernel, 2: tensor-core kernel
     uint32_t cap_rows = 0, cap_indices = 0, cap_tiles = 0, cap_tokens = 0, cap_work = 0;
     // current plan (host copy of the sizes and of what later calls need)
     bool plan_valid = false;
@@ -166,6 +182,11 @@ struct KriyaDecodeArgs {
 cudaError_t kriya_launch_decode(const KriyaDecodeArgs& a, uint32_t head_dim, uint32_t block_size, uint32_t dtype,
                                 int max_smem_optin, cudaStream_t s);
 bool kriya_decode_supported(uint32_t head_dim, uint32_t group, uint32_t num_kv_heads, uint32_t block_size);
+
+bool kriya_decode_tc_supported(uint32_t head_dim, uint32_t group, uint32_t block_size);
+cudaError_t kriya_launch_decode_tc(const KriyaDecodeArgs& a, const KriyaTcSeg* segs, const uint32_t* cta_seg_ptr, uint32_t grid,
+                                   const void* map_k, const void* map_v, uint32_t layer_row0, uint32_t dtype,
+                                   int max_smem_optin, cudaStream_t s);
 
 cudaError_t kriya_launch_merge_states(const float* m, const float* l, const float* o, uint32_t parts, uint32_t rows,
                                       uint32_t D, void* out, uint32_t dtype, cudaStream_t s);

@@ -198,6 +198,10 @@ class CudaExecutor:
         self._check(self._lib.kriya_cuda_decode_step_host(self._h, _ptr(q_host), _ptr(k_host), _ptr(v_host),
                                                           _ptr(out_host), rows, C.byref(rope), C.byref(gqa)))
 
+    def set_decode_path(self, path: int) -> None:
+        """0 = by shape, 1 = CUDA-core decode kernel, 2 = tensor-core decode kernel."""
+        self._check(self._lib.kriya_cuda_set_decode_path(self._h, path))
+
     def timing_enable(self, enable: bool) -> None:
         self._check(self._lib.kriya_cuda_timing_enable(self._h, int(enable)))
 
