@@ -56,6 +56,19 @@ struct TcParams {
 };
 
 __device__ __forceinline__ void named_bar_sync_128() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+// Barrier over the 128 softmax threads that also ORs a predicate across them.
+__device__ __forceinline__ bool bar_or_128(bool pred) {
+    uint32_t res;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "setp.ne.u32 q, %1, 0;\n\t"
+        "bar.red.or.pred p, 1, 128, q;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(res)
+        : "r"(uint32_t(pred))
+        : "memory");
+    return res != 0;
+}
 
 template <int G, typename T>
 __global__ void __launch_bounds__(kTcThreads, 1)
@@ -70,15 +83,15 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
     uint8_t* sK = sm;                                   // [stages][32 KB]
     uint8_t* sV = sK + kTcStages * kTcKvBytes;          // [stages][32 KB]
     uint8_t* sQ = sV + kTcStages * kTcKvBytes;          // [3][4 KB]
-    uint8_t* sP = sQ + 3 * kTcQBytes;                   // 4 KB
-    float* red = reinterpret_cast<float*>(sP + kTcPBytes);  // [4 warps][16]
+    uint8_t* sP = sQ + 3 * kTcQBytes;                   // [2][4 KB]
+    float* red = reinterpret_cast<float*>(sP + 2 * kTcPBytes);  // [4 warps][16]
     uint64_t* bars = reinterpret_cast<uint64_t*>(red + 64);
     uint64_t* kv_full = bars;                     // [stages]
     uint64_t* kv_empty = bars + kTcStages;        // [stages]
     uint64_t* s_full = bars + 2 * kTcStages;      // [2]
-    uint64_t* p_ready = bars + 2 * kTcStages + 2; // 128 arrivals
-    uint64_t* pv_done = bars + 2 * kTcStages + 3;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kTcStages + 4);
+    uint64_t* p_ready = bars + 2 * kTcStages + 2; // [2], 128 arrivals each; tile g uses p_ready[g & 1]
+    uint64_t* pv_done = bars + 2 * kTcStages + 4; // [2]; P.V of tile g commits to pv_done[g & 1]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kTcStages + 6);
     volatile uint32_t* abort_flag = tmem_slot + 1;
     uint32_t* ticket_s = tmem_slot + 2;
 
@@ -94,8 +107,10 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
         }
         mbar_init(&s_full[0], 1);
         mbar_init(&s_full[1], 1);
-        mbar_init(p_ready, 128);
-        mbar_init(pv_done, 1);
+        mbar_init(&p_ready[0], 128);
+        mbar_init(&p_ready[1], 128);
+        mbar_init(&pv_done[0], 1);
+        mbar_init(&pv_done[1], 1);
         *abort_flag = 0;
         mbar_fence_init();
     }
@@ -105,7 +120,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
     }
     // zero the K/V ring, the Q buffers and the P tile once: rows and pages that are never loaded must read as
     // finite values, and the padding heads of Q and P must be zero
-    for (uint32_t i = tid; i < (2 * kTcStages * kTcKvBytes + 3 * kTcQBytes + kTcPBytes) / 16; i += kTcThreads)
+    for (uint32_t i = tid; i < (2 * kTcStages * kTcKvBytes + 3 * kTcQBytes + 2 * kTcPBytes) / 16; i += kTcThreads)
         reinterpret_cast<uint4*>(sK)[i] = make_uint4(0u, 0u, 0u, 0u);
     fence_async_smem();
     tc_fence_before();
@@ -232,7 +247,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
                 if (*abort_flag) { ok = false; break; }
                 ok = la_issue();  // S^T of tile g+1 (possibly of the next run) before P.V of tile g
                 if (!ok) break;
-                ok = warp_wait(p_ready, g & 1u);
+                ok = warp_wait(&p_ready[g & 1u], (g >> 1) & 1u);
                 if (!ok) break;
                 tc_fence_after();
                 if (lane == 0) {
@@ -240,12 +255,12 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
 #pragma unroll
                     for (int ks = 0; ks < kTcTile / 16; ++ks) {
                         const uint32_t a_off = stage * kTcKvBytes + uint32_t(ks) * (kTcPage * 128);
-                        const uint32_t b_off = uint32_t(ks / 4) * 2048u + uint32_t(ks % 4) * 32u;
+                        const uint32_t b_off = (g & 1u) * kTcPBytes + uint32_t(ks / 4) * 2048u + uint32_t(ks % 4) * 32u;
                         umma_f16(tmem_base + kColO, smem_desc_sw128(v_addr + a_off, kTcPanel, 1024),
                                  smem_desc_sw128(p_addr + b_off, 16, 1024), IDESC_O, (t > t0 || ks > 0) ? 1u : 0u);
                     }
                     umma_commit(&kv_empty[stage]);
-                    umma_commit(pv_done);
+                    umma_commit(&pv_done[g & 1u]);
                 }
                 __syncwarp();
             }
@@ -286,63 +301,74 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
                 tmem_wait_ld();
                 const uint32_t tok = t * kTcTile + tid;
                 const bool valid = tok >= tok_lo && tok < tok_hi;
-                float s[G], mx[G];
+                float s[G];
+                bool over = false;  // does this token push some head's score past the exponent reference?
 #pragma unroll
                 for (int h = 0; h < G; ++h) {
                     float x = __uint_as_float(r[h]) * scale2;
                     if (softcap) x = tanhf(fminf(fmaxf(x / a.logit_softcap, -15.0f), 15.0f)) * a.logit_softcap * kTcLog2e;
                     s[h] = valid ? x : -INFINITY;
-                    mx[h] = s[h];
+                    over = over || (s[h] > m_used[h] + kTcRescale);
                 }
-#pragma unroll
-                for (int off = 16; off >= 1; off >>= 1)
-#pragma unroll
-                    for (int h = 0; h < G; ++h) mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xFFFFFFFFu, mx[h], off));
-                // `red` is free: its previous readers passed the second barrier of the previous tile
-                if (lane == 0) {
-#pragma unroll
-                    for (int h = 0; h < G; ++h) red[warp * 16 + h] = mx[h];
-                }
-                named_bar_sync_128();
-                bool need = false;
+                // One barrier-with-OR tells all 128 threads whether any score in the tile outgrew its reference.
+                // Only then (first tile of a run, or a jump of more than 2^8) is the per-head column maximum
+                // reduced and the accumulator rescaled; otherwise the reference is kept, which is exact.
                 float alpha[G];
 #pragma unroll
-                for (int h = 0; h < G; ++h) {
-                    const float m_tile = fmaxf(fmaxf(red[h], red[16 + h]), fmaxf(red[32 + h], red[48 + h]));
-                    alpha[h] = 1.0f;
-                    if (m_tile > m_used[h] + kTcRescale || (m_used[h] == -INFINITY && m_tile > -INFINITY)) {
-                        alpha[h] = (m_used[h] == -INFINITY) ? 0.0f : exp2f(m_used[h] - m_tile);
-                        m_used[h] = m_tile;
-                        need = need || (t > t0);
-                    }
-                }
-                named_bar_sync_128();  // everyone has read `red`
-                // the previous P.V must be complete before P is overwritten or O^T rescaled
-                if (g > 0) {
-                    ok = warp_wait(pv_done, (g - 1u) & 1u);
-                    if (!ok) break;
-                    tc_fence_after();
-                }
-                if (need) {  // uniform across the 128 threads: every thread computed the same maxima
-                    uint32_t o[16];
-                    tmem_ld16(tmem_base + lane_addr + kColO, o);
-                    tmem_wait_ld();
+                for (int h = 0; h < G; ++h) alpha[h] = 1.0f;
+                if (bar_or_128(over)) {
+                    float mx[G];
 #pragma unroll
-                    for (int h = 0; h < G; ++h) o[h] = __float_as_uint(__uint_as_float(o[h]) * alpha[h]);
-                    tmem_st16(tmem_base + lane_addr + kColO, o);
-                    tmem_wait_st();
+                    for (int h = 0; h < G; ++h) mx[h] = s[h];
+#pragma unroll
+                    for (int off = 16; off >= 1; off >>= 1)
+#pragma unroll
+                        for (int h = 0; h < G; ++h) mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xFFFFFFFFu, mx[h], off));
+                    if (lane == 0) {
+#pragma unroll
+                        for (int h = 0; h < G; ++h) red[warp * 16 + h] = mx[h];
+                    }
+                    named_bar_sync_128();
+#pragma unroll
+                    for (int h = 0; h < G; ++h) {
+                        const float m_tile = fmaxf(fmaxf(red[h], red[16 + h]), fmaxf(red[32 + h], red[48 + h]));
+                        if (m_tile > m_used[h]) {
+                            alpha[h] = (m_used[h] == -INFINITY) ? 0.0f : exp2f(m_used[h] - m_tile);
+                            m_used[h] = m_tile;
+                        }
+                    }
+                    named_bar_sync_128();  // everyone has read `red`
+                    if (t > t0) {
+                        // O^T holds earlier tiles: the previous P.V must be complete before it is rescaled
+                        ok = warp_wait(&pv_done[(g - 1u) & 1u], ((g - 1u) >> 1) & 1u);
+                        if (!ok) break;
+                        tc_fence_after();
+                        uint32_t o[16];
+                        tmem_ld16(tmem_base + lane_addr + kColO, o);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int h = 0; h < G; ++h) o[h] = __float_as_uint(__uint_as_float(o[h]) * alpha[h]);
+                        tmem_st16(tmem_base + lane_addr + kColO, o);
+                        tmem_wait_st();
+                    }
+#pragma unroll
+                    for (int h = 0; h < G; ++h) l_lane[h] *= alpha[h];
+                }
+                // P buffer g&1 was last read by P.V of tile g-2
+                if (g >= 2) {
+                    ok = warp_wait(&pv_done[g & 1u], ((g >> 1) - 1u) & 1u);
+                    if (!ok) break;
                 }
                 // probabilities of this token for the G heads -> P[h][token] (K-major, swizzled)
                 {
-                    const uint32_t tt = tid;  // token inside the tile
-                    const uint32_t panel = tt >> 6, col = tt & 63u;
+                    uint8_t* pbuf = sP + (g & 1u) * kTcPBytes;
+                    const uint32_t panel = tid >> 6, col = tid & 63u;
 #pragma unroll
                     for (int h = 0; h < G; ++h) {
                         const float p = (s[h] == -INFINITY) ? 0.0f : fast_exp2(s[h] - m_used[h]);
-                        const uint16_t pb = T::store(p);
-                        l_lane[h] = l_lane[h] * alpha[h] + T::load(pb);
-                        *reinterpret_cast<uint16_t*>(sP + panel * 2048u + uint32_t(h) * 128u +
-                                                     ((((col >> 3) ^ (uint32_t(h) & 7u)) << 4) | ((col & 7u) << 1))) = pb;
+                        l_lane[h] += p;
+                        *reinterpret_cast<uint16_t*>(pbuf + panel * 2048u + uint32_t(h) * 128u +
+                                                     ((((col >> 3) ^ (uint32_t(h) & 7u)) << 4) | ((col & 7u) << 1))) = T::store(p);
                     }
                 }
                 // a token outside the run (past the row end, outside the block range, or a page that was not
@@ -358,7 +384,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
                 }
                 tc_fence_before();
                 fence_async_smem();
-                mbar_arrive(p_ready);
+                mbar_arrive(&p_ready[g & 1u]);
             }
             if (!ok) break;
             // ---- end of the run piece: total l per head, then O^T / l or the partial state ----------------
@@ -381,7 +407,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
 #pragma unroll
             for (int h = 0; h < 16; ++h) o[h] = 0u;
             if (!empty) {
-                ok = warp_wait(pv_done, (g - 1u) & 1u);
+                ok = warp_wait(&pv_done[(g - 1u) & 1u], ((g - 1u) >> 1) & 1u);
                 if (!ok) break;
                 tc_fence_after();
                 tmem_ld16(tmem_base + lane_addr + kColO, o);
@@ -467,7 +493,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
 template <int G, typename T>
 cudaError_t launch_tc_t(const TcParams& pp, const CUtensorMap& mk, const CUtensorMap& mv, uint32_t grid, int max_smem_optin,
                         cudaStream_t s) {
-    const size_t smem = size_t(2 * kTcStages) * kTcKvBytes + 3 * kTcQBytes + kTcPBytes + 256 + 256 + 1024;
+    const size_t smem = size_t(2 * kTcStages) * kTcKvBytes + 3 * kTcQBytes + 2 * kTcPBytes + 256 + 256 + 1024;
     if (smem > size_t(max_smem_optin)) return cudaErrorInvalidValue;
     auto kern = decode_tc_kernel<G, T>;
     static bool attr_set = false;
