@@ -330,19 +330,36 @@ __global__ void __launch_bounds__(kDecodeThreadsMax, 1) decode_kernel(KriyaDecod
     __syncthreads();
     if (*ticket_s != w.n_parts - 1u) return;
     __threadfence();
+    // Parts are merged eight at a time with all of a chunk's loads issued before any is used, so the merge costs
+    // about one memory round trip per chunk rather than one per part.
     for (int e = int(tid); e < HQC * D; e += int(blockDim.x)) {
         const int hq = e / D, d = e % D;
-        float M = -INFINITY;
-        for (uint32_t s = 0; s < w.n_parts; ++s)
-            M = fmaxf(M, __ldcg(&a.part_ml[(size_t(w.first_slot + s) * a.num_q_heads + hq) * 2]));
-        float Ls = 0.0f, Os = 0.0f;
-        for (uint32_t s = 0; s < w.n_parts; ++s) {
-            const size_t prow = size_t(w.first_slot + s) * a.num_q_heads + hq;
-            const float ms = __ldcg(&a.part_ml[prow * 2]);
-            if (ms == -INFINITY) continue;
-            const float sc = exp2f(ms - M);
-            Ls = fmaf(sc, __ldcg(&a.part_ml[prow * 2 + 1]), Ls);
-            Os = fmaf(sc, __ldcg(&a.part_o[prow * D + d]), Os);
+        float M = -INFINITY, Ls = 0.0f, Os = 0.0f;
+        for (uint32_t c0 = 0; c0 < w.n_parts; c0 += 8u) {
+            const uint32_t cnt = min(8u, w.n_parts - c0);
+            float mv[8], lv[8], ov[8];
+#pragma unroll
+            for (int s = 0; s < 8; ++s) {
+                const bool on = uint32_t(s) < cnt;
+                const size_t prow = size_t(w.first_slot + c0 + (on ? s : 0)) * a.num_q_heads + hq;
+                mv[s] = on ? __ldcg(&a.part_ml[prow * 2]) : -INFINITY;
+                lv[s] = on ? __ldcg(&a.part_ml[prow * 2 + 1]) : 0.0f;
+                ov[s] = on ? __ldcg(&a.part_o[prow * D + d]) : 0.0f;
+            }
+            float mc = M;
+#pragma unroll
+            for (int s = 0; s < 8; ++s) mc = fmaxf(mc, mv[s]);
+            if (mc == -INFINITY) continue;
+            const float keep = (M == -INFINITY) ? 0.0f : exp2f(M - mc);
+            Ls *= keep;
+            Os *= keep;
+#pragma unroll
+            for (int s = 0; s < 8; ++s) {
+                const float wgt = (mv[s] == -INFINITY) ? 0.0f : exp2f(mv[s] - mc);
+                Ls = fmaf(wgt, lv[s], Ls);
+                Os = fmaf(wgt, ov[s], Os);
+            }
+            M = mc;
         }
         const size_t row = size_t(req) * a.num_q_heads + hq;
         if (state_mode) {

@@ -84,8 +84,8 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
     uint8_t* sV = sK + kTcStages * kTcKvBytes;          // [stages][32 KB]
     uint8_t* sQ = sV + kTcStages * kTcKvBytes;          // [3][4 KB]
     uint8_t* sP = sQ + 3 * kTcQBytes;                   // [2][4 KB]
-    float* red = reinterpret_cast<float*>(sP + 2 * kTcPBytes);  // [4 warps][16]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(red + 64);
+    float* red = reinterpret_cast<float*>(sP + 2 * kTcPBytes);  // [4 warps][16] / merge staging [8][G][2]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(red + 128);
     uint64_t* kv_full = bars;                     // [stages]
     uint64_t* kv_empty = bars + kTcStages;        // [stages]
     uint64_t* s_full = bars + 2 * kTcStages;      // [2]
@@ -447,29 +447,65 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
                 const bool last = *ticket_s == seg.n_parts - 1u;
                 named_bar_sync_128();  // ticket_s may be rewritten by the next run
                 if (last) {
+                    // Merge the run's parts, eight at a time.  All loads of a chunk are issued before any is used
+                    // (the loop over parts is unrolled with predicates), so the merge costs about one memory round
+                    // trip per chunk instead of one per part and head.
                     __threadfence();
+                    float M[G], Ls[G], Os[G];
 #pragma unroll
                     for (int h = 0; h < G; ++h) {
-                        float M = -INFINITY;
-                        for (uint32_t s2 = 0; s2 < seg.n_parts; ++s2)
-                            M = fmaxf(M, __ldcg(&a.part_ml[(size_t(seg.first_slot + s2) * G + h) * 2]));
-                        float Ls = 0.0f, Os = 0.0f;
-                        for (uint32_t s2 = 0; s2 < seg.n_parts; ++s2) {
-                            const size_t pr = size_t(seg.first_slot + s2) * G + h;
-                            const float ms = __ldcg(&a.part_ml[pr * 2]);
-                            if (ms == -INFINITY) continue;
-                            const float sc = exp2f(ms - M);
-                            Ls = fmaf(sc, __ldcg(&a.part_ml[pr * 2 + 1]), Ls);
-                            Os = fmaf(sc, __ldcg(&a.part_o[pr * kTcD + d]), Os);
+                        M[h] = -INFINITY;
+                        Ls[h] = 0.0f;
+                        Os[h] = 0.0f;
+                    }
+                    for (uint32_t c0 = 0; c0 < seg.n_parts; c0 += 8u) {
+                        const uint32_t cnt = min(8u, seg.n_parts - c0);
+                        // stage (m, l) of the chunk: [part][head][2]
+                        if (tid < cnt * uint32_t(G) * 2u)
+                            red[tid] = __ldcg(&a.part_ml[size_t(seg.first_slot + c0) * G * 2 + tid]);
+                        float ov[8][G];
+#pragma unroll
+                        for (int s2 = 0; s2 < 8; ++s2)
+#pragma unroll
+                            for (int h = 0; h < G; ++h)
+                                ov[s2][h] = (uint32_t(s2) < cnt)
+                                                ? __ldcg(&a.part_o[(size_t(seg.first_slot + c0 + s2) * G + h) * kTcD + d])
+                                                : 0.0f;
+                        named_bar_sync_128();
+#pragma unroll
+                        for (int h = 0; h < G; ++h) {
+                            float mc = M[h];
+#pragma unroll
+                            for (int s2 = 0; s2 < 8; ++s2)
+                                if (uint32_t(s2) < cnt) mc = fmaxf(mc, red[(s2 * G + h) * 2]);
+                            if (mc == -INFINITY) continue;
+                            const float keep = (M[h] == -INFINITY) ? 0.0f : exp2f(M[h] - mc);
+                            float lacc = Ls[h] * keep, oacc = Os[h] * keep;
+#pragma unroll
+                            for (int s2 = 0; s2 < 8; ++s2) {
+                                if (uint32_t(s2) < cnt) {
+                                    const float ms = red[(s2 * G + h) * 2];
+                                    const float w = (ms == -INFINITY) ? 0.0f : exp2f(ms - mc);
+                                    lacc = fmaf(w, red[(s2 * G + h) * 2 + 1], lacc);
+                                    oacc = fmaf(w, ov[s2][h], oacc);
+                                }
+                            }
+                            M[h] = mc;
+                            Ls[h] = lacc;
+                            Os[h] = oacc;
                         }
+                        named_bar_sync_128();  // `red` is rewritten by the next chunk / the next tile
+                    }
+#pragma unroll
+                    for (int h = 0; h < G; ++h) {
                         if (state_mode) {
-                            a.state_o[(row0 + h) * kTcD + d] = Os;
+                            a.state_o[(row0 + h) * kTcD + d] = Os[h];
                             if (d == 0) {
-                                a.state_m[row0 + h] = M / kTcLog2e;
-                                a.state_l[row0 + h] = Ls;
+                                a.state_m[row0 + h] = M[h] / kTcLog2e;
+                                a.state_l[row0 + h] = Ls[h];
                             }
                         } else {
-                            reinterpret_cast<uint16_t*>(a.out)[(row0 + h) * kTcD + d] = T::store(Os / fmaxf(Ls, 1e-12f));
+                            reinterpret_cast<uint16_t*>(a.out)[(row0 + h) * kTcD + d] = T::store(Os[h] / fmaxf(Ls[h], 1e-12f));
                         }
                     }
                     if (tid == 0) a.counters[req * Hkv + seg.kv_head] = 0u;
@@ -493,7 +529,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
 template <int G, typename T>
 cudaError_t launch_tc_t(const TcParams& pp, const CUtensorMap& mk, const CUtensorMap& mv, uint32_t grid, int max_smem_optin,
                         cudaStream_t s) {
-    const size_t smem = size_t(2 * kTcStages) * kTcKvBytes + 3 * kTcQBytes + 2 * kTcPBytes + 256 + 256 + 1024;
+    const size_t smem = size_t(2 * kTcStages) * kTcKvBytes + 3 * kTcQBytes + 2 * kTcPBytes + 512 + 256 + 1024;
     if (smem > size_t(max_smem_optin)) return cudaErrorInvalidValue;
     auto kern = decode_tc_kernel<G, T>;
     static bool attr_set = false;
