@@ -101,8 +101,9 @@ uint32_t build_work(const int32_t* indptr, uint32_t rows, const uint32_t* begin,
 // Tensor-core decode work: every (row, KV head) is a run of 128-token tiles; the runs laid end to end are cut
 // into `ctas` equal contiguous pieces.  Returns the number of segment records, or UINT32_MAX when `cap` is too
 // small.  `ptr` receives ctas + 1 offsets into `out`.
-uint32_t build_tc_segments(const int32_t* indptr, uint32_t rows, uint32_t hkv, const uint32_t* begin, const uint32_t* end,
-                           uint32_t ctas, KriyaTcSeg* out, uint32_t cap, uint32_t* ptr) {
+uint32_t build_tc_segments(const int32_t* indptr, const int32_t* last_len, uint32_t block_size, uint32_t rows, uint32_t hkv,
+                           const uint32_t* begin, const uint32_t* end, uint32_t ctas, KriyaTcSeg* out, uint32_t cap,
+                           uint32_t* ptr) {
     const uint32_t TP = 8;  // pages per tile
     uint64_t total = 0;
     for (uint32_t r = 0; r < rows; ++r) {
@@ -119,10 +120,12 @@ uint32_t build_tc_segments(const int32_t* indptr, uint32_t rows, uint32_t hkv, c
         const uint32_t nb = uint32_t(indptr[r + 1] - indptr[r]);
         const uint32_t b = begin ? std::min(begin[r], nb) : 0u;
         const uint32_t e = end ? std::min(end[r], nb) : nb;
+        const uint32_t tbl = uint32_t(indptr[r]);
+        const uint32_t row_tokens = nb ? (nb - 1u) * block_size + uint32_t(std::max(last_len[r], 1)) : 0u;
         for (uint32_t h = 0; h < hkv; ++h) {
             if (e <= b) {  // empty run: one zero-length record so that its output is still written
                 if (n + 1 > cap) return UINT32_MAX;
-                out[n++] = KriyaTcSeg{r, h, b, b, slot, slot, 1u, 0u};
+                out[n++] = KriyaTcSeg{r, h, b, b, slot, slot, 1u, tbl, row_tokens, {0u, 0u, 0u}};
                 slot += 1;
                 continue;
             }
@@ -134,7 +137,8 @@ uint32_t build_tc_segments(const int32_t* indptr, uint32_t rows, uint32_t hkv, c
                 const uint64_t room = cta + 1 < ctas ? cta_end(cta) - unit : uint64_t(t1 - t);
                 const uint32_t take = uint32_t(std::min<uint64_t>(room, t1 - t));
                 if (n + 1 > cap) return UINT32_MAX;
-                out[n++] = KriyaTcSeg{r, h, std::max(b, t * TP), std::min(e, (t + take) * TP), slot++, first_slot, 0u, 0u};
+                out[n++] = KriyaTcSeg{r, h, std::max(b, t * TP), std::min(e, (t + take) * TP), slot++, first_slot, 0u, tbl,
+                                      row_tokens, {0u, 0u, 0u}};
                 t += take;
                 unit += take;
             }
@@ -575,7 +579,8 @@ int32_t kriya_cuda_plan_upload(kriya_cuda_ctx* c, const int32_t* indptr, size_t 
     const uint32_t n_work =
         build_work(indptr, uint32_t(rows), nullptr, nullptr, 2u * uint32_t(c->sm_count), 2u, work, c->cap_work);
     if (n_work == UINT32_MAX) return invalid("plan needs more decode work items than the context holds");
-    const uint32_t n_seg = build_tc_segments(indptr, uint32_t(rows), c->cfg.num_kv_heads, nullptr, nullptr, uint32_t(c->sm_count),
+    const uint32_t n_seg = build_tc_segments(indptr, last_len, c->cfg.block_size_tokens, uint32_t(rows), c->cfg.num_kv_heads, nullptr,
+                                             nullptr, uint32_t(c->sm_count),
                                              reinterpret_cast<KriyaTcSeg*>(h + c->off_tcseg), c->cap_seg,
                                              reinterpret_cast<uint32_t*>(h + c->off_tcptr));
     if (n_seg == UINT32_MAX) return invalid("plan needs more decode segments than the context holds");
@@ -678,8 +683,9 @@ int32_t kriya_cuda_paged_gqa_decode_partial(kriya_cuda_ctx* c, uint32_t layer, c
                                       cudaMemcpyHostToDevice, c->stream));
     auto* segs = reinterpret_cast<KriyaTcSeg*>(c->h_plan_last + c->off_tcseg2);
     auto* sptr = reinterpret_cast<uint32_t*>(c->h_plan_last + c->off_tcptr2);
-    const uint32_t n_seg = build_tc_segments(indptr, c->n_rows, c->cfg.num_kv_heads, blk_begin, blk_end, uint32_t(c->sm_count),
-                                             segs, c->cap_seg, sptr);
+    const uint32_t n_seg = build_tc_segments(indptr, reinterpret_cast<const int32_t*>(c->h_plan_last + c->off_last_len),
+                                             c->cfg.block_size_tokens, c->n_rows, c->cfg.num_kv_heads, blk_begin, blk_end,
+                                             uint32_t(c->sm_count), segs, c->cap_seg, sptr);
     if (n_seg == UINT32_MAX) return c->fail(KRIYA_CUDA_INVALID_INPUT, "ranges need more segments than the context holds");
     KRIYA_CUDA_TRY(c, cudaMemcpyAsync(c->d_plan + c->off_tcptr2, sptr, c->off_tcseg2 - c->off_tcptr2 + size_t(n_seg) * sizeof(KriyaTcSeg),
                                       cudaMemcpyHostToDevice, c->stream));

@@ -21,6 +21,8 @@
 //     of O^T).  Per tile: read 16 scores, mask tokens past the row end, column max by warp shuffles plus a
 //     4-warp exchange in shared memory, exp2, write P (storage dtype) into the swizzled operand tile, keep
 //     the running sum per lane, rescale O^T in TMEM only when a head's max moved by more than 2^8.
+//   - Warp 6 takes over the cross-CTA merge of a piece that is not the CTA's last one, so the softmax warps go
+//     straight on to the next run while partial states are published, ticketed and (if last) merged.
 //   - Every mbarrier wait is bounded; on expiry the kernel records a status word, abandons its piece,
 //     frees its TMEM and returns.
 //
@@ -37,7 +39,7 @@ constexpr int kTcTile = 128;          // tokens per tile
 constexpr int kTcPage = 16;
 constexpr int kTcPagesPerTile = kTcTile / kTcPage;
 constexpr int kTcStages = 3;
-constexpr int kTcThreads = 192;
+constexpr int kTcThreads = 224;  // warps 0-3 softmax, 4 producer, 5 MMA issuer, 6 deferred merge
 constexpr int kTcN = 16;              // MMA N: query heads of one KV head, zero padded
 constexpr float kTcLog2e = 1.4426950408889634f;
 constexpr float kTcRescale = 8.0f;
@@ -70,6 +72,74 @@ __device__ __forceinline__ bool bar_or_128(bool pred) {
     return res != 0;
 }
 
+// Merge of a run's partial states (m, l, o) from scratch into the output, by `nthreads` threads (128: the
+// softmax warps, synchronised on named barrier 1; 32: the merge warp).  Parts are taken eight at a time and all
+// loads of a chunk are issued before any is used, so a chunk costs about one memory round trip.
+template <int G, typename T>
+__device__ __forceinline__ void merge_run_parts(const KriyaDecodeArgs& a, const KriyaTcSeg& seg, float* stage, uint32_t t,
+                                                uint32_t nthreads, bool state_mode, size_t row0) {
+    auto sync = [&]() {
+        if (nthreads == 128u) named_bar_sync_128();
+        else __syncwarp();
+    };
+    for (uint32_t d = t; d < uint32_t(kTcD); d += nthreads) {
+        float M[G], Ls[G], Os[G];
+#pragma unroll
+        for (int h = 0; h < G; ++h) {
+            M[h] = -INFINITY;
+            Ls[h] = 0.0f;
+            Os[h] = 0.0f;
+        }
+        for (uint32_t c0 = 0; c0 < seg.n_parts; c0 += 8u) {
+            const uint32_t cnt = min(8u, seg.n_parts - c0);
+            for (uint32_t i = t; i < cnt * uint32_t(G) * 2u; i += nthreads)  // (m, l) of the chunk: [part][head][2]
+                stage[i] = __ldcg(&a.part_ml[size_t(seg.first_slot + c0) * G * 2 + i]);
+            float ov[8][G];
+#pragma unroll
+            for (int s2 = 0; s2 < 8; ++s2)
+#pragma unroll
+                for (int h = 0; h < G; ++h)
+                    ov[s2][h] = (uint32_t(s2) < cnt) ? __ldcg(&a.part_o[(size_t(seg.first_slot + c0 + s2) * G + h) * kTcD + d]) : 0.0f;
+            sync();
+#pragma unroll
+            for (int h = 0; h < G; ++h) {
+                float mc = M[h];
+#pragma unroll
+                for (int s2 = 0; s2 < 8; ++s2)
+                    if (uint32_t(s2) < cnt) mc = fmaxf(mc, stage[(s2 * G + h) * 2]);
+                if (mc == -INFINITY) continue;
+                const float keep = (M[h] == -INFINITY) ? 0.0f : exp2f(M[h] - mc);
+                float lacc = Ls[h] * keep, oacc = Os[h] * keep;
+#pragma unroll
+                for (int s2 = 0; s2 < 8; ++s2) {
+                    if (uint32_t(s2) < cnt) {
+                        const float ms = stage[(s2 * G + h) * 2];
+                        const float w = (ms == -INFINITY) ? 0.0f : exp2f(ms - mc);
+                        lacc = fmaf(w, stage[(s2 * G + h) * 2 + 1], lacc);
+                        oacc = fmaf(w, ov[s2][h], oacc);
+                    }
+                }
+                M[h] = mc;
+                Ls[h] = lacc;
+                Os[h] = oacc;
+            }
+            sync();  // `stage` is rewritten by the next chunk
+        }
+#pragma unroll
+        for (int h = 0; h < G; ++h) {
+            if (state_mode) {
+                a.state_o[(row0 + h) * kTcD + d] = Os[h];
+                if (d == 0) {
+                    a.state_m[row0 + h] = M[h] / kTcLog2e;
+                    a.state_l[row0 + h] = Ls[h];
+                }
+            } else {
+                reinterpret_cast<uint16_t*>(a.out)[(row0 + h) * kTcD + d] = T::store(Os[h] / fmaxf(Ls[h], 1e-12f));
+            }
+        }
+    }
+}
+
 template <int G, typename T>
 __global__ void __launch_bounds__(kTcThreads, 1)
 decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, TcParams pp) {
@@ -94,6 +164,8 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kTcStages + 6);
     volatile uint32_t* abort_flag = tmem_slot + 1;
     uint32_t* ticket_s = tmem_slot + 2;
+    volatile uint32_t* merge_job_ok = tmem_slot + 3;
+    float* merge_stage = reinterpret_cast<float*>(tmem_slot + 4);  // [8][G][2] floats for warp 6
 
     const KriyaDecodeArgs& a = pp.a;
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
@@ -112,22 +184,26 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
         mbar_init(&pv_done[0], 1);
         mbar_init(&pv_done[1], 1);
         *abort_flag = 0;
+        *merge_job_ok = 1;
         mbar_fence_init();
     }
     if (warp == 5) {
         tmem_alloc(tmem_slot, kTcTmemCols);
         tmem_relinquish();
     }
-    // zero the K/V ring, the Q buffers and the P tile once: rows and pages that are never loaded must read as
-    // finite values, and the padding heads of Q and P must be zero
-    for (uint32_t i = tid; i < (2 * kTcStages * kTcKvBytes + 3 * kTcQBytes + 2 * kTcPBytes) / 16; i += kTcThreads)
-        reinterpret_cast<uint4*>(sK)[i] = make_uint4(0u, 0u, 0u, 0u);
+    // The padding heads of the Q and P operand tiles must be zero.  The K/V ring needs no clearing: a K row
+    // that is never loaded only produces a score that is masked by selection, and the V row of every masked
+    // token is cleared by the softmax thread that owns it.
+    for (uint32_t i = tid; i < (3 * kTcQBytes + 2 * kTcPBytes) / 16; i += kTcThreads)
+        reinterpret_cast<uint4*>(sQ)[i] = make_uint4(0u, 0u, 0u, 0u);
     fence_async_smem();
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t Hq = a.num_q_heads, Hkv = a.num_kv_heads;
+    // the CTA's first piece is merged by warp 6 when it is one part of a split run and more pieces follow
+    const bool defer_first = seg_end - seg_begin > 1u && pp.segs[seg_begin].n_parts > 1u;
 
     if (warp == 4) {
         // ---- producer ---------------------------------------------------------------------------------
@@ -138,7 +214,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
             const KriyaTcSeg seg = pp.segs[si];
             const uint32_t t0 = seg.blk_lo / kTcPagesPerTile, t1 = (seg.blk_hi + kTcPagesPerTile - 1) / kTcPagesPerTile;
             if (seg.blk_hi <= seg.blk_lo) continue;
-            const int32_t* table = a.indices + a.indptr[seg.req];
+            const int32_t* table = a.indices + seg.tbl_off;
             for (uint32_t t = t0; t < t1; ++t, ++g) {
                 if (*abort_flag) { ok = false; break; }
                 const uint32_t stage = g % kTcStages;
@@ -269,6 +345,24 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
             atomicMax(a.status, uint32_t(KRIYA_DEV_WAIT_EXPIRED));
             *abort_flag = 1;
         }
+    } else if (warp == 6) {
+        // ---- deferred merge of the CTA's first piece -----------------------------------------------------
+        if (defer_first) {
+            const KriyaTcSeg seg = pp.segs[seg_begin];
+            asm volatile("bar.sync 2, 160;" ::: "memory");  // the softmax threads have published the partial state
+            if (*merge_job_ok) {
+                __threadfence();
+                uint32_t ticket = 0;
+                if (lane == 0) ticket = atomicAdd(&a.counters[seg.req * Hkv + seg.kv_head], 1u);
+                ticket = __shfl_sync(0xFFFFFFFFu, ticket, 0);
+                if (ticket == seg.n_parts - 1u) {
+                    __threadfence();
+                    merge_run_parts<G, T>(a, seg, merge_stage, lane, 32u, a.state_o != nullptr,
+                                          size_t(seg.req) * Hq + seg.kv_head * G);
+                    if (lane == 0) a.counters[seg.req * Hkv + seg.kv_head] = 0u;
+                }
+            }
+        }
     } else {
         // ---- softmax warps ----------------------------------------------------------------------------------
         const uint32_t lane_addr = (warp * 32u) << 16;
@@ -277,11 +371,11 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
         const bool state_mode = a.state_o != nullptr;
         uint32_t g = 0;
         bool ok = true;
+        bool handed_off = false;
         for (uint32_t si = seg_begin; si < seg_end && ok; ++si) {
             const KriyaTcSeg seg = pp.segs[si];
             const uint32_t req = seg.req;
-            const uint32_t nb = uint32_t(max(a.indptr[req + 1] - a.indptr[req], 0));
-            const uint32_t row_tokens = nb ? (nb - 1u) * kTcPage + uint32_t(max(a.last_len[req], 1)) : 0u;
+            const uint32_t row_tokens = seg.row_tokens;
             const uint32_t tok_lo = seg.blk_lo * kTcPage, tok_hi = min(seg.blk_hi * kTcPage, row_tokens);
             const uint32_t t0 = seg.blk_lo / kTcPagesPerTile, t1 = (seg.blk_hi + kTcPagesPerTile - 1) / kTcPagesPerTile;
             const bool empty = seg.blk_hi <= seg.blk_lo;
@@ -440,77 +534,31 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
                         a.part_ml[(prow + h) * 2 + 1] = l_tot[h];
                     }
                 }
-                __threadfence();
-                named_bar_sync_128();
-                if (tid == 0) *ticket_s = atomicAdd(&a.counters[req * Hkv + seg.kv_head], 1u);
-                named_bar_sync_128();
-                const bool last = *ticket_s == seg.n_parts - 1u;
-                named_bar_sync_128();  // ticket_s may be rewritten by the next run
-                if (last) {
-                    // Merge the run's parts, eight at a time.  All loads of a chunk are issued before any is used
-                    // (the loop over parts is unrolled with predicates), so the merge costs about one memory round
-                    // trip per chunk instead of one per part and head.
+                if (si == seg_begin && si + 1 < seg_end) {
+                    // Not the CTA's last piece: hand the ticket and the possible merge to warp 6 and go on.
+                    __threadfence_block();
+                    handed_off = true;
+                    asm volatile("bar.arrive 2, 160;" ::: "memory");
+                } else {
                     __threadfence();
-                    float M[G], Ls[G], Os[G];
-#pragma unroll
-                    for (int h = 0; h < G; ++h) {
-                        M[h] = -INFINITY;
-                        Ls[h] = 0.0f;
-                        Os[h] = 0.0f;
+                    named_bar_sync_128();
+                    if (tid == 0) *ticket_s = atomicAdd(&a.counters[req * Hkv + seg.kv_head], 1u);
+                    named_bar_sync_128();
+                    const bool last = *ticket_s == seg.n_parts - 1u;
+                    named_bar_sync_128();  // ticket_s may be rewritten by the next run
+                    if (last) {
+                        __threadfence();
+                        merge_run_parts<G, T>(a, seg, red, tid, 128u, state_mode, row0);
+                        if (tid == 0) a.counters[req * Hkv + seg.kv_head] = 0u;
                     }
-                    for (uint32_t c0 = 0; c0 < seg.n_parts; c0 += 8u) {
-                        const uint32_t cnt = min(8u, seg.n_parts - c0);
-                        // stage (m, l) of the chunk: [part][head][2]
-                        if (tid < cnt * uint32_t(G) * 2u)
-                            red[tid] = __ldcg(&a.part_ml[size_t(seg.first_slot + c0) * G * 2 + tid]);
-                        float ov[8][G];
-#pragma unroll
-                        for (int s2 = 0; s2 < 8; ++s2)
-#pragma unroll
-                            for (int h = 0; h < G; ++h)
-                                ov[s2][h] = (uint32_t(s2) < cnt)
-                                                ? __ldcg(&a.part_o[(size_t(seg.first_slot + c0 + s2) * G + h) * kTcD + d])
-                                                : 0.0f;
-                        named_bar_sync_128();
-#pragma unroll
-                        for (int h = 0; h < G; ++h) {
-                            float mc = M[h];
-#pragma unroll
-                            for (int s2 = 0; s2 < 8; ++s2)
-                                if (uint32_t(s2) < cnt) mc = fmaxf(mc, red[(s2 * G + h) * 2]);
-                            if (mc == -INFINITY) continue;
-                            const float keep = (M[h] == -INFINITY) ? 0.0f : exp2f(M[h] - mc);
-                            float lacc = Ls[h] * keep, oacc = Os[h] * keep;
-#pragma unroll
-                            for (int s2 = 0; s2 < 8; ++s2) {
-                                if (uint32_t(s2) < cnt) {
-                                    const float ms = red[(s2 * G + h) * 2];
-                                    const float w = (ms == -INFINITY) ? 0.0f : exp2f(ms - mc);
-                                    lacc = fmaf(w, red[(s2 * G + h) * 2 + 1], lacc);
-                                    oacc = fmaf(w, ov[s2][h], oacc);
-                                }
-                            }
-                            M[h] = mc;
-                            Ls[h] = lacc;
-                            Os[h] = oacc;
-                        }
-                        named_bar_sync_128();  // `red` is rewritten by the next chunk / the next tile
-                    }
-#pragma unroll
-                    for (int h = 0; h < G; ++h) {
-                        if (state_mode) {
-                            a.state_o[(row0 + h) * kTcD + d] = Os[h];
-                            if (d == 0) {
-                                a.state_m[row0 + h] = M[h] / kTcLog2e;
-                                a.state_l[row0 + h] = Ls[h];
-                            }
-                        } else {
-                            reinterpret_cast<uint16_t*>(a.out)[(row0 + h) * kTcD + d] = T::store(Os[h] / fmaxf(Ls[h], 1e-12f));
-                        }
-                    }
-                    if (tid == 0) a.counters[req * Hkv + seg.kv_head] = 0u;
                 }
             }
+        }
+        // warp 6 waits on barrier 2 whenever the first piece is a deferred one: arrive even when bailing out
+        if (defer_first && !handed_off) {
+            *merge_job_ok = 0;
+            __threadfence_block();
+            asm volatile("bar.arrive 2, 160;" ::: "memory");
         }
         if (!ok && lane == 0) {
             atomicMax(a.status, uint32_t(KRIYA_DEV_WAIT_EXPIRED));
@@ -529,7 +577,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
 template <int G, typename T>
 cudaError_t launch_tc_t(const TcParams& pp, const CUtensorMap& mk, const CUtensorMap& mv, uint32_t grid, int max_smem_optin,
                         cudaStream_t s) {
-    const size_t smem = size_t(2 * kTcStages) * kTcKvBytes + 3 * kTcQBytes + 2 * kTcPBytes + 512 + 256 + 1024;
+    const size_t smem = size_t(2 * kTcStages) * kTcKvBytes + 3 * kTcQBytes + 2 * kTcPBytes + 512 + 256 + 512 + 1024;
     if (smem > size_t(max_smem_optin)) return cudaErrorInvalidValue;
     auto kern = decode_tc_kernel<G, T>;
     static bool attr_set = false;

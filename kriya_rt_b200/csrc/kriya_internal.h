@@ -35,9 +35,11 @@ struct KriyaTcSeg {
     uint32_t slot;
     uint32_t first_slot;
     uint32_t n_parts;
-    uint32_t _pad;
+    uint32_t tbl_off;     // page_indptr[req]: where the row's block table starts
+    uint32_t row_tokens;  // tokens in the whole row: (blocks - 1) * block size + last_page_len
+    uint32_t _pad[3];
 };
-static_assert(sizeof(KriyaTcSeg) == 32, "segment record is 32 bytes");
+static_assert(sizeof(KriyaTcSeg) == 48, "segment record is 48 bytes");
 
 // Device status word values written by kernels instead of trapping.
 enum : uint32_t {
