@@ -280,7 +280,6 @@ def run_gpu_arm(args):
     sampler = ClockSampler(local_rank)
     sampler.start()
     launches0 = ex.launch_count
-    ex.timing_enable(True)
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ev0.record(stream)
     for t in range(args.warmup, total_steps):
@@ -294,10 +293,27 @@ def run_gpu_arm(args):
     barrier()
     clocks = sampler.stop()
     elapsed_ms = ev0.elapsed_time(ev1)
+    gpu_launches = ex.launch_count - launches0
+
+    # ---- leg 1b: the same steps once more with every decode launch bracketed by CUDA events on its stream, for the
+    # per-launch duration of the dominant kernel (the brackets cost idle time between kernels, so they are kept out
+    # of the timed region above)
+    mgr_b = fresh_manager()
+    for t in range(args.warmup):
+        step_plan(mgr_b, t)
+    ex.timing_enable(True)
+    ev2, ev3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev2.record(stream)
+    for t in range(args.warmup, total_steps):
+        plan, pos = step_plan(mgr_b, t)
+        ex.upload_schedule_plan(plan, pos)
+        ex.decode_step(q, k, v, out, BATCH, rp, gp)
+    ev3.record(stream)
+    ex.sync()
     n_dec, ms_dec = ex.timing_read(0)
     n_app, ms_app = ex.timing_read(1)
     ex.timing_enable(False)
-    gpu_launches = ex.launch_count - launches0
+    bracketed_ms_per_step = ev2.elapsed_time(ev3) / args.steps
 
     # ---- leg 2: end to end through host buffers ---------------------------------------------------------
     qh = torch.empty(L, BATCH, Hq, D, dtype=torch.int16).pin_memory()
@@ -357,10 +373,13 @@ def run_gpu_arm(args):
             "config": {"workload": WORKLOAD, "l2": "inputs larger than L2: each step streams %.2f GB of KV" %
                        (kv_bytes_launch * L / 1e9), "plan": "rebuilt on the host every step by the C++ manager and uploaded inside the timed region",
                        "kv_read_gbs_whole_step": kv_bytes_launch * L / (ms_per_step * 1e-3) / 1e9,
-                       "append_us_per_launch": ms_app / max(n_app, 1) * 1e3, "decode_us_per_launch": dec_us},
+                       "kernels_per_layer": gpu_launches / args.steps / L,
+                       "bracketed_pass": {"ms_per_step": bracketed_ms_per_step, "decode_launches": n_dec,
+                                          "decode_us_per_launch": dec_us, "append_launches": n_app,
+                                          "append_us_per_launch": (ms_app / n_app * 1e3) if n_app else None}},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": (achieved / peaks["hbm_gbs"]) if achieved else None, "traffic": traffic,
-                         "kernel": "decode_kernel", "algorithmic_bytes_per_launch": alg_bytes, "peak_source": peak_kind,
+                         "kernel": "decode_tc_kernel (fused RoPE + append + paged GQA decode)", "algorithmic_bytes_per_launch": alg_bytes, "peak_source": peak_kind,
                          "frac_of_nominal_8000": (achieved / 8000.0) if achieved else None},
             "e2e": {"value": e2e_value, "unit": UNIT,
                     "h2d_bytes_per_step": int(plan_bytes + qh.numel() * 2 + kh.numel() * 2 + vh.numel() * 2),

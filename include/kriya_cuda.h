@@ -209,6 +209,18 @@ int32_t kriya_cuda_decode_layer_host(kriya_cuda_ctx* ctx, uint32_t layer, const 
                                      const void* v_host, void* out_host, uint32_t rows,
                                      const kriya_rope_kv_write_params* rope, const kriya_bsr_gqa_params* gqa);
 
+/* The append and the decode of one layer in ONE launch (head_dim 128, group size <= 8, no QK norm): queries are
+ * rotated on their way into the attention kernel, and for every row the rotated new key and the new value are
+ * written to their cache slot by the same kernel before it reads that page.  Cache contents and attention output
+ * equal kriya_cuda_rope_kv_append followed by kriya_cuda_paged_gqa_decode (enc:4945-5053); q itself is NOT modified:
+ * the rotated queries are written to q_rope_out [rows][Hq][D] when it is not NULL (it must not alias q). */
+int32_t kriya_cuda_append_decode(kriya_cuda_ctx* ctx, uint32_t layer, const void* q_dev, const void* k_in_dev,
+                                 const void* v_in_dev, void* out_dev, void* q_rope_out_dev,
+                                 const kriya_rope_kv_write_params* rope, const kriya_bsr_gqa_params* gqa);
+/* Whether kriya_cuda_decode_step / _host use the fused launch where it applies (default 1).  With 1 the step leaves
+ * q un-rotated; with 0 it rotates q in place like the two separate kernels. */
+int32_t kriya_cuda_set_fused_append(kriya_cuda_ctx* ctx, int32_t enable);
+
 /* One decode step over ALL layers with device activations: for layer l = 0..num_layers-1, append then
  * decode with the current plan.  q/k/v/out hold the layers back to back: q and out [layers][rows][Hq][D],
  * k and v [layers][rows][Hkv][D].  One host call per step instead of two per layer; the per-layer loop of

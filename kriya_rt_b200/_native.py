@@ -120,6 +120,9 @@ CUDA_SYMBOLS = {
     "kriya_cuda_kv_slot_write": (C.c_int32, [_VP, C.c_uint32, _VP, _VP, _VP, C.c_uint32]),
     "kriya_cuda_decode_layer_host": (C.c_int32, [_VP, C.c_uint32, _VP, _VP, _VP, _VP, C.c_uint32,
                                                  C.POINTER(RopeKvWriteParams), C.POINTER(BsrGqaParams)]),
+    "kriya_cuda_append_decode": (C.c_int32, [_VP, C.c_uint32, _VP, _VP, _VP, _VP, _VP, C.POINTER(RopeKvWriteParams),
+                                             C.POINTER(BsrGqaParams)]),
+    "kriya_cuda_set_fused_append": (C.c_int32, [_VP, C.c_int32]),
     "kriya_cuda_decode_step": (C.c_int32, [_VP, _VP, _VP, _VP, _VP, C.c_uint32, C.POINTER(RopeKvWriteParams),
                                            C.POINTER(BsrGqaParams)]),
     "kriya_cuda_decode_step_host": (C.c_int32, [_VP, _VP, _VP, _VP, _VP, C.c_uint32, C.POINTER(RopeKvWriteParams),

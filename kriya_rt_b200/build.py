@@ -64,7 +64,7 @@ def build_cuda(force: bool = False) -> Path:
         src, obj = pair
         if not force and _newer(obj, [CSRC / src] + headers):
             return
-        _run([_nvcc(), *NVCC_FLAGS, "-I", str(INCLUDE), "-I", str(CSRC), "-c", str(CSRC / src), "-o", str(obj)],
+        _run([_nvcc(), *NVCC_FLAGS, *os.environ.get("KRIYA_NVCC_EXTRA", "").split(), "-I", str(INCLUDE), "-I", str(CSRC), "-c", str(CSRC / src), "-o", str(obj)],
              log=OBJ / (Path(src).stem + ".ptxas.log"))
 
     with ThreadPoolExecutor(max_workers=min(8, len(sources))) as pool:

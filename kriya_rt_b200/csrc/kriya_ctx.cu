@@ -259,7 +259,8 @@ bool use_tc_decode(const kriya_cuda_ctx* c) {
 }
 
 int32_t launch_decode(kriya_cuda_ctx* c, uint32_t layer, const void* q, void* out, float* sm, float* sl, float* so,
-                      bool range_list, uint32_t n_work, const kriya_bsr_gqa_params* p) {
+                      bool range_list, uint32_t n_work, const kriya_bsr_gqa_params* p,
+                      const KriyaFusedAppend& fused = KriyaFusedAppend()) {
     KriyaDecodeArgs a{};
     a.q = q;
     a.cache_k = c->layer_k(layer);
@@ -289,7 +290,7 @@ int32_t launch_decode(kriya_cuda_ctx* c, uint32_t layer, const void* q, void* ou
         KRIYA_CUDA_TRY(c, kriya_launch_decode_tc(a, c->plan_dev<KriyaTcSeg>(range_list ? c->off_tcseg2 : c->off_tcseg),
                                                  c->plan_dev<uint32_t>(range_list ? c->off_tcptr2 : c->off_tcptr),
                                                  uint32_t(c->sm_count), c->tmap_k, c->tmap_v, layer_row0, c->cfg.dtype,
-                                                 c->max_smem_optin, c->stream));
+                                                 c->max_smem_optin, fused, c->stream));
     } else {
         KRIYA_CUDA_TRY(c, kriya_launch_decode(a, c->cfg.head_dim, c->cfg.block_size_tokens, c->cfg.dtype,
                                               c->max_smem_optin, c->stream));
@@ -831,6 +832,36 @@ int32_t kriya_cuda_decode_layer_host(kriya_cuda_ctx* c, uint32_t layer, const vo
     return kriya_cuda_sync(c, 0);
 }
 
+int32_t kriya_cuda_append_decode(kriya_cuda_ctx* c, uint32_t layer, const void* q, const void* k, const void* v, void* out,
+                                 void* q_rope_out, const kriya_rope_kv_write_params* rope, const kriya_bsr_gqa_params* gqa) {
+    if (!c) return KRIYA_CUDA_INVALID_INPUT;
+    if (int32_t rc = check_layer(c, layer)) return rc;
+    if (int32_t rc = check_rope(c, rope)) return rc;
+    if (int32_t rc = check_gqa(c, gqa)) return rc;
+    if (!c->plan_valid) return c->fail(KRIYA_CUDA_INVALID_INPUT, "no plan uploaded");
+    if (!q || !k || !v || !out) return c->fail(KRIYA_CUDA_INVALID_INPUT, "q, k, v and out must not be null");
+    if (q_rope_out == q) return c->fail(KRIYA_CUDA_INVALID_INPUT, "q_rope_out must not alias q");
+    if (c->n_positions != c->n_rows)
+        return c->fail(KRIYA_CUDA_INVALID_INPUT, "input_tokens has " + std::to_string(c->n_rows) + " entries but seq_positions has " +
+                                                     std::to_string(c->n_positions));
+    if (rope->apply_qk_norm || !use_tc_decode(c))
+        return c->fail(KRIYA_CUDA_UNSUPPORTED, "the fused append + decode launch covers head_dim 128, group size 1..8, no QK norm");
+    cudaSetDevice(c->cfg.device);
+    KriyaFusedAppend f;
+    f.k_in = k;
+    f.v_in = v;
+    f.q_rope_out = q_rope_out;
+    f.positions = c->plan_dev<uint32_t>(c->off_positions);
+    f.table = table_for(c, rope);
+    f.cache_k_w = c->layer_k(layer);
+    f.cache_v_w = c->layer_v(layer);
+    f.rotary_dim = rope->rotary_dim;
+    f.max_seq_len = rope->max_seq_len;
+    f.has_table = rope->has_table;
+    f.rope_theta = rope->rope_theta;
+    return launch_decode(c, layer, q, out, nullptr, nullptr, nullptr, false, c->n_work, gqa, f);
+}
+
 int32_t kriya_cuda_decode_step(kriya_cuda_ctx* c, void* q, const void* k, const void* v, void* out, uint32_t rows,
                                const kriya_rope_kv_write_params* rope, const kriya_bsr_gqa_params* gqa) {
     if (!c) return KRIYA_CUDA_INVALID_INPUT;
@@ -844,8 +875,12 @@ int32_t kriya_cuda_decode_step(kriya_cuda_ctx* c, void* q, const void* k, const 
         const uint8_t* kl = static_cast<const uint8_t*>(k) + layer * kb;
         const uint8_t* vl = static_cast<const uint8_t*>(v) + layer * kb;
         uint8_t* ol = static_cast<uint8_t*>(out) + layer * qb;
-        if (int32_t rc = kriya_cuda_rope_kv_append(c, layer, ql, kl, vl, nullptr, nullptr, rows, rope)) return rc;
-        if (int32_t rc = kriya_cuda_paged_gqa_decode(c, layer, ql, ol, gqa)) return rc;
+        if (c->fuse_append && use_tc_decode(c) && !rope->apply_qk_norm) {
+            if (int32_t rc = kriya_cuda_append_decode(c, layer, ql, kl, vl, ol, nullptr, rope, gqa)) return rc;
+        } else {
+            if (int32_t rc = kriya_cuda_rope_kv_append(c, layer, ql, kl, vl, nullptr, nullptr, rows, rope)) return rc;
+            if (int32_t rc = kriya_cuda_paged_gqa_decode(c, layer, ql, ol, gqa)) return rc;
+        }
     }
     return KRIYA_CUDA_OK;
 }
@@ -889,6 +924,12 @@ int32_t kriya_cuda_set_decode_path(kriya_cuda_ctx* c, int32_t path) {
                                                                  c->cfg.block_size_tokens)))
         return c->fail(KRIYA_CUDA_UNSUPPORTED, "the tensor-core decode kernel covers head_dim 128, group size 1..8, 16-token blocks");
     c->decode_path = path;
+    return KRIYA_CUDA_OK;
+}
+
+int32_t kriya_cuda_set_fused_append(kriya_cuda_ctx* c, int32_t enable) {
+    if (!c) return KRIYA_CUDA_INVALID_INPUT;
+    c->fuse_append = enable != 0;
     return KRIYA_CUDA_OK;
 }
 

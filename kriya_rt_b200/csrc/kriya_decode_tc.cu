@@ -29,6 +29,8 @@
 // HBM roofline: algorithmic bytes per launch = attended tokens * 2 * Hkv * D * 2 B; every K/V byte is read
 // from HBM once (one TMA load) and from shared memory once (one MMA operand read).
 #include <algorithm>
+#include <cstdio>
+#include <cstdlib>
 
 #include "kriya_tc.cuh"
 
@@ -55,8 +57,57 @@ struct TcParams {
     const KriyaTcSeg* segs;
     const uint32_t* cta_seg_ptr;  // [grid + 1]
     uint32_t layer_row0;
+    KriyaFusedAppend f;
 };
 
+// RoPE of eight (x[i], x[i + D/2]) pairs held as two 16-byte chunks, in the operation order of the append kernel
+// (fma(x0, c, -(x1 * s)), fma(x0, s, x1 * c), round to nearest even), so both paths write identical bits.
+template <typename T>
+__device__ __forceinline__ void rope8(uint4& lo, uint4& hi, uint32_t first_pair, uint32_t position, const KriyaFusedAppend& f) {
+    const uint32_t half_rot = f.rotary_dim / 2u;
+    const bool use_table = f.has_table != 0u && position < f.max_seq_len && f.table != nullptr;
+    uint32_t* lw = reinterpret_cast<uint32_t*>(&lo);
+    uint32_t* hw = reinterpret_cast<uint32_t*>(&hi);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        uint16_t l2[2] = {uint16_t(lw[j] & 0xFFFFu), uint16_t(lw[j] >> 16)};
+        uint16_t h2[2] = {uint16_t(hw[j] & 0xFFFFu), uint16_t(hw[j] >> 16)};
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            const uint32_t i = first_pair + 2 * j + e;
+            if (i < half_rot) {
+                float c, s;
+                if (use_table) {
+                    const float2 cs = reinterpret_cast<const float2*>(f.table)[size_t(position) * half_rot + i];
+                    c = cs.x;
+                    s = cs.y;
+                } else {
+                    const float freq_exp = float(2u * i) / float(f.rotary_dim);
+                    const float inv_freq = powf(f.rope_theta, -freq_exp);
+                    const float angle = __fmul_rn(float(position), inv_freq);
+                    c = cosf(angle);
+                    s = sinf(angle);
+                }
+                const float x0 = T::load(l2[e]), x1 = T::load(h2[e]);
+                l2[e] = T::store(__fmaf_rn(x0, c, -__fmul_rn(x1, s)));
+                h2[e] = T::store(__fmaf_rn(x0, s, __fmul_rn(x1, c)));
+            }
+        }
+        lw[j] = uint32_t(l2[0]) | (uint32_t(l2[1]) << 16);
+        hw[j] = uint32_t(h2[0]) | (uint32_t(h2[1]) << 16);
+    }
+}
+
+// Optional per-CTA timeline (compile with -DKRIYA_TC_TRACE): wall-clock stamps at a few points of the kernel, dumped
+// to stderr by the launcher on the tenth launch when KRIYA_TRACE is set in the environment.
+#ifdef KRIYA_TC_TRACE
+__device__ unsigned long long g_trace[160 * 16];
+#define TR(k) do { g_trace[blockIdx.x * 16 + (k)] = global_timer_ns(); } while (0)
+#define TRV(k, v) do { g_trace[blockIdx.x * 16 + (k)] = (v); } while (0)
+#else
+#define TR(k) do { } while (0)
+#define TRV(k, v) do { } while (0)
+#endif
 __device__ __forceinline__ void named_bar_sync_128() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 // Barrier over the 128 softmax threads that also ORs a predicate across them.
 __device__ __forceinline__ bool bar_or_128(bool pred) {
@@ -169,6 +220,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
 
     const KriyaDecodeArgs& a = pp.a;
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
+    if (threadIdx.x == 0) TR(0);
     const uint32_t seg_begin = pp.cta_seg_ptr[blockIdx.x], seg_end = pp.cta_seg_ptr[blockIdx.x + 1];
     if (seg_begin == seg_end) return;  // whole CTA idle: nothing allocated yet
 
@@ -204,6 +256,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
     const uint32_t Hq = a.num_q_heads, Hkv = a.num_kv_heads;
     // the CTA's first piece is merged by warp 6 when it is one part of a split run and more pieces follow
     const bool defer_first = seg_end - seg_begin > 1u && pp.segs[seg_begin].n_parts > 1u;
+    if (tid == 0) TR(1);
 
     if (warp == 4) {
         // ---- producer ---------------------------------------------------------------------------------
@@ -228,10 +281,58 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
                     // S^T MMAs belong to tiles <= g - 3, which the wait has just shown to be complete.
                     uint8_t* qb = sQ + (runs % 3u) * kTcQBytes;
                     const uint16_t* qg = reinterpret_cast<const uint16_t*>(a.q) + (size_t(seg.req) * Hq + seg.kv_head * G) * kTcD;
-                    for (uint32_t i = lane; i < uint32_t(G) * 16u; i += 32u) {
-                        const uint32_t h = i >> 4, c = i & 15u;
-                        const uint4 val = *reinterpret_cast<const uint4*>(qg + h * kTcD + c * 8);
-                        *reinterpret_cast<uint4*>(qb + (c >> 3) * 2048u + h * 128u + (((c & 7u) ^ (h & 7u)) << 4)) = val;
+                    if (pp.f.k_in == nullptr) {
+                        for (uint32_t i = lane; i < uint32_t(G) * 16u; i += 32u) {
+                            const uint32_t h = i >> 4, c = i & 15u;
+                            const uint4 val = *reinterpret_cast<const uint4*>(qg + h * kTcD + c * 8);
+                            *reinterpret_cast<uint4*>(qb + (c >> 3) * 2048u + h * 128u + (((c & 7u) ^ (h & 7u)) << 4)) = val;
+                        }
+                    } else {
+                        // Fused append: the queries are rotated on their way into the operand tile, and the piece
+                        // that holds the row's last block also rotates the new key and writes it, with the new
+                        // value, into the cache slot before its own TMA loads read that page.
+                        const uint32_t position = pp.f.positions[seg.req];
+                        const bool owns_last = uint64_t(seg.blk_hi) * kTcPage >= seg.row_tokens;
+                        for (uint32_t i = lane; i < uint32_t(G) * 8u; i += 32u) {
+                            const uint32_t h = i >> 3, c = i & 7u;
+                            uint4 lo = *reinterpret_cast<const uint4*>(qg + h * kTcD + c * 8);
+                            uint4 hi = *reinterpret_cast<const uint4*>(qg + h * kTcD + 64 + c * 8);
+                            rope8<T>(lo, hi, c * 8u, position, pp.f);
+                            *reinterpret_cast<uint4*>(qb + h * 128u + ((c ^ (h & 7u)) << 4)) = lo;
+                            *reinterpret_cast<uint4*>(qb + 2048u + h * 128u + ((c ^ (h & 7u)) << 4)) = hi;
+                            if (owns_last && pp.f.q_rope_out != nullptr) {
+                                uint16_t* qo = reinterpret_cast<uint16_t*>(pp.f.q_rope_out) + (size_t(seg.req) * Hq + seg.kv_head * G + h) * kTcD;
+                                *reinterpret_cast<uint4*>(qo + c * 8) = lo;
+                                *reinterpret_cast<uint4*>(qo + 64 + c * 8) = hi;
+                            }
+                        }
+                        if (owns_last && seg.row_tokens > 0u) {
+                            const uint32_t tok = seg.row_tokens - 1u;
+                            uint32_t blk = uint32_t(table[tok / kTcPage]);
+                            if (blk >= a.num_blocks) {
+                                if (lane == 0) atomicMax(a.status, uint32_t(KRIYA_DEV_BAD_BLOCK_INDEX));
+                            } else {
+                                const size_t off = ((size_t(blk) * kTcPage + tok % kTcPage) * Hkv + seg.kv_head) * kTcD;
+                                const size_t src = (size_t(seg.req) * Hkv + seg.kv_head) * kTcD;
+                                uint16_t* kd = reinterpret_cast<uint16_t*>(pp.f.cache_k_w) + off;
+                                uint16_t* vd = reinterpret_cast<uint16_t*>(pp.f.cache_v_w) + off;
+                                const uint16_t* ks = reinterpret_cast<const uint16_t*>(pp.f.k_in) + src;
+                                const uint16_t* vs = reinterpret_cast<const uint16_t*>(pp.f.v_in) + src;
+                                if (lane < 8u) {
+                                    uint4 lo = *reinterpret_cast<const uint4*>(ks + lane * 8);
+                                    uint4 hi = *reinterpret_cast<const uint4*>(ks + 64 + lane * 8);
+                                    rope8<T>(lo, hi, lane * 8u, position, pp.f);
+                                    *reinterpret_cast<uint4*>(kd + lane * 8) = lo;
+                                    *reinterpret_cast<uint4*>(kd + 64 + lane * 8) = hi;
+                                } else if (lane < 24u) {
+                                    const uint32_t c = lane - 8u;
+                                    *reinterpret_cast<uint4*>(vd + c * 8) = *reinterpret_cast<const uint4*>(vs + c * 8);
+                                }
+                            }
+                            // order the cache writes (generic proxy) before this warp's TMA loads (async proxy)
+                            __threadfence();
+                            asm volatile("fence.proxy.async.global;" ::: "memory");
+                        }
                     }
                     fence_async_smem();
                     __syncwarp();
@@ -248,6 +349,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
                         blk = 0;
                     }
                 }
+                if (lane == 0 && g == 0) TR(2);
                 if (lane == 0) mbar_arrive_expect_tx(&kv_full[stage], npages * uint32_t(4 * kTcPage * 128));
                 __syncwarp();
                 if (lane < npages) {
@@ -315,6 +417,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
             return true;
         };
         ok = la_issue();  // S^T of the first tile
+        if (lane == 0) TR(3);
         for (uint32_t si = seg_begin; si < seg_end && ok; ++si) {
             const KriyaTcSeg seg = pp.segs[si];
             if (seg.blk_hi <= seg.blk_lo) continue;
@@ -373,6 +476,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
         bool ok = true;
         bool handed_off = false;
         for (uint32_t si = seg_begin; si < seg_end && ok; ++si) {
+            if (tid == 0 && si == seg_begin + 1) TR(6);
             const KriyaTcSeg seg = pp.segs[si];
             const uint32_t req = seg.req;
             const uint32_t row_tokens = seg.row_tokens;
@@ -390,6 +494,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
                 ok = warp_wait(&s_full[g & 1u], (g >> 1) & 1u);
                 if (!ok) break;
                 tc_fence_after();
+                if (tid == 0 && g == 0) TR(4);
                 uint32_t r[16];
                 tmem_ld16(tmem_base + lane_addr + ((g & 1u) ? kColS1 : kColS0), r);
                 tmem_wait_ld();
@@ -481,6 +586,11 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
                 mbar_arrive(&p_ready[g & 1u]);
             }
             if (!ok) break;
+            if (tid == 0 && si == seg_begin) {
+                TR(5);
+                TRV(9, g);
+                TRV(10, seg_end - seg_begin);
+            }
             // ---- end of the run piece: total l per head, then O^T / l or the partial state ----------------
             float l_tot[G];
 #pragma unroll
@@ -560,6 +670,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
             __threadfence_block();
             asm volatile("bar.arrive 2, 160;" ::: "memory");
         }
+        if (tid == 0) TR(7);
         if (!ok && lane == 0) {
             atomicMax(a.status, uint32_t(KRIYA_DEV_WAIT_EXPIRED));
             *abort_flag = 1;
@@ -568,6 +679,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
 
     tc_fence_before();
     __syncthreads();
+    if (tid == 0) TR(8);
     if (warp == 5) {
         tc_fence_after();
         tmem_dealloc(tmem_base, kTcTmemCols);
@@ -587,6 +699,26 @@ cudaError_t launch_tc_t(const TcParams& pp, const CUtensorMap& mk, const CUtenso
         attr_set = true;
     }
     kern<<<grid, kTcThreads, smem, s>>>(mk, mv, pp);
+#ifdef KRIYA_TC_TRACE
+    if (getenv("KRIYA_TRACE")) {
+        static int calls = 0;
+        if (++calls == 10) {
+            cudaDeviceSynchronize();
+            static unsigned long long h[160 * 16];
+            cudaMemcpyFromSymbol(h, g_trace, sizeof(h));
+            unsigned long long t0 = ~0ull;
+            for (uint32_t c = 0; c < grid; ++c)
+                if (h[c * 16]) t0 = std::min(t0, h[c * 16]);
+            // columns: entry, set-up done, first TMA, first S^T issued, first scores read, first piece streamed,
+            // second piece begins, softmax warps done, CTA done (microseconds from the earliest entry)
+            for (uint32_t c = 0; c < grid; ++c) {
+                fprintf(stderr, "cta %3u:", c);
+                for (int k = 0; k < 9; ++k) fprintf(stderr, " %6.1f", h[c * 16 + k] >= t0 ? (h[c * 16 + k] - t0) / 1000.0 : -1.0);
+                fprintf(stderr, "  tiles %llu segs %llu\n", h[c * 16 + 9], h[c * 16 + 10]);
+            }
+        }
+    }
+#endif
     return cudaGetLastError();
 }
 
@@ -614,7 +746,7 @@ bool kriya_decode_tc_supported(uint32_t head_dim, uint32_t group, uint32_t block
 
 cudaError_t kriya_launch_decode_tc(const KriyaDecodeArgs& a, const KriyaTcSeg* segs, const uint32_t* cta_seg_ptr, uint32_t grid,
                                    const void* map_k, const void* map_v, uint32_t layer_row0, uint32_t dtype,
-                                   int max_smem_optin, cudaStream_t s) {
+                                   int max_smem_optin, const KriyaFusedAppend& fused, cudaStream_t s) {
     if (grid == 0) return cudaSuccess;
     const uint32_t group = a.num_q_heads / a.num_kv_heads;
     if (!kriya_decode_tc_supported(kriya::kTcD, group, kriya::kTcPage) || !map_k || !map_v) return cudaErrorInvalidValue;
@@ -623,6 +755,7 @@ cudaError_t kriya_launch_decode_tc(const KriyaDecodeArgs& a, const KriyaTcSeg* s
     pp.segs = segs;
     pp.cta_seg_ptr = cta_seg_ptr;
     pp.layer_row0 = layer_row0;
+    pp.f = fused;
     const CUtensorMap& mk = *static_cast<const CUtensorMap*>(map_k);
     const CUtensorMap& mv = *static_cast<const CUtensorMap*>(map_v);
     return dtype == KRIYA_DTYPE_FP16 ? kriya::launch_tc_g<kriya::Fp16>(group, pp, mk, mv, grid, max_smem_optin, s)

@@ -79,6 +79,7 @@ struct kriya_cuda_ctx {
     size_t off_indptr = 0, off_indices = 0, off_last_len = 0, off_tiles = 0, off_positions = 0, off_work = 0,
            off_range = 0, off_tcseg = 0, off_tcptr = 0, off_tcseg2 = 0, off_tcptr2 = 0;
     uint32_t cap_seg = 0, n_seg = 0;
+    bool fuse_append = true;  // whole-step calls use the fused append + decode launch where it applies
     int decode_path = 0;  // 0: pick per shape, 1: CUDA-core kernel, 2: tensor-core kernel
     uint32_t cap_rows = 0, cap_indices = 0, cap_tiles = 0, cap_tokens = 0, cap_work = 0;
     // current plan (host copy of the sizes and of what later calls need)
@@ -185,10 +186,24 @@ cudaError_t kriya_launch_decode(const KriyaDecodeArgs& a, uint32_t head_dim, uin
                                 int max_smem_optin, cudaStream_t s);
 bool kriya_decode_supported(uint32_t head_dim, uint32_t group, uint32_t num_kv_heads, uint32_t block_size);
 
+// Optional fused RoPE + KV append inside the tensor-core decode launch (null k_in: plain decode).
+struct KriyaFusedAppend {
+    const void* k_in = nullptr;     // [rows][Hkv][D] new keys (un-rotated)
+    const void* v_in = nullptr;     // [rows][Hkv][D] new values
+    void* q_rope_out = nullptr;     // optional [rows][Hq][D]: rotated queries (must not alias q)
+    const uint32_t* positions = nullptr;
+    const float* table = nullptr;   // cos/sin table or null
+    void* cache_k_w = nullptr;      // writable layer bases
+    void* cache_v_w = nullptr;
+    uint32_t rotary_dim = 0;
+    uint32_t max_seq_len = 0;
+    uint32_t has_table = 0;
+    float rope_theta = 0.0f;
+};
 bool kriya_decode_tc_supported(uint32_t head_dim, uint32_t group, uint32_t block_size);
 cudaError_t kriya_launch_decode_tc(const KriyaDecodeArgs& a, const KriyaTcSeg* segs, const uint32_t* cta_seg_ptr, uint32_t grid,
                                    const void* map_k, const void* map_v, uint32_t layer_row0, uint32_t dtype,
-                                   int max_smem_optin, cudaStream_t s);
+                                   int max_smem_optin, const KriyaFusedAppend& fused, cudaStream_t s);
 
 cudaError_t kriya_launch_merge_states(const float* m, const float* l, const float* o, uint32_t parts, uint32_t rows,
                                       uint32_t D, void* out, uint32_t dtype, cudaStream_t s);

@@ -198,6 +198,15 @@ class CudaExecutor:
         self._check(self._lib.kriya_cuda_decode_step_host(self._h, _ptr(q_host), _ptr(k_host), _ptr(v_host),
                                                           _ptr(out_host), rows, C.byref(rope), C.byref(gqa)))
 
+    def append_decode(self, layer: int, q, k_in, v_in, out, rope: RopeKvWriteParams, gqa: BsrGqaParams,
+                      q_rope_out=None) -> None:
+        """Append + decode of one layer in one launch; q is left un-rotated (see kriya_cuda_append_decode)."""
+        self._check(self._lib.kriya_cuda_append_decode(self._h, layer, _ptr(q), _ptr(k_in), _ptr(v_in), _ptr(out),
+                                                       _ptr(q_rope_out), C.byref(rope), C.byref(gqa)))
+
+    def set_fused_append(self, enable: bool) -> None:
+        self._check(self._lib.kriya_cuda_set_fused_append(self._h, int(enable)))
+
     def set_decode_path(self, path: int) -> None:
         """0 = by shape, 1 = CUDA-core decode kernel, 2 = tensor-core decode kernel."""
         self._check(self._lib.kriya_cuda_set_decode_path(self._h, path))
