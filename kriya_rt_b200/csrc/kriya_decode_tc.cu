@@ -212,11 +212,13 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
     uint64_t* s_full = bars + 2 * kTcStages;      // [2]
     uint64_t* p_ready = bars + 2 * kTcStages + 2; // [2], 128 arrivals each; tile g uses p_ready[g & 1]
     uint64_t* pv_done = bars + 2 * kTcStages + 4; // [2]; P.V of tile g commits to pv_done[g & 1]
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kTcStages + 6);
+    uint64_t* q_ready = bars + 2 * kTcStages + 6; // [3]; one arrival when a run's query operand is staged
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kTcStages + 9);
     volatile uint32_t* abort_flag = tmem_slot + 1;
     uint32_t* ticket_s = tmem_slot + 2;
     volatile uint32_t* merge_job_ok = tmem_slot + 3;
     float* merge_stage = reinterpret_cast<float*>(tmem_slot + 4);  // [8][G][2] floats for warp 6
+    KriyaTcSeg* segs_s = reinterpret_cast<KriyaTcSeg*>(merge_stage + 128);  // first 8 segment records of this CTA
 
     const KriyaDecodeArgs& a = pp.a;
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
@@ -235,6 +237,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
         mbar_init(&p_ready[1], 128);
         mbar_init(&pv_done[0], 1);
         mbar_init(&pv_done[1], 1);
+        for (int b = 0; b < 3; ++b) mbar_init(&q_ready[b], 1);
         *abort_flag = 0;
         *merge_job_ok = 1;
         mbar_fence_init();
@@ -243,6 +246,12 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
         tmem_alloc(tmem_slot, kTcTmemCols);
         tmem_relinquish();
     }
+    {   // every role walks the same segment list: keep the first records in shared memory
+        const uint32_t nstage = min(seg_end - seg_begin, 8u) * uint32_t(sizeof(KriyaTcSeg) / 4);
+        const uint32_t* src = reinterpret_cast<const uint32_t*>(pp.segs + seg_begin);
+        for (uint32_t i = tid; i < nstage; i += kTcThreads) reinterpret_cast<uint32_t*>(segs_s)[i] = src[i];
+    }
+    auto seg_at = [&](uint32_t si) -> KriyaTcSeg { return (si - seg_begin < 8u) ? segs_s[si - seg_begin] : pp.segs[si]; };
     // The padding heads of the Q and P operand tiles must be zero.  The K/V ring needs no clearing: a K row
     // that is never loaded only produces a score that is masked by selection, and the V row of every masked
     // token is cleared by the softmax thread that owns it.
@@ -255,44 +264,111 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t Hq = a.num_q_heads, Hkv = a.num_kv_heads;
     // the CTA's first piece is merged by warp 6 when it is one part of a split run and more pieces follow
-    const bool defer_first = seg_end - seg_begin > 1u && pp.segs[seg_begin].n_parts > 1u;
+    const bool defer_first = seg_end - seg_begin > 1u && segs_s[0].n_parts > 1u;
     if (tid == 0) TR(1);
 
     if (warp == 4) {
         // ---- producer ---------------------------------------------------------------------------------
+        // Order of work at the start of a run piece: the first tile's TMA loads go out first, then the query
+        // operand is staged (and, fused, rotated) while they are in flight, then the new token's K/V row is
+        // written; the MMA warp learns that Q is in place through q_ready.  Page indices of the next tile are
+        // fetched while the current tile's loads are in flight, so the table read is off the critical path.
         uint32_t g = 0;     // tiles issued by this CTA so far
         uint32_t runs = 0;  // non-empty run pieces started so far (selects the Q buffer)
         bool ok = true;
+        const bool fused = pp.f.k_in != nullptr;
         for (uint32_t si = seg_begin; si < seg_end && ok; ++si) {
-            const KriyaTcSeg seg = pp.segs[si];
+            const KriyaTcSeg seg = seg_at(si);
             const uint32_t t0 = seg.blk_lo / kTcPagesPerTile, t1 = (seg.blk_hi + kTcPagesPerTile - 1) / kTcPagesPerTile;
             if (seg.blk_hi <= seg.blk_lo) continue;
             const int32_t* table = a.indices + seg.tbl_off;
+            const bool owns_last = fused && seg.row_tokens > 0u && uint64_t(seg.blk_hi) * kTcPage >= seg.row_tokens;
+            bool kv_written = !owns_last;
+            uint32_t position = 0;
+            if (fused) position = pp.f.positions[seg.req];
+            auto write_new_kv = [&]() {
+                // the rotated new key and the new value go into their cache slot; ordered before this warp's
+                // later TMA loads (async proxy) by the fences at the end
+                const uint32_t tok = seg.row_tokens - 1u;
+                const uint32_t blk = uint32_t(table[tok / kTcPage]);
+                if (blk >= a.num_blocks) {
+                    if (lane == 0) atomicMax(a.status, uint32_t(KRIYA_DEV_BAD_BLOCK_INDEX));
+                } else {
+                    const size_t off = ((size_t(blk) * kTcPage + tok % kTcPage) * Hkv + seg.kv_head) * kTcD;
+                    const size_t src = (size_t(seg.req) * Hkv + seg.kv_head) * kTcD;
+                    uint16_t* kd = reinterpret_cast<uint16_t*>(pp.f.cache_k_w) + off;
+                    uint16_t* vd = reinterpret_cast<uint16_t*>(pp.f.cache_v_w) + off;
+                    const uint16_t* ks = reinterpret_cast<const uint16_t*>(pp.f.k_in) + src;
+                    const uint16_t* vs = reinterpret_cast<const uint16_t*>(pp.f.v_in) + src;
+                    if (lane < 8u) {
+                        uint4 lo = *reinterpret_cast<const uint4*>(ks + lane * 8);
+                        uint4 hi = *reinterpret_cast<const uint4*>(ks + 64 + lane * 8);
+                        rope8<T>(lo, hi, lane * 8u, position, pp.f);
+                        *reinterpret_cast<uint4*>(kd + lane * 8) = lo;
+                        *reinterpret_cast<uint4*>(kd + 64 + lane * 8) = hi;
+                    } else if (lane < 24u) {
+                        const uint32_t c = lane - 8u;
+                        *reinterpret_cast<uint4*>(vd + c * 8) = *reinterpret_cast<const uint4*>(vs + c * 8);
+                    }
+                }
+                __threadfence();
+                asm volatile("fence.proxy.async.global;" ::: "memory");
+                __syncwarp();
+            };
+            int32_t pf_blk = 0;      // page index of this lane for the coming tile, fetched one tile ahead
+            bool pf_valid = false;
             for (uint32_t t = t0; t < t1; ++t, ++g) {
                 if (*abort_flag) { ok = false; break; }
                 const uint32_t stage = g % kTcStages;
+                const uint32_t p_lo = max(t * kTcPagesPerTile, seg.blk_lo), p_hi = min((t + 1) * kTcPagesPerTile, seg.blk_hi);
+                const uint32_t npages = p_hi - p_lo;
+                const uint32_t my_page = p_lo + lane;
+                int32_t blk = pf_blk;
+                if (!pf_valid && lane < npages) blk = table[my_page];
                 if (g >= kTcStages && !warp_wait(&kv_empty[stage], ((g / kTcStages) - 1u) & 1u)) {
                     ok = false;
                     break;
                 }
+                if (t + 1u == t1 && !kv_written) {  // the piece's last tile reads the slot written here
+                    write_new_kv();
+                    kv_written = true;
+                }
+                if (lane < npages && uint32_t(blk) >= a.num_blocks) {
+                    atomicMax(a.status, uint32_t(KRIYA_DEV_BAD_BLOCK_INDEX));
+                    blk = 0;
+                }
+                if (lane == 0 && g == 0) TR(2);
+                if (lane == 0) mbar_arrive_expect_tx(&kv_full[stage], npages * uint32_t(4 * kTcPage * 128));
+                __syncwarp();
+                if (lane < npages) {
+                    const int32_t y = int32_t(pp.layer_row0) + blk * kTcPage;
+                    const uint32_t row_off = (my_page - t * kTcPagesPerTile) * (kTcPage * 128);
+#pragma unroll
+                    for (int p = 0; p < 2; ++p) {
+                        const int32_t x = int32_t(seg.kv_head) * kTcD + p * 64;
+                        tma_load_2d(sK + stage * kTcKvBytes + p * kTcPanel + row_off, &map_k, x, y, &kv_full[stage]);
+                        tma_load_2d(sV + stage * kTcKvBytes + p * kTcPanel + row_off, &map_v, x, y, &kv_full[stage]);
+                    }
+                }
+                // next tile's page indices
+                pf_valid = t + 1u < t1;
+                if (pf_valid) {
+                    const uint32_t n_lo = (t + 1u) * kTcPagesPerTile, n_hi = min((t + 2u) * kTcPagesPerTile, seg.blk_hi);
+                    pf_blk = (n_lo + lane < n_hi) ? table[n_lo + lane] : 0;
+                }
                 if (t == t0) {
-                    // The run's query heads as a 16-row K-major operand (rows >= G stay zero).  Staged after the
-                    // ring wait above: the buffer's previous user is three non-empty runs back, so all of its
-                    // S^T MMAs belong to tiles <= g - 3, which the wait has just shown to be complete.
+                    // The run's query heads as a 16-row K-major operand (rows >= G stay zero).  The buffer's
+                    // previous user is three non-empty runs back, so all of its S^T MMAs belong to tiles <= g - 3,
+                    // which the ring wait above has shown to be complete.
                     uint8_t* qb = sQ + (runs % 3u) * kTcQBytes;
                     const uint16_t* qg = reinterpret_cast<const uint16_t*>(a.q) + (size_t(seg.req) * Hq + seg.kv_head * G) * kTcD;
-                    if (pp.f.k_in == nullptr) {
+                    if (!fused) {
                         for (uint32_t i = lane; i < uint32_t(G) * 16u; i += 32u) {
                             const uint32_t h = i >> 4, c = i & 15u;
                             const uint4 val = *reinterpret_cast<const uint4*>(qg + h * kTcD + c * 8);
                             *reinterpret_cast<uint4*>(qb + (c >> 3) * 2048u + h * 128u + (((c & 7u) ^ (h & 7u)) << 4)) = val;
                         }
                     } else {
-                        // Fused append: the queries are rotated on their way into the operand tile, and the piece
-                        // that holds the row's last block also rotates the new key and writes it, with the new
-                        // value, into the cache slot before its own TMA loads read that page.
-                        const uint32_t position = pp.f.positions[seg.req];
-                        const bool owns_last = uint64_t(seg.blk_hi) * kTcPage >= seg.row_tokens;
                         for (uint32_t i = lane; i < uint32_t(G) * 8u; i += 32u) {
                             const uint32_t h = i >> 3, c = i & 7u;
                             uint4 lo = *reinterpret_cast<const uint4*>(qg + h * kTcD + c * 8);
@@ -306,60 +382,14 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
                                 *reinterpret_cast<uint4*>(qo + 64 + c * 8) = hi;
                             }
                         }
-                        if (owns_last && seg.row_tokens > 0u) {
-                            const uint32_t tok = seg.row_tokens - 1u;
-                            uint32_t blk = uint32_t(table[tok / kTcPage]);
-                            if (blk >= a.num_blocks) {
-                                if (lane == 0) atomicMax(a.status, uint32_t(KRIYA_DEV_BAD_BLOCK_INDEX));
-                            } else {
-                                const size_t off = ((size_t(blk) * kTcPage + tok % kTcPage) * Hkv + seg.kv_head) * kTcD;
-                                const size_t src = (size_t(seg.req) * Hkv + seg.kv_head) * kTcD;
-                                uint16_t* kd = reinterpret_cast<uint16_t*>(pp.f.cache_k_w) + off;
-                                uint16_t* vd = reinterpret_cast<uint16_t*>(pp.f.cache_v_w) + off;
-                                const uint16_t* ks = reinterpret_cast<const uint16_t*>(pp.f.k_in) + src;
-                                const uint16_t* vs = reinterpret_cast<const uint16_t*>(pp.f.v_in) + src;
-                                if (lane < 8u) {
-                                    uint4 lo = *reinterpret_cast<const uint4*>(ks + lane * 8);
-                                    uint4 hi = *reinterpret_cast<const uint4*>(ks + 64 + lane * 8);
-                                    rope8<T>(lo, hi, lane * 8u, position, pp.f);
-                                    *reinterpret_cast<uint4*>(kd + lane * 8) = lo;
-                                    *reinterpret_cast<uint4*>(kd + 64 + lane * 8) = hi;
-                                } else if (lane < 24u) {
-                                    const uint32_t c = lane - 8u;
-                                    *reinterpret_cast<uint4*>(vd + c * 8) = *reinterpret_cast<const uint4*>(vs + c * 8);
-                                }
-                            }
-                            // order the cache writes (generic proxy) before this warp's TMA loads (async proxy)
-                            __threadfence();
-                            asm volatile("fence.proxy.async.global;" ::: "memory");
-                        }
                     }
                     fence_async_smem();
                     __syncwarp();
+                    if (lane == 0) mbar_arrive(&q_ready[runs % 3u]);
                     ++runs;
-                }
-                const uint32_t p_lo = max(t * kTcPagesPerTile, seg.blk_lo), p_hi = min((t + 1) * kTcPagesPerTile, seg.blk_hi);
-                const uint32_t npages = p_hi - p_lo;
-                const uint32_t my_page = p_lo + lane;
-                int32_t blk = 0;
-                if (lane < npages) {
-                    blk = table[my_page];
-                    if (uint32_t(blk) >= a.num_blocks) {
-                        atomicMax(a.status, uint32_t(KRIYA_DEV_BAD_BLOCK_INDEX));
-                        blk = 0;
-                    }
-                }
-                if (lane == 0 && g == 0) TR(2);
-                if (lane == 0) mbar_arrive_expect_tx(&kv_full[stage], npages * uint32_t(4 * kTcPage * 128));
-                __syncwarp();
-                if (lane < npages) {
-                    const int32_t y = int32_t(pp.layer_row0) + blk * kTcPage;
-                    const uint32_t row_off = (my_page - t * kTcPagesPerTile) * (kTcPage * 128);
-#pragma unroll
-                    for (int p = 0; p < 2; ++p) {
-                        const int32_t x = int32_t(seg.kv_head) * kTcD + p * 64;
-                        tma_load_2d(sK + stage * kTcKvBytes + p * kTcPanel + row_off, &map_k, x, y, &kv_full[stage]);
-                        tma_load_2d(sV + stage * kTcKvBytes + p * kTcPanel + row_off, &map_v, x, y, &kv_full[stage]);
+                    if (!kv_written) {  // long piece: write the new token now, well ahead of the tile that reads it
+                        write_new_kv();
+                        kv_written = true;
                     }
                 }
             }
@@ -389,12 +419,14 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
         bool ok = true;
         // look-ahead cursor
         uint32_t la_si = seg_begin, la_t = 0, la_t1 = 0, la_g = 0, la_run = 0;
+        bool la_first = true;  // the look-ahead tile is the first of its run: its query operand must be in place
         auto la_load = [&]() {
             while (la_si < seg_end) {
-                const KriyaTcSeg s2 = pp.segs[la_si];
+                const KriyaTcSeg s2 = seg_at(la_si);
                 if (s2.blk_hi > s2.blk_lo) {
                     la_t = s2.blk_lo / kTcPagesPerTile;
                     la_t1 = (s2.blk_hi + kTcPagesPerTile - 1) / kTcPagesPerTile;
+                    la_first = true;
                     return true;
                 }
                 ++la_si;
@@ -405,6 +437,10 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
         auto la_issue = [&]() -> bool {  // issue S^T for the look-ahead tile and advance the cursor
             if (!la_valid) return true;
             if (!warp_wait(&kv_full[la_g % kTcStages], (la_g / kTcStages) & 1u)) return false;
+            if (la_first) {
+                if (!warp_wait(&q_ready[la_run % 3u], (la_run / 3u) & 1u)) return false;
+                la_first = false;
+            }
             tc_fence_after();
             if (lane == 0) issue_s(la_g, la_run % 3u);
             __syncwarp();
@@ -419,7 +455,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
         ok = la_issue();  // S^T of the first tile
         if (lane == 0) TR(3);
         for (uint32_t si = seg_begin; si < seg_end && ok; ++si) {
-            const KriyaTcSeg seg = pp.segs[si];
+            const KriyaTcSeg seg = seg_at(si);
             if (seg.blk_hi <= seg.blk_lo) continue;
             const uint32_t t0 = seg.blk_lo / kTcPagesPerTile, t1 = (seg.blk_hi + kTcPagesPerTile - 1) / kTcPagesPerTile;
             for (uint32_t t = t0; t < t1 && ok; ++t, ++g) {
@@ -451,7 +487,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
     } else if (warp == 6) {
         // ---- deferred merge of the CTA's first piece -----------------------------------------------------
         if (defer_first) {
-            const KriyaTcSeg seg = pp.segs[seg_begin];
+            const KriyaTcSeg seg = segs_s[0];
             asm volatile("bar.sync 2, 160;" ::: "memory");  // the softmax threads have published the partial state
             if (*merge_job_ok) {
                 __threadfence();
@@ -477,7 +513,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
         bool handed_off = false;
         for (uint32_t si = seg_begin; si < seg_end && ok; ++si) {
             if (tid == 0 && si == seg_begin + 1) TR(6);
-            const KriyaTcSeg seg = pp.segs[si];
+            const KriyaTcSeg seg = seg_at(si);
             const uint32_t req = seg.req;
             const uint32_t row_tokens = seg.row_tokens;
             const uint32_t tok_lo = seg.blk_lo * kTcPage, tok_hi = min(seg.blk_hi * kTcPage, row_tokens);
@@ -689,7 +725,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
 template <int G, typename T>
 cudaError_t launch_tc_t(const TcParams& pp, const CUtensorMap& mk, const CUtensorMap& mv, uint32_t grid, int max_smem_optin,
                         cudaStream_t s) {
-    const size_t smem = size_t(2 * kTcStages) * kTcKvBytes + 3 * kTcQBytes + 2 * kTcPBytes + 512 + 256 + 512 + 1024;
+    const size_t smem = size_t(2 * kTcStages) * kTcKvBytes + 3 * kTcQBytes + 2 * kTcPBytes + 512 + 256 + 512 + 8 * sizeof(KriyaTcSeg) + 1024;
     if (smem > size_t(max_smem_optin)) return cudaErrorInvalidValue;
     auto kern = decode_tc_kernel<G, T>;
     static bool attr_set = false;
