@@ -13,7 +13,7 @@
 //     piece to finish (atomic ticket, no waiting) merges them.
 //   - Warp 4 (producer) walks its piece: per tile it reads up to 8 page indices and issues TMA tensor loads
 //     of K and V ([16 tokens] x [64 d] boxes, 128-byte swizzle, no multicast) into a 3-stage shared-memory
-//     ring; it also stages the G query heads of each run as a 16-row MMA operand.
+//     ring.
 //   - Warp 5 (one thread) issues tcgen05.mma:  S^T[128 tokens x 16] = K_tile . Q^T   (K-major operands) and
 //     O^T[128 d x 16] += V_tile^T . P^T  (V consumed in place as an MN-major operand), accumulators in TMEM.
 //     S^T of tile g+1 is issued before P.V of tile g so the softmax overlaps the tensor pipe.
@@ -21,6 +21,9 @@
 //     of O^T).  Per tile: read 16 scores, mask tokens past the row end, column max by warp shuffles plus a
 //     4-warp exchange in shared memory, exp2, write P (storage dtype) into the swizzled operand tile, keep
 //     the running sum per lane, rescale O^T in TMEM only when a head's max moved by more than 2^8.
+//   - Warp 7 (stager) prepares each run piece ahead of time: the G query heads as a 16-row MMA operand (rotated in
+//     flight when the append is fused) and, fused, the rotated new key and the new value written to their cache slot
+//     before the producer loads that page.
 //   - Warp 6 takes over the cross-CTA merge of a piece that is not the CTA's last one, so the softmax warps go
 //     straight on to the next run while partial states are published, ticketed and (if last) merged.
 //   - Every mbarrier wait is bounded; on expiry the kernel records a status word, abandons its piece,
@@ -41,7 +44,7 @@ constexpr int kTcTile = 128;          // tokens per tile
 constexpr int kTcPage = 16;
 constexpr int kTcPagesPerTile = kTcTile / kTcPage;
 constexpr int kTcStages = 3;
-constexpr int kTcThreads = 224;  // warps 0-3 softmax, 4 producer, 5 MMA issuer, 6 deferred merge
+constexpr int kTcThreads = 256;  // warps 0-3 softmax, 4 producer, 5 MMA issuer, 6 deferred merge, 7 query/new-token stager
 constexpr int kTcN = 16;              // MMA N: query heads of one KV head, zero padded
 constexpr float kTcLog2e = 1.4426950408889634f;
 constexpr float kTcRescale = 8.0f;
@@ -212,8 +215,10 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
     uint64_t* s_full = bars + 2 * kTcStages;      // [2]
     uint64_t* p_ready = bars + 2 * kTcStages + 2; // [2], 128 arrivals each; tile g uses p_ready[g & 1]
     uint64_t* pv_done = bars + 2 * kTcStages + 4; // [2]; P.V of tile g commits to pv_done[g & 1]
-    uint64_t* q_ready = bars + 2 * kTcStages + 6; // [3]; one arrival when a run's query operand is staged
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kTcStages + 9);
+    uint64_t* q_ready = bars + 2 * kTcStages + 6;   // [3]; run r's query operand is staged in buffer r % 3
+    uint64_t* q_free = bars + 2 * kTcStages + 9;    // [3]; all S^T MMAs of the run that used the buffer are complete
+    uint64_t* kv_ready = bars + 2 * kTcStages + 12; // [3]; run r's new-token K/V row is in the cache (fused append)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kTcStages + 15);
     volatile uint32_t* abort_flag = tmem_slot + 1;
     uint32_t* ticket_s = tmem_slot + 2;
     volatile uint32_t* merge_job_ok = tmem_slot + 3;
@@ -237,7 +242,11 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
         mbar_init(&p_ready[1], 128);
         mbar_init(&pv_done[0], 1);
         mbar_init(&pv_done[1], 1);
-        for (int b = 0; b < 3; ++b) mbar_init(&q_ready[b], 1);
+        for (int b = 0; b < 3; ++b) {
+            mbar_init(&q_ready[b], 1);
+            mbar_init(&q_free[b], 1);
+            mbar_init(&kv_ready[b], 1);
+        }
         *abort_flag = 0;
         *merge_job_ok = 1;
         mbar_fence_init();
@@ -268,13 +277,9 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
     if (tid == 0) TR(1);
 
     if (warp == 4) {
-        // ---- producer ---------------------------------------------------------------------------------
-        // Order of work at the start of a run piece: the first tile's TMA loads go out first, then the query
-        // operand is staged (and, fused, rotated) while they are in flight, then the new token's K/V row is
-        // written; the MMA warp learns that Q is in place through q_ready.  Page indices of the next tile are
-        // fetched while the current tile's loads are in flight, so the table read is off the critical path.
+        // ---- producer: page indices one tile ahead, TMA loads into the ring -------------------------------
         uint32_t g = 0;     // tiles issued by this CTA so far
-        uint32_t runs = 0;  // non-empty run pieces started so far (selects the Q buffer)
+        uint32_t runs = 0;  // non-empty run pieces started so far
         bool ok = true;
         const bool fused = pp.f.k_in != nullptr;
         for (uint32_t si = seg_begin; si < seg_end && ok; ++si) {
@@ -283,12 +288,103 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
             if (seg.blk_hi <= seg.blk_lo) continue;
             const int32_t* table = a.indices + seg.tbl_off;
             const bool owns_last = fused && seg.row_tokens > 0u && uint64_t(seg.blk_hi) * kTcPage >= seg.row_tokens;
-            bool kv_written = !owns_last;
+            int32_t pf_blk = 0;
+            bool pf_valid = false;
+            for (uint32_t t = t0; t < t1; ++t, ++g) {
+                if (*abort_flag) { ok = false; break; }
+                const uint32_t stage = g % kTcStages;
+                const uint32_t p_lo = max(t * kTcPagesPerTile, seg.blk_lo), p_hi = min((t + 1) * kTcPagesPerTile, seg.blk_hi);
+                const uint32_t npages = p_hi - p_lo;
+                const uint32_t my_page = p_lo + lane;
+                int32_t blk = pf_blk;
+                if (!pf_valid && lane < npages) blk = table[my_page];
+                if (g >= kTcStages && !warp_wait(&kv_empty[stage], ((g / kTcStages) - 1u) & 1u)) {
+                    ok = false;
+                    break;
+                }
+                // the piece's last tile reads the slot the stager warp writes: wait until it is in the cache
+                if (owns_last && t + 1u == t1 && !warp_wait(&kv_ready[runs % 3u], (runs / 3u) & 1u)) {
+                    ok = false;
+                    break;
+                }
+                if (lane < npages && uint32_t(blk) >= a.num_blocks) {
+                    atomicMax(a.status, uint32_t(KRIYA_DEV_BAD_BLOCK_INDEX));
+                    blk = 0;
+                }
+                if (lane == 0 && g == 0) TR(2);
+                if (lane == 0) mbar_arrive_expect_tx(&kv_full[stage], npages * uint32_t(4 * kTcPage * 128));
+                __syncwarp();
+                if (lane < npages) {
+                    const int32_t y = int32_t(pp.layer_row0) + blk * kTcPage;
+                    const uint32_t row_off = (my_page - t * kTcPagesPerTile) * (kTcPage * 128);
+#pragma unroll
+                    for (int p = 0; p < 2; ++p) {
+                        const int32_t x = int32_t(seg.kv_head) * kTcD + p * 64;
+                        tma_load_2d(sK + stage * kTcKvBytes + p * kTcPanel + row_off, &map_k, x, y, &kv_full[stage]);
+                        tma_load_2d(sV + stage * kTcKvBytes + p * kTcPanel + row_off, &map_v, x, y, &kv_full[stage]);
+                    }
+                }
+                pf_valid = t + 1u < t1;
+                if (pf_valid) {
+                    const uint32_t n_lo = (t + 1u) * kTcPagesPerTile, n_hi = min((t + 2u) * kTcPagesPerTile, seg.blk_hi);
+                    pf_blk = (n_lo + lane < n_hi) ? table[n_lo + lane] : 0;
+                }
+            }
+            ++runs;
+        }
+        if (!ok && lane == 0) {
+            atomicMax(a.status, uint32_t(KRIYA_DEV_WAIT_EXPIRED));
+            *abort_flag = 1;
+        }
+    } else if (warp == 7) {
+        // ---- stager: per run piece, the query operand (rotated when fused) and the new token's K/V row ---------
+        // Runs up to three pieces ahead of the MMA warp; a Q buffer is reused once q_free says that every S^T MMA
+        // of its previous run has completed.
+        uint32_t runs = 0;
+        bool ok = true;
+        const bool fused = pp.f.k_in != nullptr;
+        for (uint32_t si = seg_begin; si < seg_end && ok; ++si) {
+            const KriyaTcSeg seg = seg_at(si);
+            if (seg.blk_hi <= seg.blk_lo) continue;
+            if (*abort_flag) break;
+            if (runs >= 3u && !warp_wait(&q_free[runs % 3u], ((runs / 3u) - 1u) & 1u)) {
+                ok = false;
+                break;
+            }
+            const int32_t* table = a.indices + seg.tbl_off;
+            const bool owns_last = fused && seg.row_tokens > 0u && uint64_t(seg.blk_hi) * kTcPage >= seg.row_tokens;
+            uint8_t* qb = sQ + (runs % 3u) * kTcQBytes;
+            const uint16_t* qg = reinterpret_cast<const uint16_t*>(a.q) + (size_t(seg.req) * Hq + seg.kv_head * G) * kTcD;
             uint32_t position = 0;
-            if (fused) position = pp.f.positions[seg.req];
-            auto write_new_kv = [&]() {
-                // the rotated new key and the new value go into their cache slot; ordered before this warp's
-                // later TMA loads (async proxy) by the fences at the end
+            if (!fused) {
+                // 16 rows x 256 B as two swizzled K-major panels; rows >= G stay zero
+                for (uint32_t i = lane; i < uint32_t(G) * 16u; i += 32u) {
+                    const uint32_t h = i >> 4, c = i & 15u;
+                    const uint4 val = *reinterpret_cast<const uint4*>(qg + h * kTcD + c * 8);
+                    *reinterpret_cast<uint4*>(qb + (c >> 3) * 2048u + h * 128u + (((c & 7u) ^ (h & 7u)) << 4)) = val;
+                }
+            } else {
+                position = pp.f.positions[seg.req];
+                for (uint32_t i = lane; i < uint32_t(G) * 8u; i += 32u) {
+                    const uint32_t h = i >> 3, c = i & 7u;
+                    uint4 lo = *reinterpret_cast<const uint4*>(qg + h * kTcD + c * 8);
+                    uint4 hi = *reinterpret_cast<const uint4*>(qg + h * kTcD + 64 + c * 8);
+                    rope8<T>(lo, hi, c * 8u, position, pp.f);
+                    *reinterpret_cast<uint4*>(qb + h * 128u + ((c ^ (h & 7u)) << 4)) = lo;
+                    *reinterpret_cast<uint4*>(qb + 2048u + h * 128u + ((c ^ (h & 7u)) << 4)) = hi;
+                    if (owns_last && pp.f.q_rope_out != nullptr) {
+                        uint16_t* qo = reinterpret_cast<uint16_t*>(pp.f.q_rope_out) + (size_t(seg.req) * Hq + seg.kv_head * G + h) * kTcD;
+                        *reinterpret_cast<uint4*>(qo + c * 8) = lo;
+                        *reinterpret_cast<uint4*>(qo + 64 + c * 8) = hi;
+                    }
+                }
+            }
+            fence_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&q_ready[runs % 3u]);
+            if (owns_last) {
+                // the rotated new key and the new value go into their cache slot; the fences order these generic-proxy
+                // writes before the TMA loads (async proxy) the producer issues after it has seen kv_ready
                 const uint32_t tok = seg.row_tokens - 1u;
                 const uint32_t blk = uint32_t(table[tok / kTcPage]);
                 if (blk >= a.num_blocks) {
@@ -314,85 +410,9 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
                 __threadfence();
                 asm volatile("fence.proxy.async.global;" ::: "memory");
                 __syncwarp();
-            };
-            int32_t pf_blk = 0;      // page index of this lane for the coming tile, fetched one tile ahead
-            bool pf_valid = false;
-            for (uint32_t t = t0; t < t1; ++t, ++g) {
-                if (*abort_flag) { ok = false; break; }
-                const uint32_t stage = g % kTcStages;
-                const uint32_t p_lo = max(t * kTcPagesPerTile, seg.blk_lo), p_hi = min((t + 1) * kTcPagesPerTile, seg.blk_hi);
-                const uint32_t npages = p_hi - p_lo;
-                const uint32_t my_page = p_lo + lane;
-                int32_t blk = pf_blk;
-                if (!pf_valid && lane < npages) blk = table[my_page];
-                if (g >= kTcStages && !warp_wait(&kv_empty[stage], ((g / kTcStages) - 1u) & 1u)) {
-                    ok = false;
-                    break;
-                }
-                if (t + 1u == t1 && !kv_written) {  // the piece's last tile reads the slot written here
-                    write_new_kv();
-                    kv_written = true;
-                }
-                if (lane < npages && uint32_t(blk) >= a.num_blocks) {
-                    atomicMax(a.status, uint32_t(KRIYA_DEV_BAD_BLOCK_INDEX));
-                    blk = 0;
-                }
-                if (lane == 0 && g == 0) TR(2);
-                if (lane == 0) mbar_arrive_expect_tx(&kv_full[stage], npages * uint32_t(4 * kTcPage * 128));
-                __syncwarp();
-                if (lane < npages) {
-                    const int32_t y = int32_t(pp.layer_row0) + blk * kTcPage;
-                    const uint32_t row_off = (my_page - t * kTcPagesPerTile) * (kTcPage * 128);
-#pragma unroll
-                    for (int p = 0; p < 2; ++p) {
-                        const int32_t x = int32_t(seg.kv_head) * kTcD + p * 64;
-                        tma_load_2d(sK + stage * kTcKvBytes + p * kTcPanel + row_off, &map_k, x, y, &kv_full[stage]);
-                        tma_load_2d(sV + stage * kTcKvBytes + p * kTcPanel + row_off, &map_v, x, y, &kv_full[stage]);
-                    }
-                }
-                // next tile's page indices
-                pf_valid = t + 1u < t1;
-                if (pf_valid) {
-                    const uint32_t n_lo = (t + 1u) * kTcPagesPerTile, n_hi = min((t + 2u) * kTcPagesPerTile, seg.blk_hi);
-                    pf_blk = (n_lo + lane < n_hi) ? table[n_lo + lane] : 0;
-                }
-                if (t == t0) {
-                    // The run's query heads as a 16-row K-major operand (rows >= G stay zero).  The buffer's
-                    // previous user is three non-empty runs back, so all of its S^T MMAs belong to tiles <= g - 3,
-                    // which the ring wait above has shown to be complete.
-                    uint8_t* qb = sQ + (runs % 3u) * kTcQBytes;
-                    const uint16_t* qg = reinterpret_cast<const uint16_t*>(a.q) + (size_t(seg.req) * Hq + seg.kv_head * G) * kTcD;
-                    if (!fused) {
-                        for (uint32_t i = lane; i < uint32_t(G) * 16u; i += 32u) {
-                            const uint32_t h = i >> 4, c = i & 15u;
-                            const uint4 val = *reinterpret_cast<const uint4*>(qg + h * kTcD + c * 8);
-                            *reinterpret_cast<uint4*>(qb + (c >> 3) * 2048u + h * 128u + (((c & 7u) ^ (h & 7u)) << 4)) = val;
-                        }
-                    } else {
-                        for (uint32_t i = lane; i < uint32_t(G) * 8u; i += 32u) {
-                            const uint32_t h = i >> 3, c = i & 7u;
-                            uint4 lo = *reinterpret_cast<const uint4*>(qg + h * kTcD + c * 8);
-                            uint4 hi = *reinterpret_cast<const uint4*>(qg + h * kTcD + 64 + c * 8);
-                            rope8<T>(lo, hi, c * 8u, position, pp.f);
-                            *reinterpret_cast<uint4*>(qb + h * 128u + ((c ^ (h & 7u)) << 4)) = lo;
-                            *reinterpret_cast<uint4*>(qb + 2048u + h * 128u + ((c ^ (h & 7u)) << 4)) = hi;
-                            if (owns_last && pp.f.q_rope_out != nullptr) {
-                                uint16_t* qo = reinterpret_cast<uint16_t*>(pp.f.q_rope_out) + (size_t(seg.req) * Hq + seg.kv_head * G + h) * kTcD;
-                                *reinterpret_cast<uint4*>(qo + c * 8) = lo;
-                                *reinterpret_cast<uint4*>(qo + 64 + c * 8) = hi;
-                            }
-                        }
-                    }
-                    fence_async_smem();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&q_ready[runs % 3u]);
-                    ++runs;
-                    if (!kv_written) {  // long piece: write the new token now, well ahead of the tile that reads it
-                        write_new_kv();
-                        kv_written = true;
-                    }
-                }
             }
+            if (lane == 0) mbar_arrive(&kv_ready[runs % 3u]);
+            ++runs;
         }
         if (!ok && lane == 0) {
             atomicMax(a.status, uint32_t(KRIYA_DEV_WAIT_EXPIRED));
@@ -446,6 +466,8 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
             __syncwarp();
             ++la_g;
             if (++la_t >= la_t1) {
+                if (lane == 0) umma_commit(&q_free[la_run % 3u]);  // the run's last S^T is issued: its Q buffer frees when it completes
+                __syncwarp();
                 ++la_si;
                 ++la_run;
                 la_valid = la_load();
@@ -725,7 +747,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
 template <int G, typename T>
 cudaError_t launch_tc_t(const TcParams& pp, const CUtensorMap& mk, const CUtensorMap& mv, uint32_t grid, int max_smem_optin,
                         cudaStream_t s) {
-    const size_t smem = size_t(2 * kTcStages) * kTcKvBytes + 3 * kTcQBytes + 2 * kTcPBytes + 512 + 256 + 512 + 8 * sizeof(KriyaTcSeg) + 1024;
+    const size_t smem = size_t(2 * kTcStages) * kTcKvBytes + 3 * kTcQBytes + 2 * kTcPBytes + 512 + 320 + 512 + 8 * sizeof(KriyaTcSeg) + 1024;
     if (smem > size_t(max_smem_optin)) return cudaErrorInvalidValue;
     auto kern = decode_tc_kernel<G, T>;
     static bool attr_set = false;
