@@ -402,6 +402,7 @@ def run_gpu_arm(args):
 def run_kernel_case(args):
     """A small single-kernel case for profiling under ncu: a few launches of one kernel, nothing else.
     decode : Qwen2.5-3B shape, one layer, batch 32, contexts U[2048,8192] (about 170 MB of KV, larger than L2)
+    decode_fused: the benchmark's own layer (contexts U[512,4096], about 80 MB) through the fused append + decode launch
     prefill: Qwen2.5-1.5B shape, one 2048-token prompt, last 512-token chunk (prefix 1536)
     append : Qwen2.5-3B shape, 32 tokens;  copy: 64 pairs x 36 layers"""
     import torch
@@ -420,9 +421,10 @@ def run_kernel_case(args):
     def rnd(*shape):
         return torch.randn(*shape, device="cuda", generator=gen).to(torch.bfloat16).view(torch.int16)
 
-    if case in ("decode", "append"):
+    if case in ("decode", "append", "decode_fused"):
         sh = SHAPE
-        ctx = W.config2_contexts(seed_tables=2002, batch=BATCH, lo=2048, hi=8192)
+        lo, hi = (CTX_LO, CTX_HI) if case == "decode_fused" else (2048, 8192)
+        ctx = W.config2_contexts(seed_tables=2002, batch=BATCH, lo=lo, hi=hi)
         batch = W.make_decode_batch(sh, ctx, NUM_BLOCKS, seed=2002)
         ex = CudaExecutor(num_layers=1, num_kv_blocks=NUM_BLOCKS, block_size_tokens=16, num_q_heads=16, num_kv_heads=2,
                           head_dim=128, rope_theta=sh.rope_theta, rope_max_seq_len=16384, max_page_indices=NUM_BLOCKS)
@@ -432,22 +434,24 @@ def run_kernel_case(args):
         torch.cuda.synchronize()
         ex.upload_schedule_plan(batch, batch.positions)
         rp, gp = ex.rope_params(), ex.gqa_params()
-        for _ in range(2):  # untimed: module load and first-launch set-up
+        def one():
             if case == "append":
                 ex.rope_kv_append(0, q, k, v, BATCH, rp)
+            elif case == "decode_fused":
+                ex.append_decode(0, q, k, v, out, rp, gp)
             else:
                 ex.paged_gqa_decode(0, q, out, gp)
+
+        for _ in range(2):  # untimed: module load and first-launch set-up
+            one()
         ex.timing_enable(True)
         for _ in range(reps):
-            if case == "append":
-                ex.rope_kv_append(0, q, k, v, BATCH, rp)
-            else:
-                ex.paged_gqa_decode(0, q, out, gp)
+            one()
         n, ms = ex.timing_read(1 if case == "append" else 0)
         kv_bytes = batch.kv_bytes_per_layer
         print(json.dumps({"case": case, "launches": n, "us_per_launch": ms / max(n, 1) * 1e3,
                           "kv_bytes_per_launch": kv_bytes, "attended_tokens": batch.attended_tokens,
-                          "kv_gbs": kv_bytes / (ms / max(n, 1) * 1e-3) / 1e9 if case == "decode" and n else None}))
+                          "kv_gbs": kv_bytes / (ms / max(n, 1) * 1e-3) / 1e9 if case != "append" and n else None}))
         ex.close()
     elif case == "prefill":
         sh = W.QWEN25_1P5B
@@ -503,7 +507,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--kernel-case", default=None, choices=["decode", "prefill", "append", "copy"],
+    ap.add_argument("--kernel-case", default=None, choices=["decode", "decode_fused", "prefill", "append", "copy"],
                     help="run a few launches of one kernel on a small case (for ncu), --steps = launches")
     args = ap.parse_args()
     if args.kernel_case:

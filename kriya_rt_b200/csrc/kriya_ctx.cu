@@ -99,8 +99,11 @@ uint32_t build_work(const int32_t* indptr, uint32_t rows, const uint32_t* begin,
 }
 
 // Tensor-core decode work: every (row, KV head) is a run of 128-token tiles; the runs laid end to end are cut
-// into `ctas` equal contiguous pieces.  Returns the number of segment records, or UINT32_MAX when `cap` is too
-// small.  `ptr` receives ctas + 1 offsets into `out`.
+// into `ctas` contiguous pieces of equal WEIGHT, where a run's first tile weighs kRunStartWeight extra tiles: a CTA
+// that has to finish one run and start another pays an epilogue and a pipeline restart, which measures at about
+// two tiles' worth of streaming.  Returns the number of segment records, or UINT32_MAX when `cap` is too small.
+// `ptr` receives ctas + 1 offsets into `out`.
+constexpr uint32_t kRunStartWeight = 2;
 uint32_t build_tc_segments(const int32_t* indptr, const int32_t* last_len, uint32_t block_size, uint32_t rows, uint32_t hkv,
                            const uint32_t* begin, const uint32_t* end, uint32_t ctas, KriyaTcSeg* out, uint32_t cap,
                            uint32_t* ptr) {
@@ -110,10 +113,10 @@ uint32_t build_tc_segments(const int32_t* indptr, const int32_t* last_len, uint3
         const uint32_t nb = uint32_t(indptr[r + 1] - indptr[r]);
         const uint32_t b = begin ? std::min(begin[r], nb) : 0u;
         const uint32_t e = end ? std::min(end[r], nb) : nb;
-        if (e > b) total += uint64_t((e + TP - 1) / TP - b / TP) * hkv;
+        if (e > b) total += uint64_t((e + TP - 1) / TP - b / TP + kRunStartWeight) * hkv;
     }
     uint32_t n = 0, slot = 0, cta = 0;
-    uint64_t unit = 0;  // index of the next tile in the stream
+    uint64_t unit = 0;  // weight consumed so far
     auto cta_end = [&](uint32_t c) { return total * (c + 1) / ctas; };  // first unit NOT owned by cta c
     ptr[0] = 0;
     for (uint32_t r = 0; r < rows; ++r) {
@@ -132,15 +135,24 @@ uint32_t build_tc_segments(const int32_t* indptr, const int32_t* last_len, uint3
             const uint32_t t0 = b / TP, t1 = (e + TP - 1) / TP;
             const uint32_t first = n, first_slot = slot;
             uint32_t t = t0;
+            uint64_t lead = kRunStartWeight;  // weight carried by the run's first tile
             while (t < t1) {
                 while (cta + 1 < ctas && unit >= cta_end(cta)) ptr[++cta] = n;
-                const uint64_t room = cta + 1 < ctas ? cta_end(cta) - unit : uint64_t(t1 - t);
-                const uint32_t take = uint32_t(std::min<uint64_t>(room, t1 - t));
+                uint32_t take;
+                if (cta + 1 < ctas) {
+                    const uint64_t room = cta_end(cta) - unit;  // > 0
+                    // the first tile goes with its lead weight even when that overshoots the boundary a little
+                    take = uint32_t(std::min<uint64_t>(room > lead ? room - lead : 1u, t1 - t));
+                    take = std::max(take, 1u);
+                } else {
+                    take = t1 - t;
+                }
                 if (n + 1 > cap) return UINT32_MAX;
                 out[n++] = KriyaTcSeg{r, h, std::max(b, t * TP), std::min(e, (t + take) * TP), slot++, first_slot, 0u, tbl,
                                       row_tokens, {0u, 0u, 0u}};
                 t += take;
-                unit += take;
+                unit += take + lead;
+                lead = 0;
             }
             for (uint32_t i = first; i < n; ++i) out[i].n_parts = n - first;
         }
