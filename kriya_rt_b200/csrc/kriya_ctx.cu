@@ -5,6 +5,7 @@
 // cos/sin table, the per-step plan buffers and all scratch, allocated once.  Nothing on the step path
 // allocates.
 #include <math.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <algorithm>
@@ -99,11 +100,12 @@ uint32_t build_work(const int32_t* indptr, uint32_t rows, const uint32_t* begin,
 }
 
 // Tensor-core decode work: every (row, KV head) is a run of 128-token tiles; the runs laid end to end are cut
-// into `ctas` contiguous pieces of equal WEIGHT, where a run's first tile weighs kRunStartWeight extra tiles: a CTA
-// that has to finish one run and start another pays an epilogue and a pipeline restart, which measures at about
-// two tiles' worth of streaming.  Returns the number of segment records, or UINT32_MAX when `cap` is too small.
-// `ptr` receives ctas + 1 offsets into `out`.
-constexpr uint32_t kRunStartWeight = 2;
+// into `ctas` contiguous pieces of equal weight.  A run's first tile can be given kRunStartWeight extra tiles of
+// weight (a CTA that finishes one run and starts another pays an epilogue and a pipeline restart); measured on the
+// benchmark shape, weights of 2 and 4 made the launch about a third slower than 0 because they multiply short
+// leftover pieces, so plain tile counts are used.  Returns the number of segment records, or UINT32_MAX when `cap`
+// is too small.  `ptr` receives ctas + 1 offsets into `out`.
+constexpr uint32_t kRunStartWeight = 0;
 uint32_t build_tc_segments(const int32_t* indptr, const int32_t* last_len, uint32_t block_size, uint32_t rows, uint32_t hkv,
                            const uint32_t* begin, const uint32_t* end, uint32_t ctas, KriyaTcSeg* out, uint32_t cap,
                            uint32_t* ptr) {
