@@ -247,6 +247,28 @@ int32_t kriya_cuda_set_decode_path(kriya_cuda_ctx* ctx, int32_t path);
 int32_t kriya_cuda_timing_enable(kriya_cuda_ctx* ctx, int32_t enable);
 int32_t kriya_cuda_timing_read(kriya_cuda_ctx* ctx, uint32_t kind, uint64_t* out_launches, double* out_total_ms);
 
+/* Paged GQA decode without a context and without any allocation.  No counterpart in the reference: it exists for
+ * hosts that may not call cudaMalloc (a process whose device memory is handed out up front by its own arena, a plugin
+ * inside such a process, code running inside a stream capture), and which therefore cannot own a kriya_cuda_ctx.
+ * The caller passes every input and the output; the split-KV scratch (partial states, tickets, work list, status
+ * word) lives in a fixed array of about 4.3 MB inside the library image, present on every GPU that loads the library
+ * until the process exits.  Limits, rejected with KRIYA_CUDA_INVALID_INPUT and a message in `err`: at most 256 plan
+ * rows, num_q_heads * head_dim <= 2048, at most 512 work items (long batches are cut coarser to fit).
+ *   - q_dev / out_dev [rows][Hq][D], cache_*_dev one layer's pools [num_kv_blocks][16][Hkv][D], plan arrays as for
+ *     kriya_cuda_plan_upload but already on the device; page_indptr_host is the same indptr on the host (the work
+ *     split is computed from it).  Work is queued on `stream` (a cudaStream_t, may be 0); the call does not wait.
+ *   - The first call on a device looks up the array's device address; make that first call outside any stream
+ *     capture.  Every call shares the array and starts by clearing its tickets and status word, so two calls whose
+ *     kernels can overlap on the GPU (different streams, or different host threads) race: serialise them.
+ *   - Page indices outside [0, num_kv_blocks) are not dereferenced (block 0 is read instead); there is no context
+ *     to report them through, so validate tables on the host. */
+int32_t kriya_cuda_paged_gqa_decode_static(int32_t device, void* stream, uint32_t dtype, const void* q_dev,
+                                           const void* cache_k_dev, const void* cache_v_dev, uint32_t num_kv_blocks,
+                                           const int32_t* page_indptr_host, const int32_t* page_indptr_dev,
+                                           const int32_t* page_indices_dev, const int32_t* last_page_len_dev,
+                                           uint32_t rows, void* out_dev, const kriya_bsr_gqa_params* params, char* err,
+                                           size_t err_len);
+
 /* Number of kernels this library has launched on `ctx` since creation (for launch accounting). */
 uint64_t kriya_cuda_launch_count(const kriya_cuda_ctx* ctx);
 

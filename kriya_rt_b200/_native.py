@@ -130,6 +130,9 @@ CUDA_SYMBOLS = {
     "kriya_cuda_set_decode_path": (C.c_int32, [_VP, C.c_int32]),
     "kriya_cuda_timing_enable": (C.c_int32, [_VP, C.c_int32]),
     "kriya_cuda_timing_read": (C.c_int32, [_VP, C.c_uint32, C.POINTER(C.c_uint64), C.POINTER(C.c_double)]),
+    "kriya_cuda_paged_gqa_decode_static": (C.c_int32, [C.c_int32, _VP, C.c_uint32, _VP, _VP, _VP, C.c_uint32, _VP, _VP,
+                                                       _VP, _VP, C.c_uint32, _VP, C.POINTER(BsrGqaParams), C.c_char_p,
+                                                       C.c_size_t]),
     "kriya_cuda_launch_count": (C.c_uint64, [_VP]),
 }
 
