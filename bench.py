@@ -453,6 +453,62 @@ def run_kernel_case(args):
                           "kv_bytes_per_launch": kv_bytes, "attended_tokens": batch.attended_tokens,
                           "kv_gbs": kv_bytes / (ms / max(n, 1) * 1e-3) / 1e9 if case != "append" and n else None}))
         ex.close()
+    elif case == "kvsplit":
+        # one 131072-token sequence (Qwen2.5-3B shape) cut along the KV axis over WORLD_SIZE GPUs: per layer, the
+        # partial-state decode over this rank's block range, one all-gather of (m, l, o), the merge
+        import torch.distributed as dist
+
+        from kriya_rt_b200 import sharding
+
+        rank = int(os.environ.get("RANK", "0")); world = int(os.environ.get("WORLD_SIZE", "1"))
+        torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+        if world > 1:
+            dist.init_process_group("nccl", device_id=torch.device("cuda", torch.cuda.current_device()))
+        tokens, nb = 131072, 8192
+        b, e = sharding.kv_axis_ranges([nb], world)[rank]
+        n_local = int(e[0] - b[0])
+        ex = CudaExecutor(num_layers=1, num_kv_blocks=n_local, block_size_tokens=16, num_q_heads=16, num_kv_heads=2,
+                          head_dim=128, device=torch.cuda.current_device(), max_page_indices=nb)
+        fill(ex, 1)
+        table = sharding.local_block_table(np.zeros(nb), int(b[0]), int(e[0]), np.random.default_rng(rank).permutation(n_local))
+        ex.plan_upload([0, nb], table, [16], None, [tokens - 1])
+        q = rnd(1, 16, 128)
+        out = torch.zeros_like(q)
+        gp = ex.gqa_params()
+        rows = 16
+        scratch = (torch.empty(rows, device="cuda"), torch.empty(rows, device="cuda"), torch.empty(rows, 128, device="cuda"))
+        torch.cuda.synchronize()
+
+        def one(gather=True):
+            if world > 1 and gather:
+                sharding.kv_split_decode(ex, 0, q, b, e, out, gp, scratch=scratch)
+            else:
+                ex.paged_gqa_decode_partial(0, q, b, e, *scratch, gp)
+                ex.merge_states(*scratch, 1, rows, out)
+            ex.sync()
+
+        res = {}
+        for name, gather in (("with_gather", True), ("local_only", False)):
+            for _ in range(3):
+                one(gather)
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            for _ in range(reps):
+                one(gather)
+            torch.cuda.synchronize()
+            dt = torch.tensor([(time.perf_counter() - t0) / reps * 1e6], device="cuda", dtype=torch.float64)
+            if world > 1:
+                dist.all_reduce(dt, op=dist.ReduceOp.MAX)
+            res[name] = float(dt[0])
+        if rank == 0:
+            print(json.dumps({"case": case, "n_gpus": world, "tokens": tokens, "us_per_layer": res["with_gather"],
+                              "us_per_layer_without_gather": res["local_only"],
+                              "kv_bytes_per_gpu": n_local * 16 * 1024, "note": "host-timed, includes stream syncs around the collective"}))
+        ex.close()
+        if world > 1:
+            dist.destroy_process_group()
     elif case == "prefill":
         sh = W.QWEN25_1P5B
         total, chunk = 2048, 512
@@ -507,7 +563,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--kernel-case", default=None, choices=["decode", "decode_fused", "prefill", "append", "copy"],
+    ap.add_argument("--kernel-case", default=None, choices=["decode", "decode_fused", "prefill", "append", "copy", "kvsplit"],
                     help="run a few launches of one kernel on a small case (for ncu), --steps = launches")
     args = ap.parse_args()
     if args.kernel_case:

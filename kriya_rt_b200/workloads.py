@@ -8,7 +8,7 @@ Everything here is host-side numpy; nothing touches the GPU.
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import List, Optional
+from typing import Optional
 
 import numpy as np
 
@@ -169,15 +169,3 @@ def config1(seed_tensors: int = 1001, seed_tables: int = 2001, dtype: Optional[i
 def config2_contexts(seed_tables: int = 2002, batch: int = 32, lo: int = 512, hi: int = 4096) -> np.ndarray:
     rng = np.random.default_rng(seed_tables)
     return rng.integers(lo, hi + 1, size=batch)
-
-
-def lpt_assign(lengths: np.ndarray, ranks: int) -> List[List[int]]:
-    """Longest-processing-time assignment of sequences to ranks (balances attended tokens)."""
-    order = np.argsort(-np.asarray(lengths), kind="stable")
-    load = [0] * ranks
-    out: List[List[int]] = [[] for _ in range(ranks)]
-    for i in order:
-        r = int(np.argmin(load))
-        out[r].append(int(i))
-        load[r] += int(lengths[i])
-    return out
