@@ -180,6 +180,12 @@ int32_t kriya_cuda_paged_gqa_decode_partial(kriya_cuda_ctx* ctx, uint32_t layer,
 int32_t kriya_cuda_merge_states(kriya_cuda_ctx* ctx, const float* m_dev, const float* l_dev, const float* o_dev,
                                 uint32_t parts, uint32_t rows_times_heads, void* out_dev);
 
+/* The same merge for states that were gathered as ONE buffer per part: part s occupies
+ * packed[s * R * (D + 2) ...] as [m (R) | l (R) | o (R * D)], R = rows_times_heads.  A rank points the m / l / o outputs of
+ * kriya_cuda_paged_gqa_decode_partial into such a buffer and needs a single all-gather per layer. */
+int32_t kriya_cuda_merge_packed_states(kriya_cuda_ctx* ctx, const float* packed_dev, uint32_t parts,
+                                       uint32_t rows_times_heads, void* out_dev);
+
 /* bsr_paged_gqa_prefill_stage1 / _bq8 / bsr_paged_gqa_tiled_mma_prefill
  * (paged_gqa_and_deltanet.metal:508-847,851-1192,1206-1468; selection and dispatch enc:4262-4311).
  * Causal attention of a chunk of `num_tokens` queries of ONE sequence (row 0 of the current plan is

@@ -713,7 +713,20 @@ int32_t kriya_cuda_merge_states(kriya_cuda_ctx* c, const float* m, const float* 
     if (!c) return KRIYA_CUDA_INVALID_INPUT;
     if (!m || !l || !o || !out || parts == 0) return c->fail(KRIYA_CUDA_INVALID_INPUT, "merge needs states, an output and parts >= 1");
     cudaSetDevice(c->cfg.device);
-    KRIYA_CUDA_TRY(c, kriya_launch_merge_states(m, l, o, parts, rows_times_heads, c->cfg.head_dim, out, c->cfg.dtype, c->stream));
+    KRIYA_CUDA_TRY(c, kriya_launch_merge_states(m, l, o, parts, rows_times_heads, c->cfg.head_dim, rows_times_heads,
+                                                size_t(rows_times_heads) * c->cfg.head_dim, out, c->cfg.dtype, c->stream));
+    c->launches += 1;
+    return KRIYA_CUDA_OK;
+}
+
+int32_t kriya_cuda_merge_packed_states(kriya_cuda_ctx* c, const float* packed, uint32_t parts, uint32_t rows_times_heads,
+                                       void* out) {
+    if (!c) return KRIYA_CUDA_INVALID_INPUT;
+    if (!packed || !out || parts == 0) return c->fail(KRIYA_CUDA_INVALID_INPUT, "merge needs states, an output and parts >= 1");
+    cudaSetDevice(c->cfg.device);
+    const size_t R = rows_times_heads, stride = R * (size_t(c->cfg.head_dim) + 2);
+    KRIYA_CUDA_TRY(c, kriya_launch_merge_states(packed, packed + R, packed + 2 * R, parts, rows_times_heads, c->cfg.head_dim,
+                                                stride, stride, out, c->cfg.dtype, c->stream));
     c->launches += 1;
     return KRIYA_CUDA_OK;
 }

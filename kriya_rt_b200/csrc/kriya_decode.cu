@@ -377,25 +377,26 @@ __global__ void __launch_bounds__(kDecodeThreadsMax, 1) decode_kernel(KriyaDecod
 
 // Merge of partial states gathered from several ranks: [parts][rows] (m natural-log units, l) and
 // [parts][rows][D] (o)  ->  normalised 16-bit [rows][D].
+// `stride_ml` / `stride_o` are the distances, in floats, between consecutive parts of m, l and of o.
 template <typename T>
 __global__ void merge_states_kernel(const float* __restrict__ m, const float* __restrict__ l,
                                     const float* __restrict__ o, uint32_t parts, uint32_t rows, uint32_t D,
-                                    uint16_t* __restrict__ out) {
+                                    size_t stride_ml, size_t stride_o, uint16_t* __restrict__ out) {
     const uint32_t row = blockIdx.x;
     if (row >= rows) return;
     float M = -INFINITY;
-    for (uint32_t s = 0; s < parts; ++s) M = fmaxf(M, m[size_t(s) * rows + row]);
+    for (uint32_t s = 0; s < parts; ++s) M = fmaxf(M, m[s * stride_ml + row]);
     float den = 0.0f;
     for (uint32_t s = 0; s < parts; ++s) {
-        const float ms = m[size_t(s) * rows + row];
-        if (ms > -INFINITY) den = fmaf(expf(ms - M), l[size_t(s) * rows + row], den);
+        const float ms = m[s * stride_ml + row];
+        if (ms > -INFINITY) den = fmaf(expf(ms - M), l[s * stride_ml + row], den);
     }
     const float inv = 1.0f / fmaxf(den, 1e-12f);
     for (uint32_t d = threadIdx.x; d < D; d += blockDim.x) {
         float acc = 0.0f;
         for (uint32_t s = 0; s < parts; ++s) {
-            const float ms = m[size_t(s) * rows + row];
-            if (ms > -INFINITY) acc = fmaf(expf(ms - M), o[(size_t(s) * rows + row) * D + d], acc);
+            const float ms = m[s * stride_ml + row];
+            if (ms > -INFINITY) acc = fmaf(expf(ms - M), o[s * stride_o + size_t(row) * D + d], acc);
         }
         out[size_t(row) * D + d] = T::store(acc * inv);
     }
@@ -467,11 +468,14 @@ cudaError_t kriya_launch_decode(const KriyaDecodeArgs& a, uint32_t head_dim, uin
 }
 
 cudaError_t kriya_launch_merge_states(const float* m, const float* l, const float* o, uint32_t parts, uint32_t rows,
-                                      uint32_t D, void* out, uint32_t dtype, cudaStream_t s) {
+                                      uint32_t D, size_t stride_ml, size_t stride_o, void* out, uint32_t dtype,
+                                      cudaStream_t s) {
     if (rows == 0) return cudaSuccess;
     if (dtype == KRIYA_DTYPE_FP16)
-        kriya::merge_states_kernel<kriya::Fp16><<<rows, 128, 0, s>>>(m, l, o, parts, rows, D, static_cast<uint16_t*>(out));
+        kriya::merge_states_kernel<kriya::Fp16><<<rows, 128, 0, s>>>(m, l, o, parts, rows, D, stride_ml, stride_o,
+                                                                     static_cast<uint16_t*>(out));
     else
-        kriya::merge_states_kernel<kriya::Bf16><<<rows, 128, 0, s>>>(m, l, o, parts, rows, D, static_cast<uint16_t*>(out));
+        kriya::merge_states_kernel<kriya::Bf16><<<rows, 128, 0, s>>>(m, l, o, parts, rows, D, stride_ml, stride_o,
+                                                                     static_cast<uint16_t*>(out));
     return cudaGetLastError();
 }

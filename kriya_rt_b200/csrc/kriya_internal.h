@@ -206,7 +206,8 @@ cudaError_t kriya_launch_decode_tc(const KriyaDecodeArgs& a, const KriyaTcSeg* s
                                    int max_smem_optin, const KriyaFusedAppend& fused, cudaStream_t s);
 
 cudaError_t kriya_launch_merge_states(const float* m, const float* l, const float* o, uint32_t parts, uint32_t rows,
-                                      uint32_t D, void* out, uint32_t dtype, cudaStream_t s);
+                                      uint32_t D, size_t stride_ml, size_t stride_o, void* out, uint32_t dtype,
+                                      cudaStream_t s);
 
 cudaError_t kriya_launch_block_copy(uint8_t* pool_k, uint8_t* pool_v, size_t layer_stride_bytes, uint32_t num_layers,
                                     size_t block_bytes, const uint32_t* pairs_dev, uint32_t n_pairs, int sm_count,

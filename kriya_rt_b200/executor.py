@@ -168,6 +168,10 @@ class CudaExecutor:
         self._check(self._lib.kriya_cuda_merge_states(self._h, _ptr(m), _ptr(l), _ptr(o), parts, rows_times_heads,
                                                       _ptr(out)))
 
+    def merge_packed_states(self, packed, parts: int, rows_times_heads: int, out) -> None:
+        """States gathered as one [parts, R*(D+2)] buffer, each part laid out [m | l | o]."""
+        self._check(self._lib.kriya_cuda_merge_packed_states(self._h, _ptr(packed), parts, rows_times_heads, _ptr(out)))
+
     def paged_gqa_prefill(self, layer: int, q, out, prefix_tokens: int, num_tokens: int, params: BsrGqaParams) -> None:
         self._check(self._lib.kriya_cuda_paged_gqa_prefill(self._h, layer, _ptr(q), _ptr(out), prefix_tokens,
                                                            num_tokens, C.byref(params)))

@@ -65,19 +65,22 @@ def gather_states(m, l, o, group=None):
 
 def kv_split_decode(ex, layer: int, q, blk_begin, blk_end, out, gqa, group=None, scratch=None):
     """One KV-axis-split decode on this rank: partial state over [blk_begin, blk_end) of every row of the current
-    plan, all-gather, merge into `out` ([rows, Hq, D] in the storage dtype).  `scratch` may carry preallocated
-    (m, l, o) device tensors to keep the step path allocation-free."""
+    plan, ONE all-gather of the packed (m, l, o) states, merge into `out` ([rows, Hq, D] in the storage dtype).
+    Everything is queued on the executor's stream (the collective is ordered behind it by torch), so the host does
+    not wait in between.  `scratch` may carry preallocated (local [R*(D+2)], gathered [world, R*(D+2)]) fp32 device
+    tensors to keep the step path allocation-free."""
     import torch
+    import torch.distributed as dist
 
-    rows = ex.num_q_heads * int(len(blk_begin))
+    R = ex.num_q_heads * int(len(blk_begin))
+    D = ex.head_dim
+    world = dist.get_world_size(group)
     if scratch is None:
-        dev = q.device
-        scratch = (torch.empty(rows, device=dev), torch.empty(rows, device=dev), torch.empty(rows, ex.head_dim, device=dev))
-    m, l, o = scratch
-    ex.paged_gqa_decode_partial(layer, q, blk_begin, blk_end, m, l, o, gqa)
-    # the collective runs on torch's stream: order it after the context's stream
-    ex.sync()
-    m_all, l_all, o_all = gather_states(m, l, o, group)
-    torch.cuda.current_stream().synchronize()
-    ex.merge_states(m_all, l_all, o_all, m_all.shape[0], rows, out)
+        scratch = (torch.empty(R * (D + 2), device=q.device), torch.empty(world, R * (D + 2), device=q.device))
+    local, gathered = scratch
+    stream = torch.cuda.ExternalStream(ex.stream_ptr, device=q.device)
+    with torch.cuda.stream(stream):
+        ex.paged_gqa_decode_partial(layer, q, blk_begin, blk_end, local[:R], local[R:2 * R], local[2 * R:], gqa)
+        dist.all_gather_into_tensor(gathered, local, group=group)
+        ex.merge_packed_states(gathered, world, R, out)
     return out
