@@ -219,6 +219,8 @@ def run_gpu_arm(args):
                       head_dim=D, dtype=W.BF16, device=local_rank, rope_theta=SHAPE.rope_theta, rope_max_seq_len=8192,
                       max_batch_rows=64, max_page_indices=NUM_BLOCKS, max_tiles=4096, max_query_tokens=64)
     stream = torch.cuda.ExternalStream(ex.stream_ptr, device=torch.device("cuda", local_rank))
+    if args.serial_layers:
+        ex.set_fused_append(3)
 
     # KV pool: N(0,1) in every block of every layer (bf16), generated on the device
     gen = torch.Generator(device="cuda").manual_seed(1002 + rank)
@@ -571,6 +573,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--serial-layers", action="store_true",
+                    help="keep the layers' launches of a step strictly serialised (default: they may overlap at their edges)")
     ap.add_argument("--kernel-case", default=None, choices=["decode", "decode_fused", "prefill", "append", "copy", "kvsplit"],
                     help="run a few launches of one kernel on a small case (for ncu), --steps = launches")
     args = ap.parse_args()

@@ -223,8 +223,12 @@ int32_t kriya_cuda_decode_layer_host(kriya_cuda_ctx* ctx, uint32_t layer, const 
 int32_t kriya_cuda_append_decode(kriya_cuda_ctx* ctx, uint32_t layer, const void* q_dev, const void* k_in_dev,
                                  const void* v_in_dev, void* out_dev, void* q_rope_out_dev,
                                  const kriya_rope_kv_write_params* rope, const kriya_bsr_gqa_params* gqa);
-/* Whether kriya_cuda_decode_step / _host use the fused launch where it applies (default 1).  With 1 the step leaves
- * q un-rotated; with 0 it rotates q in place like the two separate kernels. */
+/* How kriya_cuda_decode_step / _host run a step.  Bit 0 (default set): use the fused launch where it applies; the step
+ * then leaves q un-rotated, while with bit 0 clear q is rotated in place by the separate append kernel.  Bit 1
+ * (default clear): keep the layers' launches strictly serialised; by default, from the second layer of a step on,
+ * a fused launch may begin while the previous layer's last thread blocks drain (programmatic dependent launch):
+ * layers of a step share only the split-row scratch, which the kernel does not touch before the previous grid has
+ * completed.  Pass 1 for the default, 0 for separate kernels, 3 for fused but serialised. */
 int32_t kriya_cuda_set_fused_append(kriya_cuda_ctx* ctx, int32_t enable);
 
 /* One decode step over ALL layers with device activations: for layer l = 0..num_layers-1, append then

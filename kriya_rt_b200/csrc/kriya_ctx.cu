@@ -859,8 +859,9 @@ int32_t kriya_cuda_decode_layer_host(kriya_cuda_ctx* c, uint32_t layer, const vo
     return kriya_cuda_sync(c, 0);
 }
 
-int32_t kriya_cuda_append_decode(kriya_cuda_ctx* c, uint32_t layer, const void* q, const void* k, const void* v, void* out,
-                                 void* q_rope_out, const kriya_rope_kv_write_params* rope, const kriya_bsr_gqa_params* gqa) {
+static int32_t append_decode_impl(kriya_cuda_ctx* c, uint32_t layer, const void* q, const void* k, const void* v, void* out,
+                                  void* q_rope_out, const kriya_rope_kv_write_params* rope, const kriya_bsr_gqa_params* gqa,
+                                  bool overlap_previous) {
     if (!c) return KRIYA_CUDA_INVALID_INPUT;
     if (int32_t rc = check_layer(c, layer)) return rc;
     if (int32_t rc = check_rope(c, rope)) return rc;
@@ -886,7 +887,13 @@ int32_t kriya_cuda_append_decode(kriya_cuda_ctx* c, uint32_t layer, const void* 
     f.max_seq_len = rope->max_seq_len;
     f.has_table = rope->has_table;
     f.rope_theta = rope->rope_theta;
+    f.overlap_previous = (overlap_previous && !c->timing) ? 1u : 0u;
     return launch_decode(c, layer, q, out, nullptr, nullptr, nullptr, false, c->n_work, gqa, f);
+}
+
+int32_t kriya_cuda_append_decode(kriya_cuda_ctx* c, uint32_t layer, const void* q, const void* k, const void* v, void* out,
+                                 void* q_rope_out, const kriya_rope_kv_write_params* rope, const kriya_bsr_gqa_params* gqa) {
+    return append_decode_impl(c, layer, q, k, v, out, q_rope_out, rope, gqa, false);
 }
 
 int32_t kriya_cuda_decode_step(kriya_cuda_ctx* c, void* q, const void* k, const void* v, void* out, uint32_t rows,
@@ -903,7 +910,10 @@ int32_t kriya_cuda_decode_step(kriya_cuda_ctx* c, void* q, const void* k, const 
         const uint8_t* vl = static_cast<const uint8_t*>(v) + layer * kb;
         uint8_t* ol = static_cast<uint8_t*>(out) + layer * qb;
         if (c->fuse_append && use_tc_decode(c) && !rope->apply_qk_norm) {
-            if (int32_t rc = kriya_cuda_append_decode(c, layer, ql, kl, vl, ol, nullptr, rope, gqa)) return rc;
+            // Layers of one step share nothing but the split-row scratch, which the kernel guards itself: from the
+            // second layer on, a launch may start while the previous layer's last CTAs drain.
+            if (int32_t rc = append_decode_impl(c, layer, ql, kl, vl, ol, nullptr, rope, gqa, layer > 0 && c->overlap_layers))
+                return rc;
         } else {
             if (int32_t rc = kriya_cuda_rope_kv_append(c, layer, ql, kl, vl, nullptr, nullptr, rows, rope)) return rc;
             if (int32_t rc = kriya_cuda_paged_gqa_decode(c, layer, ql, ol, gqa)) return rc;
@@ -956,7 +966,8 @@ int32_t kriya_cuda_set_decode_path(kriya_cuda_ctx* c, int32_t path) {
 
 int32_t kriya_cuda_set_fused_append(kriya_cuda_ctx* c, int32_t enable) {
     if (!c) return KRIYA_CUDA_INVALID_INPUT;
-    c->fuse_append = enable != 0;
+    c->fuse_append = (enable & 1) != 0;
+    c->overlap_layers = (enable & 2) == 0;  // bit 1 set: keep the layers of a step strictly serialised
     return KRIYA_CUDA_OK;
 }
 

@@ -111,6 +111,9 @@ __device__ unsigned long long g_trace[160 * 16];
 #define TR(k) do { } while (0)
 #define TRV(k, v) do { } while (0)
 #endif
+// Programmatic dependent launch: both are no-ops when the launch did not ask for it.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait_previous_grid() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void named_bar_sync_128() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 // Barrier over the 128 softmax threads that also ORs a predicate across them.
 __device__ __forceinline__ bool bar_or_128(bool pred) {
@@ -229,6 +232,9 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     if (threadIdx.x == 0) TR(0);
     const uint32_t seg_begin = pp.cta_seg_ptr[blockIdx.x], seg_end = pp.cta_seg_ptr[blockIdx.x + 1];
+    // The next launch of the stream may start as SMs free up: it only shares the split-row scratch with this one, and
+    // waits for this grid before touching it (see pdl_wait_previous_grid below).
+    if (threadIdx.x == 0) pdl_launch_dependents();
     if (seg_begin == seg_end) return;  // whole CTA idle: nothing allocated yet
 
     if (tid == 0) {
@@ -512,6 +518,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
             const KriyaTcSeg seg = segs_s[0];
             asm volatile("bar.sync 2, 160;" ::: "memory");  // the softmax threads have published the partial state
             if (*merge_job_ok) {
+                pdl_wait_previous_grid();
                 __threadfence();
                 uint32_t ticket = 0;
                 if (lane == 0) ticket = atomicAdd(&a.counters[seg.req * Hkv + seg.kv_head], 1u);
@@ -693,6 +700,8 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
                     }
                 }
             } else {
+                // the scratch and the tickets are shared with the previous launch: it must have drained first
+                pdl_wait_previous_grid();
                 const size_t prow = size_t(seg.slot) * G;
 #pragma unroll
                 for (int h = 0; h < G; ++h) {
@@ -746,7 +755,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
 
 template <int G, typename T>
 cudaError_t launch_tc_t(const TcParams& pp, const CUtensorMap& mk, const CUtensorMap& mv, uint32_t grid, int max_smem_optin,
-                        cudaStream_t s) {
+                        bool overlap_previous, cudaStream_t s) {
     const size_t smem = size_t(2 * kTcStages) * kTcKvBytes + 3 * kTcQBytes + 2 * kTcPBytes + 512 + 320 + 512 + 8 * sizeof(KriyaTcSeg) + 1024;
     if (smem > size_t(max_smem_optin)) return cudaErrorInvalidValue;
     auto kern = decode_tc_kernel<G, T>;
@@ -756,7 +765,22 @@ cudaError_t launch_tc_t(const TcParams& pp, const CUtensorMap& mk, const CUtenso
         if (e != cudaSuccess) return e;
         attr_set = true;
     }
-    kern<<<grid, kTcThreads, smem, s>>>(mk, mv, pp);
+    if (overlap_previous) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(grid);
+        cfg.blockDim = dim3(kTcThreads);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = s;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        cudaError_t e = cudaLaunchKernelEx(&cfg, kern, mk, mv, pp);
+        if (e != cudaSuccess) return e;
+    } else {
+        kern<<<grid, kTcThreads, smem, s>>>(mk, mv, pp);
+    }
 #ifdef KRIYA_TC_TRACE
     if (getenv("KRIYA_TRACE")) {
         static int calls = 0;
@@ -782,16 +806,16 @@ cudaError_t launch_tc_t(const TcParams& pp, const CUtensorMap& mk, const CUtenso
 
 template <typename T>
 cudaError_t launch_tc_g(uint32_t group, const TcParams& pp, const CUtensorMap& mk, const CUtensorMap& mv, uint32_t grid,
-                        int max_smem_optin, cudaStream_t s) {
+                        int max_smem_optin, bool ov, cudaStream_t s) {
     switch (group) {
-        case 1: return launch_tc_t<1, T>(pp, mk, mv, grid, max_smem_optin, s);
-        case 2: return launch_tc_t<2, T>(pp, mk, mv, grid, max_smem_optin, s);
-        case 3: return launch_tc_t<3, T>(pp, mk, mv, grid, max_smem_optin, s);
-        case 4: return launch_tc_t<4, T>(pp, mk, mv, grid, max_smem_optin, s);
-        case 5: return launch_tc_t<5, T>(pp, mk, mv, grid, max_smem_optin, s);
-        case 6: return launch_tc_t<6, T>(pp, mk, mv, grid, max_smem_optin, s);
-        case 7: return launch_tc_t<7, T>(pp, mk, mv, grid, max_smem_optin, s);
-        case 8: return launch_tc_t<8, T>(pp, mk, mv, grid, max_smem_optin, s);
+        case 1: return launch_tc_t<1, T>(pp, mk, mv, grid, max_smem_optin, ov, s);
+        case 2: return launch_tc_t<2, T>(pp, mk, mv, grid, max_smem_optin, ov, s);
+        case 3: return launch_tc_t<3, T>(pp, mk, mv, grid, max_smem_optin, ov, s);
+        case 4: return launch_tc_t<4, T>(pp, mk, mv, grid, max_smem_optin, ov, s);
+        case 5: return launch_tc_t<5, T>(pp, mk, mv, grid, max_smem_optin, ov, s);
+        case 6: return launch_tc_t<6, T>(pp, mk, mv, grid, max_smem_optin, ov, s);
+        case 7: return launch_tc_t<7, T>(pp, mk, mv, grid, max_smem_optin, ov, s);
+        case 8: return launch_tc_t<8, T>(pp, mk, mv, grid, max_smem_optin, ov, s);
         default: return cudaErrorInvalidValue;
     }
 }
@@ -816,6 +840,7 @@ cudaError_t kriya_launch_decode_tc(const KriyaDecodeArgs& a, const KriyaTcSeg* s
     pp.f = fused;
     const CUtensorMap& mk = *static_cast<const CUtensorMap*>(map_k);
     const CUtensorMap& mv = *static_cast<const CUtensorMap*>(map_v);
-    return dtype == KRIYA_DTYPE_FP16 ? kriya::launch_tc_g<kriya::Fp16>(group, pp, mk, mv, grid, max_smem_optin, s)
-                                     : kriya::launch_tc_g<kriya::Bf16>(group, pp, mk, mv, grid, max_smem_optin, s);
+    const bool ov = fused.overlap_previous != 0;
+    return dtype == KRIYA_DTYPE_FP16 ? kriya::launch_tc_g<kriya::Fp16>(group, pp, mk, mv, grid, max_smem_optin, ov, s)
+                                     : kriya::launch_tc_g<kriya::Bf16>(group, pp, mk, mv, grid, max_smem_optin, ov, s);
 }

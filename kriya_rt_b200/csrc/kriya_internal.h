@@ -79,6 +79,7 @@ struct kriya_cuda_ctx {
     size_t off_indptr = 0, off_indices = 0, off_last_len = 0, off_tiles = 0, off_positions = 0, off_work = 0,
            off_range = 0, off_tcseg = 0, off_tcptr = 0, off_tcseg2 = 0, off_tcptr2 = 0;
     uint32_t cap_seg = 0, n_seg = 0;
+    bool overlap_layers = true;  // whole-step calls let consecutive layers' launches overlap at their edges
     bool fuse_append = true;  // whole-step calls use the fused append + decode launch where it applies
     int decode_path = 0;  // 0: pick per shape, 1: CUDA-core kernel, 2: tensor-core kernel
     uint32_t cap_rows = 0, cap_indices = 0, cap_tiles = 0, cap_tokens = 0, cap_work = 0;
@@ -199,6 +200,10 @@ struct KriyaFusedAppend {
     uint32_t max_seq_len = 0;
     uint32_t has_table = 0;
     float rope_theta = 0.0f;
+    // Host-side launch option: let this launch begin while the previous kernel of the stream drains (programmatic
+    // dependent launch).  Only valid when every input of this launch is already complete, i.e. between the layers
+    // of one whole-step call; the kernel itself waits for the previous grid before it touches the shared scratch.
+    uint32_t overlap_previous = 0;
 };
 bool kriya_decode_tc_supported(uint32_t head_dim, uint32_t group, uint32_t block_size);
 cudaError_t kriya_launch_decode_tc(const KriyaDecodeArgs& a, const KriyaTcSeg* segs, const uint32_t* cta_seg_ptr, uint32_t grid,

@@ -208,8 +208,10 @@ class CudaExecutor:
         self._check(self._lib.kriya_cuda_append_decode(self._h, layer, _ptr(q), _ptr(k_in), _ptr(v_in), _ptr(out),
                                                        _ptr(q_rope_out), C.byref(rope), C.byref(gqa)))
 
-    def set_fused_append(self, enable: bool) -> None:
-        self._check(self._lib.kriya_cuda_set_fused_append(self._h, int(enable)))
+    def set_fused_append(self, mode) -> None:
+        """1 / True: fused launches, consecutive layers may overlap at their edges (default); 0 / False: separate
+        append and decode kernels; 3: fused but strictly serialised layers."""
+        self._check(self._lib.kriya_cuda_set_fused_append(self._h, int(mode)))
 
     def set_decode_path(self, path: int) -> None:
         """0 = by shape, 1 = CUDA-core decode kernel, 2 = tensor-core decode kernel."""
