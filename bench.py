@@ -519,6 +519,41 @@ def run_kernel_case(args):
         ex.close()
         if world > 1:
             dist.destroy_process_group()
+    elif case == "prefill_batch":
+        # Qwen2.5-1.5B shape, eight 2048-token prompts, the four 512-token chunks of every prompt, one launch per chunk index
+        sh = W.QWEN25_1P5B
+        n_seq, total, chunk = 8, 2048, 512
+        nb = n_seq * total // 16
+        ex = CudaExecutor(num_layers=1, num_kv_blocks=nb, block_size_tokens=16, num_q_heads=12, num_kv_heads=2,
+                          head_dim=128, rope_theta=sh.rope_theta, max_query_tokens=n_seq * chunk)
+        fill(ex, 1)
+        perm = np.random.default_rng(3).permutation(nb).astype(np.int32)
+        per = total // 16
+        ex.plan_upload(np.arange(n_seq + 1) * per, perm, [16] * n_seq)
+        q = rnd(n_seq * chunk, 12, 128)
+        out = torch.zeros_like(q)
+        torch.cuda.synchronize()
+        gp = ex.gqa_params(max_query_tokens=chunk)
+        stream = torch.cuda.ExternalStream(ex.stream_ptr)
+        starts = np.arange(n_seq) * chunk
+
+        def all_chunks():
+            for prefix in range(0, total, chunk):
+                ex.paged_gqa_prefill_batch(0, q, out, starts, [prefix] * n_seq, [chunk] * n_seq, gp)
+
+        all_chunks()
+        ex.sync()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(reps):
+            all_chunks()
+        e1.record(stream)
+        ex.sync()
+        us = e0.elapsed_time(e1) / reps * 1e3
+        flop = n_seq * 4 * 12 * 128 * (total * (total + 1) // 2)
+        print(json.dumps({"case": case, "launches_per_pass": total // chunk, "us_per_pass": us, "flop_per_pass": flop,
+                          "tflops": flop / (us * 1e-6) / 1e12, "prompt_tokens_per_s_per_layer": n_seq * total / (us * 1e-6)}))
+        ex.close()
     elif case == "prefill":
         sh = W.QWEN25_1P5B
         total, chunk = 2048, 512
@@ -575,7 +610,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--serial-layers", action="store_true",
                     help="keep the layers' launches of a step strictly serialised (default: they may overlap at their edges)")
-    ap.add_argument("--kernel-case", default=None, choices=["decode", "decode_fused", "prefill", "append", "copy", "kvsplit"],
+    ap.add_argument("--kernel-case", default=None, choices=["decode", "decode_fused", "prefill", "prefill_batch", "append", "copy", "kvsplit"],
                     help="run a few launches of one kernel on a small case (for ncu), --steps = launches")
     args = ap.parse_args()
     if args.kernel_case:

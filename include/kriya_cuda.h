@@ -194,6 +194,14 @@ int32_t kriya_cuda_merge_packed_states(kriya_cuda_ctx* ctx, const float* packed_
 int32_t kriya_cuda_paged_gqa_prefill(kriya_cuda_ctx* ctx, uint32_t layer, const void* q_dev, void* out_dev,
                                      uint32_t prefix_tokens, uint32_t num_tokens, const kriya_bsr_gqa_params* params);
 
+/* The same for the chunks of several sequences in ONE launch (the reference loops over requests on the host, one
+ * forward_prefill_batch call each, crates/kriya-server/src/runtime.rs:315-377): plan row r is sequence r's block table;
+ * its `count_host[r]` queries start at row `q_start_host[r]` of q / out and sit at absolute positions
+ * `prefix_host[r] + i`.  All arrays are host memory with n_seqs entries. */
+int32_t kriya_cuda_paged_gqa_prefill_batch(kriya_cuda_ctx* ctx, uint32_t layer, const void* q_dev, void* out_dev,
+                                           uint32_t n_seqs, const uint32_t* q_start_host, const uint32_t* prefix_host,
+                                           const uint32_t* count_host, const kriya_bsr_gqa_params* params);
+
 /* Copy-on-write block copy: for every (src, dst) pair, in order, block dst := block src in every
  * layer, K and V.  Consumes the pairs produced by append_token_slot (bsr_paged.rs:412-420) and
  * collected in ScheduledIterationBatch.cow_block_copies (crates/kriya-scheduler/src/orca_engine.rs:

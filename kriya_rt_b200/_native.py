@@ -117,6 +117,8 @@ CUDA_SYMBOLS = {
     "kriya_cuda_merge_packed_states": (C.c_int32, [_VP, _VP, C.c_uint32, C.c_uint32, _VP]),
     "kriya_cuda_paged_gqa_prefill": (C.c_int32, [_VP, C.c_uint32, _VP, _VP, C.c_uint32, C.c_uint32,
                                                  C.POINTER(BsrGqaParams)]),
+    "kriya_cuda_paged_gqa_prefill_batch": (C.c_int32, [_VP, C.c_uint32, _VP, _VP, C.c_uint32, _VP, _VP, _VP,
+                                                       C.POINTER(BsrGqaParams)]),
     "kriya_cuda_kv_block_copy": (C.c_int32, [_VP, _VP, C.c_uint32]),
     "kriya_cuda_kv_slot_write": (C.c_int32, [_VP, C.c_uint32, _VP, _VP, _VP, C.c_uint32]),
     "kriya_cuda_decode_layer_host": (C.c_int32, [_VP, C.c_uint32, _VP, _VP, _VP, _VP, C.c_uint32,

@@ -731,35 +731,56 @@ int32_t kriya_cuda_merge_packed_states(kriya_cuda_ctx* c, const float* packed, u
     return KRIYA_CUDA_OK;
 }
 
-int32_t kriya_cuda_paged_gqa_prefill(kriya_cuda_ctx* c, uint32_t layer, const void* q, void* out, uint32_t prefix_tokens,
-                                     uint32_t num_tokens, const kriya_bsr_gqa_params* p) {
+int32_t kriya_cuda_paged_gqa_prefill_batch(kriya_cuda_ctx* c, uint32_t layer, const void* q, void* out, uint32_t n_seqs,
+                                           const uint32_t* q_start, const uint32_t* prefix, const uint32_t* count,
+                                           const kriya_bsr_gqa_params* p) {
     if (!c) return KRIYA_CUDA_INVALID_INPUT;
     if (int32_t rc = check_layer(c, layer)) return rc;
     if (int32_t rc = check_gqa(c, p)) return rc;
     if (!c->plan_valid) return c->fail(KRIYA_CUDA_INVALID_INPUT, "no plan uploaded");
-    if (!q || !out) return c->fail(KRIYA_CUDA_INVALID_INPUT, "q and out must not be null");
-    if (num_tokens == 0) return c->fail(KRIYA_CUDA_INVALID_INPUT, "input_tokens must not be empty");
-    if (num_tokens > c->cap_tokens) return c->fail(KRIYA_CUDA_INVALID_INPUT, "chunk exceeds max_query_tokens");
-    const uint64_t end = uint64_t(prefix_tokens) + num_tokens;
-    if (end > uint64_t(c->row0_blocks) * c->cfg.block_size_tokens)
-        return c->fail(KRIYA_CUDA_INVALID_INPUT, "chunk ends at token " + std::to_string(end) + " but row 0 of the plan holds " +
-                                                     std::to_string(c->row0_blocks) + " blocks");
+    if (!q || !out || !q_start || !prefix || !count) return c->fail(KRIYA_CUDA_INVALID_INPUT, "q, out and the per-sequence arrays must not be null");
+    if (n_seqs == 0) return c->fail(KRIYA_CUDA_INVALID_INPUT, "input_tokens must not be empty");
+    if (n_seqs > c->n_rows) return c->fail(KRIYA_CUDA_INVALID_INPUT, "more sequences than plan rows");
     if (!kriya_prefill_supported(c->cfg.head_dim, c->cfg.num_q_heads / c->cfg.num_kv_heads, c->cfg.block_size_tokens,
                                  c->cfg.dtype) || !c->tmaps_ok)
         return c->fail(KRIYA_CUDA_UNSUPPORTED, "prefill kernels cover head_dim 64/128 and 16-token blocks");
     cudaSetDevice(c->cfg.device);
+    KRIYA_CUDA_TRY(c, cudaEventSynchronize(c->h_pairs_free));
+    const int32_t* indptr = reinterpret_cast<const int32_t*>(c->h_plan_last + c->off_indptr);
+    auto* tiles = reinterpret_cast<KriyaPrefillTile*>(c->h_pairs);
+    const uint32_t cap_tiles = uint32_t(size_t(c->cap_pairs) * 3 * sizeof(uint32_t) / sizeof(KriyaPrefillTile));
+    uint32_t n = 0;
+    for (uint32_t r = 0; r < n_seqs; ++r) {
+        if (count[r] == 0) return c->fail(KRIYA_CUDA_INVALID_INPUT, "input_tokens must not be empty");
+        const uint64_t end = uint64_t(prefix[r]) + count[r];
+        const uint64_t row_cap = uint64_t(indptr[r + 1] - indptr[r]) * c->cfg.block_size_tokens;
+        if (end > row_cap)
+            return c->fail(KRIYA_CUDA_INVALID_INPUT, "chunk of sequence " + std::to_string(r) + " ends at token " + std::to_string(end) +
+                                                         " but its plan row holds " + std::to_string(row_cap / c->cfg.block_size_tokens) + " blocks");
+        if (uint64_t(q_start[r]) + count[r] > c->cap_tokens) return c->fail(KRIYA_CUDA_INVALID_INPUT, "chunk exceeds max_query_tokens");
+        for (uint32_t t0 = 0; t0 < count[r]; t0 += 128u) {
+            if (n >= cap_tiles) return c->fail(KRIYA_CUDA_INVALID_INPUT, "more query tiles than the context holds");
+            tiles[n++] = KriyaPrefillTile{uint32_t(indptr[r]), q_start[r] + t0, std::min(128u, count[r] - t0), prefix[r] + t0,
+                                          uint32_t(end), {0u, 0u, 0u}};
+        }
+    }
+    std::stable_sort(tiles, tiles + n, [](const KriyaPrefillTile& x, const KriyaPrefillTile& y) {
+        return (x.pos0 + x.rows) > (y.pos0 + y.rows);
+    });
+    KRIYA_CUDA_TRY(c, cudaMemcpyAsync(c->d_pairs, tiles, size_t(n) * sizeof(KriyaPrefillTile), cudaMemcpyHostToDevice, c->stream));
+    KRIYA_CUDA_TRY(c, cudaEventRecord(c->h_pairs_free, c->stream));
     KriyaPrefillArgs a{};
     a.q = q;
     a.cache_k = c->layer_k(layer);
     a.cache_v = c->layer_v(layer);
     a.layer_row0 = uint32_t(size_t(layer) * c->layer_stride_bytes / (size_t(c->cfg.num_kv_heads) * c->cfg.head_dim * 2));
     a.table = c->plan_dev<int32_t>(c->off_indices);
+    a.tiles = reinterpret_cast<const KriyaPrefillTile*>(c->d_pairs);
     a.map_k = c->tmap_k;
     a.map_v = c->tmap_v;
     a.out = out;
     a.status = c->d_status;
-    a.num_tokens = num_tokens;
-    a.prefix_tokens = prefix_tokens;
+    a.n_tiles = n;
     a.num_blocks = c->cfg.num_kv_blocks;
     a.num_q_heads = c->cfg.num_q_heads;
     a.num_kv_heads = c->cfg.num_kv_heads;
@@ -769,6 +790,12 @@ int32_t kriya_cuda_paged_gqa_prefill(kriya_cuda_ctx* c, uint32_t layer, const vo
                                            c->stream));
     c->launches += 1;
     return KRIYA_CUDA_OK;
+}
+
+int32_t kriya_cuda_paged_gqa_prefill(kriya_cuda_ctx* c, uint32_t layer, const void* q, void* out, uint32_t prefix_tokens,
+                                     uint32_t num_tokens, const kriya_bsr_gqa_params* p) {
+    const uint32_t zero = 0;
+    return kriya_cuda_paged_gqa_prefill_batch(c, layer, q, out, 1, &zero, &prefix_tokens, &num_tokens, p);
 }
 
 int32_t kriya_cuda_kv_block_copy(kriya_cuda_ctx* c, const uint32_t* pairs, uint32_t n_pairs) {

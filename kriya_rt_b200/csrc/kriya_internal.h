@@ -221,17 +221,28 @@ cudaError_t kriya_launch_slot_write(uint8_t* cache_k, uint8_t* cache_v, const vo
                                     size_t row_bytes, uint32_t block_size, const uint32_t* triples_dev, uint32_t n,
                                     uint32_t num_blocks, uint32_t* status, cudaStream_t s);
 
+// One 128-query tile of a prefill launch.
+struct KriyaPrefillTile {
+    uint32_t tbl_off;  // where the sequence's block table starts inside page_indices
+    uint32_t q_row0;   // first row of the tile in q / out
+    uint32_t rows;     // 1..128
+    uint32_t pos0;     // absolute position of the tile's first query (prefix + offset inside the chunk)
+    uint32_t seq_end;  // tokens of the sequence present in the cache (prefix + chunk length)
+    uint32_t _pad[3];
+};
+static_assert(sizeof(KriyaPrefillTile) == 32, "tile record is 32 bytes");
+
 struct KriyaPrefillArgs {
     const void* q;        // [T][Hq][D]
     const void* cache_k;  // layer base
     const void* cache_v;
     const void* map_k;    // CUtensorMap over the K pool (host copy)
     const void* map_v;
-    const int32_t* table; // row 0 of the plan
+    const int32_t* table; // page_indices of the plan
+    const KriyaPrefillTile* tiles;
     void* out;            // [T][Hq][D]
     uint32_t* status;
-    uint32_t num_tokens;
-    uint32_t prefix_tokens;
+    uint32_t n_tiles;
     uint32_t num_blocks;
     uint32_t num_q_heads;
     uint32_t num_kv_heads;

@@ -36,7 +36,7 @@ constexpr float kRescaleThreshold = 8.0f;
 
 struct PrefillParams {
     KriyaPrefillArgs a;
-    uint32_t q_tiles;
+    uint32_t q_tiles;  // query tiles of the whole launch (all sequences)
     uint32_t dtype;
 };
 
@@ -77,15 +77,16 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
     const KriyaPrefillArgs& a = pp.a;
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     // heavy tiles (late queries see more keys) first
-    const uint32_t q_tile = pp.q_tiles - 1u - (blockIdx.x % pp.q_tiles);
+    // tiles arrive sorted, most keys first
+    const KriyaPrefillTile qt = a.tiles[blockIdx.x % pp.q_tiles];
     const uint32_t q_head = blockIdx.x / pp.q_tiles;
     const uint32_t group = a.num_q_heads / a.num_kv_heads;
     const uint32_t kv_head = q_head / group;
-    const uint32_t tile_start = q_tile * kQTile;
-    const uint32_t tile_rows = min(uint32_t(kQTile), a.num_tokens - tile_start);
-    const uint32_t kv_limit = a.prefix_tokens + tile_start + tile_rows;  // keys [0, kv_limit) can be seen by this tile
+    const uint32_t tile_start = qt.q_row0;  // first row of this tile in q / out
+    const uint32_t tile_rows = qt.rows;
+    const uint32_t kv_limit = qt.pos0 + tile_rows;  // keys [0, kv_limit) of the sequence can be seen by this tile
     const uint32_t n_tiles = (kv_limit + kKvTile - 1) / kKvTile;
-    const uint32_t seq_end = a.prefix_tokens + a.num_tokens;  // tokens that exist in the cache
+    const uint32_t seq_end = qt.seq_end;  // tokens of the sequence that exist in the cache
 
     // ---- setup -------------------------------------------------------------------------------------------
     if (tid == 0) {
@@ -128,7 +129,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
 
     if (warp == 4) {
         // ---- producer: gather the tile's pages through the block table --------------------------------
-        const int32_t* table = a.table;
+        const int32_t* table = a.table + qt.tbl_off;
         for (uint32_t j = 0; j < n_tiles; ++j) {
             if (*abort_flag) break;
             const uint32_t stage = j & 1u;
@@ -219,7 +220,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
         const uint32_t lane_addr = (warp * 32u) << 16;
         const bool softcap = a.logit_softcap > 0.0f;
         const float scale2 = softcap ? a.sm_scale : a.sm_scale * kLog2ePf;
-        const uint32_t q_pos = a.prefix_tokens + tile_start + min(row, tile_rows - 1u);  // absolute position
+        const uint32_t q_pos = qt.pos0 + min(row, tile_rows - 1u);  // absolute position
         float m_used = -INFINITY, l_run = 0.0f;
         bool ok = true;
         for (uint32_t j = 0; j < n_tiles; ++j) {
@@ -229,7 +230,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
             tc_fence_after();
             const uint32_t s_addr = tmem_base + lane_addr + ((j & 1u) ? COL_S1 : COL_S0);
             const uint32_t key0 = j * kKvTile;
-            const bool diag = key0 + kKvTile - 1u > a.prefix_tokens + tile_start;  // some row of the tile masks some key
+            const bool diag = key0 + kKvTile - 1u > qt.pos0;  // some row of the tile masks some key
             // pass 1: row maximum
             float m_tile = -INFINITY;
 #pragma unroll 1
@@ -377,7 +378,7 @@ cudaError_t launch_prefill_t(const KriyaPrefillArgs& a, const CUtensorMap& mk, c
     if (e != cudaSuccess) return e;
     PrefillParams pp;
     pp.a = a;
-    pp.q_tiles = (a.num_tokens + kQTile - 1) / kQTile;
+    pp.q_tiles = a.n_tiles;
     pp.dtype = T::kDtype;
     kern<<<pp.q_tiles * a.num_q_heads, kPrefillThreads, smem, s>>>(mk, mv, pp);
     return cudaGetLastError();
@@ -420,7 +421,7 @@ cudaError_t kriya_prefill_encode_maps(void* pool_k, void* pool_v, uint64_t total
 
 cudaError_t kriya_launch_prefill(const KriyaPrefillArgs& a, uint32_t head_dim, uint32_t block_size, uint32_t dtype,
                                  int max_smem_optin, cudaStream_t s) {
-    if (a.num_tokens == 0) return cudaSuccess;
+    if (a.n_tiles == 0) return cudaSuccess;
     if (!kriya_prefill_supported(head_dim, a.num_q_heads / a.num_kv_heads, block_size, dtype) || !a.map_k || !a.map_v)
         return cudaErrorInvalidValue;
     const CUtensorMap& mk = *static_cast<const CUtensorMap*>(a.map_k);

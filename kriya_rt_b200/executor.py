@@ -176,6 +176,14 @@ class CudaExecutor:
         self._check(self._lib.kriya_cuda_paged_gqa_prefill(self._h, layer, _ptr(q), _ptr(out), prefix_tokens,
                                                            num_tokens, C.byref(params)))
 
+    def paged_gqa_prefill_batch(self, layer: int, q, out, q_start, prefix, count, params: BsrGqaParams) -> None:
+        """Chunks of several sequences in one launch; plan row r is sequence r's table."""
+        qs = np.ascontiguousarray(q_start, np.uint32)
+        pf = np.ascontiguousarray(prefix, np.uint32)
+        ct = np.ascontiguousarray(count, np.uint32)
+        self._check(self._lib.kriya_cuda_paged_gqa_prefill_batch(self._h, layer, _ptr(q), _ptr(out), qs.size, qs.ctypes.data,
+                                                                 pf.ctypes.data, ct.ctypes.data, C.byref(params)))
+
     def kv_block_copy(self, pairs: Sequence) -> None:
         arr = np.ascontiguousarray(pairs, dtype=np.uint32).reshape(-1, 2)
         self._check(self._lib.kriya_cuda_kv_block_copy(self._h, arr.ctypes.data, arr.shape[0]))

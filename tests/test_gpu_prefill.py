@@ -107,3 +107,34 @@ def test_prefill_last_row_equals_decode():
     total = 517
     got, ref, (gk, gv), _ = chunked_prefill(shape, total, 517, seed=3, poison=False)
     assert np.abs(got[-1] - ref[-1]).max() <= 1e-2
+
+
+def test_batched_prefill_three_sequences_one_launch():
+    """Chunks of three sequences (different prefixes, ragged lengths) in one launch, each against the oracle."""
+    shape = W.AttnShape("batch", 12, 2, 128, W.BF16, rope_theta=1e6)
+    Hq, Hkv, D = 12, 2, 128
+    nb = 256
+    mgr = PagedKvCacheManager(nb, 0, 16)
+    specs = [(300, 140, 160), (64, 0, 64), (517, 400, 117)]  # (total tokens so far, prefix, chunk length)
+    rng = np.random.default_rng(91)
+    ck = W.normal16(rng, (nb, 16, Hkv, D), W.BF16); cv = W.normal16(rng, (nb, 16, Hkv, D), W.BF16)
+    for i, (total, _, _) in enumerate(specs):
+        mgr.allocate_sequence(i, list(range(1000 * i, 1000 * i + total)))
+    plan = mgr.build_schedule_plan([0, 1, 2], 8)
+    counts = [c for _, _, c in specs]
+    starts = np.concatenate([[0], np.cumsum(counts)[:-1]])
+    q = W.normal16(rng, (sum(counts), Hq, D), W.BF16)
+    ex = make_executor(shape, nb)
+    fill_cache(ex, 0, ck, cv)
+    dq = dev16(q)
+    out = torch.zeros_like(dq)
+    torch.cuda.synchronize()
+    ex.upload_schedule_plan(plan)
+    ex.paged_gqa_prefill_batch(0, dq, out, starts, [p for _, p, _ in specs], counts, ex.gqa_params(max_query_tokens=160))
+    ex.sync()
+    got = W.from_storage(host16(out), W.BF16)
+    for i, (total, prefix, cnt) in enumerate(specs):
+        table, _ = mgr.sequence_table(i)
+        _, ref = O.prefill_causal(q[starts[i]:starts[i] + cnt], ck, cv, np.asarray(table, np.int32), prefix, oracle_gqa(ex), W.BF16)
+        assert np.abs(got[starts[i]:starts[i] + cnt] - ref).max() <= 1e-2, i
+    ex.close()
