@@ -34,6 +34,7 @@ void destroy(kriya_cuda_ctx* c) {
     cudaSetDevice(c->cfg.device);
     if (c->stream) cudaStreamSynchronize(c->stream);
     if (c->copy_stream) cudaStreamSynchronize(c->copy_stream);
+    if (c->copy_stream_out) cudaStreamSynchronize(c->copy_stream_out);
     cudaFree(c->pool_k);
     cudaFree(c->pool_v);
     cudaFree(c->rope_table);
@@ -54,8 +55,13 @@ void destroy(kriya_cuda_ctx* c) {
     if (c->h_act) cudaFreeHost(c->h_act);
     if (c->h_pairs) cudaFreeHost(c->h_pairs);
     if (c->h_pairs_free) cudaEventDestroy(c->h_pairs_free);
+    for (cudaEvent_t e : c->ev_in) cudaEventDestroy(e);
+    for (cudaEvent_t e : c->ev_done) cudaEventDestroy(e);
+    if (c->ev_step_begin) cudaEventDestroy(c->ev_step_begin);
+    if (c->ev_step_end) cudaEventDestroy(c->ev_step_end);
     if (c->stream) cudaStreamDestroy(c->stream);
     if (c->copy_stream) cudaStreamDestroy(c->copy_stream);
+    if (c->copy_stream_out) cudaStreamDestroy(c->copy_stream_out);
     delete c;
 }
 
@@ -384,6 +390,15 @@ int32_t kriya_cuda_ctx_create(const kriya_cuda_config* cfg_in, kriya_cuda_ctx** 
 
     CREATE_TRY(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
     CREATE_TRY(cudaStreamCreateWithFlags(&c->copy_stream, cudaStreamNonBlocking));
+    CREATE_TRY(cudaStreamCreateWithFlags(&c->copy_stream_out, cudaStreamNonBlocking));
+    CREATE_TRY(cudaEventCreateWithFlags(&c->ev_step_begin, cudaEventDisableTiming));
+    CREATE_TRY(cudaEventCreateWithFlags(&c->ev_step_end, cudaEventDisableTiming));
+    c->ev_in.resize((cfg.num_layers + 3) / 4);
+    c->ev_done.resize((cfg.num_layers + 3) / 4);
+    for (size_t i = 0; i < c->ev_in.size(); ++i) {
+        CREATE_TRY(cudaEventCreateWithFlags(&c->ev_in[i], cudaEventDisableTiming));
+        CREATE_TRY(cudaEventCreateWithFlags(&c->ev_done[i], cudaEventDisableTiming));
+    }
     const size_t pool_bytes = c->layer_stride_bytes * cfg.num_layers;
     CREATE_TRY(cudaMalloc(&c->pool_k, pool_bytes));
     CREATE_TRY(cudaMalloc(&c->pool_v, pool_bytes));
@@ -923,15 +938,13 @@ int32_t kriya_cuda_append_decode(kriya_cuda_ctx* c, uint32_t layer, const void* 
     return append_decode_impl(c, layer, q, k, v, out, q_rope_out, rope, gqa, false);
 }
 
-int32_t kriya_cuda_decode_step(kriya_cuda_ctx* c, void* q, const void* k, const void* v, void* out, uint32_t rows,
-                               const kriya_rope_kv_write_params* rope, const kriya_bsr_gqa_params* gqa) {
-    if (!c) return KRIYA_CUDA_INVALID_INPUT;
-    if (!q || !k || !v || !out) return c->fail(KRIYA_CUDA_INVALID_INPUT, "q, k, v and out must not be null");
-    if (!c->plan_valid) return c->fail(KRIYA_CUDA_INVALID_INPUT, "no plan uploaded");
-    if (rows == 0 || rows != c->n_rows) return c->fail(KRIYA_CUDA_INVALID_INPUT, "rows must equal the plan's row count");
+// Layers [l0, l1) of one step; `first_of_chain` says that the launch for l0 must not overlap what precedes it.
+static int32_t decode_layers(kriya_cuda_ctx* c, uint32_t l0, uint32_t l1, bool first_of_chain, void* q, const void* k,
+                             const void* v, void* out, uint32_t rows, const kriya_rope_kv_write_params* rope,
+                             const kriya_bsr_gqa_params* gqa) {
     const size_t qb = size_t(rows) * c->cfg.num_q_heads * c->cfg.head_dim * 2;
     const size_t kb = size_t(rows) * c->cfg.num_kv_heads * c->cfg.head_dim * 2;
-    for (uint32_t layer = 0; layer < c->cfg.num_layers; ++layer) {
+    for (uint32_t layer = l0; layer < l1; ++layer) {
         uint8_t* ql = static_cast<uint8_t*>(q) + layer * qb;
         const uint8_t* kl = static_cast<const uint8_t*>(k) + layer * kb;
         const uint8_t* vl = static_cast<const uint8_t*>(v) + layer * kb;
@@ -939,14 +952,24 @@ int32_t kriya_cuda_decode_step(kriya_cuda_ctx* c, void* q, const void* k, const 
         if (c->fuse_append && use_tc_decode(c) && !rope->apply_qk_norm) {
             // Layers of one step share nothing but the split-row scratch, which the kernel guards itself: from the
             // second layer on, a launch may start while the previous layer's last CTAs drain.
-            if (int32_t rc = append_decode_impl(c, layer, ql, kl, vl, ol, nullptr, rope, gqa, layer > 0 && c->overlap_layers))
-                return rc;
+            const bool overlap = c->overlap_layers && !(first_of_chain && layer == l0);
+            if (int32_t rc = append_decode_impl(c, layer, ql, kl, vl, ol, nullptr, rope, gqa, overlap)) return rc;
         } else {
             if (int32_t rc = kriya_cuda_rope_kv_append(c, layer, ql, kl, vl, nullptr, nullptr, rows, rope)) return rc;
             if (int32_t rc = kriya_cuda_paged_gqa_decode(c, layer, ql, ol, gqa)) return rc;
         }
     }
     return KRIYA_CUDA_OK;
+}
+
+int32_t kriya_cuda_decode_step(kriya_cuda_ctx* c, void* q, const void* k, const void* v, void* out, uint32_t rows,
+                               const kriya_rope_kv_write_params* rope, const kriya_bsr_gqa_params* gqa) {
+    if (!c) return KRIYA_CUDA_INVALID_INPUT;
+    if (!q || !k || !v || !out) return c->fail(KRIYA_CUDA_INVALID_INPUT, "q, k, v and out must not be null");
+    if (!c->plan_valid) return c->fail(KRIYA_CUDA_INVALID_INPUT, "no plan uploaded");
+    if (rows == 0 || rows != c->n_rows) return c->fail(KRIYA_CUDA_INVALID_INPUT, "rows must equal the plan's row count");
+    cudaSetDevice(c->cfg.device);
+    return decode_layers(c, 0, c->cfg.num_layers, true, q, k, v, out, rows, rope, gqa);
 }
 
 int32_t kriya_cuda_decode_step_host(kriya_cuda_ctx* c, const void* q_host, const void* k_host, const void* v_host,
@@ -973,11 +996,29 @@ int32_t kriya_cuda_decode_step_host(kriya_cuda_ctx* c, const void* q_host, const
     uint8_t* dk = dq + qb;
     uint8_t* dv = dk + kb;
     uint8_t* dout = dv + kb;
-    KRIYA_CUDA_TRY(c, cudaMemcpyAsync(dq, q_host, qb, cudaMemcpyHostToDevice, c->stream));
-    KRIYA_CUDA_TRY(c, cudaMemcpyAsync(dk, k_host, kb, cudaMemcpyHostToDevice, c->stream));
-    KRIYA_CUDA_TRY(c, cudaMemcpyAsync(dv, v_host, kb, cudaMemcpyHostToDevice, c->stream));
-    if (int32_t rc = kriya_cuda_decode_step(c, dq, dk, dv, dout, rows, rope, gqa)) return rc;
-    KRIYA_CUDA_TRY(c, cudaMemcpyAsync(out_host, dout, qb, cudaMemcpyDeviceToHost, c->stream));
+    // Three-way pipeline over groups of layers: inputs of group g+1 travel host->device on one copy stream and the
+    // results of group g-1 travel back on another while group g computes, so the PCIe time hides behind the kernels.
+    const uint32_t group = 4, n_groups = (uint32_t(L) + group - 1) / group;
+    const size_t qbl = qb / L, kbl = kb / L;
+    KRIYA_CUDA_TRY(c, cudaEventRecord(c->ev_step_begin, c->stream));  // the plan upload and earlier work come first
+    KRIYA_CUDA_TRY(c, cudaStreamWaitEvent(c->copy_stream, c->ev_step_begin, 0));
+    KRIYA_CUDA_TRY(c, cudaStreamWaitEvent(c->copy_stream_out, c->ev_step_begin, 0));
+    for (uint32_t g = 0; g < n_groups; ++g) {
+        const uint32_t l0 = g * group, l1 = std::min(uint32_t(L), l0 + group);
+        const size_t nq = size_t(l1 - l0) * qbl, nk = size_t(l1 - l0) * kbl;
+        KRIYA_CUDA_TRY(c, cudaMemcpyAsync(dq + l0 * qbl, static_cast<const uint8_t*>(q_host) + l0 * qbl, nq, cudaMemcpyHostToDevice, c->copy_stream));
+        KRIYA_CUDA_TRY(c, cudaMemcpyAsync(dk + l0 * kbl, static_cast<const uint8_t*>(k_host) + l0 * kbl, nk, cudaMemcpyHostToDevice, c->copy_stream));
+        KRIYA_CUDA_TRY(c, cudaMemcpyAsync(dv + l0 * kbl, static_cast<const uint8_t*>(v_host) + l0 * kbl, nk, cudaMemcpyHostToDevice, c->copy_stream));
+        KRIYA_CUDA_TRY(c, cudaEventRecord(c->ev_in[g], c->copy_stream));
+        KRIYA_CUDA_TRY(c, cudaStreamWaitEvent(c->stream, c->ev_in[g], 0));
+        if (int32_t rc = decode_layers(c, l0, l1, true, dq, dk, dv, dout, rows, rope, gqa)) return rc;
+        KRIYA_CUDA_TRY(c, cudaEventRecord(c->ev_done[g], c->stream));
+        KRIYA_CUDA_TRY(c, cudaStreamWaitEvent(c->copy_stream_out, c->ev_done[g], 0));
+        KRIYA_CUDA_TRY(c, cudaMemcpyAsync(static_cast<uint8_t*>(out_host) + l0 * qbl, dout + l0 * qbl, nq, cudaMemcpyDeviceToHost, c->copy_stream_out));
+    }
+    KRIYA_CUDA_TRY(c, cudaEventRecord(c->ev_step_end, c->copy_stream_out));
+    KRIYA_CUDA_TRY(c, cudaStreamWaitEvent(c->stream, c->ev_step_end, 0));  // later work on the context's stream follows the step
+    KRIYA_CUDA_TRY(c, cudaStreamSynchronize(c->copy_stream_out));
     return kriya_cuda_sync(c, 0);
 }
 
