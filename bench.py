@@ -70,7 +70,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
             return
@@ -519,6 +519,60 @@ def run_kernel_case(args):
         ex.close()
         if world > 1:
             dist.destroy_process_group()
+    elif case == "decode_long":
+        # long-context sharded decode: 256 sequences, contexts U[8192,32768], Qwen2.5-3B shape, ONE layer resident
+        # (36 layers of this workload are 193 GB); with WORLD_SIZE > 1 the sequences are dealt to ranks longest-first
+        import torch.distributed as dist
+
+        from kriya_rt_b200 import sharding
+
+        rank = int(os.environ.get("RANK", "0")); world = int(os.environ.get("WORLD_SIZE", "1"))
+        torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+        if world > 1:
+            dist.init_process_group("nccl", device_id=torch.device("cuda", torch.cuda.current_device()))
+        lengths = np.random.default_rng(2005).integers(8192, 32768 + 1, size=256)
+        mine = sharding.assign_sequences(lengths, world)[rank]
+        ctx = lengths[mine]
+        nblocks = int(((ctx + 16) // 16).sum()) + 16
+        batch = W.make_decode_batch(SHAPE, ctx, nblocks, seed=2005 + rank)
+        ex = CudaExecutor(num_layers=1, num_kv_blocks=nblocks, block_size_tokens=16, num_q_heads=16, num_kv_heads=2,
+                          head_dim=128, device=torch.cuda.current_device(), rope_theta=SHAPE.rope_theta, rope_max_seq_len=32768 + 64,
+                          max_batch_rows=256, max_page_indices=nblocks, max_tiles=65536)
+        for view in ex.layer_cache_views(0):  # values do not matter for timing; keep the fill cheap but finite
+            view.view(-1)[: 1 << 24].copy_(torch.randn(1 << 24, device="cuda", generator=gen).to(torch.bfloat16).view(torch.int16))
+        n = len(mine)
+        q, k, v = rnd(n, 16, 128), rnd(n, 2, 128), rnd(n, 2, 128)
+        out = torch.zeros_like(q)
+        torch.cuda.synchronize()
+        ex.upload_schedule_plan(batch, batch.positions)
+        rp, gp = ex.rope_params(), ex.gqa_params()
+        stream = torch.cuda.ExternalStream(ex.stream_ptr)
+        for _ in range(3):
+            ex.append_decode(0, q, k, v, out, rp, gp)
+        ex.sync()
+        if world > 1:
+            dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(reps):
+            ex.append_decode(0, q, k, v, out, rp, gp)
+        e1.record(stream)
+        ex.sync()
+        t = torch.tensor([e0.elapsed_time(e1) / reps * 1e3, float(batch.kv_bytes_per_layer)], device="cuda", dtype=torch.float64)
+        if world > 1:
+            tmax = t.clone(); dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+            tsum = t.clone(); dist.all_reduce(tsum, op=dist.ReduceOp.SUM)
+            us, total_bytes = float(tmax[0]), float(tsum[1])
+        else:
+            us, total_bytes = float(t[0]), float(t[1])
+        if rank == 0:
+            print(json.dumps({"case": case, "n_gpus": world, "sequences": 256, "us_per_layer": us,
+                              "kv_bytes_all_gpus": total_bytes, "kv_gbs_aggregate": total_bytes / (us * 1e-6) / 1e9,
+                              "kv_gbs_per_gpu": total_bytes / world / (us * 1e-6) / 1e9,
+                              "tokens_per_s_one_layer": 256 / (us * 1e-6), "tokens_per_s_36_layers": 256 / (us * 36e-6)}))
+        ex.close()
+        if world > 1:
+            dist.destroy_process_group()
     elif case == "prefill_batch":
         # Qwen2.5-1.5B shape, eight 2048-token prompts, the four 512-token chunks of every prompt, one launch per chunk index
         sh = W.QWEN25_1P5B
@@ -610,7 +664,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--serial-layers", action="store_true",
                     help="keep the layers' launches of a step strictly serialised (default: they may overlap at their edges)")
-    ap.add_argument("--kernel-case", default=None, choices=["decode", "decode_fused", "prefill", "prefill_batch", "append", "copy", "kvsplit"],
+    ap.add_argument("--kernel-case", default=None, choices=["decode", "decode_fused", "decode_long", "prefill", "prefill_batch", "append", "copy", "kvsplit"],
                     help="run a few launches of one kernel on a small case (for ncu), --steps = launches")
     args = ap.parse_args()
     if args.kernel_case:
