@@ -19,6 +19,7 @@
 namespace {
 
 thread_local std::string g_create_error;
+constexpr uint32_t kScratchSets = 4;  // independent split-row scratch sets (see launch_decode)
 
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
@@ -290,9 +291,11 @@ int32_t launch_decode(kriya_cuda_ctx* c, uint32_t layer, const void* q, void* ou
     a.last_len = c->plan_dev<int32_t>(c->off_last_len);
     a.work = c->plan_dev<KriyaDecodeWork>(range_list ? c->off_range : c->off_work);
     a.out = out;
-    a.part_o = c->part_o;
-    a.part_ml = c->part_ml;
-    a.counters = c->part_counter;
+    // a free-running overlapped launch (see decode_layers) gets the scratch set of its layer; everything else set 0
+    const uint32_t set = fused.overlap_previous == 2u ? layer % kScratchSets : 0u;
+    a.part_o = c->part_o + set * c->set_o_floats;
+    a.part_ml = c->part_ml + set * c->set_ml_floats;
+    a.counters = c->part_counter + set * c->set_counters;
     a.state_m = sm;
     a.state_l = sl;
     a.state_o = so;
@@ -468,12 +471,16 @@ int32_t kriya_cuda_ctx_create(const kriya_cuda_config* cfg_in, kriya_cuda_ctx** 
         CREATE_TRY(cudaEventCreateWithFlags(&c->h_plan_free[i], cudaEventDisableTiming));
     }
 
+    // split-row scratch: kScratchSets independent sets, so that the launches of consecutive layers, which may overlap
+    // at their edges, never share one
     const size_t rows_hq = size_t(std::max(c->cap_work, c->cap_seg)) * cfg.num_q_heads;
-    CREATE_TRY(cudaMalloc(&c->part_o, rows_hq * cfg.head_dim * sizeof(float)));
-    CREATE_TRY(cudaMalloc(&c->part_ml, rows_hq * 2 * sizeof(float)));
-    const size_t n_counters = size_t(c->cap_rows) * cfg.num_kv_heads;
-    CREATE_TRY(cudaMalloc(&c->part_counter, n_counters * sizeof(uint32_t)));
-    CREATE_TRY(cudaMemsetAsync(c->part_counter, 0, n_counters * sizeof(uint32_t), c->stream));
+    c->set_o_floats = rows_hq * cfg.head_dim;
+    c->set_ml_floats = rows_hq * 2;
+    c->set_counters = size_t(c->cap_rows) * cfg.num_kv_heads;
+    CREATE_TRY(cudaMalloc(&c->part_o, kScratchSets * c->set_o_floats * sizeof(float)));
+    CREATE_TRY(cudaMalloc(&c->part_ml, kScratchSets * c->set_ml_floats * sizeof(float)));
+    CREATE_TRY(cudaMalloc(&c->part_counter, kScratchSets * c->set_counters * sizeof(uint32_t)));
+    CREATE_TRY(cudaMemsetAsync(c->part_counter, 0, kScratchSets * c->set_counters * sizeof(uint32_t), c->stream));
     CREATE_TRY(cudaMalloc(&c->d_status, 256));
     CREATE_TRY(cudaMemsetAsync(c->d_status, 0, 256, c->stream));
     CREATE_TRY(cudaMallocHost(&c->h_status, 256));
@@ -615,6 +622,17 @@ int32_t kriya_cuda_plan_upload(kriya_cuda_ctx* c, const int32_t* indptr, size_t 
                                              reinterpret_cast<uint32_t*>(h + c->off_tcptr));
     if (n_seg == UINT32_MAX) return invalid("plan needs more decode segments than the context holds");
     c->n_seg = n_seg;
+    {
+        const uint32_t* sp = reinterpret_cast<const uint32_t*>(h + c->off_tcptr);
+        const KriyaTcSeg* sg = reinterpret_cast<const KriyaTcSeg*>(h + c->off_tcseg);
+        bool all = true;
+        for (int cta = 0; cta < c->sm_count && all; ++cta) {
+            bool busy = false;
+            for (uint32_t i = sp[cta]; i < sp[cta + 1]; ++i) busy = busy || sg[i].blk_hi > sg[i].blk_lo;
+            all = busy;
+        }
+        c->tc_all_ctas_busy = all;
+    }
     const size_t used = c->off_indices + indices_len * 4;
     KRIYA_CUDA_TRY(c, cudaMemcpyAsync(c->d_plan, h, used, cudaMemcpyHostToDevice, c->stream));
     KRIYA_CUDA_TRY(c, cudaEventRecord(c->h_plan_free[cur], c->stream));
@@ -929,7 +947,11 @@ static int32_t append_decode_impl(kriya_cuda_ctx* c, uint32_t layer, const void*
     f.max_seq_len = rope->max_seq_len;
     f.has_table = rope->has_table;
     f.rope_theta = rope->rope_theta;
-    f.overlap_previous = (overlap_previous && !c->timing) ? 1u : 0u;
+    // 1: may start while the previous launch drains, waits for it before touching the scratch;
+    // 2: the same without the wait, on a scratch set of its own.  Only sound when every CTA of every launch holds
+    //    work: a launch's CTAs each need a whole SM, so launch L+1 has started all of them only once launch L has
+    //    vacated every SM, and launch L+2 cannot begin before that; a set is reused four launches later.
+    f.overlap_previous = (overlap_previous && !c->timing) ? (c->tc_all_ctas_busy ? 2u : 1u) : 0u;
     return launch_decode(c, layer, q, out, nullptr, nullptr, nullptr, false, c->n_work, gqa, f);
 }
 

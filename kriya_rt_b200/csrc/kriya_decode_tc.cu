@@ -518,7 +518,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
             const KriyaTcSeg seg = segs_s[0];
             asm volatile("bar.sync 2, 160;" ::: "memory");  // the softmax threads have published the partial state
             if (*merge_job_ok) {
-                pdl_wait_previous_grid();
+                if (pp.f.overlap_previous != 2u) pdl_wait_previous_grid();
                 __threadfence();
                 uint32_t ticket = 0;
                 if (lane == 0) ticket = atomicAdd(&a.counters[seg.req * Hkv + seg.kv_head], 1u);
@@ -527,7 +527,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
                     __threadfence();
                     merge_run_parts<G, T>(a, seg, merge_stage, lane, 32u, a.state_o != nullptr,
                                           size_t(seg.req) * Hq + seg.kv_head * G);
-                    if (lane == 0) a.counters[seg.req * Hkv + seg.kv_head] = 0u;
+                    if (lane == 0) atomicExch(&a.counters[seg.req * Hkv + seg.kv_head], 0u);
                 }
             }
         }
@@ -700,8 +700,8 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
                     }
                 }
             } else {
-                // the scratch and the tickets are shared with the previous launch: it must have drained first
-                pdl_wait_previous_grid();
+                // a scratch set shared with the previous launch must not be touched before that launch has drained
+                if (pp.f.overlap_previous != 2u) pdl_wait_previous_grid();
                 const size_t prow = size_t(seg.slot) * G;
 #pragma unroll
                 for (int h = 0; h < G; ++h) {
@@ -726,7 +726,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
                     if (last) {
                         __threadfence();
                         merge_run_parts<G, T>(a, seg, red, tid, 128u, state_mode, row0);
-                        if (tid == 0) a.counters[req * Hkv + seg.kv_head] = 0u;
+                        if (tid == 0) atomicExch(&a.counters[req * Hkv + seg.kv_head], 0u);
                     }
                 }
             }

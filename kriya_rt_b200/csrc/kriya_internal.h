@@ -97,6 +97,8 @@ struct kriya_cuda_ctx {
     float* part_o = nullptr;        // [cap_work][Hq][D]
     float* part_ml = nullptr;       // [cap_work][Hq][2]
     uint32_t* part_counter = nullptr;  // [cap_rows * head_groups]
+    size_t set_o_floats = 0, set_ml_floats = 0, set_counters = 0;  // size of one scratch set
+    bool tc_all_ctas_busy = false;  // current plan gives every CTA of the tensor-core decode launch some tiles
     uint32_t* d_status = nullptr;   // device status word
     uint32_t* h_status = nullptr;   // pinned mirror
 
@@ -206,6 +208,7 @@ struct KriyaFusedAppend {
     // Host-side launch option: let this launch begin while the previous kernel of the stream drains (programmatic
     // dependent launch).  Only valid when every input of this launch is already complete, i.e. between the layers
     // of one whole-step call; the kernel itself waits for the previous grid before it touches the shared scratch.
+    // 2 = as 1, but on a scratch set of its own and without that wait (see kriya_ctx.cu for when this is sound).
     uint32_t overlap_previous = 0;
 };
 bool kriya_decode_tc_supported(uint32_t head_dim, uint32_t group, uint32_t block_size);
