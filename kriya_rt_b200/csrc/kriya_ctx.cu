@@ -649,6 +649,11 @@ int32_t kriya_cuda_plan_upload(kriya_cuda_ctx* c, const int32_t* indptr, size_t 
     for (size_t r = 0; r < rows; ++r)
         tokens += uint64_t(indptr[r + 1] - indptr[r] - 1) * c->cfg.block_size_tokens + uint32_t(last_len[r]);
     c->total_row_tokens = tokens;
+    c->positions_are_context = n_positions == rows;
+    for (size_t r = 0; r < rows && c->positions_are_context; ++r) {
+        const uint64_t row_tokens = uint64_t(indptr[r + 1] - indptr[r] - 1) * c->cfg.block_size_tokens + uint32_t(last_len[r]);
+        c->positions_are_context = uint64_t(positions[r]) + 1u == row_tokens;
+    }
     c->plan_valid = true;
     return KRIYA_CUDA_OK;
 }
@@ -947,6 +952,7 @@ static int32_t append_decode_impl(kriya_cuda_ctx* c, uint32_t layer, const void*
     f.max_seq_len = rope->max_seq_len;
     f.has_table = rope->has_table;
     f.rope_theta = rope->rope_theta;
+    f.positions_are_context = c->positions_are_context ? 1u : 0u;
     // 1: may start while the previous launch drains, waits for it before touching the scratch;
     // 2: the same without the wait, on a scratch set of its own.  Only sound when every CTA of every launch holds
     //    work: a launch's CTAs each need a whole SM, so launch L+1 has started all of them only once launch L has

@@ -370,7 +370,9 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
                     *reinterpret_cast<uint4*>(qb + (c >> 3) * 2048u + h * 128u + (((c & 7u) ^ (h & 7u)) << 4)) = val;
                 }
             } else {
-                position = pp.f.positions[seg.req];
+                // the usual decode step appends at position = tokens already in the row; then the segment record
+                // already holds it and the dependent global load is skipped
+                position = pp.f.positions_are_context ? seg.row_tokens - 1u : pp.f.positions[seg.req];
                 for (uint32_t i = lane; i < uint32_t(G) * 8u; i += 32u) {
                     const uint32_t h = i >> 3, c = i & 7u;
                     uint4 lo = *reinterpret_cast<const uint4*>(qg + h * kTcD + c * 8);

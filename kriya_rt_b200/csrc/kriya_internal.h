@@ -98,6 +98,7 @@ struct kriya_cuda_ctx {
     float* part_ml = nullptr;       // [cap_work][Hq][2]
     uint32_t* part_counter = nullptr;  // [cap_rows * head_groups]
     size_t set_o_floats = 0, set_ml_floats = 0, set_counters = 0;  // size of one scratch set
+    bool positions_are_context = false;  // current plan: seq_positions[r] == tokens in row r - 1 for every row
     bool tc_all_ctas_busy = false;  // current plan gives every CTA of the tensor-core decode launch some tiles
     uint32_t* d_status = nullptr;   // device status word
     uint32_t* h_status = nullptr;   // pinned mirror
@@ -205,6 +206,7 @@ struct KriyaFusedAppend {
     uint32_t max_seq_len = 0;
     uint32_t has_table = 0;
     float rope_theta = 0.0f;
+    uint32_t positions_are_context = 0;  // every row's position equals its token count - 1 (checked on the host)
     // Host-side launch option: let this launch begin while the previous kernel of the stream drains (programmatic
     // dependent launch).  Only valid when every input of this launch is already complete, i.e. between the layers
     // of one whole-step call; the kernel itself waits for the previous grid before it touches the shared scratch.
