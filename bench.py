@@ -493,11 +493,13 @@ def run_kernel_case(args):
         stream = torch.cuda.ExternalStream(ex.stream_ptr)
         torch.cuda.synchronize()
 
+        ex.plan_set_ranges(b, e)  # once per plan; every layer re-uses the split
+
         def one(gather=True):
             if world > 1 and gather:
-                sharding.kv_split_decode(ex, 0, q, b, e, out, gp, scratch=(local, gathered))
+                sharding.kv_split_decode(ex, 0, q, None, None, out, gp, scratch=(local, gathered))
             else:
-                ex.paged_gqa_decode_partial(0, q, b, e, local[:rows], local[rows:2 * rows], local[2 * rows:], gp)
+                ex.paged_gqa_decode_partial(0, q, None, None, local[:rows], local[rows:2 * rows], local[2 * rows:], gp)
                 ex.merge_packed_states(local, 1, rows, out)
 
         res = {}

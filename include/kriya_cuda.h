@@ -165,7 +165,8 @@ int32_t kriya_cuda_paged_gqa_decode(kriya_cuda_ctx* ctx, uint32_t layer, const v
 /* Decode restricted to a block range of every row, returning the un-normalised softmax state instead
  * of the output: m [rows][Hq] (running maximum, natural-log units, -inf for an empty range),
  * l [rows][Hq] and o [rows][Hq][D], all fp32.  Row r covers logical blocks
- * [blk_begin_host[r], blk_end_host[r]) (NULL: the whole row).  This is the per-GPU half of splitting
+ * [blk_begin_host[r], blk_end_host[r]) (both NULL: the ranges of the last
+ * kriya_cuda_plan_set_ranges on this plan, else the whole row).  This is the per-GPU half of splitting
  * one long sequence along the KV axis; kriya_cuda_merge_states() finishes it.  The reference has no
  * multi-GPU path; the state is the (max, sum, output) triple of its split-K design
  * (paged_gqa_and_deltanet.metal:328-342). */
@@ -173,6 +174,10 @@ int32_t kriya_cuda_paged_gqa_decode_partial(kriya_cuda_ctx* ctx, uint32_t layer,
                                             const uint32_t* blk_begin_host, const uint32_t* blk_end_host,
                                             float* out_m_dev, float* out_l_dev, float* out_o_dev,
                                             const kriya_bsr_gqa_params* params);
+
+/* Sets the block ranges once for the current plan (they stay until the next plan upload): the partial-state decode of
+ * every following layer can then pass NULL ranges and re-uses the work split instead of rebuilding it per call. */
+int32_t kriya_cuda_plan_set_ranges(kriya_cuda_ctx* ctx, const uint32_t* blk_begin_host, const uint32_t* blk_end_host);
 
 /* Merge `parts` partial states laid out [parts][rows*Hq] (m, l) and [parts][rows*Hq][D] (o), e.g.
  * gathered from all ranks, into the normalised 16-bit output [rows*Hq][D]: the split-K reduce

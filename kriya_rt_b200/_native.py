@@ -113,6 +113,7 @@ CUDA_SYMBOLS = {
     "kriya_cuda_paged_gqa_decode": (C.c_int32, [_VP, C.c_uint32, _VP, _VP, C.POINTER(BsrGqaParams)]),
     "kriya_cuda_paged_gqa_decode_partial": (C.c_int32, [_VP, C.c_uint32, _VP, _VP, _VP, _VP, _VP, _VP,
                                                         C.POINTER(BsrGqaParams)]),
+    "kriya_cuda_plan_set_ranges": (C.c_int32, [_VP, _VP, _VP]),
     "kriya_cuda_merge_states": (C.c_int32, [_VP, _VP, _VP, _VP, C.c_uint32, C.c_uint32, _VP]),
     "kriya_cuda_merge_packed_states": (C.c_int32, [_VP, _VP, C.c_uint32, C.c_uint32, _VP]),
     "kriya_cuda_paged_gqa_prefill": (C.c_int32, [_VP, C.c_uint32, _VP, _VP, C.c_uint32, C.c_uint32,

@@ -560,6 +560,7 @@ int32_t kriya_cuda_plan_upload(kriya_cuda_ctx* c, const int32_t* indptr, size_t 
                                size_t n_positions) {
     if (!c) return KRIYA_CUDA_INVALID_INPUT;
     c->plan_valid = false;
+    c->ranges_valid = false;
     auto invalid = [&](const std::string& m) { return c->fail(KRIYA_CUDA_INVALID_INPUT, m); };
     // validate_batch_inputs, enc:2159-2218
     if (!indptr || indptr_len < 2) return invalid("page_indptr must hold at least one row");
@@ -712,20 +713,11 @@ int32_t kriya_cuda_paged_gqa_decode(kriya_cuda_ctx* c, uint32_t layer, const voi
     return launch_decode(c, layer, q, out, nullptr, nullptr, nullptr, false, c->n_work, p);
 }
 
-int32_t kriya_cuda_paged_gqa_decode_partial(kriya_cuda_ctx* c, uint32_t layer, const void* q, const uint32_t* blk_begin,
-                                            const uint32_t* blk_end, float* out_m, float* out_l, float* out_o,
-                                            const kriya_bsr_gqa_params* p) {
+int32_t kriya_cuda_plan_set_ranges(kriya_cuda_ctx* c, const uint32_t* blk_begin, const uint32_t* blk_end) {
     if (!c) return KRIYA_CUDA_INVALID_INPUT;
-    if (int32_t rc = check_layer(c, layer)) return rc;
-    if (int32_t rc = check_gqa(c, p)) return rc;
     if (!c->plan_valid) return c->fail(KRIYA_CUDA_INVALID_INPUT, "no plan uploaded");
-    if (!q || !out_m || !out_l || !out_o) return c->fail(KRIYA_CUDA_INVALID_INPUT, "q and state outputs must not be null");
-    if (!use_tc_decode(c) && !kriya_decode_supported(c->cfg.head_dim, c->cfg.num_q_heads / c->cfg.num_kv_heads,
-                                                     c->cfg.num_kv_heads, c->cfg.block_size_tokens))
-        return c->fail(KRIYA_CUDA_UNSUPPORTED,
-                       "decode kernels cover head_dim 64/128, group size 1..8, 16-token blocks (head_dim 64: up to 8 KV heads)");
     cudaSetDevice(c->cfg.device);
-    // work list for the requested ranges, staged behind the plan's own list
+    // work lists for the requested ranges, staged behind the plan's own lists
     KRIYA_CUDA_TRY(c, cudaEventSynchronize(c->h_pairs_free));
     const int32_t* indptr = reinterpret_cast<const int32_t*>(c->h_plan_last + c->off_indptr);
     auto* work = reinterpret_cast<KriyaDecodeWork*>(c->h_plan_last + c->off_range);
@@ -743,6 +735,31 @@ int32_t kriya_cuda_paged_gqa_decode_partial(kriya_cuda_ctx* c, uint32_t layer, c
     KRIYA_CUDA_TRY(c, cudaMemcpyAsync(c->d_plan + c->off_tcptr2, sptr, c->off_tcseg2 - c->off_tcptr2 + size_t(n_seg) * sizeof(KriyaTcSeg),
                                       cudaMemcpyHostToDevice, c->stream));
     KRIYA_CUDA_TRY(c, cudaEventRecord(c->h_pairs_free, c->stream));
+    c->n_work_ranges = n_work;
+    c->ranges_valid = true;
+    return KRIYA_CUDA_OK;
+}
+
+int32_t kriya_cuda_paged_gqa_decode_partial(kriya_cuda_ctx* c, uint32_t layer, const void* q, const uint32_t* blk_begin,
+                                            const uint32_t* blk_end, float* out_m, float* out_l, float* out_o,
+                                            const kriya_bsr_gqa_params* p) {
+    if (!c) return KRIYA_CUDA_INVALID_INPUT;
+    if (int32_t rc = check_layer(c, layer)) return rc;
+    if (int32_t rc = check_gqa(c, p)) return rc;
+    if (!c->plan_valid) return c->fail(KRIYA_CUDA_INVALID_INPUT, "no plan uploaded");
+    if (!q || !out_m || !out_l || !out_o) return c->fail(KRIYA_CUDA_INVALID_INPUT, "q and state outputs must not be null");
+    if (!use_tc_decode(c) && !kriya_decode_supported(c->cfg.head_dim, c->cfg.num_q_heads / c->cfg.num_kv_heads,
+                                                     c->cfg.num_kv_heads, c->cfg.block_size_tokens))
+        return c->fail(KRIYA_CUDA_UNSUPPORTED,
+                       "decode kernels cover head_dim 64/128, group size 1..8, 16-token blocks (head_dim 64: up to 8 KV heads)");
+    cudaSetDevice(c->cfg.device);
+    if (blk_begin != nullptr || blk_end != nullptr) {
+        if (int32_t rc = kriya_cuda_plan_set_ranges(c, blk_begin, blk_end)) return rc;
+    } else if (!c->ranges_valid) {
+        // whole rows: the lists built by the plan upload serve
+        return launch_decode(c, layer, q, nullptr, out_m, out_l, out_o, false, c->n_work, p);
+    }
+    const uint32_t n_work = c->n_work_ranges;
     return launch_decode(c, layer, q, nullptr, out_m, out_l, out_o, true, n_work, p);
 }
 

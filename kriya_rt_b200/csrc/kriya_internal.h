@@ -98,6 +98,8 @@ struct kriya_cuda_ctx {
     float* part_ml = nullptr;       // [cap_work][Hq][2]
     uint32_t* part_counter = nullptr;  // [cap_rows * head_groups]
     size_t set_o_floats = 0, set_ml_floats = 0, set_counters = 0;  // size of one scratch set
+    bool ranges_valid = false;      // block ranges set for the current plan (kriya_cuda_plan_set_ranges)
+    uint32_t n_work_ranges = 0;
     bool positions_are_context = false;  // current plan: seq_positions[r] == tokens in row r - 1 for every row
     bool tc_all_ctas_busy = false;  // current plan gives every CTA of the tensor-core decode launch some tiles
     uint32_t* d_status = nullptr;   // device status word

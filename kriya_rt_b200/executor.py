@@ -164,6 +164,12 @@ class CudaExecutor:
         self._check(self._lib.kriya_cuda_paged_gqa_decode_partial(
             self._h, layer, _ptr(q), _ptr(b), _ptr(e), _ptr(out_m), _ptr(out_l), _ptr(out_o), C.byref(params)))
 
+    def plan_set_ranges(self, blk_begin, blk_end) -> None:
+        """Block ranges for the partial-state decode of every layer of this plan (pass None ranges afterwards)."""
+        b = np.ascontiguousarray(blk_begin, np.uint32)
+        e = np.ascontiguousarray(blk_end, np.uint32)
+        self._check(self._lib.kriya_cuda_plan_set_ranges(self._h, b.ctypes.data, e.ctypes.data))
+
     def merge_states(self, m, l, o, parts: int, rows_times_heads: int, out) -> None:
         self._check(self._lib.kriya_cuda_merge_states(self._h, _ptr(m), _ptr(l), _ptr(o), parts, rows_times_heads,
                                                       _ptr(out)))

@@ -63,16 +63,20 @@ def gather_states(m, l, o, group=None):
     return m_all, l_all, o_all
 
 
-def kv_split_decode(ex, layer: int, q, blk_begin, blk_end, out, gqa, group=None, scratch=None):
+def kv_split_decode(ex, layer: int, q, blk_begin, blk_end, out, gqa, group=None, scratch=None, rows_hint=None):
     """One KV-axis-split decode on this rank: partial state over [blk_begin, blk_end) of every row of the current
     plan, ONE all-gather of the packed (m, l, o) states, merge into `out` ([rows, Hq, D] in the storage dtype).
     Everything is queued on the executor's stream (the collective is ordered behind it by torch), so the host does
     not wait in between.  `scratch` may carry preallocated (local [R*(D+2)], gathered [world, R*(D+2)]) fp32 device
-    tensors to keep the step path allocation-free."""
+    tensors to keep the step path allocation-free.  With blk_begin = blk_end = None the ranges set by
+    `ex.plan_set_ranges` are used and `rows_hint` gives the number of plan rows (default 1)."""
     import torch
     import torch.distributed as dist
 
-    R = ex.num_q_heads * int(len(blk_begin))
+    if blk_begin is None:  # ranges were set once for the plan (CudaExecutor.plan_set_ranges)
+        R = ex.num_q_heads * int(rows_hint if rows_hint is not None else 1)
+    else:
+        R = ex.num_q_heads * int(len(blk_begin))
     D = ex.head_dim
     world = dist.get_world_size(group)
     if scratch is None:
