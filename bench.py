@@ -584,9 +584,9 @@ def run_kernel_case(args):
         if world > 1:
             dist.destroy_process_group()
     elif case == "prefill_batch":
-        # Qwen2.5-1.5B shape, eight 2048-token prompts, the four 512-token chunks of every prompt, one launch per chunk index
+        # Qwen2.5-1.5B shape, --case-seqs (default eight) 2048-token prompts, the four 512-token chunks of every prompt, one launch per chunk index
         sh = W.QWEN25_1P5B
-        n_seq, total, chunk = 8, 2048, 512
+        n_seq, total, chunk = args.case_seqs, 2048, 512
         nb = n_seq * total // 16
         ex = CudaExecutor(num_layers=1, num_kv_blocks=nb, block_size_tokens=16, num_q_heads=12, num_kv_heads=2,
                           head_dim=128, rope_theta=sh.rope_theta, max_query_tokens=n_seq * chunk)
@@ -674,6 +674,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--serial-layers", action="store_true",
                     help="keep the layers' launches of a step strictly serialised (default: they may overlap at their edges)")
+    ap.add_argument("--case-seqs", type=int, default=8, help="prompts in the prefill_batch kernel case")
     ap.add_argument("--kernel-case", default=None, choices=["decode", "decode_fused", "decode_long", "prefill", "prefill_batch", "append", "copy", "kvsplit"],
                     help="run a few launches of one kernel on a small case (for ncu), --steps = launches")
     args = ap.parse_args()

@@ -60,17 +60,25 @@ def build_cuda(force: bool = False) -> Path:
     out = LIB / "libkriya_cuda.so"
     objs = [OBJ / (Path(s).stem + ".o") for s in sources]
 
+    # objects built with other flags are stale even when they are newer than their sources
+    extra = os.environ.get("KRIYA_NVCC_EXTRA", "").split()
+    flags_file = OBJ / "nvcc_flags.txt"
+    flags_now = " ".join([*NVCC_FLAGS, *extra])
+    if not flags_file.exists() or flags_file.read_text() != flags_now:
+        force = True
+
     def compile_one(pair):
         src, obj = pair
         if not force and _newer(obj, [CSRC / src] + headers):
             return
-        _run([_nvcc(), *NVCC_FLAGS, *os.environ.get("KRIYA_NVCC_EXTRA", "").split(), "-I", str(INCLUDE), "-I", str(CSRC), "-c", str(CSRC / src), "-o", str(obj)],
+        _run([_nvcc(), *NVCC_FLAGS, *extra, "-I", str(INCLUDE), "-I", str(CSRC), "-c", str(CSRC / src), "-o", str(obj)],
              log=OBJ / (Path(src).stem + ".ptxas.log"))
 
     with ThreadPoolExecutor(max_workers=min(8, len(sources))) as pool:
         list(pool.map(compile_one, zip(sources, objs)))
     if force or not _newer(out, objs):
         _run([_nvcc(), "-shared", "-o", str(out), *map(str, objs)])  # cudart is linked statically (nvcc default)
+    flags_file.write_text(flags_now)
     return out
 
 

@@ -804,9 +804,10 @@ int32_t kriya_cuda_paged_gqa_prefill_batch(kriya_cuda_ctx* c, uint32_t layer, co
     const int32_t* indptr = reinterpret_cast<const int32_t*>(c->h_plan_last + c->off_indptr);
     auto* tiles = reinterpret_cast<KriyaPrefillTile*>(c->h_pairs);
     const uint32_t cap_tiles = uint32_t(size_t(c->cap_pairs) * 3 * sizeof(uint32_t) / sizeof(KriyaPrefillTile));
-    uint32_t n = 0;
+    uint32_t n = 0, q_rows = 0;
     for (uint32_t r = 0; r < n_seqs; ++r) {
         if (count[r] == 0) return c->fail(KRIYA_CUDA_INVALID_INPUT, "input_tokens must not be empty");
+        q_rows = std::max(q_rows, q_start[r] + count[r]);
         const uint64_t end = uint64_t(prefix[r]) + count[r];
         const uint64_t row_cap = uint64_t(indptr[r + 1] - indptr[r]) * c->cfg.block_size_tokens;
         if (end > row_cap)
@@ -836,6 +837,7 @@ int32_t kriya_cuda_paged_gqa_prefill_batch(kriya_cuda_ctx* c, uint32_t layer, co
     a.out = out;
     a.status = c->d_status;
     a.n_tiles = n;
+    a.q_rows = q_rows;
     a.num_blocks = c->cfg.num_kv_blocks;
     a.num_q_heads = c->cfg.num_q_heads;
     a.num_kv_heads = c->cfg.num_kv_heads;

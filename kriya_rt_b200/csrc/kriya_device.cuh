@@ -23,6 +23,13 @@ struct Bf16 {
     __device__ __forceinline__ static float2 load2(uint32_t w) {
         return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xFFFF0000u));
     }
+    // two finite values rounded to nearest even and packed (low half = lo): one instruction; equal to store() on
+    // every finite input, used for probabilities
+    __device__ __forceinline__ static uint32_t pack2(float lo, float hi) {
+        uint32_t w;
+        asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(w) : "f"(hi), "f"(lo));
+        return w;
+    }
 };
 
 struct Fp16 {
@@ -31,6 +38,11 @@ struct Fp16 {
     __device__ __forceinline__ static uint16_t store(float v) { return __half_as_ushort(__float2half_rn(v)); }
     __device__ __forceinline__ static float2 load2(uint32_t w) {
         return __half22float2(*reinterpret_cast<const __half2*>(&w));
+    }
+    __device__ __forceinline__ static uint32_t pack2(float lo, float hi) {
+        uint32_t w;
+        asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(w) : "f"(hi), "f"(lo));
+        return w;
     }
 };
 
@@ -92,6 +104,12 @@ __device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src_gmem, u
                      smem_u32(dst_smem)),
                  "l"(src_gmem), "r"(bytes), "r"(smem_u32(bar))
                  : "memory");
+}
+
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
 }
 
 __device__ __forceinline__ float fast_exp2(float x) {

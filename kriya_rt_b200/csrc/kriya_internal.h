@@ -253,6 +253,7 @@ struct KriyaPrefillArgs {
     void* out;            // [T][Hq][D]
     uint32_t* status;
     uint32_t n_tiles;
+    uint32_t q_rows;      // rows of q / out that the launch may touch (extent of the query tensor map)
     uint32_t num_blocks;
     uint32_t num_q_heads;
     uint32_t num_kv_heads;

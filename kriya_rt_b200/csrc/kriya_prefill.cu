@@ -2,25 +2,30 @@
 // bsr_paged_gqa_prefill_stage1 / _bq8 / bsr_paged_gqa_tiled_mma_prefill,
 // kernels/metal/paged_gqa_and_deltanet.metal:508-847,851-1192,1206-1468).
 //
-// One CTA owns a tile of 128 query tokens of one query head and walks the sequence's KV pages 128 tokens
-// (8 pages) at a time:
-//   - a producer thread gathers the tile's K and V pages through the block table with TMA tensor loads
-//     (2-D map over the pool [rows = block*16 + token][cols = kv_head*D + d], box 64 x 16, 128-byte swizzle)
-//     into a two-stage shared-memory ring, completion on mbarriers;
-//   - one thread issues tcgen05.mma: S = Q.K^T (128 x 128 x D) into one of two TMEM score buffers, and
-//     O += P.V (128 x D x 128) into a TMEM accumulator; V is consumed straight from its [token][d] layout as
-//     an MN-major operand, so no transpose is ever materialised;
-//   - four softmax warps (one thread per query row = one TMEM lane) read S with tcgen05.ld, apply scale and
-//     the causal mask (key position <= prefix + query index), keep the running max / sum in registers,
-//     write P in the storage dtype into a swizzled shared-memory tile and rescale O in TMEM only when the
-//     running max moved by more than 2^8 (the exponent reference is otherwise kept, which is exact in fp32);
-//   - S(j+1) is issued before P.V(j), so the tensor pipe works on the next scores while the softmax of the
-//     current tile runs.
-// Every mbarrier wait is bounded; on expiry the kernel records a status word, skips the remaining work,
-// frees its TMEM and returns.
+// One CTA owns a tile of 128 query tokens of one sequence for TWO query heads of the same KV head (heads A and B;
+// an odd group size leaves the last CTA of a group with one head).  The two heads share every K/V tile the CTA
+// loads and are processed by two independent softmax warpgroups, so that while one head's softmax runs the
+// tensor pipe works on the other head:
+//   - warp 8 (producer) loads the two query tiles with TMA (a 2-D map over q encoded per launch) and gathers the KV
+//     pages 128 tokens (8 pages) at a time through the block table with TMA tensor loads (2-D map over the pool
+//     [rows = block*16 + token][cols = kv_head*D + d], box 64 x 16, 128-byte swizzle, no multicast) into
+//     shared-memory rings (K two deep, V three deep), completion on mbarriers;
+//   - warp 9 issues tcgen05.mma in the order P_A.V(j), S_A(j+1), P_B.V(j), S_B(j+1): S_x = Q_x.K^T (128 x 128 x D) into head x's TMEM score tile and
+//     O_x += P_x.V (128 x D x 128) into its TMEM accumulator.  P_x is read from TMEM (it is written in place over
+//     the first half of S_x), V straight from its [token][d] layout as an MN-major operand: nothing is transposed
+//     and P never touches shared memory;
+//   - warps 0-3 (head A) and 4-7 (head B): one thread per query row = one TMEM lane.  A thread reads its 128 scores
+//     once into registers, applies scale and the causal mask (key position <= prefix + query index), keeps the
+//     running max / sum, writes P in the storage dtype back to TMEM and rescales O only when the running max moved
+//     by more than 2^8 (the exponent reference is otherwise kept, which is exact in fp32).  The softmax warpgroups
+//     take registers from the third warpgroup (setmaxnreg) so that the score row does not spill.
+// Every mbarrier wait is bounded; on expiry the kernel records a status word, skips the remaining work, frees its
+// TMEM and returns.
 //
 // Roofline: 4 * Hq * D * sum_q (prefix + q + 1) FLOP per chunk against the dense bf16 tensor peak.
 #include <algorithm>
+#include <cstdio>
+#include <cstdlib>
 
 #include "kriya_tc.cuh"
 
@@ -30,58 +35,124 @@ constexpr int kQTile = 128;   // query rows per CTA (= TMEM lanes)
 constexpr int kKvTile = 128;  // keys per iteration (8 pages)
 constexpr int kPagePf = 16;
 constexpr int kPagesPerTile = kKvTile / kPagePf;
-constexpr int kPrefillThreads = 192;  // warps 0-3 softmax, warp 4 producer, warp 5 MMA issuer
+constexpr int kKStages = 2;  // K tile ring: a K tile is free again once both heads' S MMAs of its KV tile are done
+constexpr int kVStages = 3;  // V tile ring: freed one softmax later, so it is one deeper
+// Three warpgroups: warps 0-3 softmax A, 4-7 softmax B, 8 producer, 9 MMA issuer, 10-11 idle.  The kernel starts with
+// 168 registers per thread; the third warpgroup hands most of its registers back and the softmax warpgroups take
+// them (128 x 72 + 256 x 216 = 384 x 168), so a thread can hold a whole score row without spilling.
+constexpr int kPrefillThreads = 384;
+constexpr int kRegsWorkers = 72;
+constexpr int kRegsSoftmax = 216;
+template <int N>
+__device__ __forceinline__ void setmaxnreg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
+template <int N>
+__device__ __forceinline__ void setmaxnreg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
 constexpr float kLog2ePf = 1.4426950408889634f;
 constexpr float kRescaleThreshold = 8.0f;
+
+// Optional timeline of CTA 0 (compile with -DKRIYA_PF_TRACE): SM clock stamps per KV tile for the MMA warp and the
+// two softmax groups, dumped to stderr by the launcher on the sixth launch when KRIYA_TRACE is set.
+#ifdef KRIYA_PF_TRACE
+__device__ long long g_pf_trace[3 * 32 * 8];
+#define PTR(role, j, k) do { if (blockIdx.x == 0 && (j) < 32) g_pf_trace[((role) * 32 + (j)) * 8 + (k)] = clock64(); } while (0)
+#else
+#define PTR(role, j, k) do { } while (0)
+#endif
 
 struct PrefillParams {
     KriyaPrefillArgs a;
     uint32_t q_tiles;  // query tiles of the whole launch (all sequences)
-    uint32_t dtype;
+    uint32_t pairs;    // head pairs per KV head = ceil(group / 2)
 };
 
+// Bulk copy shared -> global (both 16-byte aligned, size a multiple of 16), tracked by the thread's bulk group.
+__device__ __forceinline__ void bulk_s2g(void* dst_gmem, const void* src_smem, uint32_t bytes) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst_gmem), "r"(smem_u32(src_smem)), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_commit_wait_read() {
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+
+// tcgen05.mma issue forms.  The _ts form takes the A operand from tensor memory (rows = lanes, two 16-bit K elements
+// per 32-bit column).  Both are warp-uniform: every lane of the issuing warp runs the (uniform) descriptor arithmetic and the
+// instruction itself is predicated on `elected`, which keeps the operands in uniform registers instead of
+// moving them there from one diverged lane for every instruction.
+__device__ __forceinline__ void umma_ss_pred(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                             uint32_t accumulate, uint32_t elected) {
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "setp.ne.b32 q, %5, 0;\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(elected)
+        : "memory");
+}
+__device__ __forceinline__ void umma_ts_pred(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                             uint32_t accumulate, uint32_t elected) {
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "setp.ne.b32 q, %5, 0;\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(elected)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit_pred(uint64_t* bar, uint32_t elected) {
+    asm volatile(
+        "{\n\t.reg .pred q;\n\t"
+        "setp.ne.b32 q, %1, 0;\n\t"
+        "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}" ::"r"(smem_u32(bar)),
+        "r"(elected)
+        : "memory");
+}
+
 // Shared memory (all tiles 1024-byte aligned):
-//   Q  : D/64 panels x [128 rows][128 B]
-//   K,V: 2 stages x D/64 panels x [128 tokens][128 B] each
-//   P  : 2 panels x [128 rows][128 B]
+//   Q_A, Q_B: D/64 panels x [128 rows][128 B] each
+//   K ring  : 2 stages x D/64 panels x [128 tokens][128 B]
+//   V ring  : 3 stages of the same size, each ring with its own full / empty barriers
+// Tensor memory (512 columns): head A: S/P at 0, O at 128; head B: S/P at 256, O at 384.
 template <int D, typename T>
 __global__ void __launch_bounds__(kPrefillThreads, 1)
-prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, PrefillParams pp) {
+prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+               const __grid_constant__ CUtensorMap map_q, PrefillParams pp) {
     constexpr int PANELS = D / 64;
     constexpr uint32_t PANEL_BYTES = 128 * 128;  // 128 rows x 128 B
     constexpr uint32_t Q_BYTES = PANELS * PANEL_BYTES;
     constexpr uint32_t KV_BYTES = PANELS * PANEL_BYTES;  // one of K or V, one stage
-    constexpr uint32_t P_BYTES = 2 * PANEL_BYTES;
     constexpr uint32_t FMT = (T::kDtype == KRIYA_DTYPE_BF16) ? 1u : 0u;
     constexpr uint32_t IDESC_S = make_idesc(FMT, 128, 128, 0, 0);
     constexpr uint32_t IDESC_O = make_idesc(FMT, 128, D, 0, 1);
     constexpr uint32_t TMEM_COLS = 512;
-    constexpr uint32_t COL_S0 = 0, COL_S1 = 128, COL_O = 256;
 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* sm = smem_raw + (base - smem_u32(smem_raw));
-    uint8_t* sQ = sm;
-    uint8_t* sK = sQ + Q_BYTES;            // [2][KV_BYTES]
-    uint8_t* sV = sK + 2 * KV_BYTES;       // [2][KV_BYTES]
-    uint8_t* sP = sV + 2 * KV_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sP + P_BYTES);
-    uint64_t* kv_full = bars;        // [2]
-    uint64_t* kv_empty = bars + 2;   // [2]
-    uint64_t* s_full = bars + 4;     // [2]
-    uint64_t* p_ready = bars + 6;    // 128 arrivals
-    uint64_t* pv_done = bars + 7;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+    uint8_t* sQ = sm;                      // [2 heads][Q_BYTES]
+    uint8_t* sK = sQ + 2 * Q_BYTES;        // [kKStages][KV_BYTES]
+    uint8_t* sV = sK + kKStages * KV_BYTES;  // [kVStages][KV_BYTES]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sV + kVStages * KV_BYTES);
+    uint64_t* k_full = bars;         // [2]
+    uint64_t* k_empty = bars + 2;    // [2]
+    uint64_t* v_full = bars + 4;     // [3]
+    uint64_t* v_empty = bars + 7;    // [3]
+    uint64_t* s_full = bars + 10;    // [2 heads]
+    uint64_t* p_ready = bars + 12;   // [2 heads], one arrival per softmax warp
+    uint64_t* pv_done = bars + 14;   // [2 heads]
+    uint64_t* q_full = bars + 16;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
     const KriyaPrefillArgs& a = pp.a;
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
-    // heavy tiles (late queries see more keys) first
-    // tiles arrive sorted, most keys first
+    // tiles arrive sorted, most keys first; blockIdx = (kv head, pair, tile) with the tile fastest
     const KriyaPrefillTile qt = a.tiles[blockIdx.x % pp.q_tiles];
-    const uint32_t q_head = blockIdx.x / pp.q_tiles;
+    const uint32_t hp = blockIdx.x / pp.q_tiles;
     const uint32_t group = a.num_q_heads / a.num_kv_heads;
-    const uint32_t kv_head = q_head / group;
+    const uint32_t kv_head = hp / pp.pairs, pair = hp % pp.pairs;
+    const uint32_t head0 = kv_head * group + pair * 2u;
+    const uint32_t n_heads = min(2u, group - pair * 2u);
     const uint32_t tile_start = qt.q_row0;  // first row of this tile in q / out
     const uint32_t tile_rows = qt.rows;
     const uint32_t kv_limit = qt.pos0 + tile_rows;  // keys [0, kv_limit) of the sequence can be seen by this tile
@@ -89,57 +160,55 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
     const uint32_t seq_end = qt.seq_end;  // tokens of the sequence that exist in the cache
 
     // ---- setup -------------------------------------------------------------------------------------------
+    if (tid == 0) PTR(2, 31, 0);
     if (tid == 0) {
-        mbar_init(&kv_full[0], 1);
-        mbar_init(&kv_full[1], 1);
-        mbar_init(&kv_empty[0], 1);
-        mbar_init(&kv_empty[1], 1);
-        mbar_init(&s_full[0], 1);
-        mbar_init(&s_full[1], 1);
-        mbar_init(p_ready, 128);
-        mbar_init(pv_done, 1);
+        for (int i = 0; i < kKStages; ++i) {
+            mbar_init(&k_full[i], 1);
+            mbar_init(&k_empty[i], 1);
+        }
+        for (int i = 0; i < kVStages; ++i) {
+            mbar_init(&v_full[i], 1);
+            mbar_init(&v_empty[i], 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&s_full[i], 1);
+            mbar_init(&p_ready[i], 4);
+            mbar_init(&pv_done[i], 1);
+        }
+        mbar_init(q_full, 1);
         *abort_flag = 0;
         mbar_fence_init();
     }
-    if (warp == 5) {
+    if (warp == 9) {
         tmem_alloc(tmem_slot, TMEM_COLS);
         tmem_relinquish();
+        if (lane == 0) PTR(2, 30, 0);
     }
-    // zero the K/V ring once: pages a tile does not load must read as finite values
-    for (uint32_t i = tid; i < (4 * KV_BYTES) / 16; i += kPrefillThreads)
-        reinterpret_cast<uint4*>(sK)[i] = make_uint4(0u, 0u, 0u, 0u);
-    // Q tile -> swizzled K-major panels (rows past the chunk are zero)
-    {
-        const uint16_t* qg = reinterpret_cast<const uint16_t*>(a.q);
-        constexpr int CHUNKS = D / 8;  // 16-byte chunks per row
-        for (uint32_t i = tid; i < uint32_t(kQTile * CHUNKS); i += kPrefillThreads) {
-            const uint32_t r = i / CHUNKS, c = i % CHUNKS;
-            uint4 val = make_uint4(0u, 0u, 0u, 0u);
-            if (r < tile_rows)
-                val = *reinterpret_cast<const uint4*>(qg + (size_t(tile_start + r) * a.num_q_heads + q_head) * D + c * 8);
-            const uint32_t panel = c >> 3, cc = c & 7u;
-            *reinterpret_cast<uint4*>(sQ + panel * PANEL_BYTES + r * 128u + ((cc ^ (r & 7u)) << 4)) = val;
-        }
-    }
-    fence_async_smem();  // generic-proxy writes (zero fill, Q) visible to the tensor core / TMA proxy
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    if (tid == 0) PTR(2, 31, 1);
 
-    if (warp == 4) {
+    if (warp >= 8) {
+    setmaxnreg_dec<kRegsWorkers>();
+    if (warp == 8) {
         // ---- producer: gather the tile's pages through the block table --------------------------------
         const int32_t* table = a.table + qt.tbl_off;
+        // the query tiles of the CTA's heads: one 64-column x 128-row box per panel (rows past the end of q read as zero;
+        // rows past the tile but inside q belong to another sequence and only feed output rows that are never stored)
+        if (lane == 0) {
+            mbar_arrive_expect_tx(q_full, n_heads * Q_BYTES);
+            for (uint32_t x = 0; x < n_heads; ++x)
+#pragma unroll
+                for (int p = 0; p < PANELS; ++p)
+                    tma_load_2d(sQ + x * Q_BYTES + p * PANEL_BYTES, &map_q, int32_t(head0 + x) * D + p * 64, int32_t(tile_start), q_full);
+        }
+        __syncwarp();
+        uint32_t vs = 0, v_round = 0;  // V stage of tile j = j % kVStages, round = j / kVStages
         for (uint32_t j = 0; j < n_tiles; ++j) {
             if (*abort_flag) break;
-            const uint32_t stage = j & 1u;
-            if (j >= 2 && !warp_wait(&kv_empty[stage], ((j >> 1) - 1u) & 1u)) {
-                if (lane == 0) {
-                    atomicMax(a.status, uint32_t(KRIYA_DEV_WAIT_EXPIRED));
-                    *abort_flag = 1;
-                }
-                break;
-            }
+            const uint32_t ks = j & 1u;
             const uint32_t first_page = j * kPagesPerTile;
             const uint32_t last_needed = (min(kv_limit, (j + 1) * uint32_t(kKvTile)) + kPagePf - 1) / kPagePf;  // exclusive
             const uint32_t npages = last_needed - first_page;
@@ -151,108 +220,152 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
                     blk = 0;
                 }
             }
-            if (lane == 0) mbar_arrive_expect_tx(&kv_full[stage], npages * uint32_t(2 * PANELS * kPagePf * 128));
+            const int32_t y = int32_t(a.layer_row0) + blk * kPagePf;
+            bool ok = j < uint32_t(kKStages) || warp_wait(&k_empty[ks], ((j >> 1) - 1u) & 1u);
+            if (ok) {
+                if (lane == 0) mbar_arrive_expect_tx(&k_full[ks], npages * uint32_t(PANELS * kPagePf * 128));
+                __syncwarp();
+                if (lane < npages) {
+#pragma unroll
+                    for (int p = 0; p < PANELS; ++p)
+                        tma_load_2d(sK + ks * KV_BYTES + p * PANEL_BYTES + lane * (kPagePf * 128), &map_k, int32_t(kv_head) * D + p * 64, y, &k_full[ks]);
+                }
+                ok = j < uint32_t(kVStages) || warp_wait(&v_empty[vs], (v_round - 1u) & 1u);
+            }
+            if (!ok) {
+                if (lane == 0) {
+                    atomicMax(a.status, uint32_t(KRIYA_DEV_WAIT_EXPIRED));
+                    *abort_flag = 1;
+                }
+                break;
+            }
+            if (lane == 0) mbar_arrive_expect_tx(&v_full[vs], npages * uint32_t(PANELS * kPagePf * 128));
             __syncwarp();
             if (lane < npages) {
-                const int32_t y = int32_t(a.layer_row0) + blk * kPagePf;
 #pragma unroll
-                for (int p = 0; p < PANELS; ++p) {
-                    const int32_t x = int32_t(kv_head) * D + p * 64;
-                    tma_load_2d(sK + stage * KV_BYTES + p * PANEL_BYTES + lane * (kPagePf * 128), &map_k, x, y, &kv_full[stage]);
-                    tma_load_2d(sV + stage * KV_BYTES + p * PANEL_BYTES + lane * (kPagePf * 128), &map_v, x, y, &kv_full[stage]);
-                }
+                for (int p = 0; p < PANELS; ++p)
+                    tma_load_2d(sV + vs * KV_BYTES + p * PANEL_BYTES + lane * (kPagePf * 128), &map_v, int32_t(kv_head) * D + p * 64, y, &v_full[vs]);
             }
+            if (++vs == uint32_t(kVStages)) { vs = 0; ++v_round; }
         }
-    } else if (warp == 5) {
+    } else if (warp == 9) {
         // ---- MMA issuer ------------------------------------------------------------------------------------
-        const uint32_t q_addr = smem_u32(sQ), k_addr = smem_u32(sK), v_addr = smem_u32(sV), p_addr = smem_u32(sP);
-        auto issue_s = [&](uint32_t j) {
-            const uint32_t stage = j & 1u;
-            const uint32_t d_tmem = tmem_base + ((j & 1u) ? COL_S1 : COL_S0);
+        // Issue order: S_A(0), S_B(0), then per KV tile j: P_A.V(j), S_A(j+1), P_B.V(j), S_B(j+1).  The tensor pipe runs
+        // one thread's MMAs in issue order, so S_x(j+1) may overwrite the score tile that holds P_x(j) as soon as
+        // P_x.V(j) has been issued, and the commit behind S_x(j+1) also covers P_x.V(j): a softmax group that sees
+        // s_full[x] may rescale O_x.  While one head is in its softmax the pipe works on the other head.
+        // Every lane runs this code; only the tensor-core instructions themselves are predicated on the elected lane.
+        const uint32_t el = (lane == 0) ? 1u : 0u;
+        const uint64_t q_desc = smem_desc_sw128(smem_u32(sQ), 16, 1024);
+        const uint64_t k_desc = smem_desc_sw128(smem_u32(sK), 16, 1024);
+        const uint64_t v_desc = smem_desc_sw128(smem_u32(sV), PANEL_BYTES, 1024);
+        auto issue_s = [&](uint32_t x, uint32_t stage, bool last_head) {
+            const uint32_t d_tmem = tmem_base + x * 256u;
+            const uint64_t qd = q_desc + uint64_t((x * Q_BYTES) >> 4), kd = k_desc + uint64_t((stage * KV_BYTES) >> 4);
 #pragma unroll
             for (int ks = 0; ks < D / 16; ++ks) {
-                const uint32_t off = uint32_t(ks / 4) * PANEL_BYTES + uint32_t(ks % 4) * 32u;
-                umma_f16(d_tmem, smem_desc_sw128(q_addr + off, 16, 1024), smem_desc_sw128(k_addr + stage * KV_BYTES + off, 16, 1024),
-                         IDESC_S, ks > 0 ? 1u : 0u);
+                const uint64_t off = uint64_t((uint32_t(ks / 4) * PANEL_BYTES + uint32_t(ks % 4) * 32u) >> 4);
+                umma_ss_pred(d_tmem, qd + off, kd + off, IDESC_S, ks > 0 ? 1u : 0u, el);
             }
-            umma_commit(&s_full[j & 1u]);
+            umma_commit_pred(&s_full[x], el);
+            if (last_head) umma_commit_pred(&k_empty[stage], el);
         };
-        bool ok = true;
+        bool ok = n_tiles > 0 && warp_wait(q_full, 0u) && warp_wait(&k_full[0], 0u);
+        if (ok) {
+            tc_fence_after();
+            for (uint32_t x = 0; x < n_heads; ++x) issue_s(x, 0u, x + 1u == n_heads);
+        }
+        uint32_t vs = 0, v_round = 0;
         for (uint32_t j = 0; j < n_tiles && ok; ++j) {
             if (*abort_flag) break;
-            if (j == 0) {
-                ok = warp_wait(&kv_full[0], 0);
+            const uint32_t stage = j & 1u;
+            const bool more = j + 1u < n_tiles;
+            const uint64_t vd = v_desc + uint64_t((vs * KV_BYTES) >> 4);
+            for (uint32_t x = 0; x < n_heads && ok; ++x) {
+                if (x == 0u) {  // the tiles land long before the probabilities are ready: take these waits first
+                    ok = warp_wait(&v_full[vs], v_round & 1u);
+                    if (ok && more) ok = warp_wait(&k_full[stage ^ 1u], ((j + 1u) >> 1) & 1u);
+                    if (!ok) break;
+                }
+                if (lane == 0 && x == 0) PTR(2, j, 6);
+                ok = warp_wait(&p_ready[x], j & 1u);
+                if (lane == 0 && x == 0) PTR(2, j, 7);
                 if (!ok) break;
                 tc_fence_after();
-                if (lane == 0) issue_s(0);
-            }
-            if (j + 1 < n_tiles) {
-                ok = warp_wait(&kv_full[(j + 1) & 1u], ((j + 1) >> 1) & 1u);
-                if (!ok) break;
-                tc_fence_after();
-                if (lane == 0) issue_s(j + 1);
-            }
-            ok = warp_wait(p_ready, j & 1u);
-            if (!ok) break;
-            tc_fence_after();
-            if (lane == 0) {
-                const uint32_t stage = j & 1u;
+                if (lane == 0) PTR(2, j, x * 3);
 #pragma unroll
                 for (int ks = 0; ks < kKvTile / 16; ++ks) {
-                    // A = P (K-major, 16 keys = 32 B inside a 64-key panel), B = V page ks (MN-major)
-                    const uint32_t a_off = uint32_t(ks / 4) * PANEL_BYTES + uint32_t(ks % 4) * 32u;
-                    const uint32_t b_off = stage * KV_BYTES + uint32_t(ks) * (kPagePf * 128);
-                    umma_f16(tmem_base + COL_O, smem_desc_sw128(p_addr + a_off, 16, 1024),
-                             smem_desc_sw128(v_addr + b_off, PANEL_BYTES, 1024), IDESC_O, (j > 0 || ks > 0) ? 1u : 0u);
+                    // A = P_x from tensor memory (16 keys = 8 columns), B = V page ks (MN-major)
+                    umma_ts_pred(tmem_base + x * 256u + 128u, tmem_base + x * 256u + uint32_t(ks) * 8u,
+                                 vd + uint64_t((uint32_t(ks) * (kPagePf * 128)) >> 4), IDESC_O, (j > 0 || ks > 0) ? 1u : 0u, el);
                 }
-                umma_commit(&kv_empty[stage]);
-                umma_commit(pv_done);
+                if (x + 1u == n_heads) umma_commit_pred(&v_empty[vs], el);
+                if (lane == 0) PTR(2, j, x * 3 + 1);
+                if (more) issue_s(x, stage ^ 1u, x + 1u == n_heads);
+                else umma_commit_pred(&pv_done[x], el);
+                if (lane == 0) PTR(2, j, x * 3 + 2);
             }
-            __syncwarp();
+            if (++vs == uint32_t(kVStages)) { vs = 0; ++v_round; }
         }
-        if (!ok && lane == 0) {
+        if (!ok && n_tiles > 0 && lane == 0) {
             atomicMax(a.status, uint32_t(KRIYA_DEV_WAIT_EXPIRED));
             *abort_flag = 1;
         }
+    }
     } else {
-        // ---- softmax warps: thread = query row = TMEM lane ---------------------------------------------------
-        const uint32_t row = tid;  // 0..127
-        const uint32_t lane_addr = (warp * 32u) << 16;
+    setmaxnreg_inc<kRegsSoftmax>();
+    if ((warp >> 2) < n_heads) {
+        // ---- softmax warpgroups: x = 0 (warps 0-3) / 1 (warps 4-7); thread = query row = TMEM lane -------------
+        const uint32_t x = warp >> 2;
+        const uint32_t row = tid & 127u;
+        const uint32_t lane_addr = ((warp & 3u) * 32u) << 16;
+        const uint32_t s_addr = tmem_base + lane_addr + x * 256u;
+        const uint32_t o_addr = s_addr + 128u;
         const bool softcap = a.logit_softcap > 0.0f;
-        const float scale2 = softcap ? a.sm_scale : a.sm_scale * kLog2ePf;
+        const float scale2 = softcap ? kLog2ePf : a.sm_scale * kLog2ePf;
         const uint32_t q_pos = qt.pos0 + min(row, tile_rows - 1u);  // absolute position
         float m_used = -INFINITY, l_run = 0.0f;
         bool ok = true;
-        for (uint32_t j = 0; j < n_tiles; ++j) {
+        uint32_t vs = 0, v_round = 0;
+        for (uint32_t j = 0; j < n_tiles; ++j, vs = (vs + 1u == uint32_t(kVStages)) ? 0u : vs + 1u, v_round += (vs == 0u)) {
             if (*abort_flag) { ok = false; break; }
-            ok = warp_wait(&s_full[j & 1u], (j >> 1) & 1u);
+            ok = warp_wait(&s_full[x], j & 1u);
             if (!ok) break;
             tc_fence_after();
-            const uint32_t s_addr = tmem_base + lane_addr + ((j & 1u) ? COL_S1 : COL_S0);
+            if (row == 0) PTR(x, j, 0);
             const uint32_t key0 = j * kKvTile;
             const bool diag = key0 + kKvTile - 1u > qt.pos0;  // some row of the tile masks some key
-            // pass 1: row maximum
-            float m_tile = -INFINITY;
-#pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
-                uint32_t r[32];
-                tmem_ld32(s_addr + c * 32, r);
-                tmem_wait_ld();
+            // the whole score row into registers, once
+            uint32_t sr[4][32];
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    float s = __uint_as_float(r[i]) * scale2;
-                    if (softcap) s = tanhf(fminf(fmaxf(s / a.logit_softcap, -15.0f), 15.0f)) * a.logit_softcap * kLog2ePf;
-                    const uint32_t key = key0 + c * 32 + i;
-                    if (diag && key > q_pos) s = -INFINITY;
-                    m_tile = fmaxf(m_tile, s);
-                }
+            for (int c = 0; c < 4; ++c) tmem_ld32(s_addr + c * 32, sr[c]);
+            tmem_wait_ld();
+            if (row == 0) PTR(x, j, 1);
+            // the scores stay raw in registers; scale and exponent reference are folded into one fma per pair below
+            if (softcap) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const float s = __uint_as_float(sr[c][i]) * a.sm_scale;
+                        sr[c][i] = __float_as_uint(tanhf(fminf(fmaxf(s / a.logit_softcap, -15.0f), 15.0f)) * a.logit_softcap);
+                    }
             }
-            // the previous P.V must be complete before P is overwritten or O rescaled
-            if (j > 0) {
-                ok = warp_wait(pv_done, (j - 1u) & 1u);
-                if (!ok) break;
-                tc_fence_after();
+            if (diag) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        if (key0 + uint32_t(c * 32 + i) > q_pos) sr[c][i] = 0xFF800000u;  // -inf
             }
+            float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four independent chains
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) m4[c] = max3(m4[c], __uint_as_float(sr[c][i]), __uint_as_float(sr[c][i + 1]));
+            const float m_tile = fmaxf(max3(m4[0], m4[1], m4[2]), m4[3]) * scale2;  // scale2 > 0
+            if (row == 0) PTR(x, j, 2);
+            // the commit behind S_x(j) covers P_x.V(j-1): O_x may be rescaled and the score tile rewritten
             float alpha = 1.0f;
             bool need = false;
             if (j == 0) {
@@ -266,90 +379,96 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
 #pragma unroll 1
                 for (int c = 0; c < D / 32; ++c) {
                     uint32_t r[32];
-                    tmem_ld32(tmem_base + lane_addr + COL_O + c * 32, r);
+                    tmem_ld32(o_addr + c * 32, r);
                     tmem_wait_ld();
 #pragma unroll
                     for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-                    tmem_st32(tmem_base + lane_addr + COL_O + c * 32, r);
+                    tmem_st32(o_addr + c * 32, r);
                 }
-                tmem_wait_st();
             }
-            // pass 2: probabilities -> P tile (storage dtype, swizzled K-major), row sum
-            float psum = 0.0f;
-#pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
-                uint32_t r[32];
-                tmem_ld32(s_addr + c * 32, r);
-                tmem_wait_ld();
+            // probabilities in the storage dtype, two keys per 32-bit column, over the first 64 columns of the score tile
+            if (row == 0) PTR(x, j, 3);
+            float2 psum2 = make_float2(0.0f, 0.0f);
+            const float2 sc2 = make_float2(scale2, scale2), neg_m2 = make_float2(-m_used, -m_used);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {  // 32 keys = 16 columns at a time, each stored as soon as it is ready
                 uint32_t packed[16];
 #pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    float s0 = __uint_as_float(r[i]) * scale2, s1 = __uint_as_float(r[i + 1]) * scale2;
-                    if (softcap) {
-                        s0 = tanhf(fminf(fmaxf(s0 / a.logit_softcap, -15.0f), 15.0f)) * a.logit_softcap * kLog2ePf;
-                        s1 = tanhf(fminf(fmaxf(s1 / a.logit_softcap, -15.0f), 15.0f)) * a.logit_softcap * kLog2ePf;
-                    }
-                    const uint32_t key = key0 + c * 32 + i;
-                    float p0 = fast_exp2(s0 - m_used), p1 = fast_exp2(s1 - m_used);
-                    if (diag && key > q_pos) p0 = 0.0f;
-                    if (diag && key + 1u > q_pos) p1 = 0.0f;
-                    const uint16_t b0 = T::store(p0), b1 = T::store(p1);
-                    // the sum uses the rounded probabilities, so that numerator and denominator agree
-                    psum += T::load(b0) + T::load(b1);
-                    packed[i >> 1] = uint32_t(b0) | (uint32_t(b1) << 16);
+                for (int i = 0; i < 16; ++i) {
+                    const float2 e = __ffma2_rn(make_float2(__uint_as_float(sr[c][2 * i]), __uint_as_float(sr[c][2 * i + 1])), sc2, neg_m2);
+                    const float2 pr = make_float2(fast_exp2(e.x), fast_exp2(e.y));
+                    psum2 = __fadd2_rn(psum2, pr);
+                    packed[i] = T::pack2(pr.x, pr.y);
                 }
-                // 32 keys = 64 B = four 16-byte chunks of this row; chunk index inside the 64-key panel
-                const uint32_t panel = uint32_t(c) >> 1;
-#pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4) {
-                    const uint32_t cc = (uint32_t(c) & 1u) * 4u + q4;
-                    *reinterpret_cast<uint4*>(sP + panel * PANEL_BYTES + row * 128u + ((cc ^ (row & 7u)) << 4)) =
-                        make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2], packed[4 * q4 + 3]);
-                }
+                tmem_st16(s_addr + c * 16, packed);
             }
+            const float psum = psum2.x + psum2.y;
+            if (row == 0) PTR(x, j, 4);
+            tmem_wait_st();
+            if (row == 0) PTR(x, j, 5);
+            if (row == 0) PTR(x, j, 6);
             l_run = l_run * alpha + psum;
-            // slots past the end of the sequence may hold anything: their V rows must not reach the MMA
-            if ((j + 1u) * kKvTile > seq_end) {
-                const uint32_t stage = j & 1u;
-                const uint32_t first_bad = seq_end > key0 ? seq_end - key0 : 0u;
-                const uint32_t end_row = min(uint32_t(kKvTile), ((seq_end + kPagePf - 1) / kPagePf) * kPagePf - min(key0, ((seq_end + kPagePf - 1) / kPagePf) * kPagePf));
-                for (uint32_t i = first_bad * 8u + row; i < end_row * 8u; i += 128u) {
-                    const uint32_t rr = i >> 3, ch = i & 7u;
+            // Only the last tile can hold rows that are not valid V data: slots past the end of the sequence (loaded, but
+            // they may hold anything) and pages the producer did not load (shared memory as the previous kernel left
+            // it).  Their probabilities are zero, but 0 x NaN is NaN, so head A's warpgroup clears those rows; P.V of
+            // head B is issued after P.V of head A and sees the cleared rows too.
+            if (x == 0u && j + 1u == n_tiles) {
+                const uint32_t loaded_end = ((kv_limit + kPagePf - 1) / kPagePf) * kPagePf;
+                const uint32_t first_bad = min(seq_end, loaded_end) - key0;  // seq_end >= kv_limit > key0
+                if (first_bad < uint32_t(kKvTile)) {
+                    ok = warp_wait(&v_full[vs], v_round & 1u);  // the tile must have landed before rows of it are cleared
+                    if (!ok) break;
+                    for (uint32_t i = first_bad * 8u + row; i < uint32_t(kKvTile) * 8u; i += 128u) {
+                        const uint32_t rr = i >> 3, ch = i & 7u;
 #pragma unroll
-                    for (int p = 0; p < PANELS; ++p)
-                        *reinterpret_cast<uint4*>(sV + stage * KV_BYTES + p * PANEL_BYTES + rr * 128u + (ch << 4)) =
-                            make_uint4(0u, 0u, 0u, 0u);
+                        for (int p = 0; p < PANELS; ++p)
+                            *reinterpret_cast<uint4*>(sV + vs * KV_BYTES + p * PANEL_BYTES + rr * 128u + (ch << 4)) =
+                                make_uint4(0u, 0u, 0u, 0u);
+                    }
+                    fence_async_smem();
                 }
             }
+            if (row == 0) PTR(x, j, 7);
             tc_fence_before();
-            fence_async_smem();
-            mbar_arrive(p_ready);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&p_ready[x]);
         }
+        if (tid == 0) PTR(2, 31, 2);
         if (ok && n_tiles > 0) {
-            ok = warp_wait(pv_done, (n_tiles - 1u) & 1u);
+            ok = warp_wait(&pv_done[x], 0u);
+            if (tid == 0) PTR(2, 31, 3);
             if (ok) {
                 tc_fence_after();
                 const float inv_l = 1.0f / fmaxf(l_run, 1e-12f);
-                uint16_t* og = reinterpret_cast<uint16_t*>(a.out) + (size_t(tile_start + row) * a.num_q_heads + q_head) * D;
+                // The output row goes through shared memory: every S MMA is complete once pv_done[x] has fired, so the
+                // Q tiles and the K ring are free.  A thread writes its own row (rows padded by 16 bytes: no bank
+                // conflicts) and sends it to global memory with one bulk copy; only the thread itself reads the row back,
+                // so no barrier is needed.
+                constexpr uint32_t ROW_BYTES = D * 2, ROW_STRIDE = ROW_BYTES + 16;
+                uint8_t* stage_row = sm + x * (kQTile * ROW_STRIDE) + row * ROW_STRIDE;
 #pragma unroll 1
                 for (int c = 0; c < D / 32; ++c) {
                     uint32_t r[32];
-                    tmem_ld32(tmem_base + lane_addr + COL_O + c * 32, r);
+                    tmem_ld32(o_addr + c * 32, r);
                     tmem_wait_ld();
-                    if (row < tile_rows) {
 #pragma unroll
-                        for (int q4 = 0; q4 < 4; ++q4) {
-                            uint32_t w[4];
+                    for (int q4 = 0; q4 < 4; ++q4) {
+                        uint32_t w[4];
 #pragma unroll
-                            for (int i = 0; i < 4; ++i) {
-                                const float x0 = __uint_as_float(r[q4 * 8 + 2 * i]) * inv_l;
-                                const float x1 = __uint_as_float(r[q4 * 8 + 2 * i + 1]) * inv_l;
-                                w[i] = uint32_t(T::store(x0)) | (uint32_t(T::store(x1)) << 16);
-                            }
-                            *reinterpret_cast<uint4*>(og + c * 32 + q4 * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+                        for (int i = 0; i < 4; ++i) {
+                            const float x0 = __uint_as_float(r[q4 * 8 + 2 * i]) * inv_l;
+                            const float x1 = __uint_as_float(r[q4 * 8 + 2 * i + 1]) * inv_l;
+                            w[i] = uint32_t(T::store(x0)) | (uint32_t(T::store(x1)) << 16);
                         }
+                        *reinterpret_cast<uint4*>(stage_row + c * 64 + q4 * 16) = make_uint4(w[0], w[1], w[2], w[3]);
                     }
                 }
+                fence_async_smem();
+                if (row < tile_rows) {
+                    uint16_t* og = reinterpret_cast<uint16_t*>(a.out) + (size_t(tile_start + row) * a.num_q_heads + head0 + x) * D;
+                    bulk_s2g(og, stage_row, ROW_BYTES);
+                }
+                bulk_commit_wait_read();  // the rows must have been read before the CTA gives its shared memory back
             }
         }
         if (!ok && lane == 0) {
@@ -358,20 +477,23 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
         }
     }
 
+    }
+    if (tid == 0) PTR(2, 31, 4);
     // ---- teardown: every thread gets here; TMEM is returned by the warp that took it ------------------
     tc_fence_before();
     __syncthreads();
-    if (warp == 5) {
+    if (warp == 9) {
         tc_fence_after();
         tmem_dealloc(tmem_base, TMEM_COLS);
     }
+    if (tid == 0) PTR(2, 31, 5);
 }
 
 template <int D, typename T>
-cudaError_t launch_prefill_t(const KriyaPrefillArgs& a, const CUtensorMap& mk, const CUtensorMap& mv, int max_smem_optin,
-                             cudaStream_t s) {
+cudaError_t launch_prefill_t(const KriyaPrefillArgs& a, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mq,
+                             int max_smem_optin, cudaStream_t s) {
     constexpr int PANELS = D / 64;
-    const size_t smem = size_t(PANELS) * 128 * 128 * 5 + 2 * 128 * 128 + 256 + 1024;
+    const size_t smem = size_t(PANELS) * 128 * 128 * (2 + kKStages + kVStages) + 256 + 1024;  // Q x 2 heads, K ring, V ring
     if (smem > size_t(max_smem_optin)) return cudaErrorInvalidValue;
     auto kern = prefill_kernel<D, T>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
@@ -379,8 +501,30 @@ cudaError_t launch_prefill_t(const KriyaPrefillArgs& a, const CUtensorMap& mk, c
     PrefillParams pp;
     pp.a = a;
     pp.q_tiles = a.n_tiles;
-    pp.dtype = T::kDtype;
-    kern<<<pp.q_tiles * a.num_q_heads, kPrefillThreads, smem, s>>>(mk, mv, pp);
+    const uint32_t group = a.num_q_heads / a.num_kv_heads;
+    pp.pairs = (group + 1u) / 2u;
+    kern<<<pp.q_tiles * pp.pairs * a.num_kv_heads, kPrefillThreads, smem, s>>>(mk, mv, mq, pp);
+#ifdef KRIYA_PF_TRACE
+    if (getenv("KRIYA_TRACE")) {
+        static int calls = 0;
+        if (++calls == 6) {
+            cudaDeviceSynchronize();
+            static long long h[3 * 32 * 8];
+            cudaMemcpyFromSymbol(h, g_pf_trace, sizeof(h));
+            long long t0 = h[0];
+            for (int i = 0; i < 3 * 32 * 8; ++i)
+                if (h[i] && llabs(h[i] - h[0]) < 1000000 && h[i] < t0) t0 = h[i];
+            const char* role[3] = {"smA", "smB", "mma"};
+            for (int j = 0; j < 32; ++j)
+                for (int r = 0; r < 3; ++r) {
+                    if (!h[(r * 32 + j) * 8] || llabs(h[(r * 32 + j) * 8] - t0) > 1000000) continue;
+                    fprintf(stderr, "tile %2d %s", j, role[r]);
+                    for (int k = 0; k < 8; ++k) fprintf(stderr, " %7lld", h[(r * 32 + j) * 8 + k] ? h[(r * 32 + j) * 8 + k] - t0 : -1);
+                    fprintf(stderr, "\n");
+                }
+        }
+    }
+#endif
     return cudaGetLastError();
 }
 
@@ -391,32 +535,49 @@ bool kriya_prefill_supported(uint32_t head_dim, uint32_t group, uint32_t block_s
     return (head_dim == 64 || head_dim == 128) && group >= 1 && block_size == uint32_t(kriya::kPagePf);
 }
 
+namespace {
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                              const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// The driver's tensor-map encoder, looked up once per process through the runtime.
+cudaError_t tensor_map_encoder(EncodeFn* out) {
+    static EncodeFn cached = nullptr;
+    if (cached == nullptr) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        const cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+        if (e != cudaSuccess) return e;
+        if (fn == nullptr || qres != cudaDriverEntryPointSuccess) return cudaErrorNotSupported;
+        cached = reinterpret_cast<EncodeFn>(fn);
+    }
+    *out = cached;
+    return cudaSuccess;
+}
+
+// 2-D map over a row-major 16-bit matrix [rows][row_elems]; box = 64 columns x box_rows rows, 128-byte swizzle, zero
+// fill outside the matrix.
+cudaError_t encode_rows_map(void* base, uint64_t rows, uint32_t row_elems, uint32_t box_rows, CUtensorMap* out) {
+    EncodeFn enc = nullptr;
+    const cudaError_t e = tensor_map_encoder(&enc);
+    if (e != cudaSuccess) return e;
+    const cuuint64_t dims[2] = {row_elems, rows};
+    const cuuint64_t strides[1] = {cuuint64_t(row_elems) * 2};
+    const cuuint32_t box[2] = {64, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+}
+}  // namespace
+
 // Encodes the 2-D tensor maps over the K and V pools (all layers): rows = (layer, block, token), columns =
 // (kv head, d); box = 64 columns x 16 rows with the 128-byte swizzle the MMA descriptors expect.
 cudaError_t kriya_prefill_encode_maps(void* pool_k, void* pool_v, uint64_t total_rows, uint32_t row_elems,
                                       void* out_map_k, void* out_map_v) {
-    using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-    void* fn = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+    cudaError_t e = encode_rows_map(pool_k, total_rows, row_elems, uint32_t(kriya::kPagePf), static_cast<CUtensorMap*>(out_map_k));
     if (e != cudaSuccess) return e;
-    if (fn == nullptr || qres != cudaDriverEntryPointSuccess) return cudaErrorNotSupported;
-    const cuuint64_t dims[2] = {row_elems, total_rows};
-    const cuuint64_t strides[1] = {cuuint64_t(row_elems) * 2};
-    const cuuint32_t box[2] = {64, uint32_t(kriya::kPagePf)};
-    const cuuint32_t estr[2] = {1, 1};
-    void* pools[2] = {pool_k, pool_v};
-    void* outs[2] = {out_map_k, out_map_v};
-    for (int i = 0; i < 2; ++i) {
-        const CUresult r = reinterpret_cast<EncodeFn>(fn)(
-            static_cast<CUtensorMap*>(outs[i]), CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, pools[i], dims, strides, box, estr,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-        if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
-    }
-    return cudaSuccess;
+    return encode_rows_map(pool_v, total_rows, row_elems, uint32_t(kriya::kPagePf), static_cast<CUtensorMap*>(out_map_v));
 }
 
 cudaError_t kriya_launch_prefill(const KriyaPrefillArgs& a, uint32_t head_dim, uint32_t block_size, uint32_t dtype,
@@ -426,10 +587,17 @@ cudaError_t kriya_launch_prefill(const KriyaPrefillArgs& a, uint32_t head_dim, u
         return cudaErrorInvalidValue;
     const CUtensorMap& mk = *static_cast<const CUtensorMap*>(a.map_k);
     const CUtensorMap& mv = *static_cast<const CUtensorMap*>(a.map_v);
+    // the query matrix changes with every call: its map ([q_rows][Hq * D], one box = 64 columns x 128 rows) is encoded here
+    // and travels to the kernel by value
+    if ((reinterpret_cast<uintptr_t>(a.q) & 15u) != 0 || (reinterpret_cast<uintptr_t>(a.out) & 15u) != 0 || a.q_rows == 0)
+        return cudaErrorInvalidValue;
+    alignas(64) CUtensorMap mq;
+    const cudaError_t e = encode_rows_map(const_cast<void*>(a.q), a.q_rows, a.num_q_heads * head_dim, uint32_t(kriya::kQTile), &mq);
+    if (e != cudaSuccess) return e;
     using namespace kriya;
     if (head_dim == 128)
-        return dtype == KRIYA_DTYPE_FP16 ? launch_prefill_t<128, Fp16>(a, mk, mv, max_smem_optin, s)
-                                         : launch_prefill_t<128, Bf16>(a, mk, mv, max_smem_optin, s);
-    return dtype == KRIYA_DTYPE_FP16 ? launch_prefill_t<64, Fp16>(a, mk, mv, max_smem_optin, s)
-                                     : launch_prefill_t<64, Bf16>(a, mk, mv, max_smem_optin, s);
+        return dtype == KRIYA_DTYPE_FP16 ? launch_prefill_t<128, Fp16>(a, mk, mv, mq, max_smem_optin, s)
+                                         : launch_prefill_t<128, Bf16>(a, mk, mv, mq, max_smem_optin, s);
+    return dtype == KRIYA_DTYPE_FP16 ? launch_prefill_t<64, Fp16>(a, mk, mv, mq, max_smem_optin, s)
+                                     : launch_prefill_t<64, Bf16>(a, mk, mv, mq, max_smem_optin, s);
 }
