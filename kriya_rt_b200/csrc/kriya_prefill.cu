@@ -116,7 +116,7 @@ __device__ __forceinline__ void umma_commit_pred(uint64_t* bar, uint32_t elected
 template <int D, typename T>
 __global__ void __launch_bounds__(kPrefillThreads, 1)
 prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
-               const __grid_constant__ CUtensorMap map_q, PrefillParams pp) {
+               const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_o, PrefillParams pp) {
     constexpr int PANELS = D / 64;
     constexpr uint32_t PANEL_BYTES = 128 * 128;  // 128 rows x 128 B
     constexpr uint32_t Q_BYTES = PANELS * PANEL_BYTES;
@@ -141,7 +141,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
     uint64_t* p_ready = bars + 12;   // [2 heads], one arrival per softmax warp
     uint64_t* pv_done = bars + 14;   // [2 heads]
     uint64_t* q_full = bars + 16;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
+    uint64_t* o_staged = bars + 17;  // [2 heads], one arrival per softmax warp: the output tile is in shared memory
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 19);
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
     const KriyaPrefillArgs& a = pp.a;
@@ -160,6 +161,11 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
     const uint32_t seq_end = qt.seq_end;  // tokens of the sequence that exist in the cache
 
     // ---- setup -------------------------------------------------------------------------------------------
+    if (tid == 8 * 32) {  // the producer's first lane: the descriptors are on their way while the barriers are set up
+        tma_prefetch_map(&map_q);
+        tma_prefetch_map(&map_k);
+        tma_prefetch_map(&map_v);
+    }
     if (tid == 0) PTR(2, 31, 0);
     if (tid == 0) {
         for (int i = 0; i < kKStages; ++i) {
@@ -174,6 +180,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
             mbar_init(&s_full[i], 1);
             mbar_init(&p_ready[i], 4);
             mbar_init(&pv_done[i], 1);
+            mbar_init(&o_staged[i], 4);
         }
         mbar_init(q_full, 1);
         *abort_flag = 0;
@@ -204,6 +211,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
                 for (int p = 0; p < PANELS; ++p)
                     tma_load_2d(sQ + x * Q_BYTES + p * PANEL_BYTES, &map_q, int32_t(head0 + x) * D + p * 64, int32_t(tile_start), q_full);
         }
+        if (lane == 0) PTR(2, 30, 1);
         __syncwarp();
         uint32_t vs = 0, v_round = 0;  // V stage of tile j = j % kVStages, round = j / kVStages
         for (uint32_t j = 0; j < n_tiles; ++j) {
@@ -221,6 +229,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
                 }
             }
             const int32_t y = int32_t(a.layer_row0) + blk * kPagePf;
+            if (lane == 0 && j == 0) PTR(2, 30, 2);
             bool ok = j < uint32_t(kKStages) || warp_wait(&k_empty[ks], ((j >> 1) - 1u) & 1u);
             if (ok) {
                 if (lane == 0) mbar_arrive_expect_tx(&k_full[ks], npages * uint32_t(PANELS * kPagePf * 128));
@@ -270,7 +279,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
             umma_commit_pred(&s_full[x], el);
             if (last_head) umma_commit_pred(&k_empty[stage], el);
         };
-        bool ok = n_tiles > 0 && warp_wait(q_full, 0u) && warp_wait(&k_full[0], 0u);
+        bool ok = n_tiles > 0 && warp_wait(q_full, 0u);
+        if (lane == 0) PTR(2, 30, 3);
+        ok = ok && warp_wait(&k_full[0], 0u);
+        if (lane == 0) PTR(2, 30, 4);
         if (ok) {
             tc_fence_after();
             for (uint32_t x = 0; x < n_heads; ++x) issue_s(x, 0u, x + 1u == n_heads);
@@ -440,12 +452,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
             if (ok) {
                 tc_fence_after();
                 const float inv_l = 1.0f / fmaxf(l_run, 1e-12f);
-                // The output row goes through shared memory: every S MMA is complete once pv_done[x] has fired, so the
-                // Q tiles and the K ring are free.  A thread writes its own row (rows padded by 16 bytes: no bank
-                // conflicts) and sends it to global memory with one bulk copy; only the thread itself reads the row back,
-                // so no barrier is needed.
-                constexpr uint32_t ROW_BYTES = D * 2, ROW_STRIDE = ROW_BYTES + 16;
-                uint8_t* stage_row = sm + x * (kQTile * ROW_STRIDE) + row * ROW_STRIDE;
+                // The output tile goes through shared memory in the layout of the query tile it replaces (every S MMA is
+                // complete once pv_done[x] has fired): a full tile leaves with one tensor store per 64-column panel, a
+                // partial one row by row, since a tensor store would also write the rows of the next sequence.
+                uint8_t* stage = sQ + x * Q_BYTES;
 #pragma unroll 1
                 for (int c = 0; c < D / 32; ++c) {
                     uint32_t r[32];
@@ -455,20 +465,32 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
                     for (int q4 = 0; q4 < 4; ++q4) {
                         uint32_t w[4];
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            const float x0 = __uint_as_float(r[q4 * 8 + 2 * i]) * inv_l;
-                            const float x1 = __uint_as_float(r[q4 * 8 + 2 * i + 1]) * inv_l;
-                            w[i] = uint32_t(T::store(x0)) | (uint32_t(T::store(x1)) << 16);
-                        }
-                        *reinterpret_cast<uint4*>(stage_row + c * 64 + q4 * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+                        for (int i = 0; i < 4; ++i)
+                            w[i] = T::pack2(__uint_as_float(r[q4 * 8 + 2 * i]) * inv_l, __uint_as_float(r[q4 * 8 + 2 * i + 1]) * inv_l);
+                        const uint32_t chunk = uint32_t(c & 1) * 4u + uint32_t(q4);  // 16-byte chunk inside the 64-column panel
+                        *reinterpret_cast<uint4*>(stage + uint32_t(c >> 1) * PANEL_BYTES + row * 128u + ((chunk ^ (row & 7u)) << 4)) =
+                            make_uint4(w[0], w[1], w[2], w[3]);
                     }
                 }
+                if (tid == 0) PTR(2, 31, 6);
                 fence_async_smem();
-                if (row < tile_rows) {
+                if (tile_rows == uint32_t(kQTile)) {
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&o_staged[x]);
+                    if (row == 0 && mbar_wait(&o_staged[x], 0u)) {  // bounded: the group's 128 rows are in place
+#pragma unroll
+                        for (int p = 0; p < PANELS; ++p)
+                            tma_store_2d(&map_o, stage + p * PANEL_BYTES, int32_t(head0 + x) * D + p * 64, int32_t(tile_start));
+                    }
+                } else if (row < tile_rows) {
+                    // swizzled row: chunk c of the row sits at position c ^ (row & 7) of its 128-byte line
                     uint16_t* og = reinterpret_cast<uint16_t*>(a.out) + (size_t(tile_start + row) * a.num_q_heads + head0 + x) * D;
-                    bulk_s2g(og, stage_row, ROW_BYTES);
+#pragma unroll
+                    for (int c = 0; c < D / 8; ++c)
+                        bulk_s2g(og + c * 8, stage + uint32_t(c >> 3) * PANEL_BYTES + row * 128u + (((uint32_t(c) & 7u) ^ (row & 7u)) << 4), 16);
                 }
-                bulk_commit_wait_read();  // the rows must have been read before the CTA gives its shared memory back
+                if (tid == 0) PTR(2, 31, 7);
+                bulk_commit_wait_read();  // the tile must have been read before the CTA gives its shared memory back
             }
         }
         if (!ok && lane == 0) {
@@ -491,7 +513,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
 
 template <int D, typename T>
 cudaError_t launch_prefill_t(const KriyaPrefillArgs& a, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mq,
-                             int max_smem_optin, cudaStream_t s) {
+                             const CUtensorMap& mo, int max_smem_optin, cudaStream_t s) {
     constexpr int PANELS = D / 64;
     const size_t smem = size_t(PANELS) * 128 * 128 * (2 + kKStages + kVStages) + 256 + 1024;  // Q x 2 heads, K ring, V ring
     if (smem > size_t(max_smem_optin)) return cudaErrorInvalidValue;
@@ -503,7 +525,7 @@ cudaError_t launch_prefill_t(const KriyaPrefillArgs& a, const CUtensorMap& mk, c
     pp.q_tiles = a.n_tiles;
     const uint32_t group = a.num_q_heads / a.num_kv_heads;
     pp.pairs = (group + 1u) / 2u;
-    kern<<<pp.q_tiles * pp.pairs * a.num_kv_heads, kPrefillThreads, smem, s>>>(mk, mv, mq, pp);
+    kern<<<pp.q_tiles * pp.pairs * a.num_kv_heads, kPrefillThreads, smem, s>>>(mk, mv, mq, mo, pp);
 #ifdef KRIYA_PF_TRACE
     if (getenv("KRIYA_TRACE")) {
         static int calls = 0;
@@ -587,17 +609,18 @@ cudaError_t kriya_launch_prefill(const KriyaPrefillArgs& a, uint32_t head_dim, u
         return cudaErrorInvalidValue;
     const CUtensorMap& mk = *static_cast<const CUtensorMap*>(a.map_k);
     const CUtensorMap& mv = *static_cast<const CUtensorMap*>(a.map_v);
-    // the query matrix changes with every call: its map ([q_rows][Hq * D], one box = 64 columns x 128 rows) is encoded here
+    // the query and output matrices change with every call: their maps ([q_rows][Hq * D], one box = 64 columns x 128 rows) is encoded here
     // and travels to the kernel by value
     if ((reinterpret_cast<uintptr_t>(a.q) & 15u) != 0 || (reinterpret_cast<uintptr_t>(a.out) & 15u) != 0 || a.q_rows == 0)
         return cudaErrorInvalidValue;
-    alignas(64) CUtensorMap mq;
-    const cudaError_t e = encode_rows_map(const_cast<void*>(a.q), a.q_rows, a.num_q_heads * head_dim, uint32_t(kriya::kQTile), &mq);
+    alignas(64) CUtensorMap mq, mo;
+    cudaError_t e = encode_rows_map(const_cast<void*>(a.q), a.q_rows, a.num_q_heads * head_dim, uint32_t(kriya::kQTile), &mq);
+    if (e == cudaSuccess) e = encode_rows_map(a.out, a.q_rows, a.num_q_heads * head_dim, uint32_t(kriya::kQTile), &mo);
     if (e != cudaSuccess) return e;
     using namespace kriya;
     if (head_dim == 128)
-        return dtype == KRIYA_DTYPE_FP16 ? launch_prefill_t<128, Fp16>(a, mk, mv, mq, max_smem_optin, s)
-                                         : launch_prefill_t<128, Bf16>(a, mk, mv, mq, max_smem_optin, s);
-    return dtype == KRIYA_DTYPE_FP16 ? launch_prefill_t<64, Fp16>(a, mk, mv, mq, max_smem_optin, s)
-                                     : launch_prefill_t<64, Bf16>(a, mk, mv, mq, max_smem_optin, s);
+        return dtype == KRIYA_DTYPE_FP16 ? launch_prefill_t<128, Fp16>(a, mk, mv, mq, mo, max_smem_optin, s)
+                                         : launch_prefill_t<128, Bf16>(a, mk, mv, mq, mo, max_smem_optin, s);
+    return dtype == KRIYA_DTYPE_FP16 ? launch_prefill_t<64, Fp16>(a, mk, mv, mq, mo, max_smem_optin, s)
+                                     : launch_prefill_t<64, Bf16>(a, mk, mv, mq, mo, max_smem_optin, s);
 }

@@ -73,6 +73,17 @@ __device__ __forceinline__ void tma_load_2d(void* dst_smem, const CUtensorMap* m
         : "memory");
 }
 
+// Tensor store shared -> global of one box (x a multiple of 8 elements for 16-bit data, y not negative), tracked by
+// the issuing thread's bulk group.  The part of the box outside the tensor is not written.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* src_smem, int32_t x, int32_t y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];" ::"l"(map), "r"(x), "r"(y),
+                 "r"(smem_u32(src_smem))
+                 : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_map(const CUtensorMap* map) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
+
 // Shared-memory matrix descriptor, 128-byte swizzle, descriptor version 1 (sm_100).
 //   K-major operand  : rows of 128 bytes (64 elements of K), 8-row groups `sbo` bytes apart.
 //   MN-major operand : 128-byte rows hold 64 elements of M/N for one k; 8-k groups `sbo` bytes apart,
