@@ -65,11 +65,7 @@ struct PrefillParams {
     uint32_t pairs;    // head pairs per KV head = ceil(group / 2)
 };
 
-// Bulk copy shared -> global (both 16-byte aligned, size a multiple of 16), tracked by the thread's bulk group.
-__device__ __forceinline__ void bulk_s2g(void* dst_gmem, const void* src_smem, uint32_t bytes) {
-    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst_gmem), "r"(smem_u32(src_smem)), "r"(bytes)
-                 : "memory");
-}
+// Closes the thread's bulk group (tensor stores) and waits until their source has been read.
 __device__ __forceinline__ void bulk_commit_wait_read() {
     asm volatile("cp.async.bulk.commit_group;" ::: "memory");
     asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
@@ -452,10 +448,12 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
             if (ok) {
                 tc_fence_after();
                 const float inv_l = 1.0f / fmaxf(l_run, 1e-12f);
-                // The output tile goes through shared memory in the layout of the query tile it replaces (every S MMA is
-                // complete once pv_done[x] has fired): a full tile leaves with one tensor store per 64-column panel, a
-                // partial one row by row, since a tensor store would also write the rows of the next sequence.
+                // A full tile goes through shared memory in the layout of the query tile it replaces (every S MMA is
+                // complete once pv_done[x] has fired) and leaves with one tensor store per 64-column panel.  A partial
+                // tile is written row by row from registers: a tensor store would also write the next sequence's rows.
+                const bool full = tile_rows == uint32_t(kQTile);
                 uint8_t* stage = sQ + x * Q_BYTES;
+                uint16_t* og = reinterpret_cast<uint16_t*>(a.out) + (size_t(tile_start + row) * a.num_q_heads + head0 + x) * D;
 #pragma unroll 1
                 for (int c = 0; c < D / 32; ++c) {
                     uint32_t r[32];
@@ -467,14 +465,17 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
 #pragma unroll
                         for (int i = 0; i < 4; ++i)
                             w[i] = T::pack2(__uint_as_float(r[q4 * 8 + 2 * i]) * inv_l, __uint_as_float(r[q4 * 8 + 2 * i + 1]) * inv_l);
+                        const uint4 val = make_uint4(w[0], w[1], w[2], w[3]);
                         const uint32_t chunk = uint32_t(c & 1) * 4u + uint32_t(q4);  // 16-byte chunk inside the 64-column panel
-                        *reinterpret_cast<uint4*>(stage + uint32_t(c >> 1) * PANEL_BYTES + row * 128u + ((chunk ^ (row & 7u)) << 4)) =
-                            make_uint4(w[0], w[1], w[2], w[3]);
+                        if (full)
+                            *reinterpret_cast<uint4*>(stage + uint32_t(c >> 1) * PANEL_BYTES + row * 128u + ((chunk ^ (row & 7u)) << 4)) = val;
+                        else if (row < tile_rows)
+                            *reinterpret_cast<uint4*>(og + c * 32 + q4 * 8) = val;
                     }
                 }
                 if (tid == 0) PTR(2, 31, 6);
-                fence_async_smem();
-                if (tile_rows == uint32_t(kQTile)) {
+                if (full) {
+                    fence_async_smem();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&o_staged[x]);
                     if (row == 0 && mbar_wait(&o_staged[x], 0u)) {  // bounded: the group's 128 rows are in place
@@ -482,12 +483,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
                         for (int p = 0; p < PANELS; ++p)
                             tma_store_2d(&map_o, stage + p * PANEL_BYTES, int32_t(head0 + x) * D + p * 64, int32_t(tile_start));
                     }
-                } else if (row < tile_rows) {
-                    // swizzled row: chunk c of the row sits at position c ^ (row & 7) of its 128-byte line
-                    uint16_t* og = reinterpret_cast<uint16_t*>(a.out) + (size_t(tile_start + row) * a.num_q_heads + head0 + x) * D;
-#pragma unroll
-                    for (int c = 0; c < D / 8; ++c)
-                        bulk_s2g(og + c * 8, stage + uint32_t(c >> 3) * PANEL_BYTES + row * 128u + (((uint32_t(c) & 7u) ^ (row & 7u)) << 4), 16);
                 }
                 if (tid == 0) PTR(2, 31, 7);
                 bulk_commit_wait_read();  // the tile must have been read before the CTA gives its shared memory back
