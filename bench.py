@@ -63,14 +63,21 @@ class ClockSampler:
     def __init__(self, gpu_index: int):
         self.gpu_index = gpu_index
         self.proc = None
-        self.lines = []
+        self.lines = []  # (arrival time, text)
         self.thread = None
+        self.t0 = self.t1 = None
+
+    def mark_start(self):
+        self.t0 = time.perf_counter()
+
+    def mark_end(self):
+        self.t1 = time.perf_counter()
 
     def start(self):
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "10"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
             return
@@ -79,7 +86,7 @@ class ClockSampler:
 
     def _pump(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.perf_counter(), line.strip()))
 
     def stop(self):
         if self.proc is None:
@@ -89,8 +96,14 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except Exception:
             pass
+        # nvidia-smi is started before the warm-up (it takes tens of ms to print its first line); only the samples that
+        # arrived inside the timed region count.  A region too short to hold one falls back to every sample of the run.
+        inside = [ln for (t, ln) in self.lines if self.t0 is not None and self.t1 is not None and self.t0 <= t <= self.t1]
+        window = "timed region"
+        if not inside:
+            inside, window = [ln for (_, ln) in self.lines], "warm-up + timed region"
         sm, mx, reasons = [], None, set()
-        for ln in self.lines:
+        for ln in inside:
             parts = [p.strip() for p in ln.split(",")]
             if len(parts) < 8:
                 continue
@@ -103,7 +116,7 @@ class ClockSampler:
                 if val.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
-                "samples": len(sm)}
+                "samples": len(sm), "window": window}
 
 
 def contexts_for_rank(rank: int) -> np.ndarray:
@@ -274,6 +287,8 @@ def run_gpu_arm(args):
     mgr = fresh_manager()
     attended = []
     ex.timing_enable(False)
+    sampler = ClockSampler(local_rank)
+    sampler.start()
     for t in range(args.warmup):
         plan, pos = step_plan(mgr, t)
         ex.upload_schedule_plan(plan, pos)
@@ -281,8 +296,7 @@ def run_gpu_arm(args):
     ex.sync()
     barrier()
     torch.cuda.synchronize()
-    sampler = ClockSampler(local_rank)
-    sampler.start()
+    sampler.mark_start()
     launches0 = ex.launch_count
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ev0.record(stream)
@@ -294,6 +308,7 @@ def run_gpu_arm(args):
     ev1.record(stream)
     ex.sync()
     torch.cuda.synchronize()
+    sampler.mark_end()
     barrier()
     clocks = sampler.stop()
     elapsed_ms = ev0.elapsed_time(ev1)
