@@ -292,6 +292,36 @@ int32_t kriya_cuda_paged_gqa_decode_static(int32_t device, void* stream, uint32_
                                            uint32_t rows, void* out_dev, const kriya_bsr_gqa_params* params, char* err,
                                            size_t err_len);
 
+/* TreeVerifyGqaParams (crates/kriya-backend-metal/src/encoder.rs:189-200; kernels/metal/paged_gqa_and_deltanet.metal:1604-1613),
+ * byte-identical, 32 bytes. */
+typedef struct kriya_tree_verify_params {
+    uint32_t num_tree_nodes;    /* e.g. 11: the root and ten drafted nodes */
+    uint32_t num_q_heads;
+    uint32_t num_kv_heads;
+    uint32_t head_dim;
+    uint32_t block_size_tokens;
+    uint32_t prefix_kv_blocks;  /* blocks of cached context before the draft tree */
+    uint32_t prefix_last_len;   /* valid tokens in the last of them */
+    float sm_scale;
+} kriya_tree_verify_params;
+
+/* apply_rope_inplace (paged_gqa_and_deltanet.metal:1738-1829; dispatch enc:3258-3306): optional QK RMS norm and RoPE of
+ * q [num_tokens][Hq][D] and k [num_tokens][Hkv][D] where they are; nothing is written to the cache.  Positions are the
+ * ones uploaded with the current plan (num_tokens of them). */
+int32_t kriya_cuda_rope_inplace(kriya_cuda_ctx* ctx, void* q_inout_dev, void* k_inout_dev, const void* q_norm_w_dev,
+                                const void* k_norm_w_dev, uint32_t num_tokens, const kriya_rope_kv_write_params* params);
+
+/* bsr_paged_gqa_tree_verify (paged_gqa_and_deltanet.metal:1620-1729; dispatch enc:3308-3345): every node i of a draft tree
+ * attends the cached prefix and the in-flight K/V of the tree nodes j with tree_mask[i * n + j] != 0, in one call.
+ * tree_q / tree_out are [n][Hq][D], tree_k / tree_v [n][Hkv][D] (q and k already rotated), tree_mask_host is n * n bytes
+ * of host memory.  The prefix comes from the current plan: it must have exactly n rows, every row the sequence's
+ * prefix table (prefix_kv_blocks blocks, last_page_len = prefix_last_len; build_schedule_plan with the sequence id
+ * repeated n times) - the reference reads one table for all nodes, here each node is a decode row over the same
+ * blocks.  prefix_kv_blocks = 0 verifies a tree without cached context.  At most 128 nodes. */
+int32_t kriya_cuda_tree_verify(kriya_cuda_ctx* ctx, uint32_t layer, const void* tree_q_dev, const void* tree_k_dev,
+                               const void* tree_v_dev, const uint8_t* tree_mask_host, void* tree_out_dev,
+                               const kriya_tree_verify_params* params);
+
 /* Number of kernels this library has launched on `ctx` since creation (for launch accounting). */
 uint64_t kriya_cuda_launch_count(const kriya_cuda_ctx* ctx);
 

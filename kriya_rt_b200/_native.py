@@ -40,6 +40,12 @@ class BsrGqaParams(C.Structure):  # crates/kriya-backend-metal/src/encoder.rs:17
                 ("max_query_tokens", C.c_uint32), ("sm_scale", C.c_float), ("logit_softcap", C.c_float)]
 
 
+class TreeVerifyParams(C.Structure):  # crates/kriya-backend-metal/src/encoder.rs:189-200
+    _fields_ = [("num_tree_nodes", C.c_uint32), ("num_q_heads", C.c_uint32), ("num_kv_heads", C.c_uint32),
+                ("head_dim", C.c_uint32), ("block_size_tokens", C.c_uint32), ("prefix_kv_blocks", C.c_uint32),
+                ("prefix_last_len", C.c_uint32), ("sm_scale", C.c_float)]
+
+
 class KvPlanView(C.Structure):
     _fields_ = [("page_indptr", C.POINTER(C.c_int32)), ("page_indptr_len", C.c_size_t),
                 ("page_indices", C.POINTER(C.c_int32)), ("page_indices_len", C.c_size_t),
@@ -138,6 +144,8 @@ CUDA_SYMBOLS = {
                                                        _VP, _VP, C.c_uint32, _VP, C.POINTER(BsrGqaParams), C.c_char_p,
                                                        C.c_size_t]),
     "kriya_cuda_launch_count": (C.c_uint64, [_VP]),
+    "kriya_cuda_rope_inplace": (C.c_int32, [_VP, _VP, _VP, _VP, _VP, C.c_uint32, C.POINTER(RopeKvWriteParams)]),
+    "kriya_cuda_tree_verify": (C.c_int32, [_VP, C.c_uint32, _VP, _VP, _VP, _VP, _VP, C.POINTER(TreeVerifyParams)]),
 }
 
 

@@ -2,7 +2,8 @@
 // kernels/metal/paged_gqa_and_deltanet.metal:115-226).
 //
 // One warp per (token, head): query heads are rotated in place, key heads are rotated into their
-// cache slot, value heads are copied bit for bit.  The arithmetic keeps the reference's operation
+// cache slot, value heads are copied bit for bit.  The in-place mode is apply_rope_inplace
+// (paged_gqa_and_deltanet.metal:1738-1829): keys are rotated where they are and nothing touches the cache.  The arithmetic keeps the reference's operation
 // order (fma(x0, c, -x1*s), fma(x0, s, x1*c), round-to-nearest-even on store) so that with the
 // precomputed cos/sin table the cache contents are bit-identical to a host evaluation.
 //
@@ -31,7 +32,9 @@ __global__ void __launch_bounds__(kAppendWarps * 32) append_kernel(KriyaAppendAr
     const uint16_t* src = is_q ? q_row : k_row;
 
     uint32_t position, blk = 0, slot = 0;
-    if (a.chunk_mode) {
+    if (a.inplace) {
+        position = a.positions[r];  // apply_rope_inplace: no cache slot, keys are rotated where they are
+    } else if (a.chunk_mode) {
         position = a.prefix_tokens + r;
         if (!is_q) {
             blk = uint32_t(a.indices[a.indptr[0] + int32_t(position / a.p.block_size_tokens)]);
@@ -44,7 +47,7 @@ __global__ void __launch_bounds__(kAppendWarps * 32) append_kernel(KriyaAppendAr
             slot = uint32_t(a.last_len[r] - 1);
         }
     }
-    if (!is_q && (blk >= a.num_blocks || slot >= a.p.block_size_tokens)) {
+    if (!is_q && !a.inplace && (blk >= a.num_blocks || slot >= a.p.block_size_tokens)) {
         if (lane == 0) atomicMax(a.status, blk >= a.num_blocks ? KRIYA_DEV_BAD_BLOCK_INDEX : KRIYA_DEV_BAD_SLOT);
         return;
     }
@@ -69,7 +72,9 @@ __global__ void __launch_bounds__(kAppendWarps * 32) append_kernel(KriyaAppendAr
     uint16_t* dst_k = nullptr;
     uint16_t* dst_v = nullptr;
     const uint16_t* v_row = nullptr;
-    if (!is_q) {
+    if (!is_q && a.inplace) {
+        dst_k = const_cast<uint16_t*>(k_row);
+    } else if (!is_q) {
         const size_t off = ((size_t(blk) * a.p.block_size_tokens + slot) * Hkv + lh) * D;
         dst_k = reinterpret_cast<uint16_t*>(a.cache_k) + off;
         dst_v = reinterpret_cast<uint16_t*>(a.cache_v) + off;
@@ -108,8 +113,10 @@ __global__ void __launch_bounds__(kAppendWarps * 32) append_kernel(KriyaAppendAr
         } else {
             dst_k[d0] = T::store(x0);
             dst_k[d1] = T::store(x1);
-            dst_v[d0] = v_row[d0];
-            dst_v[d1] = v_row[d1];
+            if (dst_v != nullptr) {
+                dst_v[d0] = v_row[d0];
+                dst_v[d1] = v_row[d1];
+            }
         }
     }
 }

@@ -46,6 +46,7 @@ void destroy(kriya_cuda_ctx* c) {
     cudaFree(c->d_status);
     cudaFree(c->d_act);
     cudaFree(c->d_pairs);
+    cudaFree(c->d_tree_state);
     cudaFree(c->d_step);
     for (cudaEvent_t e : c->ev_pool) cudaEventDestroy(e);
     for (int i = 0; i < 2; ++i) {
@@ -491,6 +492,7 @@ int32_t kriya_cuda_ctx_create(const kriya_cuda_config* cfg_in, kriya_cuda_ctx** 
     CREATE_TRY(cudaMalloc(&c->d_act, c->act_bytes));
     CREATE_TRY(cudaMallocHost(&c->h_act, c->act_bytes));
     CREATE_TRY(cudaMalloc(&c->d_pairs, size_t(c->cap_pairs) * 3 * sizeof(uint32_t)));
+    CREATE_TRY(cudaMalloc(&c->d_tree_state, size_t(kTreeMaxNodes) * c->cfg.num_q_heads * (c->cfg.head_dim + 2) * sizeof(float)));
     CREATE_TRY(cudaMallocHost(&c->h_pairs, size_t(c->cap_pairs) * 3 * sizeof(uint32_t)));
     CREATE_TRY(cudaEventCreateWithFlags(&c->h_pairs_free, cudaEventDisableTiming));
     CREATE_TRY(cudaStreamSynchronize(c->stream));
@@ -696,6 +698,109 @@ int32_t kriya_cuda_rope_kv_append_chunk(kriya_cuda_ctx* c, uint32_t layer, void*
                                                      std::to_string(c->row0_blocks) + " blocks");
     cudaSetDevice(c->cfg.device);
     return launch_append(c, layer, q, k, v, qw, kw, num_tokens, 1, prefix_tokens, p);
+}
+
+int32_t kriya_cuda_rope_inplace(kriya_cuda_ctx* c, void* q, void* k, const void* qw, const void* kw, uint32_t num_tokens,
+                                const kriya_rope_kv_write_params* p) {
+    if (!c) return KRIYA_CUDA_INVALID_INPUT;
+    if (int32_t rc = check_rope(c, p)) return rc;
+    if (!c->plan_valid) return c->fail(KRIYA_CUDA_INVALID_INPUT, "no plan uploaded");
+    if (num_tokens == 0) return c->fail(KRIYA_CUDA_INVALID_INPUT, "input_tokens must not be empty");
+    if (!q || !k) return c->fail(KRIYA_CUDA_INVALID_INPUT, "q and k must not be null");
+    if (p->apply_qk_norm && (!qw || !kw)) return c->fail(KRIYA_CUDA_INVALID_INPUT, "apply_qk_norm needs both norm weights");
+    if (num_tokens != c->n_positions)
+        return c->fail(KRIYA_CUDA_INVALID_INPUT, "input_tokens has " + std::to_string(num_tokens) +
+                                                     " entries but seq_positions has " + std::to_string(c->n_positions));
+    cudaSetDevice(c->cfg.device);
+    KriyaAppendArgs a{};
+    a.q_inout = q;
+    a.k_in = k;
+    a.q_norm_w = qw;
+    a.k_norm_w = kw;
+    a.positions = c->plan_dev<uint32_t>(c->off_positions);
+    a.table = table_for(c, p);
+    a.status = c->d_status;
+    a.num_tokens = num_tokens;
+    a.num_blocks = c->cfg.num_kv_blocks;
+    a.inplace = 1;
+    a.p = *p;
+    KRIYA_CUDA_TRY(c, kriya_launch_append(a, c->cfg.dtype, c->stream));
+    c->launches += 1;
+    return KRIYA_CUDA_OK;
+}
+
+int32_t kriya_cuda_tree_verify(kriya_cuda_ctx* c, uint32_t layer, const void* tq, const void* tk, const void* tv,
+                               const uint8_t* mask, void* out, const kriya_tree_verify_params* p) {
+    if (!c) return KRIYA_CUDA_INVALID_INPUT;
+    if (int32_t rc = check_layer(c, layer)) return rc;
+    if (!p) return c->fail(KRIYA_CUDA_INVALID_INPUT, "params must not be null");
+    if (p->num_q_heads != c->cfg.num_q_heads || p->num_kv_heads != c->cfg.num_kv_heads || p->head_dim != c->cfg.head_dim ||
+        p->block_size_tokens != c->cfg.block_size_tokens)
+        return c->fail(KRIYA_CUDA_INVALID_INPUT, "tree-verify params do not match the context's attention shape");
+    if (!tq || !tk || !tv || !mask || !out) return c->fail(KRIYA_CUDA_INVALID_INPUT, "tree q, k, v, mask and out must not be null");
+    const uint32_t n = p->num_tree_nodes;
+    if (n == 0) return c->fail(KRIYA_CUDA_INVALID_INPUT, "input_tokens must not be empty");
+    if (n > kTreeMaxNodes) return c->fail(KRIYA_CUDA_INVALID_INPUT, "a draft tree may hold at most 128 nodes");
+    if (c->cfg.head_dim != 64 && c->cfg.head_dim != 128)
+        return c->fail(KRIYA_CUDA_UNSUPPORTED, "tree verification covers head_dim 64/128");
+    const bool has_prefix = p->prefix_kv_blocks > 0;
+    if (has_prefix) {
+        if (p->prefix_last_len == 0 || p->prefix_last_len > p->block_size_tokens)
+            return c->fail(KRIYA_CUDA_INVALID_INPUT, "prefix_last_len must be in 1..=block_size_tokens");
+        if (!c->plan_valid || c->n_rows != n)
+            return c->fail(KRIYA_CUDA_INVALID_INPUT, "tree verification over a cached prefix needs a plan with one row per tree node");
+        const int32_t* indptr = reinterpret_cast<const int32_t*>(c->h_plan_last + c->off_indptr);
+        const int32_t* last = reinterpret_cast<const int32_t*>(c->h_plan_last + c->off_last_len);
+        for (uint32_t r = 0; r < n; ++r)
+            if (uint32_t(indptr[r + 1] - indptr[r]) != p->prefix_kv_blocks || uint32_t(last[r]) != p->prefix_last_len)
+                return c->fail(KRIYA_CUDA_INVALID_INPUT, "plan row " + std::to_string(r) + " does not describe the prefix (" +
+                                                             std::to_string(p->prefix_kv_blocks) + " blocks, last length " +
+                                                             std::to_string(p->prefix_last_len) + ")");
+        if (!use_tc_decode(c) && !kriya_decode_supported(c->cfg.head_dim, c->cfg.num_q_heads / c->cfg.num_kv_heads,
+                                                         c->cfg.num_kv_heads, c->cfg.block_size_tokens))
+            return c->fail(KRIYA_CUDA_UNSUPPORTED,
+                           "decode kernels cover head_dim 64/128, group size 1..8, 16-token blocks (head_dim 64: up to 8 KV heads)");
+    }
+    cudaSetDevice(c->cfg.device);
+    // the mask goes through the pinned staging buffer the copy lists use
+    KRIYA_CUDA_TRY(c, cudaEventSynchronize(c->h_pairs_free));
+    memcpy(c->h_pairs, mask, size_t(n) * n);
+    KRIYA_CUDA_TRY(c, cudaMemcpyAsync(c->d_pairs, c->h_pairs, size_t(n) * n, cudaMemcpyHostToDevice, c->stream));
+    KRIYA_CUDA_TRY(c, cudaEventRecord(c->h_pairs_free, c->stream));
+    const size_t R = size_t(n) * c->cfg.num_q_heads;
+    float* st_m = c->d_tree_state;
+    float* st_l = st_m + R;
+    float* st_o = st_l + R;
+    if (has_prefix) {
+        // part A: every node is a decode row over the same prefix blocks; the state is left un-normalised
+        kriya_bsr_gqa_params g{};
+        g.num_q_heads = p->num_q_heads;
+        g.num_kv_heads = p->num_kv_heads;
+        g.head_dim = p->head_dim;
+        g.block_size_tokens = p->block_size_tokens;
+        g.max_split_k_tiles = 1;
+        g.max_query_tokens = n;
+        g.sm_scale = p->sm_scale;
+        g.logit_softcap = 0.0f;
+        if (int32_t rc = launch_decode(c, layer, tq, nullptr, st_m, st_l, st_o, false, c->n_work, &g)) return rc;
+    }
+    KriyaTreeArgs a{};
+    a.q = tq;
+    a.k = tk;
+    a.v = tv;
+    a.mask = reinterpret_cast<const uint8_t*>(c->d_pairs);
+    a.st_m = st_m;
+    a.st_l = st_l;
+    a.st_o = st_o;
+    a.out = out;
+    a.n_nodes = n;
+    a.num_q_heads = c->cfg.num_q_heads;
+    a.num_kv_heads = c->cfg.num_kv_heads;
+    a.has_prefix = has_prefix ? 1u : 0u;
+    a.sm_scale = p->sm_scale;
+    KRIYA_CUDA_TRY(c, kriya_launch_tree_finish(a, c->cfg.head_dim, c->cfg.dtype, c->stream));
+    c->launches += 1;
+    return KRIYA_CUDA_OK;
 }
 
 int32_t kriya_cuda_paged_gqa_decode(kriya_cuda_ctx* c, uint32_t layer, const void* q, void* out,

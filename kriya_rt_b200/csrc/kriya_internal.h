@@ -112,6 +112,7 @@ struct kriya_cuda_ctx {
     uint32_t* d_pairs = nullptr;  // copy pairs / slot triples
     uint32_t* h_pairs = nullptr;
     uint32_t cap_pairs = 0;
+    float* d_tree_state = nullptr;  // [kTreeMaxNodes * Hq * (D + 2)] prefix states of a tree verification
     cudaEvent_t h_pairs_free = nullptr;
 
     // staging for whole-step host calls (grown on demand by kriya_cuda_decode_step_host)
@@ -143,6 +144,8 @@ struct kriya_cuda_ctx {
 
 // ---- kernel launchers (one per translation unit) ---------------------------------------------
 
+constexpr uint32_t kTreeMaxNodes = 128;
+
 struct KriyaAppendArgs {
     void* q_inout;
     const void* k_in;
@@ -162,6 +165,7 @@ struct KriyaAppendArgs {
     // chunk mode: token i of row 0 at absolute position prefix + i (plan rows are not per token)
     uint32_t chunk_mode;
     uint32_t prefix_tokens;
+    uint32_t inplace;  // rotate q and k where they are (k_in is written); v and the cache are not touched
     kriya_rope_kv_write_params p;
 };
 cudaError_t kriya_launch_append(const KriyaAppendArgs& a, uint32_t dtype, cudaStream_t s);
@@ -261,6 +265,25 @@ struct KriyaPrefillArgs {
     float sm_scale;
     float logit_softcap;
 };
+// Tree verification: attention of every draft-tree node over its ancestors in the tree (in-flight K/V, `mask`), started
+// from the state (m, l, o) of the node's attention over the cached prefix.
+struct KriyaTreeArgs {
+    const void* q;        // [nodes][Hq][D], rotated
+    const void* k;        // [nodes][Hkv][D], rotated
+    const void* v;        // [nodes][Hkv][D]
+    const uint8_t* mask;  // [nodes][nodes], 1 = node j is visible to node i
+    const float* st_m;    // [nodes * Hq] prefix state, ignored when has_prefix == 0
+    const float* st_l;
+    const float* st_o;    // [nodes * Hq][D]
+    void* out;            // [nodes][Hq][D]
+    uint32_t n_nodes;
+    uint32_t num_q_heads;
+    uint32_t num_kv_heads;
+    uint32_t has_prefix;
+    float sm_scale;
+};
+cudaError_t kriya_launch_tree_finish(const KriyaTreeArgs& a, uint32_t head_dim, uint32_t dtype, cudaStream_t s);
+
 cudaError_t kriya_launch_prefill(const KriyaPrefillArgs& a, uint32_t head_dim, uint32_t block_size, uint32_t dtype,
                                  int max_smem_optin, cudaStream_t s);
 bool kriya_prefill_supported(uint32_t head_dim, uint32_t group, uint32_t block_size, uint32_t dtype);

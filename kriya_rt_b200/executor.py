@@ -14,7 +14,7 @@ from typing import Optional, Sequence
 import numpy as np
 
 from . import _native as N
-from ._native import BsrGqaParams, RopeKvWriteParams
+from ._native import BsrGqaParams, RopeKvWriteParams, TreeVerifyParams
 
 DTYPE_BF16, DTYPE_FP16 = 0, 1
 
@@ -153,6 +153,28 @@ class CudaExecutor:
         self._check(self._lib.kriya_cuda_rope_kv_append_chunk(
             self._h, layer, _ptr(q_inout), _ptr(k_in), _ptr(v_in), _ptr(q_norm_w), _ptr(k_norm_w), prefix_tokens,
             num_tokens, C.byref(params)))
+
+    def rope_inplace(self, q_inout, k_inout, num_tokens: int, params: RopeKvWriteParams, q_norm_w=None,
+                     k_norm_w=None) -> None:
+        """apply_rope_inplace (paged_gqa_and_deltanet.metal:1738-1829): q and k rotated where they are, positions of the plan."""
+        self._check(self._lib.kriya_cuda_rope_inplace(self._h, _ptr(q_inout), _ptr(k_inout), _ptr(q_norm_w), _ptr(k_norm_w),
+                                                      num_tokens, C.byref(params)))
+
+    def tree_verify_params(self, num_tree_nodes: int, prefix_tokens: int, sm_scale: Optional[float] = None) -> TreeVerifyParams:
+        """TreeVerifyGqaParams for a prefix of `prefix_tokens` cached tokens (enc:3313-3326)."""
+        bs = self.block_size_tokens
+        blocks = (prefix_tokens + bs - 1) // bs
+        last = prefix_tokens - (blocks - 1) * bs if blocks else 0
+        scale = float(sm_scale) if sm_scale is not None else 1.0 / float(np.sqrt(self.head_dim))
+        return TreeVerifyParams(num_tree_nodes, self.num_q_heads, self.num_kv_heads, self.head_dim, bs, blocks, last, scale)
+
+    def tree_verify(self, layer: int, tree_q, tree_k, tree_v, tree_mask, tree_out, params: TreeVerifyParams) -> None:
+        """bsr_paged_gqa_tree_verify (metal:1620-1729): the plan holds one row per tree node, each the prefix table."""
+        mask = np.ascontiguousarray(tree_mask, np.uint8)
+        if mask.size != params.num_tree_nodes ** 2:
+            raise ValueError("tree_mask must hold num_tree_nodes x num_tree_nodes bytes")
+        self._check(self._lib.kriya_cuda_tree_verify(self._h, layer, _ptr(tree_q), _ptr(tree_k), _ptr(tree_v),
+                                                     mask.ctypes.data, _ptr(tree_out), C.byref(params)))
 
     def paged_gqa_decode(self, layer: int, q, out, params: BsrGqaParams) -> None:
         self._check(self._lib.kriya_cuda_paged_gqa_decode(self._h, layer, _ptr(q), _ptr(out), C.byref(params)))

@@ -30,6 +30,12 @@ class GqaParams(C.Structure):
                 ("max_query_tokens", C.c_uint32), ("sm_scale", C.c_float), ("logit_softcap", C.c_float)]
 
 
+class TreeParams(C.Structure):
+    _fields_ = [("num_tree_nodes", C.c_uint32), ("num_q_heads", C.c_uint32), ("num_kv_heads", C.c_uint32),
+                ("head_dim", C.c_uint32), ("block_size_tokens", C.c_uint32), ("prefix_kv_blocks", C.c_uint32),
+                ("prefix_last_len", C.c_uint32), ("sm_scale", C.c_float)]
+
+
 def _cpu_stamp() -> str:
     """The library is built with -march=native, so it is only valid on the CPU model it was built on."""
     try:
@@ -194,6 +200,20 @@ def prefill_causal(q, cache_k, cache_v, table, prefix_tokens: int, params: GqaPa
     outf = np.empty(q.shape, np.float32)
     lib().ko_prefill_causal(_p(q), _p(_u16(cache_k)), _p(_u16(cache_v)), _p(table), C.c_uint32(prefix_tokens),
                             C.c_uint32(q.shape[0]), _p(out), _p(outf), C.byref(params), dtype)
+    return out, outf
+
+
+def tree_verify(tree_q, tree_k, tree_v, cache_k, cache_v, page_indices, tree_mask, params: TreeParams, dtype: int):
+    """bsr_paged_gqa_tree_verify: returns (out 16-bit, out fp32), both [nodes, Hq, D]."""
+    tree_q = _u16(tree_q)
+    idx = np.ascontiguousarray(page_indices, np.int32)
+    if idx.size == 0:
+        idx = np.zeros(1, np.int32)
+    mask = np.ascontiguousarray(tree_mask, np.uint8)
+    out = np.empty(tree_q.shape, np.uint16)
+    outf = np.empty(tree_q.shape, np.float32)
+    lib().ko_tree_verify(_p(tree_q), _p(_u16(tree_k)), _p(_u16(tree_v)), _p(_u16(cache_k)), _p(_u16(cache_v)), _p(idx),
+                         _p(mask), _p(out), _p(outf), C.byref(params), dtype)
     return out, outf
 
 

@@ -452,6 +452,76 @@ KO_EXPORT void ko_merge_states(const float* m, const float* l, const float* o, u
     }
 }
 
+/* ---- speculative tree verification ------------------------------------------- */
+
+typedef struct {
+    uint32_t num_tree_nodes, num_q_heads, num_kv_heads, head_dim, block_size_tokens, prefix_kv_blocks, prefix_last_len;
+    float sm_scale;
+} ko_tree_params; /* TreeVerifyGqaParams, 32 bytes (enc:189-200, metal:1604-1613) */
+
+/* One warp of bsr_paged_gqa_tree_verify (metal:1620-1729): lane l holds elements 4l..4l+3 (those below D), the score is
+ * the butterfly sum of the lanes' fma chains, the recurrence uses plain exp (this kernel has no clamp), part A walks the
+ * prefix pages of `page_indices`, part B the tree nodes the mask lets node i see.  The reference's own tests do not
+ * cover this kernel: its parity is pinned by this restatement and by its agreement with the causal prefill when the
+ * mask is lower-triangular (tests/test_oracle_numerics.py). */
+KO_EXPORT void ko_tree_verify(const uint16_t* tree_q, const uint16_t* tree_k, const uint16_t* tree_v,
+                              const uint16_t* cache_k, const uint16_t* cache_v, const int32_t* page_indices,
+                              const uint8_t* tree_mask, uint16_t* tree_out, float* out_f32, const ko_tree_params* p,
+                              int dtype) {
+    const uint32_t N = p->num_tree_nodes, Hq = p->num_q_heads, Hkv = p->num_kv_heads, D = p->head_dim;
+    const uint32_t G = Hq / Hkv, page = p->block_size_tokens;
+#pragma omp parallel for schedule(dynamic, 1)
+    for (int64_t job = 0; job < (int64_t)N * Hq; ++job) {
+        const uint32_t node = (uint32_t)(job / Hq), qh = (uint32_t)(job % Hq), kvh = qh / G;
+        const size_t q_base = ((size_t)node * Hq + qh) * D;
+        float q[128], o[128];
+        for (uint32_t d = 0; d < 128; ++d) {
+            q[d] = d < D ? load16(tree_q[q_base + d], dtype) * p->sm_scale : 0.0f; /* metal:1651-1654 */
+            o[d] = 0.0f;
+        }
+        float m = -INFINITY, l = 0.0f;
+        const uint32_t n_keys_prefix =
+            p->prefix_kv_blocks ? (p->prefix_kv_blocks - 1u) * page + p->prefix_last_len : 0u; /* metal:1662-1664 */
+        for (uint32_t key = 0; key < n_keys_prefix + N; ++key) {
+            const uint16_t *kr, *vr;
+            if (key < n_keys_prefix) { /* part A, metal:1660-1692 */
+                const uint32_t phys = (uint32_t)page_indices[key / page];
+                const size_t off = (((size_t)phys * page + key % page) * Hkv + kvh) * D;
+                kr = cache_k + off;
+                vr = cache_v + off;
+            } else { /* part B, metal:1695-1718 */
+                const uint32_t j = key - n_keys_prefix;
+                if (tree_mask[(size_t)node * N + j] == 0) continue;
+                const size_t off = ((size_t)j * Hkv + kvh) * D;
+                kr = tree_k + off;
+                vr = tree_v + off;
+            }
+            float lane[32];
+            for (uint32_t ln = 0; ln < 32; ++ln) {
+                float dot = 0.0f;
+                for (uint32_t i = 0; i < 4u; ++i) {
+                    const uint32_t d = ln * 4u + i;
+                    if (d < D) dot = fmaf(q[d], load16(kr[d], dtype), dot);
+                }
+                lane[ln] = dot;
+            }
+            const float score = simd_sum32(lane);
+            const float m_new = fmaxf(m, score);
+            const float alpha = expf(m - m_new);
+            const float beta = expf(score - m_new);
+            l = fmaf(l, alpha, beta);
+            for (uint32_t d = 0; d < D; ++d) o[d] = fmaf(o[d], alpha, beta * load16(vr[d], dtype));
+            m = m_new;
+        }
+        const float inv_l = 1.0f / fmaxf(l, 1e-12f);
+        for (uint32_t d = 0; d < D; ++d) {
+            const float val = o[d] * inv_l;
+            if (tree_out) tree_out[q_base + d] = store16(val, dtype);
+            if (out_f32) out_f32[q_base + d] = val;
+        }
+    }
+}
+
 /* ---- causal prefill over the paged cache ------------------------------------- */
 
 /* Query i of the chunk sits at absolute position prefix+i and attends cache positions

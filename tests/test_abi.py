@@ -69,3 +69,12 @@ def test_product_package_never_imports_the_oracle():
         assert "import oracle" not in src and "from oracle" not in src, py
     for cu in (ROOT / "kriya_rt_b200" / "csrc").iterdir():
         assert "oracle" not in cu.read_text().lower() or cu.suffix not in (".cu", ".cpp", ".h", ".cuh"), cu
+
+
+def test_tree_verify_params_are_32_bytes():
+    """TreeVerifyGqaParams, crates/kriya-backend-metal/src/encoder.rs:189-200: 7 x u32 + f32."""
+    import ctypes as C
+    from kriya_rt_b200._native import TreeVerifyParams
+    from oracle.c_oracle import TreeParams
+    assert C.sizeof(TreeVerifyParams) == 32 and C.sizeof(TreeParams) == 32
+    assert TreeVerifyParams.sm_scale.offset == 28 and TreeVerifyParams.prefix_kv_blocks.offset == 20

@@ -200,3 +200,28 @@ def test_block_copy_and_slot_write_are_bytewise():
     sv = rng.integers(0, 65536, (4, 128), dtype=np.uint16)
     O.slot_write(ck[0], cv[0], sk, sv, 16, [(2, 3, 7), (0, 4, 15)])
     assert np.array_equal(ck[0, 3, 7].ravel(), sk[2]) and np.array_equal(cv[0, 4, 15].ravel(), sv[0])
+
+
+def test_tree_verify_with_a_chain_mask_is_causal_prefill():
+    """A draft 'tree' that is a chain (mask lower-triangular) over a cached prefix is the causal prefill of those tokens: the two
+    restatements (metal:1620-1729 and the prefill loop) must agree, which pins ko_tree_verify without a reference test."""
+    from kriya_rt_b200 import workloads as W
+    Hq, Hkv, D, dt = 6, 2, 64, W.BF16
+    rng = np.random.default_rng(11)
+    for prefix in (0, 5, 16, 77):
+        n = 9
+        nblk = (prefix + n + 15) // 16
+        table = rng.permutation(12)[:nblk].astype(np.int32)
+        ck = W.normal16(rng, (12, 16, Hkv, D), dt); cv = W.normal16(rng, (12, 16, Hkv, D), dt)
+        q = W.normal16(rng, (n, Hq, D), dt); k = W.normal16(rng, (n, Hkv, D), dt); v = W.normal16(rng, (n, Hkv, D), dt)
+        ck2, cv2 = ck.copy(), cv.copy()
+        for i in range(n):  # the chunk's K/V at positions prefix + i
+            pos = prefix + i
+            ck2[table[pos // 16], pos % 16] = k[i]
+            cv2[table[pos // 16], pos % 16] = v[i]
+        gp = O.GqaParams(Hq, Hkv, D, 16, 16, n, 1.0 / np.sqrt(D), 0.0)
+        _, want = O.prefill_causal(q, ck2, cv2, table, prefix, gp, dt)
+        pb = (prefix + 15) // 16
+        tp = O.TreeParams(n, Hq, Hkv, D, 16, pb, prefix - (pb - 1) * 16 if pb else 0, 1.0 / np.sqrt(D))
+        _, got = O.tree_verify(q, k, v, ck, cv, table[:pb], np.tril(np.ones((n, n), np.uint8)), tp, dt)
+        assert np.abs(got - want).max() <= 2e-6
