@@ -660,6 +660,41 @@ def run_kernel_case(args):
         print(json.dumps({"case": case, "launches": reps, "us_per_launch": us, "flop_per_launch": flop,
                           "tflops": flop / (us * 1e-6) / 1e12}))
         ex.close()
+    elif case == "tree_verify":
+        # Qwen2.5-3B shape: a draft tree of 11 nodes (root + 10) verified over a cached prefix of 4096 tokens, one layer
+        n, prefix, nb = 11, 4096, 512
+        ex = CudaExecutor(num_layers=1, num_kv_blocks=nb, block_size_tokens=16, num_q_heads=16, num_kv_heads=2, head_dim=128,
+                          rope_theta=1e6, max_batch_rows=32)
+        fill(ex, 1)
+        blocks = prefix // 16
+        table = np.random.default_rng(5).permutation(nb)[:blocks].astype(np.int32)
+        ex.plan_upload(np.arange(n + 1) * blocks, np.tile(table, n), [16] * n, seq_positions=np.full(n, prefix, np.uint32))
+        tq, tk, tv = rnd(n, 16, 128), rnd(n, 2, 128), rnd(n, 2, 128)
+        out = torch.zeros_like(tq)
+        mask = np.tril(np.ones((n, n), np.uint8))
+        tp = ex.tree_verify_params(n, prefix)
+        rp = ex.rope_params()
+        torch.cuda.synchronize()
+        stream = torch.cuda.ExternalStream(ex.stream_ptr)
+
+        def one():
+            ex.rope_inplace(tq, tk, n, rp)
+            ex.tree_verify(0, tq, tk, tv, mask, out, tp)
+
+        one(); one()
+        ex.sync()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(reps):
+            one()
+        e1.record(stream)
+        ex.sync()
+        us = e0.elapsed_time(e1) / reps * 1e3
+        kv_bytes = prefix * 2 * 2 * 128 * 2
+        print(json.dumps({"case": case, "nodes": n, "prefix_tokens": prefix, "launches_per_call": 3, "us_per_layer": us,
+                          "prefix_kv_bytes": kv_bytes, "kv_gbs_read_once": kv_bytes / (us * 1e-6) / 1e9,
+                          "note": "rope_inplace + prefix decode of 11 rows over the same blocks + draft-tree kernel; the 4 MB prefix stays in L2"}))
+        ex.close()
     elif case == "copy":
         layers, nb = 36, 2048
         ex = CudaExecutor(num_layers=layers, num_kv_blocks=nb, block_size_tokens=16, num_q_heads=16, num_kv_heads=2, head_dim=128)
@@ -690,7 +725,7 @@ def main():
     ap.add_argument("--serial-layers", action="store_true",
                     help="keep the layers' launches of a step strictly serialised (default: they may overlap at their edges)")
     ap.add_argument("--case-seqs", type=int, default=8, help="prompts in the prefill_batch kernel case")
-    ap.add_argument("--kernel-case", default=None, choices=["decode", "decode_fused", "decode_long", "prefill", "prefill_batch", "append", "copy", "kvsplit"],
+    ap.add_argument("--kernel-case", default=None, choices=["decode", "decode_fused", "decode_long", "prefill", "prefill_batch", "append", "copy", "kvsplit", "tree_verify"],
                     help="run a few launches of one kernel on a small case (for ncu), --steps = launches")
     args = ap.parse_args()
     if args.kernel_case:
