@@ -114,6 +114,16 @@ uint32_t build_work(const int32_t* indptr, uint32_t rows, const uint32_t* begin,
 // leftover pieces, so plain tile counts are used.  Returns the number of segment records, or UINT32_MAX when `cap`
 // is too small.  `ptr` receives ctas + 1 offsets into `out`.
 constexpr uint32_t kRunStartWeight = 0;
+// Fewest 128-token tiles a CTA of the tensor-core decode kernel is given before another CTA is brought in.
+uint32_t tc_min_tiles_per_cta() {
+    static const uint32_t v = [] {
+        const char* e = getenv("KRIYA_TC_MIN_TILES");
+        const int x = e ? atoi(e) : 8;
+        return uint32_t(x < 1 ? 1 : x);
+    }();
+    return v;
+}
+
 uint32_t build_tc_segments(const int32_t* indptr, const int32_t* last_len, uint32_t block_size, uint32_t rows, uint32_t hkv,
                            const uint32_t* begin, const uint32_t* end, uint32_t ctas, KriyaTcSeg* out, uint32_t cap,
                            uint32_t* ptr) {
@@ -125,6 +135,10 @@ uint32_t build_tc_segments(const int32_t* indptr, const int32_t* last_len, uint3
         const uint32_t e = end ? std::min(end[r], nb) : nb;
         if (e > b) total += uint64_t((e + TP - 1) / TP - b / TP + kRunStartWeight) * hkv;
     }
+    // A short plan is not spread over every CTA: a CTA that streams only a tile or two costs its start-up latency all
+    // the same, and every extra piece of a run is one more partial state for the run's merge to read.
+    const uint32_t all_ctas = ctas;
+    ctas = uint32_t(std::min<uint64_t>(ctas, std::max<uint64_t>(1, (total + tc_min_tiles_per_cta() - 1) / tc_min_tiles_per_cta())));
     uint32_t n = 0, slot = 0, cta = 0;
     uint64_t unit = 0;  // weight consumed so far
     auto cta_end = [&](uint32_t c) { return total * (c + 1) / ctas; };  // first unit NOT owned by cta c
@@ -167,7 +181,7 @@ uint32_t build_tc_segments(const int32_t* indptr, const int32_t* last_len, uint3
             for (uint32_t i = first; i < n; ++i) out[i].n_parts = n - first;
         }
     }
-    while (cta < ctas) ptr[++cta] = n;
+    while (cta < all_ctas) ptr[++cta] = n;
     return n;
 }
 
