@@ -259,6 +259,15 @@ int32_t kriya_cuda_decode_step_host(kriya_cuda_ctx* ctx, const void* q_host, con
                                     void* out_host, uint32_t rows, const kriya_rope_kv_write_params* rope,
                                     const kriya_bsr_gqa_params* gqa);
 
+/* The same step in two halves, so that the host can prepare the next step (block allocation, next plan, even its upload,
+ * which queues behind this step) while the GPU works: _begin queues the copies in, the layers and the copies back and
+ * returns; _end waits until out_host is complete (timeout_ms as for kriya_cuda_sync).  The host buffers must stay
+ * valid and untouched in between. */
+int32_t kriya_cuda_decode_step_host_begin(kriya_cuda_ctx* ctx, const void* q_host, const void* k_host, const void* v_host,
+                                          void* out_host, uint32_t rows, const kriya_rope_kv_write_params* rope,
+                                          const kriya_bsr_gqa_params* gqa);
+int32_t kriya_cuda_decode_step_host_end(kriya_cuda_ctx* ctx, uint32_t timeout_ms);
+
 /* Chooses between the two decode kernels, which compute the same result: 0 = by shape (tensor-core kernel for
  * head_dim 128, CUDA-core kernel otherwise), 1 = CUDA-core kernel, 2 = tensor-core kernel.  The reference picks
  * kernels by shape in the same way (enc:4262-4281); this switch exists so that tests can hold both to the oracle. */

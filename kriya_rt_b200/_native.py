@@ -137,6 +137,9 @@ CUDA_SYMBOLS = {
                                            C.POINTER(BsrGqaParams)]),
     "kriya_cuda_decode_step_host": (C.c_int32, [_VP, _VP, _VP, _VP, _VP, C.c_uint32, C.POINTER(RopeKvWriteParams),
                                                 C.POINTER(BsrGqaParams)]),
+    "kriya_cuda_decode_step_host_begin": (C.c_int32, [_VP, _VP, _VP, _VP, _VP, C.c_uint32, C.POINTER(RopeKvWriteParams),
+                                                C.POINTER(BsrGqaParams)]),
+    "kriya_cuda_decode_step_host_end": (C.c_int32, [_VP, C.c_uint32]),
     "kriya_cuda_set_decode_path": (C.c_int32, [_VP, C.c_int32]),
     "kriya_cuda_timing_enable": (C.c_int32, [_VP, C.c_int32]),
     "kriya_cuda_timing_read": (C.c_int32, [_VP, C.c_uint32, C.POINTER(C.c_uint64), C.POINTER(C.c_double)]),

@@ -411,8 +411,8 @@ int32_t kriya_cuda_ctx_create(const kriya_cuda_config* cfg_in, kriya_cuda_ctx** 
     CREATE_TRY(cudaStreamCreateWithFlags(&c->copy_stream_out, cudaStreamNonBlocking));
     CREATE_TRY(cudaEventCreateWithFlags(&c->ev_step_begin, cudaEventDisableTiming));
     CREATE_TRY(cudaEventCreateWithFlags(&c->ev_step_end, cudaEventDisableTiming));
-    c->ev_in.resize((cfg.num_layers + 3) / 4);
-    c->ev_done.resize((cfg.num_layers + 3) / 4);
+    c->ev_in.resize(4);
+    c->ev_done.resize(4);
     for (size_t i = 0; i < c->ev_in.size(); ++i) {
         CREATE_TRY(cudaEventCreateWithFlags(&c->ev_in[i], cudaEventDisableTiming));
         CREATE_TRY(cudaEventCreateWithFlags(&c->ev_done[i], cudaEventDisableTiming));
@@ -1138,9 +1138,9 @@ int32_t kriya_cuda_decode_step(kriya_cuda_ctx* c, void* q, const void* k, const 
     return decode_layers(c, 0, c->cfg.num_layers, true, q, k, v, out, rows, rope, gqa);
 }
 
-int32_t kriya_cuda_decode_step_host(kriya_cuda_ctx* c, const void* q_host, const void* k_host, const void* v_host,
-                                    void* out_host, uint32_t rows, const kriya_rope_kv_write_params* rope,
-                                    const kriya_bsr_gqa_params* gqa) {
+int32_t kriya_cuda_decode_step_host_begin(kriya_cuda_ctx* c, const void* q_host, const void* k_host, const void* v_host,
+                                          void* out_host, uint32_t rows, const kriya_rope_kv_write_params* rope,
+                                          const kriya_bsr_gqa_params* gqa) {
     if (!c) return KRIYA_CUDA_INVALID_INPUT;
     if (!q_host || !k_host || !v_host || !out_host) return c->fail(KRIYA_CUDA_INVALID_INPUT, "host buffers must not be null");
     if (!c->plan_valid) return c->fail(KRIYA_CUDA_INVALID_INPUT, "no plan uploaded");
@@ -1162,30 +1162,63 @@ int32_t kriya_cuda_decode_step_host(kriya_cuda_ctx* c, const void* q_host, const
     uint8_t* dk = dq + qb;
     uint8_t* dv = dk + kb;
     uint8_t* dout = dv + kb;
-    // Three-way pipeline over groups of layers: inputs of group g+1 travel host->device on one copy stream and the
-    // results of group g-1 travel back on another while group g computes, so the PCIe time hides behind the kernels.
-    const uint32_t group = 4, n_groups = (uint32_t(L) + group - 1) / group;
+    // Three-way pipeline: inputs travel host->device on one copy stream and results travel back on another while the
+    // layers compute.  A layer's inputs cross PCIe several times faster than the layer computes, so the input groups
+    // grow (1, 3, 9, rest: only the first layer's copy is exposed) and the output groups shrink (rest, 9, 3, 1: only the
+    // last layer's copy is exposed).  Every group boundary is an event between two launches, which costs the overlap
+    // of those two layers, hence few groups.
+    const uint32_t Lu = uint32_t(L);
     const size_t qbl = qb / L, kbl = kb / L;
+    uint32_t in_start[5], out_end[5], n_in = 0, n_out = 0;
+    for (uint32_t b : {0u, 1u, 4u, 13u})
+        if (b < Lu && (n_in == 0 || b > in_start[n_in - 1])) in_start[n_in++] = b;
+    in_start[n_in] = Lu;
+    for (uint32_t back : {13u, 4u, 1u, 0u}) {
+        const uint32_t e = Lu - std::min(back, Lu);
+        if (e > 0 && (n_out == 0 || e > out_end[n_out - 1])) out_end[n_out++] = e;
+    }
     KRIYA_CUDA_TRY(c, cudaEventRecord(c->ev_step_begin, c->stream));  // the plan upload and earlier work come first
     KRIYA_CUDA_TRY(c, cudaStreamWaitEvent(c->copy_stream, c->ev_step_begin, 0));
     KRIYA_CUDA_TRY(c, cudaStreamWaitEvent(c->copy_stream_out, c->ev_step_begin, 0));
-    for (uint32_t g = 0; g < n_groups; ++g) {
-        const uint32_t l0 = g * group, l1 = std::min(uint32_t(L), l0 + group);
+    for (uint32_t g = 0; g < n_in; ++g) {  // all input copies are queued at once, in layer order
+        const uint32_t l0 = in_start[g], l1 = in_start[g + 1];
         const size_t nq = size_t(l1 - l0) * qbl, nk = size_t(l1 - l0) * kbl;
         KRIYA_CUDA_TRY(c, cudaMemcpyAsync(dq + l0 * qbl, static_cast<const uint8_t*>(q_host) + l0 * qbl, nq, cudaMemcpyHostToDevice, c->copy_stream));
         KRIYA_CUDA_TRY(c, cudaMemcpyAsync(dk + l0 * kbl, static_cast<const uint8_t*>(k_host) + l0 * kbl, nk, cudaMemcpyHostToDevice, c->copy_stream));
         KRIYA_CUDA_TRY(c, cudaMemcpyAsync(dv + l0 * kbl, static_cast<const uint8_t*>(v_host) + l0 * kbl, nk, cudaMemcpyHostToDevice, c->copy_stream));
         KRIYA_CUDA_TRY(c, cudaEventRecord(c->ev_in[g], c->copy_stream));
-        KRIYA_CUDA_TRY(c, cudaStreamWaitEvent(c->stream, c->ev_in[g], 0));
-        if (int32_t rc = decode_layers(c, l0, l1, true, dq, dk, dv, dout, rows, rope, gqa)) return rc;
-        KRIYA_CUDA_TRY(c, cudaEventRecord(c->ev_done[g], c->stream));
-        KRIYA_CUDA_TRY(c, cudaStreamWaitEvent(c->copy_stream_out, c->ev_done[g], 0));
-        KRIYA_CUDA_TRY(c, cudaMemcpyAsync(static_cast<uint8_t*>(out_host) + l0 * qbl, dout + l0 * qbl, nq, cudaMemcpyDeviceToHost, c->copy_stream_out));
+    }
+    uint32_t gi = 0, go = 0, layer = 0, out_from = 0;
+    while (layer < Lu) {
+        if (gi < n_in && in_start[gi] == layer) KRIYA_CUDA_TRY(c, cudaStreamWaitEvent(c->stream, c->ev_in[gi++], 0));
+        uint32_t stop = out_end[go];                                  // next boundary of either kind
+        if (gi < n_in && in_start[gi] < stop) stop = in_start[gi];
+        if (int32_t rc = decode_layers(c, layer, stop, true, dq, dk, dv, dout, rows, rope, gqa)) return rc;
+        layer = stop;
+        if (layer == out_end[go]) {
+            KRIYA_CUDA_TRY(c, cudaEventRecord(c->ev_done[go], c->stream));
+            KRIYA_CUDA_TRY(c, cudaStreamWaitEvent(c->copy_stream_out, c->ev_done[go], 0));
+            KRIYA_CUDA_TRY(c, cudaMemcpyAsync(static_cast<uint8_t*>(out_host) + out_from * qbl, dout + out_from * qbl,
+                                              size_t(layer - out_from) * qbl, cudaMemcpyDeviceToHost, c->copy_stream_out));
+            out_from = layer;
+            ++go;
+        }
     }
     KRIYA_CUDA_TRY(c, cudaEventRecord(c->ev_step_end, c->copy_stream_out));
     KRIYA_CUDA_TRY(c, cudaStreamWaitEvent(c->stream, c->ev_step_end, 0));  // later work on the context's stream follows the step
-    KRIYA_CUDA_TRY(c, cudaStreamSynchronize(c->copy_stream_out));
-    return kriya_cuda_sync(c, 0);
+    return KRIYA_CUDA_OK;
+}
+
+int32_t kriya_cuda_decode_step_host_end(kriya_cuda_ctx* c, uint32_t timeout_ms) {
+    if (!c) return KRIYA_CUDA_INVALID_INPUT;
+    return kriya_cuda_sync(c, timeout_ms);  // the context's stream waits for the last copy back: one wait covers the step
+}
+
+int32_t kriya_cuda_decode_step_host(kriya_cuda_ctx* c, const void* q_host, const void* k_host, const void* v_host,
+                                    void* out_host, uint32_t rows, const kriya_rope_kv_write_params* rope,
+                                    const kriya_bsr_gqa_params* gqa) {
+    if (int32_t rc = kriya_cuda_decode_step_host_begin(c, q_host, k_host, v_host, out_host, rows, rope, gqa)) return rc;
+    return kriya_cuda_decode_step_host_end(c, 0);
 }
 
 int32_t kriya_cuda_set_decode_path(kriya_cuda_ctx* c, int32_t path) {

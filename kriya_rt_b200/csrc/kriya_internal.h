@@ -55,7 +55,7 @@ struct kriya_cuda_ctx {
     cudaStream_t copy_stream = nullptr;      // host -> device inputs of whole-step host calls
     cudaStream_t copy_stream_out = nullptr;  // device -> host results
     cudaEvent_t ev_step_begin = nullptr, ev_step_end = nullptr;
-    std::vector<cudaEvent_t> ev_in, ev_done;  // per group of four layers
+    std::vector<cudaEvent_t> ev_in, ev_done;  // per input / output group of the host-buffer step
     int sm_count = 0;
     int max_smem_optin = 0;
 

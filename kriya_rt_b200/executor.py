@@ -238,6 +238,16 @@ class CudaExecutor:
         self._check(self._lib.kriya_cuda_decode_step_host(self._h, _ptr(q_host), _ptr(k_host), _ptr(v_host),
                                                           _ptr(out_host), rows, C.byref(rope), C.byref(gqa)))
 
+    def decode_step_host_begin(self, q_host, k_host, v_host, out_host, rows: int, rope: RopeKvWriteParams,
+                               gqa: BsrGqaParams) -> None:
+        """Queues the whole step (copies in, layers, copies back) and returns; the host buffers stay untouched until
+        decode_step_host_end().  The next step's plan may be built and uploaded in between: it queues behind this step."""
+        self._check(self._lib.kriya_cuda_decode_step_host_begin(self._h, _ptr(q_host), _ptr(k_host), _ptr(v_host),
+                                                                _ptr(out_host), rows, C.byref(rope), C.byref(gqa)))
+
+    def decode_step_host_end(self, timeout_ms: int = 0) -> None:
+        self._check(self._lib.kriya_cuda_decode_step_host_end(self._h, timeout_ms))
+
     def append_decode(self, layer: int, q, k_in, v_in, out, rope: RopeKvWriteParams, gqa: BsrGqaParams,
                       q_rope_out=None) -> None:
         """Append + decode of one layer in one launch; q is left un-rotated (see kriya_cuda_append_decode)."""
