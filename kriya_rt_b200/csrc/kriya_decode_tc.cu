@@ -64,11 +64,30 @@ struct TcParams {
 };
 
 // RoPE of eight (x[i], x[i + D/2]) pairs held as two 16-byte chunks, in the operation order of the append kernel
-// (fma(x0, c, -(x1 * s)), fma(x0, s, x1 * c), round to nearest even), so both paths write identical bits.
-template <typename T>
-__device__ __forceinline__ void rope8(uint4& lo, uint4& hi, uint32_t first_pair, uint32_t position, const KriyaFusedAppend& f) {
+// (fma(x0, c, -(x1 * s)), fma(x0, s, x1 * c), round to nearest even), so both paths write identical bits.  The
+// cos/sin pairs are fetched (or computed) separately: they depend on the position and the chunk only, so one fetch serves
+// every head of a run and its loads go out together with the loads of the vectors they rotate.
+__device__ __forceinline__ void rope8_coeffs(float2 (&cs)[8], uint32_t first_pair, uint32_t position, const KriyaFusedAppend& f) {
     const uint32_t half_rot = f.rotary_dim / 2u;
     const bool use_table = f.has_table != 0u && position < f.max_seq_len && f.table != nullptr;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const uint32_t i = first_pair + j;
+        cs[j] = make_float2(1.0f, 0.0f);
+        if (i < half_rot) {
+            if (use_table) {
+                cs[j] = reinterpret_cast<const float2*>(f.table)[size_t(position) * half_rot + i];
+            } else {
+                const float freq_exp = float(2u * i) / float(f.rotary_dim);
+                const float inv_freq = powf(f.rope_theta, -freq_exp);
+                const float angle = __fmul_rn(float(position), inv_freq);
+                cs[j] = make_float2(cosf(angle), sinf(angle));
+            }
+        }
+    }
+}
+template <typename T>
+__device__ __forceinline__ void rope8_apply(uint4& lo, uint4& hi, uint32_t first_pair, const float2 (&cs)[8], uint32_t half_rot) {
     uint32_t* lw = reinterpret_cast<uint32_t*>(&lo);
     uint32_t* hw = reinterpret_cast<uint32_t*>(&hi);
 #pragma unroll
@@ -77,23 +96,11 @@ __device__ __forceinline__ void rope8(uint4& lo, uint4& hi, uint32_t first_pair,
         uint16_t h2[2] = {uint16_t(hw[j] & 0xFFFFu), uint16_t(hw[j] >> 16)};
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
-            const uint32_t i = first_pair + 2 * j + e;
-            if (i < half_rot) {
-                float c, s;
-                if (use_table) {
-                    const float2 cs = reinterpret_cast<const float2*>(f.table)[size_t(position) * half_rot + i];
-                    c = cs.x;
-                    s = cs.y;
-                } else {
-                    const float freq_exp = float(2u * i) / float(f.rotary_dim);
-                    const float inv_freq = powf(f.rope_theta, -freq_exp);
-                    const float angle = __fmul_rn(float(position), inv_freq);
-                    c = cosf(angle);
-                    s = sinf(angle);
-                }
+            if (first_pair + 2 * j + e < half_rot) {  // pairs past the rotary dimension keep their bits
+                const float c = cs[2 * j + e].x, sn = cs[2 * j + e].y;
                 const float x0 = T::load(l2[e]), x1 = T::load(h2[e]);
-                l2[e] = T::store(__fmaf_rn(x0, c, -__fmul_rn(x1, s)));
-                h2[e] = T::store(__fmaf_rn(x0, s, __fmul_rn(x1, c)));
+                l2[e] = T::store(__fmaf_rn(x0, c, -__fmul_rn(x1, sn)));
+                h2[e] = T::store(__fmaf_rn(x0, sn, __fmul_rn(x1, c)));
             }
         }
         lw[j] = uint32_t(l2[0]) | (uint32_t(l2[1]) << 16);
@@ -362,6 +369,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
             uint8_t* qb = sQ + (runs % 3u) * kTcQBytes;
             const uint16_t* qg = reinterpret_cast<const uint16_t*>(a.q) + (size_t(seg.req) * Hq + seg.kv_head * G) * kTcD;
             uint32_t position = 0;
+            float2 cs[8];  // cos/sin of the run's position for this lane's chunk (fused form)
             if (!fused) {
                 // 16 rows x 256 B as two swizzled K-major panels; rows >= G stay zero
                 for (uint32_t i = lane; i < uint32_t(G) * 16u; i += 32u) {
@@ -373,17 +381,32 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
                 // the usual decode step appends at position = tokens already in the row; then the segment record
                 // already holds it and the dependent global load is skipped
                 position = pp.f.positions_are_context ? seg.row_tokens - 1u : pp.f.positions[seg.req];
-                for (uint32_t i = lane; i < uint32_t(G) * 8u; i += 32u) {
-                    const uint32_t h = i >> 3, c = i & 7u;
-                    uint4 lo = *reinterpret_cast<const uint4*>(qg + h * kTcD + c * 8);
-                    uint4 hi = *reinterpret_cast<const uint4*>(qg + h * kTcD + 64 + c * 8);
-                    rope8<T>(lo, hi, c * 8u, position, pp.f);
-                    *reinterpret_cast<uint4*>(qb + h * 128u + ((c ^ (h & 7u)) << 4)) = lo;
-                    *reinterpret_cast<uint4*>(qb + 2048u + h * 128u + ((c ^ (h & 7u)) << 4)) = hi;
-                    if (owns_last && pp.f.q_rope_out != nullptr) {
-                        uint16_t* qo = reinterpret_cast<uint16_t*>(pp.f.q_rope_out) + (size_t(seg.req) * Hq + seg.kv_head * G + h) * kTcD;
-                        *reinterpret_cast<uint4*>(qo + c * 8) = lo;
-                        *reinterpret_cast<uint4*>(qo + 64 + c * 8) = hi;
+                // item i = (head i / 8, 16-byte chunk i % 8); a lane's items all share the chunk lane % 8, hence the
+                // coefficients; every load of the run goes out before the first result is needed
+                constexpr int ITEMS = (G * 8 + 31) / 32;
+                const uint32_t c = lane & 7u;
+                rope8_coeffs(cs, c * 8u, position, pp.f);
+                uint4 lo[ITEMS], hi[ITEMS];
+#pragma unroll
+                for (int it = 0; it < ITEMS; ++it) {
+                    const uint32_t h = (lane + 32u * it) >> 3;
+                    if (h < uint32_t(G)) {
+                        lo[it] = *reinterpret_cast<const uint4*>(qg + h * kTcD + c * 8);
+                        hi[it] = *reinterpret_cast<const uint4*>(qg + h * kTcD + 64 + c * 8);
+                    }
+                }
+#pragma unroll
+                for (int it = 0; it < ITEMS; ++it) {
+                    const uint32_t h = (lane + 32u * it) >> 3;
+                    if (h < uint32_t(G)) {
+                        rope8_apply<T>(lo[it], hi[it], c * 8u, cs, pp.f.rotary_dim / 2u);
+                        *reinterpret_cast<uint4*>(qb + h * 128u + ((c ^ (h & 7u)) << 4)) = lo[it];
+                        *reinterpret_cast<uint4*>(qb + 2048u + h * 128u + ((c ^ (h & 7u)) << 4)) = hi[it];
+                        if (owns_last && pp.f.q_rope_out != nullptr) {
+                            uint16_t* qo = reinterpret_cast<uint16_t*>(pp.f.q_rope_out) + (size_t(seg.req) * Hq + seg.kv_head * G + h) * kTcD;
+                            *reinterpret_cast<uint4*>(qo + c * 8) = lo[it];
+                            *reinterpret_cast<uint4*>(qo + 64 + c * 8) = hi[it];
+                        }
                     }
                 }
             }
@@ -404,10 +427,10 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
                     uint16_t* vd = reinterpret_cast<uint16_t*>(pp.f.cache_v_w) + off;
                     const uint16_t* ks = reinterpret_cast<const uint16_t*>(pp.f.k_in) + src;
                     const uint16_t* vs = reinterpret_cast<const uint16_t*>(pp.f.v_in) + src;
-                    if (lane < 8u) {
+                    if (lane < 8u) {  // chunk = lane: the coefficients fetched for the queries apply
                         uint4 lo = *reinterpret_cast<const uint4*>(ks + lane * 8);
                         uint4 hi = *reinterpret_cast<const uint4*>(ks + 64 + lane * 8);
-                        rope8<T>(lo, hi, lane * 8u, position, pp.f);
+                        rope8_apply<T>(lo, hi, lane * 8u, cs, pp.f.rotary_dim / 2u);
                         *reinterpret_cast<uint4*>(kd + lane * 8) = lo;
                         *reinterpret_cast<uint4*>(kd + 64 + lane * 8) = hi;
                     } else if (lane < 24u) {
