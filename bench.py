@@ -151,6 +151,12 @@ def cpu_sample(layers_in_sample: int, repeats: int, seed: int = 1002):
     rp = O.RopeParams(Hq, Hkv, D, D, 16, 0, 1e-6, SHAPE.rope_theta, 8192, 1, 0, 0)
     gp = O.GqaParams(Hq, Hkv, D, 16, 16, 1, float(np.float32(1.0) / np.sqrt(np.float32(D))), 0.0)
     table = O.rope_table(8192, D, SHAPE.rope_theta)
+    # all the host cores this process may use, whatever OMP_NUM_THREADS says (torchrun sets it to 1 for its workers)
+    try:
+        avail = len(os.sched_getaffinity(0))
+    except AttributeError:
+        avail = os.cpu_count() or 1
+    O.set_num_threads(max(1, avail))
     cores = O.num_threads()
 
     def one_sample():
