@@ -138,3 +138,46 @@ def test_batched_prefill_three_sequences_one_launch():
         _, ref = O.prefill_causal(q[starts[i]:starts[i] + cnt], ck, cv, np.asarray(table, np.int32), prefix, oracle_gqa(ex), W.BF16)
         assert np.abs(got[starts[i]:starts[i] + cnt] - ref).max() <= 1e-2, i
     ex.close()
+
+
+def test_config4_full_size_last_chunk_of_eight_prompts():
+    """BASELINE config 4 at full size: eight 2048-token prompts (Hq 12, Hkv 2, D 128), the 512-token chunk at prefix 1536 of
+    all of them in one launch.  Two prompts are compared row by row with the oracle; every prompt is checked through a
+    size-independent property: the same launch repeated over relocated blocks (a different permutation of the pool with the
+    cache contents moved along) must not change a single bit."""
+    shape = W.AttnShape("c4", 12, 2, 128, W.BF16, rope_theta=1e6)
+    Hq, Hkv, D = 12, 2, 128
+    n_seq, total, chunk = 8, 2048, 512
+    per = total // 16
+    nb = n_seq * per + 64
+    rng = np.random.default_rng(404)
+    ck = W.normal16(rng, (nb, 16, Hkv, D), W.BF16); cv = W.normal16(rng, (nb, 16, Hkv, D), W.BF16)
+    q = W.normal16(rng, (n_seq * chunk, Hq, D), W.BF16)
+    starts = np.arange(n_seq) * chunk
+    outs = []
+    perm0 = None
+    for trial in range(2):
+        perm = np.random.default_rng(500 + trial).permutation(nb).astype(np.int32)
+        if trial == 0:
+            perm0, k_t, v_t = perm, ck, cv
+        else:  # logical block j of the pool image moves from perm0[j] to perm[j]
+            k_t, v_t = np.empty_like(ck), np.empty_like(cv)
+            k_t[perm] = ck[perm0]
+            v_t[perm] = cv[perm0]
+        ex = make_executor(shape, nb, max_query_tokens=n_seq * chunk)
+        fill_cache(ex, 0, k_t, v_t)
+        ex.plan_upload(np.arange(n_seq + 1) * per, perm[: n_seq * per], [16] * n_seq)
+        dq = dev16(q)
+        out = torch.zeros_like(dq)
+        torch.cuda.synchronize()
+        ex.paged_gqa_prefill_batch(0, dq, out, starts, [total - chunk] * n_seq, [chunk] * n_seq, ex.gqa_params(max_query_tokens=chunk))
+        ex.sync()
+        outs.append(host16(out).copy())
+        if trial == 0:
+            got = W.from_storage(outs[0], W.BF16)
+            for s in (0, n_seq - 1):
+                table = perm[s * per:(s + 1) * per]
+                _, ref = O.prefill_causal(q[starts[s]:starts[s] + chunk], ck, cv, table, total - chunk, oracle_gqa(ex), W.BF16)
+                assert np.abs(got[starts[s]:starts[s] + chunk] - ref).max() <= 1e-2, s
+        ex.close()
+    assert np.array_equal(outs[0], outs[1])
