@@ -568,7 +568,7 @@ def run_kernel_case(args):
         torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
         if world > 1:
             dist.init_process_group("nccl", device_id=torch.device("cuda", torch.cuda.current_device()))
-        lengths = np.random.default_rng(2005).integers(8192, 32768 + 1, size=256)
+        lengths = np.random.default_rng(2005).integers(8192, 32768 + 1, size=args.case_long_seqs)
         mine = sharding.assign_sequences(lengths, world)[rank]
         ctx = lengths[mine]
         nblocks = int(((ctx + 16) // 16).sum()) + 16
@@ -737,6 +737,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--serial-layers", action="store_true",
                     help="keep the layers' launches of a step strictly serialised (default: they may overlap at their edges)")
+    ap.add_argument("--case-long-seqs", type=int, default=256, help="sequences in the decode_long kernel case")
     ap.add_argument("--case-seqs", type=int, default=8, help="prompts in the prefill_batch kernel case")
     ap.add_argument("--kernel-case", default=None, choices=["decode", "decode_fused", "decode_long", "prefill", "prefill_batch", "append", "copy", "kvsplit", "tree_verify"],
                     help="run a few launches of one kernel on a small case (for ncu), --steps = launches")

@@ -22,7 +22,8 @@ LIB = ROOT / "kriya_rt_b200" / "lib"
 INCLUDE = ROOT / "include"
 OBJ = ROOT / "build" / "obj"
 
-CUDA_SOURCES = ["kriya_ctx.cu", "kriya_append.cu", "kriya_decode.cu", "kriya_decode_tc.cu", "kriya_copy.cu", "kriya_prefill.cu", "kriya_tree.cu", "kriya_static_scratch.cu"]
+CUDA_SOURCES = ["kriya_ctx.cu", "kriya_append.cu", "kriya_decode.cu", "kriya_decode_tc.cu", "kriya_decode_tc64.cu", "kriya_copy.cu", "kriya_prefill.cu", "kriya_tree.cu", "kriya_static_scratch.cu"]
+INCLUDED_SOURCES = {"kriya_decode_tc64.cu": ["kriya_decode_tc.cu"]}  # sources that #include another source
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr", "-Xptxas", "-v",
@@ -69,7 +70,7 @@ def build_cuda(force: bool = False) -> Path:
 
     def compile_one(pair):
         src, obj = pair
-        if not force and _newer(obj, [CSRC / src] + headers):
+        if not force and _newer(obj, [CSRC / src] + headers + [CSRC / d for d in INCLUDED_SOURCES.get(src, [])]):
             return
         _run([_nvcc(), *NVCC_FLAGS, *extra, "-I", str(INCLUDE), "-I", str(CSRC), "-c", str(CSRC / src), "-o", str(obj)],
              log=OBJ / (Path(src).stem + ".ptxas.log"))

@@ -118,16 +118,15 @@ constexpr uint32_t kRunStartWeight = 0;
 uint32_t tc_min_tiles_per_cta() {
     static const uint32_t v = [] {
         const char* e = getenv("KRIYA_TC_MIN_TILES");
-        const int x = e ? atoi(e) : 8;
+        const int x = e ? atoi(e) : 8;  // 1024 tokens at 128-token tiles, 512 at 64-token tiles
         return uint32_t(x < 1 ? 1 : x);
     }();
     return v;
 }
 
 uint32_t build_tc_segments(const int32_t* indptr, const int32_t* last_len, uint32_t block_size, uint32_t rows, uint32_t hkv,
-                           const uint32_t* begin, const uint32_t* end, uint32_t ctas, KriyaTcSeg* out, uint32_t cap,
-                           uint32_t* ptr) {
-    const uint32_t TP = 8;  // pages per tile
+                           const uint32_t* begin, const uint32_t* end, uint32_t ctas, uint32_t TP, KriyaTcSeg* out, uint32_t cap,
+                           uint32_t* ptr) {  // TP = pages per tile of the kernel variant the list is for
     uint64_t total = 0;
     for (uint32_t r = 0; r < rows; ++r) {
         const uint32_t nb = uint32_t(indptr[r + 1] - indptr[r]);
@@ -183,6 +182,20 @@ uint32_t build_tc_segments(const int32_t* indptr, const int32_t* last_len, uint3
     }
     while (cta < all_ctas) ptr[++cta] = n;
     return n;
+}
+
+// Which build of the tensor-core decode kernel serves a plan: the 64-token-tile build (two CTAs per SM) streams faster
+// but pays its per-CTA costs twice as often, so it is taken when every SM has a long stream ahead of it.
+bool choose_tc64(const kriya_cuda_ctx* c, const int32_t* indptr, uint32_t rows, const uint32_t* begin, const uint32_t* end) {
+    if (c->tc_force == 64) return true;
+    if (c->tc_force == 128) return false;
+    uint64_t tiles = 0;  // 128-token tiles of the whole launch
+    for (uint32_t r = 0; r < rows; ++r) {
+        const uint32_t nb = uint32_t(indptr[r + 1] - indptr[r]);
+        const uint32_t b = begin ? std::min(begin[r], nb) : 0u, e = end ? std::min(end[r], nb) : nb;
+        if (e > b) tiles += uint64_t((e - b + 7) / 8) * c->cfg.num_kv_heads;
+    }
+    return tiles >= uint64_t(c->tc64_min_tiles) * uint64_t(c->sm_count);
 }
 
 int32_t check_layer(kriya_cuda_ctx* c, uint32_t layer) {
@@ -325,10 +338,12 @@ int32_t launch_decode(kriya_cuda_ctx* c, uint32_t layer, const void* q, void* ou
     if (use_tc_decode(c)) {
         const uint32_t layer_row0 =
             uint32_t(size_t(layer) * c->layer_stride_bytes / (size_t(c->cfg.num_kv_heads) * c->cfg.head_dim * 2));
-        KRIYA_CUDA_TRY(c, kriya_launch_decode_tc(a, c->plan_dev<KriyaTcSeg>(range_list ? c->off_tcseg2 : c->off_tcseg),
-                                                 c->plan_dev<uint32_t>(range_list ? c->off_tcptr2 : c->off_tcptr),
-                                                 uint32_t(c->sm_count), c->tmap_k, c->tmap_v, layer_row0, c->cfg.dtype,
-                                                 c->max_smem_optin, fused, c->stream));
+        const bool t64 = range_list ? c->tc_t64_ranges : c->tc_t64;
+        const auto launch = t64 ? kriya_launch_decode_tc_t64 : kriya_launch_decode_tc;
+        const uint32_t grid = uint32_t(c->sm_count) * (t64 ? kriya_decode_tc_ctas_per_sm_t64() : kriya_decode_tc_ctas_per_sm());
+        KRIYA_CUDA_TRY(c, launch(a, c->plan_dev<KriyaTcSeg>(range_list ? c->off_tcseg2 : c->off_tcseg),
+                                 c->plan_dev<uint32_t>(range_list ? c->off_tcptr2 : c->off_tcptr), grid, c->tmap_k, c->tmap_v,
+                                 layer_row0, c->cfg.dtype, c->max_smem_optin, fused, c->stream));
     } else {
         KRIYA_CUDA_TRY(c, kriya_launch_decode(a, c->cfg.head_dim, c->cfg.block_size_tokens, c->cfg.dtype,
                                               c->max_smem_optin, c->stream));
@@ -385,6 +400,14 @@ int32_t kriya_cuda_ctx_create(const kriya_cuda_config* cfg_in, kriya_cuda_ctx** 
     auto* c = new kriya_cuda_ctx();
     c->cfg = cfg;
     c->sm_count = prop.multiProcessorCount;
+    // the plan arrays hold the larger of the two kernel variants' grids
+    c->tc_ctas = uint32_t(c->sm_count) * std::max(kriya_decode_tc_ctas_per_sm(), kriya_decode_tc_ctas_per_sm_t64());
+    {
+        const char* e = getenv("KRIYA_TC_VARIANT");  // 128 or 64: force one kernel variant (default: by plan)
+        c->tc_force = e ? atoi(e) : 0;
+        const char* m = getenv("KRIYA_TC64_MIN_TILES");
+        c->tc64_min_tiles = m ? uint32_t(std::max(1, atoi(m))) : 96u;
+    }
     c->max_smem_optin = int(prop.sharedMemPerBlockOptin);
     c->block_bytes = size_t(cfg.block_size_tokens) * cfg.num_kv_heads * cfg.head_dim * 2;
     c->layer_stride_bytes = align_up(size_t(cfg.num_kv_blocks) * c->block_bytes, 256);  // enc:1890-1894
@@ -464,13 +487,13 @@ int32_t kriya_cuda_ctx_create(const kriya_cuda_config* cfg_in, kriya_cuda_ctx** 
     off = align_up(off + size_t(c->cap_work) * sizeof(KriyaDecodeWork), 256);
     c->off_range = off;  // second work list, used by the block-range (partial state) decode
     off = align_up(off + size_t(c->cap_work) * sizeof(KriyaDecodeWork), 256);
-    c->cap_seg = c->cap_rows * cfg.num_kv_heads + uint32_t(c->sm_count) + 8u;
+    c->cap_seg = c->cap_rows * cfg.num_kv_heads + c->tc_ctas + 8u;
     c->off_tcptr = off;
-    off = align_up(off + (size_t(c->sm_count) + 1) * 4, 256);
+    off = align_up(off + (size_t(c->tc_ctas) + 1) * 4, 256);
     c->off_tcseg = off;
     off = align_up(off + size_t(c->cap_seg) * sizeof(KriyaTcSeg), 256);
     c->off_tcptr2 = off;
-    off = align_up(off + (size_t(c->sm_count) + 1) * 4, 256);
+    off = align_up(off + (size_t(c->tc_ctas) + 1) * 4, 256);
     c->off_tcseg2 = off;
     off = align_up(off + size_t(c->cap_seg) * sizeof(KriyaTcSeg), 256);
     c->off_tiles = off;
@@ -633,8 +656,11 @@ int32_t kriya_cuda_plan_upload(kriya_cuda_ctx* c, const int32_t* indptr, size_t 
     const uint32_t n_work =
         build_work(indptr, uint32_t(rows), nullptr, nullptr, 2u * uint32_t(c->sm_count), 2u, work, c->cap_work);
     if (n_work == UINT32_MAX) return invalid("plan needs more decode work items than the context holds");
+    c->tc_t64 = choose_tc64(c, indptr, uint32_t(rows), nullptr, nullptr);
+    const uint32_t plan_ctas = uint32_t(c->sm_count) * (c->tc_t64 ? kriya_decode_tc_ctas_per_sm_t64() : kriya_decode_tc_ctas_per_sm());
     const uint32_t n_seg = build_tc_segments(indptr, last_len, c->cfg.block_size_tokens, uint32_t(rows), c->cfg.num_kv_heads, nullptr,
-                                             nullptr, uint32_t(c->sm_count),
+                                             nullptr, plan_ctas,
+                                             c->tc_t64 ? kriya_decode_tc_pages_per_tile_t64() : kriya_decode_tc_pages_per_tile(),
                                              reinterpret_cast<KriyaTcSeg*>(h + c->off_tcseg), c->cap_seg,
                                              reinterpret_cast<uint32_t*>(h + c->off_tcptr));
     if (n_seg == UINT32_MAX) return invalid("plan needs more decode segments than the context holds");
@@ -643,7 +669,7 @@ int32_t kriya_cuda_plan_upload(kriya_cuda_ctx* c, const int32_t* indptr, size_t 
         const uint32_t* sp = reinterpret_cast<const uint32_t*>(h + c->off_tcptr);
         const KriyaTcSeg* sg = reinterpret_cast<const KriyaTcSeg*>(h + c->off_tcseg);
         bool all = true;
-        for (int cta = 0; cta < c->sm_count && all; ++cta) {
+        for (uint32_t cta = 0; cta < plan_ctas && all; ++cta) {
             bool busy = false;
             for (uint32_t i = sp[cta]; i < sp[cta + 1]; ++i) busy = busy || sg[i].blk_hi > sg[i].blk_lo;
             all = busy;
@@ -847,9 +873,12 @@ int32_t kriya_cuda_plan_set_ranges(kriya_cuda_ctx* c, const uint32_t* blk_begin,
                                       cudaMemcpyHostToDevice, c->stream));
     auto* segs = reinterpret_cast<KriyaTcSeg*>(c->h_plan_last + c->off_tcseg2);
     auto* sptr = reinterpret_cast<uint32_t*>(c->h_plan_last + c->off_tcptr2);
-    const uint32_t n_seg = build_tc_segments(indptr, reinterpret_cast<const int32_t*>(c->h_plan_last + c->off_last_len),
-                                             c->cfg.block_size_tokens, c->n_rows, c->cfg.num_kv_heads, blk_begin, blk_end,
-                                             uint32_t(c->sm_count), segs, c->cap_seg, sptr);
+    c->tc_t64_ranges = choose_tc64(c, indptr, c->n_rows, blk_begin, blk_end);
+    const uint32_t n_seg = build_tc_segments(
+        indptr, reinterpret_cast<const int32_t*>(c->h_plan_last + c->off_last_len), c->cfg.block_size_tokens, c->n_rows,
+        c->cfg.num_kv_heads, blk_begin, blk_end,
+        uint32_t(c->sm_count) * (c->tc_t64_ranges ? kriya_decode_tc_ctas_per_sm_t64() : kriya_decode_tc_ctas_per_sm()),
+        c->tc_t64_ranges ? kriya_decode_tc_pages_per_tile_t64() : kriya_decode_tc_pages_per_tile(), segs, c->cap_seg, sptr);
     if (n_seg == UINT32_MAX) return c->fail(KRIYA_CUDA_INVALID_INPUT, "ranges need more segments than the context holds");
     KRIYA_CUDA_TRY(c, cudaMemcpyAsync(c->d_plan + c->off_tcptr2, sptr, c->off_tcseg2 - c->off_tcptr2 + size_t(n_seg) * sizeof(KriyaTcSeg),
                                       cudaMemcpyHostToDevice, c->stream));

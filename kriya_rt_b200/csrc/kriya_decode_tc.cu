@@ -37,10 +37,33 @@
 
 #include "kriya_tc.cuh"
 
+// This file is compiled twice: as it is (128-token tiles, one CTA per SM) and through kriya_decode_tc64.cu with
+// KRIYA_TC_TILE64 defined (64-token tiles, two CTAs per SM); the two builds live in different namespaces and export
+// differently named launchers, and the context picks one per plan.
+#ifdef KRIYA_TC_TILE64
+#define KRIYA_TC_NS t64
+#define KRIYA_TC_FN(name) name##_t64
+#else
+#define KRIYA_TC_NS t128
+#define KRIYA_TC_FN(name) name
+#endif
+
 namespace kriya {
+namespace KRIYA_TC_NS {
 
 constexpr int kTcD = 128;
+// Tile of the K/V stream.  The default is 128 tokens with one resident CTA per SM.  KRIYA_TC_TILE64 builds the variant
+// with 64-token tiles (M = 64 score MMAs: accumulator row r lands in tensor-memory lane (r % 16) + 32 * (r / 16), so each
+// softmax warp owns 16 tokens of a tile and its upper 16 lanes idle) whose rings fit twice into an SM.
+#ifdef KRIYA_TC_TILE64
+constexpr int kTcTile = 64;
+constexpr int kTcCtasPerSm = 2;
+constexpr int kTcQBufs = 2;
+#else
 constexpr int kTcTile = 128;          // tokens per tile
+constexpr int kTcCtasPerSm = 1;
+constexpr int kTcQBufs = 3;
+#endif
 constexpr int kTcPage = 16;
 constexpr int kTcPagesPerTile = kTcTile / kTcPage;
 constexpr int kTcStages = 3;
@@ -48,10 +71,10 @@ constexpr int kTcThreads = 256;  // warps 0-3 softmax, 4 producer, 5 MMA issuer,
 constexpr int kTcN = 16;              // MMA N: query heads of one KV head, zero padded
 constexpr float kTcLog2e = 1.4426950408889634f;
 constexpr float kTcRescale = 8.0f;
-constexpr uint32_t kTcPanel = 128 * 128;           // one 64-d panel of a 128-token tile
-constexpr uint32_t kTcKvBytes = 2 * kTcPanel;      // K (or V) tile, both panels: 32 KB
+constexpr uint32_t kTcPanel = kTcTile * 128;       // one 64-d panel of a tile
+constexpr uint32_t kTcKvBytes = 2 * kTcPanel;      // K (or V) tile, both panels: 32 KB at 128 tokens
 constexpr uint32_t kTcQBytes = 2 * 16 * 128;       // 16 rows x 256 B as two panels: 4 KB
-constexpr uint32_t kTcPBytes = 2 * 16 * 128;       // [16 heads][128 tokens] as two 64-token panels: 4 KB
+constexpr uint32_t kTcPBytes = (kTcTile / 64) * 16 * 128;  // [16 heads][tile tokens] as 64-token panels: 4 KB at 128 tokens
 constexpr uint32_t kTcTmemCols = 64;
 constexpr uint32_t kColS0 = 0, kColS1 = 16, kColO = 32;
 
@@ -111,7 +134,7 @@ __device__ __forceinline__ void rope8_apply(uint4& lo, uint4& hi, uint32_t first
 // Optional per-CTA timeline (compile with -DKRIYA_TC_TRACE): wall-clock stamps at a few points of the kernel, dumped
 // to stderr by the launcher on the tenth launch when KRIYA_TRACE is set in the environment.
 #ifdef KRIYA_TC_TRACE
-__device__ unsigned long long g_trace[160 * 16];
+__device__ unsigned long long g_trace[320 * 16];
 #define TR(k) do { g_trace[blockIdx.x * 16 + (k)] = global_timer_ns(); } while (0)
 #define TRV(k, v) do { g_trace[blockIdx.x * 16 + (k)] = (v); } while (0)
 #else
@@ -205,10 +228,10 @@ __device__ __forceinline__ void merge_run_parts(const KriyaDecodeArgs& a, const 
 }
 
 template <int G, typename T>
-__global__ void __launch_bounds__(kTcThreads, 1)
+__global__ void __launch_bounds__(kTcThreads, kTcCtasPerSm)
 decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, TcParams pp) {
     constexpr uint32_t FMT = (T::kDtype == KRIYA_DTYPE_BF16) ? 1u : 0u;
-    constexpr uint32_t IDESC_S = make_idesc(FMT, 128, kTcN, 0, 0);  // A = K tile (K-major), B = Q (K-major)
+    constexpr uint32_t IDESC_S = make_idesc(FMT, kTcTile, kTcN, 0, 0);  // A = K tile (K-major), B = Q (K-major)
     constexpr uint32_t IDESC_O = make_idesc(FMT, 128, kTcN, 1, 0);  // A = V tile (MN-major), B = P (K-major)
 
     extern __shared__ uint8_t smem_raw[];
@@ -217,7 +240,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
     uint8_t* sK = sm;                                   // [stages][32 KB]
     uint8_t* sV = sK + kTcStages * kTcKvBytes;          // [stages][32 KB]
     uint8_t* sQ = sV + kTcStages * kTcKvBytes;          // [3][4 KB]
-    uint8_t* sP = sQ + 3 * kTcQBytes;                   // [2][4 KB]
+    uint8_t* sP = sQ + kTcQBufs * kTcQBytes;                   // [2][4 KB]
     float* red = reinterpret_cast<float*>(sP + 2 * kTcPBytes);  // [4 warps][16] / merge staging [8][G][2]
     uint64_t* bars = reinterpret_cast<uint64_t*>(red + 128);
     uint64_t* kv_full = bars;                     // [stages]
@@ -277,7 +300,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
     // The padding heads of the Q and P operand tiles must be zero.  The K/V ring needs no clearing: a K row
     // that is never loaded only produces a score that is masked by selection, and the V row of every masked
     // token is cleared by the softmax thread that owns it.
-    for (uint32_t i = tid; i < (3 * kTcQBytes + 2 * kTcPBytes) / 16; i += kTcThreads)
+    for (uint32_t i = tid; i < (kTcQBufs * kTcQBytes + 2 * kTcPBytes) / 16; i += kTcThreads)
         reinterpret_cast<uint4*>(sQ)[i] = make_uint4(0u, 0u, 0u, 0u);
     fence_async_smem();
     tc_fence_before();
@@ -316,7 +339,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
                     break;
                 }
                 // the piece's last tile reads the slot the stager warp writes: wait until it is in the cache
-                if (owns_last && t + 1u == t1 && !warp_wait(&kv_ready[runs % 3u], (runs / 3u) & 1u)) {
+                if (owns_last && t + 1u == t1 && !warp_wait(&kv_ready[runs % uint32_t(kTcQBufs)], (runs / uint32_t(kTcQBufs)) & 1u)) {
                     ok = false;
                     break;
                 }
@@ -360,13 +383,13 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
             const KriyaTcSeg seg = seg_at(si);
             if (seg.blk_hi <= seg.blk_lo) continue;
             if (*abort_flag) break;
-            if (runs >= 3u && !warp_wait(&q_free[runs % 3u], ((runs / 3u) - 1u) & 1u)) {
+            if (runs >= uint32_t(kTcQBufs) && !warp_wait(&q_free[runs % uint32_t(kTcQBufs)], ((runs / uint32_t(kTcQBufs)) - 1u) & 1u)) {
                 ok = false;
                 break;
             }
             const int32_t* table = a.indices + seg.tbl_off;
             const bool owns_last = fused && seg.row_tokens > 0u && uint64_t(seg.blk_hi) * kTcPage >= seg.row_tokens;
-            uint8_t* qb = sQ + (runs % 3u) * kTcQBytes;
+            uint8_t* qb = sQ + (runs % uint32_t(kTcQBufs)) * kTcQBytes;
             const uint16_t* qg = reinterpret_cast<const uint16_t*>(a.q) + (size_t(seg.req) * Hq + seg.kv_head * G) * kTcD;
             uint32_t position = 0;
             float2 cs[8];  // cos/sin of the run's position for this lane's chunk (fused form)
@@ -412,7 +435,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
             }
             fence_async_smem();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&q_ready[runs % 3u]);
+            if (lane == 0) mbar_arrive(&q_ready[runs % uint32_t(kTcQBufs)]);
             if (owns_last) {
                 // the rotated new key and the new value go into their cache slot; the fences order these generic-proxy
                 // writes before the TMA loads (async proxy) the producer issues after it has seen kv_ready
@@ -442,7 +465,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
                 asm volatile("fence.proxy.async.global;" ::: "memory");
                 __syncwarp();
             }
-            if (lane == 0) mbar_arrive(&kv_ready[runs % 3u]);
+            if (lane == 0) mbar_arrive(&kv_ready[runs % uint32_t(kTcQBufs)]);
             ++runs;
         }
         if (!ok && lane == 0) {
@@ -489,15 +512,15 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
             if (!la_valid) return true;
             if (!warp_wait(&kv_full[la_g % kTcStages], (la_g / kTcStages) & 1u)) return false;
             if (la_first) {
-                if (!warp_wait(&q_ready[la_run % 3u], (la_run / 3u) & 1u)) return false;
+                if (!warp_wait(&q_ready[la_run % uint32_t(kTcQBufs)], (la_run / uint32_t(kTcQBufs)) & 1u)) return false;
                 la_first = false;
             }
             tc_fence_after();
-            if (lane == 0) issue_s(la_g, la_run % 3u);
+            if (lane == 0) issue_s(la_g, la_run % uint32_t(kTcQBufs));
             __syncwarp();
             ++la_g;
             if (++la_t >= la_t1) {
-                if (lane == 0) umma_commit(&q_free[la_run % 3u]);  // the run's last S^T is issued: its Q buffer frees when it completes
+                if (lane == 0) umma_commit(&q_free[la_run % uint32_t(kTcQBufs)]);  // the run's last S^T is issued: its Q buffer frees when it completes
                 __syncwarp();
                 ++la_si;
                 ++la_run;
@@ -588,8 +611,11 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
                 uint32_t r[16];
                 tmem_ld16(tmem_base + lane_addr + ((g & 1u) ? kColS1 : kColS0), r);
                 tmem_wait_ld();
-                const uint32_t tok = t * kTcTile + tid;
-                const bool valid = tok >= tok_lo && tok < tok_hi;
+                // the token (= accumulator row) this thread owns in the tile, and whether it owns one at all
+                const uint32_t tile_row = (kTcTile == 128) ? tid : warp * 16u + lane;
+                const bool has_row = (kTcTile == 128) || lane < 16u;
+                const uint32_t tok = t * kTcTile + tile_row;
+                const bool valid = has_row && tok >= tok_lo && tok < tok_hi;
                 float s[G];
                 bool over = false;  // does this token push some head's score past the exponent reference?
 #pragma unroll
@@ -651,24 +677,25 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
                 // probabilities of this token for the G heads -> P[h][token] (K-major, swizzled)
                 {
                     uint8_t* pbuf = sP + (g & 1u) * kTcPBytes;
-                    const uint32_t panel = tid >> 6, col = tid & 63u;
+                    const uint32_t panel = tile_row >> 6, col = tile_row & 63u;
 #pragma unroll
                     for (int h = 0; h < G; ++h) {
                         const float p = (s[h] == -INFINITY) ? 0.0f : fast_exp2(s[h] - m_used[h]);
                         l_lane[h] += p;
-                        *reinterpret_cast<uint16_t*>(pbuf + panel * 2048u + uint32_t(h) * 128u +
-                                                     ((((col >> 3) ^ (uint32_t(h) & 7u)) << 4) | ((col & 7u) << 1))) = T::store(p);
+                        if (has_row)
+                            *reinterpret_cast<uint16_t*>(pbuf + panel * 2048u + uint32_t(h) * 128u +
+                                                         ((((col >> 3) ^ (uint32_t(h) & 7u)) << 4) | ((col & 7u) << 1))) = T::store(p);
                     }
                 }
                 // a token outside the run (past the row end, outside the block range, or a page that was not
                 // loaded) must contribute nothing: its V row is cleared so that 0 * garbage cannot appear
-                if (!valid) {
+                if (!valid && has_row) {
                     const uint32_t stage = g % kTcStages;
 #pragma unroll
                     for (int p = 0; p < 2; ++p)
 #pragma unroll
                         for (int c = 0; c < 8; ++c)
-                            *reinterpret_cast<uint4*>(sV + stage * kTcKvBytes + p * kTcPanel + tid * 128u + (c << 4)) =
+                            *reinterpret_cast<uint4*>(sV + stage * kTcKvBytes + p * kTcPanel + tile_row * 128u + (c << 4)) =
                                 make_uint4(0u, 0u, 0u, 0u);
                 }
                 tc_fence_before();
@@ -781,7 +808,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
 template <int G, typename T>
 cudaError_t launch_tc_t(const TcParams& pp, const CUtensorMap& mk, const CUtensorMap& mv, uint32_t grid, int max_smem_optin,
                         bool overlap_previous, cudaStream_t s) {
-    const size_t smem = size_t(2 * kTcStages) * kTcKvBytes + 3 * kTcQBytes + 2 * kTcPBytes + 512 + 320 + 512 + 8 * sizeof(KriyaTcSeg) + 1024;
+    const size_t smem = size_t(2 * kTcStages) * kTcKvBytes + kTcQBufs * kTcQBytes + 2 * kTcPBytes + 512 + 320 + 512 + 8 * sizeof(KriyaTcSeg) + 1024;
     if (smem > size_t(max_smem_optin)) return cudaErrorInvalidValue;
     auto kern = decode_tc_kernel<G, T>;
     static bool attr_set = false;
@@ -811,7 +838,7 @@ cudaError_t launch_tc_t(const TcParams& pp, const CUtensorMap& mk, const CUtenso
         static int calls = 0;
         if (++calls == 10) {
             cudaDeviceSynchronize();
-            static unsigned long long h[160 * 16];
+            static unsigned long long h[320 * 16];
             cudaMemcpyFromSymbol(h, g_trace, sizeof(h));
             unsigned long long t0 = ~0ull;
             for (uint32_t c = 0; c < grid; ++c)
@@ -845,19 +872,25 @@ cudaError_t launch_tc_g(uint32_t group, const TcParams& pp, const CUtensorMap& m
     }
 }
 
+}  // namespace KRIYA_TC_NS
 }  // namespace kriya
 
-bool kriya_decode_tc_supported(uint32_t head_dim, uint32_t group, uint32_t block_size) {
-    return head_dim == uint32_t(kriya::kTcD) && group >= 1 && group <= 8 && block_size == uint32_t(kriya::kTcPage);
+namespace ktc = kriya::KRIYA_TC_NS;
+
+uint32_t KRIYA_TC_FN(kriya_decode_tc_ctas_per_sm)() { return uint32_t(ktc::kTcCtasPerSm); }
+uint32_t KRIYA_TC_FN(kriya_decode_tc_pages_per_tile)() { return uint32_t(ktc::kTcPagesPerTile); }
+
+bool KRIYA_TC_FN(kriya_decode_tc_supported)(uint32_t head_dim, uint32_t group, uint32_t block_size) {
+    return head_dim == uint32_t(ktc::kTcD) && group >= 1 && group <= 8 && block_size == uint32_t(ktc::kTcPage);
 }
 
-cudaError_t kriya_launch_decode_tc(const KriyaDecodeArgs& a, const KriyaTcSeg* segs, const uint32_t* cta_seg_ptr, uint32_t grid,
+cudaError_t KRIYA_TC_FN(kriya_launch_decode_tc)(const KriyaDecodeArgs& a, const KriyaTcSeg* segs, const uint32_t* cta_seg_ptr, uint32_t grid,
                                    const void* map_k, const void* map_v, uint32_t layer_row0, uint32_t dtype,
                                    int max_smem_optin, const KriyaFusedAppend& fused, cudaStream_t s) {
     if (grid == 0) return cudaSuccess;
     const uint32_t group = a.num_q_heads / a.num_kv_heads;
-    if (!kriya_decode_tc_supported(kriya::kTcD, group, kriya::kTcPage) || !map_k || !map_v) return cudaErrorInvalidValue;
-    kriya::TcParams pp;
+    if (!KRIYA_TC_FN(kriya_decode_tc_supported)(ktc::kTcD, group, ktc::kTcPage) || !map_k || !map_v) return cudaErrorInvalidValue;
+    ktc::TcParams pp;
     pp.a = a;
     pp.segs = segs;
     pp.cta_seg_ptr = cta_seg_ptr;
@@ -866,6 +899,6 @@ cudaError_t kriya_launch_decode_tc(const KriyaDecodeArgs& a, const KriyaTcSeg* s
     const CUtensorMap& mk = *static_cast<const CUtensorMap*>(map_k);
     const CUtensorMap& mv = *static_cast<const CUtensorMap*>(map_v);
     const bool ov = fused.overlap_previous != 0;
-    return dtype == KRIYA_DTYPE_FP16 ? kriya::launch_tc_g<kriya::Fp16>(group, pp, mk, mv, grid, max_smem_optin, ov, s)
-                                     : kriya::launch_tc_g<kriya::Bf16>(group, pp, mk, mv, grid, max_smem_optin, ov, s);
+    return dtype == KRIYA_DTYPE_FP16 ? ktc::launch_tc_g<kriya::Fp16>(group, pp, mk, mv, grid, max_smem_optin, ov, s)
+                                     : ktc::launch_tc_g<kriya::Bf16>(group, pp, mk, mv, grid, max_smem_optin, ov, s);
 }

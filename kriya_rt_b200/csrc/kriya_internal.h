@@ -57,6 +57,10 @@ struct kriya_cuda_ctx {
     cudaEvent_t ev_step_begin = nullptr, ev_step_end = nullptr;
     std::vector<cudaEvent_t> ev_in, ev_done;  // per input / output group of the host-buffer step
     int sm_count = 0;
+    uint32_t tc_ctas = 0;  // largest grid of the tensor-core decode kernel variants: resident CTAs per SM x SMs
+    bool tc_t64 = false, tc_t64_ranges = false;  // the current plan's (range) lists are for the 64-token-tile build
+    int tc_force = 0;                            // KRIYA_TC_VARIANT
+    uint32_t tc64_min_tiles = 96;                // 128-token tiles per SM from which the 64-token-tile build is used
     int max_smem_optin = 0;
 
     // KV pools, all layers: layer l at l * layer_stride_bytes
@@ -220,6 +224,14 @@ struct KriyaFusedAppend {
     uint32_t overlap_previous = 0;
 };
 bool kriya_decode_tc_supported(uint32_t head_dim, uint32_t group, uint32_t block_size);
+uint32_t kriya_decode_tc_ctas_per_sm();
+uint32_t kriya_decode_tc_pages_per_tile();
+// the same kernel built with 64-token tiles and two resident CTAs per SM (kriya_decode_tc64.cu)
+uint32_t kriya_decode_tc_ctas_per_sm_t64();
+uint32_t kriya_decode_tc_pages_per_tile_t64();
+cudaError_t kriya_launch_decode_tc_t64(const KriyaDecodeArgs& a, const KriyaTcSeg* segs, const uint32_t* cta_seg_ptr, uint32_t grid,
+                                       const void* map_k, const void* map_v, uint32_t layer_row0, uint32_t dtype,
+                                       int max_smem_optin, const KriyaFusedAppend& fused, cudaStream_t s);
 cudaError_t kriya_launch_decode_tc(const KriyaDecodeArgs& a, const KriyaTcSeg* segs, const uint32_t* cta_seg_ptr, uint32_t grid,
                                    const void* map_k, const void* map_v, uint32_t layer_row0, uint32_t dtype,
                                    int max_smem_optin, const KriyaFusedAppend& fused, cudaStream_t s);
