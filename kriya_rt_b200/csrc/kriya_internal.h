@@ -84,7 +84,7 @@ struct kriya_cuda_ctx {
     uint8_t* d_plan = nullptr;
     size_t plan_bytes = 0;
     size_t off_indptr = 0, off_indices = 0, off_last_len = 0, off_tiles = 0, off_positions = 0, off_work = 0,
-           off_range = 0, off_tcseg = 0, off_tcptr = 0, off_tcseg2 = 0, off_tcptr2 = 0;
+           off_range = 0, off_tcseg = 0, off_tcptr = 0, off_tcseg2 = 0, off_tcptr2 = 0, dyn_base = 0;
     uint32_t cap_seg = 0, n_seg = 0;
     bool overlap_layers = true;  // whole-step calls let consecutive layers' launches overlap at their edges
     bool fuse_append = true;  // whole-step calls use the fused append + decode launch where it applies
