@@ -577,7 +577,8 @@ def run_kernel_case(args):
                           head_dim=128, device=torch.cuda.current_device(), rope_theta=SHAPE.rope_theta, rope_max_seq_len=32768 + 64,
                           max_batch_rows=256, max_page_indices=nblocks, max_tiles=65536)
         for view in ex.layer_cache_views(0):  # values do not matter for timing; keep the fill cheap but finite
-            view.view(-1)[: 1 << 24].copy_(torch.randn(1 << 24, device="cuda", generator=gen).to(torch.bfloat16).view(torch.int16))
+            nfill = min(1 << 24, view.numel())
+            view.view(-1)[:nfill].copy_(torch.randn(nfill, device="cuda", generator=gen).to(torch.bfloat16).view(torch.int16))
         n = len(mine)
         q, k, v = rnd(n, 16, 128), rnd(n, 2, 128), rnd(n, 2, 128)
         out = torch.zeros_like(q)

@@ -186,6 +186,14 @@ uint32_t build_tc_segments(const int32_t* indptr, const int32_t* last_len, uint3
 
 // Which build of the tensor-core decode kernel serves a plan: the 64-token-tile build (two CTAs per SM) streams faster
 // but pays its per-CTA costs twice as often, so it is taken when every SM has a long stream ahead of it.
+constexpr uint32_t kLateMergeParts = 12;  // runs cut into more pieces are merged by late_merge_kernel
+
+uint32_t max_parts_of(const KriyaTcSeg* segs, uint32_t n) {
+    uint32_t m = 0;
+    for (uint32_t i = 0; i < n; ++i) m = std::max(m, segs[i].n_parts);
+    return m;
+}
+
 bool choose_tc64(const kriya_cuda_ctx* c, const int32_t* indptr, uint32_t rows, const uint32_t* begin, const uint32_t* end) {
     if (c->tc_force == 64) return true;
     if (c->tc_force == 128) return false;
@@ -341,9 +349,15 @@ int32_t launch_decode(kriya_cuda_ctx* c, uint32_t layer, const void* q, void* ou
         const bool t64 = range_list ? c->tc_t64_ranges : c->tc_t64;
         const auto launch = t64 ? kriya_launch_decode_tc_t64 : kriya_launch_decode_tc;
         const uint32_t grid = uint32_t(c->sm_count) * (t64 ? kriya_decode_tc_ctas_per_sm_t64() : kriya_decode_tc_ctas_per_sm());
+        // A run spread over many CTAs (one long row) is merged by a kernel of its own behind the launch; launches that
+        // overlap with their neighbours keep the merge inside, the scratch-set rotation relies on it.
+        const uint32_t max_parts = range_list ? c->tc_max_parts_ranges : c->tc_max_parts;
+        const bool late = fused.overlap_previous == 0u && max_parts > kLateMergeParts;
         KRIYA_CUDA_TRY(c, launch(a, c->plan_dev<KriyaTcSeg>(range_list ? c->off_tcseg2 : c->off_tcseg),
                                  c->plan_dev<uint32_t>(range_list ? c->off_tcptr2 : c->off_tcptr), grid, c->tmap_k, c->tmap_v,
-                                 layer_row0, c->cfg.dtype, c->max_smem_optin, fused, c->stream));
+                                 layer_row0, c->cfg.dtype, c->max_smem_optin, fused, late ? kLateMergeParts : UINT32_MAX,
+                                 range_list ? c->n_seg_ranges : c->n_seg, c->stream));
+        if (late) c->launches += 1;
     } else {
         KRIYA_CUDA_TRY(c, kriya_launch_decode(a, c->cfg.head_dim, c->cfg.block_size_tokens, c->cfg.dtype,
                                               c->max_smem_optin, c->stream));
@@ -697,6 +711,7 @@ int32_t kriya_cuda_plan_upload(kriya_cuda_ctx* c, const int32_t* indptr, size_t 
     c->off_indices = o_indices;
     c->tc_t64 = t64;
     c->n_seg = n_seg;
+    c->tc_max_parts = max_parts_of(reinterpret_cast<const KriyaTcSeg*>(h + o_seg), n_seg);
     c->tc_all_ctas_busy = all_busy;
 
     c->n_rows = uint32_t(rows);
@@ -899,6 +914,8 @@ int32_t kriya_cuda_plan_set_ranges(kriya_cuda_ctx* c, const uint32_t* blk_begin,
         uint32_t(c->sm_count) * (c->tc_t64_ranges ? kriya_decode_tc_ctas_per_sm_t64() : kriya_decode_tc_ctas_per_sm()),
         c->tc_t64_ranges ? kriya_decode_tc_pages_per_tile_t64() : kriya_decode_tc_pages_per_tile(), segs, c->cap_seg, sptr);
     if (n_seg == UINT32_MAX) return c->fail(KRIYA_CUDA_INVALID_INPUT, "ranges need more segments than the context holds");
+    c->n_seg_ranges = n_seg;
+    c->tc_max_parts_ranges = max_parts_of(segs, n_seg);
     KRIYA_CUDA_TRY(c, cudaMemcpyAsync(c->d_plan + c->off_tcptr2, sptr, c->off_tcseg2 - c->off_tcptr2 + size_t(n_seg) * sizeof(KriyaTcSeg),
                                       cudaMemcpyHostToDevice, c->stream));
     KRIYA_CUDA_TRY(c, cudaEventRecord(c->h_pairs_free, c->stream));

@@ -83,6 +83,9 @@ struct TcParams {
     const KriyaTcSeg* segs;
     const uint32_t* cta_seg_ptr;  // [grid + 1]
     uint32_t layer_row0;
+    // runs cut into more pieces than this are not merged by their last piece but by late_merge_kernel after the launch
+    uint32_t late_parts;
+    uint32_t n_seg;  // host side only: segments of the list (grid of the late merge)
     KriyaFusedAppend f;
 };
 
@@ -565,7 +568,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
         if (defer_first) {
             const KriyaTcSeg seg = segs_s[0];
             asm volatile("bar.sync 2, 160;" ::: "memory");  // the softmax threads have published the partial state
-            if (*merge_job_ok) {
+            if (*merge_job_ok && seg.n_parts <= pp.late_parts) {
                 if (pp.f.overlap_previous != 2u) pdl_wait_previous_grid();
                 __threadfence();
                 uint32_t ticket = 0;
@@ -768,7 +771,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
                     __threadfence_block();
                     handed_off = true;
                     asm volatile("bar.arrive 2, 160;" ::: "memory");
-                } else {
+                } else if (seg.n_parts <= pp.late_parts) {
                     __threadfence();
                     named_bar_sync_128();
                     if (tid == 0) *ticket_s = atomicAdd(&a.counters[req * Hkv + seg.kv_head], 1u);
@@ -805,6 +808,53 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
     }
 }
 
+// Merge of the runs that were cut into many pieces (one long row spread over the whole machine): one CTA per
+// (run, query head), one thread per output dimension, eight partial states in flight per thread.  With dozens of
+// pieces this is several times faster than the single warp or warpgroup that would otherwise do it at the tail of the
+// decode launch.
+template <int G, typename T>
+__global__ void __launch_bounds__(kTcD) late_merge_kernel(KriyaDecodeArgs a, const KriyaTcSeg* segs, uint32_t late_parts) {
+    const KriyaTcSeg seg = segs[blockIdx.x];
+    if (seg.slot != seg.first_slot || seg.n_parts <= late_parts) return;  // not the first piece of a late-merged run
+    const uint32_t h = blockIdx.y, d = threadIdx.x;
+    float M = -INFINITY, L = 0.0f, O = 0.0f;
+    for (uint32_t c0 = 0; c0 < seg.n_parts; c0 += 8u) {
+        const uint32_t cnt = min(8u, seg.n_parts - c0);
+        float ms[8], ls[8], ov[8];
+#pragma unroll
+        for (int s2 = 0; s2 < 8; ++s2) {
+            const size_t row = size_t(seg.first_slot + c0 + min(uint32_t(s2), cnt - 1u)) * G + h;
+            ms[s2] = uint32_t(s2) < cnt ? a.part_ml[row * 2 + 0] : -INFINITY;
+            ls[s2] = a.part_ml[row * 2 + 1];
+            ov[s2] = a.part_o[row * kTcD + d];
+        }
+        float mc = M;
+#pragma unroll
+        for (int s2 = 0; s2 < 8; ++s2) mc = fmaxf(mc, ms[s2]);
+        if (mc == -INFINITY) continue;
+        const float keep = (M == -INFINITY) ? 0.0f : exp2f(M - mc);
+        L *= keep;
+        O *= keep;
+#pragma unroll
+        for (int s2 = 0; s2 < 8; ++s2) {
+            const float w = (ms[s2] == -INFINITY) ? 0.0f : exp2f(ms[s2] - mc);
+            L = fmaf(w, ls[s2], L);
+            O = fmaf(w, ov[s2], O);
+        }
+        M = mc;
+    }
+    const size_t row0 = size_t(seg.req) * a.num_q_heads + seg.kv_head * G + h;
+    if (a.state_o != nullptr) {
+        a.state_o[row0 * kTcD + d] = O;
+        if (d == 0) {
+            a.state_m[row0] = M / kTcLog2e;
+            a.state_l[row0] = L;
+        }
+    } else {
+        reinterpret_cast<uint16_t*>(a.out)[row0 * kTcD + d] = T::store(O / fmaxf(L, 1e-12f));
+    }
+}
+
 template <int G, typename T>
 cudaError_t launch_tc_t(const TcParams& pp, const CUtensorMap& mk, const CUtensorMap& mv, uint32_t grid, int max_smem_optin,
                         bool overlap_previous, cudaStream_t s) {
@@ -833,6 +883,8 @@ cudaError_t launch_tc_t(const TcParams& pp, const CUtensorMap& mk, const CUtenso
     } else {
         kern<<<grid, kTcThreads, smem, s>>>(mk, mv, pp);
     }
+    if (pp.late_parts != UINT32_MAX && pp.n_seg != 0u)
+        late_merge_kernel<G, T><<<dim3(pp.n_seg, G), kTcD, 0, s>>>(pp.a, pp.segs, pp.late_parts);
 #ifdef KRIYA_TC_TRACE
     if (getenv("KRIYA_TRACE")) {
         static int calls = 0;
@@ -886,7 +938,8 @@ bool KRIYA_TC_FN(kriya_decode_tc_supported)(uint32_t head_dim, uint32_t group, u
 
 cudaError_t KRIYA_TC_FN(kriya_launch_decode_tc)(const KriyaDecodeArgs& a, const KriyaTcSeg* segs, const uint32_t* cta_seg_ptr, uint32_t grid,
                                    const void* map_k, const void* map_v, uint32_t layer_row0, uint32_t dtype,
-                                   int max_smem_optin, const KriyaFusedAppend& fused, cudaStream_t s) {
+                                   int max_smem_optin, const KriyaFusedAppend& fused, uint32_t late_parts, uint32_t n_seg,
+                                   cudaStream_t s) {
     if (grid == 0) return cudaSuccess;
     const uint32_t group = a.num_q_heads / a.num_kv_heads;
     if (!KRIYA_TC_FN(kriya_decode_tc_supported)(ktc::kTcD, group, ktc::kTcPage) || !map_k || !map_v) return cudaErrorInvalidValue;
@@ -895,6 +948,8 @@ cudaError_t KRIYA_TC_FN(kriya_launch_decode_tc)(const KriyaDecodeArgs& a, const 
     pp.segs = segs;
     pp.cta_seg_ptr = cta_seg_ptr;
     pp.layer_row0 = layer_row0;
+    pp.late_parts = late_parts;
+    pp.n_seg = n_seg;
     pp.f = fused;
     const CUtensorMap& mk = *static_cast<const CUtensorMap*>(map_k);
     const CUtensorMap& mv = *static_cast<const CUtensorMap*>(map_v);

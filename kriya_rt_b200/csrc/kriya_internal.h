@@ -85,7 +85,8 @@ struct kriya_cuda_ctx {
     size_t plan_bytes = 0;
     size_t off_indptr = 0, off_indices = 0, off_last_len = 0, off_tiles = 0, off_positions = 0, off_work = 0,
            off_range = 0, off_tcseg = 0, off_tcptr = 0, off_tcseg2 = 0, off_tcptr2 = 0, dyn_base = 0;
-    uint32_t cap_seg = 0, n_seg = 0;
+    uint32_t cap_seg = 0, n_seg = 0, n_seg_ranges = 0;
+    uint32_t tc_max_parts = 0, tc_max_parts_ranges = 0;  // most pieces any run of the current (range) lists is cut into
     bool overlap_layers = true;  // whole-step calls let consecutive layers' launches overlap at their edges
     bool fuse_append = true;  // whole-step calls use the fused append + decode launch where it applies
     int decode_path = 0;  // 0: pick per shape, 1: CUDA-core kernel, 2: tensor-core kernel
@@ -231,10 +232,10 @@ uint32_t kriya_decode_tc_ctas_per_sm_t64();
 uint32_t kriya_decode_tc_pages_per_tile_t64();
 cudaError_t kriya_launch_decode_tc_t64(const KriyaDecodeArgs& a, const KriyaTcSeg* segs, const uint32_t* cta_seg_ptr, uint32_t grid,
                                        const void* map_k, const void* map_v, uint32_t layer_row0, uint32_t dtype,
-                                       int max_smem_optin, const KriyaFusedAppend& fused, cudaStream_t s);
+                                       int max_smem_optin, const KriyaFusedAppend& fused, uint32_t late_parts, uint32_t n_seg, cudaStream_t s);
 cudaError_t kriya_launch_decode_tc(const KriyaDecodeArgs& a, const KriyaTcSeg* segs, const uint32_t* cta_seg_ptr, uint32_t grid,
                                    const void* map_k, const void* map_v, uint32_t layer_row0, uint32_t dtype,
-                                   int max_smem_optin, const KriyaFusedAppend& fused, cudaStream_t s);
+                                   int max_smem_optin, const KriyaFusedAppend& fused, uint32_t late_parts, uint32_t n_seg, cudaStream_t s);
 
 cudaError_t kriya_launch_merge_states(const float* m, const float* l, const float* o, uint32_t parts, uint32_t rows,
                                       uint32_t D, size_t stride_ml, size_t stride_o, void* out, uint32_t dtype,
