@@ -47,6 +47,7 @@ void destroy(kriya_cuda_ctx* c) {
     cudaFree(c->d_act);
     cudaFree(c->d_pairs);
     cudaFree(c->d_tree_state);
+    cudaFree(c->d_tree_mask);
     cudaFree(c->d_step);
     for (cudaEvent_t e : c->ev_pool) cudaEventDestroy(e);
     for (int i = 0; i < 2; ++i) {
@@ -540,6 +541,7 @@ int32_t kriya_cuda_ctx_create(const kriya_cuda_config* cfg_in, kriya_cuda_ctx** 
     CREATE_TRY(cudaMallocHost(&c->h_act, c->act_bytes));
     CREATE_TRY(cudaMalloc(&c->d_pairs, size_t(c->cap_pairs) * 3 * sizeof(uint32_t)));
     CREATE_TRY(cudaMalloc(&c->d_tree_state, size_t(kTreeMaxNodes) * c->cfg.num_q_heads * (c->cfg.head_dim + 2) * sizeof(float)));
+    CREATE_TRY(cudaMalloc(&c->d_tree_mask, size_t(kTreeMaxNodes) * kTreeMaxNodes));
     CREATE_TRY(cudaMallocHost(&c->h_pairs, size_t(c->cap_pairs) * 3 * sizeof(uint32_t)));
     CREATE_TRY(cudaEventCreateWithFlags(&c->h_pairs_free, cudaEventDisableTiming));
     CREATE_TRY(cudaStreamSynchronize(c->stream));
@@ -836,11 +838,15 @@ int32_t kriya_cuda_tree_verify(kriya_cuda_ctx* c, uint32_t layer, const void* tq
                            "decode kernels cover head_dim 64/128, group size 1..8, 16-token blocks (head_dim 64: up to 8 KV heads)");
     }
     cudaSetDevice(c->cfg.device);
-    // the mask goes through the pinned staging buffer the copy lists use
-    KRIYA_CUDA_TRY(c, cudaEventSynchronize(c->h_pairs_free));
-    memcpy(c->h_pairs, mask, size_t(n) * n);
-    KRIYA_CUDA_TRY(c, cudaMemcpyAsync(c->d_pairs, c->h_pairs, size_t(n) * n, cudaMemcpyHostToDevice, c->stream));
-    KRIYA_CUDA_TRY(c, cudaEventRecord(c->h_pairs_free, c->stream));
+    // The layers of one verification pass the same mask: it is copied (through the pinned staging buffer the copy lists
+    // use) only when it differs from the one already on the device.
+    if (c->tree_mask_last.size() != size_t(n) * n || memcmp(c->tree_mask_last.data(), mask, size_t(n) * n) != 0) {
+        KRIYA_CUDA_TRY(c, cudaEventSynchronize(c->h_pairs_free));
+        memcpy(c->h_pairs, mask, size_t(n) * n);
+        KRIYA_CUDA_TRY(c, cudaMemcpyAsync(c->d_tree_mask, c->h_pairs, size_t(n) * n, cudaMemcpyHostToDevice, c->stream));
+        KRIYA_CUDA_TRY(c, cudaEventRecord(c->h_pairs_free, c->stream));
+        c->tree_mask_last.assign(mask, mask + size_t(n) * n);
+    }
     const size_t R = size_t(n) * c->cfg.num_q_heads;
     float* st_m = c->d_tree_state;
     float* st_l = st_m + R;
@@ -862,7 +868,7 @@ int32_t kriya_cuda_tree_verify(kriya_cuda_ctx* c, uint32_t layer, const void* tq
     a.q = tq;
     a.k = tk;
     a.v = tv;
-    a.mask = reinterpret_cast<const uint8_t*>(c->d_pairs);
+    a.mask = c->d_tree_mask;
     a.st_m = st_m;
     a.st_l = st_l;
     a.st_o = st_o;

@@ -118,6 +118,8 @@ struct kriya_cuda_ctx {
     uint32_t* h_pairs = nullptr;
     uint32_t cap_pairs = 0;
     float* d_tree_state = nullptr;  // [kTreeMaxNodes * Hq * (D + 2)] prefix states of a tree verification
+    uint8_t* d_tree_mask = nullptr;  // [kTreeMaxNodes^2] the tree mask of the last verification
+    std::vector<uint8_t> tree_mask_last;  // its host copy: the layers of one verification pass the same mask
     cudaEvent_t h_pairs_free = nullptr;
 
     // staging for whole-step host calls (grown on demand by kriya_cuda_decode_step_host)
