@@ -39,6 +39,8 @@ SHAPE = W.QWEN25_3B
 BATCH = 32
 NUM_BLOCKS = 16384
 CTX_LO, CTX_HI = 512, 4096
+TIMED_DEVICE_S = 0.5   # device time the repeated timed region must add up to
+MAX_REPEATS = 200
 WORKLOAD = ("qwen2.5-3b attention decode: Hq16 Hkv2 D128 bf16, 36 layers, batch 32/GPU, ctx U[512,4096], "
             "16-token blocks, 16384-block pool/layer, append+attention per layer per step")
 
@@ -233,13 +235,11 @@ def run_gpu_arm(args):
     from kriya_rt_b200.kv import PagedKvCacheManager
 
     L, Hq, Hkv, D = SHAPE.num_layers, SHAPE.num_q_heads, SHAPE.num_kv_heads, SHAPE.head_dim
-    total_steps = args.warmup + args.steps
+    K, Wu = args.steps, args.warmup
     ex = CudaExecutor(num_layers=L, num_kv_blocks=NUM_BLOCKS, block_size_tokens=16, num_q_heads=Hq, num_kv_heads=Hkv,
                       head_dim=D, dtype=W.BF16, device=local_rank, rope_theta=SHAPE.rope_theta, rope_max_seq_len=8192,
                       max_batch_rows=64, max_page_indices=NUM_BLOCKS, max_tiles=4096, max_query_tokens=64)
     stream = torch.cuda.ExternalStream(ex.stream_ptr, device=torch.device("cuda", local_rank))
-    if args.serial_layers:
-        ex.set_fused_append(3)
 
     # KV pool: N(0,1) in every block of every layer (bf16), generated on the device
     gen = torch.Generator(device="cuda").manual_seed(1002 + rank)
@@ -262,7 +262,6 @@ def run_gpu_arm(args):
     rp = ex.rope_params()
     gp = ex.gqa_params()
 
-    # ---- leg 1: device-resident throughput (`value`) -------------------------------------------------
     # Bookkeeping runs in the compiled manager exactly as a scheduler would drive it: one append_token_slot
     # per sequence, then build_schedule_plan, every step.
     def fresh_manager():
@@ -290,55 +289,71 @@ def run_gpu_arm(args):
         if dist is not None:
             dist.barrier()
 
-    mgr = fresh_manager()
-    attended = []
+    def device_pass(mode, steps, warm):
+        """`warm` untimed and exactly `steps` timed decode steps from a fresh sequence state, bracketed by a barrier and
+        a device synchronisation on both sides; returns (device ms of the timed steps, launches in them)."""
+        ex.set_fused_append(mode)
+        mgr = fresh_manager()
+        for t in range(warm):
+            plan, pos = step_plan(mgr, t)
+            ex.upload_schedule_plan(plan, pos)
+            ex.decode_step(q, k, v, out, BATCH, rp, gp)
+        ex.sync()
+        barrier()
+        torch.cuda.synchronize()
+        launches0 = ex.launch_count
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record(stream)
+        for t in range(warm, warm + steps):
+            plan, pos = step_plan(mgr, t)
+            ex.upload_schedule_plan(plan, pos)
+            ex.decode_step(q, k, v, out, BATCH, rp, gp)
+        ev1.record(stream)
+        ex.sync()
+        torch.cuda.synchronize()
+        barrier()
+        return ev0.elapsed_time(ev1), ex.launch_count - launches0
+
+    # ---- leg 1: device-resident throughput (`value`) -------------------------------------------------
+    # The region of exactly --steps steps is repeated (every repeat from the same sequence state, so the work does not
+    # drift) until at least TIMED_DEVICE_S of device time has been measured; the median repeat is the figure.
+    attended = [int((ctx0 + t + 1).sum()) for t in range(Wu, Wu + K)]
     ex.timing_enable(False)
     sampler = ClockSampler(local_rank)
     sampler.start()
-    for t in range(args.warmup):
-        plan, pos = step_plan(mgr, t)
-        ex.upload_schedule_plan(plan, pos)
-        ex.decode_step(q, k, v, out, BATCH, rp, gp)
-    ex.sync()
-    barrier()
-    torch.cuda.synchronize()
+    device_pass(1, min(K, 3), Wu)  # module load, first-launch set-up, clocks up
     sampler.mark_start()
-    launches0 = ex.launch_count
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    ev0.record(stream)
-    for t in range(args.warmup, total_steps):
-        plan, pos = step_plan(mgr, t)
-        attended.append(int((ctx0 + t + 1).sum()))
-        ex.upload_schedule_plan(plan, pos)
-        ex.decode_step(q, k, v, out, BATCH, rp, gp)
-    ev1.record(stream)
-    ex.sync()
-    torch.cuda.synchronize()
+    repeats_ms, gpu_launches = [], 0
+    while sum(repeats_ms) < TIMED_DEVICE_S * 1e3 and len(repeats_ms) < MAX_REPEATS:
+        ms, n_launch = device_pass(1, K, Wu)
+        if dist is not None:  # every rank must agree on the repeat count: the slowest rank's time decides
+            t_rep = torch.tensor([ms], device="cuda", dtype=torch.float64)
+            dist.all_reduce(t_rep, op=dist.ReduceOp.MAX)
+            ms = float(t_rep[0])
+        repeats_ms.append(ms)
+        gpu_launches = n_launch
     sampler.mark_end()
-    barrier()
     clocks = sampler.stop()
-    elapsed_ms = ev0.elapsed_time(ev1)
-    gpu_launches = ex.launch_count - launches0
+    elapsed_ms = float(np.median(repeats_ms))
 
-    # ---- leg 1b: the same steps once more with every decode launch bracketed by CUDA events on its stream, for the
-    # per-launch duration of the dominant kernel (the brackets cost idle time between kernels, so they are kept out
-    # of the timed region above)
+    # ---- leg 1b: the same steps under three more launch disciplines (one repeat each), for the per-launch figures -----
+    #   serialised: a layer's launch may be set up early but touches nothing before the previous layer has completed;
+    #   dependent : a layer's activations wait for the previous layer (as in a model), its cached K/V streams at once;
+    #   bracketed : every launch between two CUDA events (which costs idle time around each launch).
+    serial_ms, n_serial = device_pass(3, K, Wu)
+    dep_ms, n_dep = device_pass(5, K, Wu)
+    ex.set_fused_append(1)
     mgr_b = fresh_manager()
-    for t in range(args.warmup):
+    for t in range(Wu):
         step_plan(mgr_b, t)
     ex.timing_enable(True)
-    ev2, ev3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    ev2.record(stream)
-    for t in range(args.warmup, total_steps):
+    for t in range(Wu, Wu + K):
         plan, pos = step_plan(mgr_b, t)
         ex.upload_schedule_plan(plan, pos)
         ex.decode_step(q, k, v, out, BATCH, rp, gp)
-    ev3.record(stream)
     ex.sync()
     n_dec, ms_dec = ex.timing_read(0)
-    n_app, ms_app = ex.timing_read(1)
     ex.timing_enable(False)
-    bracketed_ms_per_step = ev2.elapsed_time(ev3) / args.steps
 
     # ---- leg 2: end to end through host buffers ---------------------------------------------------------
     qh = torch.empty(L, BATCH, Hq, D, dtype=torch.int16).pin_memory()
@@ -346,39 +361,42 @@ def run_gpu_arm(args):
     vh = torch.empty(L, BATCH, Hkv, D, dtype=torch.int16).pin_memory()
     oh = torch.empty(L, BATCH, Hq, D, dtype=torch.int16).pin_memory()
     qh.copy_(q.cpu()); kh.copy_(k.cpu()); vh.copy_(v.cpu())
-    mgr2 = fresh_manager()
-    e2e_steps = args.steps
     plan_bytes = 0
-    for t in range(args.warmup):
-        plan, pos = step_plan(mgr2, t)
-        ex.upload_schedule_plan(plan, pos)
-        ex.decode_step_host(qh, kh, vh, oh, BATCH, rp, gp)
-    barrier()
-    # Every timed step copies its inputs from pinned host memory, runs the 36 layers, copies the result back and waits
-    # for it.  The host's work for the NEXT step (block allocation, plan build, plan upload) runs between the begin and
-    # the end of the current step, i.e. while the GPU is busy; the upload queues behind the step on the same stream.
-    t0 = time.perf_counter()
-    plan, pos = step_plan(mgr2, args.warmup)
-    ex.upload_schedule_plan(plan, pos)
-    for t in range(args.warmup, args.warmup + e2e_steps):
-        plan_bytes = 4 * (plan.page_indptr.size + plan.page_indices.size + plan.last_page_len.size + pos.size) + \
-            16 * plan.cta_work_tiles.shape[0]
-        ex.decode_step_host_begin(qh, kh, vh, oh, BATCH, rp, gp)
-        if t + 1 < args.warmup + e2e_steps:
-            plan, pos = step_plan(mgr2, t + 1)
+    e2e_repeats = []
+    while sum(e2e_repeats) < TIMED_DEVICE_S and len(e2e_repeats) < MAX_REPEATS:
+        mgr2 = fresh_manager()
+        for t in range(Wu):
+            plan, pos = step_plan(mgr2, t)
             ex.upload_schedule_plan(plan, pos)
-        ex.decode_step_host_end()  # the step's result is in host memory
-    e2e_s = time.perf_counter() - t0
-    barrier()
+            ex.decode_step_host(qh, kh, vh, oh, BATCH, rp, gp)
+        barrier()
+        # Every timed step copies its inputs from pinned host memory, runs the 36 layers, copies the result back and waits
+        # for it.  The host's work for the NEXT step (block allocation, plan build, plan upload) runs between the begin and
+        # the end of the current step, i.e. while the GPU is busy; the upload queues behind the step on the same stream.
+        t0 = time.perf_counter()
+        plan, pos = step_plan(mgr2, Wu)
+        ex.upload_schedule_plan(plan, pos)
+        for t in range(Wu, Wu + K):
+            plan_bytes = 4 * (plan.page_indptr.size + plan.page_indices.size + plan.last_page_len.size + pos.size) + \
+                16 * plan.cta_work_tiles.shape[0]
+            ex.decode_step_host_begin(qh, kh, vh, oh, BATCH, rp, gp)
+            if t + 1 < Wu + K:
+                plan, pos = step_plan(mgr2, t + 1)
+                ex.upload_schedule_plan(plan, pos)
+            ex.decode_step_host_end()  # the step's result is in host memory
+        dt = time.perf_counter() - t0
+        if dist is not None:
+            t_rep = torch.tensor([dt], device="cuda", dtype=torch.float64)
+            dist.all_reduce(t_rep, op=dist.ReduceOp.MAX)
+            dt = float(t_rep[0])
+        e2e_repeats.append(dt)
+        barrier()
+    e2e_ms = float(np.median(e2e_repeats)) * 1e3
 
-    # max over ranks
-    t_dev = torch.tensor([elapsed_ms, e2e_s * 1e3], device="cuda", dtype=torch.float64)
-    if dist is not None:
-        dist.all_reduce(t_dev, op=dist.ReduceOp.MAX)
-    elapsed_ms, e2e_ms = float(t_dev[0]), float(t_dev[1])
-    ms_per_step = elapsed_ms / args.steps
+    # max over ranks (the repeats were reduced as they were taken)
+    ms_per_step = elapsed_ms / K
     value = world * BATCH / (ms_per_step * 1e-3)
-    e2e_value = world * BATCH / (e2e_ms / e2e_steps * 1e-3)
+    e2e_value = world * BATCH / (e2e_ms / K * 1e-3)
 
     # roofline of the dominant kernel (paged decode): algorithmic bytes per launch / mean launch time
     kv_bytes_launch = float(np.mean(attended)) * SHAPE.kv_bytes_per_token  # K and V, each element once
@@ -386,12 +404,16 @@ def run_gpu_arm(args):
     table_bytes = 4 * float(np.mean([(c + 15) // 16 for c in attended])) + 4 * (2 * BATCH + 1)
     alg_bytes = kv_bytes_launch + qo_bytes + table_bytes
     peaks, peak_kind = measured_peaks()
-    dec_us = ms_dec / max(n_dec, 1) * 1e3          # one launch alone: bracketed by events, no overlap with its neighbours
-    isolated = alg_bytes / (dec_us * 1e-6) / 1e9 if n_dec else None
-    # In the timed region the launches of consecutive layers overlap at their edges, so a launch's share of the stream
-    # is the region's device time divided by its launches (the decode launch is the only kernel of the step).
+    peak = peaks["hbm_gbs"]
+
+    def gbs(us):
+        return alg_bytes / (us * 1e-6) / 1e9
+
+    dec_us = ms_dec / max(n_dec, 1) * 1e3
     instream_us = elapsed_ms * 1e3 / max(gpu_launches, 1)
-    achieved = alg_bytes / (instream_us * 1e-6) / 1e9
+    serial_us = serial_ms * 1e3 / max(n_serial, 1)
+    dep_us = dep_ms * 1e3 / max(n_dep, 1)
+    achieved = gbs(instream_us)
     traffic = None
     tfile = ROOT / "profiles" / "decode_traffic.json"
     if tfile.exists():
@@ -401,31 +423,49 @@ def run_gpu_arm(args):
         except Exception:
             traffic = None
 
+    ex.close()
+    del q, k, v, out
+    torch.cuda.empty_cache()
+    config5 = run_config5(args, rank, local_rank, world, dist, peak)
+
     if rank == 0:
         line = {
-            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": Wu,
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic",
             "config": {"workload": WORKLOAD, "l2": "inputs larger than L2: each step streams %.2f GB of KV" %
                        (kv_bytes_launch * L / 1e9), "plan": "rebuilt on the host every step by the C++ manager and uploaded inside the timed region",
                        "kv_read_gbs_whole_step": kv_bytes_launch * L / (ms_per_step * 1e-3) / 1e9,
-                       "kernels_per_layer": gpu_launches / args.steps / L,
-                       "bracketed_pass": {"ms_per_step": bracketed_ms_per_step, "decode_launches": n_dec,
-                                          "decode_us_per_launch": dec_us, "append_launches": n_app,
-                                          "append_us_per_launch": (ms_app / n_app * 1e3) if n_app else None}},
-            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                         "frac": (achieved / peaks["hbm_gbs"]) if achieved else None, "traffic": traffic,
-                         "launch_us_in_stream": instream_us, "launch_us_isolated": dec_us,
-                         "achieved_isolated": isolated, "frac_isolated": (isolated / peaks["hbm_gbs"]) if isolated else None,
-                         "how": "achieved = algorithmic bytes per launch / (device time of the timed region / launches in it); "
-                                "the isolated figures bracket every launch with events in a second pass, which forbids the overlap",
-                         "kernel": "decode_tc_kernel (fused RoPE + append + paged GQA decode)", "algorithmic_bytes_per_launch": alg_bytes, "peak_source": peak_kind,
-                         "frac_of_nominal_8000": (achieved / 8000.0) if achieved else None},
+                       "kernels_per_layer": gpu_launches / K / L,
+                       "timed_region": {"repeats": len(repeats_ms), "steps_per_repeat": K, "device_s_total": sum(repeats_ms) / 1e3,
+                                        "ms_per_step_median": ms_per_step, "ms_per_step_min": min(repeats_ms) / K,
+                                        "ms_per_step_max": max(repeats_ms) / K,
+                                        "ms_per_step_x_sm_mhz": (ms_per_step * clocks["sm_mhz"]) if clocks.get("sm_mhz") else None,
+                                        "how": "exactly --steps steps per repeat between barrier + synchronize, every repeat from the same "
+                                               "sequence state; value is the median repeat (max over ranks per repeat)"},
+                       "e2e_repeats": len(e2e_repeats)},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": achieved / peak, "traffic": traffic,
+                         "launch_us_in_stream": instream_us,
+                         "launch_us_dependent": dep_us, "achieved_dependent": gbs(dep_us), "frac_dependent": gbs(dep_us) / peak,
+                         "launch_us_serial": serial_us, "achieved_serial": gbs(serial_us), "frac_serial": gbs(serial_us) / peak,
+                         "launch_us_isolated": dec_us, "achieved_isolated": gbs(dec_us) if n_dec else None,
+                         "frac_isolated": (gbs(dec_us) / peak) if n_dec else None,
+                         "how": "achieved = algorithmic bytes per launch / (device time of the timed region / launches in it), CUDA events on "
+                                "the launching stream.  in_stream: the 36 launches of a step have independent inputs and may overlap at their "
+                                "edges (programmatic dependent launch); dependent: every layer's queries and new K/V wait for the previous "
+                                "layer's launch, only its cached K/V streams early; serial: nothing of a launch but its set-up precedes the "
+                                "previous launch's completion; isolated: every launch between two events of its own (includes the idle time "
+                                "the events cost)",
+                         "kernel": "decode_tcp_kernel (fused RoPE + append + paged GQA decode, whole pages per copy)",
+                         "algorithmic_bytes_per_launch": alg_bytes, "peak_source": peak_kind,
+                         "frac_of_nominal_8000": achieved / 8000.0},
             "e2e": {"value": e2e_value, "unit": UNIT,
                     "h2d_bytes_per_step": int(plan_bytes + qh.numel() * 2 + kh.numel() * 2 + vh.numel() * 2),
                     "d2h_bytes_per_step": int(oh.numel() * 2 + 4)},
             "gpu_launches": int(gpu_launches),
             "clocks": clocks,
+            "config5": config5,
         }
         if world == 1 and not args.no_cpu_baseline:
             t1, cores, _ = cpu_sample(1, 1)
@@ -434,9 +474,165 @@ def run_gpu_arm(args):
             line["cpu_baseline"] = {"value": BATCH / (ts * L / layers), "unit": UNIT, "cores": cores, "kind": "port",
                                     "sample": desc}
         print(json.dumps(line))
-    ex.close()
     if dist is not None:
         dist.destroy_process_group()
+
+
+def run_config5(args, rank, local_rank, world, dist, peak):
+    """BASELINE config 5 on the GPUs of this run, one layer resident (36 layers of it are 193 GB):
+    (a) 256 sequences of U[8192,32768] tokens dealt longest-first over the ranks (strong scaling: the total is fixed),
+        one fused append + decode launch per rank and layer;
+    (b) one 131072-token sequence: on one GPU as a whole; on N > 1 GPUs split along the KV axis, every rank holding its
+        block range, partial-state decode + exchange over NVLink + merge through kriya_cuda_kvsplit_decode.  Before it is
+        timed, a small split case is compared with the CPU oracle on rank 0 (max_abs_err)."""
+    import torch
+
+    from kriya_rt_b200 import sharding
+    from kriya_rt_b200.executor import CudaExecutor
+
+    dev = torch.device("cuda", local_rank)
+    gen = torch.Generator(device="cuda").manual_seed(7 + rank)
+    reps = 10
+
+    def fill_all(ex):
+        for view in ex.layer_cache_views(0):
+            flat = view.view(-1)
+            chunk = 1 << 26
+            for s in range(0, flat.numel(), chunk):
+                n = min(chunk, flat.numel() - s)
+                flat[s:s + n] = torch.randn(n, device="cuda", generator=gen).to(torch.bfloat16).view(torch.int16)
+
+    def rnd(*shape):
+        return torch.randn(*shape, device="cuda", generator=gen).to(torch.bfloat16).view(torch.int16)
+
+    def reduce_max_sum(us, nbytes):
+        t = torch.tensor([us, float(nbytes)], device="cuda", dtype=torch.float64)
+        if dist is None:
+            return float(t[0]), float(t[1])
+        tmax, tsum = t.clone(), t.clone()
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        dist.all_reduce(tsum, op=dist.ReduceOp.SUM)
+        return float(tmax[0]), float(tsum[1])
+
+    res = {}
+    # ---- (a) sequences partitioned over the ranks -------------------------------------------------------------
+    lengths = np.random.default_rng(2005).integers(8192, 32768 + 1, size=256)
+    mine = sharding.assign_sequences(lengths, world)[rank]
+    ctx = lengths[mine]
+    nblocks = int(((ctx + 16) // 16).sum()) + 16
+    batch = W.make_decode_batch(SHAPE, ctx, nblocks, seed=2005 + rank)
+    ex = CudaExecutor(num_layers=1, num_kv_blocks=nblocks, block_size_tokens=16, num_q_heads=16, num_kv_heads=2, head_dim=128,
+                      device=local_rank, rope_theta=SHAPE.rope_theta, rope_max_seq_len=32768 + 64, max_batch_rows=256,
+                      max_page_indices=nblocks, max_tiles=65536)
+    fill_all(ex)  # the whole pool holds N(0,1) data
+    n = len(mine)
+    q, k, v = rnd(n, 16, 128), rnd(n, 2, 128), rnd(n, 2, 128)
+    out = torch.zeros_like(q)
+    torch.cuda.synchronize()
+    ex.upload_schedule_plan(batch, batch.positions)
+    rp, gp = ex.rope_params(), ex.gqa_params()
+    stream = torch.cuda.ExternalStream(ex.stream_ptr, device=dev)
+    for _ in range(3):
+        ex.append_decode(0, q, k, v, out, rp, gp)
+    ex.sync()
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(reps):
+        ex.append_decode(0, q, k, v, out, rp, gp)
+    e1.record(stream)
+    ex.sync()
+    torch.cuda.synchronize()
+    us, total_bytes = reduce_max_sum(e0.elapsed_time(e1) / reps * 1e3, batch.kv_bytes_per_layer)
+    res["sequences_partitioned"] = {
+        "sequences": 256, "ctx": "U[8192,32768]", "assignment": "longest first", "us_per_layer": us, "kv_bytes_all_gpus": total_bytes,
+        "kv_gbs_aggregate": total_bytes / (us * 1e-6) / 1e9, "kv_gbs_per_gpu": total_bytes / world / (us * 1e-6) / 1e9,
+        "frac_of_hbm_peak_per_gpu": total_bytes / world / (us * 1e-6) / 1e9 / peak,
+        "tokens_per_s_36_layers": 256 / (us * 36e-6), "launches_timed": reps, "pool": "whole pool filled with N(0,1)"}
+    ex.close()
+    del q, k, v, out
+    torch.cuda.empty_cache()
+
+    # ---- (b) one 131072-token sequence ------------------------------------------------------------------------
+    def kvsplit_case(tokens, check):
+        nb = (tokens + 15) // 16
+        b, e = sharding.kv_axis_ranges([nb], world)[rank]
+        b0, e0_ = int(b[0]), int(e[0])
+        n_local = e0_ - b0
+        exs = CudaExecutor(num_layers=1, num_kv_blocks=max(n_local, 1), block_size_tokens=16, num_q_heads=16, num_kv_heads=2,
+                           head_dim=128, device=local_rank, max_page_indices=nb, rope_max_seq_len=4096)
+        local_ids = np.random.default_rng(90 + rank).permutation(max(n_local, 1))[:n_local]
+        if check:
+            rng = np.random.default_rng(81)  # the same stream on every rank: the whole K/V exists on the host only
+            kk = W.normal16(rng, (nb, 16, 2, 128), W.BF16)
+            vv = W.normal16(rng, (nb, 16, 2, 128), W.BF16)
+            q16 = W.normal16(rng, (1, 16, 128), W.BF16)
+            kview, vview = exs.layer_cache_views(0)
+            ids = torch.from_numpy(local_ids.astype(np.int64)).cuda()
+            kview[ids] = torch.from_numpy(kk[b0:e0_].view(np.int16)).cuda()
+            vview[ids] = torch.from_numpy(vv[b0:e0_].view(np.int16)).cuda()
+            qd = torch.from_numpy(q16.view(np.int16)).cuda()
+        else:
+            fill_all(exs)
+            qd = rnd(1, 16, 128)
+        table = sharding.local_block_table(np.zeros(nb), b0, e0_, local_ids)
+        outd = torch.zeros_like(qd)
+        torch.cuda.synchronize()
+        exs.plan_upload([0, nb], table, [tokens - (nb - 1) * 16], None, [tokens - 1])
+        exs.plan_set_ranges(b, e)
+        gps = exs.gqa_params()
+        if world > 1:
+            handles = [None] * world
+            dist.all_gather_object(handles, exs.comm_export(1))
+            exs.comm_init(rank, handles)
+            call = lambda: exs.kvsplit_decode(0, qd, outd, gps)  # noqa: E731
+        else:
+            call = lambda: exs.paged_gqa_decode(0, qd, outd, gps)  # noqa: E731
+        if check:
+            call()
+            exs.sync()
+            err = None
+            if rank == 0:
+                from oracle import c_oracle as O
+
+                p = O.GqaParams(16, 2, 128, 16, 16, 1, float(np.float32(1.0) / np.sqrt(np.float32(128))), 0.0)
+                _, ref = O.decode(q16, kk, vv, [0, nb], np.arange(nb), [tokens - (nb - 1) * 16], p, W.BF16)
+                err = float(np.abs(W.from_storage(outd.cpu().numpy().view(np.uint16), W.BF16) - ref).max())
+            if dist is not None:
+                dist.barrier()
+            exs.close()
+            return err
+        st = torch.cuda.ExternalStream(exs.stream_ptr, device=dev)
+        for _ in range(5):
+            call()
+        exs.sync()
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+        a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        n_calls = 50
+        a0.record(st)
+        for _ in range(n_calls):
+            call()
+        a1.record(st)
+        exs.sync()
+        torch.cuda.synchronize()
+        us_l, _ = reduce_max_sum(a0.elapsed_time(a1) / n_calls * 1e3, 0)
+        exs.close()
+        return us_l
+
+    err = kvsplit_case(16384 + 5, True)
+    us_split = kvsplit_case(131072, False)
+    res["one_sequence_131072"] = {
+        "n_gpus": world, "us_per_layer": us_split,
+        "how": ("whole sequence on one GPU, one decode launch per layer" if world == 1 else
+                "KV axis split over the ranks: partial-state decode + one exchange kernel (peer stores into every rank's buffer "
+                "over NVLink, bounded wait, merge) per layer through kriya_cuda_kvsplit_decode; no collective library"),
+        "kv_bytes_per_gpu": 131072 * 1024 // world, "max_abs_err": err,
+        "check": "16389-token sequence split the same way, against the CPU oracle on rank 0 (bar 1e-2 for bf16)"}
+    return res
 
 
 def run_kernel_case(args):
@@ -517,15 +713,18 @@ def run_kernel_case(args):
         gp = ex.gqa_params()
         rows = 16
         local = torch.empty(rows * 130, device="cuda")
-        gathered = torch.empty(max(world, 1), rows * 130, device="cuda")
         stream = torch.cuda.ExternalStream(ex.stream_ptr)
         torch.cuda.synchronize()
 
         ex.plan_set_ranges(b, e)  # once per plan; every layer re-uses the split
+        if world > 1:
+            handles = [None] * world
+            dist.all_gather_object(handles, ex.comm_export(1))
+            ex.comm_init(rank, handles)
 
         def one(gather=True):
             if world > 1 and gather:
-                sharding.kv_split_decode(ex, 0, q, None, None, out, gp, scratch=(local, gathered))
+                ex.kvsplit_decode(0, q, out, gp)  # partial decode + exchange over NVLink + merge, all behind the C ABI
             else:
                 ex.paged_gqa_decode_partial(0, q, None, None, local[:rows], local[rows:2 * rows], local[2 * rows:], gp)
                 ex.merge_packed_states(local, 1, rows, out)
@@ -553,7 +752,7 @@ def run_kernel_case(args):
             print(json.dumps({"case": case, "n_gpus": world, "tokens": tokens, "us_per_layer": res["with_gather"],
                               "us_per_layer_without_gather": res["local_only"],
                               "kv_bytes_per_gpu": n_local * 16 * 1024,
-                              "note": "CUDA events on the executor's stream, max over ranks; one all-gather of Hq*(D+2) floats per rank per layer"}))
+                              "note": "CUDA events on the executor's stream, max over ranks; the exchange is one kernel per rank and layer (peer stores over NVLink, bounded wait, merge)"}))
         ex.close()
         if world > 1:
             dist.destroy_process_group()
@@ -576,9 +775,11 @@ def run_kernel_case(args):
         ex = CudaExecutor(num_layers=1, num_kv_blocks=nblocks, block_size_tokens=16, num_q_heads=16, num_kv_heads=2,
                           head_dim=128, device=torch.cuda.current_device(), rope_theta=SHAPE.rope_theta, rope_max_seq_len=32768 + 64,
                           max_batch_rows=256, max_page_indices=nblocks, max_tiles=65536)
-        for view in ex.layer_cache_views(0):  # values do not matter for timing; keep the fill cheap but finite
-            nfill = min(1 << 24, view.numel())
-            view.view(-1)[:nfill].copy_(torch.randn(nfill, device="cuda", generator=gen).to(torch.bfloat16).view(torch.int16))
+        for view in ex.layer_cache_views(0):  # the whole pool holds N(0,1) data
+            flat = view.view(-1)
+            for s0 in range(0, flat.numel(), 1 << 26):
+                nfill = min(1 << 26, flat.numel() - s0)
+                flat[s0:s0 + nfill] = torch.randn(nfill, device="cuda", generator=gen).to(torch.bfloat16).view(torch.int16)
         n = len(mine)
         q, k, v = rnd(n, 16, 128), rnd(n, 2, 128), rnd(n, 2, 128)
         out = torch.zeros_like(q)
@@ -736,8 +937,6 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--serial-layers", action="store_true",
-                    help="keep the layers' launches of a step strictly serialised (default: they may overlap at their edges)")
     ap.add_argument("--case-long-seqs", type=int, default=256, help="sequences in the decode_long kernel case")
     ap.add_argument("--case-seqs", type=int, default=8, help="prompts in the prefill_batch kernel case")
     ap.add_argument("--kernel-case", default=None, choices=["decode", "decode_fused", "decode_long", "prefill", "prefill_batch", "append", "copy", "kvsplit", "tree_verify"],

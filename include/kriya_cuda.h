@@ -191,6 +191,39 @@ int32_t kriya_cuda_merge_states(kriya_cuda_ctx* ctx, const float* m_dev, const f
 int32_t kriya_cuda_merge_packed_states(kriya_cuda_ctx* ctx, const float* packed_dev, uint32_t parts,
                                        uint32_t rows_times_heads, void* out_dev);
 
+/* ---- one long sequence split along the KV axis over the GPUs of one box ----------------------------------------
+ * The reference is single-GPU (crates/kriya-scheduler/src/orca_engine.rs:21-24: one ColocatedHybrid role); these entry
+ * points carry its split-K design (paged_gqa_and_deltanet.metal:328-342,1493-1524) across devices.  Every rank (one
+ * context per GPU, in one process or in several) holds a contiguous block range of each row in its own pool.  Set-up, once:
+ *   1. every rank calls kriya_cuda_comm_export() and hands the 128-byte handle to all other ranks by whatever channel
+ *      the host has (the handle is plain bytes);
+ *   2. every rank calls kriya_cuda_comm_init() with the handles of all ranks, ordered by rank.
+ * Per step: kriya_cuda_plan_upload(), kriya_cuda_plan_set_ranges() with the rank's block range, then
+ * kriya_cuda_kvsplit_decode() per layer (or kriya_cuda_kvsplit_decode_step() for all layers).  All ranks must make the
+ * same sequence of kvsplit calls: the exchange pairs the n-th call of every rank.  The new token of a step is appended by
+ * the rank that owns the row's last block, with kriya_cuda_rope_kv_append, before the call.
+ * Data plane: no collective library.  After the partial-state decode one kernel stores the rank's (max, sum, output)
+ * states into its slot of an exchange buffer in every peer's own memory (plain peer stores over NVLink), then waits, with a
+ * bound of about a second, until the slots of all ranks in its OWN buffer carry this call's stamp, merges them and writes
+ * the normalised output.  A peer that never delivers ends the wait with KRIYA_CUDA_EXECUTION_ERROR from the next
+ * kriya_cuda_sync(); the context stays usable. */
+#define KRIYA_COMM_MAX_RANKS 8
+#define KRIYA_COMM_HANDLE_BYTES 128
+/* Allocates this context's exchange buffer for plans of up to `max_rows` rows (set-up path: this allocates) and writes its
+ * handle (KRIYA_COMM_HANDLE_BYTES bytes) to handle_out. */
+int32_t kriya_cuda_comm_export(kriya_cuda_ctx* ctx, uint32_t max_rows, void* handle_out);
+/* Maps the exchange buffers of all ranks: `handles` holds nranks handles of KRIYA_COMM_HANDLE_BYTES bytes each, ordered
+ * by rank; handles[rank] must be this context's own.  Contexts of other processes are opened through CUDA IPC, contexts
+ * of this process through peer access. */
+int32_t kriya_cuda_comm_init(kriya_cuda_ctx* ctx, uint32_t nranks, uint32_t rank, const void* handles);
+/* Partial-state decode over the rank's block ranges of the current plan, exchange, merge: out [rows][Hq][D] holds the
+ * attention over the WHOLE rows on every rank.  Queued on the context's stream; the call does not wait. */
+int32_t kriya_cuda_kvsplit_decode(kriya_cuda_ctx* ctx, uint32_t layer, const void* q_dev, void* out_dev,
+                                  const kriya_bsr_gqa_params* params);
+/* The same for every layer of the context in one call: q and out are [layers][rows][Hq][D]. */
+int32_t kriya_cuda_kvsplit_decode_step(kriya_cuda_ctx* ctx, const void* q_dev, void* out_dev,
+                                       const kriya_bsr_gqa_params* params);
+
 /* bsr_paged_gqa_prefill_stage1 / _bq8 / bsr_paged_gqa_tiled_mma_prefill
  * (paged_gqa_and_deltanet.metal:508-847,851-1192,1206-1468; selection and dispatch enc:4262-4311).
  * Causal attention of a chunk of `num_tokens` queries of ONE sequence (row 0 of the current plan is
@@ -237,11 +270,17 @@ int32_t kriya_cuda_append_decode(kriya_cuda_ctx* ctx, uint32_t layer, const void
                                  const void* v_in_dev, void* out_dev, void* q_rope_out_dev,
                                  const kriya_rope_kv_write_params* rope, const kriya_bsr_gqa_params* gqa);
 /* How kriya_cuda_decode_step / _host run a step.  Bit 0 (default set): use the fused launch where it applies; the step
- * then leaves q un-rotated, while with bit 0 clear q is rotated in place by the separate append kernel.  Bit 1
- * (default clear): keep the layers' launches strictly serialised; by default, from the second layer of a step on,
- * a fused launch may begin while the previous layer's last thread blocks drain (programmatic dependent launch):
- * layers of a step share only the split-row scratch, which the kernel does not touch before the previous grid has
- * completed.  Pass 1 for the default, 0 for separate kernels, 3 for fused but serialised. */
+ * then leaves q un-rotated, while with bit 0 clear q is rotated in place by the separate append kernel.  Bits 1-2 say how
+ * the fused launch of layer l+1 relates to that of layer l (the first layer of a call is always an ordinary launch):
+ *   0 (default)  the layers' inputs are independent and complete when the call is made, so a launch may begin while the
+ *                previous layer's last thread blocks drain (programmatic dependent launch) and waits for nothing;
+ *   1 (value 3)  serialised: a launch may be set up early (barriers, tensor memory) but reads and writes nothing before
+ *                the previous layer has completed;
+ *   2 (value 5)  layer l+1's activations depend on layer l (as in a model, where a projection sits between two attention
+ *                layers): queries, the new K/V rows and outputs wait for the previous launch, the stream of cached K/V,
+ *                which is older, starts at once;
+ *   3 (value 7)  ordinary launches, one after the other.
+ * Pass 1 for the default, 0 for separate kernels. */
 int32_t kriya_cuda_set_fused_append(kriya_cuda_ctx* ctx, int32_t enable);
 
 /* One decode step over ALL layers with device activations: for layer l = 0..num_layers-1, append then
@@ -268,10 +307,30 @@ int32_t kriya_cuda_decode_step_host_begin(kriya_cuda_ctx* ctx, const void* q_hos
                                           const kriya_bsr_gqa_params* gqa);
 int32_t kriya_cuda_decode_step_host_end(kriya_cuda_ctx* ctx, uint32_t timeout_ms);
 
-/* Chooses between the two decode kernels, which compute the same result: 0 = by shape (tensor-core kernel for
- * head_dim 128, CUDA-core kernel otherwise), 1 = CUDA-core kernel, 2 = tensor-core kernel.  The reference picks
- * kernels by shape in the same way (enc:4262-4281); this switch exists so that tests can hold both to the oracle. */
+/* Chooses between the decode kernels, which compute the same result: 0 = by shape (for head_dim 128 a tensor-core kernel:
+ * the one that moves whole pages of both KV heads with one copy where the shape is 2 KV heads, the one that moves one KV
+ * head per copy otherwise; the CUDA-core kernel for head_dim 64), 1 = CUDA-core kernel, 2 = a tensor-core kernel (as 0,
+ * refused where there is none), 3 = the one-KV-head-per-copy tensor-core kernel.  The reference picks kernels by shape in
+ * the same way (enc:4262-4281); this switch exists so that tests can hold every kernel to the oracle.  The current plan's
+ * work lists are cut for one kernel: upload the plan again after changing the path. */
 int32_t kriya_cuda_set_decode_path(kriya_cuda_ctx* ctx, int32_t path);
+
+/* Every wait inside a kernel of this library (on a copy, on another warp, on another thread block's partial state) is
+ * bounded: when the limit passes, the kernel records a status word and returns, and the next kriya_cuda_sync() reports
+ * KRIYA_CUDA_EXECUTION_ERROR ("a bounded wait inside a kernel expired") with the context still usable - the CUDA
+ * counterpart of wait_for_gpu's bounded polling (enc:2070-2109).  The limit is 2 s unless set here (tensor-core decode
+ * kernels; the other kernels keep 2 s). */
+int32_t kriya_cuda_set_wait_limit_us(kriya_cuda_ctx* ctx, uint32_t limit_us);
+/* Queues a one-block kernel that waits, with the context's limit, on a barrier nobody arrives at: the expiry path
+ * exercised on purpose and without any fault.  The next kriya_cuda_sync() must return KRIYA_CUDA_EXECUTION_ERROR. */
+int32_t kriya_cuda_selftest_wait_expiry(kriya_cuda_ctx* ctx);
+
+/* AttentionMaskVariant::SlidingWindowCausal { window_size } (crates/kriya-core/src/descriptor.rs:63-70; declared by the
+ * reference, read by none of its kernels).  With window_size > 0 a query at position p attends keys p + 1 - window_size
+ * ..= p (itself included) in every following decode and prefill call; 0 (the default) is the plain causal mask.  Decode
+ * rows then start at the window's first block, so the blocks in front of it are not read.  The setting takes part in
+ * the work split: upload the plan again after changing it. */
+int32_t kriya_cuda_set_attention_window(kriya_cuda_ctx* ctx, uint32_t window_size);
 
 /* Per-kernel device timing.  While enabled, every decode (kind 0) and append (kind 1) launch is bracketed
  * by CUDA events on the context's stream; kriya_cuda_timing_read() waits for the stream, adds up the
@@ -280,15 +339,17 @@ int32_t kriya_cuda_timing_enable(kriya_cuda_ctx* ctx, int32_t enable);
 int32_t kriya_cuda_timing_read(kriya_cuda_ctx* ctx, uint32_t kind, uint64_t* out_launches, double* out_total_ms);
 
 /* Paged GQA decode without a context and without any allocation.  No counterpart in the reference: it exists for
- * hosts that may not call cudaMalloc (a process whose device memory is handed out up front by its own arena, a plugin
- * inside such a process, code running inside a stream capture), and which therefore cannot own a kriya_cuda_ctx.
+ * hosts that may not call cudaMalloc (a process whose device memory is handed out up front by its own arena, or a plugin
+ * inside such a process), and which therefore cannot own a kriya_cuda_ctx.
  * The caller passes every input and the output; the split-KV scratch (partial states, tickets, work list, status
  * word) lives in a fixed array of about 4.3 MB inside the library image, present on every GPU that loads the library
  * until the process exits.  Limits, rejected with KRIYA_CUDA_INVALID_INPUT and a message in `err`: at most 256 plan
  * rows, num_q_heads * head_dim <= 2048, at most 512 work items (long batches are cut coarser to fit).
  *   - q_dev / out_dev [rows][Hq][D], cache_*_dev one layer's pools [num_kv_blocks][16][Hkv][D], plan arrays as for
- *     kriya_cuda_plan_upload but already on the device; page_indptr_host is the same indptr on the host (the work
- *     split is computed from it).  Work is queued on `stream` (a cudaStream_t, may be 0); the call does not wait.
+ *     kriya_cuda_plan_upload but already on the device; page_indptr_host is the same indptr on the host: the number of
+ *     work items (the launch's grid) is computed from it, the items themselves are written on the device from
+ *     page_indptr_dev, so the two must hold the same values.  Work is queued on `stream` (a cudaStream_t, may be 0);
+ *     the call does not wait and nothing it queues reads host memory.  The caller's current device is left as it was.
  *   - The first call on a device looks up the array's device address; make that first call outside any stream
  *     capture.  Every call shares the array and starts by clearing its tickets and status word, so two calls whose
  *     kernels can overlap on the GPU (different streams, or different host threads) race: serialise them.

@@ -141,12 +141,19 @@ CUDA_SYMBOLS = {
                                                 C.POINTER(BsrGqaParams)]),
     "kriya_cuda_decode_step_host_end": (C.c_int32, [_VP, C.c_uint32]),
     "kriya_cuda_set_decode_path": (C.c_int32, [_VP, C.c_int32]),
+    "kriya_cuda_set_attention_window": (C.c_int32, [_VP, C.c_uint32]),
+    "kriya_cuda_set_wait_limit_us": (C.c_int32, [_VP, C.c_uint32]),
+    "kriya_cuda_selftest_wait_expiry": (C.c_int32, [_VP]),
     "kriya_cuda_timing_enable": (C.c_int32, [_VP, C.c_int32]),
     "kriya_cuda_timing_read": (C.c_int32, [_VP, C.c_uint32, C.POINTER(C.c_uint64), C.POINTER(C.c_double)]),
     "kriya_cuda_paged_gqa_decode_static": (C.c_int32, [C.c_int32, _VP, C.c_uint32, _VP, _VP, _VP, C.c_uint32, _VP, _VP,
                                                        _VP, _VP, C.c_uint32, _VP, C.POINTER(BsrGqaParams), C.c_char_p,
                                                        C.c_size_t]),
     "kriya_cuda_launch_count": (C.c_uint64, [_VP]),
+    "kriya_cuda_comm_export": (C.c_int32, [_VP, C.c_uint32, _VP]),
+    "kriya_cuda_comm_init": (C.c_int32, [_VP, C.c_uint32, C.c_uint32, _VP]),
+    "kriya_cuda_kvsplit_decode": (C.c_int32, [_VP, C.c_uint32, _VP, _VP, C.POINTER(BsrGqaParams)]),
+    "kriya_cuda_kvsplit_decode_step": (C.c_int32, [_VP, _VP, _VP, C.POINTER(BsrGqaParams)]),
     "kriya_cuda_rope_inplace": (C.c_int32, [_VP, _VP, _VP, _VP, _VP, C.c_uint32, C.POINTER(RopeKvWriteParams)]),
     "kriya_cuda_tree_verify": (C.c_int32, [_VP, C.c_uint32, _VP, _VP, _VP, _VP, _VP, C.POINTER(TreeVerifyParams)]),
 }

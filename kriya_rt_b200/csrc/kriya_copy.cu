@@ -69,3 +69,25 @@ cudaError_t kriya_launch_slot_write(uint8_t* cache_k, uint8_t* cache_v, const vo
                                                     triples_dev, n, num_blocks, status);
     return cudaGetLastError();
 }
+
+// ---- self-test of the bounded waits --------------------------------------------------------------------------------
+// Every wait inside this library's kernels is bounded: when its limit passes, the kernel records a status word and
+// returns instead of hanging.  This one-block kernel exercises exactly that path without any fault: it initialises a
+// barrier that nobody ever arrives at, waits on it with the given limit and reports the expiry.
+namespace kriya {
+__global__ void wait_selftest_kernel(uint32_t* status, uint64_t wait_ns) {
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        mbar_fence_init();
+    }
+    __syncthreads();
+    const bool ok = warp_wait(&bar, 0u, wait_ns);
+    if (!ok && threadIdx.x == 0) atomicMax(status, uint32_t(KRIYA_DEV_WAIT_EXPIRED));
+}
+}  // namespace kriya
+
+cudaError_t kriya_launch_wait_selftest(uint32_t* status, uint64_t wait_ns, cudaStream_t s) {
+    kriya::wait_selftest_kernel<<<1, 32, 0, s>>>(status, wait_ns);
+    return cudaGetLastError();
+}

@@ -19,7 +19,7 @@
 namespace {
 
 thread_local std::string g_create_error;
-constexpr uint32_t kScratchSets = 4;  // independent split-row scratch sets (see launch_decode)
+constexpr uint32_t kTcScratchSets = 4;  // split-run scratch sets of the tensor-core decode kernel (see launch_decode)
 
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
@@ -36,6 +36,7 @@ void destroy(kriya_cuda_ctx* c) {
     if (c->stream) cudaStreamSynchronize(c->stream);
     if (c->copy_stream) cudaStreamSynchronize(c->copy_stream);
     if (c->copy_stream_out) cudaStreamSynchronize(c->copy_stream_out);
+    kriya_comm_destroy(c);
     cudaFree(c->pool_k);
     cudaFree(c->pool_v);
     cudaFree(c->rope_table);
@@ -43,6 +44,9 @@ void destroy(kriya_cuda_ctx* c) {
     cudaFree(c->part_o);
     cudaFree(c->part_ml);
     cudaFree(c->part_counter);
+    cudaFree(c->tc_ll_o);
+    cudaFree(c->tc_ll_ml);
+    cudaFree(c->tc_set_done);
     cudaFree(c->d_status);
     cudaFree(c->d_act);
     cudaFree(c->d_pairs);
@@ -70,12 +74,26 @@ void destroy(kriya_cuda_ctx* c) {
 
 // Splits every plan row into near-equal contiguous block ranges so that about `target` work items of
 // similar size exist, largest first.  `begin`/`end` (optional) restrict each row to a block range.
-uint32_t build_work(const int32_t* indptr, uint32_t rows, const uint32_t* begin, const uint32_t* end, uint32_t target,
-                    uint32_t min_chunk, KriyaDecodeWork* out, uint32_t cap) {
+// First token of row r inside a sliding window of `window` tokens that ends at the row's last token (0 = no window).
+inline uint32_t window_first_token(const int32_t* indptr, const int32_t* last_len, uint32_t block_size, uint32_t r, uint32_t window) {
+    if (window == 0u) return 0u;
+    const uint32_t nb = uint32_t(indptr[r + 1] - indptr[r]);
+    if (nb == 0u) return 0u;
+    const uint64_t tokens = uint64_t(nb - 1u) * block_size + uint32_t(std::max(last_len[r], 1));
+    return tokens > window ? uint32_t(tokens - window) : 0u;
+}
+
+uint32_t build_work(const int32_t* indptr, const int32_t* last_len, uint32_t block_size, uint32_t window, uint32_t rows,
+                    const uint32_t* begin, const uint32_t* end, uint32_t target, uint32_t min_chunk, KriyaDecodeWork* out,
+                    uint32_t cap) {
     uint64_t total = 0;
+    auto first_block = [&](uint32_t r, uint32_t nb) {  // the row's range begins no earlier than the window does
+        const uint32_t wb = window_first_token(indptr, last_len, block_size, r, window) / block_size;
+        return std::min(std::max(begin ? begin[r] : 0u, wb), nb);
+    };
     for (uint32_t r = 0; r < rows; ++r) {
         const uint32_t nb = uint32_t(indptr[r + 1] - indptr[r]);
-        const uint32_t b = begin ? std::min(begin[r], nb) : 0u;
+        const uint32_t b = first_block(r, nb);
         const uint32_t e = end ? std::min(end[r], nb) : nb;
         total += e > b ? e - b : 0u;
     }
@@ -84,7 +102,7 @@ uint32_t build_work(const int32_t* indptr, uint32_t rows, const uint32_t* begin,
     uint32_t n = 0, slot = 0;
     for (uint32_t r = 0; r < rows; ++r) {
         const uint32_t nb = uint32_t(indptr[r + 1] - indptr[r]);
-        const uint32_t b = begin ? std::min(begin[r], nb) : 0u;
+        const uint32_t b = first_block(r, nb);
         const uint32_t e = end ? std::min(end[r], nb) : nb;
         const uint32_t len = e > b ? e - b : 0u;
         const uint32_t parts = std::max(1u, (len + chunk - 1) / chunk);
@@ -93,6 +111,7 @@ uint32_t build_work(const int32_t* indptr, uint32_t rows, const uint32_t* begin,
         for (uint32_t k = 0; k < parts; ++k) {
             KriyaDecodeWork w{};
             w.req = r;
+            w.tok_first = window_first_token(indptr, last_len, block_size, r, window);
             w.blk_begin = b + std::min(k * size, len);
             w.blk_end = b + std::min((k + 1) * size, len);
             w.slot = slot + k;
@@ -127,32 +146,37 @@ uint32_t tc_min_tiles_per_cta() {
 
 uint32_t build_tc_segments(const int32_t* indptr, const int32_t* last_len, uint32_t block_size, uint32_t rows, uint32_t hkv,
                            const uint32_t* begin, const uint32_t* end, uint32_t ctas, uint32_t TP, KriyaTcSeg* out, uint32_t cap,
-                           uint32_t* ptr) {  // TP = pages per tile of the kernel variant the list is for
+                           uint32_t* ptr, uint32_t min_tiles, uint32_t window) {  // TP = pages per tile of the kernel variant the list is for
     uint64_t total = 0;
+    auto first_block = [&](uint32_t r, uint32_t nb) {  // the row's range begins no earlier than the sliding window does
+        const uint32_t wb = window_first_token(indptr, last_len, block_size, r, window) / block_size;
+        return std::min(std::max(begin ? begin[r] : 0u, wb), nb);
+    };
     for (uint32_t r = 0; r < rows; ++r) {
         const uint32_t nb = uint32_t(indptr[r + 1] - indptr[r]);
-        const uint32_t b = begin ? std::min(begin[r], nb) : 0u;
+        const uint32_t b = first_block(r, nb);
         const uint32_t e = end ? std::min(end[r], nb) : nb;
         if (e > b) total += uint64_t((e + TP - 1) / TP - b / TP + kRunStartWeight) * hkv;
     }
     // A short plan is not spread over every CTA: a CTA that streams only a tile or two costs its start-up latency all
     // the same, and every extra piece of a run is one more partial state for the run's merge to read.
     const uint32_t all_ctas = ctas;
-    ctas = uint32_t(std::min<uint64_t>(ctas, std::max<uint64_t>(1, (total + tc_min_tiles_per_cta() - 1) / tc_min_tiles_per_cta())));
+    ctas = uint32_t(std::min<uint64_t>(ctas, std::max<uint64_t>(1, (total + min_tiles - 1) / min_tiles)));
     uint32_t n = 0, slot = 0, cta = 0;
     uint64_t unit = 0;  // weight consumed so far
     auto cta_end = [&](uint32_t c) { return total * (c + 1) / ctas; };  // first unit NOT owned by cta c
     ptr[0] = 0;
     for (uint32_t r = 0; r < rows; ++r) {
         const uint32_t nb = uint32_t(indptr[r + 1] - indptr[r]);
-        const uint32_t b = begin ? std::min(begin[r], nb) : 0u;
+        const uint32_t b = first_block(r, nb);
         const uint32_t e = end ? std::min(end[r], nb) : nb;
         const uint32_t tbl = uint32_t(indptr[r]);
         const uint32_t row_tokens = nb ? (nb - 1u) * block_size + uint32_t(std::max(last_len[r], 1)) : 0u;
+        const uint32_t tok_first = window_first_token(indptr, last_len, block_size, r, window);
         for (uint32_t h = 0; h < hkv; ++h) {
             if (e <= b) {  // empty run: one zero-length record so that its output is still written
                 if (n + 1 > cap) return UINT32_MAX;
-                out[n++] = KriyaTcSeg{r, h, b, b, slot, slot, 1u, tbl, row_tokens, {0u, 0u, 0u}};
+                out[n++] = KriyaTcSeg{r, h, b, b, slot, slot, 1u, tbl, row_tokens, tok_first, {0u, 0u}};
                 slot += 1;
                 continue;
             }
@@ -173,7 +197,7 @@ uint32_t build_tc_segments(const int32_t* indptr, const int32_t* last_len, uint3
                 }
                 if (n + 1 > cap) return UINT32_MAX;
                 out[n++] = KriyaTcSeg{r, h, std::max(b, t * TP), std::min(e, (t + take) * TP), slot++, first_slot, 0u, tbl,
-                                      row_tokens, {0u, 0u, 0u}};
+                                      row_tokens, tok_first, {0u, 0u}};
                 t += take;
                 unit += take + lead;
                 lead = 0;
@@ -182,6 +206,12 @@ uint32_t build_tc_segments(const int32_t* indptr, const int32_t* last_len, uint3
         }
     }
     while (cta < all_ctas) ptr[++cta] = n;
+    // A CTA whose list begins with the continuation of a run that started in an earlier CTA takes that piece last.  The
+    // run's last piece finishes the run (it gathers the other pieces' states): taken last, it finds them published.  It
+    // is also the piece that reads the token the same launch appends, which is then in the cache long before.
+    for (uint32_t k = 0; k < all_ctas; ++k)
+        if (ptr[k + 1] - ptr[k] > 1u && out[ptr[k]].slot != out[ptr[k]].first_slot)
+            std::rotate(out + ptr[k], out + ptr[k] + 1, out + ptr[k + 1]);
     return n;
 }
 
@@ -195,16 +225,30 @@ uint32_t max_parts_of(const KriyaTcSeg* segs, uint32_t n) {
     return m;
 }
 
-bool choose_tc64(const kriya_cuda_ctx* c, const int32_t* indptr, uint32_t rows, const uint32_t* begin, const uint32_t* end) {
-    if (c->tc_force == 64) return true;
-    if (c->tc_force == 128) return false;
+// Which tensor-core decode kernel serves a plan (see kriya_cuda_ctx::tc_variant).  The whole-page kernel is taken wherever
+// the shape allows it.  Between the two one-head-per-copy builds, the 64-token-tile build (two CTAs per SM) streams faster
+// but pays its per-CTA costs twice as often, so it is taken when every SM has a long stream ahead of it.
+int choose_tc_variant(const kriya_cuda_ctx* c, const int32_t* indptr, uint32_t rows, const uint32_t* begin, const uint32_t* end) {
+    if (c->tc_force == 64) return 1;
+    if (c->tc_force == 128) return 0;
+    if (c->tcp_ok && c->decode_path != 3) return 2;
     uint64_t tiles = 0;  // 128-token tiles of the whole launch
     for (uint32_t r = 0; r < rows; ++r) {
         const uint32_t nb = uint32_t(indptr[r + 1] - indptr[r]);
         const uint32_t b = begin ? std::min(begin[r], nb) : 0u, e = end ? std::min(end[r], nb) : nb;
         if (e > b) tiles += uint64_t((e - b + 7) / 8) * c->cfg.num_kv_heads;
     }
-    return tiles >= uint64_t(c->tc64_min_tiles) * uint64_t(c->sm_count);
+    return tiles >= uint64_t(c->tc64_min_tiles) * uint64_t(c->sm_count) ? 1 : 0;
+}
+struct TcVariantGeometry {
+    uint32_t ctas, pages_per_tile, runs_per_row, min_tiles;
+};
+TcVariantGeometry tc_geometry(const kriya_cuda_ctx* c, int variant) {
+    const uint32_t sms = uint32_t(c->sm_count);
+    // the fewest tiles a CTA is given are the same 64 KB of K/V per unit of tc_min_tiles_per_cta() for every variant
+    if (variant == 2) return {sms, kriya_decode_tcp_pages_per_tile(), 1u, 2u * tc_min_tiles_per_cta()};
+    if (variant == 1) return {sms * kriya_decode_tc_ctas_per_sm_t64(), kriya_decode_tc_pages_per_tile_t64(), c->cfg.num_kv_heads, tc_min_tiles_per_cta()};
+    return {sms * kriya_decode_tc_ctas_per_sm(), kriya_decode_tc_pages_per_tile(), c->cfg.num_kv_heads, tc_min_tiles_per_cta()};
 }
 
 int32_t check_layer(kriya_cuda_ctx* c, uint32_t layer) {
@@ -328,11 +372,9 @@ int32_t launch_decode(kriya_cuda_ctx* c, uint32_t layer, const void* q, void* ou
     a.last_len = c->plan_dev<int32_t>(c->off_last_len);
     a.work = c->plan_dev<KriyaDecodeWork>(range_list ? c->off_range : c->off_work);
     a.out = out;
-    // a free-running overlapped launch (see decode_layers) gets the scratch set of its layer; everything else set 0
-    const uint32_t set = fused.overlap_previous == 2u ? layer % kScratchSets : 0u;
-    a.part_o = c->part_o + set * c->set_o_floats;
-    a.part_ml = c->part_ml + set * c->set_ml_floats;
-    a.counters = c->part_counter + set * c->set_counters;
+    a.part_o = c->part_o;
+    a.part_ml = c->part_ml;
+    a.counters = c->part_counter;
     a.state_m = sm;
     a.state_l = sl;
     a.state_o = so;
@@ -343,21 +385,41 @@ int32_t launch_decode(kriya_cuda_ctx* c, uint32_t layer, const void* q, void* ou
     a.num_kv_heads = c->cfg.num_kv_heads;
     a.sm_scale = p->sm_scale;
     a.logit_softcap = p->logit_softcap;
+    a.wait_ns = c->wait_ns;
     TimingScope ts(c, 0);
     if (use_tc_decode(c)) {
         const uint32_t layer_row0 =
             uint32_t(size_t(layer) * c->layer_stride_bytes / (size_t(c->cfg.num_kv_heads) * c->cfg.head_dim * 2));
-        const bool t64 = range_list ? c->tc_t64_ranges : c->tc_t64;
-        const auto launch = t64 ? kriya_launch_decode_tc_t64 : kriya_launch_decode_tc;
-        const uint32_t grid = uint32_t(c->sm_count) * (t64 ? kriya_decode_tc_ctas_per_sm_t64() : kriya_decode_tc_ctas_per_sm());
+        const int variant = range_list ? c->tc_variant_ranges : c->tc_variant;
+        const uint32_t grid = tc_geometry(c, variant).ctas;
         // A run spread over many CTAs (one long row) is merged by a kernel of its own behind the launch; launches that
         // overlap with their neighbours keep the merge inside, the scratch-set rotation relies on it.
         const uint32_t max_parts = range_list ? c->tc_max_parts_ranges : c->tc_max_parts;
         const bool late = fused.overlap_previous == 0u && max_parts > kLateMergeParts;
-        KRIYA_CUDA_TRY(c, launch(a, c->plan_dev<KriyaTcSeg>(range_list ? c->off_tcseg2 : c->off_tcseg),
-                                 c->plan_dev<uint32_t>(range_list ? c->off_tcptr2 : c->off_tcptr), grid, c->tmap_k, c->tmap_v,
-                                 layer_row0, c->cfg.dtype, c->max_smem_optin, fused, late ? kLateMergeParts : UINT32_MAX,
-                                 range_list ? c->n_seg_ranges : c->n_seg, c->stream));
+        // Successive launches take the scratch sets in turn and stamp what they publish with their own number.  The launches
+        // of one step may overlap at their edges; a set comes round again kTcScratchSets launches later, and the kernel
+        // then checks the set's counter (every CTA of every earlier user has counted itself off) before it publishes.
+        if (++c->tc_epoch == 0u) c->tc_epoch = 1u;
+        const uint32_t set = c->tc_epoch % kTcScratchSets;
+        KriyaTcScratch sc;
+        sc.ll_o = c->tc_ll_o + size_t(set) * c->tc_set_o_bytes;
+        sc.ll_ml = c->tc_ll_ml + size_t(set) * c->tc_set_ml_bytes;
+        sc.set_done = c->tc_set_done + set * 16u;
+        sc.done_expect = c->tc_done_expect[set];
+        sc.epoch = c->tc_epoch;
+        const KriyaTcSeg* segs = c->plan_dev<KriyaTcSeg>(range_list ? c->off_tcseg2 : c->off_tcseg);
+        const uint32_t* seg_ptr = c->plan_dev<uint32_t>(range_list ? c->off_tcptr2 : c->off_tcptr);
+        const uint32_t n_seg = range_list ? c->n_seg_ranges : c->n_seg;
+        const uint32_t late_parts = late ? kLateMergeParts : UINT32_MAX;
+        if (variant == 2) {
+            KRIYA_CUDA_TRY(c, kriya_launch_decode_tcp(a, segs, seg_ptr, grid, c->tmap_kp, c->tmap_vp, layer * c->cfg.num_kv_blocks,
+                                                      c->cfg.dtype, c->max_smem_optin, fused, late_parts, n_seg, sc, c->stream));
+        } else {
+            const auto launch = variant == 1 ? kriya_launch_decode_tc_t64 : kriya_launch_decode_tc;
+            KRIYA_CUDA_TRY(c, launch(a, segs, seg_ptr, grid, c->tmap_k, c->tmap_v, layer_row0, c->cfg.dtype, c->max_smem_optin, fused,
+                                     late_parts, n_seg, sc, c->stream));
+        }
+        c->tc_done_expect[set] += grid;  // every CTA of the grid counts itself off, idle ones included
         if (late) c->launches += 1;
     } else {
         KRIYA_CUDA_TRY(c, kriya_launch_decode(a, c->cfg.head_dim, c->cfg.block_size_tokens, c->cfg.dtype,
@@ -419,7 +481,7 @@ int32_t kriya_cuda_ctx_create(const kriya_cuda_config* cfg_in, kriya_cuda_ctx** 
     c->tc_ctas = uint32_t(c->sm_count) * std::max(kriya_decode_tc_ctas_per_sm(), kriya_decode_tc_ctas_per_sm_t64());
     {
         const char* e = getenv("KRIYA_TC_VARIANT");  // 128 or 64: force one kernel variant (default: by plan)
-        c->tc_force = e ? atoi(e) : 0;
+        c->tc_force = e ? atoi(e) : 0;  // 128 / 64: one KV head per copy, 128- or 64-token tiles; default: by shape and plan
         const char* m = getenv("KRIYA_TC64_MIN_TILES");
         c->tc64_min_tiles = m ? uint32_t(std::max(1, atoi(m))) : 96u;
     }
@@ -468,6 +530,14 @@ int32_t kriya_cuda_ctx_create(const kriya_cuda_config* cfg_in, kriya_cuda_ctx** 
         const uint32_t row_elems = cfg.num_kv_heads * cfg.head_dim;
         const uint64_t total_rows = pool_bytes / (size_t(row_elems) * 2);
         c->tmaps_ok = kriya_prefill_encode_maps(c->pool_k, c->pool_v, total_rows, row_elems, c->tmap_k, c->tmap_v) == cudaSuccess;
+    }
+
+    // one-page-per-copy maps of the whole-page decode kernel
+    if (c->tmaps_ok && kriya_decode_tcp_supported(cfg.head_dim, cfg.num_kv_heads, cfg.num_q_heads / cfg.num_kv_heads, cfg.block_size_tokens) &&
+        c->layer_stride_bytes == size_t(cfg.num_kv_blocks) * c->block_bytes) {
+        c->tcp_ok = kriya_decode_tcp_encode_maps(c->pool_k, c->pool_v, uint64_t(cfg.num_kv_blocks) * cfg.num_layers, c->tmap_kp,
+                                                 c->tmap_vp) == cudaSuccess;
+        (void)cudaGetLastError();
     }
 
     // RoPE table, enc:1939-1955: f32 cos/sin of pos * theta^-(2i/rot)
@@ -520,16 +590,25 @@ int32_t kriya_cuda_ctx_create(const kriya_cuda_config* cfg_in, kriya_cuda_ctx** 
         CREATE_TRY(cudaEventCreateWithFlags(&c->h_plan_free[i], cudaEventDisableTiming));
     }
 
-    // split-row scratch: kScratchSets independent sets, so that the launches of consecutive layers, which may overlap
-    // at their edges, never share one
-    const size_t rows_hq = size_t(std::max(c->cap_work, c->cap_seg)) * cfg.num_q_heads;
-    c->set_o_floats = rows_hq * cfg.head_dim;
-    c->set_ml_floats = rows_hq * 2;
-    c->set_counters = size_t(c->cap_rows) * cfg.num_kv_heads;
-    CREATE_TRY(cudaMalloc(&c->part_o, kScratchSets * c->set_o_floats * sizeof(float)));
-    CREATE_TRY(cudaMalloc(&c->part_ml, kScratchSets * c->set_ml_floats * sizeof(float)));
-    CREATE_TRY(cudaMalloc(&c->part_counter, kScratchSets * c->set_counters * sizeof(uint32_t)));
-    CREATE_TRY(cudaMemsetAsync(c->part_counter, 0, kScratchSets * c->set_counters * sizeof(uint32_t), c->stream));
+    // split-row scratch of the CUDA-core decode kernel (its launches never overlap: one set)
+    const size_t rows_hq = size_t(c->cap_work) * cfg.num_q_heads;
+    CREATE_TRY(cudaMalloc(&c->part_o, rows_hq * cfg.head_dim * sizeof(float)));
+    CREATE_TRY(cudaMalloc(&c->part_ml, rows_hq * 2 * sizeof(float)));
+    CREATE_TRY(cudaMalloc(&c->part_counter, size_t(c->cap_rows) * sizeof(uint32_t)));
+    CREATE_TRY(cudaMemsetAsync(c->part_counter, 0, size_t(c->cap_rows) * sizeof(uint32_t), c->stream));
+    // split-run scratch of the tensor-core decode kernel: (value, stamp) pairs, zero stamps to begin with
+    if (kriya_decode_tc_supported(cfg.head_dim, cfg.num_q_heads / cfg.num_kv_heads, cfg.block_size_tokens)) {
+        // a slot holds the state of one run piece: one KV head's query heads, or all of the row's in the whole-page kernel
+        const size_t heads = cfg.num_q_heads;
+        c->tc_set_o_bytes = align_up(size_t(c->cap_seg) * heads * cfg.head_dim * 8, 256);
+        c->tc_set_ml_bytes = align_up(size_t(c->cap_seg) * heads * 2 * 8, 256);
+        CREATE_TRY(cudaMalloc(&c->tc_ll_o, kTcScratchSets * c->tc_set_o_bytes));
+        CREATE_TRY(cudaMalloc(&c->tc_ll_ml, kTcScratchSets * c->tc_set_ml_bytes));
+        CREATE_TRY(cudaMalloc(&c->tc_set_done, kTcScratchSets * 64));
+        CREATE_TRY(cudaMemsetAsync(c->tc_ll_o, 0, kTcScratchSets * c->tc_set_o_bytes, c->stream));
+        CREATE_TRY(cudaMemsetAsync(c->tc_ll_ml, 0, kTcScratchSets * c->tc_set_ml_bytes, c->stream));
+        CREATE_TRY(cudaMemsetAsync(c->tc_set_done, 0, kTcScratchSets * 64, c->stream));
+    }
     CREATE_TRY(cudaMalloc(&c->d_status, 256));
     CREATE_TRY(cudaMemsetAsync(c->d_status, 0, 256, c->stream));
     CREATE_TRY(cudaMallocHost(&c->h_status, 256));
@@ -673,30 +752,20 @@ int32_t kriya_cuda_plan_upload(kriya_cuda_ctx* c, const int32_t* indptr, size_t 
     const size_t o_work = off;
     auto* work = reinterpret_cast<KriyaDecodeWork*>(h + o_work);
     const uint32_t n_work =
-        build_work(indptr, uint32_t(rows), nullptr, nullptr, 2u * uint32_t(c->sm_count), 2u, work, c->cap_work);
+        build_work(indptr, last_len, c->cfg.block_size_tokens, c->attention_window, uint32_t(rows), nullptr, nullptr,
+                   2u * uint32_t(c->sm_count), 2u, work, c->cap_work);
     if (n_work == UINT32_MAX) return invalid("plan needs more decode work items than the context holds");
     place(size_t(n_work) * sizeof(KriyaDecodeWork));
-    const bool t64 = choose_tc64(c, indptr, uint32_t(rows), nullptr, nullptr);
-    const uint32_t plan_ctas = uint32_t(c->sm_count) * (t64 ? kriya_decode_tc_ctas_per_sm_t64() : kriya_decode_tc_ctas_per_sm());
+    const int variant = choose_tc_variant(c, indptr, uint32_t(rows), nullptr, nullptr);
+    const TcVariantGeometry geo = tc_geometry(c, variant);
+    const uint32_t plan_ctas = geo.ctas;
     const size_t o_ptr = place((size_t(plan_ctas) + 1) * 4);
     const size_t o_seg = off;
-    const uint32_t n_seg = build_tc_segments(indptr, last_len, c->cfg.block_size_tokens, uint32_t(rows), c->cfg.num_kv_heads, nullptr,
-                                             nullptr, plan_ctas,
-                                             t64 ? kriya_decode_tc_pages_per_tile_t64() : kriya_decode_tc_pages_per_tile(),
-                                             reinterpret_cast<KriyaTcSeg*>(h + o_seg), c->cap_seg,
-                                             reinterpret_cast<uint32_t*>(h + o_ptr));
+    const uint32_t n_seg = build_tc_segments(indptr, last_len, c->cfg.block_size_tokens, uint32_t(rows), geo.runs_per_row, nullptr,
+                                             nullptr, plan_ctas, geo.pages_per_tile, reinterpret_cast<KriyaTcSeg*>(h + o_seg),
+                                             c->cap_seg, reinterpret_cast<uint32_t*>(h + o_ptr), geo.min_tiles, c->attention_window);
     if (n_seg == UINT32_MAX) return invalid("plan needs more decode segments than the context holds");
     place(size_t(n_seg) * sizeof(KriyaTcSeg));
-    bool all_busy = true;
-    {
-        const uint32_t* sp = reinterpret_cast<const uint32_t*>(h + o_ptr);
-        const KriyaTcSeg* sg = reinterpret_cast<const KriyaTcSeg*>(h + o_seg);
-        for (uint32_t cta = 0; cta < plan_ctas && all_busy; ++cta) {
-            bool busy = false;
-            for (uint32_t i = sp[cta]; i < sp[cta + 1]; ++i) busy = busy || sg[i].blk_hi > sg[i].blk_lo;
-            all_busy = busy;
-        }
-    }
     const size_t o_tiles = place(std::max<size_t>(tiles_len, 1) * sizeof(kriya_cta_work_tile));
     if (tiles_len) memcpy(h + o_tiles, tiles, tiles_len * sizeof(kriya_cta_work_tile));
     const size_t o_indices = place(std::max<size_t>(indices_len, 1) * 4);
@@ -711,10 +780,9 @@ int32_t kriya_cuda_plan_upload(kriya_cuda_ctx* c, const int32_t* indptr, size_t 
     c->off_tcseg = o_seg;
     c->off_tiles = o_tiles;
     c->off_indices = o_indices;
-    c->tc_t64 = t64;
+    c->tc_variant = variant;
     c->n_seg = n_seg;
     c->tc_max_parts = max_parts_of(reinterpret_cast<const KriyaTcSeg*>(h + o_seg), n_seg);
-    c->tc_all_ctas_busy = all_busy;
 
     c->n_rows = uint32_t(rows);
     c->n_indices = uint32_t(indices_len);
@@ -906,19 +974,20 @@ int32_t kriya_cuda_plan_set_ranges(kriya_cuda_ctx* c, const uint32_t* blk_begin,
     KRIYA_CUDA_TRY(c, cudaEventSynchronize(c->h_pairs_free));
     const int32_t* indptr = reinterpret_cast<const int32_t*>(c->h_plan_last + c->off_indptr);
     auto* work = reinterpret_cast<KriyaDecodeWork*>(c->h_plan_last + c->off_range);
-    const uint32_t n_work =
-        build_work(indptr, c->n_rows, blk_begin, blk_end, 2u * uint32_t(c->sm_count), 2u, work, c->cap_work);
+    const int32_t* last_len_h = reinterpret_cast<const int32_t*>(c->h_plan_last + c->off_last_len);
+    const uint32_t n_work = build_work(indptr, last_len_h, c->cfg.block_size_tokens, c->attention_window, c->n_rows, blk_begin,
+                                       blk_end, 2u * uint32_t(c->sm_count), 2u, work, c->cap_work);
     if (n_work == UINT32_MAX) return c->fail(KRIYA_CUDA_INVALID_INPUT, "ranges need more work items than the context holds");
     KRIYA_CUDA_TRY(c, cudaMemcpyAsync(c->d_plan + c->off_range, work, size_t(n_work) * sizeof(KriyaDecodeWork),
                                       cudaMemcpyHostToDevice, c->stream));
     auto* segs = reinterpret_cast<KriyaTcSeg*>(c->h_plan_last + c->off_tcseg2);
     auto* sptr = reinterpret_cast<uint32_t*>(c->h_plan_last + c->off_tcptr2);
-    c->tc_t64_ranges = choose_tc64(c, indptr, c->n_rows, blk_begin, blk_end);
+    c->tc_variant_ranges = choose_tc_variant(c, indptr, c->n_rows, blk_begin, blk_end);
+    const TcVariantGeometry geo = tc_geometry(c, c->tc_variant_ranges);
     const uint32_t n_seg = build_tc_segments(
         indptr, reinterpret_cast<const int32_t*>(c->h_plan_last + c->off_last_len), c->cfg.block_size_tokens, c->n_rows,
-        c->cfg.num_kv_heads, blk_begin, blk_end,
-        uint32_t(c->sm_count) * (c->tc_t64_ranges ? kriya_decode_tc_ctas_per_sm_t64() : kriya_decode_tc_ctas_per_sm()),
-        c->tc_t64_ranges ? kriya_decode_tc_pages_per_tile_t64() : kriya_decode_tc_pages_per_tile(), segs, c->cap_seg, sptr);
+        geo.runs_per_row, blk_begin, blk_end, geo.ctas, geo.pages_per_tile, segs, c->cap_seg, sptr, geo.min_tiles,
+        c->attention_window);
     if (n_seg == UINT32_MAX) return c->fail(KRIYA_CUDA_INVALID_INPUT, "ranges need more segments than the context holds");
     c->n_seg_ranges = n_seg;
     c->tc_max_parts_ranges = max_parts_of(segs, n_seg);
@@ -1031,6 +1100,7 @@ int32_t kriya_cuda_paged_gqa_prefill_batch(kriya_cuda_ctx* c, uint32_t layer, co
     a.num_blocks = c->cfg.num_kv_blocks;
     a.num_q_heads = c->cfg.num_q_heads;
     a.num_kv_heads = c->cfg.num_kv_heads;
+    a.window = c->attention_window;
     a.sm_scale = p->sm_scale;
     a.logit_softcap = p->logit_softcap;
     KRIYA_CUDA_TRY(c, kriya_launch_prefill(a, c->cfg.head_dim, c->cfg.block_size_tokens, c->cfg.dtype, c->max_smem_optin,
@@ -1060,16 +1130,21 @@ int32_t kriya_cuda_kv_block_copy(kriya_cuda_ctx* c, const uint32_t* pairs, uint3
     KRIYA_CUDA_TRY(c, cudaMemcpyAsync(c->d_pairs, c->h_pairs, size_t(n_pairs) * 2 * sizeof(uint32_t),
                                       cudaMemcpyHostToDevice, c->stream));
     KRIYA_CUDA_TRY(c, cudaEventRecord(c->h_pairs_free, c->stream));
-    // Pairs apply in order.  A launch copies its pairs concurrently, so a batch ends where a pair reads or
-    // rewrites a block an earlier pair of the batch wrote.
+    // Pairs apply in order.  A launch copies its pairs concurrently, so a batch ends where a pair reads a block an earlier
+    // pair of the batch wrote, or writes a block an earlier pair of the batch read or wrote.
     uint32_t start = 0;
-    std::vector<uint32_t> written;
+    std::vector<uint32_t> written, read;
     for (uint32_t i = 0; i <= n_pairs; ++i) {
         bool cut = i == n_pairs;
         if (!cut) {
             const uint32_t src = pairs[2 * i], dst = pairs[2 * i + 1];
             for (uint32_t wv : written)
                 if (wv == src || wv == dst) {
+                    cut = true;
+                    break;
+                }
+            for (uint32_t rv : read)
+                if (rv == dst && src != dst) {
                     cut = true;
                     break;
                 }
@@ -1081,8 +1156,12 @@ int32_t kriya_cuda_kv_block_copy(kriya_cuda_ctx* c, const uint32_t* pairs, uint3
             c->launches += 1;
             start = i;
             written.clear();
+            read.clear();
         }
-        if (i < n_pairs) written.push_back(pairs[2 * i + 1]);
+        if (i < n_pairs) {
+            written.push_back(pairs[2 * i + 1]);
+            read.push_back(pairs[2 * i]);
+        }
     }
     return KRIYA_CUDA_OK;
 }
@@ -1135,7 +1214,7 @@ int32_t kriya_cuda_decode_layer_host(kriya_cuda_ctx* c, uint32_t layer, const vo
 
 static int32_t append_decode_impl(kriya_cuda_ctx* c, uint32_t layer, const void* q, const void* k, const void* v, void* out,
                                   void* q_rope_out, const kriya_rope_kv_write_params* rope, const kriya_bsr_gqa_params* gqa,
-                                  bool overlap_previous) {
+                                  uint32_t overlap_previous) {
     if (!c) return KRIYA_CUDA_INVALID_INPUT;
     if (int32_t rc = check_layer(c, layer)) return rc;
     if (int32_t rc = check_rope(c, rope)) return rc;
@@ -1162,17 +1241,14 @@ static int32_t append_decode_impl(kriya_cuda_ctx* c, uint32_t layer, const void*
     f.has_table = rope->has_table;
     f.rope_theta = rope->rope_theta;
     f.positions_are_context = c->positions_are_context ? 1u : 0u;
-    // 1: may start while the previous launch drains, waits for it before touching the scratch;
-    // 2: the same without the wait, on a scratch set of its own.  Only sound when every CTA of every launch holds
-    //    work: a launch's CTAs each need a whole SM, so launch L+1 has started all of them only once launch L has
-    //    vacated every SM, and launch L+2 cannot begin before that; a set is reused four launches later.
-    f.overlap_previous = (overlap_previous && !c->timing) ? (c->tc_all_ctas_busy ? 2u : 1u) : 0u;
+    // how the launch relates to the kernel before it (KriyaFusedAppend::overlap_previous); event brackets forbid any overlap
+    f.overlap_previous = c->timing ? 0u : overlap_previous;
     return launch_decode(c, layer, q, out, nullptr, nullptr, nullptr, false, c->n_work, gqa, f);
 }
 
 int32_t kriya_cuda_append_decode(kriya_cuda_ctx* c, uint32_t layer, const void* q, const void* k, const void* v, void* out,
                                  void* q_rope_out, const kriya_rope_kv_write_params* rope, const kriya_bsr_gqa_params* gqa) {
-    return append_decode_impl(c, layer, q, k, v, out, q_rope_out, rope, gqa, false);
+    return append_decode_impl(c, layer, q, k, v, out, q_rope_out, rope, gqa, 0u);
 }
 
 // Layers [l0, l1) of one step; `first_of_chain` says that the launch for l0 must not overlap what precedes it.
@@ -1187,10 +1263,10 @@ static int32_t decode_layers(kriya_cuda_ctx* c, uint32_t l0, uint32_t l1, bool f
         const uint8_t* vl = static_cast<const uint8_t*>(v) + layer * kb;
         uint8_t* ol = static_cast<uint8_t*>(out) + layer * qb;
         if (c->fuse_append && use_tc_decode(c) && !rope->apply_qk_norm) {
-            // Layers of one step share nothing but the split-row scratch, which the kernel guards itself: from the
-            // second layer on, a launch may start while the previous layer's last CTAs drain.
-            const bool overlap = c->overlap_layers && !(first_of_chain && layer == l0);
-            if (int32_t rc = append_decode_impl(c, layer, ql, kl, vl, ol, nullptr, rope, gqa, overlap)) return rc;
+            // Layers of one step share nothing but the split-run scratch, which the kernel guards itself: from the
+            // second layer on, a launch may start while the previous layer's last CTAs drain (by default).
+            const uint32_t mode = (first_of_chain && layer == l0) ? 0u : c->layer_chain_mode;
+            if (int32_t rc = append_decode_impl(c, layer, ql, kl, vl, ol, nullptr, rope, gqa, mode)) return rc;
         } else {
             if (int32_t rc = kriya_cuda_rope_kv_append(c, layer, ql, kl, vl, nullptr, nullptr, rows, rope)) return rc;
             if (int32_t rc = kriya_cuda_paged_gqa_decode(c, layer, ql, ol, gqa)) return rc;
@@ -1294,18 +1370,43 @@ int32_t kriya_cuda_decode_step_host(kriya_cuda_ctx* c, const void* q_host, const
 
 int32_t kriya_cuda_set_decode_path(kriya_cuda_ctx* c, int32_t path) {
     if (!c) return KRIYA_CUDA_INVALID_INPUT;
-    if (path < 0 || path > 2) return c->fail(KRIYA_CUDA_INVALID_INPUT, "decode path must be 0 (auto), 1 (CUDA-core) or 2 (tensor-core)");
-    if (path == 2 && !(c->tmaps_ok && kriya_decode_tc_supported(c->cfg.head_dim, c->cfg.num_q_heads / c->cfg.num_kv_heads,
+    if (path < 0 || path > 3)
+        return c->fail(KRIYA_CUDA_INVALID_INPUT, "decode path must be 0 (auto), 1 (CUDA-core), 2 (tensor-core) or 3 (tensor-core, one KV head per copy)");
+    if (path >= 2 && !(c->tmaps_ok && kriya_decode_tc_supported(c->cfg.head_dim, c->cfg.num_q_heads / c->cfg.num_kv_heads,
                                                                  c->cfg.block_size_tokens)))
         return c->fail(KRIYA_CUDA_UNSUPPORTED, "the tensor-core decode kernel covers head_dim 128, group size 1..8, 16-token blocks");
     c->decode_path = path;
+    c->plan_valid = false;  // the work lists of an uploaded plan were cut for the kernel chosen before
+    return KRIYA_CUDA_OK;
+}
+
+int32_t kriya_cuda_set_wait_limit_us(kriya_cuda_ctx* c, uint32_t limit_us) {
+    if (!c) return KRIYA_CUDA_INVALID_INPUT;
+    if (limit_us == 0) return c->fail(KRIYA_CUDA_INVALID_INPUT, "the wait limit must be positive");
+    c->wait_ns = uint64_t(limit_us) * 1000ull;
+    return KRIYA_CUDA_OK;
+}
+
+int32_t kriya_cuda_selftest_wait_expiry(kriya_cuda_ctx* c) {
+    if (!c) return KRIYA_CUDA_INVALID_INPUT;
+    cudaSetDevice(c->cfg.device);
+    KRIYA_CUDA_TRY(c, kriya_launch_wait_selftest(c->d_status, c->wait_ns, c->stream));
+    c->launches += 1;
+    return KRIYA_CUDA_OK;
+}
+
+int32_t kriya_cuda_set_attention_window(kriya_cuda_ctx* c, uint32_t window_size) {
+    if (!c) return KRIYA_CUDA_INVALID_INPUT;
+    c->attention_window = window_size;
+    c->plan_valid = false;  // the work lists of an uploaded plan were cut for the mask set before
     return KRIYA_CUDA_OK;
 }
 
 int32_t kriya_cuda_set_fused_append(kriya_cuda_ctx* c, int32_t enable) {
     if (!c) return KRIYA_CUDA_INVALID_INPUT;
     c->fuse_append = (enable & 1) != 0;
-    c->overlap_layers = (enable & 2) == 0;  // bit 1 set: keep the layers of a step strictly serialised
+    static const uint32_t modes[4] = {2u, 1u, 3u, 0u};  // bits 1-2: free, serialised, dependent activations, ordinary launches
+    c->layer_chain_mode = modes[(enable >> 1) & 3];
     return KRIYA_CUDA_OK;
 }
 

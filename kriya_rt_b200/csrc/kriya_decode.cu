@@ -183,6 +183,9 @@ __global__ void __launch_bounds__(kDecodeThreadsMax, 1) decode_kernel(KriyaDecod
             const uint8_t* Ks = ring + size_t(stage) * L.stage_bytes;
             const uint8_t* Vs = Ks + L.page_bytes;
             const uint32_t valid = (w.blk_begin + uint32_t(i) + 1u == total_blocks) ? uint32_t(last_len) : uint32_t(kPage);
+            // tokens of this page in front of the sliding window (only the window's first page has any)
+            const uint32_t page_tok0 = (w.blk_begin + uint32_t(i)) * uint32_t(kPage);
+            const uint32_t first = w.tok_first > page_tok0 ? min(w.tok_first - page_tok0, uint32_t(kPage)) : 0u;
 
             // phase A: scores of the page's tokens for the G query heads
             float s[NSTEP];
@@ -207,7 +210,7 @@ __global__ void __launch_bounds__(kDecodeThreadsMax, 1) decode_kernel(KriyaDecod
                 my_g = group_reduce<GP, LPT>(part, dl);
                 float sc = part[0];
                 if (softcap) sc = tanhf(fminf(fmaxf(sc / a.logit_softcap, -15.0f), 15.0f)) * a.logit_softcap * kLog2e;
-                s[st] = (tok < valid) ? sc : -INFINITY;
+                s[st] = (tok < valid && tok >= first) ? sc : -INFINITY;
             }
             // phase B: one online-softmax update per page
             float m_loc = s[0];
@@ -240,7 +243,7 @@ __global__ void __launch_bounds__(kDecodeThreadsMax, 1) decode_kernel(KriyaDecod
             for (int st = 0; st < NSTEP; ++st) {
                 const uint32_t tok = uint32_t(st) * TPW + slot;
                 uint4 raw = *reinterpret_cast<const uint4*>(Vs + ((size_t(tok) * HPC + hh) * D + dl * 8) * 2);
-                if (tok >= valid) raw = make_uint4(0u, 0u, 0u, 0u);  // slots past the row's end may hold anything
+                if (tok >= valid || tok < first) raw = make_uint4(0u, 0u, 0u, 0u);  // slots no token of the row's window occupies may hold anything
                 const float2 v0 = T::load2(raw.x), v1 = T::load2(raw.y), v2 = T::load2(raw.z), v3 = T::load2(raw.w);
                 const float* pg = p_s + (st * TPW + int(slot)) * GP;
 #pragma unroll

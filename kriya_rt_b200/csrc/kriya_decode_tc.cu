@@ -32,6 +32,7 @@
 // HBM roofline: algorithmic bytes per launch = attended tokens * 2 * Hkv * D * 2 B; every K/V byte is read
 // from HBM once (one TMA load) and from shared memory once (one MMA operand read).
 #include <algorithm>
+#include <atomic>
 #include <cstdio>
 #include <cstdlib>
 
@@ -86,7 +87,17 @@ struct TcParams {
     // runs cut into more pieces than this are not merged by their last piece but by late_merge_kernel after the launch
     uint32_t late_parts;
     uint32_t n_seg;  // host side only: segments of the list (grid of the late merge)
+    // Partial states of split runs, written as (value, epoch) pairs so that a reader needs no fence and no flag of its own
+    // (see ll_store): ll_o [slot][G][128], ll_ml [slot][G][2] = (running max in log2 units, sum).
+    uint2* ll_o;
+    uint2* ll_ml;
+    uint32_t* set_done;    // CTAs that have finished with this scratch set, over all launches so far
+    uint32_t done_expect;  // its value once every earlier launch that used the set has finished with it
+    uint32_t epoch;        // this launch's stamp, never zero
     KriyaFusedAppend f;
+#ifdef KRIYA_TC_TRACE
+    uint32_t trace_idx;
+#endif
 };
 
 // RoPE of eight (x[i], x[i + D/2]) pairs held as two 16-byte chunks, in the operation order of the append kernel
@@ -134,12 +145,13 @@ __device__ __forceinline__ void rope8_apply(uint4& lo, uint4& hi, uint32_t first
     }
 }
 
-// Optional per-CTA timeline (compile with -DKRIYA_TC_TRACE): wall-clock stamps at a few points of the kernel, dumped
-// to stderr by the launcher on the tenth launch when KRIYA_TRACE is set in the environment.
+// Optional per-CTA timeline (compile with -DKRIYA_TC_TRACE): wall-clock stamps at a few points of the kernel for the last
+// kTrLaunches launches, read back through kriya_trace_read.
 #ifdef KRIYA_TC_TRACE
-__device__ unsigned long long g_trace[320 * 16];
-#define TR(k) do { g_trace[blockIdx.x * 16 + (k)] = global_timer_ns(); } while (0)
-#define TRV(k, v) do { g_trace[blockIdx.x * 16 + (k)] = (v); } while (0)
+constexpr int kTrLaunches = 128, kTrCtas = 304, kTrSlots = 24;
+__device__ unsigned long long g_trace[kTrLaunches * kTrCtas * kTrSlots];
+#define TRV(k, v) do { g_trace[(size_t(pp.trace_idx % kTrLaunches) * kTrCtas + blockIdx.x) * kTrSlots + (k)] = (v); } while (0)
+#define TR(k) TRV(k, global_timer_ns())
 #else
 #define TR(k) do { } while (0)
 #define TRV(k, v) do { } while (0)
@@ -162,72 +174,96 @@ __device__ __forceinline__ bool bar_or_128(bool pred) {
     return res != 0;
 }
 
-// Merge of a run's partial states (m, l, o) from scratch into the output, by `nthreads` threads (128: the
-// softmax warps, synchronised on named barrier 1; 32: the merge warp).  Parts are taken eight at a time and all
-// loads of a chunk are issued before any is used, so a chunk costs about one memory round trip.
-template <int G, typename T>
-__device__ __forceinline__ void merge_run_parts(const KriyaDecodeArgs& a, const KriyaTcSeg& seg, float* stage, uint32_t t,
-                                                uint32_t nthreads, bool state_mode, size_t row0) {
-    auto sync = [&]() {
-        if (nthreads == 128u) named_bar_sync_128();
-        else __syncwarp();
-    };
-    for (uint32_t d = t; d < uint32_t(kTcD); d += nthreads) {
-        float M[G], Ls[G], Os[G];
+// A partial-state word travels with the stamp of the launch that wrote it: one 8-byte store, so a reader that sees the
+// stamp of its own launch also sees the value, without a fence on the writer's side or a separate flag to wait for.
+__device__ __forceinline__ void ll_store(uint2* p, float v, uint32_t epoch) {
+    asm volatile("st.global.cg.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(v)), "r"(epoch) : "memory");
+}
+// Loads of such words are volatile: they go to L2 (the writer may be any SM) and a polling loop really repeats them
+// (an ordinary load may be moved out of the loop by the assembler).  A polling loop issues a whole batch of them before
+// it looks at the first result, so that the batch is in flight together.
+__device__ __forceinline__ uint2 ll_load(const uint2* p) {
+    uint2 r;
+    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(r.x), "=r"(r.y) : "l"(p) : "memory");
+    return r;
+}
+__device__ __forceinline__ uint32_t ld_volatile_u32(const uint32_t* p) {
+    uint32_t r;
+    asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(r) : "l"(p) : "memory");
+    return r;
+}
+
+// Waits (bounded) until the counter of a scratch set says that every CTA of every earlier launch on the set is done.
+__device__ __forceinline__ bool warp_wait_l(uint64_t limit_ns, uint64_t* bar, uint32_t parity) { return warp_wait(bar, parity, limit_ns); }
+__device__ __forceinline__ bool wait_set_free(const uint32_t* set_done, uint32_t done_expect, uint64_t wait_ns) {
+    const uint64_t t_start = global_timer_ns();
+    for (uint32_t spin = 0;; ++spin) {
+        if (int32_t(ld_volatile_u32(set_done) - done_expect) >= 0) return true;
+        if ((spin & 63u) == 63u && global_timer_ns() - t_start > wait_ns) return false;
+    }
+}
+
+// The run's last piece gathers the other pieces' partial states and finishes the run.  Called by the 128 softmax threads
+// with their own piece's state in registers: thread t owns output dimension t; M / L are the piece's running maximum (log2
+// units) and sum per head, O its accumulator values for dimension t.  Other pieces are taken four at a time; every load of
+// a chunk is issued before any is examined and is repeated until it carries this launch's stamp (bounded).  Returns false
+// when a stamp never arrived.
+template <int G>
+__device__ __forceinline__ bool gather_merge(const uint2* __restrict__ ll_o, const uint2* __restrict__ ll_ml, const KriyaTcSeg& seg,
+                                             uint32_t epoch, uint64_t wait_ns, float* stage, uint32_t t, float (&M)[G], float (&L)[G], float (&O)[G]) {
+    const uint32_t others = seg.n_parts - 1u;
+    for (uint32_t c0 = 0; c0 < others; c0 += 4u) {
+        const uint32_t cnt = min(4u, others - c0);
+        const size_t slot0 = size_t(seg.first_slot) + c0;
+        uint2 w[4][G];
+        uint2 mlw = make_uint2(0u, epoch);
+        const bool has_ml = t < cnt * uint32_t(G) * 2u;  // (m, l) words of the chunk: [part][head][2], one per thread
+        const uint2* mlp = &ll_ml[slot0 * G * 2 + (has_ml ? t : 0u)];
+        bool got = false;
+        const uint64_t t_start = global_timer_ns();
+        for (uint32_t spin = 0; !got; ++spin) {
+            // all loads first (a part past the chunk re-reads the chunk's last part), then the stamps
 #pragma unroll
-        for (int h = 0; h < G; ++h) {
-            M[h] = -INFINITY;
-            Ls[h] = 0.0f;
-            Os[h] = 0.0f;
-        }
-        for (uint32_t c0 = 0; c0 < seg.n_parts; c0 += 8u) {
-            const uint32_t cnt = min(8u, seg.n_parts - c0);
-            for (uint32_t i = t; i < cnt * uint32_t(G) * 2u; i += nthreads)  // (m, l) of the chunk: [part][head][2]
-                stage[i] = __ldcg(&a.part_ml[size_t(seg.first_slot + c0) * G * 2 + i]);
-            float ov[8][G];
-#pragma unroll
-            for (int s2 = 0; s2 < 8; ++s2)
+            for (int s2 = 0; s2 < 4; ++s2)
 #pragma unroll
                 for (int h = 0; h < G; ++h)
-                    ov[s2][h] = (uint32_t(s2) < cnt) ? __ldcg(&a.part_o[(size_t(seg.first_slot + c0 + s2) * G + h) * kTcD + d]) : 0.0f;
-            sync();
+                    w[s2][h] = ll_load(&ll_o[((slot0 + min(uint32_t(s2), cnt - 1u)) * G + h) * kTcD + t]);
+            mlw = ll_load(mlp);
+            uint32_t bad = mlw.y ^ epoch;
 #pragma unroll
-            for (int h = 0; h < G; ++h) {
-                float mc = M[h];
+            for (int s2 = 0; s2 < 4; ++s2)
 #pragma unroll
-                for (int s2 = 0; s2 < 8; ++s2)
-                    if (uint32_t(s2) < cnt) mc = fmaxf(mc, stage[(s2 * G + h) * 2]);
-                if (mc == -INFINITY) continue;
-                const float keep = (M[h] == -INFINITY) ? 0.0f : exp2f(M[h] - mc);
-                float lacc = Ls[h] * keep, oacc = Os[h] * keep;
-#pragma unroll
-                for (int s2 = 0; s2 < 8; ++s2) {
-                    if (uint32_t(s2) < cnt) {
-                        const float ms = stage[(s2 * G + h) * 2];
-                        const float w = (ms == -INFINITY) ? 0.0f : exp2f(ms - mc);
-                        lacc = fmaf(w, stage[(s2 * G + h) * 2 + 1], lacc);
-                        oacc = fmaf(w, ov[s2][h], oacc);
-                    }
-                }
-                M[h] = mc;
-                Ls[h] = lacc;
-                Os[h] = oacc;
-            }
-            sync();  // `stage` is rewritten by the next chunk
+                for (int h = 0; h < G; ++h) bad |= w[s2][h].y ^ epoch;
+            got = bad == 0u;
+            if (!got && (spin & 63u) == 63u && global_timer_ns() - t_start > wait_ns) break;
         }
+        if (has_ml) stage[t] = __uint_as_float(mlw.x);
+        if (bar_or_128(!got)) return false;  // also orders the writes to `stage` before its readers
 #pragma unroll
         for (int h = 0; h < G; ++h) {
-            if (state_mode) {
-                a.state_o[(row0 + h) * kTcD + d] = Os[h];
-                if (d == 0) {
-                    a.state_m[row0 + h] = M[h] / kTcLog2e;
-                    a.state_l[row0 + h] = Ls[h];
+            float mc = M[h];
+#pragma unroll
+            for (int s2 = 0; s2 < 4; ++s2)
+                if (uint32_t(s2) < cnt) mc = fmaxf(mc, stage[(s2 * G + h) * 2]);
+            if (mc == -INFINITY) continue;
+            const float keep = (M[h] == -INFINITY) ? 0.0f : exp2f(M[h] - mc);
+            float lacc = L[h] * keep, oacc = O[h] * keep;
+#pragma unroll
+            for (int s2 = 0; s2 < 4; ++s2) {
+                if (uint32_t(s2) < cnt) {
+                    const float ms = stage[(s2 * G + h) * 2];
+                    const float wgt = (ms == -INFINITY) ? 0.0f : exp2f(ms - mc);
+                    lacc = fmaf(wgt, stage[(s2 * G + h) * 2 + 1], lacc);
+                    oacc = fmaf(wgt, __uint_as_float(w[s2][h].x), oacc);
                 }
-            } else {
-                reinterpret_cast<uint16_t*>(a.out)[(row0 + h) * kTcD + d] = T::store(Os[h] / fmaxf(Ls[h], 1e-12f));
             }
+            M[h] = mc;
+            L[h] = lacc;
+            O[h] = oacc;
         }
+        named_bar_sync_128();  // `stage` is rewritten by the next chunk
     }
+    return true;
 }
 
 template <int G, typename T>
@@ -256,19 +292,38 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
     uint64_t* kv_ready = bars + 2 * kTcStages + 12; // [3]; run r's new-token K/V row is in the cache (fused append)
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kTcStages + 15);
     volatile uint32_t* abort_flag = tmem_slot + 1;
-    uint32_t* ticket_s = tmem_slot + 2;
-    volatile uint32_t* merge_job_ok = tmem_slot + 3;
-    float* merge_stage = reinterpret_cast<float*>(tmem_slot + 4);  // [8][G][2] floats for warp 6
-    KriyaTcSeg* segs_s = reinterpret_cast<KriyaTcSeg*>(merge_stage + 128);  // first 8 segment records of this CTA
+    volatile uint32_t* set_free_s = tmem_slot + 2;  // 0: not known yet, 1: the scratch set may be written, 2: the wait for it gave up
+    KriyaTcSeg* segs_s = reinterpret_cast<KriyaTcSeg*>(tmem_slot + 4 + 128);  // first 8 segment records of this CTA
 
     const KriyaDecodeArgs& a = pp.a;
+    const uint64_t wait_ns = a.wait_ns;
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
-    if (threadIdx.x == 0) TR(0);
+    if (threadIdx.x == 0) {
+        TR(0);
+#ifdef KRIYA_TC_TRACE
+        uint32_t smid;
+        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+        TRV(11, smid);
+        TRV(14, 0);
+        TRV(6, 0);
+        TRV(8, 0);
+        TRV(15, 0);
+        TRV(19, 0);
+        TRV(20, 0);
+#endif
+    }
     const uint32_t seg_begin = pp.cta_seg_ptr[blockIdx.x], seg_end = pp.cta_seg_ptr[blockIdx.x + 1];
-    // The next launch of the stream may start as SMs free up: it only shares the split-row scratch with this one, and
-    // waits for this grid before touching it (see pdl_wait_previous_grid below).
+    // The next launch of the stream may start as SMs free up (it decides itself what it must wait for, see `pdl` below).
     if (threadIdx.x == 0) pdl_launch_dependents();
-    if (seg_begin == seg_end) return;  // whole CTA idle: nothing allocated yet
+    if (seg_begin == seg_end) {  // whole CTA idle: nothing allocated yet
+        // Every CTA counts itself off in the scratch set's counter, and only once the set's earlier launches are complete:
+        // the counter then never runs ahead of them (see the guard in warp 6 below).
+        if (threadIdx.x == 0) {
+            if (!wait_set_free(pp.set_done, pp.done_expect, pp.a.wait_ns)) atomicMax(pp.a.status, uint32_t(KRIYA_DEV_WAIT_EXPIRED));
+            atomicAdd(pp.set_done, 1u);
+        }
+        return;
+    }
 
     if (tid == 0) {
         for (int s = 0; s < kTcStages; ++s) {
@@ -287,7 +342,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
             mbar_init(&kv_ready[b], 1);
         }
         *abort_flag = 0;
-        *merge_job_ok = 1;
+        *set_free_s = 0;
         mbar_fence_init();
     }
     if (warp == 5) {
@@ -311,8 +366,12 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t Hq = a.num_q_heads, Hkv = a.num_kv_heads;
-    // the CTA's first piece is merged by warp 6 when it is one part of a split run and more pieces follow
-    const bool defer_first = seg_end - seg_begin > 1u && segs_s[0].n_parts > 1u;
+    // How this launch relates to the kernel before it in the stream when it was allowed to start early (programmatic
+    // dependent launch): 1 = nothing but the set-up above may precede that kernel's completion; 3 = only the cache and the
+    // plan are older than that kernel, so the K/V stream starts at once while everything that touches activations (queries,
+    // the new token's K/V, outputs) waits; 2 = nothing to wait for; 0 = ordinary launch.
+    const uint32_t pdl = pp.f.overlap_previous;
+    if (pdl == 1u) pdl_wait_previous_grid();
     if (tid == 0) TR(1);
 
     if (warp == 4) {
@@ -337,12 +396,12 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
                 const uint32_t my_page = p_lo + lane;
                 int32_t blk = pf_blk;
                 if (!pf_valid && lane < npages) blk = table[my_page];
-                if (g >= kTcStages && !warp_wait(&kv_empty[stage], ((g / kTcStages) - 1u) & 1u)) {
+                if (g >= kTcStages && !warp_wait_l(wait_ns, &kv_empty[stage], ((g / kTcStages) - 1u) & 1u)) {
                     ok = false;
                     break;
                 }
                 // the piece's last tile reads the slot the stager warp writes: wait until it is in the cache
-                if (owns_last && t + 1u == t1 && !warp_wait(&kv_ready[runs % uint32_t(kTcQBufs)], (runs / uint32_t(kTcQBufs)) & 1u)) {
+                if (owns_last && t + 1u == t1 && !warp_wait_l(wait_ns, &kv_ready[runs % uint32_t(kTcQBufs)], (runs / uint32_t(kTcQBufs)) & 1u)) {
                     ok = false;
                     break;
                 }
@@ -382,11 +441,12 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
         uint32_t runs = 0;
         bool ok = true;
         const bool fused = pp.f.k_in != nullptr;
+        if (pdl == 3u) pdl_wait_previous_grid();
         for (uint32_t si = seg_begin; si < seg_end && ok; ++si) {
             const KriyaTcSeg seg = seg_at(si);
             if (seg.blk_hi <= seg.blk_lo) continue;
             if (*abort_flag) break;
-            if (runs >= uint32_t(kTcQBufs) && !warp_wait(&q_free[runs % uint32_t(kTcQBufs)], ((runs / uint32_t(kTcQBufs)) - 1u) & 1u)) {
+            if (runs >= uint32_t(kTcQBufs) && !warp_wait_l(wait_ns, &q_free[runs % uint32_t(kTcQBufs)], ((runs / uint32_t(kTcQBufs)) - 1u) & 1u)) {
                 ok = false;
                 break;
             }
@@ -513,9 +573,9 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
         bool la_valid = la_load();
         auto la_issue = [&]() -> bool {  // issue S^T for the look-ahead tile and advance the cursor
             if (!la_valid) return true;
-            if (!warp_wait(&kv_full[la_g % kTcStages], (la_g / kTcStages) & 1u)) return false;
+            if (!warp_wait_l(wait_ns, &kv_full[la_g % kTcStages], (la_g / kTcStages) & 1u)) return false;
             if (la_first) {
-                if (!warp_wait(&q_ready[la_run % uint32_t(kTcQBufs)], (la_run / uint32_t(kTcQBufs)) & 1u)) return false;
+                if (!warp_wait_l(wait_ns, &q_ready[la_run % uint32_t(kTcQBufs)], (la_run / uint32_t(kTcQBufs)) & 1u)) return false;
                 la_first = false;
             }
             tc_fence_after();
@@ -541,7 +601,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
                 if (*abort_flag) { ok = false; break; }
                 ok = la_issue();  // S^T of tile g+1 (possibly of the next run) before P.V of tile g
                 if (!ok) break;
-                ok = warp_wait(&p_ready[g & 1u], (g >> 1) & 1u);
+                ok = warp_wait_l(wait_ns, &p_ready[g & 1u], (g >> 1) & 1u);
                 if (!ok) break;
                 tc_fence_after();
                 if (lane == 0) {
@@ -564,23 +624,18 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
             *abort_flag = 1;
         }
     } else if (warp == 6) {
-        // ---- deferred merge of the CTA's first piece -----------------------------------------------------
-        if (defer_first) {
-            const KriyaTcSeg seg = segs_s[0];
-            asm volatile("bar.sync 2, 160;" ::: "memory");  // the softmax threads have published the partial state
-            if (*merge_job_ok && seg.n_parts <= pp.late_parts) {
-                if (pp.f.overlap_previous != 2u) pdl_wait_previous_grid();
-                __threadfence();
-                uint32_t ticket = 0;
-                if (lane == 0) ticket = atomicAdd(&a.counters[seg.req * Hkv + seg.kv_head], 1u);
-                ticket = __shfl_sync(0xFFFFFFFFu, ticket, 0);
-                if (ticket == seg.n_parts - 1u) {
-                    __threadfence();
-                    merge_run_parts<G, T>(a, seg, merge_stage, lane, 32u, a.state_o != nullptr,
-                                          size_t(seg.req) * Hq + seg.kv_head * G);
-                    if (lane == 0) atomicExch(&a.counters[seg.req * Hkv + seg.kv_head], 0u);
-                }
-            }
+        // ---- scratch-set guard ----------------------------------------------------------------------------
+        // The set this launch publishes partial states into was last used a few launches ago.  Launches of one step may
+        // overlap (deeply, when a plan leaves most CTAs idle), so before anything is published every CTA of the set's
+        // earlier launches must have finished with it: they count themselves off in set_done on their way out.  A CTA
+        // counts itself off only after this guard has passed, so the counter holds completions of earlier launches only
+        // until they are all in.  One lane looks the counter up while the first piece streams; the softmax threads find
+        // the answer in shared memory.
+        if (lane == 0) {
+            const bool free_now = wait_set_free(pp.set_done, pp.done_expect, pp.a.wait_ns);
+            if (!free_now) atomicMax(a.status, uint32_t(KRIYA_DEV_WAIT_EXPIRED));
+            __threadfence_block();
+            *set_free_s = free_now ? 1u : 2u;
         }
     } else {
         // ---- softmax warps ----------------------------------------------------------------------------------
@@ -590,13 +645,13 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
         const bool state_mode = a.state_o != nullptr;
         uint32_t g = 0;
         bool ok = true;
-        bool handed_off = false;
+        bool set_known = false;  // the scratch-set guard has been consulted
         for (uint32_t si = seg_begin; si < seg_end && ok; ++si) {
             if (tid == 0 && si == seg_begin + 1) TR(6);
             const KriyaTcSeg seg = seg_at(si);
             const uint32_t req = seg.req;
             const uint32_t row_tokens = seg.row_tokens;
-            const uint32_t tok_lo = seg.blk_lo * kTcPage, tok_hi = min(seg.blk_hi * kTcPage, row_tokens);
+            const uint32_t tok_lo = max(seg.blk_lo * kTcPage, seg.tok_first), tok_hi = min(seg.blk_hi * kTcPage, row_tokens);
             const uint32_t t0 = seg.blk_lo / kTcPagesPerTile, t1 = (seg.blk_hi + kTcPagesPerTile - 1) / kTcPagesPerTile;
             const bool empty = seg.blk_hi <= seg.blk_lo;
             float m_used[G], l_lane[G];
@@ -607,7 +662,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
             }
             for (uint32_t t = empty ? t1 : t0; t < t1; ++t, ++g) {
                 if (*abort_flag) { ok = false; break; }
-                ok = warp_wait(&s_full[g & 1u], (g >> 1) & 1u);
+                ok = warp_wait_l(wait_ns, &s_full[g & 1u], (g >> 1) & 1u);
                 if (!ok) break;
                 tc_fence_after();
                 if (tid == 0 && g == 0) TR(4);
@@ -658,7 +713,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
                     named_bar_sync_128();  // everyone has read `red`
                     if (t > t0) {
                         // O^T holds earlier tiles: the previous P.V must be complete before it is rescaled
-                        ok = warp_wait(&pv_done[(g - 1u) & 1u], ((g - 1u) >> 1) & 1u);
+                        ok = warp_wait_l(wait_ns, &pv_done[(g - 1u) & 1u], ((g - 1u) >> 1) & 1u);
                         if (!ok) break;
                         tc_fence_after();
                         uint32_t o[16];
@@ -674,7 +729,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
                 }
                 // P buffer g&1 was last read by P.V of tile g-2
                 if (g >= 2) {
-                    ok = warp_wait(&pv_done[g & 1u], ((g >> 1) - 1u) & 1u);
+                    ok = warp_wait_l(wait_ns, &pv_done[g & 1u], ((g >> 1) - 1u) & 1u);
                     if (!ok) break;
                 }
                 // probabilities of this token for the G heads -> P[h][token] (K-major, swizzled)
@@ -706,6 +761,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
                 mbar_arrive(&p_ready[g & 1u]);
             }
             if (!ok) break;
+            if (tid == 0) { TR(13); TRV(12, g); }
             if (tid == 0 && si == seg_begin) {
                 TR(5);
                 TRV(9, g);
@@ -727,70 +783,76 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
 #pragma unroll
             for (int h = 0; h < G; ++h) l_tot[h] = (red[h] + red[16 + h]) + (red[32 + h] + red[48 + h]);
             named_bar_sync_128();
+            if (tid == 0 && si == seg_begin) TR(16);
             uint32_t o[16];
 #pragma unroll
             for (int h = 0; h < 16; ++h) o[h] = 0u;
             if (!empty) {
-                ok = warp_wait(&pv_done[(g - 1u) & 1u], ((g - 1u) >> 1) & 1u);
+                ok = warp_wait_l(wait_ns, &pv_done[(g - 1u) & 1u], ((g - 1u) >> 1) & 1u);
                 if (!ok) break;
                 tc_fence_after();
+                if (tid == 0 && si == seg_begin) TR(17);
                 tmem_ld16(tmem_base + lane_addr + kColO, o);
                 tmem_wait_ld();
                 tc_fence_before();
             }
+            if (tid == 0 && si == seg_begin) TR(18);
             const uint32_t d = tid;  // output dimension owned by this thread
             const size_t row0 = size_t(req) * Hq + seg.kv_head * G;
-            if (seg.n_parts == 1u) {
+            // A run cut into pieces: every piece but the last publishes its partial state; the last piece (which its CTA
+            // processes last, see the host's segment order) gathers them and finishes the run.  Runs in very many pieces
+            // are finished by late_merge_kernel behind the launch instead; then every piece publishes.
+            if (pdl == 3u) pdl_wait_previous_grid();  // outputs follow; returns at once when the wait is over already
+            const bool split = seg.n_parts > 1u;
+            const bool finisher = !split || (seg.n_parts <= pp.late_parts && seg.slot + 1u == seg.first_slot + seg.n_parts);
+            if (finisher) {
+                float Mh[G], Lh[G], Oh[G];
 #pragma unroll
                 for (int h = 0; h < G; ++h) {
-                    const float ov = __uint_as_float(o[h]);
+                    Mh[h] = m_used[h];
+                    Lh[h] = l_tot[h];
+                    Oh[h] = __uint_as_float(o[h]);
+                }
+                if (split) {
+                    if (tid == 0) { TR(15); TRV(14, seg.n_parts); }
+                    ok = gather_merge<G>(pp.ll_o, pp.ll_ml, seg, pp.epoch, wait_ns, red, tid, Mh, Lh, Oh);
+                    if (!ok) break;
+                    if (tid == 0) TR(20);
+                }
+#pragma unroll
+                for (int h = 0; h < G; ++h) {
                     if (state_mode) {
-                        a.state_o[(row0 + h) * kTcD + d] = ov;
+                        a.state_o[(row0 + h) * kTcD + d] = Oh[h];
                         if (d == 0) {
-                            a.state_m[row0 + h] = m_used[h] / kTcLog2e;
-                            a.state_l[row0 + h] = l_tot[h];
+                            a.state_m[row0 + h] = Mh[h] / kTcLog2e;
+                            a.state_l[row0 + h] = Lh[h];
                         }
                     } else {
-                        reinterpret_cast<uint16_t*>(a.out)[(row0 + h) * kTcD + d] = T::store(ov / fmaxf(l_tot[h], 1e-12f));
+                        reinterpret_cast<uint16_t*>(a.out)[(row0 + h) * kTcD + d] = T::store(Oh[h] / fmaxf(Lh[h], 1e-12f));
                     }
                 }
             } else {
-                // a scratch set shared with the previous launch must not be touched before that launch has drained
-                if (pp.f.overlap_previous != 2u) pdl_wait_previous_grid();
+                // the scratch set must be free of its previous user (warp 6 looks that up at the start of the CTA)
+                if (!set_known) {
+                    uint32_t st = *set_free_s;
+                    const uint64_t t_start = global_timer_ns();
+                    for (uint32_t spin = 0; st == 0u; ++spin) {
+                        st = *set_free_s;
+                        if (st == 0u && (spin & 63u) == 63u && global_timer_ns() - t_start > 2u * wait_ns) break;
+                    }
+                    ok = !bar_or_128(st != 1u);
+                    if (!ok) break;
+                    set_known = true;
+                }
+                if (tid == 0 && si == seg_begin) TR(19);
                 const size_t prow = size_t(seg.slot) * G;
 #pragma unroll
                 for (int h = 0; h < G; ++h) {
-                    a.part_o[(prow + h) * kTcD + d] = __uint_as_float(o[h]);
-                    if (d == 0) {
-                        a.part_ml[(prow + h) * 2 + 0] = m_used[h];
-                        a.part_ml[(prow + h) * 2 + 1] = l_tot[h];
-                    }
-                }
-                if (si == seg_begin && si + 1 < seg_end) {
-                    // Not the CTA's last piece: hand the ticket and the possible merge to warp 6 and go on.
-                    __threadfence_block();
-                    handed_off = true;
-                    asm volatile("bar.arrive 2, 160;" ::: "memory");
-                } else if (seg.n_parts <= pp.late_parts) {
-                    __threadfence();
-                    named_bar_sync_128();
-                    if (tid == 0) *ticket_s = atomicAdd(&a.counters[req * Hkv + seg.kv_head], 1u);
-                    named_bar_sync_128();
-                    const bool last = *ticket_s == seg.n_parts - 1u;
-                    named_bar_sync_128();  // ticket_s may be rewritten by the next run
-                    if (last) {
-                        __threadfence();
-                        merge_run_parts<G, T>(a, seg, red, tid, 128u, state_mode, row0);
-                        if (tid == 0) atomicExch(&a.counters[req * Hkv + seg.kv_head], 0u);
-                    }
+                    ll_store(&pp.ll_o[(prow + h) * kTcD + d], __uint_as_float(o[h]), pp.epoch);
+                    if (tid == uint32_t(2 * h)) ll_store(&pp.ll_ml[(prow + h) * 2 + 0], m_used[h], pp.epoch);
+                    if (tid == uint32_t(2 * h + 1)) ll_store(&pp.ll_ml[(prow + h) * 2 + 1], l_tot[h], pp.epoch);
                 }
             }
-        }
-        // warp 6 waits on barrier 2 whenever the first piece is a deferred one: arrive even when bailing out
-        if (defer_first && !handed_off) {
-            *merge_job_ok = 0;
-            __threadfence_block();
-            asm volatile("bar.arrive 2, 160;" ::: "memory");
         }
         if (tid == 0) TR(7);
         if (!ok && lane == 0) {
@@ -801,7 +863,10 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
 
     tc_fence_before();
     __syncthreads();
-    if (tid == 0) TR(8);
+    if (tid == 0) {
+        TR(8);
+        atomicAdd(pp.set_done, 1u);  // every read of the scratch set by this CTA is complete, and warp 6 has seen the guard
+    }
     if (warp == 5) {
         tc_fence_after();
         tmem_dealloc(tmem_base, kTcTmemCols);
@@ -813,7 +878,8 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
 // pieces this is several times faster than the single warp or warpgroup that would otherwise do it at the tail of the
 // decode launch.
 template <int G, typename T>
-__global__ void __launch_bounds__(kTcD) late_merge_kernel(KriyaDecodeArgs a, const KriyaTcSeg* segs, uint32_t late_parts) {
+__global__ void __launch_bounds__(kTcD) late_merge_kernel(KriyaDecodeArgs a, const KriyaTcSeg* segs, uint32_t late_parts,
+                                                          const uint2* __restrict__ ll_o, const uint2* __restrict__ ll_ml) {
     const KriyaTcSeg seg = segs[blockIdx.x];
     if (seg.slot != seg.first_slot || seg.n_parts <= late_parts) return;  // not the first piece of a late-merged run
     const uint32_t h = blockIdx.y, d = threadIdx.x;
@@ -824,9 +890,9 @@ __global__ void __launch_bounds__(kTcD) late_merge_kernel(KriyaDecodeArgs a, con
 #pragma unroll
         for (int s2 = 0; s2 < 8; ++s2) {
             const size_t row = size_t(seg.first_slot + c0 + min(uint32_t(s2), cnt - 1u)) * G + h;
-            ms[s2] = uint32_t(s2) < cnt ? a.part_ml[row * 2 + 0] : -INFINITY;
-            ls[s2] = a.part_ml[row * 2 + 1];
-            ov[s2] = a.part_o[row * kTcD + d];
+            ms[s2] = uint32_t(s2) < cnt ? __uint_as_float(ll_ml[row * 2 + 0].x) : -INFINITY;
+            ls[s2] = __uint_as_float(ll_ml[row * 2 + 1].x);
+            ov[s2] = __uint_as_float(ll_o[row * kTcD + d].x);
         }
         float mc = M;
 #pragma unroll
@@ -861,11 +927,21 @@ cudaError_t launch_tc_t(const TcParams& pp, const CUtensorMap& mk, const CUtenso
     const size_t smem = size_t(2 * kTcStages) * kTcKvBytes + kTcQBufs * kTcQBytes + 2 * kTcPBytes + 512 + 320 + 512 + 8 * sizeof(KriyaTcSeg) + 1024;
     if (smem > size_t(max_smem_optin)) return cudaErrorInvalidValue;
     auto kern = decode_tc_kernel<G, T>;
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+#ifdef KRIYA_TC_TRACE
+    static uint32_t trace_launch = 0;
+    const_cast<TcParams&>(pp).trace_idx = trace_launch++;
+#endif
+    {   // the attribute belongs to the device: set it once on every device this process launches the kernel on
+        static std::atomic<uint64_t> attr_set{0};
+        int dev = 0;
+        cudaError_t e = cudaGetDevice(&dev);
         if (e != cudaSuccess) return e;
-        attr_set = true;
+        const uint64_t bit = uint64_t(1) << (dev & 63);
+        if (!(attr_set.load(std::memory_order_acquire) & bit)) {
+            e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+            if (e != cudaSuccess) return e;
+            attr_set.fetch_or(bit, std::memory_order_release);
+        }
     }
     if (overlap_previous) {
         cudaLaunchConfig_t cfg = {};
@@ -884,27 +960,7 @@ cudaError_t launch_tc_t(const TcParams& pp, const CUtensorMap& mk, const CUtenso
         kern<<<grid, kTcThreads, smem, s>>>(mk, mv, pp);
     }
     if (pp.late_parts != UINT32_MAX && pp.n_seg != 0u)
-        late_merge_kernel<G, T><<<dim3(pp.n_seg, G), kTcD, 0, s>>>(pp.a, pp.segs, pp.late_parts);
-#ifdef KRIYA_TC_TRACE
-    if (getenv("KRIYA_TRACE")) {
-        static int calls = 0;
-        if (++calls == 10) {
-            cudaDeviceSynchronize();
-            static unsigned long long h[320 * 16];
-            cudaMemcpyFromSymbol(h, g_trace, sizeof(h));
-            unsigned long long t0 = ~0ull;
-            for (uint32_t c = 0; c < grid; ++c)
-                if (h[c * 16]) t0 = std::min(t0, h[c * 16]);
-            // columns: entry, set-up done, first TMA, first S^T issued, first scores read, first piece streamed,
-            // second piece begins, softmax warps done, CTA done (microseconds from the earliest entry)
-            for (uint32_t c = 0; c < grid; ++c) {
-                fprintf(stderr, "cta %3u:", c);
-                for (int k = 0; k < 9; ++k) fprintf(stderr, " %6.1f", h[c * 16 + k] >= t0 ? (h[c * 16 + k] - t0) / 1000.0 : -1.0);
-                fprintf(stderr, "  tiles %llu segs %llu\n", h[c * 16 + 9], h[c * 16 + 10]);
-            }
-        }
-    }
-#endif
+        late_merge_kernel<G, T><<<dim3(pp.n_seg, G), kTcD, 0, s>>>(pp.a, pp.segs, pp.late_parts, pp.ll_o, pp.ll_ml);
     return cudaGetLastError();
 }
 
@@ -929,6 +985,14 @@ cudaError_t launch_tc_g(uint32_t group, const TcParams& pp, const CUtensorMap& m
 
 namespace ktc = kriya::KRIYA_TC_NS;
 
+#ifdef KRIYA_TC_TRACE
+// copies the timeline buffer [kTrLaunches][kTrCtas][kTrSlots] of this build to the host
+extern "C" int KRIYA_TC_FN(kriya_trace_read)(void* dst, size_t bytes) {
+    cudaDeviceSynchronize();
+    return int(cudaMemcpyFromSymbol(dst, ktc::g_trace, std::min(bytes, sizeof(ktc::g_trace))));
+}
+#endif
+
 uint32_t KRIYA_TC_FN(kriya_decode_tc_ctas_per_sm)() { return uint32_t(ktc::kTcCtasPerSm); }
 uint32_t KRIYA_TC_FN(kriya_decode_tc_pages_per_tile)() { return uint32_t(ktc::kTcPagesPerTile); }
 
@@ -939,7 +1003,7 @@ bool KRIYA_TC_FN(kriya_decode_tc_supported)(uint32_t head_dim, uint32_t group, u
 cudaError_t KRIYA_TC_FN(kriya_launch_decode_tc)(const KriyaDecodeArgs& a, const KriyaTcSeg* segs, const uint32_t* cta_seg_ptr, uint32_t grid,
                                    const void* map_k, const void* map_v, uint32_t layer_row0, uint32_t dtype,
                                    int max_smem_optin, const KriyaFusedAppend& fused, uint32_t late_parts, uint32_t n_seg,
-                                   cudaStream_t s) {
+                                   const KriyaTcScratch& scratch, cudaStream_t s) {
     if (grid == 0) return cudaSuccess;
     const uint32_t group = a.num_q_heads / a.num_kv_heads;
     if (!KRIYA_TC_FN(kriya_decode_tc_supported)(ktc::kTcD, group, ktc::kTcPage) || !map_k || !map_v) return cudaErrorInvalidValue;
@@ -950,6 +1014,11 @@ cudaError_t KRIYA_TC_FN(kriya_launch_decode_tc)(const KriyaDecodeArgs& a, const 
     pp.layer_row0 = layer_row0;
     pp.late_parts = late_parts;
     pp.n_seg = n_seg;
+    pp.ll_o = static_cast<uint2*>(scratch.ll_o);
+    pp.ll_ml = static_cast<uint2*>(scratch.ll_ml);
+    pp.set_done = scratch.set_done;
+    pp.done_expect = scratch.done_expect;
+    pp.epoch = scratch.epoch;
     pp.f = fused;
     const CUtensorMap& mk = *static_cast<const CUtensorMap*>(map_k);
     const CUtensorMap& mv = *static_cast<const CUtensorMap*>(map_v);

@@ -72,28 +72,28 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Bounded wait: polls until the phase completes or `kWaitNs` of wall time have passed, so a lost copy
-// or a missing arrival can never hang the GPU.  Returns false on expiry.  Callers that go on to use
-// warp-synchronous primitives must agree on the outcome first (see warp_wait).
+// Bounded wait: polls until the phase completes or `limit_ns` of wall time have passed (default kWaitNs; a context may
+// set its own, see kriya_cuda_set_wait_limit_us), so a lost copy or a missing arrival can never hang the GPU.  Returns
+// false on expiry.  Callers that go on to use warp-synchronous primitives must agree on the outcome first (see warp_wait).
 constexpr uint64_t kWaitNs = 2000000000ull;
 __device__ __forceinline__ uint64_t global_timer_ns() {
     uint64_t t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
 }
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint64_t limit_ns = kWaitNs) {
     if (mbar_try_wait(bar, parity)) return true;
     const uint64_t t0 = global_timer_ns();
     for (;;) {
 #pragma unroll 1
         for (int i = 0; i < 64; ++i)
             if (mbar_try_wait(bar, parity)) return true;
-        if (global_timer_ns() - t0 > kWaitNs) return false;
+        if (global_timer_ns() - t0 > limit_ns) return false;
     }
 }
 // All 32 lanes wait, then agree: true only if every lane saw the phase complete.
-__device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity) {
-    const bool ok = mbar_wait(bar, parity);
+__device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, uint64_t limit_ns = kWaitNs) {
+    const bool ok = mbar_wait(bar, parity, limit_ns);
     return __all_sync(0xFFFFFFFFu, ok);
 }
 

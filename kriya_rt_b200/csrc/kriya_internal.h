@@ -20,7 +20,7 @@ struct KriyaDecodeWork {
     uint32_t slot;
     uint32_t first_slot;
     uint32_t n_parts;
-    uint32_t _pad0;
+    uint32_t tok_first;  // first token of the row that may be attended (sliding window); 0 without a window
     uint32_t _pad1;
 };
 static_assert(sizeof(KriyaDecodeWork) == 32, "work item is 32 bytes");
@@ -37,7 +37,8 @@ struct KriyaTcSeg {
     uint32_t n_parts;
     uint32_t tbl_off;     // page_indptr[req]: where the row's block table starts
     uint32_t row_tokens;  // tokens in the whole row: (blocks - 1) * block size + last_page_len
-    uint32_t _pad[3];
+    uint32_t tok_first;   // first token of the row that may be attended (sliding window); 0 without a window
+    uint32_t _pad[2];
 };
 static_assert(sizeof(KriyaTcSeg) == 48, "segment record is 48 bytes");
 
@@ -49,8 +50,12 @@ enum : uint32_t {
     KRIYA_DEV_BAD_SLOT = 3          // append slot outside its block
 };
 
+struct kriya_comm_state;  // exchange buffers of the KV-axis split (kriya_comm.cu)
+void kriya_comm_destroy(struct kriya_cuda_ctx* c);
+
 struct kriya_cuda_ctx {
     kriya_cuda_config cfg{};
+    kriya_comm_state* comm = nullptr;
     cudaStream_t stream = nullptr;
     cudaStream_t copy_stream = nullptr;      // host -> device inputs of whole-step host calls
     cudaStream_t copy_stream_out = nullptr;  // device -> host results
@@ -58,8 +63,10 @@ struct kriya_cuda_ctx {
     std::vector<cudaEvent_t> ev_in, ev_done;  // per input / output group of the host-buffer step
     int sm_count = 0;
     uint32_t tc_ctas = 0;  // largest grid of the tensor-core decode kernel variants: resident CTAs per SM x SMs
-    bool tc_t64 = false, tc_t64_ranges = false;  // the current plan's (range) lists are for the 64-token-tile build
-    int tc_force = 0;                            // KRIYA_TC_VARIANT
+    // which tensor-core decode kernel the current plan's (range) lists are cut for: 0 = 128-token tiles of one KV head,
+    // 1 = 64-token tiles of one KV head (two CTAs per SM), 2 = whole pages of both KV heads
+    int tc_variant = 0, tc_variant_ranges = 0;
+    int tc_force = 0;                            // KRIYA_TC_VARIANT: 128, 64 or 2 (whole pages)
     uint32_t tc64_min_tiles = 96;                // 128-token tiles per SM from which the 64-token-tile build is used
     int max_smem_optin = 0;
 
@@ -73,6 +80,10 @@ struct kriya_cuda_ctx {
     alignas(64) unsigned char tmap_k[128];
     alignas(64) unsigned char tmap_v[128];
     bool tmaps_ok = false;
+    // 5-D maps with one page (both KV heads) per box, valid when tcp_ok
+    alignas(64) unsigned char tmap_kp[128];
+    alignas(64) unsigned char tmap_vp[128];
+    bool tcp_ok = false;
 
     float* rope_table = nullptr;  // [rope_max_seq_len][rotary_dim/2][2]
     uint32_t rope_rotary_dim = 0;
@@ -87,9 +98,11 @@ struct kriya_cuda_ctx {
            off_range = 0, off_tcseg = 0, off_tcptr = 0, off_tcseg2 = 0, off_tcptr2 = 0, dyn_base = 0;
     uint32_t cap_seg = 0, n_seg = 0, n_seg_ranges = 0;
     uint32_t tc_max_parts = 0, tc_max_parts_ranges = 0;  // most pieces any run of the current (range) lists is cut into
-    bool overlap_layers = true;  // whole-step calls let consecutive layers' launches overlap at their edges
+    uint32_t layer_chain_mode = 2;  // KriyaFusedAppend::overlap_previous for the second and later layers of a whole-step call
     bool fuse_append = true;  // whole-step calls use the fused append + decode launch where it applies
-    int decode_path = 0;  // 0: pick per shape, 1: CUDA-core kernel, 2: tensor-core kernel
+    uint64_t wait_ns = 2000000000ull;  // limit of the bounded waits inside kernels (kriya_cuda_set_wait_limit_us)
+    uint32_t attention_window = 0;  // SlidingWindowCausal window_size; 0 = plain causal
+    int decode_path = 0;  // 0: pick per shape, 1: CUDA-core kernel, 2: tensor-core kernel, 3: tensor-core kernel with one KV head per copy
     uint32_t cap_rows = 0, cap_indices = 0, cap_tiles = 0, cap_tokens = 0, cap_work = 0;
     // current plan (host copy of the sizes and of what later calls need)
     bool plan_valid = false;
@@ -98,15 +111,20 @@ struct kriya_cuda_ctx {
     uint64_t total_row_tokens = 0;
     uint8_t* h_plan_last = nullptr;  // staging buffer holding the current plan (for partial-range rebuilds)
 
-    // split-KV scratch
+    // split-KV scratch of the CUDA-core decode kernel
     float* part_o = nullptr;        // [cap_work][Hq][D]
     float* part_ml = nullptr;       // [cap_work][Hq][2]
-    uint32_t* part_counter = nullptr;  // [cap_rows * head_groups]
-    size_t set_o_floats = 0, set_ml_floats = 0, set_counters = 0;  // size of one scratch set
+    uint32_t* part_counter = nullptr;  // [cap_rows]
+    // split-run scratch of the tensor-core decode kernel: kTcScratchSets sets, taken in turn by successive launches
+    uint8_t* tc_ll_o = nullptr;     // per set: uint2 [cap_seg][G][128]
+    uint8_t* tc_ll_ml = nullptr;    // per set: uint2 [cap_seg][G][2]
+    uint32_t* tc_set_done = nullptr;  // per set, 64 bytes apart
+    size_t tc_set_o_bytes = 0, tc_set_ml_bytes = 0;
+    uint32_t tc_epoch = 0;
+    uint32_t tc_done_expect[4] = {0, 0, 0, 0};
     bool ranges_valid = false;      // block ranges set for the current plan (kriya_cuda_plan_set_ranges)
     uint32_t n_work_ranges = 0;
     bool positions_are_context = false;  // current plan: seq_positions[r] == tokens in row r - 1 for every row
-    bool tc_all_ctas_busy = false;  // current plan gives every CTA of the tensor-core decode launch some tiles
     uint32_t* d_status = nullptr;   // device status word
     uint32_t* h_status = nullptr;   // pinned mirror
 
@@ -200,6 +218,7 @@ struct KriyaDecodeArgs {
     uint32_t num_kv_heads;
     float sm_scale;
     float logit_softcap;
+    uint64_t wait_ns;  // limit of every bounded wait inside the kernel
 };
 // Returns cudaErrorInvalidValue for shapes the kernels are not instantiated for.
 cudaError_t kriya_launch_decode(const KriyaDecodeArgs& a, uint32_t head_dim, uint32_t block_size, uint32_t dtype,
@@ -220,11 +239,21 @@ struct KriyaFusedAppend {
     uint32_t has_table = 0;
     float rope_theta = 0.0f;
     uint32_t positions_are_context = 0;  // every row's position equals its token count - 1 (checked on the host)
-    // Host-side launch option: let this launch begin while the previous kernel of the stream drains (programmatic
-    // dependent launch).  Only valid when every input of this launch is already complete, i.e. between the layers
-    // of one whole-step call; the kernel itself waits for the previous grid before it touches the shared scratch.
-    // 2 = as 1, but on a scratch set of its own and without that wait (see kriya_ctx.cu for when this is sound).
+    // Launch option: 0 = ordinary launch; otherwise the launch may begin while the previous kernel of the stream drains
+    // (programmatic dependent launch) and the kernel waits for that kernel's completion as far as the mode says:
+    // 1 = before anything but its own set-up, 3 = before it touches activations (queries, new K/V, outputs) while the K/V
+    // stream of the cache starts at once, 2 = never (every input is known to be complete).
     uint32_t overlap_previous = 0;
+};
+// Scratch of one tensor-core decode launch: the partial states of runs that are cut across CTAs, stored as (value, stamp)
+// pairs, the counter the CTAs of the launch count themselves off in, and what that counter reads once every earlier
+// launch on the same set has finished with it.
+struct KriyaTcScratch {
+    void* ll_o = nullptr;          // uint2 [segments][G][128]
+    void* ll_ml = nullptr;         // uint2 [segments][G][2]
+    uint32_t* set_done = nullptr;
+    uint32_t done_expect = 0;
+    uint32_t epoch = 1;            // stamp of the launch, never zero
 };
 bool kriya_decode_tc_supported(uint32_t head_dim, uint32_t group, uint32_t block_size);
 uint32_t kriya_decode_tc_ctas_per_sm();
@@ -234,10 +263,24 @@ uint32_t kriya_decode_tc_ctas_per_sm_t64();
 uint32_t kriya_decode_tc_pages_per_tile_t64();
 cudaError_t kriya_launch_decode_tc_t64(const KriyaDecodeArgs& a, const KriyaTcSeg* segs, const uint32_t* cta_seg_ptr, uint32_t grid,
                                        const void* map_k, const void* map_v, uint32_t layer_row0, uint32_t dtype,
-                                       int max_smem_optin, const KriyaFusedAppend& fused, uint32_t late_parts, uint32_t n_seg, cudaStream_t s);
+                                       int max_smem_optin, const KriyaFusedAppend& fused, uint32_t late_parts, uint32_t n_seg,
+                                       const KriyaTcScratch& scratch, cudaStream_t s);
 cudaError_t kriya_launch_decode_tc(const KriyaDecodeArgs& a, const KriyaTcSeg* segs, const uint32_t* cta_seg_ptr, uint32_t grid,
                                    const void* map_k, const void* map_v, uint32_t layer_row0, uint32_t dtype,
-                                   int max_smem_optin, const KriyaFusedAppend& fused, uint32_t late_parts, uint32_t n_seg, cudaStream_t s);
+                                   int max_smem_optin, const KriyaFusedAppend& fused, uint32_t late_parts, uint32_t n_seg,
+                                   const KriyaTcScratch& scratch, cudaStream_t s);
+
+// The tensor-core decode kernel that moves whole pages (both KV heads) with one copy: head_dim 128, 2 KV heads, 16-token pages.
+bool kriya_decode_tcp_supported(uint32_t head_dim, uint32_t num_kv_heads, uint32_t group, uint32_t block_size);
+uint32_t kriya_decode_tcp_pages_per_tile();
+cudaError_t kriya_decode_tcp_encode_maps(void* pool_k, void* pool_v, uint64_t total_pages, void* out_map_k, void* out_map_v);
+cudaError_t kriya_launch_decode_tcp(const KriyaDecodeArgs& a, const KriyaTcSeg* segs, const uint32_t* cta_seg_ptr, uint32_t grid,
+                                    const void* map_k, const void* map_v, uint32_t page0, uint32_t dtype, int max_smem_optin,
+                                    const KriyaFusedAppend& fused, uint32_t late_parts, uint32_t n_seg, const KriyaTcScratch& scratch,
+                                    cudaStream_t s);
+
+// A one-block kernel that waits, with the given limit, on a barrier nobody arrives at and reports the expiry in `status`.
+cudaError_t kriya_launch_wait_selftest(uint32_t* status, uint64_t wait_ns, cudaStream_t s);
 
 cudaError_t kriya_launch_merge_states(const float* m, const float* l, const float* o, uint32_t parts, uint32_t rows,
                                       uint32_t D, size_t stride_ml, size_t stride_o, void* out, uint32_t dtype,
@@ -277,6 +320,7 @@ struct KriyaPrefillArgs {
     uint32_t num_q_heads;
     uint32_t num_kv_heads;
     uint32_t layer_row0;  // first row of this layer inside the all-layer tensor map
+    uint32_t window;      // sliding-window size in tokens, 0 = plain causal
     float sm_scale;
     float logit_softcap;
 };

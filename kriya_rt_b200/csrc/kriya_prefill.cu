@@ -153,7 +153,12 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
     const uint32_t tile_start = qt.q_row0;  // first row of this tile in q / out
     const uint32_t tile_rows = qt.rows;
     const uint32_t kv_limit = qt.pos0 + tile_rows;  // keys [0, kv_limit) of the sequence can be seen by this tile
-    const uint32_t n_tiles = (kv_limit + kKvTile - 1) / kKvTile;
+    // Sliding window (0 = none): query row r at position pos0 + r attends keys pos0 + r + 1 - window ..= pos0 + r.  The
+    // earliest window start of the tile is row 0's, so KV tiles in front of it are skipped altogether: the loops below
+    // count j = 0 .. n_tiles over the tiles tile0 + j.
+    const uint32_t window = a.window;
+    const uint32_t tile0 = (window != 0u && qt.pos0 + 1u > window) ? (qt.pos0 + 1u - window) / uint32_t(kKvTile) : 0u;
+    const uint32_t n_tiles = (kv_limit + kKvTile - 1) / kKvTile - tile0;
     const uint32_t seq_end = qt.seq_end;  // tokens of the sequence that exist in the cache
 
     // ---- setup -------------------------------------------------------------------------------------------
@@ -213,8 +218,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
         for (uint32_t j = 0; j < n_tiles; ++j) {
             if (*abort_flag) break;
             const uint32_t ks = j & 1u;
-            const uint32_t first_page = j * kPagesPerTile;
-            const uint32_t last_needed = (min(kv_limit, (j + 1) * uint32_t(kKvTile)) + kPagePf - 1) / kPagePf;  // exclusive
+            const uint32_t first_page = (tile0 + j) * kPagesPerTile;
+            const uint32_t last_needed = (min(kv_limit, (tile0 + j + 1) * uint32_t(kKvTile)) + kPagePf - 1) / kPagePf;  // exclusive
             const uint32_t npages = last_needed - first_page;
             int32_t blk = 0;
             if (lane < npages) {
@@ -341,8 +346,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
             if (!ok) break;
             tc_fence_after();
             if (row == 0) PTR(x, j, 0);
-            const uint32_t key0 = j * kKvTile;
+            const uint32_t key0 = (tile0 + j) * kKvTile;
             const bool diag = key0 + kKvTile - 1u > qt.pos0;  // some row of the tile masks some key
+            // some key of the tile lies in front of some row's window (the last row's window starts latest)
+            const bool wdiag = window != 0u && key0 + window < qt.pos0 + tile_rows;
             // the whole score row into registers, once
             uint32_t sr[4][32];
 #pragma unroll
@@ -365,6 +372,13 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
 #pragma unroll
                     for (int i = 0; i < 32; ++i)
                         if (key0 + uint32_t(c * 32 + i) > q_pos) sr[c][i] = 0xFF800000u;  // -inf
+            }
+            if (wdiag) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        if (key0 + uint32_t(c * 32 + i) + window <= q_pos) sr[c][i] = 0xFF800000u;  // in front of the window
             }
             float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four independent chains
 #pragma unroll
@@ -397,7 +411,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
             // probabilities in the storage dtype, two keys per 32-bit column, over the first 64 columns of the score tile
             if (row == 0) PTR(x, j, 3);
             float2 psum2 = make_float2(0.0f, 0.0f);
-            const float2 sc2 = make_float2(scale2, scale2), neg_m2 = make_float2(-m_used, -m_used);
+            // a row that has seen no key yet (its window begins behind this tile) has m_used = -inf: its exponents must
+            // come out as -inf, not as inf - inf
+            const float neg_m = (m_used == -INFINITY) ? 0.0f : -m_used;
+            const float2 sc2 = make_float2(scale2, scale2), neg_m2 = make_float2(neg_m, neg_m);
 #pragma unroll
             for (int c = 0; c < 4; ++c) {  // 32 keys = 16 columns at a time, each stored as soon as it is ready
                 uint32_t packed[16];

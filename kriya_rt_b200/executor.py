@@ -192,6 +192,29 @@ class CudaExecutor:
         e = np.ascontiguousarray(blk_end, np.uint32)
         self._check(self._lib.kriya_cuda_plan_set_ranges(self._h, b.ctypes.data, e.ctypes.data))
 
+    # ---- KV-axis split over several GPUs (kriya_comm.cu) -------------------------------------------------
+    COMM_HANDLE_BYTES = 128
+
+    def comm_export(self, max_rows: int = 1) -> bytes:
+        """Allocates the exchange buffer and returns its handle (plain bytes, to be handed to every other rank)."""
+        buf = C.create_string_buffer(self.COMM_HANDLE_BYTES)
+        self._check(self._lib.kriya_cuda_comm_export(self._h, max_rows, buf))
+        return buf.raw
+
+    def comm_init(self, rank: int, handles: Sequence[bytes]) -> None:
+        """`handles`: the handles of all ranks, ordered by rank (handles[rank] is this executor's own)."""
+        blob = b"".join(bytes(h) for h in handles)
+        if len(blob) != self.COMM_HANDLE_BYTES * len(handles):
+            raise ValueError("every handle must hold COMM_HANDLE_BYTES bytes")
+        self._check(self._lib.kriya_cuda_comm_init(self._h, len(handles), rank, C.c_char_p(blob)))
+
+    def kvsplit_decode(self, layer: int, q, out, params: BsrGqaParams) -> None:
+        """Partial decode over this rank's block ranges + exchange with the peers + merge, all on the executor's stream."""
+        self._check(self._lib.kriya_cuda_kvsplit_decode(self._h, layer, _ptr(q), _ptr(out), C.byref(params)))
+
+    def kvsplit_decode_step(self, q, out, params: BsrGqaParams) -> None:
+        self._check(self._lib.kriya_cuda_kvsplit_decode_step(self._h, _ptr(q), _ptr(out), C.byref(params)))
+
     def merge_states(self, m, l, o, parts: int, rows_times_heads: int, out) -> None:
         self._check(self._lib.kriya_cuda_merge_states(self._h, _ptr(m), _ptr(l), _ptr(o), parts, rows_times_heads,
                                                       _ptr(out)))
@@ -256,12 +279,26 @@ class CudaExecutor:
 
     def set_fused_append(self, mode) -> None:
         """1 / True: fused launches, consecutive layers may overlap at their edges (default); 0 / False: separate
-        append and decode kernels; 3: fused but strictly serialised layers."""
+        append and decode kernels; 3: fused, layers serialised (set-up may start early); 5: fused, a layer's activations
+        wait for the previous layer while its cached K/V streams at once; 7: fused, ordinary launches."""
         self._check(self._lib.kriya_cuda_set_fused_append(self._h, int(mode)))
 
     def set_decode_path(self, path: int) -> None:
-        """0 = by shape, 1 = CUDA-core decode kernel, 2 = tensor-core decode kernel."""
+        """0 = by shape, 1 = CUDA-core decode kernel, 2 = a tensor-core decode kernel, 3 = the tensor-core kernel that
+        copies one KV head at a time.  Upload the plan again afterwards."""
         self._check(self._lib.kriya_cuda_set_decode_path(self._h, path))
+
+    def set_wait_limit_us(self, limit_us: int) -> None:
+        """Limit of the bounded waits inside the tensor-core decode kernels (default 2 s)."""
+        self._check(self._lib.kriya_cuda_set_wait_limit_us(self._h, limit_us))
+
+    def selftest_wait_expiry(self) -> None:
+        """Queues a kernel whose bounded wait runs out on purpose; the next sync() raises."""
+        self._check(self._lib.kriya_cuda_selftest_wait_expiry(self._h))
+
+    def set_attention_window(self, window_size: int) -> None:
+        """SlidingWindowCausal { window_size } (descriptor.rs:63-70); 0 = plain causal.  Upload the plan again afterwards."""
+        self._check(self._lib.kriya_cuda_set_attention_window(self._h, window_size))
 
     def timing_enable(self, enable: bool) -> None:
         self._check(self._lib.kriya_cuda_timing_enable(self._h, int(enable)))

@@ -125,6 +125,11 @@ def rope_kv_append(q_inout, k_in, v_in, cache_k, cache_v, indptr, indices, last_
                             C.c_uint32(positions.size), C.byref(params), _p(table), dtype)
 
 
+def set_attention_window(window_size: int) -> None:
+    """Sliding-window causal mask for every following decode / prefill call of the oracle (0 = plain causal)."""
+    lib().ko_set_attention_window(C.c_uint32(window_size))
+
+
 def decode(q, cache_k, cache_v, indptr, indices, last_len, params: GqaParams, dtype: int):
     """Whole-row fp32 decode.  Returns (out16 uint16, out_f32)."""
     q = _u16(q)

@@ -271,6 +271,14 @@ typedef struct {
     float o[256];
 } ko_state;
 
+/* AttentionMaskVariant::SlidingWindowCausal { window_size } (crates/kriya-core/src/descriptor.rs:63-70): the reference
+ * declares the mask and no kernel reads it.  Semantics restated here: a query at position p attends the window_size most
+ * recent positions, itself included, i.e. keys p + 1 - window_size ..= p.  0 = plain causal.  Every caller of
+ * stream_blocks describes the keys visible to ONE query as a row whose last token is the query's own position, so the
+ * window is the last `window` tokens of the row. */
+static uint32_t g_attention_window = 0u;
+KO_EXPORT void ko_set_attention_window(uint32_t window_size) { g_attention_window = window_size; }
+
 /* The token-serial online softmax of metal:289-326 / 357-398 / 430-467 over logical
  * blocks [blk_begin, blk_end) of request `req`, in fp32, shader operation order. */
 static void stream_blocks(const uint16_t* q_row, const uint16_t* cache_k, const uint16_t* cache_v,
@@ -289,6 +297,12 @@ static void stream_blocks(const uint16_t* q_row, const uint16_t* cache_k, const 
     for (uint32_t d = 0; d < 256; ++d) st->o[d] = 0.0f;
     if (blk_end > total) blk_end = total; /* metal:274 */
     const size_t tok_stride = (size_t)p->num_kv_heads * D;
+    uint32_t tok_first = 0u; /* first token inside the sliding window */
+    if (g_attention_window != 0u && total > 0u) {
+        int32_t ll = last_len[req];
+        const uint32_t row_tokens = (total - 1u) * page + (uint32_t)(ll > 1 ? ll : 1);
+        tok_first = row_tokens > g_attention_window ? row_tokens - g_attention_window : 0u;
+    }
     for (uint32_t lb = blk_begin; lb < blk_end; ++lb) {
         const uint32_t phys = (uint32_t)indices[row0 + (int32_t)lb];
         uint32_t valid = page;
@@ -298,6 +312,7 @@ static void stream_blocks(const uint16_t* q_row, const uint16_t* cache_k, const 
         }
         const size_t base = ((size_t)phys * page * p->num_kv_heads + kv_head) * D;
         for (uint32_t t = 0; t < valid; ++t) {
+            if (lb * page + t < tok_first) continue;
             const uint16_t* kr = cache_k + base + t * tok_stride;
             const uint16_t* vr = cache_v + base + t * tok_stride;
             float lane[32];

@@ -45,7 +45,8 @@ def test_chained_pairs_apply_in_order():
     ex = make_executor(shape, 16, num_layers=2)
     for l in range(2):
         fill_cache(ex, l, ck[l], cv[l])
-    pairs = [(0, 1), (1, 2), (2, 3), (5, 5), (7, 3), (3, 9)]
+    # (10 -> 11) then (12 -> 10): block 10 is overwritten after it was read, block 11 must receive the old block 10
+    pairs = [(0, 1), (1, 2), (2, 3), (5, 5), (7, 3), (3, 9), (10, 11), (12, 10)]
     ex.kv_block_copy(pairs)
     O.block_copy(ck, cv, 2, pairs)
     for l in range(2):

@@ -11,7 +11,7 @@ from gpu_util import TOL, dev16, fill_cache, host16, make_executor, oracle_gqa, 
 pytestmark = pytest.mark.gpu
 
 
-def chunked_prefill(shape, total, chunk, num_blocks=256, seed=0, poison=True, other_seq_tokens=100):
+def chunked_prefill(shape, total, chunk, num_blocks=256, seed=0, poison=True, other_seq_tokens=100, window=0):
     """Runs a whole prompt through append_chunk + prefill in chunks on the GPU and the same through the oracle.
     Returns (gpu_out f32 [total,Hq,D], oracle_out f32, gpu cache, oracle cache)."""
     Hq, Hkv, D, dt = shape.num_q_heads, shape.num_kv_heads, shape.head_dim, shape.dtype
@@ -26,6 +26,7 @@ def chunked_prefill(shape, total, chunk, num_blocks=256, seed=0, poison=True, ot
     ck = np.full((num_blocks, 16, Hkv, D), fillbits, np.uint16)
     cv = np.full((num_blocks, 16, Hkv, D), fillbits, np.uint16)
     ex = make_executor(shape, num_blocks, max_query_tokens=max(chunk, 64))
+    ex.set_attention_window(window)
     fill_cache(ex, 0, ck, cv)
     rp, gp = ex.rope_params(), ex.gqa_params(max_query_tokens=chunk)
     outs = []
@@ -49,7 +50,11 @@ def chunked_prefill(shape, total, chunk, num_blocks=256, seed=0, poison=True, ot
         O.rope_kv_append(oq, k[start:start + n], v[start:start + n], ok, ov, rows.page_indptr, rows.page_indices,
                          rows.last_page_len, np.arange(start, start + n), oracle_rope(rp), dt, table=tab)
         assert np.array_equal(host16(dq), oq)
-        _, of = O.prefill_causal(oq, ok, ov, np.asarray(table, np.int32), start, oracle_gqa(ex), dt)
+        O.set_attention_window(window)
+        try:
+            _, of = O.prefill_causal(oq, ok, ov, np.asarray(table, np.int32), start, oracle_gqa(ex), dt)
+        finally:
+            O.set_attention_window(0)
         oouts.append(of)
     gk, gv = read_cache(ex, 0)
     ex.close()
@@ -73,6 +78,17 @@ def test_smollm_shape_head_dim_64(dtype):
     # P is rounded to the storage dtype before the P.V product, like the reference's tensor-core kernel
     # (paged_gqa_and_deltanet.metal:1386 stores P as half; its test allows 0.05)
     assert np.abs(got - ref).max() <= (4e-3 if dtype == W.FP16 else 1e-2)
+
+
+@pytest.mark.parametrize("window", [1, 100, 128, 300])
+def test_sliding_window_prefill(window):
+    """SlidingWindowCausal in the chunked prefill: every query attends its `window` most recent keys; KV tiles wholly in
+    front of a query tile's windows are skipped, rows whose window begins behind a tile see nothing of it."""
+    shape = W.AttnShape("pwin", 12, 2, 128, W.BF16, rope_theta=1e6)
+    got, ref, (gk, gv), (ok, ov) = chunked_prefill(shape, 700, 256, seed=17, window=window)
+    assert np.isfinite(got).all()
+    assert np.abs(got - ref).max() <= TOL[W.BF16]
+    assert np.array_equal(gk, ok) and np.array_equal(gv, ov)
 
 
 def test_reference_tiled_mma_prefill_case():

@@ -187,6 +187,52 @@ def test_decode_against_float64_softmax():
             assert np.abs(w @ v[:, h // (Hq // Hkv)] - outf[r, h]).max() < 1e-5
 
 
+@pytest.mark.parametrize("window", [1, 7, 64, 1000])
+def test_sliding_window_decode_and_prefill_against_float64_softmax(window):
+    """SlidingWindowCausal (crates/kriya-core/src/descriptor.rs:63-70; the reference declares the mask, no kernel of its
+    own reads it): the oracle's window - the last `window` keys of every query, the query's own position included -
+    against numpy float64 softmax over exactly those keys, for decode rows and for the queries of a prefill chunk."""
+    shape, batch, data = W.config1(dtype=O.BF16)
+    Hq, Hkv, D = shape.num_q_heads, shape.num_kv_heads, shape.head_dim
+    p = gqa(Hq, Hkv, D)
+    q = W.from_storage(data["q"], W.BF16).astype(np.float64)
+    K = W.from_storage(data["cache_k"], W.BF16).astype(np.float64)
+    V = W.from_storage(data["cache_v"], W.BF16).astype(np.float64)
+    scale = float(np.float32(p.sm_scale))
+
+    def softmax_attend(qv, k, v):
+        s = (k @ qv) * scale
+        w = np.exp(s - s.max())
+        return (w / w.sum()) @ v
+
+    O.set_attention_window(window)
+    try:
+        _, outf = O.decode(data["q"], data["cache_k"], data["cache_v"], batch.page_indptr, batch.page_indices,
+                           batch.last_page_len, p, O.BF16)
+        table = batch.page_indices[batch.page_indptr[3]:batch.page_indptr[4]]
+        prefix, n = 100, 40
+        _, pf = O.prefill_causal(np.tile(data["q"][:1], (n, 1, 1)), data["cache_k"], data["cache_v"], table, prefix, p, O.BF16)
+    finally:
+        O.set_attention_window(0)
+    for r in range(batch.batch):
+        blocks = batch.page_indices[batch.page_indptr[r]:batch.page_indptr[r + 1]]
+        L = (len(blocks) - 1) * 16 + batch.last_page_len[r]
+        lo = max(L - window, 0)
+        k = K[blocks].reshape(-1, Hkv, D)[lo:L]
+        v = V[blocks].reshape(-1, Hkv, D)[lo:L]
+        for h in range(Hq):
+            g = h // (Hq // Hkv)
+            assert np.abs(softmax_attend(q[r, h], k[:, g], v[:, g]) - outf[r, h]).max() < 1e-5
+    kk = K[table].reshape(-1, Hkv, D)
+    vv = V[table].reshape(-1, Hkv, D)
+    for i in (0, 1, n - 1):
+        hi = prefix + i + 1
+        lo = max(hi - window, 0)
+        for h in (0, Hq - 1):
+            g = h // (Hq // Hkv)
+            assert np.abs(softmax_attend(q[0, h], kk[lo:hi, g], vv[lo:hi, g]) - pf[i, h]).max() < 1e-5
+
+
 def test_block_copy_and_slot_write_are_bytewise():
     rng = np.random.default_rng(5)
     ck = rng.integers(0, 65536, (3, 8, 16, 2, 64), dtype=np.uint16)

@@ -2,8 +2,9 @@
 
 It serves callers that may not call cudaMalloc and so cannot create a context: every buffer here is the caller's
 (torch tensors stand in for the host application's arena), the library's scratch is its built-in device array.
-The result must equal the context-based entry point's on the same inputs, on two calls in a row (the second call
-finds the array as the first one left it)."""
+The result must equal the context-based entry point's bit for bit on the same inputs (both run the same kernel over
+the same work split) and agree with the CPU oracle, on two calls in a row (the second call finds the array as the
+first one left it)."""
 import ctypes as C
 
 import numpy as np
@@ -13,6 +14,7 @@ import torch
 from kriya_rt_b200 import _native as N
 from kriya_rt_b200 import workloads as W
 from gpu_util import TOL, dev16, fill_cache, host16, make_executor
+from oracle import c_oracle as O
 
 pytestmark = pytest.mark.gpu
 
@@ -34,6 +36,26 @@ def _call_static(lib, shape, batch, q, ck_dev, cv_dev, out, stream=0):
     return rc, err.value.decode()
 
 
+def _oracle_decode(shape, batch, q16, ck, cv):
+    scale = float(np.float32(1.0) / np.sqrt(np.float32(shape.head_dim)))
+    p = O.GqaParams(shape.num_q_heads, shape.num_kv_heads, shape.head_dim, 16, 16, 1, scale, 0.0)
+    return O.decode(q16, ck, cv, batch.page_indptr, batch.page_indices, batch.last_page_len, p, shape.dtype)[1]
+
+
+def _context_decode(shape, batch, q, ck, cv, num_blocks):
+    """The existing entry point on the CUDA-core kernel (the kernel the static variant launches)."""
+    ex = make_executor(shape, num_blocks, max_batch_rows=max(64, batch.batch), max_page_indices=max(16384, num_blocks))
+    ex.set_decode_path(1)
+    fill_cache(ex, 0, ck, cv)
+    out = torch.zeros_like(q)
+    torch.cuda.synchronize()
+    ex.upload_schedule_plan(batch, batch.positions)
+    ex.paged_gqa_decode(0, q, out, ex.gqa_params())
+    ex.sync()
+    ex.close()
+    return out
+
+
 @pytest.mark.parametrize("Hq,Hkv,D,dtype", [(16, 2, 128, W.BF16), (9, 3, 64, W.FP16)])
 def test_static_scratch_decode_matches_context_decode_twice(Hq, Hkv, D, dtype):
     lib = N.cuda_lib()
@@ -49,20 +71,39 @@ def test_static_scratch_decode_matches_context_decode_twice(Hq, Hkv, D, dtype):
         out_static = torch.zeros_like(q)
         rc, msg = _call_static(lib, shape, batch, q, ck_dev, cv_dev, out_static)
         assert rc == 0, msg
-        # the existing entry point, CUDA-core kernel (the same kernel the static variant launches)
-        ex = make_executor(shape, 1024)
-        ex.set_decode_path(1)
-        fill_cache(ex, 0, ck, cv)
-        out_ctx = torch.zeros_like(q)
+        out_ctx = _context_decode(shape, batch, q, ck, cv, 1024)
+        assert np.array_equal(host16(out_static), host16(out_ctx))  # same kernel, same split: the same bits
+        got = W.from_storage(host16(out_static), dtype)
+        assert np.isfinite(got).all()
+        assert np.abs(got - _oracle_decode(shape, batch, q16, ck, cv)).max() <= TOL[dtype]
+
+
+def test_static_scratch_on_a_side_stream_with_the_coarser_split():
+    """A batch whose first split would need more than 512 work items takes the coarser second cut; the call is queued
+    on a stream of the caller's own and leaves the caller's current device alone."""
+    lib = N.cuda_lib()
+    shape = W.AttnShape("static", 16, 2, 128, W.BF16)
+    ctx = np.concatenate([np.full(200, 10), 3000 + 37 * np.arange(56)])  # 200 one-block rows + 56 long rows
+    nb = 14336
+    rng = np.random.default_rng(73)
+    batch = W.make_decode_batch(shape, ctx, nb, seed=74)
+    ck = W.normal16(rng, (nb, 16, 2, 128), W.BF16)
+    cv = W.normal16(rng, (nb, 16, 2, 128), W.BF16)
+    ck_dev, cv_dev = dev16(ck), dev16(cv)
+    q16 = W.normal16(rng, (ctx.size, 16, 128), W.BF16)
+    q = dev16(q16)
+    ref = _oracle_decode(shape, batch, q16, ck, cv)
+    side = torch.cuda.Stream()
+    dev_before = torch.cuda.current_device()
+    for _ in range(2):
+        out = torch.zeros_like(q)
         torch.cuda.synchronize()
-        ex.upload_schedule_plan(batch, batch.positions)
-        ex.paged_gqa_decode(0, q, out_ctx, ex.gqa_params())
-        ex.sync()
-        ex.close()
-        a = W.from_storage(host16(out_static), dtype)
-        b = W.from_storage(host16(out_ctx), dtype)
-        assert np.isfinite(a).all()
-        assert np.abs(a - b).max() <= TOL[dtype]
+        rc, msg = _call_static(lib, shape, batch, q, ck_dev, cv_dev, out, stream=side.cuda_stream)
+        assert rc == 0, msg
+        assert torch.cuda.current_device() == dev_before
+        got = W.from_storage(host16(out), W.BF16)
+        assert np.isfinite(got).all()
+        assert np.abs(got - ref).max() <= TOL[W.BF16]
 
 
 def test_static_scratch_limits_are_rejected_with_a_message():
