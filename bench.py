@@ -279,8 +279,7 @@ def run_gpu_arm(args):
     seq_ids = list(range(BATCH))
 
     def step_plan(mgr, t):
-        for s in seq_ids:
-            mgr.append_token_slot(s)
+        mgr.append_token_slots(seq_ids)  # one append_token_slot per sequence, in the scheduler's order
         plan = mgr.build_schedule_plan(seq_ids, 8)
         positions = (ctx0 + t).astype(np.uint32)
         return plan, positions
@@ -825,28 +824,38 @@ def run_kernel_case(args):
         per = total // 16
         ex.plan_upload(np.arange(n_seq + 1) * per, perm, [16] * n_seq)
         q = rnd(n_seq * chunk, 12, 128)
+        kin, vin = rnd(n_seq * chunk, 2, 128), rnd(n_seq * chunk, 2, 128)
         out = torch.zeros_like(q)
         torch.cuda.synchronize()
         gp = ex.gqa_params(max_query_tokens=chunk)
+        rp = ex.rope_params()
         stream = torch.cuda.ExternalStream(ex.stream_ptr)
         starts = np.arange(n_seq) * chunk
 
-        def all_chunks():
+        def all_chunks(with_append):
             for prefix in range(0, total, chunk):
+                if with_append:  # each chunk writes its RoPE'd K/V into the 16-token blocks, then attends
+                    ex.rope_kv_append_chunk_batch(0, q, kin, vin, starts, [prefix] * n_seq, [chunk] * n_seq, rp)
                 ex.paged_gqa_prefill_batch(0, q, out, starts, [prefix] * n_seq, [chunk] * n_seq, gp)
 
-        all_chunks()
-        ex.sync()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(stream)
-        for _ in range(reps):
-            all_chunks()
-        e1.record(stream)
-        ex.sync()
-        us = e0.elapsed_time(e1) / reps * 1e3
+        res = {}
+        for name, with_append in (("append_and_attention", True), ("attention_only", False)):
+            all_chunks(with_append)
+            ex.sync()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(reps):
+                all_chunks(with_append)
+            e1.record(stream)
+            ex.sync()
+            res[name] = e0.elapsed_time(e1) / reps * 1e3
+        us = res["append_and_attention"]
         flop = n_seq * 4 * 12 * 128 * (total * (total + 1) // 2)
-        print(json.dumps({"case": case, "launches_per_pass": total // chunk, "us_per_pass": us, "flop_per_pass": flop,
-                          "tflops": flop / (us * 1e-6) / 1e12, "prompt_tokens_per_s_per_layer": n_seq * total / (us * 1e-6)}))
+        print(json.dumps({"case": case, "launches_per_pass": 2 * (total // chunk), "us_per_pass": us, "flop_per_pass": flop,
+                          "tflops": flop / (us * 1e-6) / 1e12, "us_per_pass_attention_only": res["attention_only"],
+                          "tflops_attention_only": flop / (res["attention_only"] * 1e-6) / 1e12,
+                          "prompt_tokens_per_s_per_layer": n_seq * total / (us * 1e-6),
+                          "note": "every chunk: one append launch (RoPE + K/V into the paged cache, all prompts) + one attention launch"}))
         ex.close()
     elif case == "prefill":
         sh = W.QWEN25_1P5B

@@ -45,6 +45,10 @@ typedef enum kriya_cuda_status {
 } kriya_cuda_status;
 
 enum { KRIYA_DTYPE_BF16 = 0, KRIYA_DTYPE_FP16 = 1 };
+/* Storage of the KV cache.  KRIYA_KV_Q4_GROUP32 is DType::Q4KvGroup32 (crates/kriya-core/src/tensor.rs:50-51,77,91; switched
+ * on by compress_kv_cache_q4, crates/kriya-core/src/hardware.rs:57,159-165): every 32 values of a cached K or V row are 16
+ * bytes of 4-bit codes + f16 scale + f16 min = 20 bytes, value = code * scale + min.  Activations stay 16-bit. */
+enum { KRIYA_KV_16BIT = 0, KRIYA_KV_Q4_GROUP32 = 1 };
 
 /* RopeKvWriteParams, 48 bytes, byte-identical to enc:159-174 / paged_gqa_and_deltanet.metal:72-85. */
 typedef struct kriya_rope_kv_write_params {
@@ -94,6 +98,7 @@ typedef struct kriya_cuda_config {
     uint32_t max_page_indices;   /* page_indices entries per plan; 0 -> max(16384, num_kv_blocks) */
     uint32_t max_tiles;          /* cta_work_tiles entries per plan; 0 -> 4096 */
     uint32_t max_query_tokens;   /* tokens per append / prefill call; 0 -> 8192 */
+    uint32_t kv_format;          /* KRIYA_KV_*: 16-bit cache (default) or Q4KvGroup32 */
 } kriya_cuda_config;
 
 /* ---- context ------------------------------------------------------------------------------- */
@@ -151,6 +156,15 @@ int32_t kriya_cuda_rope_kv_append_chunk(kriya_cuda_ctx* ctx, uint32_t layer, voi
                                         const void* v_in_dev, const void* q_norm_w_dev, const void* k_norm_w_dev,
                                         uint32_t prefix_tokens, uint32_t num_tokens,
                                         const kriya_rope_kv_write_params* params);
+
+/* The same for the chunks of several sequences in ONE launch, with the arguments of kriya_cuda_paged_gqa_prefill_batch:
+ * plan row r is sequence r's block table, its count_host[r] tokens are rows q_start_host[r] .. of q / k / v and land at
+ * absolute positions prefix_host[r] + i.  (The reference appends per request, enc:4218-4256, one forward_prefill_batch
+ * call each, crates/kriya-server/src/runtime.rs:315-377.) */
+int32_t kriya_cuda_rope_kv_append_chunk_batch(kriya_cuda_ctx* ctx, uint32_t layer, void* q_inout_dev, const void* k_in_dev,
+                                              const void* v_in_dev, const void* q_norm_w_dev, const void* k_norm_w_dev,
+                                              uint32_t n_seqs, const uint32_t* q_start_host, const uint32_t* prefix_host,
+                                              const uint32_t* count_host, const kriya_rope_kv_write_params* params);
 
 /* bsr_paged_gqa_decode_stage1 + bsr_paged_gqa_split_k_reduce (paged_gqa_and_deltanet.metal:242-495,
  * 1474-1525; dispatch enc:4986-5053) behind one call.  For every row r of the current plan, query

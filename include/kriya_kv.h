@@ -81,6 +81,12 @@ int32_t kriya_kv_allocate_sequence(kriya_kv_manager* m, uint64_t seq_id, const u
 /* append_token_slot, bsr_paged.rs:389-426.  *out_has_cow is 1 when a (src,dst) pair is returned. */
 int32_t kriya_kv_append_token_slot(kriya_kv_manager* m, uint64_t seq_id, uint32_t* out_block, int32_t* out_has_cow,
                                    uint32_t* out_cow_src, uint32_t* out_cow_dst);
+/* The scheduler's per-iteration loop over the running sequences (crates/kriya-scheduler/src/orca_engine.rs:267-278): one
+ * append_token_slot per sequence, in order, collecting the copy-on-write pairs.  out_blocks holds n entries, out_cow_pairs
+ * up to n (src, dst) pairs, *out_n_cow how many were emitted.  Stops at the first failing sequence (the error of
+ * append_token_slot; *out_done says how many sequences were appended before it). */
+int32_t kriya_kv_append_token_slots(kriya_kv_manager* m, const uint64_t* seq_ids, size_t n, uint32_t* out_blocks,
+                                    uint32_t* out_cow_pairs, size_t* out_n_cow, size_t* out_done);
 /* fork_sequence bsr_paged.rs:430-454, free_sequence :457-467, contains_sequence :471-473 */
 int32_t kriya_kv_fork_sequence(kriya_kv_manager* m, uint64_t parent_seq_id, uint64_t child_seq_id);
 int32_t kriya_kv_free_sequence(kriya_kv_manager* m, uint64_t seq_id);

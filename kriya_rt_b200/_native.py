@@ -63,7 +63,8 @@ class CudaConfig(C.Structure):
                 ("block_size_tokens", C.c_uint32), ("num_q_heads", C.c_uint32), ("num_kv_heads", C.c_uint32),
                 ("head_dim", C.c_uint32), ("dtype", C.c_uint32), ("rotary_dim", C.c_uint32),
                 ("rope_theta", C.c_float), ("rope_max_seq_len", C.c_uint32), ("max_batch_rows", C.c_uint32),
-                ("max_page_indices", C.c_uint32), ("max_tiles", C.c_uint32), ("max_query_tokens", C.c_uint32)]
+                ("max_page_indices", C.c_uint32), ("max_tiles", C.c_uint32), ("max_query_tokens", C.c_uint32),
+                ("kv_format", C.c_uint32)]
 
 
 assert C.sizeof(CtaWorkTile) == 16 and C.sizeof(RopeKvWriteParams) == 48 and C.sizeof(BsrGqaParams) == 32
@@ -84,6 +85,8 @@ KV_SYMBOLS = {
                                                C.POINTER(C.c_size_t)]),
     "kriya_kv_append_token_slot": (C.c_int32, [C.c_void_p, C.c_uint64, C.POINTER(C.c_uint32), C.POINTER(C.c_int32),
                                                C.POINTER(C.c_uint32), C.POINTER(C.c_uint32)]),
+    "kriya_kv_append_token_slots": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p,
+                                                C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)]),
     "kriya_kv_fork_sequence": (C.c_int32, [C.c_void_p, C.c_uint64, C.c_uint64]),
     "kriya_kv_free_sequence": (C.c_int32, [C.c_void_p, C.c_uint64]),
     "kriya_kv_contains_sequence": (C.c_int32, [C.c_void_p, C.c_uint64]),
@@ -116,6 +119,8 @@ CUDA_SYMBOLS = {
                                               C.POINTER(RopeKvWriteParams)]),
     "kriya_cuda_rope_kv_append_chunk": (C.c_int32, [_VP, C.c_uint32, _VP, _VP, _VP, _VP, _VP, C.c_uint32, C.c_uint32,
                                                     C.POINTER(RopeKvWriteParams)]),
+    "kriya_cuda_rope_kv_append_chunk_batch": (C.c_int32, [_VP, C.c_uint32, _VP, _VP, _VP, _VP, _VP, C.c_uint32, _VP, _VP, _VP,
+                                                          C.POINTER(RopeKvWriteParams)]),
     "kriya_cuda_paged_gqa_decode": (C.c_int32, [_VP, C.c_uint32, _VP, _VP, C.POINTER(BsrGqaParams)]),
     "kriya_cuda_paged_gqa_decode_partial": (C.c_int32, [_VP, C.c_uint32, _VP, _VP, _VP, _VP, _VP, _VP,
                                                         C.POINTER(BsrGqaParams)]),

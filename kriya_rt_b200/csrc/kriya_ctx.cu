@@ -215,6 +215,43 @@ uint32_t build_tc_segments(const int32_t* indptr, const int32_t* last_len, uint3
     return n;
 }
 
+// The whole-page kernel reads one 48-byte record per CTA instead of two entries of the segment-range list: word 0 the
+// CTA's first segment (the next record's word 0 is its end), word 1 the pages of the CTA's first tile that may be fetched
+// before anything else is known (0 = none: the tile holds the end of its row, which a fused append still has to write),
+// word 2 the place of the first of them inside the tile, word 3 the row of the first piece the CTA works on (UINT32_MAX:
+// none), words 4-7 the pool blocks of those pages, word 8 the position of that row's new token.  With it the first K/V
+// bytes and the first query rows are asked for one memory round trip after the CTA starts instead of three or four
+// (range list, segment, block table or position, data).
+constexpr uint32_t kTcpHdrWords = 12;
+void expand_tcp_headers(uint32_t* ptr, uint32_t ctas, const KriyaTcSeg* segs, const int32_t* indices, uint32_t TP, uint32_t block_size,
+                        const uint32_t* positions, uint32_t n_positions) {
+    for (uint32_t k = ctas + 1; k-- > 0;) {
+        const uint32_t v = ptr[k];
+        uint32_t* h = ptr + size_t(k) * kTcpHdrWords;
+        for (uint32_t i = 1; i < kTcpHdrWords; ++i) h[i] = 0u;
+        h[0] = v;
+        h[3] = UINT32_MAX;
+    }
+    for (uint32_t k = 0; k < ctas; ++k) {
+        uint32_t* h = ptr + size_t(k) * kTcpHdrWords;
+        for (uint32_t si = h[0]; si < h[kTcpHdrWords]; ++si) {
+            const KriyaTcSeg& s = segs[si];
+            if (s.blk_hi <= s.blk_lo) continue;
+            h[3] = s.req;
+            h[8] = s.req < n_positions ? positions[s.req] : (s.row_tokens ? s.row_tokens - 1u : 0u);
+            const uint32_t t0 = s.blk_lo / TP, t1 = (s.blk_hi + TP - 1) / TP;
+            const bool row_end = uint64_t(s.blk_hi) * block_size >= s.row_tokens;
+            if (!(t0 + 1 == t1 && row_end)) {
+                const uint32_t p_lo = std::max(t0 * TP, s.blk_lo), p_hi = std::min((t0 + 1) * TP, s.blk_hi);
+                h[1] = p_hi - p_lo;
+                h[2] = p_lo - t0 * TP;
+                for (uint32_t i = 0; i < p_hi - p_lo && i < 4u; ++i) h[4 + i] = uint32_t(indices[s.tbl_off + p_lo + i]);
+            }
+            break;
+        }
+    }
+}
+
 // Which build of the tensor-core decode kernel serves a plan: the 64-token-tile build (two CTAs per SM) streams faster
 // but pays its per-CTA costs twice as often, so it is taken when every SM has a long stream ahead of it.
 constexpr uint32_t kLateMergeParts = 12;  // runs cut into more pieces are merged by late_merge_kernel
@@ -245,8 +282,7 @@ struct TcVariantGeometry {
 };
 TcVariantGeometry tc_geometry(const kriya_cuda_ctx* c, int variant) {
     const uint32_t sms = uint32_t(c->sm_count);
-    // the fewest tiles a CTA is given are the same 64 KB of K/V per unit of tc_min_tiles_per_cta() for every variant
-    if (variant == 2) return {sms, kriya_decode_tcp_pages_per_tile(), 1u, 2u * tc_min_tiles_per_cta()};
+    if (variant == 2) return {sms, kriya_decode_tcp_pages_per_tile(), 1u, tc_min_tiles_per_cta()};
     if (variant == 1) return {sms * kriya_decode_tc_ctas_per_sm_t64(), kriya_decode_tc_pages_per_tile_t64(), c->cfg.num_kv_heads, tc_min_tiles_per_cta()};
     return {sms * kriya_decode_tc_ctas_per_sm(), kriya_decode_tc_pages_per_tile(), c->cfg.num_kv_heads, tc_min_tiles_per_cta()};
 }
@@ -347,6 +383,7 @@ int32_t launch_append(kriya_cuda_ctx* c, uint32_t layer, void* q, const void* k,
     a.num_blocks = c->cfg.num_kv_blocks;
     a.chunk_mode = chunk_mode;
     a.prefix_tokens = prefix;
+    a.kv_q4 = c->cfg.kv_format == KRIYA_KV_Q4_GROUP32 ? 1u : 0u;
     a.p = *p;
     TimingScope ts(c, 1);
     KRIYA_CUDA_TRY(c, kriya_launch_append(a, c->cfg.dtype, c->stream));
@@ -422,8 +459,8 @@ int32_t launch_decode(kriya_cuda_ctx* c, uint32_t layer, const void* q, void* ou
         c->tc_done_expect[set] += grid;  // every CTA of the grid counts itself off, idle ones included
         if (late) c->launches += 1;
     } else {
-        KRIYA_CUDA_TRY(c, kriya_launch_decode(a, c->cfg.head_dim, c->cfg.block_size_tokens, c->cfg.dtype,
-                                              c->max_smem_optin, c->stream));
+        KRIYA_CUDA_TRY(c, kriya_launch_decode(a, c->cfg.head_dim, c->cfg.block_size_tokens, c->cfg.dtype, c->max_smem_optin,
+                                              c->stream, c->cfg.kv_format == KRIYA_KV_Q4_GROUP32 ? 1u : 0u));
     }
     c->launches += 1;
     return KRIYA_CUDA_OK;
@@ -450,6 +487,10 @@ int32_t kriya_cuda_ctx_create(const kriya_cuda_config* cfg_in, kriya_cuda_ctx** 
         return bad(KRIYA_CUDA_INVALID_INPUT, "dtype must be KRIYA_DTYPE_BF16 or KRIYA_DTYPE_FP16");
     if ((cfg.head_dim * 2u) % 16u != 0)
         return bad(KRIYA_CUDA_UNSUPPORTED, "head_dim must make head rows a multiple of 16 bytes");
+    if (cfg.kv_format != KRIYA_KV_16BIT && cfg.kv_format != KRIYA_KV_Q4_GROUP32)
+        return bad(KRIYA_CUDA_INVALID_INPUT, "kv_format must be KRIYA_KV_16BIT or KRIYA_KV_Q4_GROUP32");
+    if (cfg.kv_format == KRIYA_KV_Q4_GROUP32 && cfg.head_dim != 64 && cfg.head_dim != 128)
+        return bad(KRIYA_CUDA_UNSUPPORTED, "the Q4KvGroup32 cache covers head_dim 64 and 128");
     if (cfg.rotary_dim == 0) cfg.rotary_dim = cfg.head_dim;  // enc:1929-1933
     if (cfg.rope_theta == 0.0f) cfg.rope_theta = 10000.0f;
     if (cfg.rope_max_seq_len == 0) cfg.rope_max_seq_len = 4096;  // enc:1939
@@ -486,7 +527,9 @@ int32_t kriya_cuda_ctx_create(const kriya_cuda_config* cfg_in, kriya_cuda_ctx** 
         c->tc64_min_tiles = m ? uint32_t(std::max(1, atoi(m))) : 96u;
     }
     c->max_smem_optin = int(prop.sharedMemPerBlockOptin);
-    c->block_bytes = size_t(cfg.block_size_tokens) * cfg.num_kv_heads * cfg.head_dim * 2;
+    c->block_bytes = cfg.kv_format == KRIYA_KV_Q4_GROUP32
+                         ? size_t(cfg.block_size_tokens) * cfg.num_kv_heads * (cfg.head_dim / 32) * 20  // 20 bytes per 32 values
+                         : size_t(cfg.block_size_tokens) * cfg.num_kv_heads * cfg.head_dim * 2;
     c->layer_stride_bytes = align_up(size_t(cfg.num_kv_blocks) * c->block_bytes, 256);  // enc:1890-1894
     c->cap_rows = cfg.max_batch_rows;
     c->cap_indices = cfg.max_page_indices;
@@ -524,7 +567,8 @@ int32_t kriya_cuda_ctx_create(const kriya_cuda_config* cfg_in, kriya_cuda_ctx** 
     CREATE_TRY(cudaMemsetAsync(c->pool_v, 0, pool_bytes, c->stream));
 
     // tensor maps for the prefill kernel's paged gather (rows of all layers back to back)
-    if (kriya_prefill_supported(cfg.head_dim, cfg.num_q_heads / cfg.num_kv_heads, cfg.block_size_tokens, cfg.dtype) &&
+    if (cfg.kv_format == KRIYA_KV_16BIT &&
+        kriya_prefill_supported(cfg.head_dim, cfg.num_q_heads / cfg.num_kv_heads, cfg.block_size_tokens, cfg.dtype) &&
         c->layer_stride_bytes % (size_t(cfg.num_kv_heads) * cfg.head_dim * 2) == 0 &&
         (size_t(cfg.num_kv_heads) * cfg.head_dim * 2) % 16 == 0) {
         const uint32_t row_elems = cfg.num_kv_heads * cfg.head_dim;
@@ -569,7 +613,7 @@ int32_t kriya_cuda_ctx_create(const kriya_cuda_config* cfg_in, kriya_cuda_ctx** 
     c->off_range = off;  // second work list, used by the block-range (partial state) decode
     off = align_up(off + size_t(c->cap_work) * sizeof(KriyaDecodeWork), 256);
     c->off_tcptr2 = off;
-    off = align_up(off + (size_t(c->tc_ctas) + 1) * 4, 256);
+    off = align_up(off + (size_t(c->tc_ctas) + 1) * 4 * kTcpHdrWords, 256);
     c->off_tcseg2 = off;
     off = align_up(off + size_t(c->cap_seg) * sizeof(KriyaTcSeg), 256);
     c->dyn_base = off;
@@ -577,7 +621,7 @@ int32_t kriya_cuda_ctx_create(const kriya_cuda_config* cfg_in, kriya_cuda_ctx** 
     off = align_up(off + size_t(c->cap_rows) * 4, 256);                            // last_page_len
     off = align_up(off + size_t(c->cap_tokens) * 4, 256);                          // positions
     off = align_up(off + size_t(c->cap_work) * sizeof(KriyaDecodeWork), 256);      // work list
-    off = align_up(off + (size_t(c->tc_ctas) + 1) * 4, 256);                       // per-CTA segment ranges
+    off = align_up(off + (size_t(c->tc_ctas) + 1) * 4 * kTcpHdrWords, 256);        // per-CTA segment ranges / records
     off = align_up(off + size_t(c->cap_seg) * sizeof(KriyaTcSeg), 256);            // segments
     off = align_up(off + size_t(c->cap_tiles) * sizeof(kriya_cta_work_tile), 256); // caller tiles
     off = align_up(off + size_t(c->cap_indices) * 4, 256);                         // page indices
@@ -759,12 +803,15 @@ int32_t kriya_cuda_plan_upload(kriya_cuda_ctx* c, const int32_t* indptr, size_t 
     const int variant = choose_tc_variant(c, indptr, uint32_t(rows), nullptr, nullptr);
     const TcVariantGeometry geo = tc_geometry(c, variant);
     const uint32_t plan_ctas = geo.ctas;
-    const size_t o_ptr = place((size_t(plan_ctas) + 1) * 4);
+    const size_t o_ptr = place((size_t(plan_ctas) + 1) * 4 * (variant == 2 ? kTcpHdrWords : 1u));
     const size_t o_seg = off;
     const uint32_t n_seg = build_tc_segments(indptr, last_len, c->cfg.block_size_tokens, uint32_t(rows), geo.runs_per_row, nullptr,
                                              nullptr, plan_ctas, geo.pages_per_tile, reinterpret_cast<KriyaTcSeg*>(h + o_seg),
                                              c->cap_seg, reinterpret_cast<uint32_t*>(h + o_ptr), geo.min_tiles, c->attention_window);
     if (n_seg == UINT32_MAX) return invalid("plan needs more decode segments than the context holds");
+    if (variant == 2)
+        expand_tcp_headers(reinterpret_cast<uint32_t*>(h + o_ptr), plan_ctas, reinterpret_cast<const KriyaTcSeg*>(h + o_seg), indices,
+                           geo.pages_per_tile, c->cfg.block_size_tokens, positions, uint32_t(n_positions));
     place(size_t(n_seg) * sizeof(KriyaTcSeg));
     const size_t o_tiles = place(std::max<size_t>(tiles_len, 1) * sizeof(kriya_cta_work_tile));
     if (tiles_len) memcpy(h + o_tiles, tiles, tiles_len * sizeof(kriya_cta_work_tile));
@@ -844,6 +891,65 @@ int32_t kriya_cuda_rope_kv_append_chunk(kriya_cuda_ctx* c, uint32_t layer, void*
     return launch_append(c, layer, q, k, v, qw, kw, num_tokens, 1, prefix_tokens, p);
 }
 
+int32_t kriya_cuda_rope_kv_append_chunk_batch(kriya_cuda_ctx* c, uint32_t layer, void* q, const void* k, const void* v,
+                                              const void* qw, const void* kw, uint32_t n_seqs, const uint32_t* q_start,
+                                              const uint32_t* prefix, const uint32_t* count, const kriya_rope_kv_write_params* p) {
+    if (!c) return KRIYA_CUDA_INVALID_INPUT;
+    if (int32_t rc = check_layer(c, layer)) return rc;
+    if (int32_t rc = check_rope(c, p)) return rc;
+    if (!c->plan_valid) return c->fail(KRIYA_CUDA_INVALID_INPUT, "no plan uploaded");
+    if (!q || !k || !v || !q_start || !prefix || !count) return c->fail(KRIYA_CUDA_INVALID_INPUT, "q, k, v and the per-sequence arrays must not be null");
+    if (p->apply_qk_norm && (!qw || !kw)) return c->fail(KRIYA_CUDA_INVALID_INPUT, "apply_qk_norm needs both norm weights");
+    if (n_seqs == 0) return c->fail(KRIYA_CUDA_INVALID_INPUT, "input_tokens must not be empty");
+    if (n_seqs > c->n_rows) return c->fail(KRIYA_CUDA_INVALID_INPUT, "more sequences than plan rows");
+    if (size_t(n_seqs) * 3 > size_t(c->cap_pairs) * 3) return c->fail(KRIYA_CUDA_INVALID_INPUT, "more sequences than the context holds");
+    const int32_t* indptr = reinterpret_cast<const int32_t*>(c->h_plan_last + c->off_indptr);
+    uint32_t rows = 0;
+    for (uint32_t r = 0; r < n_seqs; ++r) {
+        if (count[r] == 0) return c->fail(KRIYA_CUDA_INVALID_INPUT, "input_tokens must not be empty");
+        const uint64_t end = uint64_t(prefix[r]) + count[r];
+        if (end > uint64_t(indptr[r + 1] - indptr[r]) * c->cfg.block_size_tokens)
+            return c->fail(KRIYA_CUDA_INVALID_INPUT, "chunk of sequence " + std::to_string(r) + " ends at token " + std::to_string(end) +
+                                                         " but its plan row holds " + std::to_string(indptr[r + 1] - indptr[r]) + " blocks");
+        if (uint64_t(q_start[r]) + count[r] > c->cap_tokens) return c->fail(KRIYA_CUDA_INVALID_INPUT, "chunk exceeds max_query_tokens");
+        rows = std::max(rows, q_start[r] + count[r]);
+    }
+    cudaSetDevice(c->cfg.device);
+    KRIYA_CUDA_TRY(c, cudaEventSynchronize(c->h_pairs_free));
+    memcpy(c->h_pairs, q_start, size_t(n_seqs) * 4);
+    memcpy(c->h_pairs + n_seqs, prefix, size_t(n_seqs) * 4);
+    memcpy(c->h_pairs + 2 * size_t(n_seqs), count, size_t(n_seqs) * 4);
+    KRIYA_CUDA_TRY(c, cudaMemcpyAsync(c->d_pairs, c->h_pairs, size_t(n_seqs) * 12, cudaMemcpyHostToDevice, c->stream));
+    KRIYA_CUDA_TRY(c, cudaEventRecord(c->h_pairs_free, c->stream));
+    KriyaAppendArgs a{};
+    a.q_inout = q;
+    a.k_in = k;
+    a.v_in = v;
+    a.q_norm_w = qw;
+    a.k_norm_w = kw;
+    a.cache_k = c->layer_k(layer);
+    a.cache_v = c->layer_v(layer);
+    a.indptr = c->plan_dev<int32_t>(c->off_indptr);
+    a.indices = c->plan_dev<int32_t>(c->off_indices);
+    a.last_len = c->plan_dev<int32_t>(c->off_last_len);
+    a.positions = c->plan_dev<uint32_t>(c->off_positions);
+    a.table = table_for(c, p);
+    a.status = c->d_status;
+    a.num_tokens = rows;
+    a.num_blocks = c->cfg.num_kv_blocks;
+    a.chunk_mode = 2;
+    a.kv_q4 = c->cfg.kv_format == KRIYA_KV_Q4_GROUP32 ? 1u : 0u;
+    a.seq_q_start = c->d_pairs;
+    a.seq_prefix = c->d_pairs + n_seqs;
+    a.seq_count = c->d_pairs + 2 * size_t(n_seqs);
+    a.n_seqs = n_seqs;
+    a.p = *p;
+    TimingScope ts(c, 1);
+    KRIYA_CUDA_TRY(c, kriya_launch_append(a, c->cfg.dtype, c->stream));
+    c->launches += 1;
+    return KRIYA_CUDA_OK;
+}
+
 int32_t kriya_cuda_rope_inplace(kriya_cuda_ctx* c, void* q, void* k, const void* qw, const void* kw, uint32_t num_tokens,
                                 const kriya_rope_kv_write_params* p) {
     if (!c) return KRIYA_CUDA_INVALID_INPUT;
@@ -887,6 +993,7 @@ int32_t kriya_cuda_tree_verify(kriya_cuda_ctx* c, uint32_t layer, const void* tq
     if (n > kTreeMaxNodes) return c->fail(KRIYA_CUDA_INVALID_INPUT, "a draft tree may hold at most 128 nodes");
     if (c->cfg.head_dim != 64 && c->cfg.head_dim != 128)
         return c->fail(KRIYA_CUDA_UNSUPPORTED, "tree verification covers head_dim 64/128");
+    if (c->cfg.kv_format != KRIYA_KV_16BIT) return c->fail(KRIYA_CUDA_UNSUPPORTED, "tree verification covers the 16-bit cache");
     const bool has_prefix = p->prefix_kv_blocks > 0;
     if (has_prefix) {
         if (p->prefix_last_len == 0 || p->prefix_last_len > p->block_size_tokens)
@@ -989,6 +1096,9 @@ int32_t kriya_cuda_plan_set_ranges(kriya_cuda_ctx* c, const uint32_t* blk_begin,
         geo.runs_per_row, blk_begin, blk_end, geo.ctas, geo.pages_per_tile, segs, c->cap_seg, sptr, geo.min_tiles,
         c->attention_window);
     if (n_seg == UINT32_MAX) return c->fail(KRIYA_CUDA_INVALID_INPUT, "ranges need more segments than the context holds");
+    if (c->tc_variant_ranges == 2)
+        expand_tcp_headers(sptr, geo.ctas, segs, reinterpret_cast<const int32_t*>(c->h_plan_last + c->off_indices), geo.pages_per_tile,
+                           c->cfg.block_size_tokens, reinterpret_cast<const uint32_t*>(c->h_plan_last + c->off_positions), c->n_positions);
     c->n_seg_ranges = n_seg;
     c->tc_max_parts_ranges = max_parts_of(segs, n_seg);
     KRIYA_CUDA_TRY(c, cudaMemcpyAsync(c->d_plan + c->off_tcptr2, sptr, c->off_tcseg2 - c->off_tcptr2 + size_t(n_seg) * sizeof(KriyaTcSeg),
@@ -1057,7 +1167,7 @@ int32_t kriya_cuda_paged_gqa_prefill_batch(kriya_cuda_ctx* c, uint32_t layer, co
     if (n_seqs > c->n_rows) return c->fail(KRIYA_CUDA_INVALID_INPUT, "more sequences than plan rows");
     if (!kriya_prefill_supported(c->cfg.head_dim, c->cfg.num_q_heads / c->cfg.num_kv_heads, c->cfg.block_size_tokens,
                                  c->cfg.dtype) || !c->tmaps_ok)
-        return c->fail(KRIYA_CUDA_UNSUPPORTED, "prefill kernels cover head_dim 64/128 and 16-token blocks");
+        return c->fail(KRIYA_CUDA_UNSUPPORTED, "prefill kernels cover head_dim 64/128, 16-token blocks and the 16-bit cache");
     cudaSetDevice(c->cfg.device);
     KRIYA_CUDA_TRY(c, cudaEventSynchronize(c->h_pairs_free));
     const int32_t* indptr = reinterpret_cast<const int32_t*>(c->h_plan_last + c->off_indptr);
@@ -1183,7 +1293,7 @@ int32_t kriya_cuda_kv_slot_write(kriya_cuda_ctx* c, uint32_t layer, const void* 
                                       c->stream));
     KRIYA_CUDA_TRY(c, cudaEventRecord(c->h_pairs_free, c->stream));
     KRIYA_CUDA_TRY(c, kriya_launch_slot_write(c->layer_k(layer), c->layer_v(layer), stage_k, stage_v,
-                                              size_t(c->cfg.num_kv_heads) * c->cfg.head_dim * 2, c->cfg.block_size_tokens,
+                                              c->block_bytes / c->cfg.block_size_tokens, c->cfg.block_size_tokens,
                                               c->d_pairs, n, c->cfg.num_kv_blocks, c->d_status, c->stream));
     c->launches += 1;
     return KRIYA_CUDA_OK;

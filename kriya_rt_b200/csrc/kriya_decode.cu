@@ -68,7 +68,22 @@ struct DecodeLaunch {
     uint32_t page_bytes;  // one page of K (or V) for all heads
 };
 
-template <int D, int G, typename T>
+// Eight consecutive values of a Q4KvGroup32 row (DType::Q4KvGroup32, crates/kriya-core/src/tensor.rs:50-51,77,91: per 32
+// values 16 bytes of 4-bit codes + f16 scale + f16 min; value = fma(code, scale, min) as in the reference's
+// dequantize_q4_group64_to_f32, crates/kriya-core/src/quantizer.rs:112-127).  `row` is the (token, head) row of D / 32
+// blocks of 20 bytes, `dl` the index of the eight values inside the row.
+__device__ __forceinline__ void q4kv_load8(const uint8_t* row, uint32_t dl, float2 (&out)[4]) {
+    const uint8_t* blk = row + (dl >> 2) * 20u;
+    const uint32_t codes = *reinterpret_cast<const uint32_t*>(blk + (dl & 3u) * 4u);
+    const uint32_t hdr = *reinterpret_cast<const uint32_t*>(blk + 16u);
+    const float scale = __half2float(__ushort_as_half(uint16_t(hdr & 0xFFFFu)));
+    const float mn = __half2float(__ushort_as_half(uint16_t(hdr >> 16)));
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+        out[j] = make_float2(__fmaf_rn(float((codes >> (8 * j)) & 15u), scale, mn), __fmaf_rn(float((codes >> (8 * j + 4)) & 15u), scale, mn));
+}
+
+template <int D, int G, typename T, bool Q4>
 __global__ void __launch_bounds__(kDecodeThreadsMax, 1) decode_kernel(KriyaDecodeArgs a, DecodeLaunch L) {
     constexpr int LPT = D / 8;        // lanes per token
     constexpr int TPW = 32 / LPT;     // tokens per warp step
@@ -192,8 +207,15 @@ __global__ void __launch_bounds__(kDecodeThreadsMax, 1) decode_kernel(KriyaDecod
 #pragma unroll
             for (int st = 0; st < NSTEP; ++st) {
                 const uint32_t tok = uint32_t(st) * TPW + slot;
-                const uint4 raw = *reinterpret_cast<const uint4*>(Ks + ((size_t(tok) * HPC + hh) * D + dl * 8) * 2);
-                const float2 k0 = T::load2(raw.x), k1 = T::load2(raw.y), k2 = T::load2(raw.z), k3 = T::load2(raw.w);
+                float2 k0, k1, k2, k3;
+                if (Q4) {
+                    float2 kq[4];
+                    q4kv_load8(Ks + (size_t(tok) * HPC + hh) * (D / 32) * 20, dl, kq);
+                    k0 = kq[0]; k1 = kq[1]; k2 = kq[2]; k3 = kq[3];
+                } else {
+                    const uint4 raw = *reinterpret_cast<const uint4*>(Ks + ((size_t(tok) * HPC + hh) * D + dl * 8) * 2);
+                    k0 = T::load2(raw.x); k1 = T::load2(raw.y); k2 = T::load2(raw.z); k3 = T::load2(raw.w);
+                }
                 float part[GP];
 #pragma unroll
                 for (int g = 0; g < GP; ++g) {
@@ -242,9 +264,18 @@ __global__ void __launch_bounds__(kDecodeThreadsMax, 1) decode_kernel(KriyaDecod
 #pragma unroll
             for (int st = 0; st < NSTEP; ++st) {
                 const uint32_t tok = uint32_t(st) * TPW + slot;
-                uint4 raw = *reinterpret_cast<const uint4*>(Vs + ((size_t(tok) * HPC + hh) * D + dl * 8) * 2);
-                if (tok >= valid || tok < first) raw = make_uint4(0u, 0u, 0u, 0u);  // slots no token of the row's window occupies may hold anything
-                const float2 v0 = T::load2(raw.x), v1 = T::load2(raw.y), v2 = T::load2(raw.z), v3 = T::load2(raw.w);
+                float2 v0, v1, v2, v3;
+                if (Q4) {
+                    float2 vq[4];
+                    q4kv_load8(Vs + (size_t(tok) * HPC + hh) * (D / 32) * 20, dl, vq);
+                    v0 = vq[0]; v1 = vq[1]; v2 = vq[2]; v3 = vq[3];
+                } else {
+                    const uint4 raw = *reinterpret_cast<const uint4*>(Vs + ((size_t(tok) * HPC + hh) * D + dl * 8) * 2);
+                    v0 = T::load2(raw.x); v1 = T::load2(raw.y); v2 = T::load2(raw.z); v3 = T::load2(raw.w);
+                }
+                if (tok >= valid || tok < first) {  // slots no token of the row's window occupies may hold anything
+                    v0 = v1 = v2 = v3 = make_float2(0.0f, 0.0f);
+                }
                 const float* pg = p_s + (st * TPW + int(slot)) * GP;
 #pragma unroll
                 for (int g = 0; g < G; ++g) {
@@ -405,14 +436,14 @@ __global__ void merge_states_kernel(const float* __restrict__ m, const float* __
     }
 }
 
-template <int D, int G, typename T>
+template <int D, int G, typename T, bool Q4>
 cudaError_t launch_decode_t(const KriyaDecodeArgs& a, int max_smem_optin, cudaStream_t s) {
     constexpr int LPT = D / 8, TPW = 32 / LPT, GP = next_pow2(G);
     const int HPC = int(a.num_kv_heads);
     if (HPC < 1 || HPC > kMaxComputeWarps) return cudaErrorInvalidValue;
     DecodeLaunch L;
     L.rows = kMaxComputeWarps / HPC;
-    L.page_bytes = uint32_t(kPage) * HPC * D * 2u;
+    L.page_bytes = Q4 ? uint32_t(kPage) * HPC * (D / 32) * 20u : uint32_t(kPage) * HPC * D * 2u;
     L.stage_bytes = 2u * L.page_bytes;
     const int NWC = L.rows * HPC;
     const size_t extra = 2 * 64 * sizeof(uint64_t) + size_t(NWC) * (kPage * GP + GP) * sizeof(float) + 64;
@@ -428,24 +459,24 @@ cudaError_t launch_decode_t(const KriyaDecodeArgs& a, int max_smem_optin, cudaSt
     const size_t area = (std::max(ring_bytes, merge_bytes) + 15) & ~size_t(15);
     const size_t smem = area + 2 * size_t(nst) * sizeof(uint64_t) + size_t(NWC) * (kPage * GP + GP) * sizeof(float) + 16;
     if (smem > size_t(max_smem_optin)) return cudaErrorInvalidValue;
-    auto kern = decode_kernel<D, G, T>;
+    auto kern = decode_kernel<D, G, T, Q4>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
     if (e != cudaSuccess) return e;
     kern<<<a.n_work, (NWC + 1) * 32, smem, s>>>(a, L);
     return cudaGetLastError();
 }
 
-template <int D, typename T>
+template <int D, typename T, bool Q4>
 cudaError_t launch_decode_g(const KriyaDecodeArgs& a, uint32_t group, int max_smem_optin, cudaStream_t s) {
     switch (group) {
-        case 1: return launch_decode_t<D, 1, T>(a, max_smem_optin, s);
-        case 2: return launch_decode_t<D, 2, T>(a, max_smem_optin, s);
-        case 3: return launch_decode_t<D, 3, T>(a, max_smem_optin, s);
-        case 4: return launch_decode_t<D, 4, T>(a, max_smem_optin, s);
-        case 5: return launch_decode_t<D, 5, T>(a, max_smem_optin, s);
-        case 6: return launch_decode_t<D, 6, T>(a, max_smem_optin, s);
-        case 7: return launch_decode_t<D, 7, T>(a, max_smem_optin, s);
-        case 8: return launch_decode_t<D, 8, T>(a, max_smem_optin, s);
+        case 1: return launch_decode_t<D, 1, T, Q4>(a, max_smem_optin, s);
+        case 2: return launch_decode_t<D, 2, T, Q4>(a, max_smem_optin, s);
+        case 3: return launch_decode_t<D, 3, T, Q4>(a, max_smem_optin, s);
+        case 4: return launch_decode_t<D, 4, T, Q4>(a, max_smem_optin, s);
+        case 5: return launch_decode_t<D, 5, T, Q4>(a, max_smem_optin, s);
+        case 6: return launch_decode_t<D, 6, T, Q4>(a, max_smem_optin, s);
+        case 7: return launch_decode_t<D, 7, T, Q4>(a, max_smem_optin, s);
+        case 8: return launch_decode_t<D, 8, T, Q4>(a, max_smem_optin, s);
         default: return cudaErrorInvalidValue;
     }
 }
@@ -458,16 +489,23 @@ bool kriya_decode_supported(uint32_t head_dim, uint32_t group, uint32_t num_kv_h
 }
 
 cudaError_t kriya_launch_decode(const KriyaDecodeArgs& a, uint32_t head_dim, uint32_t block_size, uint32_t dtype,
-                                int max_smem_optin, cudaStream_t s) {
+                                int max_smem_optin, cudaStream_t s, uint32_t kv_q4) {
     if (a.n_work == 0) return cudaSuccess;
     const uint32_t group = a.num_kv_heads ? a.num_q_heads / a.num_kv_heads : 0;
     if (!kriya_decode_supported(head_dim, group, a.num_kv_heads, block_size)) return cudaErrorInvalidValue;
     using namespace kriya;
+    if (kv_q4) {  // the query / output type still follows `dtype`
+        if (head_dim == 128)
+            return dtype == KRIYA_DTYPE_FP16 ? launch_decode_g<128, Fp16, true>(a, group, max_smem_optin, s)
+                                             : launch_decode_g<128, Bf16, true>(a, group, max_smem_optin, s);
+        return dtype == KRIYA_DTYPE_FP16 ? launch_decode_g<64, Fp16, true>(a, group, max_smem_optin, s)
+                                         : launch_decode_g<64, Bf16, true>(a, group, max_smem_optin, s);
+    }
     if (head_dim == 128)
-        return dtype == KRIYA_DTYPE_FP16 ? launch_decode_g<128, Fp16>(a, group, max_smem_optin, s)
-                                         : launch_decode_g<128, Bf16>(a, group, max_smem_optin, s);
-    return dtype == KRIYA_DTYPE_FP16 ? launch_decode_g<64, Fp16>(a, group, max_smem_optin, s)
-                                     : launch_decode_g<64, Bf16>(a, group, max_smem_optin, s);
+        return dtype == KRIYA_DTYPE_FP16 ? launch_decode_g<128, Fp16, false>(a, group, max_smem_optin, s)
+                                         : launch_decode_g<128, Bf16, false>(a, group, max_smem_optin, s);
+    return dtype == KRIYA_DTYPE_FP16 ? launch_decode_g<64, Fp16, false>(a, group, max_smem_optin, s)
+                                     : launch_decode_g<64, Bf16, false>(a, group, max_smem_optin, s);
 }
 
 cudaError_t kriya_launch_merge_states(const float* m, const float* l, const float* o, uint32_t parts, uint32_t rows,

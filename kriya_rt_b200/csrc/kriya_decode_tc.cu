@@ -95,15 +95,23 @@ struct TcParams {
     uint32_t done_expect;  // its value once every earlier launch that used the set has finished with it
     uint32_t epoch;        // this launch's stamp, never zero
     KriyaFusedAppend f;
-#ifdef KRIYA_TC_TRACE
-    uint32_t trace_idx;
-#endif
 };
 
 // RoPE of eight (x[i], x[i + D/2]) pairs held as two 16-byte chunks, in the operation order of the append kernel
 // (fma(x0, c, -(x1 * s)), fma(x0, s, x1 * c), round to nearest even), so both paths write identical bits.  The
 // cos/sin pairs are fetched (or computed) separately: they depend on the position and the chunk only, so one fetch serves
 // every head of a run and its loads go out together with the loads of the vectors they rotate.
+// Long scalar routines are functions of their own: inlined into unrolled loops they are a large share of the kernel's
+// code, and code that runs once per CTA is paid for in instruction-cache misses.
+static __device__ __noinline__ float2 rope_pair_coeff(uint32_t i, uint32_t position, uint32_t rotary_dim, float theta) {
+    const float freq_exp = float(2u * i) / float(rotary_dim);
+    const float inv_freq = powf(theta, -freq_exp);
+    const float angle = __fmul_rn(float(position), inv_freq);
+    return make_float2(cosf(angle), sinf(angle));
+}
+static __device__ __noinline__ float softcap_log2(float x, float cap) {
+    return tanhf(fminf(fmaxf(x / cap, -15.0f), 15.0f)) * cap * kTcLog2e;
+}
 __device__ __forceinline__ void rope8_coeffs(float2 (&cs)[8], uint32_t first_pair, uint32_t position, const KriyaFusedAppend& f) {
     const uint32_t half_rot = f.rotary_dim / 2u;
     const bool use_table = f.has_table != 0u && position < f.max_seq_len && f.table != nullptr;
@@ -112,14 +120,10 @@ __device__ __forceinline__ void rope8_coeffs(float2 (&cs)[8], uint32_t first_pai
         const uint32_t i = first_pair + j;
         cs[j] = make_float2(1.0f, 0.0f);
         if (i < half_rot) {
-            if (use_table) {
+            if (use_table)
                 cs[j] = reinterpret_cast<const float2*>(f.table)[size_t(position) * half_rot + i];
-            } else {
-                const float freq_exp = float(2u * i) / float(f.rotary_dim);
-                const float inv_freq = powf(f.rope_theta, -freq_exp);
-                const float angle = __fmul_rn(float(position), inv_freq);
-                cs[j] = make_float2(cosf(angle), sinf(angle));
-            }
+            else
+                cs[j] = rope_pair_coeff(i, position, f.rotary_dim, f.rope_theta);
         }
     }
 }
@@ -145,17 +149,6 @@ __device__ __forceinline__ void rope8_apply(uint4& lo, uint4& hi, uint32_t first
     }
 }
 
-// Optional per-CTA timeline (compile with -DKRIYA_TC_TRACE): wall-clock stamps at a few points of the kernel for the last
-// kTrLaunches launches, read back through kriya_trace_read.
-#ifdef KRIYA_TC_TRACE
-constexpr int kTrLaunches = 128, kTrCtas = 304, kTrSlots = 24;
-__device__ unsigned long long g_trace[kTrLaunches * kTrCtas * kTrSlots];
-#define TRV(k, v) do { g_trace[(size_t(pp.trace_idx % kTrLaunches) * kTrCtas + blockIdx.x) * kTrSlots + (k)] = (v); } while (0)
-#define TR(k) TRV(k, global_timer_ns())
-#else
-#define TR(k) do { } while (0)
-#define TRV(k, v) do { } while (0)
-#endif
 // Programmatic dependent launch: both are no-ops when the launch did not ask for it.
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait_previous_grid() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
@@ -239,27 +232,42 @@ __device__ __forceinline__ bool gather_merge(const uint2* __restrict__ ll_o, con
         }
         if (has_ml) stage[t] = __uint_as_float(mlw.x);
         if (bar_or_128(!got)) return false;  // also orders the writes to `stage` before its readers
+        // the weights depend on (piece, head) only: thread h works them out for head h, the others just accumulate
+        float* wsm = stage + 64;       // [4][G] weights
+        float* hsm = stage + 64 + 32;  // [3][8]: new maximum, new sum, factor on what was there
+        if (t < uint32_t(G)) {
+            float mh = M[0], lh = L[0];
+#pragma unroll
+            for (int h = 1; h < G; ++h) {
+                mh = (t == uint32_t(h)) ? M[h] : mh;
+                lh = (t == uint32_t(h)) ? L[h] : lh;
+            }
+            float mc = mh;
+            for (uint32_t s2 = 0; s2 < cnt; ++s2) mc = fmaxf(mc, stage[(s2 * G + t) * 2]);
+            const float keep = (mh == -INFINITY) ? 0.0f : fast_exp2(mh - mc);
+            float lacc = lh * keep;
+            for (uint32_t s2 = 0; s2 < 4u; ++s2) {
+                float wgt = 0.0f;
+                if (s2 < cnt) {
+                    const float ms = stage[(s2 * G + t) * 2];
+                    wgt = (ms == -INFINITY) ? 0.0f : fast_exp2(ms - mc);
+                    lacc = fmaf(wgt, stage[(s2 * G + t) * 2 + 1], lacc);
+                }
+                wsm[s2 * G + t] = wgt;
+            }
+            hsm[t] = mc;
+            hsm[8 + t] = lacc;
+            hsm[16 + t] = keep;
+        }
+        named_bar_sync_128();
 #pragma unroll
         for (int h = 0; h < G; ++h) {
-            float mc = M[h];
+            float oacc = O[h] * hsm[16 + h];
 #pragma unroll
-            for (int s2 = 0; s2 < 4; ++s2)
-                if (uint32_t(s2) < cnt) mc = fmaxf(mc, stage[(s2 * G + h) * 2]);
-            if (mc == -INFINITY) continue;
-            const float keep = (M[h] == -INFINITY) ? 0.0f : exp2f(M[h] - mc);
-            float lacc = L[h] * keep, oacc = O[h] * keep;
-#pragma unroll
-            for (int s2 = 0; s2 < 4; ++s2) {
-                if (uint32_t(s2) < cnt) {
-                    const float ms = stage[(s2 * G + h) * 2];
-                    const float wgt = (ms == -INFINITY) ? 0.0f : exp2f(ms - mc);
-                    lacc = fmaf(wgt, stage[(s2 * G + h) * 2 + 1], lacc);
-                    oacc = fmaf(wgt, __uint_as_float(w[s2][h].x), oacc);
-                }
-            }
-            M[h] = mc;
-            L[h] = lacc;
+            for (int s2 = 0; s2 < 4; ++s2) oacc = fmaf(wsm[s2 * G + h], __uint_as_float(w[s2][h].x), oacc);
             O[h] = oacc;
+            M[h] = hsm[h];
+            L[h] = hsm[8 + h];
         }
         named_bar_sync_128();  // `stage` is rewritten by the next chunk
     }
@@ -299,18 +307,6 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
     const uint64_t wait_ns = a.wait_ns;
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     if (threadIdx.x == 0) {
-        TR(0);
-#ifdef KRIYA_TC_TRACE
-        uint32_t smid;
-        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
-        TRV(11, smid);
-        TRV(14, 0);
-        TRV(6, 0);
-        TRV(8, 0);
-        TRV(15, 0);
-        TRV(19, 0);
-        TRV(20, 0);
-#endif
     }
     const uint32_t seg_begin = pp.cta_seg_ptr[blockIdx.x], seg_end = pp.cta_seg_ptr[blockIdx.x + 1];
     // The next launch of the stream may start as SMs free up (it decides itself what it must wait for, see `pdl` below).
@@ -372,7 +368,6 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
     // the new token's K/V, outputs) waits; 2 = nothing to wait for; 0 = ordinary launch.
     const uint32_t pdl = pp.f.overlap_previous;
     if (pdl == 1u) pdl_wait_previous_grid();
-    if (tid == 0) TR(1);
 
     if (warp == 4) {
         // ---- producer: page indices one tile ahead, TMA loads into the ring -------------------------------
@@ -409,7 +404,6 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
                     atomicMax(a.status, uint32_t(KRIYA_DEV_BAD_BLOCK_INDEX));
                     blk = 0;
                 }
-                if (lane == 0 && g == 0) TR(2);
                 if (lane == 0) mbar_arrive_expect_tx(&kv_full[stage], npages * uint32_t(4 * kTcPage * 128));
                 __syncwarp();
                 if (lane < npages) {
@@ -537,19 +531,22 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
         }
     } else if (warp == 5) {
         // ---- MMA issuer ---------------------------------------------------------------------------------
-        const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV), q_addr = smem_u32(sQ), p_addr = smem_u32(sP);
+        // Every lane runs this code, descriptor arithmetic included; only the tensor-core instructions themselves are
+        // predicated on the elected lane, which keeps their operands in uniform registers (issued from inside a one-lane
+        // branch every instruction costs about a hundred cycles, and the issue rate then bounds the kernel).
+        const uint32_t el = (lane == 0) ? 1u : 0u;
+        const uint64_t k_desc = smem_desc_sw128(smem_u32(sK), 16, 1024), q_desc = smem_desc_sw128(smem_u32(sQ), 16, 1024);
+        const uint64_t v_desc = smem_desc_sw128(smem_u32(sV), kTcPanel, 1024), p_desc = smem_desc_sw128(smem_u32(sP), 16, 1024);
         // (segment, tile) cursor for the look-ahead S^T issue
         auto issue_s = [&](uint32_t gg, uint32_t qbuf) {
             const uint32_t stage = gg % kTcStages;
             const uint32_t d_tmem = tmem_base + ((gg & 1u) ? kColS1 : kColS0);
+            const uint64_t ad = k_desc + uint64_t((stage * kTcKvBytes) >> 4), bd = q_desc + uint64_t((qbuf * kTcQBytes) >> 4);
 #pragma unroll
-            for (int ks = 0; ks < kTcD / 16; ++ks) {
-                const uint32_t a_off = stage * kTcKvBytes + uint32_t(ks / 4) * kTcPanel + uint32_t(ks % 4) * 32u;
-                const uint32_t b_off = qbuf * kTcQBytes + uint32_t(ks / 4) * 2048u + uint32_t(ks % 4) * 32u;
-                umma_f16(d_tmem, smem_desc_sw128(k_addr + a_off, 16, 1024), smem_desc_sw128(q_addr + b_off, 16, 1024), IDESC_S,
-                         ks > 0 ? 1u : 0u);
-            }
-            umma_commit(&s_full[gg & 1u]);
+            for (int ks = 0; ks < kTcD / 16; ++ks)
+                umma_ss_pred(d_tmem, ad + uint64_t((uint32_t(ks / 4) * kTcPanel + uint32_t(ks % 4) * 32u) >> 4),
+                             bd + uint64_t((uint32_t(ks / 4) * 2048u + uint32_t(ks % 4) * 32u) >> 4), IDESC_S, ks > 0 ? 1u : 0u, el);
+            umma_commit_pred(&s_full[gg & 1u], el);
         };
         // flatten the piece into (tile -> q buffer, first-of-run) on the fly with two cursors
         uint32_t g = 0;
@@ -579,12 +576,10 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
                 la_first = false;
             }
             tc_fence_after();
-            if (lane == 0) issue_s(la_g, la_run % uint32_t(kTcQBufs));
-            __syncwarp();
+            issue_s(la_g, la_run % uint32_t(kTcQBufs));
             ++la_g;
             if (++la_t >= la_t1) {
-                if (lane == 0) umma_commit(&q_free[la_run % uint32_t(kTcQBufs)]);  // the run's last S^T is issued: its Q buffer frees when it completes
-                __syncwarp();
+                umma_commit_pred(&q_free[la_run % uint32_t(kTcQBufs)], el);  // the run's last S^T is issued: its Q buffer frees when it completes
                 ++la_si;
                 ++la_run;
                 la_valid = la_load();
@@ -592,7 +587,6 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
             return true;
         };
         ok = la_issue();  // S^T of the first tile
-        if (lane == 0) TR(3);
         for (uint32_t si = seg_begin; si < seg_end && ok; ++si) {
             const KriyaTcSeg seg = seg_at(si);
             if (seg.blk_hi <= seg.blk_lo) continue;
@@ -604,19 +598,17 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
                 ok = warp_wait_l(wait_ns, &p_ready[g & 1u], (g >> 1) & 1u);
                 if (!ok) break;
                 tc_fence_after();
-                if (lane == 0) {
+                {
                     const uint32_t stage = g % kTcStages;
+                    const uint64_t ad = v_desc + uint64_t((stage * kTcKvBytes) >> 4), bd = p_desc + uint64_t(((g & 1u) * kTcPBytes) >> 4);
+                    const uint32_t first = (t > t0) ? 1u : 0u;
 #pragma unroll
-                    for (int ks = 0; ks < kTcTile / 16; ++ks) {
-                        const uint32_t a_off = stage * kTcKvBytes + uint32_t(ks) * (kTcPage * 128);
-                        const uint32_t b_off = (g & 1u) * kTcPBytes + uint32_t(ks / 4) * 2048u + uint32_t(ks % 4) * 32u;
-                        umma_f16(tmem_base + kColO, smem_desc_sw128(v_addr + a_off, kTcPanel, 1024),
-                                 smem_desc_sw128(p_addr + b_off, 16, 1024), IDESC_O, (t > t0 || ks > 0) ? 1u : 0u);
-                    }
-                    umma_commit(&kv_empty[stage]);
-                    umma_commit(&pv_done[g & 1u]);
+                    for (int ks = 0; ks < kTcTile / 16; ++ks)
+                        umma_ss_pred(tmem_base + kColO, ad + uint64_t((uint32_t(ks) * (kTcPage * 128)) >> 4),
+                                     bd + uint64_t((uint32_t(ks / 4) * 2048u + uint32_t(ks % 4) * 32u) >> 4), IDESC_O, ks > 0 ? 1u : first, el);
+                    umma_commit_pred(&kv_empty[stage], el);
+                    umma_commit_pred(&pv_done[g & 1u], el);
                 }
-                __syncwarp();
             }
         }
         if (!ok && lane == 0) {
@@ -647,7 +639,6 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
         bool ok = true;
         bool set_known = false;  // the scratch-set guard has been consulted
         for (uint32_t si = seg_begin; si < seg_end && ok; ++si) {
-            if (tid == 0 && si == seg_begin + 1) TR(6);
             const KriyaTcSeg seg = seg_at(si);
             const uint32_t req = seg.req;
             const uint32_t row_tokens = seg.row_tokens;
@@ -665,7 +656,6 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
                 ok = warp_wait_l(wait_ns, &s_full[g & 1u], (g >> 1) & 1u);
                 if (!ok) break;
                 tc_fence_after();
-                if (tid == 0 && g == 0) TR(4);
                 uint32_t r[16];
                 tmem_ld16(tmem_base + lane_addr + ((g & 1u) ? kColS1 : kColS0), r);
                 tmem_wait_ld();
@@ -679,7 +669,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
 #pragma unroll
                 for (int h = 0; h < G; ++h) {
                     float x = __uint_as_float(r[h]) * scale2;
-                    if (softcap) x = tanhf(fminf(fmaxf(x / a.logit_softcap, -15.0f), 15.0f)) * a.logit_softcap * kTcLog2e;
+                    if (softcap) x = softcap_log2(x, a.logit_softcap);
                     s[h] = valid ? x : -INFINITY;
                     over = over || (s[h] > m_used[h] + kTcRescale);
                 }
@@ -761,12 +751,6 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
                 mbar_arrive(&p_ready[g & 1u]);
             }
             if (!ok) break;
-            if (tid == 0) { TR(13); TRV(12, g); }
-            if (tid == 0 && si == seg_begin) {
-                TR(5);
-                TRV(9, g);
-                TRV(10, seg_end - seg_begin);
-            }
             // ---- end of the run piece: total l per head, then O^T / l or the partial state ----------------
             float l_tot[G];
 #pragma unroll
@@ -783,7 +767,6 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
 #pragma unroll
             for (int h = 0; h < G; ++h) l_tot[h] = (red[h] + red[16 + h]) + (red[32 + h] + red[48 + h]);
             named_bar_sync_128();
-            if (tid == 0 && si == seg_begin) TR(16);
             uint32_t o[16];
 #pragma unroll
             for (int h = 0; h < 16; ++h) o[h] = 0u;
@@ -791,12 +774,10 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
                 ok = warp_wait_l(wait_ns, &pv_done[(g - 1u) & 1u], ((g - 1u) >> 1) & 1u);
                 if (!ok) break;
                 tc_fence_after();
-                if (tid == 0 && si == seg_begin) TR(17);
                 tmem_ld16(tmem_base + lane_addr + kColO, o);
                 tmem_wait_ld();
                 tc_fence_before();
             }
-            if (tid == 0 && si == seg_begin) TR(18);
             const uint32_t d = tid;  // output dimension owned by this thread
             const size_t row0 = size_t(req) * Hq + seg.kv_head * G;
             // A run cut into pieces: every piece but the last publishes its partial state; the last piece (which its CTA
@@ -814,10 +795,8 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
                     Oh[h] = __uint_as_float(o[h]);
                 }
                 if (split) {
-                    if (tid == 0) { TR(15); TRV(14, seg.n_parts); }
                     ok = gather_merge<G>(pp.ll_o, pp.ll_ml, seg, pp.epoch, wait_ns, red, tid, Mh, Lh, Oh);
                     if (!ok) break;
-                    if (tid == 0) TR(20);
                 }
 #pragma unroll
                 for (int h = 0; h < G; ++h) {
@@ -844,7 +823,6 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
                     if (!ok) break;
                     set_known = true;
                 }
-                if (tid == 0 && si == seg_begin) TR(19);
                 const size_t prow = size_t(seg.slot) * G;
 #pragma unroll
                 for (int h = 0; h < G; ++h) {
@@ -854,7 +832,6 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
                 }
             }
         }
-        if (tid == 0) TR(7);
         if (!ok && lane == 0) {
             atomicMax(a.status, uint32_t(KRIYA_DEV_WAIT_EXPIRED));
             *abort_flag = 1;
@@ -864,7 +841,6 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
     tc_fence_before();
     __syncthreads();
     if (tid == 0) {
-        TR(8);
         atomicAdd(pp.set_done, 1u);  // every read of the scratch set by this CTA is complete, and warp 6 has seen the guard
     }
     if (warp == 5) {
@@ -927,10 +903,6 @@ cudaError_t launch_tc_t(const TcParams& pp, const CUtensorMap& mk, const CUtenso
     const size_t smem = size_t(2 * kTcStages) * kTcKvBytes + kTcQBufs * kTcQBytes + 2 * kTcPBytes + 512 + 320 + 512 + 8 * sizeof(KriyaTcSeg) + 1024;
     if (smem > size_t(max_smem_optin)) return cudaErrorInvalidValue;
     auto kern = decode_tc_kernel<G, T>;
-#ifdef KRIYA_TC_TRACE
-    static uint32_t trace_launch = 0;
-    const_cast<TcParams&>(pp).trace_idx = trace_launch++;
-#endif
     {   // the attribute belongs to the device: set it once on every device this process launches the kernel on
         static std::atomic<uint64_t> attr_set{0};
         int dev = 0;
@@ -985,13 +957,6 @@ cudaError_t launch_tc_g(uint32_t group, const TcParams& pp, const CUtensorMap& m
 
 namespace ktc = kriya::KRIYA_TC_NS;
 
-#ifdef KRIYA_TC_TRACE
-// copies the timeline buffer [kTrLaunches][kTrCtas][kTrSlots] of this build to the host
-extern "C" int KRIYA_TC_FN(kriya_trace_read)(void* dst, size_t bytes) {
-    cudaDeviceSynchronize();
-    return int(cudaMemcpyFromSymbol(dst, ktc::g_trace, std::min(bytes, sizeof(ktc::g_trace))));
-}
-#endif
 
 uint32_t KRIYA_TC_FN(kriya_decode_tc_ctas_per_sm)() { return uint32_t(ktc::kTcCtasPerSm); }
 uint32_t KRIYA_TC_FN(kriya_decode_tc_pages_per_tile)() { return uint32_t(ktc::kTcPagesPerTile); }

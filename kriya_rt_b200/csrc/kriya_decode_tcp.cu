@@ -15,16 +15,21 @@
 //   S'[(h, p, t)][(p', j)] = sum over the 64 d of half p of  K[t][h][.] * Q[j][half p'][.]
 // is a useful partial score when p' = p and j belongs to KV head h; the score of (t, j) is the sum of the entries of rows
 // (h, 0, t) and (h, 1, t), which sit in lanes l and l + 16 of one warp: one shuffle.  The same rows are the K dimension
-// of the second MMA:  O'[d_lo][(p', j)] += sum over rows of V[row][d_lo] * P[(p', j)][row], where the probability
-// operand P holds p(t, j) at rows (h(j), p', t) and zeros elsewhere - the zero pattern never changes, every thread
-// rewrites only its own eight entries per tile.  O' has M = 64 (d_lo) and N = 32: O[j][64 p' + d_lo].
+// of the second product, taken plane by plane: the 16 rows of plane (h, p) of a page are one K = 16 step,
+//   O'[d_lo][columns (p, h, 0..7)] += V_plane^T [64 d_lo x 16 t] . P_plane [16 t x 8 heads of h]      (M = 64, N = 8)
+// so the probability operand of a page is a plain [8 heads][64 page rows] K-major tile that every softmax thread fills
+// at its own row, and O'[d_lo][(p, h, jj)] = O[8 h + jj][64 p + d_lo].
 //
-// Roles (256 threads, one CTA per SM, persistent over a list of run pieces exactly as in kriya_decode_tc.cu):
-//   warps 0-3 softmax (warp w: page w / 2 of the tile, KV head w % 2; lane: half = lane / 16, token = lane % 16),
-//   warp 4 producer (page indices, tensor copies into a 6-deep ring of 32 KB tiles: 2 pages of K, 2 pages of V),
-//   warp 5 MMA issuer, warp 6 scratch-set guard, warp 7 stager (queries, rotated in flight; the new token's K/V row).
+// Roles (384 threads, one CTA per SM, persistent over a list of run pieces exactly as in kriya_decode_tc.cu); a tile is
+// four pages: 64 tokens of both heads, 32 KB of K and 32 KB of V, 256 operand rows:
+//   warps 0-7 softmax: warp w owns operand rows 32 w .. 32 w + 31 of the tile = (page w / 2, KV head w % 2; lane: half =
+//     lane / 16, token = lane % 16); warps 0-3 read the first score MMA's accumulator, warps 4-7 the second's,
+//   warp 8 producer (page indices, one tensor copy per page of K and of V into a 3-deep ring of 64 KB tiles),
+//   warp 9 MMA issuer, warp 10 scratch-set guard, warp 11 stager (queries, rotated in flight; the new token's K/V row).
 // Split runs, the finishing piece, stamps and the set guard work as described in kriya_decode_tc.cu; a run here is a
-// whole plan row (both KV heads).  Every wait is bounded.
+// whole plan row (both KV heads).  At the end of a piece the accumulator goes through shared memory so that threads
+// 0-127 finish the query heads of KV head 0 and threads 128-255 those of KV head 1, one output dimension each.  Every
+// wait is bounded.
 #include <algorithm>
 #include <atomic>
 #include <cstdio>
@@ -38,22 +43,22 @@ namespace tcp {
 constexpr int kD = 128;
 constexpr int kPage = 16;
 constexpr int kHkv = 2;
-constexpr int kHqMax = 16;                       // query heads of a row: up to 8 per KV head
-constexpr int kPagesPerTile = 2;                 // 2 pages x 64 rows = 128 operand rows
+constexpr int kPagesPerTile = 4;                 // 4 pages x 64 operand rows = two M = 128 score MMAs
 constexpr int kTileTokens = kPagesPerTile * kPage;
 constexpr uint32_t kPageBytes = 8192;            // one page of K (or V), both heads
-constexpr uint32_t kTileKBytes = kPagesPerTile * kPageBytes;  // 16 KB
+constexpr uint32_t kTileKBytes = kPagesPerTile * kPageBytes;  // 32 KB
 constexpr uint32_t kStageBytes = 2 * kTileKBytes;             // K tile + V tile
-constexpr int kStages = 6;
+constexpr int kStages = 3;
 constexpr int kQBufs = 3;
 constexpr uint32_t kQBytes = 32 * 128;           // 32 operand rows (half', head) x 128 B
-constexpr uint32_t kPBytes = 2 * 32 * 128;       // two 64-row K blocks x 32 operand rows x 128 B
-constexpr int kThreads = 256;
-constexpr int kN = 32;
-constexpr uint32_t kTmemCols = 128;
-constexpr uint32_t kColS0 = 0, kColS1 = 32, kColO = 64;
+constexpr uint32_t kPBytes = (kPagesPerTile / 2) * 8 * 128;  // per pair of pages 8 operand rows (query heads of a KV head) x 128 B
+constexpr int kSoftmaxThreads = 256;
+constexpr int kThreads = 384;  // warps 0-7 softmax, 8 producer, 9 MMA issuer, 10 scratch-set guard, 11 stager
+constexpr uint32_t kTmemCols = 256;
+constexpr uint32_t kColS0 = 0, kColS1 = 64, kColO = 128;  // score tiles: 2 halves x 32 columns each; accumulator 32 columns
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescale = 8.0f;
+
 
 struct Params {
     KriyaDecodeArgs a;
@@ -72,19 +77,24 @@ struct Params {
 
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait_previous_grid() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-__device__ __forceinline__ void named_bar_sync_128() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
-__device__ __forceinline__ bool bar_or_128(bool pred) {
+// Named barriers: id 1 joins the 256 softmax threads; ids 2 and 3 join the 128 threads that finish KV head 0 / 1.
+__device__ __forceinline__ void bar_sync(uint32_t id, uint32_t nthreads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+__device__ __forceinline__ bool bar_or(uint32_t id, uint32_t nthreads, bool pred) {
     uint32_t res;
     asm volatile(
         "{\n\t.reg .pred p, q;\n\t"
-        "setp.ne.u32 q, %1, 0;\n\t"
-        "bar.red.or.pred p, 1, 128, q;\n\t"
+        "setp.ne.u32 q, %3, 0;\n\t"
+        "bar.red.or.pred p, %1, %2, q;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(res)
-        : "r"(uint32_t(pred))
+        : "r"(id), "r"(nthreads), "r"(uint32_t(pred))
         : "memory");
     return res != 0;
 }
+__device__ __forceinline__ void softmax_sync() { bar_sync(1u, kSoftmaxThreads); }
+__device__ __forceinline__ bool softmax_or(bool pred) { return bar_or(1u, kSoftmaxThreads, pred); }
 __device__ __forceinline__ void ll_store(uint2* p, float v, uint32_t epoch) {
     asm volatile("st.global.cg.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(v)), "r"(epoch) : "memory");
 }
@@ -93,13 +103,21 @@ __device__ __forceinline__ uint2 ll_load(const uint2* p) {
     asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(r.x), "=r"(r.y) : "l"(p) : "memory");
     return r;
 }
+// The same word by an ordinary load that bypasses L1.  Many of these may be in flight at once, which the ordered loads
+// above are not; a loop that polls with them must put a fence between two rounds, or the second round may be served from
+// the first round's registers.
+__device__ __forceinline__ uint2 ll_load_weak(const uint2* p) {
+    uint2 r;
+    asm volatile("ld.global.cg.v2.u32 {%0, %1}, [%2];" : "=r"(r.x), "=r"(r.y) : "l"(p));
+    return r;
+}
 __device__ __forceinline__ uint32_t ld_volatile_u32(const uint32_t* p) {
     uint32_t r;
     asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(r) : "l"(p) : "memory");
     return r;
 }
 __device__ __forceinline__ bool warp_wait_l(uint64_t limit_ns, uint64_t* bar, uint32_t parity) { return warp_wait(bar, parity, limit_ns); }
-__device__ __forceinline__ bool wait_set_free(const uint32_t* set_done, uint32_t done_expect, uint64_t wait_ns) {
+static __device__ __noinline__ bool wait_set_free(const uint32_t* set_done, uint32_t done_expect, uint64_t wait_ns) {
     const uint64_t t_start = global_timer_ns();
     for (uint32_t spin = 0;; ++spin) {
         if (int32_t(ld_volatile_u32(set_done) - done_expect) >= 0) return true;
@@ -124,6 +142,17 @@ __device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
 
 // RoPE of eight (x[i], x[i + 64]) pairs held as two 16-byte chunks, in the operation order of the append kernel
 // (fma(x0, c, -(x1 * s)), fma(x0, s, x1 * c), round to nearest even), so both paths write identical bits.
+// Soft-capped score in the exponent's base: a function of its own (tanhf is long and the call sits in an unrolled loop).
+static __device__ __noinline__ float softcap_log2(float x, float cap) {
+    return tanhf(fminf(fmaxf(x / cap, -15.0f), 15.0f)) * cap * kLog2e;
+}
+// (cos, sin) of one pair without the table: a function of its own, the inlined powf / cosf / sinf are kilobytes of code.
+static __device__ __noinline__ float2 rope_pair_coeff(uint32_t i, uint32_t position, uint32_t rotary_dim, float theta) {
+    const float freq_exp = float(2u * i) / float(rotary_dim);
+    const float inv_freq = powf(theta, -freq_exp);
+    const float angle = __fmul_rn(float(position), inv_freq);
+    return make_float2(cosf(angle), sinf(angle));
+}
 __device__ __forceinline__ void rope8_coeffs(float2 (&cs)[8], uint32_t first_pair, uint32_t position, const KriyaFusedAppend& f) {
     const uint32_t half_rot = f.rotary_dim / 2u;
     const bool use_table = f.has_table != 0u && position < f.max_seq_len && f.table != nullptr;
@@ -132,14 +161,10 @@ __device__ __forceinline__ void rope8_coeffs(float2 (&cs)[8], uint32_t first_pai
         const uint32_t i = first_pair + j;
         cs[j] = make_float2(1.0f, 0.0f);
         if (i < half_rot) {
-            if (use_table) {
+            if (use_table)
                 cs[j] = reinterpret_cast<const float2*>(f.table)[size_t(position) * half_rot + i];
-            } else {
-                const float freq_exp = float(2u * i) / float(f.rotary_dim);
-                const float inv_freq = powf(f.rope_theta, -freq_exp);
-                const float angle = __fmul_rn(float(position), inv_freq);
-                cs[j] = make_float2(cosf(angle), sinf(angle));
-            }
+            else
+                cs[j] = rope_pair_coeff(i, position, f.rotary_dim, f.rope_theta);
         }
     }
 }
@@ -165,60 +190,84 @@ __device__ __forceinline__ void rope8_apply(uint4& lo, uint4& hi, uint32_t first
     }
 }
 
-// The run's last piece gathers the other pieces' states (two at a time) and finishes the run.  Thread t owns output
-// dimension t of all HQ query heads.
-template <int HQ>
+// The run's last piece gathers the other pieces' states and finishes the run.  Called by the 128 threads that finish one
+// KV head (barrier `bar_id`, staging area `stage` of their own): thread t owns output dimension t of the head's G query
+// heads, which are heads head0 .. head0 + G - 1 of the row's HQ.  Other pieces are taken four at a time; every load of a
+// chunk is issued before any is examined and repeated until it carries this launch's stamp (bounded).
+template <int G>
 __device__ __forceinline__ bool gather_merge(const uint2* __restrict__ ll_o, const uint2* __restrict__ ll_ml, const KriyaTcSeg& seg,
-                                             uint32_t epoch, uint64_t wait_ns, float* stage, uint32_t t, float (&M)[HQ], float (&L)[HQ], float (&O)[HQ]) {
+                                             uint32_t epoch, uint64_t wait_ns, float* stage, uint32_t bar_id, uint32_t t, uint32_t HQ,
+                                             uint32_t head0, float (&M)[G], float (&L)[G], float (&O)[G]) {
     const uint32_t others = seg.n_parts - 1u;
-    for (uint32_t c0 = 0; c0 < others; c0 += 2u) {
-        const uint32_t cnt = min(2u, others - c0);
+    for (uint32_t c0 = 0; c0 < others; c0 += 4u) {
+        const uint32_t cnt = min(4u, others - c0);
         const size_t slot0 = size_t(seg.first_slot) + c0;
-        uint2 w[2][HQ];
+        uint2 w[4][G];
         uint2 mlw = make_uint2(0u, epoch);
-        const bool has_ml = t < cnt * uint32_t(HQ) * 2u;  // (m, l) words of the chunk: [part][head][2], one per thread
-        const uint2* mlp = &ll_ml[slot0 * HQ * 2 + (has_ml ? t : 0u)];
+        // (m, l) words of the chunk, one per thread: t = (part * G + head) * 2 + which
+        const bool has_ml = t < cnt * uint32_t(G) * 2u;
+        const uint32_t ml_part = has_ml ? t / (2u * G) : 0u, ml_rest = has_ml ? t % (2u * G) : 0u;
+        const uint2* mlp = &ll_ml[((slot0 + ml_part) * HQ + head0) * 2 + ml_rest];
         bool got = false;
         const uint64_t t_start = global_timer_ns();
         for (uint32_t spin = 0; !got; ++spin) {
 #pragma unroll
-            for (int s2 = 0; s2 < 2; ++s2)
+            for (int s2 = 0; s2 < 4; ++s2)
 #pragma unroll
-                for (int h = 0; h < HQ; ++h) w[s2][h] = ll_load(&ll_o[((slot0 + min(uint32_t(s2), cnt - 1u)) * HQ + h) * kD + t]);
-            mlw = ll_load(mlp);
+                for (int h = 0; h < G; ++h)
+                    w[s2][h] = ll_load_weak(&ll_o[((slot0 + min(uint32_t(s2), cnt - 1u)) * HQ + head0 + h) * kD + t]);
+            mlw = ll_load_weak(mlp);
             uint32_t bad = mlw.y ^ epoch;
 #pragma unroll
-            for (int s2 = 0; s2 < 2; ++s2)
+            for (int s2 = 0; s2 < 4; ++s2)
 #pragma unroll
-                for (int h = 0; h < HQ; ++h) bad |= w[s2][h].y ^ epoch;
+                for (int h = 0; h < G; ++h) bad |= w[s2][h].y ^ epoch;
             got = bad == 0u;
-            if (!got && (spin & 63u) == 63u && global_timer_ns() - t_start > wait_ns) break;
+            if (!got) {
+                __threadfence();  // the next round reads memory again
+                if ((spin & 63u) == 63u && global_timer_ns() - t_start > wait_ns) break;
+            }
         }
         if (has_ml) stage[t] = __uint_as_float(mlw.x);
-        if (bar_or_128(!got)) return false;
+        if (bar_or(bar_id, 128u, !got)) return false;
+        // the weights depend on (piece, head) only: thread h works them out for head h, the others just accumulate
+        float* wsm = stage + 64;            // [4][G] weights
+        float* hsm = stage + 64 + 32;       // [3][8]: new maximum, new sum, factor on what was there
+        if (t < uint32_t(G)) {
+            float mh = M[0], lh = L[0];
 #pragma unroll
-        for (int h = 0; h < HQ; ++h) {
-            float mc = M[h];
-#pragma unroll
-            for (int s2 = 0; s2 < 2; ++s2)
-                if (uint32_t(s2) < cnt) mc = fmaxf(mc, stage[(s2 * HQ + h) * 2]);
-            if (mc == -INFINITY) continue;
-            const float keep = (M[h] == -INFINITY) ? 0.0f : exp2f(M[h] - mc);
-            float lacc = L[h] * keep, oacc = O[h] * keep;
-#pragma unroll
-            for (int s2 = 0; s2 < 2; ++s2) {
-                if (uint32_t(s2) < cnt) {
-                    const float ms = stage[(s2 * HQ + h) * 2];
-                    const float wgt = (ms == -INFINITY) ? 0.0f : exp2f(ms - mc);
-                    lacc = fmaf(wgt, stage[(s2 * HQ + h) * 2 + 1], lacc);
-                    oacc = fmaf(wgt, __uint_as_float(w[s2][h].x), oacc);
-                }
+            for (int h = 1; h < G; ++h) {
+                mh = (t == uint32_t(h)) ? M[h] : mh;
+                lh = (t == uint32_t(h)) ? L[h] : lh;
             }
-            M[h] = mc;
-            L[h] = lacc;
-            O[h] = oacc;
+            float mc = mh;
+            for (uint32_t s2 = 0; s2 < cnt; ++s2) mc = fmaxf(mc, stage[(s2 * G + t) * 2]);
+            const float keep = (mh == -INFINITY) ? 0.0f : fast_exp2(mh - mc);
+            float lacc = lh * keep;
+            for (uint32_t s2 = 0; s2 < 4u; ++s2) {
+                float wgt = 0.0f;
+                if (s2 < cnt) {
+                    const float ms = stage[(s2 * G + t) * 2];
+                    wgt = (ms == -INFINITY) ? 0.0f : fast_exp2(ms - mc);
+                    lacc = fmaf(wgt, stage[(s2 * G + t) * 2 + 1], lacc);
+                }
+                wsm[s2 * G + t] = wgt;
+            }
+            hsm[t] = mc;
+            hsm[8 + t] = lacc;
+            hsm[16 + t] = keep;
         }
-        named_bar_sync_128();
+        bar_sync(bar_id, 128u);
+#pragma unroll
+        for (int h = 0; h < G; ++h) {
+            float oacc = O[h] * hsm[16 + h];
+#pragma unroll
+            for (int s2 = 0; s2 < 4; ++s2) oacc = fmaf(wsm[s2 * G + h], __uint_as_float(w[s2][h].x), oacc);
+            O[h] = oacc;
+            M[h] = hsm[h];
+            L[h] = hsm[8 + h];
+        }
+        bar_sync(bar_id, 128u);
     }
     return true;
 }
@@ -229,36 +278,49 @@ __global__ void __launch_bounds__(kThreads, 1)
 decode_tcp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, Params pp) {
     constexpr int HQ = kHkv * G;
     constexpr uint32_t FMT = (T::kDtype == KRIYA_DTYPE_BF16) ? 1u : 0u;
-    constexpr uint32_t IDESC_S = make_idesc(FMT, 128, kN, 0, 0);  // A = K tile rows (K-major), B = Q rows (K-major)
-    constexpr uint32_t IDESC_O = make_idesc(FMT, 64, kN, 1, 0);   // A = V tile (MN-major: M = d_lo), B = P (K-major)
+    constexpr uint32_t IDESC_S = make_idesc(FMT, 128, 32, 0, 0);  // A = 128 K rows (K-major), B = 32 query rows (K-major)
+    // A = a page's two V planes of one head (MN-major: M = d), B = 16 x 16: rows 0-7 the probabilities of the head's query heads;
+    // M = 128 allows no N below 16, so rows 8-15 are whatever follows in shared memory and their 8 result columns are never read
+    constexpr uint32_t IDESC_O = make_idesc(FMT, 128, 16, 1, 0);
 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* sm = smem_raw + (base - smem_u32(smem_raw));
-    uint8_t* sKV = sm;                                  // [stages][K tile 16 KB | V tile 16 KB]
+    uint8_t* sKV = sm;                                  // [stages][K tile 32 KB | V tile 32 KB]
     uint8_t* sQ = sKV + kStages * kStageBytes;          // [3][4 KB]
-    uint8_t* sP = sQ + kQBufs * kQBytes;                // [2][8 KB]; at the end of a piece also the [HQ][128] fp32 output staging
-    float* red = reinterpret_cast<float*>(sP + 2 * kPBytes);  // [4 warps][8] maxima / sums, merge staging [2][HQ][2]
-    float* alpha_s = red + 128;                         // [16] rescale factors per query head
+    uint8_t* sP = sQ + kQBufs * kQBytes;                // [2][2 KB]
+    float* red = reinterpret_cast<float*>(sP + 2 * kPBytes);  // [8 warps][8] maxima / sums; [64 ..): merge staging of the two KV heads
+    float* alpha_s = red + 512;                         // [16] rescale factors per query head
     float* ml_s = alpha_s + 16;                         // [16][2] (m, l) of the piece per query head
     uint64_t* bars = reinterpret_cast<uint64_t*>(ml_s + 32);
-    uint64_t* kv_full = bars;                     // [stages]
+    uint64_t* kv_full = bars;                     // [stages]: the K half of a stage has landed
     uint64_t* kv_empty = bars + kStages;          // [stages]
     uint64_t* s_full = bars + 2 * kStages;        // [2]
-    uint64_t* p_ready = bars + 2 * kStages + 2;   // [2], 128 arrivals
+    uint64_t* p_ready = bars + 2 * kStages + 2;   // [2], 256 arrivals
     uint64_t* pv_done = bars + 2 * kStages + 4;   // [2]
     uint64_t* q_ready = bars + 2 * kStages + 6;   // [3]
     uint64_t* q_free = bars + 2 * kStages + 9;    // [3]
     uint64_t* kv_ready = bars + 2 * kStages + 12; // [3]
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 15);
+    uint64_t* v_full = bars + 2 * kStages + 15;   // [stages]: the V half
+    uint64_t* aux_full = bars + 3 * kStages + 15; // [0]: the segment records below have landed; [1]: the first piece's raw query rows;
+                                                  // [2]: the other pieces' states (gather_merge_smem); [3] unused
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * kStages + 19);
     volatile uint32_t* abort_flag = tmem_slot + 1;
     volatile uint32_t* set_free_s = tmem_slot + 2;
     KriyaTcSeg* segs_s = reinterpret_cast<KriyaTcSeg*>(tmem_slot + 4);  // first 8 segment records of this CTA
+    uint8_t* sQraw = reinterpret_cast<uint8_t*>(segs_s + 8);            // [HQ][256 B]: the first piece's query rows as they are in memory
+    float2* sCs = reinterpret_cast<float2*>(sQraw + 16 * 256);          // [64]: the rotation table's row of its position
 
     const KriyaDecodeArgs& a = pp.a;
     const uint64_t wait_ns = a.wait_ns;
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
-    const uint32_t seg_begin = pp.cta_seg_ptr[blockIdx.x], seg_end = pp.cta_seg_ptr[blockIdx.x + 1];
+    // this CTA's record: first segment, pages of the first tile that may be fetched at once, their place, their blocks
+    // and the row and the position of the first piece
+    const uint4* hdr = reinterpret_cast<const uint4*>(pp.cta_seg_ptr) + size_t(blockIdx.x) * 3u;
+    const uint4 hdr0 = hdr[0], hdr1 = hdr[1];
+    const uint32_t hdr_position = reinterpret_cast<const uint32_t*>(hdr + 2)[0];
+    const uint32_t seg_begin = hdr0.x;
+    uint32_t seg_end = reinterpret_cast<const uint32_t*>(hdr + 3)[0];
     if (threadIdx.x == 0) pdl_launch_dependents();
     if (seg_begin == seg_end) {
         if (threadIdx.x == 0) {
@@ -267,15 +329,64 @@ decode_tcp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
         }
         return;
     }
-    if (tid == 0) {
-        for (int s = 0; s < kStages; ++s) {
-            mbar_init(&kv_full[s], 1);
-            mbar_init(&kv_empty[s], 1);
+    const uint32_t pdl = pp.f.overlap_previous;  // see kriya_decode_tc.cu
+    // What the CTA needs first is asked for before it is set up, by copies that complete on barriers of their own (a load
+    // into registers would hold up the CTA-wide barrier below until it has returned): the segment records, the K/V pages
+    // of the first tile, the query rows of the first piece and the rotation table's row of its position.  The K/V pages
+    // not when this launch has to wait for the whole of the previous one (it may still be writing the cache); the query
+    // rows not when the previous launch writes them.
+    const uint32_t early_pages = (pdl == 1u) ? 0u : min(hdr0.y, uint32_t(kPagesPerTile));
+    const bool stager_fused = pp.f.k_in != nullptr;
+    const uint32_t half_rot0 = pp.f.rotary_dim / 2u;
+    bool first_q = hdr0.w != UINT32_MAX;  // the CTA has a piece to work on
+    const bool q_bulk = first_q && (reinterpret_cast<uintptr_t>(a.q) & 15u) == 0u;
+    const bool cs_bulk = q_bulk && stager_fused && pp.f.has_table != 0u && hdr_position < pp.f.max_seq_len && pp.f.table != nullptr &&
+                         (half_rot0 & 1u) == 0u && half_rot0 <= 64u;
+    auto issue_q0 = [&]() {  // one thread
+        const uint32_t q_bytes = uint32_t(HQ) * kD * 2u;
+        mbar_arrive_expect_tx(&aux_full[1], q_bytes + (cs_bulk ? half_rot0 * 8u : 0u));
+        bulk_g2s(sQraw, reinterpret_cast<const uint16_t*>(a.q) + size_t(hdr0.w) * a.num_q_heads * kD, q_bytes, &aux_full[1]);
+        if (cs_bulk) bulk_g2s(sCs, reinterpret_cast<const float2*>(pp.f.table) + size_t(hdr_position) * half_rot0, half_rot0 * 8u, &aux_full[1]);
+    };
+    if (warp == 8) {
+        if (lane == 0) {
+            for (int s = 0; s < kStages; ++s) {
+                mbar_init(&kv_full[s], 1);
+                mbar_init(&v_full[s], 1);
+                mbar_init(&kv_empty[s], 1);
+            }
+            mbar_init(&aux_full[0], 1);
+            mbar_init(&aux_full[1], 1);
+            mbar_init(&aux_full[2], 1);
+            mbar_fence_init();
+            const uint32_t seg_bytes = min(seg_end - seg_begin, 8u) * uint32_t(sizeof(KriyaTcSeg));
+            mbar_arrive_expect_tx(&aux_full[0], seg_bytes);
+            bulk_g2s(segs_s, pp.segs + seg_begin, seg_bytes, &aux_full[0]);
+            // the few KB of query rows go ahead of the tile: the copy engine takes its requests in order
+            if (q_bulk && (pdl == 0u || pdl == 2u)) issue_q0();
+            if (early_pages) {
+                mbar_arrive_expect_tx(&kv_full[0], early_pages * kPageBytes);
+                mbar_arrive_expect_tx(&v_full[0], early_pages * kPageBytes);
+            }
         }
+        __syncwarp();
+        if (lane < early_pages) {
+            uint32_t blk = lane == 0 ? hdr1.x : lane == 1 ? hdr1.y : lane == 2 ? hdr1.z : hdr1.w;
+            if (blk >= a.num_blocks) {
+                atomicMax(a.status, uint32_t(KRIYA_DEV_BAD_BLOCK_INDEX));
+                blk = 0;
+            }
+            uint8_t* dst = sKV + (hdr0.z + lane) * kPageBytes;
+            const int32_t page = int32_t(pp.page0 + blk);
+            tma_load_page(dst, &map_k, page, &kv_full[0]);
+            tma_load_page(dst + kTileKBytes, &map_v, page, &v_full[0]);
+        }
+    }
+    if (tid == 0) {
         mbar_init(&s_full[0], 1);
         mbar_init(&s_full[1], 1);
-        mbar_init(&p_ready[0], 128);
-        mbar_init(&p_ready[1], 128);
+        mbar_init(&p_ready[0], kSoftmaxThreads);
+        mbar_init(&p_ready[1], kSoftmaxThreads);
         mbar_init(&pv_done[0], 1);
         mbar_init(&pv_done[1], 1);
         for (int b = 0; b < 3; ++b) {
@@ -287,29 +398,32 @@ decode_tcp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
         *set_free_s = 0;
         mbar_fence_init();
     }
-    if (warp == 5) {
+    if (warp == 9) {
         tmem_alloc(tmem_slot, kTmemCols);
         tmem_relinquish();
     }
-    {
-        const uint32_t nstage = min(seg_end - seg_begin, 8u) * uint32_t(sizeof(KriyaTcSeg) / 4);
-        const uint32_t* src = reinterpret_cast<const uint32_t*>(pp.segs + seg_begin);
-        for (uint32_t i = tid; i < nstage; i += kThreads) reinterpret_cast<uint32_t*>(segs_s)[i] = src[i];
-    }
     auto seg_at = [&](uint32_t si) -> KriyaTcSeg { return (si - seg_begin < 8u) ? segs_s[si - seg_begin] : pp.segs[si]; };
-    // Query rows of heads that do not exist (G < 8) and every probability entry outside a thread's own eight stay zero.
+    // Query rows of heads that do not exist (G < 8) stay zero (their scores and probabilities feed unused columns only).
     for (uint32_t i = tid; i < (kQBufs * kQBytes + 2 * kPBytes) / 16; i += kThreads)
         reinterpret_cast<uint4*>(sQ)[i] = make_uint4(0u, 0u, 0u, 0u);
     fence_async_smem();
     tc_fence_before();
-    __syncthreads();
+    __syncthreads();  // every barrier is set up
+    const bool segs_landed = mbar_wait(&aux_full[0], 0u, wait_ns);
+    if (__syncthreads_or(!segs_landed)) {  // nobody works on records that never came
+        if (tid == 0) atomicMax(a.status, uint32_t(KRIYA_DEV_WAIT_EXPIRED));
+        seg_end = seg_begin;
+        first_q = false;
+    }
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t Hq = a.num_q_heads;
-    const uint32_t pdl = pp.f.overlap_previous;  // see kriya_decode_tc.cu
-    if (pdl == 1u) pdl_wait_previous_grid();
+    if (pdl == 1u) {
+        pdl_wait_previous_grid();
+        if (warp == 8 && lane == 0 && q_bulk && first_q) issue_q0();
+    }
 
-    if (warp == 4) {
+    if (warp == 8) {
         // ---- producer ------------------------------------------------------------------------------------
         uint32_t g = 0, runs = 0;
         bool ok = true;
@@ -328,24 +442,29 @@ decode_tcp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                 const uint32_t p_lo = max(t * kPagesPerTile, seg.blk_lo), p_hi = min((t + 1) * kPagesPerTile, seg.blk_hi);
                 const uint32_t npages = p_hi - p_lo;
                 const uint32_t my_page = p_lo + lane;
-                int32_t blk = pf_blk;
-                if (!pf_valid && lane < npages) blk = table[my_page];
-                if (g >= kStages && !warp_wait_l(wait_ns, &kv_empty[stage], ((g / kStages) - 1u) & 1u)) { ok = false; break; }
-                if (owns_last && t + 1u == t1 && !warp_wait_l(wait_ns, &kv_ready[runs % uint32_t(kQBufs)], (runs / uint32_t(kQBufs)) & 1u)) {
-                    ok = false;
-                    break;
-                }
-                if (lane < npages && uint32_t(blk) >= a.num_blocks) {
-                    atomicMax(a.status, uint32_t(KRIYA_DEV_BAD_BLOCK_INDEX));
-                    blk = 0;
-                }
-                if (lane == 0) mbar_arrive_expect_tx(&kv_full[stage], npages * 2u * kPageBytes);
-                __syncwarp();
-                if (lane < npages) {
-                    uint8_t* dst = sKV + stage * kStageBytes + (my_page - t * kPagesPerTile) * kPageBytes;
-                    const int32_t page = int32_t(pp.page0) + blk;
-                    tma_load_page(dst, &map_k, page, &kv_full[stage]);
-                    tma_load_page(dst + kTileKBytes, &map_v, page, &kv_full[stage]);
+                if (g > 0u || early_pages == 0u) {  // the CTA's first tile may be on its way already
+                    int32_t blk = pf_blk;
+                    if (!pf_valid && lane < npages) blk = table[my_page];
+                    if (g >= kStages && !warp_wait_l(wait_ns, &kv_empty[stage], ((g / kStages) - 1u) & 1u)) { ok = false; break; }
+                    if (owns_last && t + 1u == t1 && !warp_wait_l(wait_ns, &kv_ready[runs % uint32_t(kQBufs)], (runs / uint32_t(kQBufs)) & 1u)) {
+                        ok = false;
+                        break;
+                    }
+                    if (lane < npages && uint32_t(blk) >= a.num_blocks) {
+                        atomicMax(a.status, uint32_t(KRIYA_DEV_BAD_BLOCK_INDEX));
+                        blk = 0;
+                    }
+                    if (lane == 0) {
+                        mbar_arrive_expect_tx(&kv_full[stage], npages * kPageBytes);
+                        mbar_arrive_expect_tx(&v_full[stage], npages * kPageBytes);
+                    }
+                    __syncwarp();
+                    if (lane < npages) {
+                        uint8_t* dst = sKV + stage * kStageBytes + (my_page - t * kPagesPerTile) * kPageBytes;
+                        const int32_t page = int32_t(pp.page0) + blk;
+                        tma_load_page(dst, &map_k, page, &kv_full[stage]);
+                        tma_load_page(dst + kTileKBytes, &map_v, page, &v_full[stage]);
+                    }
                 }
                 pf_valid = t + 1u < t1;
                 if (pf_valid) {
@@ -359,7 +478,7 @@ decode_tcp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
             atomicMax(a.status, uint32_t(KRIYA_DEV_WAIT_EXPIRED));
             *abort_flag = 1;
         }
-    } else if (warp == 7) {
+    } else if (warp == 11) {
         // ---- stager: per run piece the query operand (32 rows: (half, head)) and the new token's K/V row -----------
         uint32_t runs = 0;
         bool ok = true;
@@ -386,33 +505,29 @@ decode_tcp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                 const uint32_t position = pp.f.positions_are_context ? seg.row_tokens - 1u : pp.f.positions[seg.req];
                 rope8_coeffs(cs, c * 8u, position, pp.f);
             }
-            uint4 lo[ITEMS], hi[ITEMS];
-#pragma unroll
+            const bool stage_q = runs > 0u;  // the first piece's query rows are staged by warps 0-3
+            // one item at a time, not unrolled: this warp runs a whole piece ahead of the tensor cores, and code that is
+            // executed a few times per launch is paid for in instruction-cache misses
+#pragma unroll 1
             for (int it = 0; it < ITEMS; ++it) {
                 const uint32_t j = (lane + 32u * it) >> 3;
-                if (j < uint32_t(HQ)) {
-                    lo[it] = *reinterpret_cast<const uint4*>(qg + j * kD + c * 8);
-                    hi[it] = *reinterpret_cast<const uint4*>(qg + j * kD + 64 + c * 8);
-                }
-            }
-#pragma unroll
-            for (int it = 0; it < ITEMS; ++it) {
-                const uint32_t j = (lane + 32u * it) >> 3;
-                if (j < uint32_t(HQ)) {
-                    if (fused) rope8_apply<T>(lo[it], hi[it], c * 8u, cs, pp.f.rotary_dim / 2u);
+                if (stage_q && j < uint32_t(HQ)) {
+                    uint4 lo = *reinterpret_cast<const uint4*>(qg + j * kD + c * 8);
+                    uint4 hi = *reinterpret_cast<const uint4*>(qg + j * kD + 64 + c * 8);
+                    if (fused) rope8_apply<T>(lo, hi, c * 8u, cs, pp.f.rotary_dim / 2u);
                     const uint32_t row = 8u * (j / uint32_t(G)) + j % uint32_t(G);
-                    *reinterpret_cast<uint4*>(qb + row * 128u + ((c ^ (row & 7u)) << 4)) = lo[it];
-                    *reinterpret_cast<uint4*>(qb + 2048u + row * 128u + ((c ^ (row & 7u)) << 4)) = hi[it];
+                    *reinterpret_cast<uint4*>(qb + row * 128u + ((c ^ (row & 7u)) << 4)) = lo;
+                    *reinterpret_cast<uint4*>(qb + 2048u + row * 128u + ((c ^ (row & 7u)) << 4)) = hi;
                     if (fused && owns_last && pp.f.q_rope_out != nullptr) {
                         uint16_t* qo = reinterpret_cast<uint16_t*>(pp.f.q_rope_out) + (size_t(seg.req) * Hq + j) * kD;
-                        *reinterpret_cast<uint4*>(qo + c * 8) = lo[it];
-                        *reinterpret_cast<uint4*>(qo + 64 + c * 8) = hi[it];
+                        *reinterpret_cast<uint4*>(qo + c * 8) = lo;
+                        *reinterpret_cast<uint4*>(qo + 64 + c * 8) = hi;
                     }
                 }
             }
             fence_async_smem();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&q_ready[runs % uint32_t(kQBufs)]);
+            if (lane == 0 && stage_q) mbar_arrive(&q_ready[runs % uint32_t(kQBufs)]);
             if (owns_last) {
                 const uint32_t tok = seg.row_tokens - 1u;
                 const uint32_t blk = uint32_t(table[tok / kPage]);
@@ -447,20 +562,29 @@ decode_tcp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
             atomicMax(a.status, uint32_t(KRIYA_DEV_WAIT_EXPIRED));
             *abort_flag = 1;
         }
-    } else if (warp == 5) {
+    } else if (warp == 9) {
         // ---- MMA issuer ---------------------------------------------------------------------------------
-        const uint32_t kv_addr = smem_u32(sKV), q_addr = smem_u32(sQ), p_addr = smem_u32(sP);
+        // Every lane runs this code, descriptor arithmetic included; only the tensor-core instructions themselves are
+        // predicated on the elected lane.  That keeps their operands in uniform registers: issued from inside a
+        // one-lane branch every instruction costs about a hundred cycles and the issue rate, not the memory stream,
+        // bounds the kernel.
+        const uint32_t el = (lane == 0) ? 1u : 0u;
+        const uint64_t kv_desc = smem_desc_sw128(smem_u32(sKV), 16, 1024);       // K rows: K-major, 8-row groups 1 KB apart
+        // V: MN-major, M = 128 d as two groups of 64 (the head's two planes, 2 KB apart), 8-token groups 1 KB apart
+        const uint64_t v_desc = smem_desc_sw128(smem_u32(sKV), 2048, 1024);
+        const uint64_t q_desc = smem_desc_sw128(smem_u32(sQ), 16, 1024);
+        const uint64_t p_desc = smem_desc_sw128(smem_u32(sP), 16, 1024);
         auto issue_s = [&](uint32_t gg, uint32_t qbuf) {
             const uint32_t stage = gg % kStages;
             const uint32_t d_tmem = tmem_base + ((gg & 1u) ? kColS1 : kColS0);
+            const uint64_t ad = kv_desc + uint64_t((stage * kStageBytes) >> 4), bd = q_desc + uint64_t((qbuf * kQBytes) >> 4);
 #pragma unroll
-            for (int ks = 0; ks < 4; ++ks) {  // 64 d of a half = 4 steps of 16
-                const uint32_t a_off = stage * kStageBytes + uint32_t(ks) * 32u;
-                const uint32_t b_off = qbuf * kQBytes + uint32_t(ks) * 32u;
-                umma_f16(d_tmem, smem_desc_sw128(kv_addr + a_off, 16, 1024), smem_desc_sw128(q_addr + b_off, 16, 1024), IDESC_S,
-                         ks > 0 ? 1u : 0u);
-            }
-            umma_commit(&s_full[gg & 1u]);
+            for (int g2 = 0; g2 < 2; ++g2)  // the tile's two halves of 128 operand rows (2 pages each)
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks)  // 64 d of a half = 4 steps of 16
+                    umma_ss_pred(d_tmem + uint32_t(g2) * 32u, ad + uint64_t((uint32_t(g2) * 16384u + uint32_t(ks) * 32u) >> 4),
+                                 bd + uint64_t((uint32_t(ks) * 32u) >> 4), IDESC_S, ks > 0 ? 1u : 0u, el);
+            umma_commit_pred(&s_full[gg & 1u], el);
         };
         uint32_t g = 0;
         bool ok = true;
@@ -488,50 +612,51 @@ decode_tcp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                 la_first = false;
             }
             tc_fence_after();
-            if (lane == 0) issue_s(la_g, la_run % uint32_t(kQBufs));
-            __syncwarp();
+            issue_s(la_g, la_run % uint32_t(kQBufs));
             ++la_g;
             if (++la_t >= la_t1) {
-                if (lane == 0) umma_commit(&q_free[la_run % uint32_t(kQBufs)]);
-                __syncwarp();
+                umma_commit_pred(&q_free[la_run % uint32_t(kQBufs)], el);
                 ++la_si;
                 ++la_run;
                 la_valid = la_load();
             }
             return true;
         };
-        ok = la_issue();
+        bool primed = false;  // the very first tile's scores are issued together with the second's (one copy of the code)
         for (uint32_t si = seg_begin; si < seg_end && ok; ++si) {
             const KriyaTcSeg seg = seg_at(si);
             if (seg.blk_hi <= seg.blk_lo) continue;
             const uint32_t t0 = seg.blk_lo / kPagesPerTile, t1 = (seg.blk_hi + kPagesPerTile - 1) / kPagesPerTile;
             for (uint32_t t = t0; t < t1 && ok; ++t, ++g) {
                 if (*abort_flag) { ok = false; break; }
-                ok = la_issue();
+#pragma unroll 1
+                for (int k = primed ? 1 : 0; k < 2 && ok; ++k) ok = la_issue();
+                primed = true;
                 if (!ok) break;
-                ok = warp_wait_l(wait_ns, &p_ready[g & 1u], (g >> 1) & 1u);
+                const uint32_t stage = g % kStages;
+                ok = warp_wait_l(wait_ns, &p_ready[g & 1u], (g >> 1) & 1u) && warp_wait_l(wait_ns, &v_full[stage], (g / kStages) & 1u);
                 if (!ok) break;
                 tc_fence_after();
-                if (lane == 0) {
-                    const uint32_t stage = g % kStages;
+                const uint64_t ad = v_desc + uint64_t((stage * kStageBytes + kTileKBytes) >> 4);
+                const uint64_t bd = p_desc + uint64_t(((g & 1u) * kPBytes) >> 4);
+                const uint32_t first = (t > t0) ? 1u : 0u;
 #pragma unroll
-                    for (int ks = 0; ks < 8; ++ks) {  // 128 operand rows = 8 steps of 16
-                        const uint32_t a_off = stage * kStageBytes + kTileKBytes + uint32_t(ks) * 2048u;
-                        const uint32_t b_off = (g & 1u) * kPBytes + uint32_t(ks / 4) * 4096u + uint32_t(ks % 4) * 32u;
-                        umma_f16(tmem_base + kColO, smem_desc_sw128(kv_addr + a_off, 8192, 1024), smem_desc_sw128(p_addr + b_off, 16, 1024),
-                                 IDESC_O, (t > t0 || ks > 0) ? 1u : 0u);
-                    }
-                    umma_commit(&kv_empty[stage]);
-                    umma_commit(&pv_done[g & 1u]);
-                }
-                __syncwarp();
+                for (int pgi = 0; pgi < kPagesPerTile; ++pgi)
+#pragma unroll
+                    for (int h = 0; h < kHkv; ++h)  // the 16 tokens of head h of the page are one K step; its d halves the two M groups
+                        umma_ss_pred(tmem_base + kColO + 16u * uint32_t(h),
+                                     ad + uint64_t((uint32_t(pgi) * kPageBytes + uint32_t(h) * 4096u) >> 4),
+                                     bd + uint64_t((uint32_t(pgi >> 1) * 1024u + uint32_t(pgi & 1) * 64u + uint32_t(h) * 32u) >> 4), IDESC_O,
+                                     (pgi > 0) ? 1u : first, el);
+                umma_commit_pred(&kv_empty[stage], el);
+                umma_commit_pred(&pv_done[g & 1u], el);
             }
         }
         if (!ok && lane == 0) {
             atomicMax(a.status, uint32_t(KRIYA_DEV_WAIT_EXPIRED));
             *abort_flag = 1;
         }
-    } else if (warp == 6) {
+    } else if (warp == 10) {
         // ---- scratch-set guard (see kriya_decode_tc.cu) -------------------------------------------------------
         if (lane == 0) {
             const bool free_now = wait_set_free(pp.set_done, pp.done_expect, pp.a.wait_ns);
@@ -540,22 +665,75 @@ decode_tcp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
             *set_free_s = free_now ? 1u : 2u;
         }
     } else {
-        // ---- softmax warps: warp w = (page w / 2 of the tile, KV head w % 2); lane = (half lane / 16, token lane % 16) -----
-        const uint32_t lane_addr = (warp * 32u) << 16;
+        // ---- softmax warps 0-7: warp w owns operand rows 32 w .. 32 w + 31 of the tile ------------------------------------
+        // = (page w / 2, KV head w % 2); lane = (half lane / 16, token lane % 16).  Warps 0-3 read the accumulator of the
+        // tile's first score MMA (TMEM lanes 32 w ..), warps 4-7 that of the second (lanes 32 (w - 4) ..).
+        const uint32_t wq = warp & 3u, g2 = warp >> 2;
+        const uint32_t lane_addr = (wq * 32u) << 16;
         const uint32_t hd = warp & 1u, pg = warp >> 1, half = lane >> 4, tk = lane & 15u;
         const bool softcap = a.logit_softcap > 0.0f;
         const float scale2 = softcap ? a.sm_scale : a.sm_scale * kLog2e;
         const bool state_mode = a.state_o != nullptr;
-        // this thread's eight probability entries of a tile: operand row n = 16 half + 8 hd + jj, element k = 32 warp + lane
-        const uint32_t k_in = (warp & 1u) * 32u + lane;  // position inside the 64-row K block (block = page of the tile)
+        // the probability entries of this thread's token (written by the thread of the first half of d): pair of pages pg / 2,
+        // operand row jj, element k = 32 (pg % 2) + 16 hd + tk of the pair's 64
+        const uint32_t k_in = 32u * (pg & 1u) + 16u * hd + tk;
         uint32_t p_off[G];
 #pragma unroll
-        for (int jj = 0; jj < G; ++jj) {
-            const uint32_t n = 16u * half + 8u * hd + uint32_t(jj);
-            p_off[jj] = pg * 4096u + n * 128u + ((((k_in >> 3) ^ (n & 7u)) << 4) | ((k_in & 7u) << 1));
-        }
-        uint32_t g = 0;
+        for (int jj = 0; jj < G; ++jj)
+            p_off[jj] = (pg >> 1) * 1024u + uint32_t(jj) * 128u + ((((k_in >> 3) ^ uint32_t(jj)) << 4) | ((k_in & 7u) << 1));
+        // at the end of a piece threads 0-127 finish KV head 0 and threads 128-255 KV head 1, one output dimension each
+        const uint32_t fin_hd = tid >> 7, d = tid & 127u;
+        float* fin_stage = red + 64 + fin_hd * 128;
         bool ok = true;
+        if (first_q && warp < 4u) {
+            // ---- query rows of the first piece: warps 0-3 (idle until the first scores arrive), one 16-byte chunk pair per
+            // thread; rotating sixteen heads is a few thousand instructions, microseconds for the single stager warp -----
+            const uint32_t fq_j = tid >> 3, fq_c = tid & 7u;  // query head and chunk of this thread's item
+            const bool fq_active = fq_j < uint32_t(HQ);
+            if (pdl == 3u) {
+                pdl_wait_previous_grid();
+                if (tid == 0 && q_bulk) issue_q0();
+            }
+            uint32_t s0 = seg_begin;
+            while (s0 + 1u < seg_end && seg_at(s0).blk_hi <= seg_at(s0).blk_lo) ++s0;
+            const KriyaTcSeg seg0 = seg_at(s0);
+            const bool owns_last0 = stager_fused && seg0.row_tokens > 0u && uint64_t(seg0.blk_hi) * kPage >= seg0.row_tokens;
+            float2 fq_cs[8];
+            if (stager_fused && !cs_bulk) rope8_coeffs(fq_cs, fq_c * 8u, hdr_position, pp.f);
+            uint4 fq_lo = make_uint4(0u, 0u, 0u, 0u), fq_hi = make_uint4(0u, 0u, 0u, 0u);
+            if (q_bulk) {
+                ok = warp_wait_l(wait_ns, &aux_full[1], 0u);
+                if (fq_active) {
+                    fq_lo = *reinterpret_cast<const uint4*>(sQraw + fq_j * 256u + fq_c * 16u);
+                    fq_hi = *reinterpret_cast<const uint4*>(sQraw + fq_j * 256u + 128u + fq_c * 16u);
+                }
+                if (cs_bulk) {
+#pragma unroll
+                    for (int e = 0; e < 8; ++e)
+                        fq_cs[e] = (fq_c * 8u + uint32_t(e) < half_rot0) ? sCs[fq_c * 8u + uint32_t(e)] : make_float2(1.0f, 0.0f);
+                }
+            } else if (fq_active) {
+                const uint16_t* qg = reinterpret_cast<const uint16_t*>(a.q) + (size_t(hdr0.w) * Hq + fq_j) * kD;
+                fq_lo = *reinterpret_cast<const uint4*>(qg + fq_c * 8);
+                fq_hi = *reinterpret_cast<const uint4*>(qg + 64 + fq_c * 8);
+            }
+            if (fq_active) {
+                if (stager_fused) rope8_apply<T>(fq_lo, fq_hi, fq_c * 8u, fq_cs, half_rot0);
+                const uint32_t row = 8u * (fq_j / uint32_t(G)) + fq_j % uint32_t(G);
+                *reinterpret_cast<uint4*>(sQ + row * 128u + ((fq_c ^ (row & 7u)) << 4)) = fq_lo;
+                *reinterpret_cast<uint4*>(sQ + 2048u + row * 128u + ((fq_c ^ (row & 7u)) << 4)) = fq_hi;
+                if (owns_last0 && pp.f.q_rope_out != nullptr) {
+                    uint16_t* qo = reinterpret_cast<uint16_t*>(pp.f.q_rope_out) + (size_t(hdr0.w) * Hq + fq_j) * kD;
+                    *reinterpret_cast<uint4*>(qo + fq_c * 8) = fq_lo;
+                    *reinterpret_cast<uint4*>(qo + 64 + fq_c * 8) = fq_hi;
+                }
+            }
+            fence_async_smem();
+            bar_sync(4u, 128u);
+            if (tid == 0) mbar_arrive(&q_ready[0]);
+        }
+        ok = !softmax_or(!ok);
+        uint32_t g = 0;
         bool set_known = false;
         for (uint32_t si = seg_begin; si < seg_end && ok; ++si) {
             const KriyaTcSeg seg = seg_at(si);
@@ -575,9 +753,9 @@ decode_tcp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                 ok = warp_wait_l(wait_ns, &s_full[g & 1u], (g >> 1) & 1u);
                 if (!ok) break;
                 tc_fence_after();
-                // partial scores of this row: columns 16 half' + 8 hd + jj; this lane's half is the useful one
+                // partial scores of this row: columns 16 half' + 8 hd + jj of its score MMA; this lane's half is the useful one
                 uint32_t r0[8], r1[8];
-                const uint32_t s_col = tmem_base + lane_addr + ((g & 1u) ? kColS1 : kColS0) + 8u * hd;
+                const uint32_t s_col = tmem_base + lane_addr + ((g & 1u) ? kColS1 : kColS0) + 32u * g2 + 8u * hd;
                 tmem_ld8(s_col, r0);
                 tmem_ld8(s_col + 16u, r1);
                 tmem_wait_ld();
@@ -590,15 +768,15 @@ decode_tcp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                     float x = __uint_as_float(half ? r1[jj] : r0[jj]);
                     x += __shfl_xor_sync(0xFFFFFFFFu, x, 16);  // the other half of d: the same token and head, lane +- 16
                     x *= scale2;
-                    if (softcap) x = tanhf(fminf(fmaxf(x / a.logit_softcap, -15.0f), 15.0f)) * a.logit_softcap * kLog2e;
+                    if (softcap) x = softcap_log2(x, a.logit_softcap);
                     s[jj] = valid ? x : -INFINITY;
                     over = over || (s[jj] > m_used[jj] + kRescale);
                 }
                 float alpha[G];
 #pragma unroll
                 for (int jj = 0; jj < G; ++jj) alpha[jj] = 1.0f;
-                if (bar_or_128(over)) {
-                    // per-head maximum over the tile: 16 tokens of this warp, then the other page's warp of the same head
+                if (softmax_or(over)) {
+                    // per-head maximum over the tile: 16 tokens of this warp, then the four warps (pages) of the same KV head
                     float mx[G];
 #pragma unroll
                     for (int jj = 0; jj < G; ++jj) mx[jj] = s[jj];
@@ -610,37 +788,41 @@ decode_tcp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
 #pragma unroll
                         for (int jj = 0; jj < G; ++jj) red[warp * 8 + jj] = mx[jj];
                     }
-                    named_bar_sync_128();
+                    softmax_sync();
 #pragma unroll
                     for (int jj = 0; jj < G; ++jj) {
-                        const float m_tile = fmaxf(red[hd * 8 + jj], red[(hd + 2u) * 8 + jj]);
+                        const float m_tile = fmaxf(fmaxf(red[hd * 8 + jj], red[(hd + 2u) * 8 + jj]),
+                                                   fmaxf(red[(hd + 4u) * 8 + jj], red[(hd + 6u) * 8 + jj]));
                         if (m_tile > m_used[jj]) {
                             alpha[jj] = (m_used[jj] == -INFINITY) ? 0.0f : exp2f(m_used[jj] - m_tile);
                             m_used[jj] = m_tile;
                         }
                     }
                     // the accumulator's columns belong to all query heads of the row: publish the factors
-                    if (lane == 0 && pg == 0u) {
+                    if (lane == 0 && warp < 2u) {
 #pragma unroll
                         for (int jj = 0; jj < 8; ++jj) alpha_s[hd * 8 + jj] = (jj < G) ? alpha[jj < G ? jj : 0] : 1.0f;
                     }
-                    named_bar_sync_128();
+                    softmax_sync();
                     if (t > t0) {
                         ok = warp_wait_l(wait_ns, &pv_done[(g - 1u) & 1u], ((g - 1u) >> 1) & 1u);
                         if (!ok) break;
-                        tc_fence_after();
-                        // O' rows (d_lo) live in lanes 0-15 of every warp; the other lanes go through the motions
-                        uint32_t o[32];
-                        tmem_ld32(tmem_base + lane_addr + kColO, o);
-                        tmem_wait_ld();
+                        if (warp < 4u) {
+                            tc_fence_after();
+                            // O^T: lane = d, column = 16 head + jj (columns 8-15 of each head unused)
+                            uint32_t o[32];
+                            tmem_ld32(tmem_base + lane_addr + kColO, o);
+                            tmem_wait_ld();
 #pragma unroll
-                        for (int cI = 0; cI < 32; ++cI) o[cI] = __float_as_uint(__uint_as_float(o[cI]) * alpha_s[cI & 15]);
-                        tmem_st32(tmem_base + lane_addr + kColO, o);
-                        tmem_wait_st();
+                            for (int cI = 0; cI < 32; ++cI)
+                                o[cI] = __float_as_uint(__uint_as_float(o[cI]) * alpha_s[((cI >> 4) << 3) | (cI & 7)]);
+                            tmem_st32(tmem_base + lane_addr + kColO, o);
+                            tmem_wait_st();
+                        }
                     }
 #pragma unroll
                     for (int jj = 0; jj < G; ++jj) l_lane[jj] *= alpha[jj];
-                    named_bar_sync_128();  // alpha_s and red may be rewritten by the next tile
+                    softmax_sync();  // alpha_s and red may be rewritten by the next tile
                 }
                 if (g >= 2) {
                     ok = warp_wait_l(wait_ns, &pv_done[g & 1u], ((g >> 1) - 1u) & 1u);
@@ -651,9 +833,15 @@ decode_tcp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
 #pragma unroll
                     for (int jj = 0; jj < G; ++jj) {
                         const float p = (s[jj] == -INFINITY) ? 0.0f : fast_exp2(s[jj] - m_used[jj]);
-                        l_lane[jj] += half ? 0.0f : p;  // both halves hold the same probability: count it once
-                        *reinterpret_cast<uint16_t*>(pbuf + p_off[jj]) = T::store(p);
+                        if (half == 0u) {  // both halves of d hold the token's score: one of them carries it on
+                            l_lane[jj] += p;
+                            *reinterpret_cast<uint16_t*>(pbuf + p_off[jj]) = T::store(p);
+                        }
                     }
+                }
+                if (__any_sync(0xFFFFFFFFu, !valid)) {  // the V half must have landed before rows of it are cleared
+                    ok = warp_wait_l(wait_ns, &v_full[g % kStages], (g / kStages) & 1u);
+                    if (!ok) break;
                 }
                 if (!valid) {  // this thread's V row must contribute nothing: clear it (0 * garbage must not appear)
                     const uint32_t stage = g % kStages;
@@ -667,7 +855,7 @@ decode_tcp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
             }
             if (!ok) break;
             // ---- end of the run piece ---------------------------------------------------------------------------
-            // sums per head: 16 tokens of the warp (the lanes of the second half hold zeros), then the two pages' warps
+            // sums per head: 16 tokens of the warp (the lanes of the second half hold zeros), then the KV head's four warps
             float l_tot[G];
 #pragma unroll
             for (int jj = 0; jj < G; ++jj) l_tot[jj] = l_lane[jj];
@@ -679,61 +867,56 @@ decode_tcp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
 #pragma unroll
                 for (int jj = 0; jj < G; ++jj) red[warp * 8 + jj] = l_tot[jj];
             }
-            named_bar_sync_128();
-            if (lane == 0 && pg == 0u) {  // (m, l) of the piece for the G heads of this KV head, row order j = hd * G + jj
+            softmax_sync();
+            if (lane == 0 && warp < 2u) {  // (m, l) of the piece for the G heads of this KV head, row order j = hd * G + jj
 #pragma unroll
                 for (int jj = 0; jj < G; ++jj) {
                     ml_s[(hd * G + jj) * 2 + 0] = m_used[jj];
-                    ml_s[(hd * G + jj) * 2 + 1] = red[hd * 8 + jj] + red[(hd + 2u) * 8 + jj];
+                    ml_s[(hd * G + jj) * 2 + 1] = (red[hd * 8 + jj] + red[(hd + 2u) * 8 + jj]) + (red[(hd + 4u) * 8 + jj] + red[(hd + 6u) * 8 + jj]);
                 }
             }
-            // the accumulator goes through shared memory so that thread t ends up with dimension t of every head
-            float* ostage = reinterpret_cast<float*>(sP);  // [HQ][128]; the P buffers are idle here
+            // the accumulator: lane = d, columns 16 head + jj; threads 0-127 take KV head 0's columns, threads 128-255 head 1's
+            uint32_t o8[8];
+#pragma unroll
+            for (int cI = 0; cI < 8; ++cI) o8[cI] = 0u;
             if (!empty) {
                 ok = warp_wait_l(wait_ns, &pv_done[(g - 1u) & 1u], ((g - 1u) >> 1) & 1u);
                 if (!ok) break;
                 tc_fence_after();
-                uint32_t o[32];
-                tmem_ld32(tmem_base + lane_addr + kColO, o);
+                tmem_ld8(tmem_base + lane_addr + kColO + 16u * fin_hd, o8);
                 tmem_wait_ld();
                 tc_fence_before();
-                if (lane < 16u) {
-#pragma unroll
-                    for (int cI = 0; cI < 32; ++cI) {
-                        const uint32_t hh = (uint32_t(cI) & 15u) >> 3, jj = uint32_t(cI) & 7u;  // column = 16 half' + 8 head + jj
-                        if (jj < uint32_t(G)) ostage[(hh * G + jj) * kD + (uint32_t(cI) >> 4) * 64u + warp * 16u + lane] = __uint_as_float(o[cI]);
-                    }
-                }
             }
-            named_bar_sync_128();
-            const uint32_t d = tid;
-            float Mh[HQ], Lh[HQ], Oh[HQ];
+            softmax_sync();
+            float Mh[G], Lh[G], Oh[G];
 #pragma unroll
-            for (int j = 0; j < HQ; ++j) {
-                Mh[j] = empty ? -INFINITY : ml_s[j * 2];
-                Lh[j] = empty ? 0.0f : ml_s[j * 2 + 1];
-                Oh[j] = empty ? 0.0f : ostage[j * kD + d];
+            for (int jj = 0; jj < G; ++jj) {
+                Mh[jj] = empty ? -INFINITY : ml_s[(fin_hd * G + jj) * 2];
+                Lh[jj] = empty ? 0.0f : ml_s[(fin_hd * G + jj) * 2 + 1];
+                Oh[jj] = __uint_as_float(o8[jj]);
             }
-            named_bar_sync_128();  // ostage (the P buffers) and ml_s are free again
+            softmax_sync();  // ml_s is free again
             if (pdl == 3u) pdl_wait_previous_grid();
-            const size_t row0 = size_t(req) * Hq;
+            const size_t row0 = size_t(req) * Hq + fin_hd * G;
             const bool split = seg.n_parts > 1u;
             const bool finisher = !split || (seg.n_parts <= pp.late_parts && seg.slot + 1u == seg.first_slot + seg.n_parts);
             if (finisher) {
                 if (split) {
-                    ok = gather_merge<HQ>(pp.ll_o, pp.ll_ml, seg, pp.epoch, wait_ns, red, tid, Mh, Lh, Oh);
+                    const bool mine = gather_merge<G>(pp.ll_o, pp.ll_ml, seg, pp.epoch, wait_ns, fin_stage, 2u + fin_hd, d, uint32_t(HQ),
+                                                      fin_hd * G, Mh, Lh, Oh);
+                    ok = !softmax_or(!mine);
                     if (!ok) break;
                 }
 #pragma unroll
-                for (int j = 0; j < HQ; ++j) {
+                for (int jj = 0; jj < G; ++jj) {
                     if (state_mode) {
-                        a.state_o[(row0 + j) * kD + d] = Oh[j];
+                        a.state_o[(row0 + jj) * kD + d] = Oh[jj];
                         if (d == 0) {
-                            a.state_m[row0 + j] = Mh[j] / kLog2e;
-                            a.state_l[row0 + j] = Lh[j];
+                            a.state_m[row0 + jj] = Mh[jj] / kLog2e;
+                            a.state_l[row0 + jj] = Lh[jj];
                         }
                     } else {
-                        reinterpret_cast<uint16_t*>(a.out)[(row0 + j) * kD + d] = T::store(Oh[j] / fmaxf(Lh[j], 1e-12f));
+                        reinterpret_cast<uint16_t*>(a.out)[(row0 + jj) * kD + d] = T::store(Oh[jj] / fmaxf(Lh[jj], 1e-12f));
                     }
                 }
             } else {
@@ -744,22 +927,17 @@ decode_tcp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                         st = *set_free_s;
                         if (st == 0u && (spin & 63u) == 63u && global_timer_ns() - t_start > 2u * wait_ns) break;
                     }
-                    ok = !bar_or_128(st != 1u);
+                    ok = !softmax_or(st != 1u);
                     if (!ok) break;
                     set_known = true;
                 }
-                const size_t prow = size_t(seg.slot) * HQ;
+                const size_t prow = size_t(seg.slot) * HQ + fin_hd * G;
 #pragma unroll
-                for (int j = 0; j < HQ; ++j) {
-                    ll_store(&pp.ll_o[(prow + j) * kD + d], Oh[j], pp.epoch);
-                    if (tid == uint32_t(2 * j)) ll_store(&pp.ll_ml[(prow + j) * 2 + 0], Mh[j], pp.epoch);
-                    if (tid == uint32_t(2 * j + 1)) ll_store(&pp.ll_ml[(prow + j) * 2 + 1], Lh[j], pp.epoch);
+                for (int jj = 0; jj < G; ++jj) {
+                    ll_store(&pp.ll_o[(prow + jj) * kD + d], Oh[jj], pp.epoch);
+                    if (d == uint32_t(2 * jj)) ll_store(&pp.ll_ml[(prow + jj) * 2 + 0], Mh[jj], pp.epoch);
+                    if (d == uint32_t(2 * jj + 1)) ll_store(&pp.ll_ml[(prow + jj) * 2 + 1], Lh[jj], pp.epoch);
                 }
-            }
-            // the probability buffers served as output staging: their fixed zero pattern must be back before the next piece
-            if (si + 1 < seg_end) {
-                for (uint32_t i = tid; i < 2 * kPBytes / 16; i += 128u) reinterpret_cast<uint4*>(sP)[i] = make_uint4(0u, 0u, 0u, 0u);
-                named_bar_sync_128();
             }
         }
         if (!ok && lane == 0) {
@@ -771,7 +949,7 @@ decode_tcp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
     tc_fence_before();
     __syncthreads();
     if (tid == 0) atomicAdd(pp.set_done, 1u);
-    if (warp == 5) {
+    if (warp == 9) {
         tc_fence_after();
         tmem_dealloc(tmem_base, kTmemCols);
     }
@@ -826,7 +1004,7 @@ __global__ void __launch_bounds__(kD) late_merge_kernel(KriyaDecodeArgs a, const
 template <int G, typename T>
 cudaError_t launch_t(const Params& pp, const CUtensorMap& mk, const CUtensorMap& mv, uint32_t grid, int max_smem_optin,
                      bool programmatic, cudaStream_t s) {
-    const size_t smem = size_t(kStages) * kStageBytes + kQBufs * kQBytes + 2 * kPBytes + 512 + 64 + 128 + 320 + 8 * sizeof(KriyaTcSeg) + 1024;
+    const size_t smem = size_t(kStages) * kStageBytes + kQBufs * kQBytes + 2 * kPBytes + 2048 + 64 + 128 + 400 + 8 * sizeof(KriyaTcSeg) + 16 * 256 + 512 + 1024;
     if (smem > size_t(max_smem_optin)) return cudaErrorInvalidValue;
     auto kern = decode_tcp_kernel<G, T>;
     {
@@ -880,6 +1058,7 @@ cudaError_t launch_g(uint32_t group, const Params& pp, const CUtensorMap& mk, co
 
 }  // namespace tcp
 }  // namespace kriya
+
 
 bool kriya_decode_tcp_supported(uint32_t head_dim, uint32_t num_kv_heads, uint32_t group, uint32_t block_size) {
     return head_dim == uint32_t(kriya::tcp::kD) && num_kv_heads == uint32_t(kriya::tcp::kHkv) && group >= 1 && group <= 8 &&

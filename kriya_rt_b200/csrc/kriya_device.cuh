@@ -81,8 +81,9 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
 }
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint64_t limit_ns = kWaitNs) {
-    if (mbar_try_wait(bar, parity)) return true;
+// The polling loop is a function of its own: dozens of inlined copies of it would be most of a kernel's code, and code
+// that is executed once per CTA is paid for in instruction-cache misses.
+static __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, uint64_t limit_ns) {
     const uint64_t t0 = global_timer_ns();
     for (;;) {
 #pragma unroll 1
@@ -90,6 +91,20 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint64
             if (mbar_try_wait(bar, parity)) return true;
         if (global_timer_ns() - t0 > limit_ns) return false;
     }
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint64_t limit_ns = kWaitNs) {
+    if (mbar_try_wait(bar, parity)) return true;
+#ifdef KRIYA_INLINE_WAITS  // kernels that move registers between warpgroups (setmaxnreg) cannot call functions
+    const uint64_t t0 = global_timer_ns();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 64; ++i)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (global_timer_ns() - t0 > limit_ns) return false;
+    }
+#else
+    return mbar_wait_slow(bar, parity, limit_ns);
+#endif
 }
 // All 32 lanes wait, then agree: true only if every lane saw the phase complete.
 __device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, uint64_t limit_ns = kWaitNs) {

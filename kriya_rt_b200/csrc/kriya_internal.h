@@ -191,6 +191,13 @@ struct KriyaAppendArgs {
     uint32_t chunk_mode;
     uint32_t prefix_tokens;
     uint32_t inplace;  // rotate q and k where they are (k_in is written); v and the cache are not touched
+    uint32_t kv_q4 = 0;  // the cache is Q4KvGroup32: keys and values are quantised on their way in
+    // chunk_mode 2: chunks of several sequences; sequence s owns rows [seq_q_start[s], + seq_count[s]) of q / k / v, its
+    // token i sits at position seq_prefix[s] + i and its block table is plan row s
+    const uint32_t* seq_q_start = nullptr;
+    const uint32_t* seq_prefix = nullptr;
+    const uint32_t* seq_count = nullptr;
+    uint32_t n_seqs = 0;
     kriya_rope_kv_write_params p;
 };
 cudaError_t kriya_launch_append(const KriyaAppendArgs& a, uint32_t dtype, cudaStream_t s);
@@ -222,7 +229,7 @@ struct KriyaDecodeArgs {
 };
 // Returns cudaErrorInvalidValue for shapes the kernels are not instantiated for.
 cudaError_t kriya_launch_decode(const KriyaDecodeArgs& a, uint32_t head_dim, uint32_t block_size, uint32_t dtype,
-                                int max_smem_optin, cudaStream_t s);
+                                int max_smem_optin, cudaStream_t s, uint32_t kv_q4 = 0);
 bool kriya_decode_supported(uint32_t head_dim, uint32_t group, uint32_t num_kv_heads, uint32_t block_size);
 
 // Optional fused RoPE + KV append inside the tensor-core decode launch (null k_in: plain decode).

@@ -258,6 +258,26 @@ int32_t kriya_kv_allocate_sequence(kriya_kv_manager* m, uint64_t seq_id, const u
     return KRIYA_KV_OK;
 }
 
+int32_t kriya_kv_append_token_slots(kriya_kv_manager* m, const uint64_t* seq_ids, size_t n, uint32_t* out_blocks,
+                                    uint32_t* out_cow_pairs, size_t* out_n_cow, size_t* out_done) {
+    if (!m || (n && (!seq_ids || !out_blocks || !out_cow_pairs)) || !out_n_cow || !out_done) return KRIYA_KV_BAD_ARGUMENT;
+    *out_n_cow = 0;
+    *out_done = 0;
+    for (size_t i = 0; i < n; ++i) {
+        int32_t has = 0;
+        uint32_t src = 0, dst = 0;
+        const int32_t rc = kriya_kv_append_token_slot(m, seq_ids[i], &out_blocks[i], &has, &src, &dst);
+        if (rc != KRIYA_KV_OK) return rc;
+        if (has) {
+            out_cow_pairs[2 * *out_n_cow] = src;
+            out_cow_pairs[2 * *out_n_cow + 1] = dst;
+            *out_n_cow += 1;
+        }
+        *out_done = i + 1;
+    }
+    return KRIYA_KV_OK;
+}
+
 int32_t kriya_kv_append_token_slot(kriya_kv_manager* m, uint64_t seq_id, uint32_t* out_block, int32_t* out_has_cow,
                                    uint32_t* out_cow_src, uint32_t* out_cow_dst) {
     if (!m || !out_block || !out_has_cow) return KRIYA_KV_BAD_ARGUMENT;

@@ -27,6 +27,7 @@
 #include <cstdio>
 #include <cstdlib>
 
+#define KRIYA_INLINE_WAITS 1
 #include "kriya_tc.cuh"
 
 namespace kriya {
@@ -50,15 +51,6 @@ __device__ __forceinline__ void setmaxnreg_inc() { asm volatile("setmaxnreg.inc.
 constexpr float kLog2ePf = 1.4426950408889634f;
 constexpr float kRescaleThreshold = 8.0f;
 
-// Optional timeline of CTA 0 (compile with -DKRIYA_PF_TRACE): SM clock stamps per KV tile for the MMA warp and the
-// two softmax groups, dumped to stderr by the launcher on the sixth launch when KRIYA_TRACE is set.
-#ifdef KRIYA_PF_TRACE
-__device__ long long g_pf_trace[3 * 32 * 8];
-#define PTR(role, j, k) do { if (blockIdx.x == 0 && (j) < 32) g_pf_trace[((role) * 32 + (j)) * 8 + (k)] = clock64(); } while (0)
-#else
-#define PTR(role, j, k) do { } while (0)
-#endif
-
 struct PrefillParams {
     KriyaPrefillArgs a;
     uint32_t q_tiles;  // query tiles of the whole launch (all sequences)
@@ -69,39 +61,6 @@ struct PrefillParams {
 __device__ __forceinline__ void bulk_commit_wait_read() {
     asm volatile("cp.async.bulk.commit_group;" ::: "memory");
     asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-}
-
-// tcgen05.mma issue forms.  The _ts form takes the A operand from tensor memory (rows = lanes, two 16-bit K elements
-// per 32-bit column).  Both are warp-uniform: every lane of the issuing warp runs the (uniform) descriptor arithmetic and the
-// instruction itself is predicated on `elected`, which keeps the operands in uniform registers instead of
-// moving them there from one diverged lane for every instruction.
-__device__ __forceinline__ void umma_ss_pred(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                             uint32_t accumulate, uint32_t elected) {
-    asm volatile(
-        "{\n\t.reg .pred p, q;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "setp.ne.b32 q, %5, 0;\n\t"
-        "@q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
-        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(elected)
-        : "memory");
-}
-__device__ __forceinline__ void umma_ts_pred(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
-                                             uint32_t accumulate, uint32_t elected) {
-    asm volatile(
-        "{\n\t.reg .pred p, q;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "setp.ne.b32 q, %5, 0;\n\t"
-        "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
-        "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(elected)
-        : "memory");
-}
-__device__ __forceinline__ void umma_commit_pred(uint64_t* bar, uint32_t elected) {
-    asm volatile(
-        "{\n\t.reg .pred q;\n\t"
-        "setp.ne.b32 q, %1, 0;\n\t"
-        "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}" ::"r"(smem_u32(bar)),
-        "r"(elected)
-        : "memory");
 }
 
 // Shared memory (all tiles 1024-byte aligned):
@@ -167,7 +126,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
         tma_prefetch_map(&map_k);
         tma_prefetch_map(&map_v);
     }
-    if (tid == 0) PTR(2, 31, 0);
     if (tid == 0) {
         for (int i = 0; i < kKStages; ++i) {
             mbar_init(&k_full[i], 1);
@@ -190,13 +148,11 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
     if (warp == 9) {
         tmem_alloc(tmem_slot, TMEM_COLS);
         tmem_relinquish();
-        if (lane == 0) PTR(2, 30, 0);
     }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    if (tid == 0) PTR(2, 31, 1);
 
     if (warp >= 8) {
     setmaxnreg_dec<kRegsWorkers>();
@@ -212,7 +168,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
                 for (int p = 0; p < PANELS; ++p)
                     tma_load_2d(sQ + x * Q_BYTES + p * PANEL_BYTES, &map_q, int32_t(head0 + x) * D + p * 64, int32_t(tile_start), q_full);
         }
-        if (lane == 0) PTR(2, 30, 1);
         __syncwarp();
         uint32_t vs = 0, v_round = 0;  // V stage of tile j = j % kVStages, round = j / kVStages
         for (uint32_t j = 0; j < n_tiles; ++j) {
@@ -230,7 +185,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
                 }
             }
             const int32_t y = int32_t(a.layer_row0) + blk * kPagePf;
-            if (lane == 0 && j == 0) PTR(2, 30, 2);
             bool ok = j < uint32_t(kKStages) || warp_wait(&k_empty[ks], ((j >> 1) - 1u) & 1u);
             if (ok) {
                 if (lane == 0) mbar_arrive_expect_tx(&k_full[ks], npages * uint32_t(PANELS * kPagePf * 128));
@@ -281,9 +235,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
             if (last_head) umma_commit_pred(&k_empty[stage], el);
         };
         bool ok = n_tiles > 0 && warp_wait(q_full, 0u);
-        if (lane == 0) PTR(2, 30, 3);
         ok = ok && warp_wait(&k_full[0], 0u);
-        if (lane == 0) PTR(2, 30, 4);
         if (ok) {
             tc_fence_after();
             for (uint32_t x = 0; x < n_heads; ++x) issue_s(x, 0u, x + 1u == n_heads);
@@ -300,12 +252,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
                     if (ok && more) ok = warp_wait(&k_full[stage ^ 1u], ((j + 1u) >> 1) & 1u);
                     if (!ok) break;
                 }
-                if (lane == 0 && x == 0) PTR(2, j, 6);
                 ok = warp_wait(&p_ready[x], j & 1u);
-                if (lane == 0 && x == 0) PTR(2, j, 7);
                 if (!ok) break;
                 tc_fence_after();
-                if (lane == 0) PTR(2, j, x * 3);
 #pragma unroll
                 for (int ks = 0; ks < kKvTile / 16; ++ks) {
                     // A = P_x from tensor memory (16 keys = 8 columns), B = V page ks (MN-major)
@@ -313,10 +262,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
                                  vd + uint64_t((uint32_t(ks) * (kPagePf * 128)) >> 4), IDESC_O, (j > 0 || ks > 0) ? 1u : 0u, el);
                 }
                 if (x + 1u == n_heads) umma_commit_pred(&v_empty[vs], el);
-                if (lane == 0) PTR(2, j, x * 3 + 1);
                 if (more) issue_s(x, stage ^ 1u, x + 1u == n_heads);
                 else umma_commit_pred(&pv_done[x], el);
-                if (lane == 0) PTR(2, j, x * 3 + 2);
             }
             if (++vs == uint32_t(kVStages)) { vs = 0; ++v_round; }
         }
@@ -345,7 +292,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
             ok = warp_wait(&s_full[x], j & 1u);
             if (!ok) break;
             tc_fence_after();
-            if (row == 0) PTR(x, j, 0);
             const uint32_t key0 = (tile0 + j) * kKvTile;
             const bool diag = key0 + kKvTile - 1u > qt.pos0;  // some row of the tile masks some key
             // some key of the tile lies in front of some row's window (the last row's window starts latest)
@@ -355,7 +301,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
 #pragma unroll
             for (int c = 0; c < 4; ++c) tmem_ld32(s_addr + c * 32, sr[c]);
             tmem_wait_ld();
-            if (row == 0) PTR(x, j, 1);
             // the scores stay raw in registers; scale and exponent reference are folded into one fma per pair below
             if (softcap) {
 #pragma unroll
@@ -386,7 +331,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) m4[c] = max3(m4[c], __uint_as_float(sr[c][i]), __uint_as_float(sr[c][i + 1]));
             const float m_tile = fmaxf(max3(m4[0], m4[1], m4[2]), m4[3]) * scale2;  // scale2 > 0
-            if (row == 0) PTR(x, j, 2);
             // the commit behind S_x(j) covers P_x.V(j-1): O_x may be rescaled and the score tile rewritten
             float alpha = 1.0f;
             bool need = false;
@@ -409,7 +353,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
                 }
             }
             // probabilities in the storage dtype, two keys per 32-bit column, over the first 64 columns of the score tile
-            if (row == 0) PTR(x, j, 3);
             float2 psum2 = make_float2(0.0f, 0.0f);
             // a row that has seen no key yet (its window begins behind this tile) has m_used = -inf: its exponents must
             // come out as -inf, not as inf - inf
@@ -428,10 +371,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
                 tmem_st16(s_addr + c * 16, packed);
             }
             const float psum = psum2.x + psum2.y;
-            if (row == 0) PTR(x, j, 4);
             tmem_wait_st();
-            if (row == 0) PTR(x, j, 5);
-            if (row == 0) PTR(x, j, 6);
             l_run = l_run * alpha + psum;
             // Only the last tile can hold rows that are not valid V data: slots past the end of the sequence (loaded, but
             // they may hold anything) and pages the producer did not load (shared memory as the previous kernel left
@@ -453,15 +393,12 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
                     fence_async_smem();
                 }
             }
-            if (row == 0) PTR(x, j, 7);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&p_ready[x]);
         }
-        if (tid == 0) PTR(2, 31, 2);
         if (ok && n_tiles > 0) {
             ok = warp_wait(&pv_done[x], 0u);
-            if (tid == 0) PTR(2, 31, 3);
             if (ok) {
                 tc_fence_after();
                 const float inv_l = 1.0f / fmaxf(l_run, 1e-12f);
@@ -490,7 +427,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
                             *reinterpret_cast<uint4*>(og + c * 32 + q4 * 8) = val;
                     }
                 }
-                if (tid == 0) PTR(2, 31, 6);
                 if (full) {
                     fence_async_smem();
                     __syncwarp();
@@ -501,7 +437,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
                             tma_store_2d(&map_o, stage + p * PANEL_BYTES, int32_t(head0 + x) * D + p * 64, int32_t(tile_start));
                     }
                 }
-                if (tid == 0) PTR(2, 31, 7);
                 bulk_commit_wait_read();  // the tile must have been read before the CTA gives its shared memory back
             }
         }
@@ -512,7 +447,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
     }
 
     }
-    if (tid == 0) PTR(2, 31, 4);
     // ---- teardown: every thread gets here; TMEM is returned by the warp that took it ------------------
     tc_fence_before();
     __syncthreads();
@@ -520,7 +454,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
         tc_fence_after();
         tmem_dealloc(tmem_base, TMEM_COLS);
     }
-    if (tid == 0) PTR(2, 31, 5);
 }
 
 template <int D, typename T>
@@ -538,27 +471,6 @@ cudaError_t launch_prefill_t(const KriyaPrefillArgs& a, const CUtensorMap& mk, c
     const uint32_t group = a.num_q_heads / a.num_kv_heads;
     pp.pairs = (group + 1u) / 2u;
     kern<<<pp.q_tiles * pp.pairs * a.num_kv_heads, kPrefillThreads, smem, s>>>(mk, mv, mq, mo, pp);
-#ifdef KRIYA_PF_TRACE
-    if (getenv("KRIYA_TRACE")) {
-        static int calls = 0;
-        if (++calls == 6) {
-            cudaDeviceSynchronize();
-            static long long h[3 * 32 * 8];
-            cudaMemcpyFromSymbol(h, g_pf_trace, sizeof(h));
-            long long t0 = h[0];
-            for (int i = 0; i < 3 * 32 * 8; ++i)
-                if (h[i] && llabs(h[i] - h[0]) < 1000000 && h[i] < t0) t0 = h[i];
-            const char* role[3] = {"smA", "smB", "mma"};
-            for (int j = 0; j < 32; ++j)
-                for (int r = 0; r < 3; ++r) {
-                    if (!h[(r * 32 + j) * 8] || llabs(h[(r * 32 + j) * 8] - t0) > 1000000) continue;
-                    fprintf(stderr, "tile %2d %s", j, role[r]);
-                    for (int k = 0; k < 8; ++k) fprintf(stderr, " %7lld", h[(r * 32 + j) * 8 + k] ? h[(r * 32 + j) * 8 + k] - t0 : -1);
-                    fprintf(stderr, "\n");
-                }
-        }
-    }
-#endif
     return cudaGetLastError();
 }
 

@@ -17,6 +17,7 @@ from . import _native as N
 from ._native import BsrGqaParams, RopeKvWriteParams, TreeVerifyParams
 
 DTYPE_BF16, DTYPE_FP16 = 0, 1
+KV_16BIT, KV_Q4_GROUP32 = 0, 1
 
 
 class CudaBackendError(RuntimeError):
@@ -45,11 +46,11 @@ class CudaExecutor:
     def __init__(self, *, num_layers: int, num_kv_blocks: int, block_size_tokens: int, num_q_heads: int,
                  num_kv_heads: int, head_dim: int, dtype: int = DTYPE_BF16, device: int = 0, rotary_dim: int = 0,
                  rope_theta: float = 10000.0, rope_max_seq_len: int = 0, max_batch_rows: int = 0,
-                 max_page_indices: int = 0, max_tiles: int = 0, max_query_tokens: int = 0):
+                 max_page_indices: int = 0, max_tiles: int = 0, max_query_tokens: int = 0, kv_format: int = 0):
         self._lib = N.cuda_lib()
         self.cfg = N.CudaConfig(device, num_layers, num_kv_blocks, block_size_tokens, num_q_heads, num_kv_heads,
                                 head_dim, dtype, rotary_dim, rope_theta, rope_max_seq_len, max_batch_rows,
-                                max_page_indices, max_tiles, max_query_tokens)
+                                max_page_indices, max_tiles, max_query_tokens, kv_format)
         h = C.c_void_p()
         rc = self._lib.kriya_cuda_ctx_create(C.byref(self.cfg), C.byref(h))
         if rc != 0:
@@ -60,6 +61,7 @@ class CudaExecutor:
         self.rotary_dim = rotary_dim or head_dim
         self.rope_theta = rope_theta
         self.rope_max_seq_len = rope_max_seq_len or 4096
+        self.kv_format = kv_format
 
     def close(self) -> None:
         h, self._h = getattr(self, "_h", None), None
@@ -108,6 +110,8 @@ class CudaExecutor:
 
         k, v = self.kv_pool_ptrs(layer)
         shape = (self.num_kv_blocks, self.block_size_tokens, self.num_kv_heads, self.head_dim)
+        if self.kv_format == KV_Q4_GROUP32:  # 20 bytes per 32 values, seen as 10 int16 words
+            shape = shape[:3] + (self.head_dim // 32 * 10,)
 
         class _Raw:
             def __init__(self, ptr):
@@ -153,6 +157,16 @@ class CudaExecutor:
         self._check(self._lib.kriya_cuda_rope_kv_append_chunk(
             self._h, layer, _ptr(q_inout), _ptr(k_in), _ptr(v_in), _ptr(q_norm_w), _ptr(k_norm_w), prefix_tokens,
             num_tokens, C.byref(params)))
+
+    def rope_kv_append_chunk_batch(self, layer: int, q_inout, k_in, v_in, q_start, prefix, count, params: RopeKvWriteParams,
+                                   q_norm_w=None, k_norm_w=None) -> None:
+        """Chunks of several sequences appended in one launch; plan row r is sequence r's table (as paged_gqa_prefill_batch)."""
+        qs = np.ascontiguousarray(q_start, np.uint32)
+        pf = np.ascontiguousarray(prefix, np.uint32)
+        ct = np.ascontiguousarray(count, np.uint32)
+        self._check(self._lib.kriya_cuda_rope_kv_append_chunk_batch(
+            self._h, layer, _ptr(q_inout), _ptr(k_in), _ptr(v_in), _ptr(q_norm_w), _ptr(k_norm_w), qs.size, qs.ctypes.data,
+            pf.ctypes.data, ct.ctypes.data, C.byref(params)))
 
     def rope_inplace(self, q_inout, k_inout, num_tokens: int, params: RopeKvWriteParams, q_norm_w=None,
                      k_norm_w=None) -> None:

@@ -131,6 +131,17 @@ class PagedKvCacheManager:
                                                          C.byref(dst)))
         return blk.value, ((src.value, dst.value) if has.value else None)
 
+    def append_token_slots(self, seq_ids) -> Tuple[np.ndarray, List[Tuple[int, int]]]:
+        """One append_token_slot per sequence, in order, in one native call (the scheduler's per-iteration loop,
+        orca_engine.rs:267-278).  Returns (block per sequence, copy-on-write pairs)."""
+        ids = np.ascontiguousarray(seq_ids, np.uint64)
+        blocks = np.empty(ids.size, np.uint32)
+        pairs = np.empty((max(ids.size, 1), 2), np.uint32)
+        n_cow, done = C.c_size_t(), C.c_size_t()
+        self._check(self._lib.kriya_kv_append_token_slots(self._h, ids.ctypes.data, ids.size, blocks.ctypes.data,
+                                                          pairs.ctypes.data, C.byref(n_cow), C.byref(done)))
+        return blocks, [(int(a), int(b)) for a, b in pairs[: n_cow.value]]
+
     def fork_sequence(self, parent_seq_id: int, child_seq_id: int) -> None:
         self._check(self._lib.kriya_kv_fork_sequence(self._h, parent_seq_id, child_seq_id))
 

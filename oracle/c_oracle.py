@@ -125,6 +125,33 @@ def rope_kv_append(q_inout, k_in, v_in, cache_k, cache_v, indptr, indices, last_
                             C.c_uint32(positions.size), C.byref(params), _p(table), dtype)
 
 
+Q4_GROUP, Q4_BLOCK_BYTES = 32, 20
+
+
+def set_kv_format(q4: bool) -> None:
+    """Cache format of every following append / decode / prefill call of the oracle: False = 16-bit pool, True =
+    Q4KvGroup32 pool.  A Q4 pool is passed as a uint16 VIEW of its bytes (20-byte blocks in [block][token][head][d / 32]
+    order), so that the wrappers' argument handling stays the same."""
+    lib().ko_set_kv_format(C.c_int(1 if q4 else 0))
+
+
+def q4kv_quantize(values: np.ndarray) -> np.ndarray:
+    """f32 values (a multiple of 32 of them, flat order) -> Q4KvGroup32 bytes (20 per group of 32)."""
+    v = np.ascontiguousarray(values, np.float32).ravel()
+    assert v.size % Q4_GROUP == 0
+    out = np.empty(v.size // Q4_GROUP * Q4_BLOCK_BYTES, np.uint8)
+    lib().ko_q4kv_quantize(_p(v), C.c_uint32(v.size // Q4_GROUP), _p(out))
+    return out
+
+
+def q4kv_dequantize(blocks: np.ndarray) -> np.ndarray:
+    b = np.ascontiguousarray(blocks, np.uint8).ravel()
+    assert b.size % Q4_BLOCK_BYTES == 0
+    out = np.empty(b.size // Q4_BLOCK_BYTES * Q4_GROUP, np.float32)
+    lib().ko_q4kv_dequantize(_p(b), C.c_uint32(b.size // Q4_BLOCK_BYTES), _p(out))
+    return out
+
+
 def set_attention_window(window_size: int) -> None:
     """Sliding-window causal mask for every following decode / prefill call of the oracle (0 = plain causal)."""
     lib().ko_set_attention_window(C.c_uint32(window_size))

@@ -176,6 +176,68 @@ KO_EXPORT void ko_rope_table(float* table, uint32_t max_seq_len, uint32_t rotary
     }
 }
 
+/* ---- DType::Q4KvGroup32: the 4-bit KV-cache format ----------------------------- */
+
+/* crates/kriya-core/src/tensor.rs:50-51,77,91: 32 values -> 16 bytes of 4-bit codes + f16 scale + f16 min = 20 bytes
+ * ("FlexGen-style 4-bit KV cache / activation group-32 compression"), switched on by compress_kv_cache_q4
+ * (crates/kriya-core/src/hardware.rs:57,159-165).  The reference declares the format and ships neither a quantiser
+ * nor a kernel for it.  Its arithmetic is restated here from the reference's own 4-bit affine group quantiser, the only
+ * one of that family it implements (quantize_f32_to_q4_group64 / dequantize, crates/kriya-core/src/quantizer.rs:61-127),
+ * with the group size and header type of this format: min and max of the group, range = max(max - min, 1e-8),
+ * scale = range / 15, bias = min, both rounded to the header's storage type (f16 here, bf16 there); the codes are taken
+ * with the ROUNDED scale (floored at 1e-8) and bias, q = clamp(round((v - bias) / scale), 0, 15) with round-half-away
+ * (f32::round); value 2i sits in the low nibble of byte i, value 2i + 1 in the high nibble; a value is restored as
+ * fma(q, scale, bias).  Block layout: bytes 0..15 codes, 16..17 scale, 18..19 min (little endian).
+ * A cache row of D values is D / 32 consecutive blocks; the pool keeps the [block][token][head] order of the 16-bit pool. */
+#define KO_Q4_GROUP 32u
+#define KO_Q4_BLOCK_BYTES 20u
+
+KO_EXPORT void ko_q4kv_quantize(const float* v, uint32_t n_groups, uint8_t* out) {
+    for (uint32_t g = 0; g < n_groups; ++g) {
+        const float* x = v + (size_t)g * KO_Q4_GROUP;
+        uint8_t* b = out + (size_t)g * KO_Q4_BLOCK_BYTES;
+        float mn = INFINITY, mx = -INFINITY;
+        for (uint32_t i = 0; i < KO_Q4_GROUP; ++i) {
+            mn = fminf(mn, x[i]);
+            mx = fmaxf(mx, x[i]);
+        }
+        const float range = fmaxf(mx - mn, 1e-8f);
+        const uint16_t scale16 = f32_to_fp16(range / 15.0f), min16 = f32_to_fp16(mn);
+        const float eff_scale = fmaxf(fp16_to_f32(scale16), 1e-8f), eff_min = fp16_to_f32(min16);
+        for (uint32_t i = 0; i < KO_Q4_GROUP / 2u; ++i) {
+            const float q0 = clampf(roundf((x[2 * i] - eff_min) / eff_scale), 0.0f, 15.0f);
+            const float q1 = clampf(roundf((x[2 * i + 1] - eff_min) / eff_scale), 0.0f, 15.0f);
+            b[i] = (uint8_t)(((uint8_t)q0 & 0x0Fu) | (((uint8_t)q1 & 0x0Fu) << 4));
+        }
+        b[16] = (uint8_t)(scale16 & 0xFFu);
+        b[17] = (uint8_t)(scale16 >> 8);
+        b[18] = (uint8_t)(min16 & 0xFFu);
+        b[19] = (uint8_t)(min16 >> 8);
+    }
+}
+
+static inline float q4kv_value(const uint8_t* pool, size_t elem) {
+    const uint8_t* b = pool + (elem / KO_Q4_GROUP) * KO_Q4_BLOCK_BYTES;
+    const uint32_t i = (uint32_t)(elem % KO_Q4_GROUP);
+    const uint32_t q = (i & 1u) ? (uint32_t)(b[i >> 1] >> 4) : (uint32_t)(b[i >> 1] & 0x0Fu);
+    const float scale = fp16_to_f32((uint16_t)(b[16] | (b[17] << 8))), mn = fp16_to_f32((uint16_t)(b[18] | (b[19] << 8)));
+    return fmaf((float)q, scale, mn);
+}
+
+KO_EXPORT void ko_q4kv_dequantize(const uint8_t* in, uint32_t n_groups, float* out) {
+    for (size_t e = 0; e < (size_t)n_groups * KO_Q4_GROUP; ++e) out[e] = q4kv_value(in, e);
+}
+
+/* Cache format of every following append / decode / prefill call of the oracle: 0 = 16-bit pool (uint16 per element),
+ * 1 = Q4KvGroup32 pool (the cache pointers are then byte arrays of 20-byte blocks in element order). */
+static int g_kv_q4 = 0;
+KO_EXPORT void ko_set_kv_format(int q4) { g_kv_q4 = q4; }
+
+/* One cached element by its index in [block][token][head][d] order. */
+static inline float kv_elem(const uint16_t* pool, size_t elem, int dtype) {
+    return g_kv_q4 ? q4kv_value((const uint8_t*)pool, elem) : load16(pool[elem], dtype);
+}
+
 /* ---- fused QK-norm + RoPE + KV append --------------------------------------- */
 
 /* metal:115-226, one (token, head) at a time in the shader's lane order.
@@ -212,6 +274,7 @@ KO_EXPORT void ko_rope_kv_append(uint16_t* q_inout, const uint16_t* k_in, const 
             float sum_sq = simd_sum32(lane);
             rms_scale = 1.0f / sqrtf(sum_sq / (float)D + p->rms_eps);
         }
+        float k_row[256], v_row[256]; /* the rotated key and the value of this (token, head) before they are stored */
         size_t dst = 0;
         if (!is_q) { /* metal:162-167 */
             int32_t last_ptr = indptr[r + 1] - 1;
@@ -251,11 +314,22 @@ KO_EXPORT void ko_rope_kv_append(uint16_t* q_inout, const uint16_t* k_in, const 
                 qd[d1] = store16(x1, dtype);
             } else {
                 const uint16_t* vs = v_in + ((size_t)r * Hkv + lh) * D;
-                cache_k[dst + d0] = store16(x0, dtype);
-                cache_k[dst + d1] = store16(x1, dtype);
-                cache_v[dst + d0] = vs[d0];
-                cache_v[dst + d1] = vs[d1];
+                if (g_kv_q4) { /* quantised below, from the un-rounded rotated key and from the value as given */
+                    k_row[d0] = x0;
+                    k_row[d1] = x1;
+                    v_row[d0] = load16(vs[d0], dtype);
+                    v_row[d1] = load16(vs[d1], dtype);
+                } else {
+                    cache_k[dst + d0] = store16(x0, dtype);
+                    cache_k[dst + d1] = store16(x1, dtype);
+                    cache_v[dst + d0] = vs[d0];
+                    cache_v[dst + d1] = vs[d1];
+                }
             }
+        }
+        if (!is_q && g_kv_q4) {
+            ko_q4kv_quantize(k_row, D / KO_Q4_GROUP, (uint8_t*)cache_k + dst / KO_Q4_GROUP * KO_Q4_BLOCK_BYTES);
+            ko_q4kv_quantize(v_row, D / KO_Q4_GROUP, (uint8_t*)cache_v + dst / KO_Q4_GROUP * KO_Q4_BLOCK_BYTES);
         }
     }
 }
@@ -313,22 +387,22 @@ static void stream_blocks(const uint16_t* q_row, const uint16_t* cache_k, const 
         const size_t base = ((size_t)phys * page * p->num_kv_heads + kv_head) * D;
         for (uint32_t t = 0; t < valid; ++t) {
             if (lb * page + t < tok_first) continue;
-            const uint16_t* kr = cache_k + base + t * tok_stride;
-            const uint16_t* vr = cache_v + base + t * tok_stride;
+            const size_t kr = base + t * tok_stride; /* element index of the token's K (and V) row */
             float lane[32];
             for (uint32_t l = 0; l < 32; ++l) {
                 const uint32_t d0 = l * W;
                 float dot;
                 if (W == 2u) { /* metal:306 */
-                    dot = fmaf(q[d0], load16(kr[d0], dtype), q[d0 + 1] * load16(kr[d0 + 1], dtype));
+                    dot = fmaf(q[d0], kv_elem(cache_k, kr + d0, dtype), q[d0 + 1] * kv_elem(cache_k, kr + d0 + 1, dtype));
                 } else if (W == 4u) { /* metal:375 */
-                    dot = fmaf(q[d0], load16(kr[d0], dtype),
-                               fmaf(q[d0 + 1], load16(kr[d0 + 1], dtype),
-                                    fmaf(q[d0 + 2], load16(kr[d0 + 2], dtype), q[d0 + 3] * load16(kr[d0 + 3], dtype))));
+                    dot = fmaf(q[d0], kv_elem(cache_k, kr + d0, dtype),
+                               fmaf(q[d0 + 1], kv_elem(cache_k, kr + d0 + 1, dtype),
+                                    fmaf(q[d0 + 2], kv_elem(cache_k, kr + d0 + 2, dtype),
+                                         q[d0 + 3] * kv_elem(cache_k, kr + d0 + 3, dtype))));
                 } else { /* metal:441-448 */
                     dot = 0.0f;
                     for (uint32_t i = 0; i < 8u; ++i)
-                        if (d0 + i < D) dot = fmaf(q[d0 + i], load16(kr[d0 + i], dtype), dot);
+                        if (d0 + i < D) dot = fmaf(q[d0 + i], kv_elem(cache_k, kr + d0 + i, dtype), dot);
                 }
                 lane[l] = dot;
             }
@@ -338,7 +412,7 @@ static void stream_blocks(const uint16_t* q_row, const uint16_t* cache_k, const 
             float alpha = expf(clampf(st->m - m_new, -80.0f, 0.0f));
             float beta = expf(clampf(score - m_new, -80.0f, 0.0f));
             st->l = fmaf(st->l, alpha, beta);
-            for (uint32_t d = 0; d < D; ++d) st->o[d] = fmaf(st->o[d], alpha, beta * load16(vr[d], dtype));
+            for (uint32_t d = 0; d < D; ++d) st->o[d] = fmaf(st->o[d], alpha, beta * kv_elem(cache_v, kr + d, dtype));
             st->m = m_new;
         }
     }

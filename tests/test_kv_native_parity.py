@@ -149,3 +149,28 @@ def test_prefix_sharing_config_refcounts_and_cow_pairs():
         assert len({p[0] for p in pairs}) == 1 and len({p[1] for p in pairs}) == 4
         blk, cow = m.append_token_slot(100)  # parent's tail is private again after the children left it
         assert cow is None
+
+
+def test_batched_append_equals_one_call_per_sequence():
+    """kriya_kv_append_token_slots is the scheduler's loop in one native call: same blocks, same copy-on-write pairs,
+    same manager state as append_token_slot per sequence (forked children with a shared partial tail included)."""
+    from kriya_rt_b200.kv import PagedKvCacheManager
+
+    def build():
+        m = PagedKvCacheManager(64, 0, 16)
+        m.allocate_sequence(1, list(range(40)))
+        m.allocate_sequence(2, list(range(100, 132)))
+        m.fork_sequence(1, 3)
+        m.fork_sequence(1, 4)
+        return m
+
+    a, b = build(), build()
+    ids = [3, 2, 4, 1]
+    for _ in range(20):
+        one = [a.append_token_slot(s) for s in ids]
+        blocks, pairs = b.append_token_slots(ids)
+        assert [blk for blk, _ in one] == list(blocks)
+        assert [cow for _, cow in one if cow is not None] == pairs
+        assert a.gpu_allocator.num_free_blocks() == b.gpu_allocator.num_free_blocks()
+    for s in ids:
+        assert a.sequence_table(s) == b.sequence_table(s)
