@@ -323,7 +323,7 @@ def run_gpu_arm(args):
     device_pass(1, min(K, 3), Wu)  # module load, first-launch set-up, clocks up
     sampler.mark_start()
     repeats_ms, gpu_launches = [], 0
-    while sum(repeats_ms) < TIMED_DEVICE_S * 1e3 and len(repeats_ms) < MAX_REPEATS:
+    while sum(repeats_ms) < args.min_device_s * 1e3 and len(repeats_ms) < MAX_REPEATS:
         ms, n_launch = device_pass(1, K, Wu)
         if dist is not None:  # every rank must agree on the repeat count: the slowest rank's time decides
             t_rep = torch.tensor([ms], device="cuda", dtype=torch.float64)
@@ -362,7 +362,7 @@ def run_gpu_arm(args):
     qh.copy_(q.cpu()); kh.copy_(k.cpu()); vh.copy_(v.cpu())
     plan_bytes = 0
     e2e_repeats = []
-    while sum(e2e_repeats) < TIMED_DEVICE_S and len(e2e_repeats) < MAX_REPEATS:
+    while sum(e2e_repeats) < args.min_device_s and len(e2e_repeats) < MAX_REPEATS:
         mgr2 = fresh_manager()
         for t in range(Wu):
             plan, pos = step_plan(mgr2, t)
@@ -425,7 +425,7 @@ def run_gpu_arm(args):
     ex.close()
     del q, k, v, out
     torch.cuda.empty_cache()
-    config5 = run_config5(args, rank, local_rank, world, dist, peak)
+    config5 = None if args.no_config5 else run_config5(args, rank, local_rank, world, dist, peak)
 
     if rank == 0:
         line = {
@@ -946,6 +946,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--min-device-s", type=float, default=TIMED_DEVICE_S,
+                    help="the timed region is repeated until it adds up to this much device time (0: once; for runs under a profiler)")
+    ap.add_argument("--no-config5", action="store_true", help="skip the config 5 object (it fills the whole pool)")
     ap.add_argument("--case-long-seqs", type=int, default=256, help="sequences in the decode_long kernel case")
     ap.add_argument("--case-seqs", type=int, default=8, help="prompts in the prefill_batch kernel case")
     ap.add_argument("--kernel-case", default=None, choices=["decode", "decode_fused", "decode_long", "prefill", "prefill_batch", "append", "copy", "kvsplit", "tree_verify"],

@@ -50,6 +50,8 @@ void destroy(kriya_cuda_ctx* c) {
     cudaFree(c->d_status);
     cudaFree(c->d_act);
     cudaFree(c->d_pairs);
+    cudaFree(c->pf_part_o);
+    cudaFree(c->pf_part_ml);
     cudaFree(c->d_tree_state);
     cudaFree(c->d_tree_mask);
     cudaFree(c->d_step);
@@ -466,6 +468,43 @@ int32_t launch_decode(kriya_cuda_ctx* c, uint32_t layer, const void* q, void* ou
     return KRIYA_CUDA_OK;
 }
 
+// Into how many pieces (at most) the query tiles of a prefill launch are cut along the KV axis.  Only launches that do
+// not fill the machine are cut, and only so far that the pieces still run as one wave: a tile of L 128-key tiles is cut
+// into min(s, L / 2) pieces, every piece runs on `hp` CTAs (one per head pair), and the launch then takes as long as its
+// longest CTA.  Costs in units of one KV tile (about 1.7 us), from measurements at the Qwen2.5-1.5B shape: a CTA costs
+// its KV tiles plus 1.5 for its start-up (query tile, first K/V round trip) and its output; a piece costs 3 instead (its
+// state is 128 KB of fp32 stores), and a launch with pieces pays about 4 more for the merge kernel behind it.  1 (no
+// cut) stays unless a cut is at least 10 % shorter.  (Two pieces per tile at 8 prompts, 1.3 waves, measured 72 against
+// 50 us per launch: cutting does not pay once the machine is full.)
+uint32_t choose_prefill_split(const KriyaPrefillTile* tiles, uint32_t n, uint32_t hp, uint32_t sms, uint32_t max_cta_slots,
+                              uint32_t max_records) {
+    if (n == 0 || uint64_t(n) * hp >= sms) return 1u;
+    uint32_t longest = 0;
+    for (uint32_t i = 0; i < n; ++i) longest = std::max(longest, (tiles[i].pos0 + tiles[i].rows + 127u) / 128u);
+    uint32_t best_s = 1u;
+    float best = float(longest) + 1.5f;
+    for (uint32_t s : {2u, 3u, 4u, 6u, 8u}) {
+        uint64_t ctas = 0, records = 0;
+        uint32_t longest_piece = 0;
+        bool any = false;
+        for (uint32_t i = 0; i < n; ++i) {
+            const uint32_t L = (tiles[i].pos0 + tiles[i].rows + 127u) / 128u;
+            const uint32_t parts = std::max(1u, std::min(s, L / 2u));
+            any = any || parts > 1u;
+            ctas += uint64_t(parts) * hp;
+            records += parts + 1u;
+            longest_piece = std::max(longest_piece, (L + parts - 1u) / parts);
+        }
+        if (!any || ctas > sms || ctas > max_cta_slots || records > max_records) continue;
+        const float t = float(longest_piece) + 3.0f + 4.0f;
+        if (t < best * 0.90f) {
+            best = t;
+            best_s = s;
+        }
+    }
+    return best_s;
+}
+
 }  // namespace
 
 extern "C" {
@@ -663,6 +702,14 @@ int32_t kriya_cuda_ctx_create(const kriya_cuda_config* cfg_in, kriya_cuda_ctx** 
     CREATE_TRY(cudaMalloc(&c->d_act, c->act_bytes));
     CREATE_TRY(cudaMallocHost(&c->h_act, c->act_bytes));
     CREATE_TRY(cudaMalloc(&c->d_pairs, size_t(c->cap_pairs) * 3 * sizeof(uint32_t)));
+    if (c->tmaps_ok && kriya_prefill_supported(cfg.head_dim, cfg.num_q_heads / cfg.num_kv_heads, cfg.block_size_tokens, cfg.dtype)) {
+        const char* e = getenv("KRIYA_PREFILL_SPLIT");
+        c->pf_split_enable = !(e && atoi(e) == 0);
+        c->pf_split_force = (e && atoi(e) >= 2) ? uint32_t(std::min(atoi(e), 8)) : 0u;  // for tests: that many pieces whatever the policy says
+        c->pf_part_slots = 4u * uint32_t(c->sm_count);
+        CREATE_TRY(cudaMalloc(&c->pf_part_o, size_t(c->pf_part_slots) * 2 * cfg.head_dim * 128 * sizeof(float)));
+        CREATE_TRY(cudaMalloc(&c->pf_part_ml, size_t(c->pf_part_slots) * 2 * 128 * 2 * sizeof(float)));
+    }
     CREATE_TRY(cudaMalloc(&c->d_tree_state, size_t(kTreeMaxNodes) * c->cfg.num_q_heads * (c->cfg.head_dim + 2) * sizeof(float)));
     CREATE_TRY(cudaMalloc(&c->d_tree_mask, size_t(kTreeMaxNodes) * kTreeMaxNodes));
     CREATE_TRY(cudaMallocHost(&c->h_pairs, size_t(c->cap_pairs) * 3 * sizeof(uint32_t)));
@@ -1186,13 +1233,52 @@ int32_t kriya_cuda_paged_gqa_prefill_batch(kriya_cuda_ctx* c, uint32_t layer, co
         for (uint32_t t0 = 0; t0 < count[r]; t0 += 128u) {
             if (n >= cap_tiles) return c->fail(KRIYA_CUDA_INVALID_INPUT, "more query tiles than the context holds");
             tiles[n++] = KriyaPrefillTile{uint32_t(indptr[r]), q_start[r] + t0, std::min(128u, count[r] - t0), prefix[r] + t0,
-                                          uint32_t(end), {0u, 0u, 0u}};
+                                          uint32_t(end), 0u, 0u, UINT32_MAX};
         }
     }
-    std::stable_sort(tiles, tiles + n, [](const KriyaPrefillTile& x, const KriyaPrefillTile& y) {
-        return (x.pos0 + x.rows) > (y.pos0 + y.rows);
-    });
-    KRIYA_CUDA_TRY(c, cudaMemcpyAsync(c->d_pairs, tiles, size_t(n) * sizeof(KriyaPrefillTile), cudaMemcpyHostToDevice, c->stream));
+    // A launch with few tiles (one request's chunk is 24 CTAs at the Qwen2.5-1.5B shape) is cut along the KV axis so that
+    // it fills the machine; the pieces of a tile leave their states in scratch and a merge kernel combines them.
+    const uint32_t group = c->cfg.num_q_heads / c->cfg.num_kv_heads;
+    const uint32_t hp_count = c->cfg.num_kv_heads * ((group + 1u) / 2u);
+    auto kv_tiles_of = [](const KriyaPrefillTile& t) { return (t.pos0 + t.rows + 127u) / 128u; };
+    uint32_t n_merge = 0;
+    uint32_t split = 1u;
+    if (c->pf_split_enable && c->attention_window == 0u && c->pf_part_o != nullptr) {
+        split = choose_prefill_split(tiles, n, hp_count, uint32_t(c->sm_count), c->pf_part_slots, cap_tiles);
+        if (c->pf_split_force != 0u && uint64_t(n) * c->pf_split_force * hp_count <= c->pf_part_slots &&
+            uint64_t(n) * (c->pf_split_force + 1u) <= cap_tiles)
+            split = c->pf_split_force;
+    }
+    if (split > 1u) {
+        std::vector<KriyaPrefillTile> whole(tiles, tiles + n);
+        std::vector<KriyaPrefillMerge> merges;
+        uint32_t m = 0, slot = 0;
+        for (const KriyaPrefillTile& t : whole) {
+            const uint32_t L = kv_tiles_of(t), parts = std::max(1u, std::min(split, L / 2u));
+            if (parts == 1u) {
+                tiles[m++] = t;
+                continue;
+            }
+            merges.push_back(KriyaPrefillMerge{t.q_row0, t.rows, slot, parts});
+            uint32_t t0 = 0;
+            for (uint32_t pc = 0; pc < parts; ++pc) {
+                const uint32_t len = L / parts + (pc < L % parts ? 1u : 0u);
+                KriyaPrefillTile piece = t;
+                piece.kv_t0 = t0;
+                piece.kv_t1 = t0 + len;
+                piece.slot = slot++;
+                tiles[m++] = piece;
+                t0 += len;
+            }
+        }
+        n = m;
+        n_merge = uint32_t(merges.size());
+        memcpy(tiles + n, merges.data(), merges.size() * sizeof(KriyaPrefillMerge));
+    }
+    auto piece_len = [&](const KriyaPrefillTile& t) { return t.kv_t1 != 0u ? t.kv_t1 - t.kv_t0 : kv_tiles_of(t); };
+    std::stable_sort(tiles, tiles + n, [&](const KriyaPrefillTile& x, const KriyaPrefillTile& y) { return piece_len(x) > piece_len(y); });
+    KRIYA_CUDA_TRY(c, cudaMemcpyAsync(c->d_pairs, tiles, size_t(n) * sizeof(KriyaPrefillTile) + size_t(n_merge) * sizeof(KriyaPrefillMerge),
+                                      cudaMemcpyHostToDevice, c->stream));
     KRIYA_CUDA_TRY(c, cudaEventRecord(c->h_pairs_free, c->stream));
     KriyaPrefillArgs a{};
     a.q = q;
@@ -1213,9 +1299,13 @@ int32_t kriya_cuda_paged_gqa_prefill_batch(kriya_cuda_ctx* c, uint32_t layer, co
     a.window = c->attention_window;
     a.sm_scale = p->sm_scale;
     a.logit_softcap = p->logit_softcap;
+    a.part_o = c->pf_part_o;
+    a.part_ml = c->pf_part_ml;
+    a.merge_items = reinterpret_cast<const KriyaPrefillMerge*>(reinterpret_cast<const KriyaPrefillTile*>(c->d_pairs) + n);
+    a.n_merge = n_merge;
     KRIYA_CUDA_TRY(c, kriya_launch_prefill(a, c->cfg.head_dim, c->cfg.block_size_tokens, c->cfg.dtype, c->max_smem_optin,
                                            c->stream));
-    c->launches += 1;
+    c->launches += n_merge ? 2 : 1;
     return KRIYA_CUDA_OK;
 }
 

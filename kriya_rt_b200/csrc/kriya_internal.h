@@ -69,6 +69,13 @@ struct kriya_cuda_ctx {
     int tc_force = 0;                            // KRIYA_TC_VARIANT: 128, 64 or 2 (whole pages)
     uint32_t tc64_min_tiles = 96;                // 128-token tiles per SM from which the 64-token-tile build is used
     int max_smem_optin = 0;
+    // prefill launches with few query tiles are cut along the KV axis (KRIYA_PREFILL_SPLIT=0 switches that off, 2..8 forces that many pieces): states of
+    // the pieces, one slot per (piece, head pair CTA)
+    float* pf_part_o = nullptr;
+    float* pf_part_ml = nullptr;
+    uint32_t pf_part_slots = 0;
+    bool pf_split_enable = true;
+    uint32_t pf_split_force = 0;
 
     // KV pools, all layers: layer l at l * layer_stride_bytes
     uint8_t* pool_k = nullptr;
@@ -307,10 +314,22 @@ struct KriyaPrefillTile {
     uint32_t rows;     // 1..128
     uint32_t pos0;     // absolute position of the tile's first query (prefix + offset inside the chunk)
     uint32_t seq_end;  // tokens of the sequence present in the cache (prefix + chunk length)
-    uint32_t _pad[3];
+    // A tile with few companions is cut along the KV axis into pieces (one record each) so that the launch fills the
+    // machine: the piece covers the 128-key tiles kv_t0 .. kv_t1 - 1 (kv_t1 = 0: to the causal end) and, when `slot` is
+    // not UINT32_MAX, leaves its un-normalised state in scratch slot `slot` for prefill_merge_kernel instead of rows of out.
+    uint32_t kv_t0;
+    uint32_t kv_t1;
+    uint32_t slot;
 };
 static_assert(sizeof(KriyaPrefillTile) == 32, "tile record is 32 bytes");
 
+// One query tile whose pieces prefill_merge_kernel combines: pieces slot0 .. slot0 + n_parts - 1.
+struct KriyaPrefillMerge {
+    uint32_t q_row0;
+    uint32_t rows;
+    uint32_t slot0;
+    uint32_t n_parts;
+};
 struct KriyaPrefillArgs {
     const void* q;        // [T][Hq][D]
     const void* cache_k;  // layer base
@@ -330,6 +349,10 @@ struct KriyaPrefillArgs {
     uint32_t window;      // sliding-window size in tokens, 0 = plain causal
     float sm_scale;
     float logit_softcap;
+    float* part_o;        // piece states: per (slot, head pair CTA) [2 heads][D / 4][128 rows] float4, un-normalised
+    float* part_ml;       // and [2 heads][128 rows][2]: exponent reference (log2 units) and sum
+    const KriyaPrefillMerge* merge_items;  // query tiles that were cut (device), n_merge of them
+    uint32_t n_merge;
 };
 // Tree verification: attention of every draft-tree node over its ancestors in the tree (in-flight K/V, `mask`), started
 // from the state (m, l, o) of the node's attention over the cached prefix.

@@ -116,8 +116,13 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
     // earliest window start of the tile is row 0's, so KV tiles in front of it are skipped altogether: the loops below
     // count j = 0 .. n_tiles over the tiles tile0 + j.
     const uint32_t window = a.window;
-    const uint32_t tile0 = (window != 0u && qt.pos0 + 1u > window) ? (qt.pos0 + 1u - window) / uint32_t(kKvTile) : 0u;
-    const uint32_t n_tiles = (kv_limit + kKvTile - 1) / kKvTile - tile0;
+    const uint32_t wtile0 = (window != 0u && qt.pos0 + 1u > window) ? (qt.pos0 + 1u - window) / uint32_t(kKvTile) : 0u;
+    // a piece of a tile that was cut along the KV axis covers the KV tiles kv_t0 .. kv_t1 - 1 only
+    const uint32_t tile_end = (kv_limit + kKvTile - 1) / kKvTile;
+    const uint32_t tile0 = max(wtile0, qt.kv_t0);
+    const uint32_t tile1 = qt.kv_t1 != 0u ? min(qt.kv_t1, tile_end) : tile_end;
+    const uint32_t n_tiles = tile1 > tile0 ? tile1 - tile0 : 0u;
+    const bool partial = qt.slot != UINT32_MAX;
     const uint32_t seq_end = qt.seq_end;  // tokens of the sequence that exist in the cache
 
     // ---- setup -------------------------------------------------------------------------------------------
@@ -399,7 +404,25 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
         }
         if (ok && n_tiles > 0) {
             ok = warp_wait(&pv_done[x], 0u);
-            if (ok) {
+            if (ok && partial) {
+                // A piece of a tile cut along the KV axis: its state (exponent reference, sum, un-normalised accumulator)
+                // goes to the piece's scratch slot, accumulator as [d / 4][row] float4 so that a warp's stores are contiguous.
+                tc_fence_after();
+                const uint32_t hp_count = gridDim.x / pp.q_tiles;
+                const size_t cta_slot = size_t(qt.slot) * hp_count + hp;
+                float4* po = reinterpret_cast<float4*>(a.part_o) + (cta_slot * 2u + x) * size_t(D / 4) * kQTile;
+#pragma unroll 1
+                for (int c = 0; c < D / 32; ++c) {
+                    uint32_t r[32];
+                    tmem_ld32(o_addr + c * 32, r);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int q4 = 0; q4 < 8; ++q4)
+                        po[size_t(c * 8 + q4) * kQTile + row] = make_float4(__uint_as_float(r[q4 * 4]), __uint_as_float(r[q4 * 4 + 1]),
+                                                                            __uint_as_float(r[q4 * 4 + 2]), __uint_as_float(r[q4 * 4 + 3]));
+                }
+                reinterpret_cast<float2*>(a.part_ml)[(cta_slot * 2u + x) * kQTile + row] = make_float2(m_used, l_run);
+            } else if (ok) {
                 tc_fence_after();
                 const float inv_l = 1.0f / fmaxf(l_run, 1e-12f);
                 // A full tile goes through shared memory in the layout of the query tile it replaces (every S MMA is
@@ -456,6 +479,58 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
     }
 }
 
+// Combines the pieces of the query tiles that were cut along the KV axis: block = (tile, head pair, eight (head, row)
+// jobs), a warp per job, a lane per four output dimensions.  Everything a job reads is asked for before any of it is
+// used (at most kPfMaxParts pieces): the kernel is a few dependent memory round trips long, so it needs many warps and
+// no chains.
+constexpr uint32_t kPfMaxParts = 8;
+template <int D, typename T>
+__global__ void __launch_bounds__(256) prefill_merge_kernel(KriyaPrefillArgs a, const KriyaPrefillMerge* items, uint32_t pairs) {
+    // launched with programmatic stream serialisation: the blocks are resident before the attention kernel has finished
+    // and wait here for its completion (and with it for the pieces' states)
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const KriyaPrefillMerge it = items[blockIdx.x];
+    const uint32_t hp = blockIdx.y, hp_count = gridDim.y;
+    const uint32_t group = a.num_q_heads / a.num_kv_heads;
+    const uint32_t kv_head = hp / pairs, pair = hp % pairs;
+    const uint32_t head0 = kv_head * group + pair * 2u;
+    const uint32_t n_heads = min(2u, group - pair * 2u);
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const uint32_t job = blockIdx.z * 8u + warp;
+    if (job >= n_heads * it.rows) return;
+    const uint32_t x = job / it.rows, row = job % it.rows;
+    const float4* po = reinterpret_cast<const float4*>(a.part_o);
+    const float2* pml = reinterpret_cast<const float2*>(a.part_ml);
+    const bool active = lane < uint32_t(D / 4);
+    float2 ml[kPfMaxParts];
+    float4 v[kPfMaxParts];
+#pragma unroll
+    for (uint32_t p = 0; p < kPfMaxParts; ++p) {
+        const size_t cs = (size_t(it.slot0 + min(p, it.n_parts - 1u)) * hp_count + hp) * 2u + x;
+        ml[p] = pml[cs * kQTile + row];
+        v[p] = active ? po[(cs * uint32_t(D / 4) + lane) * kQTile + row] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    }
+    float m = -INFINITY;
+#pragma unroll
+    for (uint32_t p = 0; p < kPfMaxParts; ++p) m = (p < it.n_parts) ? fmaxf(m, ml[p].x) : m;
+    float l = 0.0f;
+    float4 o = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+    for (uint32_t p = 0; p < kPfMaxParts; ++p) {
+        const float w = (p < it.n_parts && ml[p].x != -INFINITY) ? exp2f(ml[p].x - m) : 0.0f;
+        l = fmaf(w, ml[p].y, l);
+        o.x = fmaf(w, v[p].x, o.x);
+        o.y = fmaf(w, v[p].y, o.y);
+        o.z = fmaf(w, v[p].z, o.z);
+        o.w = fmaf(w, v[p].w, o.w);
+    }
+    if (active) {
+        const float inv_l = 1.0f / fmaxf(l, 1e-12f);
+        uint16_t* og = reinterpret_cast<uint16_t*>(a.out) + (size_t(it.q_row0 + row) * a.num_q_heads + head0 + x) * D + lane * 4u;
+        *reinterpret_cast<uint2*>(og) = make_uint2(T::pack2(o.x * inv_l, o.y * inv_l), T::pack2(o.z * inv_l, o.w * inv_l));
+    }
+}
+
 template <int D, typename T>
 cudaError_t launch_prefill_t(const KriyaPrefillArgs& a, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mq,
                              const CUtensorMap& mo, int max_smem_optin, cudaStream_t s) {
@@ -471,6 +546,19 @@ cudaError_t launch_prefill_t(const KriyaPrefillArgs& a, const CUtensorMap& mk, c
     const uint32_t group = a.num_q_heads / a.num_kv_heads;
     pp.pairs = (group + 1u) / 2u;
     kern<<<pp.q_tiles * pp.pairs * a.num_kv_heads, kPrefillThreads, smem, s>>>(mk, mv, mq, mo, pp);
+    if (a.n_merge != 0u) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(a.n_merge, pp.pairs * a.num_kv_heads, 2 * kQTile / 8);
+        cfg.blockDim = dim3(256);
+        cfg.stream = s;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        e = cudaLaunchKernelEx(&cfg, prefill_merge_kernel<D, T>, a, a.merge_items, pp.pairs);
+        if (e != cudaSuccess) return e;
+    }
     return cudaGetLastError();
 }
 

@@ -242,3 +242,65 @@ def test_config4_full_size_last_chunk_of_eight_prompts():
                 assert np.abs(got[starts[s]:starts[s] + chunk] - ref).max() <= 1e-2, s
         ex.close()
     assert np.array_equal(outs[0], outs[1])
+
+
+@pytest.mark.parametrize("dtype,D,Hq,Hkv", [(W.BF16, 128, 12, 2), (W.FP16, 64, 9, 3)])
+def test_few_tiles_are_cut_along_the_kv_axis_and_merged(dtype, D, Hq, Hkv, monkeypatch):
+    """One request's chunk is a handful of CTAs: the launch cuts every query tile's keys into pieces, the pieces leave
+    their states in scratch and a second kernel merges them.  Same result as the un-cut launch (KRIYA_PREFILL_SPLIT=0)
+    within rounding, and all within the bar of the oracle; a cut launch counts two kernels.  Mode "1" is the library's own
+    policy (it cuts the second chunk, whose four tiles have 10 to 12 KV tiles each), mode "3" forces three pieces."""
+    shape = W.AttnShape("cut", Hq, Hkv, D, dtype, rope_theta=1e6)
+    total, prefix_chunks = 1500, (0, 1100)  # prompt in two chunks: 1100 + 400 (ragged last query tile, prefix > 0)
+    mgr = PagedKvCacheManager(256, 0, 16)
+    mgr.allocate_sequence(1, list(range(37)))
+    mgr.allocate_sequence(2, list(range(5000, 5000 + total)))
+    table, _ = mgr.sequence_table(2)
+    rng = np.random.default_rng(91)
+    q = W.normal16(rng, (total, Hq, D), dtype); k = W.normal16(rng, (total, Hkv, D), dtype); v = W.normal16(rng, (total, Hkv, D), dtype)
+    results = {}
+    for mode in ("1", "0", "3"):
+        monkeypatch.setenv("KRIYA_PREFILL_SPLIT", mode)
+        ex = make_executor(shape, 256, max_query_tokens=1100)
+        ck = np.full((256, 16, Hkv, D), 0x7FC1 if dtype == W.BF16 else 0x7E01, np.uint16)
+        fill_cache(ex, 0, ck, ck)
+        rp = ex.rope_params()
+        outs, launches = [], []
+        for start, n in ((0, 1100), (1100, 400)):
+            gp = ex.gqa_params(max_query_tokens=n)
+            dq, dk, dv = dev16(q[start:start + n]), dev16(k[start:start + n]), dev16(v[start:start + n])
+            out = torch.zeros_like(dq)
+            torch.cuda.synchronize()
+            ex.upload_schedule_plan(mgr.build_prefix_schedule_plan(2, start + n, 8))
+            ex.rope_kv_append_chunk(0, dq, dk, dv, start, n, rp)
+            before = ex.launch_count
+            ex.paged_gqa_prefill(0, dq, out, start, n, gp)
+            ex.sync()
+            launches.append(ex.launch_count - before)
+            outs.append(W.from_storage(host16(out), dtype))
+        results[mode] = (np.concatenate(outs), launches)
+        if mode == "1":
+            gk, gv = read_cache(ex, 0)
+        ex.close()
+    assert results["1"][1] == [1, 2] and results["0"][1] == [1, 1] and results["3"][1] == [2, 2]
+    # oracle over the final cache (the appended K/V are bit-exact, checked elsewhere)
+    tab = O.rope_table(4096, D, shape.rope_theta)
+    ok = np.full((256, 16, Hkv, D), 0x7FC1 if dtype == W.BF16 else 0x7E01, np.uint16); ov = ok.copy()
+    refs = []
+    exo = make_executor(shape, 256, max_query_tokens=1100)
+    for start, n in ((0, 1100), (1100, 400)):
+        rows = mgr.build_parallel_prefill_layout(2, start, n, 8)
+        oq = q[start:start + n].copy()
+        O.rope_kv_append(oq, k[start:start + n], v[start:start + n], ok, ov, rows.page_indptr, rows.page_indices,
+                         rows.last_page_len, np.arange(start, start + n), oracle_rope(exo.rope_params()), dtype, table=tab)
+        _, of = O.prefill_causal(oq, ok, ov, np.asarray(table, np.int32), start, oracle_gqa(exo), dtype)
+        refs.append(of)
+    exo.close()
+    ref = np.concatenate(refs)
+    assert np.array_equal(gk, ok) and np.array_equal(gv, ov)
+    for mode in ("1", "0", "3"):
+        got = results[mode][0]
+        assert np.isfinite(got).all()
+        assert np.abs(got - ref).max() <= TOL[dtype], mode
+    assert np.abs(results["1"][0] - results["0"][0]).max() <= TOL[dtype]
+    assert np.abs(results["3"][0] - results["0"][0]).max() <= TOL[dtype]
