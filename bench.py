@@ -323,7 +323,7 @@ def run_gpu_arm(args):
     device_pass(1, min(K, 3), Wu)  # module load, first-launch set-up, clocks up
     sampler.mark_start()
     repeats_ms, gpu_launches = [], 0
-    while sum(repeats_ms) < args.min_device_s * 1e3 and len(repeats_ms) < MAX_REPEATS:
+    while not repeats_ms or (sum(repeats_ms) < args.min_device_s * 1e3 and len(repeats_ms) < MAX_REPEATS):
         ms, n_launch = device_pass(1, K, Wu)
         if dist is not None:  # every rank must agree on the repeat count: the slowest rank's time decides
             t_rep = torch.tensor([ms], device="cuda", dtype=torch.float64)
@@ -362,7 +362,7 @@ def run_gpu_arm(args):
     qh.copy_(q.cpu()); kh.copy_(k.cpu()); vh.copy_(v.cpu())
     plan_bytes = 0
     e2e_repeats = []
-    while sum(e2e_repeats) < args.min_device_s and len(e2e_repeats) < MAX_REPEATS:
+    while not e2e_repeats or (sum(e2e_repeats) < args.min_device_s and len(e2e_repeats) < MAX_REPEATS):
         mgr2 = fresh_manager()
         for t in range(Wu):
             plan, pos = step_plan(mgr2, t)
@@ -688,6 +688,75 @@ def run_kernel_case(args):
                           "kv_bytes_per_launch": kv_bytes, "attended_tokens": batch.attended_tokens,
                           "kv_gbs": kv_bytes / (ms / max(n, 1) * 1e-3) / 1e9 if case != "append" and n else None}))
         ex.close()
+    elif case == "decode_ctx":
+        # batch 32, every context the same length (--case-ctx), 8 layers with pools of their own (every layer cold), the
+        # fused append + decode step in the stream; the three dependency modes of the step beside one another
+        sh, layers, ctxlen = SHAPE, 8, args.case_ctx
+        nblk = BATCH * ((ctxlen + 15) // 16) + 64
+        batch = W.make_decode_batch(sh, np.full(BATCH, ctxlen - 1), nblk, seed=2003)
+        ex = CudaExecutor(num_layers=layers, num_kv_blocks=nblk, block_size_tokens=16, num_q_heads=16, num_kv_heads=2,
+                          head_dim=128, rope_theta=sh.rope_theta, rope_max_seq_len=max(8192, ctxlen + 64), max_page_indices=nblk,
+                          max_batch_rows=BATCH)
+        fill(ex, layers)
+        q, k, v = rnd(layers, BATCH, 16, 128), rnd(layers, BATCH, 2, 128), rnd(layers, BATCH, 2, 128)
+        out = torch.zeros_like(q)
+        torch.cuda.synchronize()
+        ex.upload_schedule_plan(batch, batch.positions)
+        rp, gp = ex.rope_params(), ex.gqa_params()
+        stream = torch.cuda.ExternalStream(ex.stream_ptr)
+        kv_bytes = batch.kv_bytes_per_layer
+        peak = float(measured_peaks()[0]["hbm_gbs"])
+        res = {"case": case, "ctx": ctxlen, "batch": BATCH, "layers": layers, "kv_bytes_per_launch": kv_bytes, "peak_gbs": peak}
+        for name, mode in (("in_stream", 1), ("dependent", 5), ("serial", 3), ("plain", 7)):
+            ex.set_fused_append(mode)
+            for _ in range(3):
+                ex.decode_step(q, k, v, out, BATCH, rp, gp)
+            ex.sync()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(reps):
+                ex.decode_step(q, k, v, out, BATCH, rp, gp)
+            e1.record(stream)
+            ex.sync()
+            us = e0.elapsed_time(e1) / (reps * layers) * 1e3
+            res[name] = {"us_per_launch": us, "kv_gbs": kv_bytes / (us * 1e-6) / 1e9, "frac_of_peak": kv_bytes / (us * 1e-6) / 1e9 / peak}
+        print(json.dumps(res))
+        ex.close()
+    elif case == "decode_q4":
+        # the same rows over a Q4KvGroup32 cache (CUDA-core decode kernel): GB/s on the STORED bytes, 20 per 32 values
+        from kriya_rt_b200.executor import KV_Q4_GROUP32
+        sh, ctxlen = SHAPE, args.case_ctx
+        nblk = BATCH * ((ctxlen + 15) // 16) + 64
+        batch = W.make_decode_batch(sh, np.full(BATCH, ctxlen - 1), nblk, seed=2004)
+        res = {"case": case, "ctx": ctxlen, "batch": BATCH}
+        for name, fmt in (("q4", KV_Q4_GROUP32), ("bf16_same_kernel", 0)):
+            ex = CudaExecutor(num_layers=1, num_kv_blocks=nblk, block_size_tokens=16, num_q_heads=16, num_kv_heads=2, head_dim=128,
+                              rope_theta=sh.rope_theta, max_page_indices=nblk, max_batch_rows=BATCH, kv_format=fmt)
+            ex.set_decode_path(1)
+            for view in ex.layer_cache_views(0):
+                if fmt:  # valid groups: any codes, scale 2^-6 (f16 0x2400), min -0.1 (f16 0xAE66)
+                    grp = torch.randint(-32768, 32767, (view.numel() // 10, 10), device="cuda", dtype=torch.int16)
+                    grp[:, 8] = 0x2400
+                    grp[:, 9] = -0x519A
+                    view.view(-1).copy_(grp.view(-1))
+                else:
+                    view.view(-1).copy_(torch.randn(view.numel(), device="cuda", generator=gen).to(torch.bfloat16).view(torch.int16))
+            q = rnd(BATCH, 16, 128)
+            out = torch.zeros_like(q)
+            torch.cuda.synchronize()
+            ex.upload_schedule_plan(batch, batch.positions)
+            gp = ex.gqa_params()
+            for _ in range(2):
+                ex.paged_gqa_decode(0, q, out, gp)
+            ex.timing_enable(True)
+            for _ in range(reps):
+                ex.paged_gqa_decode(0, q, out, gp)
+            n, ms = ex.timing_read(0)
+            stored = batch.attended_tokens * 2 * 2 * (128 // 32 * 20 if fmt else 128 * 2)
+            res[name] = {"us_per_launch": ms / max(n, 1) * 1e3, "stored_kv_bytes": stored,
+                         "stored_gbs": stored / (ms / max(n, 1) * 1e-3) / 1e9, "finite": bool(torch.isfinite(out.view(torch.bfloat16).float()).all())}
+            ex.close()
+        print(json.dumps(res))
     elif case == "kvsplit":
         # one 131072-token sequence (Qwen2.5-3B shape) cut along the KV axis over WORLD_SIZE GPUs: per layer, the
         # partial-state decode over this rank's block range, one all-gather of (m, l, o), the merge
@@ -951,7 +1020,8 @@ def main():
     ap.add_argument("--no-config5", action="store_true", help="skip the config 5 object (it fills the whole pool)")
     ap.add_argument("--case-long-seqs", type=int, default=256, help="sequences in the decode_long kernel case")
     ap.add_argument("--case-seqs", type=int, default=8, help="prompts in the prefill_batch kernel case")
-    ap.add_argument("--kernel-case", default=None, choices=["decode", "decode_fused", "decode_long", "prefill", "prefill_batch", "append", "copy", "kvsplit", "tree_verify"],
+    ap.add_argument("--case-ctx", type=int, default=4096, help="context length of every row in the decode_ctx / decode_q4 kernel cases")
+    ap.add_argument("--kernel-case", default=None, choices=["decode", "decode_fused", "decode_ctx", "decode_q4", "decode_long", "prefill", "prefill_batch", "append", "copy", "kvsplit", "tree_verify"],
                     help="run a few launches of one kernel on a small case (for ncu), --steps = launches")
     args = ap.parse_args()
     if args.kernel_case:

@@ -702,6 +702,10 @@ int32_t kriya_cuda_ctx_create(const kriya_cuda_config* cfg_in, kriya_cuda_ctx** 
     CREATE_TRY(cudaMalloc(&c->d_act, c->act_bytes));
     CREATE_TRY(cudaMallocHost(&c->h_act, c->act_bytes));
     CREATE_TRY(cudaMalloc(&c->d_pairs, size_t(c->cap_pairs) * 3 * sizeof(uint32_t)));
+    // device staging of the host-buffer decode step (q, k, v, out of every layer for max_batch_rows rows): nothing is
+    // allocated once the context exists
+    c->step_bytes = 2 * size_t(c->cap_rows) * (cfg.num_q_heads + cfg.num_kv_heads) * cfg.head_dim * 2 * cfg.num_layers;
+    CREATE_TRY(cudaMalloc(&c->d_step, c->step_bytes));
     if (c->tmaps_ok && kriya_prefill_supported(cfg.head_dim, cfg.num_q_heads / cfg.num_kv_heads, cfg.block_size_tokens, cfg.dtype)) {
         const char* e = getenv("KRIYA_PREFILL_SPLIT");
         c->pf_split_enable = !(e && atoi(e) == 0);
@@ -1497,14 +1501,8 @@ int32_t kriya_cuda_decode_step_host_begin(kriya_cuda_ctx* c, const void* q_host,
     const size_t qb = size_t(rows) * c->cfg.num_q_heads * c->cfg.head_dim * 2 * L;
     const size_t kb = size_t(rows) * c->cfg.num_kv_heads * c->cfg.head_dim * 2 * L;
     const size_t need = 2 * qb + 2 * kb;
-    if (need > c->step_bytes) {  // first call / larger batch only
-        KRIYA_CUDA_TRY(c, cudaStreamSynchronize(c->stream));
-        cudaFree(c->d_step);
-        c->d_step = nullptr;
-        c->step_bytes = 0;
-        KRIYA_CUDA_TRY(c, cudaMalloc(&c->d_step, need));
-        c->step_bytes = need;
-    }
+    if (need > c->step_bytes)  // the staging is sized for max_batch_rows when the context is created
+        return c->fail(KRIYA_CUDA_INVALID_INPUT, "step of " + std::to_string(rows) + " rows exceeds the context's staging");
     uint8_t* dq = c->d_step;
     uint8_t* dk = dq + qb;
     uint8_t* dv = dk + kb;

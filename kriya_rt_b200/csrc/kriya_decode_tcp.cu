@@ -742,12 +742,14 @@ decode_tcp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
             const uint32_t tok_lo = max(seg.blk_lo * kPage, seg.tok_first), tok_hi = min(seg.blk_hi * kPage, row_tokens);
             const uint32_t t0 = seg.blk_lo / kPagesPerTile, t1 = (seg.blk_hi + kPagesPerTile - 1) / kPagesPerTile;
             const bool empty = seg.blk_hi <= seg.blk_lo;
-            float m_used[G], l_lane[G];
+            // The two lanes that hold a token's score (one per half of d) share the token's probabilities: the lane of the
+            // first half takes query heads 0 .. GH - 1, the other one heads GH .. G - 1 (exponential, sum, store).
+            constexpr int GH = (G + 1) / 2;
+            float m_used[G], l_own[GH];
 #pragma unroll
-            for (int jj = 0; jj < G; ++jj) {
-                m_used[jj] = -INFINITY;
-                l_lane[jj] = 0.0f;
-            }
+            for (int jj = 0; jj < G; ++jj) m_used[jj] = -INFINITY;
+#pragma unroll
+            for (int i = 0; i < GH; ++i) l_own[i] = 0.0f;
             for (uint32_t t = empty ? t1 : t0; t < t1; ++t, ++g) {
                 if (*abort_flag) { ok = false; break; }
                 ok = warp_wait_l(wait_ns, &s_full[g & 1u], (g >> 1) & 1u);
@@ -821,7 +823,7 @@ decode_tcp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                         }
                     }
 #pragma unroll
-                    for (int jj = 0; jj < G; ++jj) l_lane[jj] *= alpha[jj];
+                    for (int i = 0; i < GH; ++i) l_own[i] *= half ? alpha[(i + GH < G) ? i + GH : 0] : alpha[i];
                     softmax_sync();  // alpha_s and red may be rewritten by the next tile
                 }
                 if (g >= 2) {
@@ -831,12 +833,15 @@ decode_tcp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                 {
                     uint8_t* pbuf = sP + (g & 1u) * kPBytes;
 #pragma unroll
-                    for (int jj = 0; jj < G; ++jj) {
-                        const float p = (s[jj] == -INFINITY) ? 0.0f : fast_exp2(s[jj] - m_used[jj]);
-                        if (half == 0u) {  // both halves of d hold the token's score: one of them carries it on
-                            l_lane[jj] += p;
-                            *reinterpret_cast<uint16_t*>(pbuf + p_off[jj]) = T::store(p);
-                        }
+                    for (int i = 0; i < GH; ++i) {
+                        constexpr int kNone = 0;
+                        const int j1 = (i + GH < G) ? i + GH : kNone;  // the second lane's head of this round (none when G is odd)
+                        const bool mine = half == 0u || i + GH < G;
+                        const float sv = half ? s[j1] : s[i];
+                        const float mv = half ? m_used[j1] : m_used[i];
+                        const float p = (sv == -INFINITY || !mine) ? 0.0f : fast_exp2(sv - mv);
+                        l_own[i] += p;
+                        if (mine) *reinterpret_cast<uint16_t*>(pbuf + (half ? p_off[j1] : p_off[i])) = T::store(p);
                     }
                 }
                 if (__any_sync(0xFFFFFFFFu, !valid)) {  // the V half must have landed before rows of it are cleared
@@ -855,17 +860,19 @@ decode_tcp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
             }
             if (!ok) break;
             // ---- end of the run piece ---------------------------------------------------------------------------
-            // sums per head: 16 tokens of the warp (the lanes of the second half hold zeros), then the KV head's four warps
-            float l_tot[G];
+            // sums per head: the 16 tokens of each half of the warp (lane 0: heads 0 .. GH - 1, lane 16: the others), then
+            // the KV head's four warps
+            float l_tot[GH];
 #pragma unroll
-            for (int jj = 0; jj < G; ++jj) l_tot[jj] = l_lane[jj];
+            for (int i = 0; i < GH; ++i) l_tot[i] = l_own[i];
 #pragma unroll
-            for (int off = 16; off >= 1; off >>= 1)
+            for (int off = 8; off >= 1; off >>= 1)
 #pragma unroll
-                for (int jj = 0; jj < G; ++jj) l_tot[jj] += __shfl_xor_sync(0xFFFFFFFFu, l_tot[jj], off);
-            if (lane == 0) {
+                for (int i = 0; i < GH; ++i) l_tot[i] += __shfl_xor_sync(0xFFFFFFFFu, l_tot[i], off);
+            if (tk == 0u) {
 #pragma unroll
-                for (int jj = 0; jj < G; ++jj) red[warp * 8 + jj] = l_tot[jj];
+                for (int i = 0; i < GH; ++i)
+                    if (half == 0u || i + GH < G) red[warp * 8 + (half ? i + GH : i)] = l_tot[i];
             }
             softmax_sync();
             if (lane == 0 && warp < 2u) {  // (m, l) of the piece for the G heads of this KV head, row order j = hd * G + jj
