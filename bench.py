@@ -466,6 +466,10 @@ def run_gpu_arm(args):
             "clocks": clocks,
             "config5": config5,
         }
+        if world > 1 and config5 and "one_sequence_131072" in config5:  # the KV-axis split through the product entry point
+            one = config5["one_sequence_131072"]
+            line["kvsplit"] = {"max_abs_err": one.get("max_abs_err"), "us_per_layer": one.get("us_per_layer"),
+                               "entry_point": "kriya_cuda_kvsplit_decode", "check": one.get("check")}
         if world == 1 and not args.no_cpu_baseline:
             t1, cores, _ = cpu_sample(1, 1)
             layers = int(max(1, min(L, 15.0 / max(t1, 1e-6))))

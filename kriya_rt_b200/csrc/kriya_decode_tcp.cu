@@ -350,6 +350,8 @@ decode_tcp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
     };
     if (warp == 8) {
         if (lane == 0) {
+            tma_prefetch_map(&map_k);
+            tma_prefetch_map(&map_v);
             for (int s = 0; s < kStages; ++s) {
                 mbar_init(&kv_full[s], 1);
                 mbar_init(&v_full[s], 1);
@@ -403,9 +405,12 @@ decode_tcp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
         tmem_relinquish();
     }
     auto seg_at = [&](uint32_t si) -> KriyaTcSeg { return (si - seg_begin < 8u) ? segs_s[si - seg_begin] : pp.segs[si]; };
-    // Query rows of heads that do not exist (G < 8) stay zero (their scores and probabilities feed unused columns only).
-    for (uint32_t i = tid; i < (kQBufs * kQBytes + 2 * kPBytes) / 16; i += kThreads)
-        reinterpret_cast<uint4*>(sQ)[i] = make_uint4(0u, 0u, 0u, 0u);
+    // Query and probability rows of heads that do not exist (G < 8) stay zero (they feed unused columns only); with
+    // G = 8 every row is written before it is read.
+    if (G < 8) {
+        for (uint32_t i = tid; i < (kQBufs * kQBytes + 2 * kPBytes) / 16; i += kThreads)
+            reinterpret_cast<uint4*>(sQ)[i] = make_uint4(0u, 0u, 0u, 0u);
+    }
     fence_async_smem();
     tc_fence_before();
     __syncthreads();  // every barrier is set up
@@ -800,13 +805,13 @@ decode_tcp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                             m_used[jj] = m_tile;
                         }
                     }
-                    // the accumulator's columns belong to all query heads of the row: publish the factors
-                    if (lane == 0 && warp < 2u) {
+                    if (t > t0) {  // (a piece's first tile has nothing to rescale)
+                        // the accumulator's columns belong to all query heads of the row: publish the factors
+                        if (lane == 0 && warp < 2u) {
 #pragma unroll
-                        for (int jj = 0; jj < 8; ++jj) alpha_s[hd * 8 + jj] = (jj < G) ? alpha[jj < G ? jj : 0] : 1.0f;
-                    }
-                    softmax_sync();
-                    if (t > t0) {
+                            for (int jj = 0; jj < 8; ++jj) alpha_s[hd * 8 + jj] = (jj < G) ? alpha[jj < G ? jj : 0] : 1.0f;
+                        }
+                        softmax_sync();
                         ok = warp_wait_l(wait_ns, &pv_done[(g - 1u) & 1u], ((g - 1u) >> 1) & 1u);
                         if (!ok) break;
                         if (warp < 4u) {
