@@ -750,9 +750,9 @@ decode_tcp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
             // The two lanes that hold a token's score (one per half of d) share the token's probabilities: the lane of the
             // first half takes query heads 0 .. GH - 1, the other one heads GH .. G - 1 (exponential, sum, store).
             constexpr int GH = (G + 1) / 2;
-            float m_used[G], l_own[GH];
+            float m_used[G], m_thr[G], l_own[GH];  // m_thr: the score above which the exponent reference moves
 #pragma unroll
-            for (int jj = 0; jj < G; ++jj) m_used[jj] = -INFINITY;
+            for (int jj = 0; jj < G; ++jj) m_used[jj] = m_thr[jj] = -INFINITY;
 #pragma unroll
             for (int i = 0; i < GH; ++i) l_own[i] = 0.0f;
             for (uint32_t t = empty ? t1 : t0; t < t1; ++t, ++g) {
@@ -767,7 +767,9 @@ decode_tcp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                 tmem_ld8(s_col + 16u, r1);
                 tmem_wait_ld();
                 const uint32_t tok = t * kTileTokens + pg * kPage + tk;
-                const bool valid = tok >= tok_lo && tok < tok_hi;
+                // only a piece's first and last tile can hold tokens outside the piece
+                const bool inner = t * kTileTokens >= tok_lo && (t + 1u) * kTileTokens <= tok_hi;
+                const bool valid = inner || (tok >= tok_lo && tok < tok_hi);
                 float s[G];
                 bool over = false;
 #pragma unroll
@@ -776,13 +778,18 @@ decode_tcp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                     x += __shfl_xor_sync(0xFFFFFFFFu, x, 16);  // the other half of d: the same token and head, lane +- 16
                     x *= scale2;
                     if (softcap) x = softcap_log2(x, a.logit_softcap);
-                    s[jj] = valid ? x : -INFINITY;
-                    over = over || (s[jj] > m_used[jj] + kRescale);
+                    s[jj] = x;
                 }
-                float alpha[G];
+                if (!inner) {
 #pragma unroll
-                for (int jj = 0; jj < G; ++jj) alpha[jj] = 1.0f;
+                    for (int jj = 0; jj < G; ++jj) s[jj] = valid ? s[jj] : -INFINITY;
+                }
+#pragma unroll
+                for (int jj = 0; jj < G; ++jj) over = over || (s[jj] > m_thr[jj]);
                 if (softmax_or(over)) {
+                    float alpha[G];
+#pragma unroll
+                    for (int jj = 0; jj < G; ++jj) alpha[jj] = 1.0f;
                     // per-head maximum over the tile: 16 tokens of this warp, then the four warps (pages) of the same KV head
                     float mx[G];
 #pragma unroll
@@ -803,6 +810,7 @@ decode_tcp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                         if (m_tile > m_used[jj]) {
                             alpha[jj] = (m_used[jj] == -INFINITY) ? 0.0f : exp2f(m_used[jj] - m_tile);
                             m_used[jj] = m_tile;
+                            m_thr[jj] = m_tile + kRescale;
                         }
                     }
                     if (t > t0) {  // (a piece's first tile has nothing to rescale)
@@ -849,7 +857,7 @@ decode_tcp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                         if (mine) *reinterpret_cast<uint16_t*>(pbuf + (half ? p_off[j1] : p_off[i])) = T::store(p);
                     }
                 }
-                if (__any_sync(0xFFFFFFFFu, !valid)) {  // the V half must have landed before rows of it are cleared
+                if (!inner && __any_sync(0xFFFFFFFFu, !valid)) {  // the V half must have landed before rows of it are cleared
                     ok = warp_wait_l(wait_ns, &v_full[g % kStages], (g / kStages) & 1u);
                     if (!ok) break;
                 }
