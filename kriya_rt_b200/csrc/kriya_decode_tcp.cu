@@ -48,6 +48,10 @@ constexpr int kTileTokens = kPagesPerTile * kPage;
 constexpr uint32_t kPageBytes = 8192;            // one page of K (or V), both heads
 constexpr uint32_t kTileKBytes = kPagesPerTile * kPageBytes;  // 32 KB
 constexpr uint32_t kStageBytes = 2 * kTileKBytes;             // K tile + V tile
+// The K tile is kept as two halves of d: [half][page][head][token][64 d], so that the tile's 128 (page, head, token) rows are
+// one MMA operand per half and the two halves are steps of the same accumulation.
+constexpr uint32_t kKHalfPage = 4096;                         // one half of d of a page: 2 heads x 16 tokens x 128 B
+constexpr uint32_t kKHalfTile = kTileKBytes / 2;
 constexpr int kStages = 3;
 constexpr int kQBufs = 3;
 constexpr uint32_t kQBytes = 32 * 128;           // 32 operand rows (half', head) x 128 B
@@ -55,7 +59,7 @@ constexpr uint32_t kPBytes = (kPagesPerTile / 2) * 8 * 128;  // per pair of page
 constexpr int kSoftmaxThreads = 256;
 constexpr int kThreads = 384;  // warps 0-7 softmax, 8 producer, 9 MMA issuer, 10 scratch-set guard, 11 stager
 constexpr uint32_t kTmemCols = 256;
-constexpr uint32_t kColS0 = 0, kColS1 = 64, kColO = 128;  // score tiles: 2 halves x 32 columns each; accumulator 32 columns
+constexpr uint32_t kColS0 = 0, kColS1 = 64, kColO = 128;  // score tiles: 16 columns each; accumulator 32 columns
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescale = 8.0f;
 
@@ -131,6 +135,22 @@ __device__ __forceinline__ void tma_load_page(void* dst_smem, const CUtensorMap*
             smem_u32(dst_smem)),
         "l"(map), "r"(0), "r"(page), "r"(smem_u32(bar))
         : "memory");
+}
+// One half of d of a K page (both heads, 16 tokens x 64 d each = 4 KB): coordinates (0, 0, half, 0, page) of the map whose
+// box is one half.
+__device__ __forceinline__ void tma_load_khalf(void* dst_smem, const CUtensorMap* map, int32_t half, int32_t page, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %2, %3, %2, %4}], [%5];" ::"r"(
+            smem_u32(dst_smem)),
+        "l"(map), "r"(0), "r"(half), "r"(page), "r"(smem_u32(bar))
+        : "memory");
+}
+// 4 consecutive TMEM columns of this thread's lane.
+__device__ __forceinline__ void tmem_ld4(uint32_t taddr, uint32_t (&r)[4]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(taddr)
+                 : "memory");
 }
 // 8 consecutive TMEM columns of this thread's lane.
 __device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
@@ -278,7 +298,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 decode_tcp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, Params pp) {
     constexpr int HQ = kHkv * G;
     constexpr uint32_t FMT = (T::kDtype == KRIYA_DTYPE_BF16) ? 1u : 0u;
-    constexpr uint32_t IDESC_S = make_idesc(FMT, 128, 32, 0, 0);  // A = 128 K rows (K-major), B = 32 query rows (K-major)
+    constexpr uint32_t IDESC_S = make_idesc(FMT, 128, 16, 0, 0);  // A = the tile's 128 K rows (K-major), B = 16 query rows (K-major)
     // A = a page's two V planes of one head (MN-major: M = d), B = 16 x 16: rows 0-7 the probabilities of the head's query heads;
     // M = 128 allows no N below 16, so rows 8-15 are whatever follows in shared memory and their 8 result columns are never read
     constexpr uint32_t IDESC_O = make_idesc(FMT, 128, 16, 1, 0);
@@ -378,10 +398,11 @@ decode_tcp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                 atomicMax(a.status, uint32_t(KRIYA_DEV_BAD_BLOCK_INDEX));
                 blk = 0;
             }
-            uint8_t* dst = sKV + (hdr0.z + lane) * kPageBytes;
+            const uint32_t slot = hdr0.z + lane;  // the page's place in the tile
             const int32_t page = int32_t(pp.page0 + blk);
-            tma_load_page(dst, &map_k, page, &kv_full[0]);
-            tma_load_page(dst + kTileKBytes, &map_v, page, &v_full[0]);
+            tma_load_khalf(sKV + slot * kKHalfPage, &map_k, 0, page, &kv_full[0]);
+            tma_load_khalf(sKV + kKHalfTile + slot * kKHalfPage, &map_k, 1, page, &kv_full[0]);
+            tma_load_page(sKV + kTileKBytes + slot * kPageBytes, &map_v, page, &v_full[0]);
         }
     }
     if (tid == 0) {
@@ -465,10 +486,12 @@ decode_tcp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                     }
                     __syncwarp();
                     if (lane < npages) {
-                        uint8_t* dst = sKV + stage * kStageBytes + (my_page - t * kPagesPerTile) * kPageBytes;
+                        uint8_t* st = sKV + stage * kStageBytes;
+                        const uint32_t slot = my_page - t * kPagesPerTile;
                         const int32_t page = int32_t(pp.page0) + blk;
-                        tma_load_page(dst, &map_k, page, &kv_full[stage]);
-                        tma_load_page(dst + kTileKBytes, &map_v, page, &v_full[stage]);
+                        tma_load_khalf(st + slot * kKHalfPage, &map_k, 0, page, &kv_full[stage]);
+                        tma_load_khalf(st + kKHalfTile + slot * kKHalfPage, &map_k, 1, page, &kv_full[stage]);
+                        tma_load_page(st + kTileKBytes + slot * kPageBytes, &map_v, page, &v_full[stage]);
                     }
                 }
                 pf_valid = t + 1u < t1;
@@ -583,12 +606,13 @@ decode_tcp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
             const uint32_t stage = gg % kStages;
             const uint32_t d_tmem = tmem_base + ((gg & 1u) ? kColS1 : kColS0);
             const uint64_t ad = kv_desc + uint64_t((stage * kStageBytes) >> 4), bd = q_desc + uint64_t((qbuf * kQBytes) >> 4);
+            // scores[(page, head, token)][query head] over d = 128: eight steps of 16, four in each half of d
 #pragma unroll
-            for (int g2 = 0; g2 < 2; ++g2)  // the tile's two halves of 128 operand rows (2 pages each)
+            for (int hf = 0; hf < 2; ++hf)
 #pragma unroll
-                for (int ks = 0; ks < 4; ++ks)  // 64 d of a half = 4 steps of 16
-                    umma_ss_pred(d_tmem + uint32_t(g2) * 32u, ad + uint64_t((uint32_t(g2) * 16384u + uint32_t(ks) * 32u) >> 4),
-                                 bd + uint64_t((uint32_t(ks) * 32u) >> 4), IDESC_S, ks > 0 ? 1u : 0u, el);
+                for (int ks = 0; ks < 4; ++ks)
+                    umma_ss_pred(d_tmem, ad + uint64_t((uint32_t(hf) * kKHalfTile + uint32_t(ks) * 32u) >> 4),
+                                 bd + uint64_t((uint32_t(hf) * 2048u + uint32_t(ks) * 32u) >> 4), IDESC_S, (hf | ks) ? 1u : 0u, el);
             umma_commit_pred(&s_full[gg & 1u], el);
         };
         uint32_t g = 0;
@@ -670,22 +694,29 @@ decode_tcp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
             *set_free_s = free_now ? 1u : 2u;
         }
     } else {
-        // ---- softmax warps 0-7: warp w owns operand rows 32 w .. 32 w + 31 of the tile ------------------------------------
-        // = (page w / 2, KV head w % 2); lane = (half lane / 16, token lane % 16).  Warps 0-3 read the accumulator of the
-        // tile's first score MMA (TMEM lanes 32 w ..), warps 4-7 that of the second (lanes 32 (w - 4) ..).
-        const uint32_t wq = warp & 3u, g2 = warp >> 2;
-        const uint32_t lane_addr = (wq * 32u) << 16;
-        const uint32_t hd = warp & 1u, pg = warp >> 1, half = lane >> 4, tk = lane & 15u;
+        // ---- softmax warps 0-7: the tile's 128 score rows are (page, KV head, token) = TMEM lanes; warps w and w + 4 both
+        // read lanes 32 (w % 4) .. (page w % 4; lane = (KV head lane / 16, token lane % 16)) and share the row's query
+        // heads: warps 0-3 take heads 0 .. GH - 1 of the row's KV head, warps 4-7 heads GH .. G - 1.
+        constexpr int GH = (G + 1) / 2;
+        const uint32_t grp = warp >> 2, pg = warp & 3u;
+        const uint32_t lane_addr = (pg * 32u) << 16;
+        const uint32_t hd = lane >> 4, tk = lane & 15u;
+        const uint32_t jj0 = grp ? uint32_t(GH) : 0u;             // first query head (within the KV head) of this thread
+        const uint32_t nj = grp ? uint32_t(G - GH) : uint32_t(GH);  // and how many
         const bool softcap = a.logit_softcap > 0.0f;
         const float scale2 = softcap ? a.sm_scale : a.sm_scale * kLog2e;
         const bool state_mode = a.state_o != nullptr;
-        // the probability entries of this thread's token (written by the thread of the first half of d): pair of pages pg / 2,
-        // operand row jj, element k = 32 (pg % 2) + 16 hd + tk of the pair's 64
+        // a probability entry of this thread's token: pair of pages pg / 2, operand row jj, element k = 32 (pg % 2) + 16 hd + tk
+        // of the pair's 64 (16-byte chunks swizzled with the row)
         const uint32_t k_in = 32u * (pg & 1u) + 16u * hd + tk;
-        uint32_t p_off[G];
+        uint32_t p_off[GH];
 #pragma unroll
-        for (int jj = 0; jj < G; ++jj)
-            p_off[jj] = (pg >> 1) * 1024u + uint32_t(jj) * 128u + ((((k_in >> 3) ^ uint32_t(jj)) << 4) | ((k_in & 7u) << 1));
+        for (int i = 0; i < GH; ++i) {
+            const uint32_t jj = jj0 + uint32_t(i);
+            p_off[i] = (pg >> 1) * 1024u + jj * 128u + ((((k_in >> 3) ^ jj) << 4) | ((k_in & 7u) << 1));
+        }
+        // this thread's row of the tile's V half `grp` (cleared when its token lies outside the piece): [page][head][half][token]
+        const uint32_t v_row_off = kTileKBytes + (((pg * 2u + hd) * 2u + grp) * 16u + tk) * 128u;
         // at the end of a piece threads 0-127 finish KV head 0 and threads 128-255 KV head 1, one output dimension each
         const uint32_t fin_hd = tid >> 7, d = tid & 127u;
         float* fin_stage = red + 64 + fin_hd * 128;
@@ -747,77 +778,70 @@ decode_tcp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
             const uint32_t tok_lo = max(seg.blk_lo * kPage, seg.tok_first), tok_hi = min(seg.blk_hi * kPage, row_tokens);
             const uint32_t t0 = seg.blk_lo / kPagesPerTile, t1 = (seg.blk_hi + kPagesPerTile - 1) / kPagesPerTile;
             const bool empty = seg.blk_hi <= seg.blk_lo;
-            // The two lanes that hold a token's score (one per half of d) share the token's probabilities: the lane of the
-            // first half takes query heads 0 .. GH - 1, the other one heads GH .. G - 1 (exponential, sum, store).
-            constexpr int GH = (G + 1) / 2;
-            float m_used[G], m_thr[G], l_own[GH];  // m_thr: the score above which the exponent reference moves
+            float m_used[GH], m_thr[GH], l_own[GH];  // m_thr: the score above which the exponent reference moves
 #pragma unroll
-            for (int jj = 0; jj < G; ++jj) m_used[jj] = m_thr[jj] = -INFINITY;
-#pragma unroll
-            for (int i = 0; i < GH; ++i) l_own[i] = 0.0f;
+            for (int i = 0; i < GH; ++i) {
+                m_used[i] = m_thr[i] = -INFINITY;
+                l_own[i] = 0.0f;
+            }
             for (uint32_t t = empty ? t1 : t0; t < t1; ++t, ++g) {
                 if (*abort_flag) { ok = false; break; }
                 ok = warp_wait_l(wait_ns, &s_full[g & 1u], (g >> 1) & 1u);
                 if (!ok) break;
                 tc_fence_after();
-                // partial scores of this row: columns 16 half' + 8 hd + jj of its score MMA; this lane's half is the useful one
-                uint32_t r0[8], r1[8];
-                const uint32_t s_col = tmem_base + lane_addr + ((g & 1u) ? kColS1 : kColS0) + 32u * g2 + 8u * hd;
-                tmem_ld8(s_col, r0);
-                tmem_ld8(s_col + 16u, r1);
+                // this row's scores: columns 8 hd' + jj of the tile's score accumulator; the columns of the row's own KV head count
+                uint32_t ra[4], rb[4];
+                const uint32_t s_col = tmem_base + lane_addr + ((g & 1u) ? kColS1 : kColS0) + jj0;
+                tmem_ld4(s_col, ra);
+                tmem_ld4(s_col + 8u, rb);
                 tmem_wait_ld();
                 const uint32_t tok = t * kTileTokens + pg * kPage + tk;
                 // only a piece's first and last tile can hold tokens outside the piece
                 const bool inner = t * kTileTokens >= tok_lo && (t + 1u) * kTileTokens <= tok_hi;
                 const bool valid = inner || (tok >= tok_lo && tok < tok_hi);
-                float s[G];
+                float s[GH];
                 bool over = false;
 #pragma unroll
-                for (int jj = 0; jj < G; ++jj) {
-                    float x = __uint_as_float(half ? r1[jj] : r0[jj]);
-                    x += __shfl_xor_sync(0xFFFFFFFFu, x, 16);  // the other half of d: the same token and head, lane +- 16
-                    x *= scale2;
+                for (int i = 0; i < GH; ++i) {
+                    float x = __uint_as_float(hd ? rb[i] : ra[i]) * scale2;
                     if (softcap) x = softcap_log2(x, a.logit_softcap);
-                    s[jj] = x;
+                    s[i] = (valid && uint32_t(i) < nj) ? x : -INFINITY;
+                    over = over || (s[i] > m_thr[i]);
                 }
-                if (!inner) {
-#pragma unroll
-                    for (int jj = 0; jj < G; ++jj) s[jj] = valid ? s[jj] : -INFINITY;
-                }
-#pragma unroll
-                for (int jj = 0; jj < G; ++jj) over = over || (s[jj] > m_thr[jj]);
                 if (softmax_or(over)) {
-                    float alpha[G];
+                    float alpha[GH];
 #pragma unroll
-                    for (int jj = 0; jj < G; ++jj) alpha[jj] = 1.0f;
-                    // per-head maximum over the tile: 16 tokens of this warp, then the four warps (pages) of the same KV head
-                    float mx[G];
+                    for (int i = 0; i < GH; ++i) alpha[i] = 1.0f;
+                    // per-head maximum over the tile: the 16 tokens of this half-warp, then the four pages
+                    float mx[GH];
 #pragma unroll
-                    for (int jj = 0; jj < G; ++jj) mx[jj] = s[jj];
+                    for (int i = 0; i < GH; ++i) mx[i] = s[i];
 #pragma unroll
                     for (int off = 8; off >= 1; off >>= 1)
 #pragma unroll
-                        for (int jj = 0; jj < G; ++jj) mx[jj] = fmaxf(mx[jj], __shfl_xor_sync(0xFFFFFFFFu, mx[jj], off));
-                    if (lane == 0) {
+                        for (int i = 0; i < GH; ++i) mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xFFFFFFFFu, mx[i], off));
+                    if (tk == 0u) {
 #pragma unroll
-                        for (int jj = 0; jj < G; ++jj) red[warp * 8 + jj] = mx[jj];
+                        for (int i = 0; i < GH; ++i)
+                            if (uint32_t(i) < nj) red[(pg * 2u + hd) * 8u + jj0 + uint32_t(i)] = mx[i];
                     }
                     softmax_sync();
 #pragma unroll
-                    for (int jj = 0; jj < G; ++jj) {
-                        const float m_tile = fmaxf(fmaxf(red[hd * 8 + jj], red[(hd + 2u) * 8 + jj]),
-                                                   fmaxf(red[(hd + 4u) * 8 + jj], red[(hd + 6u) * 8 + jj]));
-                        if (m_tile > m_used[jj]) {
-                            alpha[jj] = (m_used[jj] == -INFINITY) ? 0.0f : exp2f(m_used[jj] - m_tile);
-                            m_used[jj] = m_tile;
-                            m_thr[jj] = m_tile + kRescale;
+                    for (int i = 0; i < GH; ++i) {
+                        const uint32_t c = hd * 8u + jj0 + uint32_t(i);
+                        const float m_tile = (uint32_t(i) < nj) ? fmaxf(fmaxf(red[c], red[16u + c]), fmaxf(red[32u + c], red[48u + c])) : -INFINITY;
+                        if (m_tile > m_used[i]) {
+                            alpha[i] = (m_used[i] == -INFINITY) ? 0.0f : exp2f(m_used[i] - m_tile);
+                            m_used[i] = m_tile;
+                            m_thr[i] = m_tile + kRescale;
                         }
                     }
                     if (t > t0) {  // (a piece's first tile has nothing to rescale)
                         // the accumulator's columns belong to all query heads of the row: publish the factors
-                        if (lane == 0 && warp < 2u) {
+                        if (pg == 0u && tk == 0u) {
 #pragma unroll
-                            for (int jj = 0; jj < 8; ++jj) alpha_s[hd * 8 + jj] = (jj < G) ? alpha[jj < G ? jj : 0] : 1.0f;
+                            for (int i = 0; i < GH; ++i)
+                                if (uint32_t(i) < nj) alpha_s[hd * 8u + jj0 + uint32_t(i)] = alpha[i];
                         }
                         softmax_sync();
                         ok = warp_wait_l(wait_ns, &pv_done[(g - 1u) & 1u], ((g - 1u) >> 1) & 1u);
@@ -829,14 +853,16 @@ decode_tcp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                             tmem_ld32(tmem_base + lane_addr + kColO, o);
                             tmem_wait_ld();
 #pragma unroll
-                            for (int cI = 0; cI < 32; ++cI)
-                                o[cI] = __float_as_uint(__uint_as_float(o[cI]) * alpha_s[((cI >> 4) << 3) | (cI & 7)]);
+                            for (int cI = 0; cI < 32; ++cI) {
+                                const float f = ((cI & 7) < G && (cI & 8) == 0) ? alpha_s[((cI >> 4) << 3) | (cI & 7)] : 1.0f;
+                                o[cI] = __float_as_uint(__uint_as_float(o[cI]) * f);
+                            }
                             tmem_st32(tmem_base + lane_addr + kColO, o);
                             tmem_wait_st();
                         }
                     }
 #pragma unroll
-                    for (int i = 0; i < GH; ++i) l_own[i] *= half ? alpha[(i + GH < G) ? i + GH : 0] : alpha[i];
+                    for (int i = 0; i < GH; ++i) l_own[i] *= alpha[i];
                     softmax_sync();  // alpha_s and red may be rewritten by the next tile
                 }
                 if (g >= 2) {
@@ -847,23 +873,19 @@ decode_tcp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                     uint8_t* pbuf = sP + (g & 1u) * kPBytes;
 #pragma unroll
                     for (int i = 0; i < GH; ++i) {
-                        constexpr int kNone = 0;
-                        const int j1 = (i + GH < G) ? i + GH : kNone;  // the second lane's head of this round (none when G is odd)
-                        const bool mine = half == 0u || i + GH < G;
-                        const float sv = half ? s[j1] : s[i];
-                        const float mv = half ? m_used[j1] : m_used[i];
-                        const float p = (sv == -INFINITY || !mine) ? 0.0f : fast_exp2(sv - mv);
-                        l_own[i] += p;
-                        if (mine) *reinterpret_cast<uint16_t*>(pbuf + (half ? p_off[j1] : p_off[i])) = T::store(p);
+                        if (uint32_t(i) < nj) {
+                            const float p = (s[i] == -INFINITY) ? 0.0f : fast_exp2(s[i] - m_used[i]);
+                            l_own[i] += p;
+                            *reinterpret_cast<uint16_t*>(pbuf + p_off[i]) = T::store(p);
+                        }
                     }
                 }
                 if (!inner && __any_sync(0xFFFFFFFFu, !valid)) {  // the V half must have landed before rows of it are cleared
                     ok = warp_wait_l(wait_ns, &v_full[g % kStages], (g / kStages) & 1u);
                     if (!ok) break;
                 }
-                if (!valid) {  // this thread's V row must contribute nothing: clear it (0 * garbage must not appear)
-                    const uint32_t stage = g % kStages;
-                    uint4* vrow = reinterpret_cast<uint4*>(sKV + stage * kStageBytes + kTileKBytes + tid * 128u);
+                if (!valid) {  // this token's V rows must contribute nothing (0 * garbage must not appear): this thread clears one
+                    uint4* vrow = reinterpret_cast<uint4*>(sKV + (g % kStages) * kStageBytes + v_row_off);
 #pragma unroll
                     for (int cI = 0; cI < 8; ++cI) vrow[cI] = make_uint4(0u, 0u, 0u, 0u);
                 }
@@ -873,8 +895,7 @@ decode_tcp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
             }
             if (!ok) break;
             // ---- end of the run piece ---------------------------------------------------------------------------
-            // sums per head: the 16 tokens of each half of the warp (lane 0: heads 0 .. GH - 1, lane 16: the others), then
-            // the KV head's four warps
+            // sums per head: the 16 tokens of this half-warp, then the four pages
             float l_tot[GH];
 #pragma unroll
             for (int i = 0; i < GH; ++i) l_tot[i] = l_own[i];
@@ -885,14 +906,17 @@ decode_tcp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
             if (tk == 0u) {
 #pragma unroll
                 for (int i = 0; i < GH; ++i)
-                    if (half == 0u || i + GH < G) red[warp * 8 + (half ? i + GH : i)] = l_tot[i];
+                    if (uint32_t(i) < nj) red[(pg * 2u + hd) * 8u + jj0 + uint32_t(i)] = l_tot[i];
             }
             softmax_sync();
-            if (lane == 0 && warp < 2u) {  // (m, l) of the piece for the G heads of this KV head, row order j = hd * G + jj
+            if (pg == 0u && tk == 0u) {  // (m, l) of the piece for this thread's heads, row order j = hd * G + jj
 #pragma unroll
-                for (int jj = 0; jj < G; ++jj) {
-                    ml_s[(hd * G + jj) * 2 + 0] = m_used[jj];
-                    ml_s[(hd * G + jj) * 2 + 1] = (red[hd * 8 + jj] + red[(hd + 2u) * 8 + jj]) + (red[(hd + 4u) * 8 + jj] + red[(hd + 6u) * 8 + jj]);
+                for (int i = 0; i < GH; ++i) {
+                    if (uint32_t(i) < nj) {
+                        const uint32_t c = hd * 8u + jj0 + uint32_t(i), j = hd * uint32_t(G) + jj0 + uint32_t(i);
+                        ml_s[j * 2u + 0u] = m_used[i];
+                        ml_s[j * 2u + 1u] = (red[c] + red[16u + c]) + (red[32u + c] + red[48u + c]);
+                    }
                 }
             }
             // the accumulator: lane = d, columns 16 head + jj; threads 0-127 take KV head 0's columns, threads 128-255 head 1's
@@ -1092,8 +1116,9 @@ using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, voi
                               CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 }
 
-// 5-D maps over the K and V pools of all layers with one page per box: dimensions (d_lo 64, token 16, half of d 2, head 2,
-// page), strides (512, 128, 256, 8192) bytes.
+// 5-D maps over the K and V pools of all layers: dimensions (d_lo 64, token 16, half of d 2, head 2, page), strides (512,
+// 128, 256, 8192) bytes.  A V box is a whole page (lands as [head][half][token][64]); a K box is one half of d of a page
+// (lands as [head][token][64]), so that the kernel can keep a tile's K as [half][page][head][token][64].
 cudaError_t kriya_decode_tcp_encode_maps(void* pool_k, void* pool_v, uint64_t total_pages, void* out_map_k, void* out_map_v) {
     static EncodeFn enc = nullptr;
     if (enc == nullptr) {
@@ -1106,12 +1131,12 @@ cudaError_t kriya_decode_tcp_encode_maps(void* pool_k, void* pool_v, uint64_t to
     }
     const cuuint64_t dims[5] = {64, 16, 2, 2, total_pages};
     const cuuint64_t strides[4] = {512, 128, 256, 8192};
-    const cuuint32_t box[5] = {64, 16, 2, 2, 1};
+    const cuuint32_t box_v[5] = {64, 16, 2, 2, 1}, box_k[5] = {64, 16, 1, 2, 1};
     const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
     void* pools[2] = {pool_k, pool_v};
     void* outs[2] = {out_map_k, out_map_v};
     for (int i = 0; i < 2; ++i) {
-        const CUresult r = enc(static_cast<CUtensorMap*>(outs[i]), CU_TENSOR_MAP_DATA_TYPE_UINT16, 5, pools[i], dims, strides, box, estr,
+        const CUresult r = enc(static_cast<CUtensorMap*>(outs[i]), CU_TENSOR_MAP_DATA_TYPE_UINT16, 5, pools[i], dims, strides, i == 0 ? box_k : box_v, estr,
                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
