@@ -663,7 +663,7 @@ decode_tcp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                 primed = true;
                 if (!ok) break;
                 const uint32_t stage = g % kStages;
-                ok = warp_wait_l(wait_ns, &p_ready[g & 1u], (g >> 1) & 1u) && warp_wait_l(wait_ns, &v_full[stage], (g / kStages) & 1u);
+                ok = warp_wait_l(wait_ns, &p_ready[g & 1u], (g >> 1) & 1u);  // (its arrivals have seen the V half land)
                 if (!ok) break;
                 tc_fence_after();
                 const uint64_t ad = v_desc + uint64_t((stage * kStageBytes + kTileKBytes) >> 4);
@@ -880,10 +880,11 @@ decode_tcp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                         }
                     }
                 }
-                if (!inner && __any_sync(0xFFFFFFFFu, !valid)) {  // the V half must have landed before rows of it are cleared
-                    ok = warp_wait_l(wait_ns, &v_full[g % kStages], (g / kStages) & 1u);
-                    if (!ok) break;
-                }
+                // The V half must have landed before rows of it are cleared - and before the tile's P.V is issued: the softmax
+                // warps wait for it here (they have time to spare), so that the MMA warp, which sets the pace, waits for one
+                // barrier per tile only.
+                ok = warp_wait_l(wait_ns, &v_full[g % kStages], (g / kStages) & 1u);
+                if (!ok) break;
                 if (!valid) {  // this token's V rows must contribute nothing (0 * garbage must not appear): this thread clears one
                     uint4* vrow = reinterpret_cast<uint4*>(sKV + (g % kStages) * kStageBytes + v_row_off);
 #pragma unroll
