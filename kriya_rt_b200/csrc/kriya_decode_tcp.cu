@@ -314,17 +314,20 @@ decode_tcp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
     float* ml_s = alpha_s + 16;                         // [16][2] (m, l) of the piece per query head
     uint64_t* bars = reinterpret_cast<uint64_t*>(ml_s + 32);
     uint64_t* kv_full = bars;                     // [stages]: the K half of a stage has landed
-    uint64_t* kv_empty = bars + kStages;          // [stages]
+                                                  // (bars + kStages .. + 2 are spare)
     uint64_t* s_full = bars + 2 * kStages;        // [2]
     uint64_t* p_ready = bars + 2 * kStages + 2;   // [2], 256 arrivals
-    uint64_t* pv_done = bars + 2 * kStages + 4;   // [2]
+                                                  // (bars + 2 * kStages + 4 .. + 5 are spare)
     uint64_t* q_ready = bars + 2 * kStages + 6;   // [3]
     uint64_t* q_free = bars + 2 * kStages + 9;    // [3]
     uint64_t* kv_ready = bars + 2 * kStages + 12; // [3]
     uint64_t* v_full = bars + 2 * kStages + 15;   // [stages]: the V half
     uint64_t* aux_full = bars + 3 * kStages + 15; // [0]: the segment records below have landed; [1]: the first piece's raw query rows;
                                                   // [2]: the other pieces' states (gather_merge_smem); [3] unused
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * kStages + 19);
+    uint64_t* tile_done = bars + 3 * kStages + 19;  // [6]: the P.V of tile g is complete: entry g % 6, completion g / 6.  It frees
+                                                    // the tile's stage (the producer waits for tile g - 3), its probability buffer
+                                                    // (tile g - 2) and lets the accumulator be read.
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * kStages + 25);
     volatile uint32_t* abort_flag = tmem_slot + 1;
     volatile uint32_t* set_free_s = tmem_slot + 2;
     KriyaTcSeg* segs_s = reinterpret_cast<KriyaTcSeg*>(tmem_slot + 4);  // first 8 segment records of this CTA
@@ -375,7 +378,8 @@ decode_tcp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
             for (int s = 0; s < kStages; ++s) {
                 mbar_init(&kv_full[s], 1);
                 mbar_init(&v_full[s], 1);
-                mbar_init(&kv_empty[s], 1);
+                mbar_init(&tile_done[s], 1);
+                mbar_init(&tile_done[kStages + s], 1);
             }
             mbar_init(&aux_full[0], 1);
             mbar_init(&aux_full[1], 1);
@@ -410,8 +414,6 @@ decode_tcp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
         mbar_init(&s_full[1], 1);
         mbar_init(&p_ready[0], kSoftmaxThreads);
         mbar_init(&p_ready[1], kSoftmaxThreads);
-        mbar_init(&pv_done[0], 1);
-        mbar_init(&pv_done[1], 1);
         for (int b = 0; b < 3; ++b) {
             mbar_init(&q_ready[b], 1);
             mbar_init(&q_free[b], 1);
@@ -471,7 +473,7 @@ decode_tcp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                 if (g > 0u || early_pages == 0u) {  // the CTA's first tile may be on its way already
                     int32_t blk = pf_blk;
                     if (!pf_valid && lane < npages) blk = table[my_page];
-                    if (g >= kStages && !warp_wait_l(wait_ns, &kv_empty[stage], ((g / kStages) - 1u) & 1u)) { ok = false; break; }
+                    if (g >= kStages && !warp_wait_l(wait_ns, &tile_done[(g - kStages) % 6u], ((g - kStages) / 6u) & 1u)) { ok = false; break; }
                     if (owns_last && t + 1u == t1 && !warp_wait_l(wait_ns, &kv_ready[runs % uint32_t(kQBufs)], (runs / uint32_t(kQBufs)) & 1u)) {
                         ok = false;
                         break;
@@ -677,8 +679,7 @@ decode_tcp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                                      ad + uint64_t((uint32_t(pgi) * kPageBytes + uint32_t(h) * 4096u) >> 4),
                                      bd + uint64_t((uint32_t(pgi >> 1) * 1024u + uint32_t(pgi & 1) * 64u + uint32_t(h) * 32u) >> 4), IDESC_O,
                                      (pgi > 0) ? 1u : first, el);
-                umma_commit_pred(&kv_empty[stage], el);
-                umma_commit_pred(&pv_done[g & 1u], el);
+                umma_commit_pred(&tile_done[g % 6u], el);
             }
         }
         if (!ok && lane == 0) {
@@ -844,7 +845,7 @@ decode_tcp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                                 if (uint32_t(i) < nj) alpha_s[hd * 8u + jj0 + uint32_t(i)] = alpha[i];
                         }
                         softmax_sync();
-                        ok = warp_wait_l(wait_ns, &pv_done[(g - 1u) & 1u], ((g - 1u) >> 1) & 1u);
+                        ok = warp_wait_l(wait_ns, &tile_done[(g - 1u) % 6u], ((g - 1u) / 6u) & 1u);
                         if (!ok) break;
                         if (warp < 4u) {
                             tc_fence_after();
@@ -866,7 +867,7 @@ decode_tcp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                     softmax_sync();  // alpha_s and red may be rewritten by the next tile
                 }
                 if (g >= 2) {
-                    ok = warp_wait_l(wait_ns, &pv_done[g & 1u], ((g >> 1) - 1u) & 1u);
+                    ok = warp_wait_l(wait_ns, &tile_done[(g - 2u) % 6u], ((g - 2u) / 6u) & 1u);
                     if (!ok) break;
                 }
                 {
@@ -925,7 +926,7 @@ decode_tcp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
 #pragma unroll
             for (int cI = 0; cI < 8; ++cI) o8[cI] = 0u;
             if (!empty) {
-                ok = warp_wait_l(wait_ns, &pv_done[(g - 1u) & 1u], ((g - 1u) >> 1) & 1u);
+                ok = warp_wait_l(wait_ns, &tile_done[(g - 1u) % 6u], ((g - 1u) / 6u) & 1u);
                 if (!ok) break;
                 tc_fence_after();
                 tmem_ld8(tmem_base + lane_addr + kColO + 16u * fin_hd, o8);
@@ -1049,7 +1050,7 @@ __global__ void __launch_bounds__(kD) late_merge_kernel(KriyaDecodeArgs a, const
 template <int G, typename T>
 cudaError_t launch_t(const Params& pp, const CUtensorMap& mk, const CUtensorMap& mv, uint32_t grid, int max_smem_optin,
                      bool programmatic, cudaStream_t s) {
-    const size_t smem = size_t(kStages) * kStageBytes + kQBufs * kQBytes + 2 * kPBytes + 2048 + 64 + 128 + 400 + 8 * sizeof(KriyaTcSeg) + 16 * 256 + 512 + 1024;
+    const size_t smem = size_t(kStages) * kStageBytes + kQBufs * kQBytes + 2 * kPBytes + 2048 + 64 + 128 + 448 + 8 * sizeof(KriyaTcSeg) + 16 * 256 + 512 + 1024;
     if (smem > size_t(max_smem_optin)) return cudaErrorInvalidValue;
     auto kern = decode_tcp_kernel<G, T>;
     {
