@@ -373,8 +373,6 @@ decode_tcp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
     };
     if (warp == 8) {
         if (lane == 0) {
-            tma_prefetch_map(&map_k);
-            tma_prefetch_map(&map_v);
             for (int s = 0; s < kStages; ++s) {
                 mbar_init(&kv_full[s], 1);
                 mbar_init(&v_full[s], 1);
