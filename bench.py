@@ -288,6 +288,8 @@ def run_gpu_arm(args):
         if dist is not None:
             dist.barrier()
 
+    host_times = {}
+
     def device_pass(mode, steps, warm):
         """`warm` untimed and exactly `steps` timed decode steps from a fresh sequence state, bracketed by a barrier and
         a device synchronisation on both sides; returns (device ms of the timed steps, launches in them)."""
@@ -303,14 +305,21 @@ def run_gpu_arm(args):
         launches0 = ex.launch_count
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         ev0.record(stream)
+        host_plan = host_issue = 0.0
         for t in range(warm, warm + steps):
+            h0 = time.perf_counter()
             plan, pos = step_plan(mgr, t)
             ex.upload_schedule_plan(plan, pos)
+            h1 = time.perf_counter()
             ex.decode_step(q, k, v, out, BATCH, rp, gp)
+            host_issue += time.perf_counter() - h1
+            host_plan += h1 - h0
         ev1.record(stream)
         ex.sync()
         torch.cuda.synchronize()
         barrier()
+        host_times["plan_ms_per_step"] = host_plan / steps * 1e3    # the host's share of a step: bookkeeping, plan, upload
+        host_times["issue_ms_per_step"] = host_issue / steps * 1e3  # and the time it takes to issue the step's launches
         return ev0.elapsed_time(ev1), ex.launch_count - launches0
 
     # ---- leg 1: device-resident throughput (`value`) -------------------------------------------------
@@ -339,6 +348,7 @@ def run_gpu_arm(args):
     #   serialised: a layer's launch may be set up early but touches nothing before the previous layer has completed;
     #   dependent : a layer's activations wait for the previous layer (as in a model), its cached K/V streams at once;
     #   bracketed : every launch between two CUDA events (which costs idle time around each launch).
+    host_step = dict(host_times)  # of the last repeat of the device-resident leg
     serial_ms, n_serial = device_pass(3, K, Wu)
     dep_ms, n_dep = device_pass(5, K, Wu)
     ex.set_fused_append(1)
@@ -434,7 +444,7 @@ def run_gpu_arm(args):
             "dtype": "bf16", "data": "synthetic",
             "config": {"workload": WORKLOAD, "l2": "inputs larger than L2: each step streams %.2f GB of KV" %
                        (kv_bytes_launch * L / 1e9), "plan": "rebuilt on the host every step by the C++ manager and uploaded inside the timed region",
-                       "kv_read_gbs_whole_step": kv_bytes_launch * L / (ms_per_step * 1e-3) / 1e9,
+                       "host_ms_per_step": host_step, "kv_read_gbs_whole_step": kv_bytes_launch * L / (ms_per_step * 1e-3) / 1e9,
                        "kernels_per_layer": gpu_launches / K / L,
                        "timed_region": {"repeats": len(repeats_ms), "steps_per_repeat": K, "device_s_total": sum(repeats_ms) / 1e3,
                                         "ms_per_step_median": ms_per_step, "ms_per_step_min": min(repeats_ms) / K,

@@ -22,7 +22,7 @@ LIB = ROOT / "kriya_rt_b200" / "lib"
 INCLUDE = ROOT / "include"
 OBJ = ROOT / "build" / "obj"
 
-CUDA_SOURCES = ["kriya_ctx.cu", "kriya_append.cu", "kriya_decode.cu", "kriya_decode_tc.cu", "kriya_decode_tc64.cu", "kriya_decode_tcp.cu", "kriya_copy.cu", "kriya_prefill.cu", "kriya_tree.cu", "kriya_static_scratch.cu", "kriya_comm.cu"]
+CUDA_SOURCES = ["kriya_ctx.cu", "kriya_append.cu", "kriya_decode.cu", "kriya_decode_tc.cu", "kriya_decode_tc64.cu", "kriya_decode_tcp.cu", "kriya_copy.cu", "kriya_prefill.cu", "kriya_tree.cu", "kriya_static_scratch.cu", "kriya_comm.cu", "kriya_q4.cu"]
 INCLUDED_SOURCES = {"kriya_decode_tc64.cu": ["kriya_decode_tc.cu"]}  # sources that #include another source
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

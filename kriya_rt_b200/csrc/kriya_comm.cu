@@ -44,6 +44,7 @@ struct CommKernelArgs {
     size_t slot_words;                   // uint2 words of one rank's slot: cap_R * (D + 2)
     size_t buf_off;                      // offset (uint2 words) of this call's generation inside a buffer
     uint32_t wait_previous;              // launched as a programmatic dependent of the kernel that writes `local`
+    uint64_t wait_ns;                    // how long a peer's words are waited for: the context's wait limit, a second at most
 };
 
 // One block per (row, query head), one thread per output dimension (blockDim.x == D).
@@ -73,7 +74,7 @@ __global__ void kvsplit_exchange_merge_kernel(CommKernelArgs a) {
             wm = comm_load(src + a.D);
             wl = comm_load(src + a.D + 1);
             if (wo.y == a.stamp && wm.y == a.stamp && wl.y == a.stamp) break;
-            if ((spin & 63u) == 63u && global_timer_ns() - t_start > kCommWaitNs) {
+            if ((spin & 63u) == 63u && global_timer_ns() - t_start > a.wait_ns) {
                 ok = false;
                 break;
             }
@@ -246,6 +247,7 @@ int32_t kriya_cuda_kvsplit_decode(kriya_cuda_ctx* c, uint32_t layer, const void*
     a.slot_words = size_t(s->cap_R) * (D + 2);
     a.buf_off = size_t(s->stamp % kriya::kCommBufs) * KRIYA_COMM_MAX_RANKS * a.slot_words;
     a.wait_previous = 1u;
+    a.wait_ns = std::min<uint64_t>(c->wait_ns, kriya::kCommWaitNs);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(R);
     cfg.blockDim = dim3(D);

@@ -52,6 +52,9 @@ void destroy(kriya_cuda_ctx* c) {
     cudaFree(c->d_pairs);
     cudaFree(c->pf_part_o);
     cudaFree(c->pf_part_ml);
+    cudaFree(c->q4_stage_k);
+    cudaFree(c->q4_stage_v);
+    cudaFree(c->q4_identity);
     cudaFree(c->d_tree_state);
     cudaFree(c->d_tree_mask);
     cudaFree(c->d_step);
@@ -615,6 +618,22 @@ int32_t kriya_cuda_ctx_create(const kriya_cuda_config* cfg_in, kriya_cuda_ctx** 
         c->tmaps_ok = kriya_prefill_encode_maps(c->pool_k, c->pool_v, total_rows, row_elems, c->tmap_k, c->tmap_v) == cudaSuccess;
     }
 
+    // Q4 cache: 16-bit staging pools for the prefill (see kriya_cuda_ctx::q4_stage_k), their maps and the identity table
+    if (cfg.kv_format == KRIYA_KV_Q4_GROUP32 &&
+        kriya_prefill_supported(cfg.head_dim, cfg.num_q_heads / cfg.num_kv_heads, cfg.block_size_tokens, cfg.dtype)) {
+        const uint32_t row_elems = cfg.num_kv_heads * cfg.head_dim;
+        const size_t stage_bytes = size_t(c->cap_indices) * cfg.block_size_tokens * row_elems * 2;
+        CREATE_TRY(cudaMalloc(&c->q4_stage_k, stage_bytes));
+        CREATE_TRY(cudaMalloc(&c->q4_stage_v, stage_bytes));
+        CREATE_TRY(cudaMalloc(&c->q4_identity, size_t(c->cap_indices) * sizeof(int32_t)));
+        std::vector<int32_t> iota(c->cap_indices);
+        for (uint32_t i = 0; i < c->cap_indices; ++i) iota[i] = int32_t(i);
+        CREATE_TRY(cudaMemcpy(c->q4_identity, iota.data(), iota.size() * sizeof(int32_t), cudaMemcpyHostToDevice));
+        c->q4_prefill_ok = kriya_prefill_encode_maps(c->q4_stage_k, c->q4_stage_v, uint64_t(c->cap_indices) * cfg.block_size_tokens, row_elems,
+                                                     c->tmap_k, c->tmap_v) == cudaSuccess;
+        (void)cudaGetLastError();
+    }
+
     // one-page-per-copy maps of the whole-page decode kernel
     if (c->tmaps_ok && kriya_decode_tcp_supported(cfg.head_dim, cfg.num_kv_heads, cfg.num_q_heads / cfg.num_kv_heads, cfg.block_size_tokens) &&
         c->layer_stride_bytes == size_t(cfg.num_kv_blocks) * c->block_bytes) {
@@ -706,7 +725,8 @@ int32_t kriya_cuda_ctx_create(const kriya_cuda_config* cfg_in, kriya_cuda_ctx** 
     // allocated once the context exists
     c->step_bytes = 2 * size_t(c->cap_rows) * (cfg.num_q_heads + cfg.num_kv_heads) * cfg.head_dim * 2 * cfg.num_layers;
     CREATE_TRY(cudaMalloc(&c->d_step, c->step_bytes));
-    if (c->tmaps_ok && kriya_prefill_supported(cfg.head_dim, cfg.num_q_heads / cfg.num_kv_heads, cfg.block_size_tokens, cfg.dtype)) {
+    if ((c->tmaps_ok || c->q4_prefill_ok) &&
+        kriya_prefill_supported(cfg.head_dim, cfg.num_q_heads / cfg.num_kv_heads, cfg.block_size_tokens, cfg.dtype)) {
         const char* e = getenv("KRIYA_PREFILL_SPLIT");
         c->pf_split_enable = !(e && atoi(e) == 0);
         c->pf_split_force = (e && atoi(e) >= 2) ? uint32_t(std::min(atoi(e), 8)) : 0u;  // for tests: that many pieces whatever the policy says
@@ -1217,8 +1237,9 @@ int32_t kriya_cuda_paged_gqa_prefill_batch(kriya_cuda_ctx* c, uint32_t layer, co
     if (n_seqs == 0) return c->fail(KRIYA_CUDA_INVALID_INPUT, "input_tokens must not be empty");
     if (n_seqs > c->n_rows) return c->fail(KRIYA_CUDA_INVALID_INPUT, "more sequences than plan rows");
     if (!kriya_prefill_supported(c->cfg.head_dim, c->cfg.num_q_heads / c->cfg.num_kv_heads, c->cfg.block_size_tokens,
-                                 c->cfg.dtype) || !c->tmaps_ok)
-        return c->fail(KRIYA_CUDA_UNSUPPORTED, "prefill kernels cover head_dim 64/128, 16-token blocks and the 16-bit cache");
+                                 c->cfg.dtype) || !(c->tmaps_ok || c->q4_prefill_ok))
+        return c->fail(KRIYA_CUDA_UNSUPPORTED, "prefill kernels cover head_dim 64/128 and 16-token blocks");
+    const bool q4 = c->cfg.kv_format == KRIYA_KV_Q4_GROUP32;
     cudaSetDevice(c->cfg.device);
     KRIYA_CUDA_TRY(c, cudaEventSynchronize(c->h_pairs_free));
     const int32_t* indptr = reinterpret_cast<const int32_t*>(c->h_plan_last + c->off_indptr);
@@ -1303,6 +1324,19 @@ int32_t kriya_cuda_paged_gqa_prefill_batch(kriya_cuda_ctx* c, uint32_t layer, co
     a.window = c->attention_window;
     a.sm_scale = p->sm_scale;
     a.logit_softcap = p->logit_softcap;
+    if (q4) {
+        // the plan's blocks of this layer, expanded to 16 bits in plan order; the kernel reads them with the identity table
+        KRIYA_CUDA_TRY(c, kriya_launch_q4_expand_blocks(c->layer_k(layer), c->layer_v(layer), c->q4_stage_k, c->q4_stage_v,
+                                                        c->plan_dev<int32_t>(c->off_indices), c->n_indices, c->cfg.block_size_tokens,
+                                                        c->cfg.num_kv_heads, c->cfg.head_dim, c->cfg.num_kv_blocks, c->cfg.dtype,
+                                                        c->d_status, c->stream));
+        c->launches += 1;
+        a.cache_k = c->q4_stage_k;
+        a.cache_v = c->q4_stage_v;
+        a.layer_row0 = 0;
+        a.table = c->q4_identity;
+        a.num_blocks = c->cap_indices;
+    }
     a.part_o = c->pf_part_o;
     a.part_ml = c->pf_part_ml;
     a.merge_items = reinterpret_cast<const KriyaPrefillMerge*>(reinterpret_cast<const KriyaPrefillTile*>(c->d_pairs) + n);

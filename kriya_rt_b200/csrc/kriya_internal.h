@@ -76,6 +76,13 @@ struct kriya_cuda_ctx {
     uint32_t pf_part_slots = 0;
     bool pf_split_enable = true;
     uint32_t pf_split_force = 0;
+    // Q4KvGroup32 cache: the chunked prefill reads K/V through tensor maps, so the blocks a plan names are expanded into
+    // 16-bit staging pools (max_page_indices blocks each, plan order) in front of the attention launch; tmap_k / tmap_v then
+    // cover the staging pools and the kernel walks them with the identity block table.
+    uint8_t* q4_stage_k = nullptr;
+    uint8_t* q4_stage_v = nullptr;
+    int32_t* q4_identity = nullptr;
+    bool q4_prefill_ok = false;
 
     // KV pools, all layers: layer l at l * layer_stride_bytes
     uint8_t* pool_k = nullptr;
@@ -376,5 +383,8 @@ cudaError_t kriya_launch_tree_finish(const KriyaTreeArgs& a, uint32_t head_dim, 
 cudaError_t kriya_launch_prefill(const KriyaPrefillArgs& a, uint32_t head_dim, uint32_t block_size, uint32_t dtype,
                                  int max_smem_optin, cudaStream_t s);
 bool kriya_prefill_supported(uint32_t head_dim, uint32_t group, uint32_t block_size, uint32_t dtype);
+cudaError_t kriya_launch_q4_expand_blocks(const void* pool_k, const void* pool_v, void* dst_k, void* dst_v, const int32_t* indices,
+                                          uint32_t n_indices, uint32_t block_tokens, uint32_t hkv, uint32_t head_dim, uint32_t num_blocks,
+                                          uint32_t dtype, uint32_t* status, cudaStream_t s);
 cudaError_t kriya_prefill_encode_maps(void* pool_k, void* pool_v, uint64_t total_rows, uint32_t row_elems,
                                       void* out_map_k, void* out_map_v);
