@@ -305,21 +305,28 @@ def run_gpu_arm(args):
         launches0 = ex.launch_count
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         ev0.record(stream)
-        host_plan = host_issue = 0.0
+        host_issue = 0.0
         for t in range(warm, warm + steps):
-            h0 = time.perf_counter()
             plan, pos = step_plan(mgr, t)
             ex.upload_schedule_plan(plan, pos)
             h1 = time.perf_counter()
             ex.decode_step(q, k, v, out, BATCH, rp, gp)
             host_issue += time.perf_counter() - h1
-            host_plan += h1 - h0
         ev1.record(stream)
         ex.sync()
         torch.cuda.synchronize()
         barrier()
-        host_times["plan_ms_per_step"] = host_plan / steps * 1e3    # the host's share of a step: bookkeeping, plan, upload
-        host_times["issue_ms_per_step"] = host_issue / steps * 1e3  # and the time it takes to issue the step's launches
+        host_times["issue_ms_per_step"] = host_issue / steps * 1e3  # the host's time to issue the step's 36 launches
+        # the host's own work for a step (bookkeeping, plan, upload call) with the GPU idle: inside the loop above the upload
+        # also waits for the plan buffer of two steps ago, i.e. for the GPU, which the host runs ahead of
+        host_plan = 0.0
+        for t in range(warm + steps, warm + steps + 8):
+            h0 = time.perf_counter()
+            plan, pos = step_plan(mgr, t)
+            ex.upload_schedule_plan(plan, pos)
+            host_plan += time.perf_counter() - h0
+            ex.sync()
+        host_times["plan_ms_per_step"] = host_plan / 8 * 1e3
         return ev0.elapsed_time(ev1), ex.launch_count - launches0
 
     # ---- leg 1: device-resident throughput (`value`) -------------------------------------------------

@@ -10,6 +10,7 @@
 #ifndef KRIYA_EXECUTOR_HPP
 #define KRIYA_EXECUTOR_HPP
 
+#include <array>
 #include <cstdint>
 #include <stdexcept>
 #include <string>
@@ -203,6 +204,40 @@ class CudaExecutor {
     void tree_verify(uint32_t layer, const void* tree_q, const void* tree_k, const void* tree_v, const uint8_t* tree_mask_host,
                      void* tree_out, const kriya_tree_verify_params& p) {
         check(kriya_cuda_tree_verify(ctx_, layer, tree_q, tree_k, tree_v, tree_mask_host, tree_out, &p));
+    }
+
+    // the RoPE + append half of prefill_batch: the chunks of several sequences in one launch
+    void append_chunk_batch(uint32_t layer, void* q_inout, const void* k, const void* v, const std::vector<uint32_t>& q_start,
+                            const std::vector<uint32_t>& prefix, const std::vector<uint32_t>& count,
+                            const kriya_rope_kv_write_params& rope, const void* q_norm_w = nullptr, const void* k_norm_w = nullptr) {
+        if (q_start.size() != prefix.size() || q_start.size() != count.size())
+            throw CudaError(CudaErrorKind::InvalidExecutionInput, KRIYA_CUDA_INVALID_INPUT, "q_start, prefix and count differ in length");
+        check(kriya_cuda_rope_kv_append_chunk_batch(ctx_, layer, q_inout, k, v, q_norm_w, k_norm_w, uint32_t(q_start.size()),
+                                                    q_start.data(), prefix.data(), count.data(), &rope));
+    }
+
+    // ---- AttentionMaskKind::SlidingWindowCausal { window_size } (crates/kriya-core/src/descriptor.rs:63-70); 0 = plain causal
+    void set_attention_window(uint32_t window_size) { check(kriya_cuda_set_attention_window(ctx_, window_size)); }
+    // bound of every wait inside a kernel (barriers, other CTAs' or GPUs' data); expiry surfaces as ExecutionError
+    void set_wait_limit_us(uint64_t limit_us) { check(kriya_cuda_set_wait_limit_us(ctx_, limit_us)); }
+
+    // ---- one sequence split along the KV axis over several GPUs (one executor per GPU) ---------------------------------
+    // set-up: every rank exports the handle of its exchange buffer, the host passes all handles to every rank (rank order)
+    std::array<uint8_t, KRIYA_COMM_HANDLE_BYTES> comm_export(uint32_t max_rows) {
+        std::array<uint8_t, KRIYA_COMM_HANDLE_BYTES> h{};
+        check(kriya_cuda_comm_export(ctx_, max_rows, h.data()));
+        return h;
+    }
+    void comm_init(uint32_t rank, const std::vector<std::array<uint8_t, KRIYA_COMM_HANDLE_BYTES>>& handles) {
+        check(kriya_cuda_comm_init(ctx_, uint32_t(handles.size()), rank, handles.data()));
+    }
+    // per plan: this rank's block range of every row; per layer (or per step): partial decode, exchange over NVLink, merge
+    void set_kv_ranges(const uint32_t* blk_begin, const uint32_t* blk_end) { check(kriya_cuda_plan_set_ranges(ctx_, blk_begin, blk_end)); }
+    void kvsplit_decode(uint32_t layer, const void* q, void* out, const kriya_bsr_gqa_params& gqa) {
+        check(kriya_cuda_kvsplit_decode(ctx_, layer, q, out, &gqa));
+    }
+    void kvsplit_decode_step(const void* q, void* out, const kriya_bsr_gqa_params& gqa) {
+        check(kriya_cuda_kvsplit_decode_step(ctx_, q, out, &gqa));
     }
 
     uint64_t launch_count() const { return kriya_cuda_launch_count(ctx_); }

@@ -220,14 +220,15 @@ uint32_t build_tc_segments(const int32_t* indptr, const int32_t* last_len, uint3
     return n;
 }
 
-// The whole-page kernel reads one 48-byte record per CTA instead of two entries of the segment-range list: word 0 the
+// The whole-page kernel reads one 144-byte record per CTA instead of two entries of the segment-range list: word 0 the
 // CTA's first segment (the next record's word 0 is its end), word 1 the pages of the CTA's first tile that may be fetched
 // before anything else is known (0 = none: the tile holds the end of its row, which a fused append still has to write),
 // word 2 the place of the first of them inside the tile, word 3 the row of the first piece the CTA works on (UINT32_MAX:
 // none), words 4-7 the pool blocks of those pages, word 8 the position of that row's new token.  With it the first K/V
 // bytes and the first query rows are asked for one memory round trip after the CTA starts instead of three or four
-// (range list, segment, block table or position, data).
-constexpr uint32_t kTcpHdrWords = 12;
+// (range list, segment, block table or position, data).  Words 12-35 are copies of the CTA's first two segment records, which
+// is all most CTAs have: nothing but this record has to arrive before the CTA is set up.
+constexpr uint32_t kTcpHdrWords = 36;  // 12 words of its own + copies of the CTA's first two segment records
 void expand_tcp_headers(uint32_t* ptr, uint32_t ctas, const KriyaTcSeg* segs, const int32_t* indices, uint32_t TP, uint32_t block_size,
                         const uint32_t* positions, uint32_t n_positions) {
     for (uint32_t k = ctas + 1; k-- > 0;) {
@@ -237,8 +238,10 @@ void expand_tcp_headers(uint32_t* ptr, uint32_t ctas, const KriyaTcSeg* segs, co
         h[0] = v;
         h[3] = UINT32_MAX;
     }
+    static_assert(sizeof(KriyaTcSeg) == 48, "two records fill words 12..35");
     for (uint32_t k = 0; k < ctas; ++k) {
         uint32_t* h = ptr + size_t(k) * kTcpHdrWords;
+        for (uint32_t i = 0; i < 2u && h[0] + i < h[kTcpHdrWords]; ++i) memcpy(h + 12u + 12u * i, &segs[h[0] + i], sizeof(KriyaTcSeg));
         for (uint32_t si = h[0]; si < h[kTcpHdrWords]; ++si) {
             const KriyaTcSeg& s = segs[si];
             if (s.blk_hi <= s.blk_lo) continue;

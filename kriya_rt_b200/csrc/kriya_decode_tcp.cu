@@ -339,11 +339,16 @@ decode_tcp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     // this CTA's record: first segment, pages of the first tile that may be fetched at once, their place, their blocks
     // and the row and the position of the first piece
-    const uint4* hdr = reinterpret_cast<const uint4*>(pp.cta_seg_ptr) + size_t(blockIdx.x) * 3u;
+    // followed by copies of the CTA's first two segment records (most CTAs have no more)
+    constexpr uint32_t kHdrVec = 9;  // 144 bytes per record
+    const uint4* hdr = reinterpret_cast<const uint4*>(pp.cta_seg_ptr) + size_t(blockIdx.x) * kHdrVec;
     const uint4 hdr0 = hdr[0], hdr1 = hdr[1];
     const uint32_t hdr_position = reinterpret_cast<const uint32_t*>(hdr + 2)[0];
     const uint32_t seg_begin = hdr0.x;
-    uint32_t seg_end = reinterpret_cast<const uint32_t*>(hdr + 3)[0];
+    const uint32_t seg_end = reinterpret_cast<const uint32_t*>(hdr + kHdrVec)[0];
+    // the two segment records go to shared memory by plain stores (visible after the set-up barrier); further ones come by
+    // a copy that is waited for only by whoever reads them
+    if (tid < 24u) reinterpret_cast<uint32_t*>(segs_s)[tid] = reinterpret_cast<const uint32_t*>(hdr + 3)[tid];
     if (threadIdx.x == 0) pdl_launch_dependents();
     if (seg_begin == seg_end) {
         if (threadIdx.x == 0) {
@@ -383,9 +388,11 @@ decode_tcp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
             mbar_init(&aux_full[1], 1);
             mbar_init(&aux_full[2], 1);
             mbar_fence_init();
-            const uint32_t seg_bytes = min(seg_end - seg_begin, 8u) * uint32_t(sizeof(KriyaTcSeg));
-            mbar_arrive_expect_tx(&aux_full[0], seg_bytes);
-            bulk_g2s(segs_s, pp.segs + seg_begin, seg_bytes, &aux_full[0]);
+            if (seg_end - seg_begin > 2u) {
+                const uint32_t seg_bytes = (min(seg_end - seg_begin, 8u) - 2u) * uint32_t(sizeof(KriyaTcSeg));
+                mbar_arrive_expect_tx(&aux_full[0], seg_bytes);
+                bulk_g2s(segs_s + 2, pp.segs + seg_begin + 2u, seg_bytes, &aux_full[0]);
+            }
             // the few KB of query rows go ahead of the tile: the copy engine takes its requests in order
             if (q_bulk && (pdl == 0u || pdl == 2u)) issue_q0();
             if (early_pages) {
@@ -425,7 +432,17 @@ decode_tcp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
         tmem_alloc(tmem_slot, kTmemCols);
         tmem_relinquish();
     }
-    auto seg_at = [&](uint32_t si) -> KriyaTcSeg { return (si - seg_begin < 8u) ? segs_s[si - seg_begin] : pp.segs[si]; };
+    auto seg_at = [&](uint32_t si) -> KriyaTcSeg {
+        const uint32_t i = si - seg_begin;
+        if (i < 2u) return segs_s[i];
+        if (i >= 8u) return pp.segs[si];
+        if (!mbar_wait(&aux_full[0], 0u, wait_ns)) {  // records 2 .. 7 come by a copy; one that never lands reads as an empty piece
+            atomicMax(a.status, uint32_t(KRIYA_DEV_WAIT_EXPIRED));
+            *abort_flag = 1;
+            return KriyaTcSeg{};
+        }
+        return segs_s[i];
+    };
     // Query and probability rows of heads that do not exist (G < 8) stay zero (they feed unused columns only); with
     // G = 8 every row is written before it is read.
     if (G < 8) {
@@ -434,13 +451,7 @@ decode_tcp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
     }
     fence_async_smem();
     tc_fence_before();
-    __syncthreads();  // every barrier is set up
-    const bool segs_landed = mbar_wait(&aux_full[0], 0u, wait_ns);
-    if (__syncthreads_or(!segs_landed)) {  // nobody works on records that never came
-        if (tid == 0) atomicMax(a.status, uint32_t(KRIYA_DEV_WAIT_EXPIRED));
-        seg_end = seg_begin;
-        first_q = false;
-    }
+    __syncthreads();  // every barrier is set up, the first two segment records are in place
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t Hq = a.num_q_heads;
