@@ -689,6 +689,28 @@ int32_t kriya_cuda_ctx_create(const kriya_cuda_config* cfg_in, kriya_cuda_ctx** 
     c->plan_bytes = off;
     CREATE_TRY(cudaMalloc(&c->d_plan, c->plan_bytes));
     CREATE_TRY(cudaMemsetAsync(c->d_plan, 0, c->plan_bytes, c->stream));
+    {
+        // Every layer of a step reads the same plan (records, segments, page indices) while the
+        // pools stream through L2 between two layers; a persisting window over the plan keeps
+        // those first loads of a launch out of DRAM.  A limit of this process's context only.
+        const char* e = getenv("KRIYA_PLAN_L2_PERSIST");
+        if ((!e || atoi(e) != 0) && prop.persistingL2CacheMaxSize > 0 && prop.accessPolicyMaxWindowSize > 0) {
+            const size_t want = std::min<size_t>(c->plan_bytes, size_t(prop.accessPolicyMaxWindowSize));
+            const size_t carve = std::min<size_t>(size_t(prop.persistingL2CacheMaxSize), std::max<size_t>(want, size_t(1) << 20));
+            if (cudaDeviceSetLimit(cudaLimitPersistingL2CacheSize, carve) == cudaSuccess) {
+                cudaStreamAttrValue av{};
+                av.accessPolicyWindow.base_ptr = c->d_plan;
+                av.accessPolicyWindow.num_bytes = want;
+                av.accessPolicyWindow.hitRatio = carve >= want ? 1.0f : float(double(carve) / double(want));
+                av.accessPolicyWindow.hitProp = cudaAccessPropertyPersisting;
+                av.accessPolicyWindow.missProp = cudaAccessPropertyNormal;
+                if (cudaStreamSetAttribute(c->stream, cudaStreamAttributeAccessPolicyWindow, &av) != cudaSuccess)
+                    (void)cudaGetLastError();
+            } else {
+                (void)cudaGetLastError();
+            }
+        }
+    }
     for (int i = 0; i < 2; ++i) {
         CREATE_TRY(cudaMallocHost(&c->h_plan[i], c->plan_bytes));
         memset(c->h_plan[i], 0, c->plan_bytes);
