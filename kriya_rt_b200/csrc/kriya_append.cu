@@ -179,11 +179,163 @@ __global__ void __launch_bounds__(kAppendWarps * 32) append_kernel(KriyaAppendAr
     }
 }
 
+
+// The same job for 16-bit caches without QK-norm, laid out for bandwidth: D / 16 threads per (token, head) row, each with
+// the eight values at [8 sub, 8 sub + 8) of the row's lower half and their rotation partners in the upper half (two
+// 16-byte loads, two 16-byte stores), value heads as rows of their own that are copied.  A chunk of thousands of tokens
+// moves (Hq + 2 Hkv) * D * 2 B per token in and out; with 2-byte accesses per lane the kernel above reaches a sixth of
+// the HBM rate on it.  Arithmetic per element is the kernel above's, so the cache contents are the same bits.
+constexpr int kAppendVecThreads = 256;
+
+template <typename T>
+__global__ void __launch_bounds__(kAppendVecThreads) append_vec_kernel(KriyaAppendArgs a, uint32_t tpr_log2) {
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint32_t Hq = a.p.num_q_heads, Hkv = a.p.num_kv_heads, D = a.p.head_dim;
+    const uint32_t rows_per_token = Hq + 2u * Hkv;
+    const uint32_t total = a.num_tokens * rows_per_token;
+    const uint32_t gthread = blockIdx.x * uint32_t(kAppendVecThreads) + threadIdx.x;
+    const uint32_t job = gthread >> tpr_log2, sub = gthread & ((1u << tpr_log2) - 1u);
+    bool live = job < total;
+    const uint32_t jc = live ? job : total - 1u;
+    const uint32_t r = jc / rows_per_token, head = jc % rows_per_token;
+    const uint32_t kind = head < Hq ? 0u : head < Hq + Hkv ? 1u : 2u;  // query, key, value row
+    const uint32_t lh = kind == 0u ? head : kind == 1u ? head - Hq : head - Hq - Hkv;
+    const uint32_t bs = a.p.block_size_tokens;
+
+    uint32_t position = 0, blk = 0, slot = 0;
+    if (a.inplace) {
+        position = a.positions[r];
+        if (kind == 2u) live = false;  // values are not touched
+    } else if (a.chunk_mode == 2u) {
+        // a warp's rows belong to a few consecutive tokens; the lanes look each one's sequence up together
+        const uint32_t r_lo = __shfl_sync(0xFFFFFFFFu, r, 0), r_hi = __shfl_sync(0xFFFFFFFFu, r, 31);
+        uint32_t found = UINT32_MAX;
+        for (uint32_t rr = r_lo; rr <= r_hi; ++rr) {
+            uint32_t f = UINT32_MAX;
+            for (uint32_t s0 = 0; s0 < a.n_seqs && f == UINT32_MAX; s0 += 32u) {
+                const uint32_t sq = s0 + lane;
+                const bool hit = sq < a.n_seqs && rr >= a.seq_q_start[sq] && rr - a.seq_q_start[sq] < a.seq_count[sq];
+                const uint32_t m = __ballot_sync(0xFFFFFFFFu, hit);
+                if (m) f = s0 + uint32_t(__ffs(int(m)) - 1);
+            }
+            if (r == rr) found = f;
+        }
+        if (found == UINT32_MAX) {
+            live = false;  // a row between two chunks: not part of this call
+        } else {
+            position = a.seq_prefix[found] + (r - a.seq_q_start[found]);
+            if (kind != 0u && live) {
+                blk = uint32_t(a.indices[a.indptr[found] + int32_t(position / bs)]);
+                slot = position % bs;
+            }
+        }
+    } else if (a.chunk_mode) {
+        position = a.prefix_tokens + r;
+        if (kind != 0u && live) {
+            blk = uint32_t(a.indices[a.indptr[0] + int32_t(position / bs)]);
+            slot = position % bs;
+        }
+    } else {
+        position = a.positions[r];
+        if (kind != 0u && live) {
+            blk = uint32_t(a.indices[a.indptr[r + 1] - 1]);
+            slot = uint32_t(a.last_len[r] - 1);
+        }
+    }
+    if (!live) return;
+    if (kind != 0u && !a.inplace && (blk >= a.num_blocks || slot >= bs)) {
+        if (sub == 0u) atomicMax(a.status, blk >= a.num_blocks ? KRIYA_DEV_BAD_BLOCK_INDEX : KRIYA_DEV_BAD_SLOT);
+        return;
+    }
+
+    const uint32_t half_d = D / 2u, half_rot = a.p.rotary_dim / 2u;
+    const uint32_t e0 = sub * 8u;
+    const size_t cache_off = ((size_t(blk) * bs + slot) * Hkv + lh) * D;
+    if (kind == 2u) {
+        const uint16_t* v_row = reinterpret_cast<const uint16_t*>(a.v_in) + (size_t(r) * Hkv + lh) * D;
+        uint16_t* dst_v = reinterpret_cast<uint16_t*>(a.cache_v) + cache_off;
+        const uint4 lo = *reinterpret_cast<const uint4*>(v_row + e0);
+        const uint4 hi = *reinterpret_cast<const uint4*>(v_row + half_d + e0);
+        *reinterpret_cast<uint4*>(dst_v + e0) = lo;
+        *reinterpret_cast<uint4*>(dst_v + half_d + e0) = hi;
+        return;
+    }
+    uint16_t* q_row = reinterpret_cast<uint16_t*>(a.q_inout) + (size_t(r) * Hq + lh) * D;
+    const uint16_t* k_row = reinterpret_cast<const uint16_t*>(a.k_in) + (size_t(r) * Hkv + lh) * D;
+    const uint16_t* src = kind == 0u ? q_row : k_row;
+    uint16_t* dst = kind == 0u ? q_row : a.inplace ? const_cast<uint16_t*>(k_row) : reinterpret_cast<uint16_t*>(a.cache_k) + cache_off;
+    uint4 lo = *reinterpret_cast<const uint4*>(src + e0);
+    uint4 hi = *reinterpret_cast<const uint4*>(src + half_d + e0);
+    if (e0 < half_rot) {  // half_rot is a multiple of 8 here: the eight pairs are all rotated or none is
+        const bool use_table = a.p.has_table != 0u && position < a.p.max_seq_len && a.table != nullptr;
+        float c[8], sn[8];
+        if (use_table) {
+            const float4* t4 = reinterpret_cast<const float4*>(reinterpret_cast<const float2*>(a.table) + size_t(position) * half_rot + e0);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float4 t = t4[j];
+                c[2 * j] = t.x;
+                sn[2 * j] = t.y;
+                c[2 * j + 1] = t.z;
+                sn[2 * j + 1] = t.w;
+            }
+        } else {
+            const float pos_f = float(position);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float freq_exp = float(2u * (e0 + uint32_t(j))) / float(a.p.rotary_dim);
+                const float inv_freq = powf(a.p.rope_theta, -freq_exp);
+                const float angle = __fmul_rn(pos_f, inv_freq);
+                c[j] = cosf(angle);
+                sn[j] = sinf(angle);
+            }
+        }
+        uint32_t* lw = reinterpret_cast<uint32_t*>(&lo);
+        uint32_t* hw = reinterpret_cast<uint32_t*>(&hi);
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            uint32_t out_lo = 0, out_hi = 0;
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int j = 2 * w + h;
+                const float x0 = T::load(uint16_t(lw[w] >> (16 * h)));
+                const float x1 = T::load(uint16_t(hw[w] >> (16 * h)));
+                const float rot0 = __fmaf_rn(x0, c[j], -__fmul_rn(x1, sn[j]));
+                const float rot1 = __fmaf_rn(x0, sn[j], __fmul_rn(x1, c[j]));
+                out_lo |= uint32_t(T::store(rot0)) << (16 * h);
+                out_hi |= uint32_t(T::store(rot1)) << (16 * h);
+            }
+            lw[w] = out_lo;
+            hw[w] = out_hi;
+        }
+    }
+    *reinterpret_cast<uint4*>(dst + e0) = lo;
+    *reinterpret_cast<uint4*>(dst + half_d + e0) = hi;
+}
+
 }  // namespace kriya
 
 cudaError_t kriya_launch_append(const KriyaAppendArgs& a, uint32_t dtype, cudaStream_t s) {
     const uint32_t jobs = a.num_tokens * (a.p.num_q_heads + a.p.num_kv_heads);
     if (jobs == 0) return cudaSuccess;
+    // the 16-byte form: rows of 64 / 128 / 256 values, whole chunks of eight inside or outside the rotated part, every
+    // base on a 16-byte boundary, a 16-bit cache and no QK-norm (its row sum keeps the one-warp-per-row order)
+    const uint32_t D = a.p.head_dim;
+    const uint32_t tpr_log2 = D == 64u ? 2u : D == 128u ? 3u : D == 256u ? 4u : 0u;
+    auto aligned16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0u; };
+    const bool vec = tpr_log2 != 0u && a.kv_q4 == 0u && a.p.apply_qk_norm == 0u && (a.p.rotary_dim % 16u) == 0u &&
+                     a.p.rotary_dim <= D && aligned16(a.q_inout) && aligned16(a.k_in) &&
+                     (a.inplace || (aligned16(a.v_in) && aligned16(a.cache_k) && aligned16(a.cache_v))) &&
+                     (a.table == nullptr || aligned16(a.table));
+    if (vec) {
+        const uint64_t threads = uint64_t(a.num_tokens) * (a.p.num_q_heads + 2u * a.p.num_kv_heads) << tpr_log2;
+        const uint32_t grid = uint32_t((threads + kriya::kAppendVecThreads - 1) / kriya::kAppendVecThreads);
+        if (dtype == KRIYA_DTYPE_FP16)
+            kriya::append_vec_kernel<kriya::Fp16><<<grid, kriya::kAppendVecThreads, 0, s>>>(a, tpr_log2);
+        else
+            kriya::append_vec_kernel<kriya::Bf16><<<grid, kriya::kAppendVecThreads, 0, s>>>(a, tpr_log2);
+        return cudaGetLastError();
+    }
     const uint32_t grid = (jobs + kriya::kAppendWarps - 1) / kriya::kAppendWarps;
     if (dtype == KRIYA_DTYPE_FP16)
         kriya::append_kernel<kriya::Fp16><<<grid, kriya::kAppendWarps * 32, 0, s>>>(a);

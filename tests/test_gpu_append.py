@@ -50,6 +50,38 @@ def test_append_with_table_is_bit_exact(dtype):
         assert np.array_equal(gv[blk, batch.last_page_len[r] - 1], data["v"][r])
 
 
+@pytest.mark.parametrize("dtype", [W.BF16, W.FP16])
+@pytest.mark.parametrize("head_dim,rotary_dim", [(64, 64), (64, 32), (128, 64), (256, 256), (256, 128), (128, 24)])
+def test_append_head_dims_and_partial_rotary_are_bit_exact(dtype, head_dim, rotary_dim):
+    """Rows of 64 / 128 / 256 values take the 16-byte kernel when the rotated part is a multiple of 16 values, anything
+    else (here rotary_dim 24) the one-warp-per-row kernel; both have to leave the oracle's bits."""
+    shape = W.AttnShape("dims", 8, 2, head_dim, dtype, rope_theta=1e4)
+    ctx = np.array([1, 15, 16, 17, 100, 0, 33])
+    nb = 64
+    batch = W.make_decode_batch(shape, ctx, nb, seed=11)
+    rng = np.random.default_rng(12)
+    n = len(ctx)
+    data = {"q": W.normal16(rng, (n, 8, head_dim), dtype), "k": W.normal16(rng, (n, 2, head_dim), dtype),
+            "v": W.normal16(rng, (n, 2, head_dim), dtype),
+            "cache_k": W.normal16(rng, (nb, 16, 2, head_dim), dtype), "cache_v": W.normal16(rng, (nb, 16, 2, head_dim), dtype)}
+    ex = make_executor(shape, nb, rope_max_seq_len=512, rotary_dim=rotary_dim)
+    fill_cache(ex, 0, data["cache_k"], data["cache_v"])
+    rp = ex.rope_params(has_table=True)
+    assert rp.rotary_dim == rotary_dim
+    q = dev16(data["q"]); k = dev16(data["k"]); v = dev16(data["v"])
+    torch.cuda.synchronize()
+    ex.upload_schedule_plan(batch, batch.positions)
+    ex.rope_kv_append(0, q, k, v, batch.batch, rp)
+    gk, gv = read_cache(ex, 0)
+    gq = host16(q)
+    oq = data["q"].copy(); ok = data["cache_k"].copy(); ov = data["cache_v"].copy()
+    table = O.rope_table(512, rotary_dim, shape.rope_theta)
+    O.rope_kv_append(oq, data["k"], data["v"], ok, ov, batch.page_indptr, batch.page_indices, batch.last_page_len,
+                     batch.positions, oracle_rope(rp), dtype, table=table)
+    ex.close()
+    assert np.array_equal(gq, oq) and np.array_equal(gk, ok) and np.array_equal(gv, ov)
+
+
 def test_append_slot_mapping_qwen_shape():
     shape = W.AttnShape("qwen-small", 16, 2, 128, W.BF16, rope_theta=1e6)
     ctx = np.array([15, 16, 17, 31, 32, 511, 1000, 0])
