@@ -926,10 +926,11 @@ def run_kernel_case(args):
             for prefix in range(0, total, chunk):
                 if with_append:  # each chunk writes its RoPE'd K/V into the 16-token blocks, then attends
                     ex.rope_kv_append_chunk_batch(0, q, kin, vin, starts, [prefix] * n_seq, [chunk] * n_seq, rp)
-                ex.paged_gqa_prefill_batch(0, q, out, starts, [prefix] * n_seq, [chunk] * n_seq, gp)
+                if with_append != 2:
+                    ex.paged_gqa_prefill_batch(0, q, out, starts, [prefix] * n_seq, [chunk] * n_seq, gp)
 
         res = {}
-        for name, with_append in (("append_and_attention", True), ("attention_only", False)):
+        for name, with_append in (("append_and_attention", True), ("attention_only", False), ("append_only", 2)):
             all_chunks(with_append)
             ex.sync()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -945,6 +946,10 @@ def run_kernel_case(args):
                           "tflops": flop / (us * 1e-6) / 1e12, "us_per_pass_attention_only": res["attention_only"],
                           "tflops_attention_only": flop / (res["attention_only"] * 1e-6) / 1e12,
                           "prompt_tokens_per_s_per_layer": n_seq * total / (us * 1e-6),
+                          "us_per_pass_append_only": res["append_only"],
+                          # the append reads q, k, v rows and writes q back and K/V into their blocks: 2 * (Hq + 2 Hkv) * D * 2 B per token
+                          "append_gbs": n_seq * total * 2 * (12 + 4) * 128 * 2 / (res["append_only"] * 1e-6) / 1e9,
+                          "append_frac_of_hbm_peak": n_seq * total * 2 * (12 + 4) * 128 * 2 / (res["append_only"] * 1e-6) / 1e9 / float(measured_peaks()[0]["hbm_gbs"]),
                           "note": "every chunk: one append launch (RoPE + K/V into the paged cache, all prompts) + one attention launch"}))
         ex.close()
     elif case == "prefill":

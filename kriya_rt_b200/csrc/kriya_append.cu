@@ -12,6 +12,8 @@
 // coalescing only (each warp reads and writes whole 128-256 B head rows).
 #include "kriya_device.cuh"
 
+#include <algorithm>
+
 namespace kriya {
 
 constexpr int kAppendWarps = 8;
@@ -180,34 +182,53 @@ __global__ void __launch_bounds__(kAppendWarps * 32) append_kernel(KriyaAppendAr
 }
 
 
-// The same job for 16-bit caches without QK-norm, laid out for bandwidth: D / 16 threads per (token, head) row, each with
-// the eight values at [8 sub, 8 sub + 8) of the row's lower half and their rotation partners in the upper half (two
-// 16-byte loads, two 16-byte stores), value heads as rows of their own that are copied.  A chunk of thousands of tokens
-// moves (Hq + 2 Hkv) * D * 2 B per token in and out; with 2-byte accesses per lane the kernel above reaches a sixth of
-// the HBM rate on it.  Arithmetic per element is the kernel above's, so the cache contents are the same bits.
-constexpr int kAppendVecThreads = 256;
+// The same job for 16-bit caches without QK-norm, laid out for bandwidth.  A thread has the eight values at
+// [8 sub, 8 sub + 8) of the lower half of a row and their rotation partners in the upper half (two 16-byte loads, two
+// 16-byte stores) for kAppendRows (= 2) consecutive rows of one token, the token's rows being its query heads, its key heads
+// and its value heads (copied): the 64 bytes a thread asks for are in flight together and are asked for before anything
+// else, the look-ups of where the token goes (sequence, position, block) and its eight cos / sin pairs are fetched once
+// per thread under them.  A chunk of thousands of tokens moves (Hq + 2 Hkv) * D * 2 B per token in and out; with
+// 2-byte accesses per lane the kernel above reaches a sixth of the HBM rate on it.  Arithmetic per element is the
+// kernel above's, so the cache contents are the same bits.
+constexpr int kAppendVecThreads = 128;  // about: a block is (row groups of a token * D / 16) threads wide and a few tokens deep
 
-template <typename T>
-__global__ void __launch_bounds__(kAppendVecThreads) append_vec_kernel(KriyaAppendArgs a, uint32_t tpr_log2) {
-    const uint32_t lane = threadIdx.x & 31u;
+template <typename T, int kAppendRows>
+__global__ void __launch_bounds__(512) append_vec_kernel(KriyaAppendArgs a, uint32_t tpr_log2, uint32_t bs_log2) {
+    // threadIdx.x = (group of rows of the token, 16-byte piece of a row), threadIdx.y = token of the block
+    const uint32_t lane = (threadIdx.y * blockDim.x + threadIdx.x) & 31u;
     const uint32_t Hq = a.p.num_q_heads, Hkv = a.p.num_kv_heads, D = a.p.head_dim;
-    const uint32_t rows_per_token = Hq + 2u * Hkv;
-    const uint32_t total = a.num_tokens * rows_per_token;
-    const uint32_t gthread = blockIdx.x * uint32_t(kAppendVecThreads) + threadIdx.x;
-    const uint32_t job = gthread >> tpr_log2, sub = gthread & ((1u << tpr_log2) - 1u);
-    bool live = job < total;
-    const uint32_t jc = live ? job : total - 1u;
-    const uint32_t r = jc / rows_per_token, head = jc % rows_per_token;
-    const uint32_t kind = head < Hq ? 0u : head < Hq + Hkv ? 1u : 2u;  // query, key, value row
-    const uint32_t lh = kind == 0u ? head : kind == 1u ? head - Hq : head - Hq - Hkv;
+    const uint32_t rows = Hq + 2u * Hkv;
+    const uint32_t row0 = (threadIdx.x >> tpr_log2) * uint32_t(kAppendRows), sub = threadIdx.x & ((1u << tpr_log2) - 1u);
+    const uint32_t token = blockIdx.x * blockDim.y + threadIdx.y;
+    bool live = token < a.num_tokens;
+    const uint32_t r = live ? token : a.num_tokens - 1u;
     const uint32_t bs = a.p.block_size_tokens;
+    const uint32_t half_d = D / 2u, half_rot = a.p.rotary_dim / 2u;
+    const uint32_t e0 = sub * 8u;
+    uint16_t* q_tok = reinterpret_cast<uint16_t*>(a.q_inout) + size_t(r) * Hq * D;
+    const uint16_t* k_tok = reinterpret_cast<const uint16_t*>(a.k_in) + size_t(r) * Hkv * D;
+    const uint16_t* v_tok = reinterpret_cast<const uint16_t*>(a.v_in) + size_t(r) * Hkv * D;
 
-    uint32_t position = 0, blk = 0, slot = 0;
+    uint4 lo[kAppendRows], hi[kAppendRows];
+#pragma unroll
+    for (int j = 0; j < kAppendRows; ++j) {
+        const uint32_t head = row0 + uint32_t(j);
+        lo[j] = make_uint4(0u, 0u, 0u, 0u);
+        hi[j] = lo[j];
+        if (head < rows && !(a.inplace && head >= Hq + Hkv)) {
+            const uint16_t* src = head < Hq ? q_tok + size_t(head) * D
+                                  : head < Hq + Hkv ? k_tok + size_t(head - Hq) * D : v_tok + size_t(head - Hq - Hkv) * D;
+            lo[j] = *reinterpret_cast<const uint4*>(src + e0);
+            hi[j] = *reinterpret_cast<const uint4*>(src + half_d + e0);
+        }
+    }
+
+    const bool has_kv = row0 + uint32_t(kAppendRows) > Hq;  // this thread has key or value rows: it needs the token's slot
+    uint32_t position = 0, blk = 0, slot = 0, seq_row = 0;
     if (a.inplace) {
         position = a.positions[r];
-        if (kind == 2u) live = false;  // values are not touched
     } else if (a.chunk_mode == 2u) {
-        // a warp's rows belong to a few consecutive tokens; the lanes look each one's sequence up together
+        // a warp's tokens are few and consecutive; the lanes look each one's sequence up together
         const uint32_t r_lo = __shfl_sync(0xFFFFFFFFu, r, 0), r_hi = __shfl_sync(0xFFFFFFFFu, r, 31);
         uint32_t found = UINT32_MAX;
         for (uint32_t rr = r_lo; rr <= r_hi; ++rr) {
@@ -224,51 +245,20 @@ __global__ void __launch_bounds__(kAppendVecThreads) append_vec_kernel(KriyaAppe
             live = false;  // a row between two chunks: not part of this call
         } else {
             position = a.seq_prefix[found] + (r - a.seq_q_start[found]);
-            if (kind != 0u && live) {
-                blk = uint32_t(a.indices[a.indptr[found] + int32_t(position / bs)]);
-                slot = position % bs;
-            }
+            seq_row = found;
         }
     } else if (a.chunk_mode) {
         position = a.prefix_tokens + r;
-        if (kind != 0u && live) {
-            blk = uint32_t(a.indices[a.indptr[0] + int32_t(position / bs)]);
-            slot = position % bs;
-        }
     } else {
         position = a.positions[r];
-        if (kind != 0u && live) {
-            blk = uint32_t(a.indices[a.indptr[r + 1] - 1]);
-            slot = uint32_t(a.last_len[r] - 1);
-        }
     }
     if (!live) return;
-    if (kind != 0u && !a.inplace && (blk >= a.num_blocks || slot >= bs)) {
-        if (sub == 0u) atomicMax(a.status, blk >= a.num_blocks ? KRIYA_DEV_BAD_BLOCK_INDEX : KRIYA_DEV_BAD_SLOT);
-        return;
-    }
 
-    const uint32_t half_d = D / 2u, half_rot = a.p.rotary_dim / 2u;
-    const uint32_t e0 = sub * 8u;
-    const size_t cache_off = ((size_t(blk) * bs + slot) * Hkv + lh) * D;
-    if (kind == 2u) {
-        const uint16_t* v_row = reinterpret_cast<const uint16_t*>(a.v_in) + (size_t(r) * Hkv + lh) * D;
-        uint16_t* dst_v = reinterpret_cast<uint16_t*>(a.cache_v) + cache_off;
-        const uint4 lo = *reinterpret_cast<const uint4*>(v_row + e0);
-        const uint4 hi = *reinterpret_cast<const uint4*>(v_row + half_d + e0);
-        *reinterpret_cast<uint4*>(dst_v + e0) = lo;
-        *reinterpret_cast<uint4*>(dst_v + half_d + e0) = hi;
-        return;
-    }
-    uint16_t* q_row = reinterpret_cast<uint16_t*>(a.q_inout) + (size_t(r) * Hq + lh) * D;
-    const uint16_t* k_row = reinterpret_cast<const uint16_t*>(a.k_in) + (size_t(r) * Hkv + lh) * D;
-    const uint16_t* src = kind == 0u ? q_row : k_row;
-    uint16_t* dst = kind == 0u ? q_row : a.inplace ? const_cast<uint16_t*>(k_row) : reinterpret_cast<uint16_t*>(a.cache_k) + cache_off;
-    uint4 lo = *reinterpret_cast<const uint4*>(src + e0);
-    uint4 hi = *reinterpret_cast<const uint4*>(src + half_d + e0);
-    if (e0 < half_rot) {  // half_rot is a multiple of 8 here: the eight pairs are all rotated or none is
+    // the token's cos / sin pairs go out before the block look-up: they only need the position
+    const bool rotated = e0 < half_rot;  // half_rot is a multiple of 8 here: the eight pairs are all rotated or none is
+    float c[8], sn[8];
+    if (rotated) {
         const bool use_table = a.p.has_table != 0u && position < a.p.max_seq_len && a.table != nullptr;
-        float c[8], sn[8];
         if (use_table) {
             const float4* t4 = reinterpret_cast<const float4*>(reinterpret_cast<const float2*>(a.table) + size_t(position) * half_rot + e0);
 #pragma unroll
@@ -290,27 +280,68 @@ __global__ void __launch_bounds__(kAppendVecThreads) append_vec_kernel(KriyaAppe
                 sn[j] = sinf(angle);
             }
         }
-        uint32_t* lw = reinterpret_cast<uint32_t*>(&lo);
-        uint32_t* hw = reinterpret_cast<uint32_t*>(&hi);
-#pragma unroll
-        for (int w = 0; w < 4; ++w) {
-            uint32_t out_lo = 0, out_hi = 0;
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                const int j = 2 * w + h;
-                const float x0 = T::load(uint16_t(lw[w] >> (16 * h)));
-                const float x1 = T::load(uint16_t(hw[w] >> (16 * h)));
-                const float rot0 = __fmaf_rn(x0, c[j], -__fmul_rn(x1, sn[j]));
-                const float rot1 = __fmaf_rn(x0, sn[j], __fmul_rn(x1, c[j]));
-                out_lo |= uint32_t(T::store(rot0)) << (16 * h);
-                out_hi |= uint32_t(T::store(rot1)) << (16 * h);
-            }
-            lw[w] = out_lo;
-            hw[w] = out_hi;
+    }
+    bool slot_ok = true;
+    if (has_kv && !a.inplace) {
+        if (a.chunk_mode) {
+            blk = uint32_t(a.indices[a.indptr[seq_row] + int32_t(position >> bs_log2)]);
+            slot = position & (bs - 1u);
+        } else {
+            blk = uint32_t(a.indices[a.indptr[r + 1] - 1]);
+            slot = uint32_t(a.last_len[r] - 1);
+        }
+        if (blk >= a.num_blocks || slot >= bs) {
+            if (sub == 0u) atomicMax(a.status, blk >= a.num_blocks ? KRIYA_DEV_BAD_BLOCK_INDEX : KRIYA_DEV_BAD_SLOT);
+            slot_ok = false;  // the token's key and value rows are left out, its query rows are still rotated
         }
     }
-    *reinterpret_cast<uint4*>(dst + e0) = lo;
-    *reinterpret_cast<uint4*>(dst + half_d + e0) = hi;
+    const size_t cache_tok = (size_t(blk) * bs + slot) * Hkv * D;
+
+#pragma unroll
+    for (int j = 0; j < kAppendRows; ++j) {
+        const uint32_t head = row0 + uint32_t(j);
+        if (head >= rows) break;
+        if (head >= Hq + Hkv) {  // a value row: the bits as they came
+            if (a.inplace || !slot_ok) continue;
+            uint16_t* dst_v = reinterpret_cast<uint16_t*>(a.cache_v) + cache_tok + size_t(head - Hq - Hkv) * D;
+            *reinterpret_cast<uint4*>(dst_v + e0) = lo[j];
+            *reinterpret_cast<uint4*>(dst_v + half_d + e0) = hi[j];
+            continue;
+        }
+        uint16_t* dst;
+        if (head < Hq) {
+            dst = q_tok + size_t(head) * D;
+        } else if (a.inplace) {
+            dst = const_cast<uint16_t*>(k_tok) + size_t(head - Hq) * D;
+        } else {
+            if (!slot_ok) continue;
+            dst = reinterpret_cast<uint16_t*>(a.cache_k) + cache_tok + size_t(head - Hq) * D;
+        }
+        if (rotated) {
+            uint32_t lw[4] = {lo[j].x, lo[j].y, lo[j].z, lo[j].w};
+            uint32_t hw[4] = {hi[j].x, hi[j].y, hi[j].z, hi[j].w};
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                const float2 x0 = T::load2(lw[w]), x1 = T::load2(hw[w]);
+                const float r0a = __fmaf_rn(x0.x, c[2 * w], -__fmul_rn(x1.x, sn[2 * w]));
+                const float r1a = __fmaf_rn(x0.x, sn[2 * w], __fmul_rn(x1.x, c[2 * w]));
+                const float r0b = __fmaf_rn(x0.y, c[2 * w + 1], -__fmul_rn(x1.y, sn[2 * w + 1]));
+                const float r1b = __fmaf_rn(x0.y, sn[2 * w + 1], __fmul_rn(x1.y, c[2 * w + 1]));
+                // the paired conversion leaves the bits of T::store on every value that is not a NaN
+                if (r0a == r0a && r0b == r0b && r1a == r1a && r1b == r1b) {
+                    lw[w] = T::pack2(r0a, r0b);
+                    hw[w] = T::pack2(r1a, r1b);
+                } else {
+                    lw[w] = uint32_t(T::store(r0a)) | (uint32_t(T::store(r0b)) << 16);
+                    hw[w] = uint32_t(T::store(r1a)) | (uint32_t(T::store(r1b)) << 16);
+                }
+            }
+            lo[j] = make_uint4(lw[0], lw[1], lw[2], lw[3]);
+            hi[j] = make_uint4(hw[0], hw[1], hw[2], hw[3]);
+        }
+        *reinterpret_cast<uint4*>(dst + e0) = lo[j];
+        *reinterpret_cast<uint4*>(dst + half_d + e0) = hi[j];
+    }
 }
 
 }  // namespace kriya
@@ -323,17 +354,27 @@ cudaError_t kriya_launch_append(const KriyaAppendArgs& a, uint32_t dtype, cudaSt
     const uint32_t D = a.p.head_dim;
     const uint32_t tpr_log2 = D == 64u ? 2u : D == 128u ? 3u : D == 256u ? 4u : 0u;
     auto aligned16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0u; };
-    const bool vec = tpr_log2 != 0u && a.kv_q4 == 0u && a.p.apply_qk_norm == 0u && (a.p.rotary_dim % 16u) == 0u &&
+    const uint32_t bs = a.p.block_size_tokens;
+    uint32_t bs_log2 = 0;
+    while ((1u << bs_log2) < bs) ++bs_log2;
+    const uint32_t R = 2u;  // rows of a token per thread (four measured slower: 87 registers, 20 resident warps)
+    const uint32_t bdx = ((a.p.num_q_heads + 2u * a.p.num_kv_heads + R - 1u) / R) << tpr_log2;  // threads of one token
+    // whole warps only (the lanes of a warp look the sequence up together): the block's depth is a multiple of 32 / gcd(width, 32)
+    uint32_t gcd32 = 32u;
+    while (bdx % gcd32 != 0u) gcd32 >>= 1;
+    const uint32_t ystep = 32u / gcd32;
+    const uint32_t bdy = bdx == 0u ? 0u : ystep * std::max(1u, (uint32_t(kriya::kAppendVecThreads) + bdx * ystep - 1u) / (bdx * ystep));
+    const bool vec = tpr_log2 != 0u && (1u << bs_log2) == bs && bdx * bdy <= 512u && a.kv_q4 == 0u && a.p.apply_qk_norm == 0u && (a.p.rotary_dim % 16u) == 0u &&
                      a.p.rotary_dim <= D && aligned16(a.q_inout) && aligned16(a.k_in) &&
                      (a.inplace || (aligned16(a.v_in) && aligned16(a.cache_k) && aligned16(a.cache_v))) &&
                      (a.table == nullptr || aligned16(a.table));
     if (vec) {
-        const uint64_t threads = uint64_t(a.num_tokens) * (a.p.num_q_heads + 2u * a.p.num_kv_heads) << tpr_log2;
-        const uint32_t grid = uint32_t((threads + kriya::kAppendVecThreads - 1) / kriya::kAppendVecThreads);
+        const dim3 block(bdx, bdy);
+        const uint32_t grid = (a.num_tokens + block.y - 1u) / block.y;
         if (dtype == KRIYA_DTYPE_FP16)
-            kriya::append_vec_kernel<kriya::Fp16><<<grid, kriya::kAppendVecThreads, 0, s>>>(a, tpr_log2);
+            kriya::append_vec_kernel<kriya::Fp16, 2><<<grid, block, 0, s>>>(a, tpr_log2, bs_log2);
         else
-            kriya::append_vec_kernel<kriya::Bf16><<<grid, kriya::kAppendVecThreads, 0, s>>>(a, tpr_log2);
+            kriya::append_vec_kernel<kriya::Bf16, 2><<<grid, block, 0, s>>>(a, tpr_log2, bs_log2);
         return cudaGetLastError();
     }
     const uint32_t grid = (jobs + kriya::kAppendWarps - 1) / kriya::kAppendWarps;
