@@ -301,11 +301,54 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
             const bool diag = key0 + kKvTile - 1u > qt.pos0;  // some row of the tile masks some key
             // some key of the tile lies in front of some row's window (the last row's window starts latest)
             const bool wdiag = window != 0u && key0 + window < qt.pos0 + tile_rows;
-            // the whole score row into registers, once
+            // The whole score row goes into registers, once.  A tile that needs no mask and comes behind the first one is
+            // taken a quarter at a time against the exponent reference the row already has: the next quarter's load runs
+            // under this quarter's maxima, exponentials and probability stores (P quarter c lies over score columns that
+            // have been read: 16c .. 16c+15 against 32c ..).  The tile's own maximum is known at the end; if it is above
+            // the reference by more than the threshold for some row of the warp, the tile is done again from the
+            // registers, the ordinary way.
             uint32_t sr[4][32];
+            const bool fast = j > 0 && !softcap && !diag && !wdiag && !__any_sync(0xFFFFFFFFu, m_used == -INFINITY);
+            bool redo = false;
+            if (fast) {
+                const float2 sc2f = make_float2(scale2, scale2), neg_m2f = make_float2(-m_used, -m_used);
+                float2 psum2f = make_float2(0.0f, 0.0f);
+                float mq[4];
+                tmem_ld32(s_addr, sr[0]);
+                tmem_wait_ld();
 #pragma unroll
-            for (int c = 0; c < 4; ++c) tmem_ld32(s_addr + c * 32, sr[c]);
-            tmem_wait_ld();
+                for (int c = 0; c < 4; ++c) {
+                    if (c + 1 < 4) tmem_ld32(s_addr + (c + 1) * 32, sr[c + 1]);
+                    float ma = -INFINITY, mb = -INFINITY;
+#pragma unroll
+                    for (int i = 0; i < 32; i += 4) {
+                        ma = max3(ma, __uint_as_float(sr[c][i]), __uint_as_float(sr[c][i + 1]));
+                        mb = max3(mb, __uint_as_float(sr[c][i + 2]), __uint_as_float(sr[c][i + 3]));
+                    }
+                    mq[c] = fmaxf(ma, mb);
+                    uint32_t packed[16];
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const float2 e = __ffma2_rn(make_float2(__uint_as_float(sr[c][2 * i]), __uint_as_float(sr[c][2 * i + 1])), sc2f, neg_m2f);
+                        const float2 pr = make_float2(fast_exp2(e.x), fast_exp2(e.y));
+                        psum2f = __fadd2_rn(psum2f, pr);
+                        packed[i] = T::pack2(pr.x, pr.y);
+                    }
+                    tmem_st16(s_addr + c * 16, packed);
+                    if (c + 1 < 4) tmem_wait_ld();
+                }
+                const float m_tile_f = fmaxf(max3(mq[0], mq[1], mq[2]), mq[3]) * scale2;
+                redo = __any_sync(0xFFFFFFFFu, m_tile_f > m_used + kRescaleThreshold);
+                if (!redo) {
+                    tmem_wait_st();
+                    l_run += psum2f.x + psum2f.y;
+                }
+            } else {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) tmem_ld32(s_addr + c * 32, sr[c]);
+                tmem_wait_ld();
+            }
+            if (!fast || redo) {
             // the scores stay raw in registers; scale and exponent reference are folded into one fma per pair below
             if (softcap) {
 #pragma unroll
@@ -378,6 +421,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
             const float psum = psum2.x + psum2.y;
             tmem_wait_st();
             l_run = l_run * alpha + psum;
+            }
             // Only the last tile can hold rows that are not valid V data: slots past the end of the sequence (loaded, but
             // they may hold anything) and pages the producer did not load (shared memory as the previous kernel left
             // it).  Their probabilities are zero, but 0 x NaN is NaN, so head A's warpgroup clears those rows; P.V of
