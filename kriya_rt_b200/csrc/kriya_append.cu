@@ -47,9 +47,6 @@ __device__ __forceinline__ void q4kv_store_group(uint8_t* block, float v, uint32
 
 template <typename T>
 __global__ void __launch_bounds__(kAppendWarps * 32) append_kernel(KriyaAppendArgs a) {
-    // launched with programmatic stream serialisation: resident early, working once the launch in front is complete
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const uint32_t lane = threadIdx.x & 31u;
     const uint32_t Hq = a.p.num_q_heads, Hkv = a.p.num_kv_heads, D = a.p.head_dim;
     const uint32_t heads = Hq + Hkv;
@@ -197,8 +194,6 @@ constexpr int kAppendVecThreads = 128;  // about: a block is (row groups of a to
 
 template <typename T, int kAppendRows>
 __global__ void __launch_bounds__(512) append_vec_kernel(KriyaAppendArgs a, uint32_t tpr_log2, uint32_t bs_log2) {
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     // threadIdx.x = (group of rows of the token, 16-byte piece of a row), threadIdx.y = token of the block
     const uint32_t lane = (threadIdx.y * blockDim.x + threadIdx.x) & 31u;
     const uint32_t Hq = a.p.num_q_heads, Hkv = a.p.num_kv_heads, D = a.p.head_dim;
@@ -351,21 +346,6 @@ __global__ void __launch_bounds__(512) append_vec_kernel(KriyaAppendArgs a, uint
 
 }  // namespace kriya
 
-// A launch that may become resident before the launch in front of it has finished (the kernels wait at their top).
-template <typename Kern, typename... Args>
-static cudaError_t launch_pdl(Kern kern, dim3 grid, dim3 block, cudaStream_t s, Args... args) {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = grid;
-    cfg.blockDim = block;
-    cfg.stream = s;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, kern, args...);
-}
-
 cudaError_t kriya_launch_append(const KriyaAppendArgs& a, uint32_t dtype, cudaStream_t s) {
     const uint32_t jobs = a.num_tokens * (a.p.num_q_heads + a.p.num_kv_heads);
     if (jobs == 0) return cudaSuccess;
@@ -392,11 +372,15 @@ cudaError_t kriya_launch_append(const KriyaAppendArgs& a, uint32_t dtype, cudaSt
         const dim3 block(bdx, bdy);
         const uint32_t grid = (a.num_tokens + block.y - 1u) / block.y;
         if (dtype == KRIYA_DTYPE_FP16)
-            return launch_pdl(kriya::append_vec_kernel<kriya::Fp16, 2>, dim3(grid), block, s, a, tpr_log2, bs_log2);
-        return launch_pdl(kriya::append_vec_kernel<kriya::Bf16, 2>, dim3(grid), block, s, a, tpr_log2, bs_log2);
+            kriya::append_vec_kernel<kriya::Fp16, 2><<<grid, block, 0, s>>>(a, tpr_log2, bs_log2);
+        else
+            kriya::append_vec_kernel<kriya::Bf16, 2><<<grid, block, 0, s>>>(a, tpr_log2, bs_log2);
+        return cudaGetLastError();
     }
     const uint32_t grid = (jobs + kriya::kAppendWarps - 1) / kriya::kAppendWarps;
     if (dtype == KRIYA_DTYPE_FP16)
-        return launch_pdl(kriya::append_kernel<kriya::Fp16>, dim3(grid), dim3(kriya::kAppendWarps * 32), s, a);
-    return launch_pdl(kriya::append_kernel<kriya::Bf16>, dim3(grid), dim3(kriya::kAppendWarps * 32), s, a);
+        kriya::append_kernel<kriya::Fp16><<<grid, kriya::kAppendWarps * 32, 0, s>>>(a);
+    else
+        kriya::append_kernel<kriya::Bf16><<<grid, kriya::kAppendWarps * 32, 0, s>>>(a);
+    return cudaGetLastError();
 }

@@ -158,12 +158,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    // Launched with programmatic stream serialisation: the set-up above runs under the tail of the launch in front (the
-    // append of this chunk, or the expansion of a Q4 cache), everything below reads what that launch wrote.  The launch
-    // behind (the merge of cut tiles, the next chunk's append) may take the SMs this grid's last wave leaves free; it
-    // waits for this grid in the same way.
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     if (warp >= 8) {
     setmaxnreg_dec<kRegsWorkers>();
@@ -595,20 +589,7 @@ cudaError_t launch_prefill_t(const KriyaPrefillArgs& a, const CUtensorMap& mk, c
     pp.q_tiles = a.n_tiles;
     const uint32_t group = a.num_q_heads / a.num_kv_heads;
     pp.pairs = (group + 1u) / 2u;
-    {
-        cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3(pp.q_tiles * pp.pairs * a.num_kv_heads);
-        cfg.blockDim = dim3(kPrefillThreads);
-        cfg.dynamicSmemBytes = smem;
-        cfg.stream = s;
-        cudaLaunchAttribute attr[1];
-        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[0].val.programmaticStreamSerializationAllowed = 1;
-        cfg.attrs = attr;
-        cfg.numAttrs = 1;
-        e = cudaLaunchKernelEx(&cfg, kern, mk, mv, mq, mo, pp);
-        if (e != cudaSuccess) return e;
-    }
+    kern<<<pp.q_tiles * pp.pairs * a.num_kv_heads, kPrefillThreads, smem, s>>>(mk, mv, mq, mo, pp);
     if (a.n_merge != 0u) {
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(a.n_merge, pp.pairs * a.num_kv_heads, 2 * kQTile / 8);
