@@ -50,8 +50,10 @@ constexpr uint32_t kTileKBytes = kPagesPerTile * kPageBytes;  // 32 KB
 constexpr uint32_t kStageBytes = 2 * kTileKBytes;             // K tile + V tile
 // The K tile is kept as two halves of d: [half][page][head][token][64 d], so that the tile's 128 (page, head, token) rows are
 // one MMA operand per half and the two halves are steps of the same accumulation.
-constexpr uint32_t kKHalfPage = 4096;                         // one half of d of a page: 2 heads x 16 tokens x 128 B
-constexpr uint32_t kKHalfTile = kTileKBytes / 2;
+// A K page lands as sixteen 1 KB blocks of eight rows, [eight-token group][head][half of d][token][64]: for one half of d the
+// blocks of a whole tile are 2 KB apart, all of them, so the tile's 128 (page, group, head, token) rows are one K-major MMA
+// operand per half (8-row groups 2 KB apart) although every page arrived as a single copy.
+constexpr uint32_t kKBlock = 1024;
 constexpr int kStages = 3;
 constexpr int kQBufs = 3;
 constexpr uint32_t kQBytes = 32 * 128;           // 32 operand rows (half', head) x 128 B
@@ -136,13 +138,12 @@ __device__ __forceinline__ void tma_load_page(void* dst_smem, const CUtensorMap*
         "l"(map), "r"(0), "r"(page), "r"(smem_u32(bar))
         : "memory");
 }
-// One half of d of a K page (both heads, 16 tokens x 64 d each = 4 KB): coordinates (0, 0, half, 0, page) of the map whose
-// box is one half.
-__device__ __forceinline__ void tma_load_khalf(void* dst_smem, const CUtensorMap* map, int32_t half, int32_t page, uint64_t* bar) {
+// A whole K page through the K map, whose outermost dimension counts (page, eight-token group): coordinates (0, 0, 0, 0, 2 page).
+__device__ __forceinline__ void tma_load_kpage(void* dst_smem, const CUtensorMap* map, int32_t page, uint64_t* bar) {
     asm volatile(
-        "cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %2, %3, %2, %4}], [%5];" ::"r"(
+        "cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %2, %2, %2, %3}], [%4];" ::"r"(
             smem_u32(dst_smem)),
-        "l"(map), "r"(0), "r"(half), "r"(page), "r"(smem_u32(bar))
+        "l"(map), "r"(0), "r"(2 * page), "r"(smem_u32(bar))
         : "memory");
 }
 // 4 consecutive TMEM columns of this thread's lane.
@@ -409,8 +410,7 @@ decode_tcp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
             }
             const uint32_t slot = hdr0.z + lane;  // the page's place in the tile
             const int32_t page = int32_t(pp.page0 + blk);
-            tma_load_khalf(sKV + slot * kKHalfPage, &map_k, 0, page, &kv_full[0]);
-            tma_load_khalf(sKV + kKHalfTile + slot * kKHalfPage, &map_k, 1, page, &kv_full[0]);
+            tma_load_kpage(sKV + slot * kPageBytes, &map_k, page, &kv_full[0]);
             tma_load_page(sKV + kTileKBytes + slot * kPageBytes, &map_v, page, &v_full[0]);
         }
     }
@@ -500,8 +500,7 @@ decode_tcp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                         uint8_t* st = sKV + stage * kStageBytes;
                         const uint32_t slot = my_page - t * kPagesPerTile;
                         const int32_t page = int32_t(pp.page0) + blk;
-                        tma_load_khalf(st + slot * kKHalfPage, &map_k, 0, page, &kv_full[stage]);
-                        tma_load_khalf(st + kKHalfTile + slot * kKHalfPage, &map_k, 1, page, &kv_full[stage]);
+                        tma_load_kpage(st + slot * kPageBytes, &map_k, page, &kv_full[stage]);
                         tma_load_page(st + kTileKBytes + slot * kPageBytes, &map_v, page, &v_full[stage]);
                     }
                 }
@@ -608,7 +607,7 @@ decode_tcp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
         // one-lane branch every instruction costs about a hundred cycles and the issue rate, not the memory stream,
         // bounds the kernel.
         const uint32_t el = (lane == 0) ? 1u : 0u;
-        const uint64_t kv_desc = smem_desc_sw128(smem_u32(sKV), 16, 1024);       // K rows: K-major, 8-row groups 1 KB apart
+        const uint64_t kv_desc = smem_desc_sw128(smem_u32(sKV), 16, 2 * kKBlock);  // K rows of one half of d: K-major, 8-row groups 2 KB apart
         // V: MN-major, M = 128 d as two groups of 64 (the head's two planes, 2 KB apart), 8-token groups 1 KB apart
         const uint64_t v_desc = smem_desc_sw128(smem_u32(sKV), 2048, 1024);
         const uint64_t q_desc = smem_desc_sw128(smem_u32(sQ), 16, 1024);
@@ -622,7 +621,7 @@ decode_tcp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
             for (int hf = 0; hf < 2; ++hf)
 #pragma unroll
                 for (int ks = 0; ks < 4; ++ks)
-                    umma_ss_pred(d_tmem, ad + uint64_t((uint32_t(hf) * kKHalfTile + uint32_t(ks) * 32u) >> 4),
+                    umma_ss_pred(d_tmem, ad + uint64_t((uint32_t(hf) * kKBlock + uint32_t(ks) * 32u) >> 4),
                                  bd + uint64_t((uint32_t(hf) * 2048u + uint32_t(ks) * 32u) >> 4), IDESC_S, (hf | ks) ? 1u : 0u, el);
             umma_commit_pred(&s_full[gg & 1u], el);
         };
@@ -710,7 +709,7 @@ decode_tcp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
         constexpr int GH = (G + 1) / 2;
         const uint32_t grp = warp >> 2, pg = warp & 3u;
         const uint32_t lane_addr = (pg * 32u) << 16;
-        const uint32_t hd = lane >> 4, tk = lane & 15u;
+        const uint32_t hd = (lane >> 3) & 1u, tk = ((lane >> 4) << 3) | (lane & 7u);  // rows of a page: (token group, head, token)
         const uint32_t jj0 = grp ? uint32_t(GH) : 0u;             // first query head (within the KV head) of this thread
         const uint32_t nj = grp ? uint32_t(G - GH) : uint32_t(GH);  // and how many
         const bool softcap = a.logit_softcap > 0.0f;
@@ -827,9 +826,9 @@ decode_tcp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
 #pragma unroll
                     for (int i = 0; i < GH; ++i) mx[i] = s[i];
 #pragma unroll
-                    for (int off = 8; off >= 1; off >>= 1)
+                    for (int oi = 0; oi < 4; ++oi)  // the head's 16 lanes differ in bits 4, 2, 1, 0
 #pragma unroll
-                        for (int i = 0; i < GH; ++i) mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xFFFFFFFFu, mx[i], off));
+                        for (int i = 0; i < GH; ++i) mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xFFFFFFFFu, mx[i], oi == 0 ? 16 : (4 >> (oi - 1))));
                     if (tk == 0u) {
 #pragma unroll
                         for (int i = 0; i < GH; ++i)
@@ -911,9 +910,9 @@ decode_tcp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
 #pragma unroll
             for (int i = 0; i < GH; ++i) l_tot[i] = l_own[i];
 #pragma unroll
-            for (int off = 8; off >= 1; off >>= 1)
+            for (int oi = 0; oi < 4; ++oi)
 #pragma unroll
-                for (int i = 0; i < GH; ++i) l_tot[i] += __shfl_xor_sync(0xFFFFFFFFu, l_tot[i], off);
+                for (int i = 0; i < GH; ++i) l_tot[i] += __shfl_xor_sync(0xFFFFFFFFu, l_tot[i], oi == 0 ? 16 : (4 >> (oi - 1)));
             if (tk == 0u) {
 #pragma unroll
                 for (int i = 0; i < GH; ++i)
@@ -1128,8 +1127,9 @@ using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, voi
 }
 
 // 5-D maps over the K and V pools of all layers: dimensions (d_lo 64, token 16, half of d 2, head 2, page), strides (512,
-// 128, 256, 8192) bytes.  A V box is a whole page (lands as [head][half][token][64]); a K box is one half of d of a page
-// (lands as [head][token][64]), so that the kernel can keep a tile's K as [half][page][head][token][64].
+// 128, 256, 8192) bytes for V: a V box is a whole page and lands as [head][half][token][64].  The K map splits the tokens:
+// dimensions (d_lo 64, token 8, half 2, head 2, (page, eight-token group)), strides (512, 128, 256, 4096) bytes; its box
+// {64, 8, 2, 2, 2} is a whole page as well and lands as [group][head][half][token][64] (see kKBlock).
 cudaError_t kriya_decode_tcp_encode_maps(void* pool_k, void* pool_v, uint64_t total_pages, void* out_map_k, void* out_map_v) {
     static EncodeFn enc = nullptr;
     if (enc == nullptr) {
@@ -1140,14 +1140,14 @@ cudaError_t kriya_decode_tcp_encode_maps(void* pool_k, void* pool_v, uint64_t to
         if (fn == nullptr || qres != cudaDriverEntryPointSuccess) return cudaErrorNotSupported;
         enc = reinterpret_cast<EncodeFn>(fn);
     }
-    const cuuint64_t dims[5] = {64, 16, 2, 2, total_pages};
-    const cuuint64_t strides[4] = {512, 128, 256, 8192};
-    const cuuint32_t box_v[5] = {64, 16, 2, 2, 1}, box_k[5] = {64, 16, 1, 2, 1};
+    const cuuint64_t dims_v[5] = {64, 16, 2, 2, total_pages}, dims_k[5] = {64, 8, 2, 2, 2 * total_pages};
+    const cuuint64_t strides_v[4] = {512, 128, 256, 8192}, strides_k[4] = {512, 128, 256, 4096};
+    const cuuint32_t box_v[5] = {64, 16, 2, 2, 1}, box_k[5] = {64, 8, 2, 2, 2};
     const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
     void* pools[2] = {pool_k, pool_v};
     void* outs[2] = {out_map_k, out_map_v};
     for (int i = 0; i < 2; ++i) {
-        const CUresult r = enc(static_cast<CUtensorMap*>(outs[i]), CU_TENSOR_MAP_DATA_TYPE_UINT16, 5, pools[i], dims, strides, i == 0 ? box_k : box_v, estr,
+        const CUresult r = enc(static_cast<CUtensorMap*>(outs[i]), CU_TENSOR_MAP_DATA_TYPE_UINT16, 5, pools[i], i == 0 ? dims_k : dims_v, i == 0 ? strides_k : strides_v, i == 0 ? box_k : box_v, estr,
                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
