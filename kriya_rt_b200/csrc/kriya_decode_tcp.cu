@@ -315,7 +315,8 @@ decode_tcp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
     float* ml_s = alpha_s + 16;                         // [16][2] (m, l) of the piece per query head
     uint64_t* bars = reinterpret_cast<uint64_t*>(ml_s + 32);
     uint64_t* kv_full = bars;                     // [stages]: the K half of a stage has landed
-                                                  // (bars + kStages .. + 2 are spare)
+    uint64_t* k_empty = bars + kStages;           // [stages]: the score MMAs of the stage's tile are complete, its K half may be
+                                                  // loaded again (the V half and the rest of the stage wait for tile_done)
     uint64_t* s_full = bars + 2 * kStages;        // [2]
     uint64_t* p_ready = bars + 2 * kStages + 2;   // [2], 256 arrivals
                                                   // (bars + 2 * kStages + 4 .. + 5 are spare)
@@ -381,6 +382,7 @@ decode_tcp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
         if (lane == 0) {
             for (int s = 0; s < kStages; ++s) {
                 mbar_init(&kv_full[s], 1);
+                mbar_init(&k_empty[s], 1);
                 mbar_init(&v_full[s], 1);
                 mbar_init(&tile_done[s], 1);
                 mbar_init(&tile_done[kStages + s], 1);
@@ -482,7 +484,8 @@ decode_tcp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                 if (g > 0u || early_pages == 0u) {  // the CTA's first tile may be on its way already
                     int32_t blk = pf_blk;
                     if (!pf_valid && lane < npages) blk = table[my_page];
-                    if (g >= kStages && !warp_wait_l(wait_ns, &tile_done[(g - kStages) % 6u], ((g - kStages) / 6u) & 1u)) { ok = false; break; }
+                    // the K half is free as soon as the scores of the tile it held are complete, a tile-time before the rest
+                    if (g >= kStages && !warp_wait_l(wait_ns, &k_empty[stage], ((g / kStages) - 1u) & 1u)) { ok = false; break; }
                     if (owns_last && t + 1u == t1 && !warp_wait_l(wait_ns, &kv_ready[runs % uint32_t(kQBufs)], (runs / uint32_t(kQBufs)) & 1u)) {
                         ok = false;
                         break;
@@ -491,18 +494,16 @@ decode_tcp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                         atomicMax(a.status, uint32_t(KRIYA_DEV_BAD_BLOCK_INDEX));
                         blk = 0;
                     }
-                    if (lane == 0) {
-                        mbar_arrive_expect_tx(&kv_full[stage], npages * kPageBytes);
-                        mbar_arrive_expect_tx(&v_full[stage], npages * kPageBytes);
-                    }
+                    uint8_t* st = sKV + stage * kStageBytes;
+                    const uint32_t slot = my_page - t * kPagesPerTile;
+                    const int32_t page = int32_t(pp.page0) + blk;
+                    if (lane == 0) mbar_arrive_expect_tx(&kv_full[stage], npages * kPageBytes);
                     __syncwarp();
-                    if (lane < npages) {
-                        uint8_t* st = sKV + stage * kStageBytes;
-                        const uint32_t slot = my_page - t * kPagesPerTile;
-                        const int32_t page = int32_t(pp.page0) + blk;
-                        tma_load_kpage(st + slot * kPageBytes, &map_k, page, &kv_full[stage]);
-                        tma_load_page(st + kTileKBytes + slot * kPageBytes, &map_v, page, &v_full[stage]);
-                    }
+                    if (lane < npages) tma_load_kpage(st + slot * kPageBytes, &map_k, page, &kv_full[stage]);
+                    if (g >= kStages && !warp_wait_l(wait_ns, &tile_done[(g - kStages) % 6u], ((g - kStages) / 6u) & 1u)) { ok = false; break; }
+                    if (lane == 0) mbar_arrive_expect_tx(&v_full[stage], npages * kPageBytes);
+                    __syncwarp();
+                    if (lane < npages) tma_load_page(st + kTileKBytes + slot * kPageBytes, &map_v, page, &v_full[stage]);
                 }
                 pf_valid = t + 1u < t1;
                 if (pf_valid) {
@@ -624,6 +625,7 @@ decode_tcp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                     umma_ss_pred(d_tmem, ad + uint64_t((uint32_t(hf) * kKBlock + uint32_t(ks) * 32u) >> 4),
                                  bd + uint64_t((uint32_t(hf) * 2048u + uint32_t(ks) * 32u) >> 4), IDESC_S, (hf | ks) ? 1u : 0u, el);
             umma_commit_pred(&s_full[gg & 1u], el);
+            umma_commit_pred(&k_empty[stage], el);
         };
         uint32_t g = 0;
         bool ok = true;
