@@ -7,29 +7,30 @@
 // about twice that.  One page of this cache, [16 tokens][2 heads][128 d], is 8 KB of contiguous memory, so this kernel
 // moves a page - both heads - with ONE copy and lets one CTA process both KV heads of a row together.
 //
-// Layout trick.  The copy goes through a 5-D tensor map over the pool with the dimensions permuted,
-//   {64 d_lo, 16 tokens (512 B apart), 2 halves of d (128 B), 2 heads (256 B), pages (8 KB)},  box = one page,
-// so a page lands in shared memory as four planes (head, half) of [16 tokens][128 B], 64 rows of 128 bytes with the
-// 128-byte swizzle: a valid K-major MMA operand whose rows are (head, half, token) triples.  Two pages are 128 such
-// rows = one M = 128 MMA.  The query operand has N = 32 rows (half', query head j), so the accumulator entry
-//   S'[(h, p, t)][(p', j)] = sum over the 64 d of half p of  K[t][h][.] * Q[j][half p'][.]
-// is a useful partial score when p' = p and j belongs to KV head h; the score of (t, j) is the sum of the entries of rows
-// (h, 0, t) and (h, 1, t), which sit in lanes l and l + 16 of one warp: one shuffle.  The same rows are the K dimension
-// of the second product, taken plane by plane: the 16 rows of plane (h, p) of a page are one K = 16 step,
-//   O'[d_lo][columns (p, h, 0..7)] += V_plane^T [64 d_lo x 16 t] . P_plane [16 t x 8 heads of h]      (M = 64, N = 8)
-// so the probability operand of a page is a plain [8 heads][64 page rows] K-major tile that every softmax thread fills
-// at its own row, and O'[d_lo][(p, h, jj)] = O[8 h + jj][64 p + d_lo].
+// Layout.  Both pools are read through 5-D tensor maps with the dimensions permuted, one copy per page, 128-byte swizzle.
+//   V: {64 d_lo, 16 tokens (512 B apart), 2 halves of d (128 B), 2 heads (256 B), pages (8 KB)}, box = one page: a page
+//      lands as four planes [head][half] of [16 tokens][128 B].  The two planes of a head are the MN-major A operand
+//      (M = 128 d as two groups of 64, K = the page's 16 tokens) of  O^T[d][jj] += V_page_head^T . P[jj][tokens].
+//   K: {64 d_lo, 8 tokens, 2 halves, 2 heads, (page, eight-token group) (4 KB apart)}, box {64, 8, 2, 2, 2} = one page: a
+//      page lands as sixteen 1 KB blocks of eight rows, [group][head][half][token][64].  For one half of d the blocks of
+//      a whole tile are 2 KB apart, all of them, so the tile's 128 rows (page, group, head, token) are ONE K-major A
+//      operand per half (8-row groups 2 KB apart) and the two halves are K steps of one accumulation:
+//        S[(page, group, head, token)][8 h' + jj] = sum over d of K[token][head][d] * Q[h' G + jj][d]     (M128 N16 K16 x 8)
+//      whose entry is a score where h' is the row's own KV head.
+// The probability operand of P.V is a K-major [query head][token] tile per pair of pages that every softmax thread fills at
+// its own token; M = 128 allows no N below 16, so its upper eight rows are zero and their result columns are not read.
 //
 // Roles (384 threads, one CTA per SM, persistent over a list of run pieces exactly as in kriya_decode_tc.cu); a tile is
-// four pages: 64 tokens of both heads, 32 KB of K and 32 KB of V, 256 operand rows:
-//   warps 0-7 softmax: warp w owns operand rows 32 w .. 32 w + 31 of the tile = (page w / 2, KV head w % 2; lane: half =
-//     lane / 16, token = lane % 16); warps 0-3 read the first score MMA's accumulator, warps 4-7 the second's,
-//   warp 8 producer (page indices, one tensor copy per page of K and of V into a 3-deep ring of 64 KB tiles),
-//   warp 9 MMA issuer, warp 10 scratch-set guard, warp 11 stager (queries, rotated in flight; the new token's K/V row).
+// four pages: 64 tokens of both heads, 32 KB of K and 32 KB of V:
+//   warps 0-7 softmax: a thread owns one score row; warps w and w + 4 both read the TMEM lanes of page w % 4 (lane = (group,
+//     head, token)) and share the row's query heads (warps 0-3 the first half of the group, warps 4-7 the second),
+//   warp 8 producer (page indices, one tensor copy per page of K and one of V into a 3-deep ring of 64 KB stages; the K
+//     half of a stage is loaded again as soon as its score MMAs are complete, the V half when the tile is done),
+//   warp 9 MMA issuer (scores two tiles ahead of P.V), warp 10 scratch-set guard, warp 11 stager (queries, rotated in
+//     flight; the new token's K/V row).
 // Split runs, the finishing piece, stamps and the set guard work as described in kriya_decode_tc.cu; a run here is a
-// whole plan row (both KV heads).  At the end of a piece the accumulator goes through shared memory so that threads
-// 0-127 finish the query heads of KV head 0 and threads 128-255 those of KV head 1, one output dimension each.  Every
-// wait is bounded.
+// whole plan row (both KV heads).  At the end of a piece threads 0-127 finish the query heads of KV head 0 and threads
+// 128-255 those of KV head 1, one output dimension each.  Every wait is bounded.
 #include <algorithm>
 #include <atomic>
 #include <cstdio>
@@ -43,13 +44,11 @@ namespace tcp {
 constexpr int kD = 128;
 constexpr int kPage = 16;
 constexpr int kHkv = 2;
-constexpr int kPagesPerTile = 4;                 // 4 pages x 64 operand rows = two M = 128 score MMAs
+constexpr int kPagesPerTile = 4;                 // 4 pages x 2 heads x 16 tokens = the 128 rows of a score MMA
 constexpr int kTileTokens = kPagesPerTile * kPage;
 constexpr uint32_t kPageBytes = 8192;            // one page of K (or V), both heads
 constexpr uint32_t kTileKBytes = kPagesPerTile * kPageBytes;  // 32 KB
 constexpr uint32_t kStageBytes = 2 * kTileKBytes;             // K tile + V tile
-// The K tile is kept as two halves of d: [half][page][head][token][64 d], so that the tile's 128 (page, head, token) rows are
-// one MMA operand per half and the two halves are steps of the same accumulation.
 // A K page lands as sixteen 1 KB blocks of eight rows, [eight-token group][head][half of d][token][64]: for one half of d the
 // blocks of a whole tile are 2 KB apart, all of them, so the tile's 128 (page, group, head, token) rows are one K-major MMA
 // operand per half (8-row groups 2 KB apart) although every page arrived as a single copy.
