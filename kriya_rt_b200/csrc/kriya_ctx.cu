@@ -1584,20 +1584,27 @@ int32_t kriya_cuda_decode_step_host_begin(kriya_cuda_ctx* c, const void* q_host,
     KRIYA_CUDA_TRY(c, cudaEventRecord(c->ev_step_begin, c->stream));  // the plan upload and earlier work come first
     KRIYA_CUDA_TRY(c, cudaStreamWaitEvent(c->copy_stream, c->ev_step_begin, 0));
     KRIYA_CUDA_TRY(c, cudaStreamWaitEvent(c->copy_stream_out, c->ev_step_begin, 0));
-    for (uint32_t g = 0; g < n_in; ++g) {  // all input copies are queued at once, in layer order
+    // The first group's copies are queued, then its launches, then the next group's copies and so on: a group's copies go
+    // out as soon as the launches of the group in front of it have been issued (they run under that group's compute),
+    // so the first launch is not held up by the host queuing a dozen copies.
+    auto queue_in = [&](uint32_t g) -> cudaError_t {
         const uint32_t l0 = in_start[g], l1 = in_start[g + 1];
         const size_t nq = size_t(l1 - l0) * qbl, nk = size_t(l1 - l0) * kbl;
-        KRIYA_CUDA_TRY(c, cudaMemcpyAsync(dq + l0 * qbl, static_cast<const uint8_t*>(q_host) + l0 * qbl, nq, cudaMemcpyHostToDevice, c->copy_stream));
-        KRIYA_CUDA_TRY(c, cudaMemcpyAsync(dk + l0 * kbl, static_cast<const uint8_t*>(k_host) + l0 * kbl, nk, cudaMemcpyHostToDevice, c->copy_stream));
-        KRIYA_CUDA_TRY(c, cudaMemcpyAsync(dv + l0 * kbl, static_cast<const uint8_t*>(v_host) + l0 * kbl, nk, cudaMemcpyHostToDevice, c->copy_stream));
-        KRIYA_CUDA_TRY(c, cudaEventRecord(c->ev_in[g], c->copy_stream));
-    }
-    uint32_t gi = 0, go = 0, layer = 0, out_from = 0;
+        cudaError_t e = cudaMemcpyAsync(dq + l0 * qbl, static_cast<const uint8_t*>(q_host) + l0 * qbl, nq, cudaMemcpyHostToDevice, c->copy_stream);
+        if (e == cudaSuccess) e = cudaMemcpyAsync(dk + l0 * kbl, static_cast<const uint8_t*>(k_host) + l0 * kbl, nk, cudaMemcpyHostToDevice, c->copy_stream);
+        if (e == cudaSuccess) e = cudaMemcpyAsync(dv + l0 * kbl, static_cast<const uint8_t*>(v_host) + l0 * kbl, nk, cudaMemcpyHostToDevice, c->copy_stream);
+        if (e == cudaSuccess) e = cudaEventRecord(c->ev_in[g], c->copy_stream);
+        return e;
+    };
+    KRIYA_CUDA_TRY(c, queue_in(0));
+    uint32_t gi = 0, go = 0, layer = 0, out_from = 0, queued = 1;
     while (layer < Lu) {
-        if (gi < n_in && in_start[gi] == layer) KRIYA_CUDA_TRY(c, cudaStreamWaitEvent(c->stream, c->ev_in[gi++], 0));
+        const bool group_start = gi < n_in && in_start[gi] == layer;
+        if (group_start) KRIYA_CUDA_TRY(c, cudaStreamWaitEvent(c->stream, c->ev_in[gi++], 0));
         uint32_t stop = out_end[go];                                  // next boundary of either kind
         if (gi < n_in && in_start[gi] < stop) stop = in_start[gi];
         if (int32_t rc = decode_layers(c, layer, stop, true, dq, dk, dv, dout, rows, rope, gqa)) return rc;
+        if (group_start && queued < n_in) KRIYA_CUDA_TRY(c, queue_in(queued++));
         layer = stop;
         if (layer == out_end[go]) {
             KRIYA_CUDA_TRY(c, cudaEventRecord(c->ev_done[go], c->stream));
