@@ -439,7 +439,8 @@ int32_t launch_decode(kriya_cuda_ctx* c, uint32_t layer, const void* q, void* ou
         const uint32_t grid = tc_geometry(c, variant).ctas;
         // A run spread over many CTAs (one long row) is merged by a kernel of its own behind the launch; launches that
         // overlap with their neighbours keep the merge inside, the scratch-set rotation relies on it.
-        const uint32_t max_parts = range_list ? c->tc_max_parts_ranges : c->tc_max_parts;
+        const bool chain_list = !range_list && c->use_chain_list && c->chain_list_valid && variant == 2;
+        const uint32_t max_parts = range_list ? c->tc_max_parts_ranges : chain_list ? c->tc_max_parts_chain : c->tc_max_parts;
         const bool late = fused.overlap_previous == 0u && max_parts > kLateMergeParts;
         // Successive launches take the scratch sets in turn and stamp what they publish with their own number.  The launches
         // of one step may overlap at their edges; a set comes round again kTcScratchSets launches later, and the kernel
@@ -452,9 +453,9 @@ int32_t launch_decode(kriya_cuda_ctx* c, uint32_t layer, const void* q, void* ou
         sc.set_done = c->tc_set_done + set * 16u;
         sc.done_expect = c->tc_done_expect[set];
         sc.epoch = c->tc_epoch;
-        const KriyaTcSeg* segs = c->plan_dev<KriyaTcSeg>(range_list ? c->off_tcseg2 : c->off_tcseg);
-        const uint32_t* seg_ptr = c->plan_dev<uint32_t>(range_list ? c->off_tcptr2 : c->off_tcptr);
-        const uint32_t n_seg = range_list ? c->n_seg_ranges : c->n_seg;
+        const KriyaTcSeg* segs = c->plan_dev<KriyaTcSeg>(range_list ? c->off_tcseg2 : chain_list ? c->off_tcseg3 : c->off_tcseg);
+        const uint32_t* seg_ptr = c->plan_dev<uint32_t>(range_list ? c->off_tcptr2 : chain_list ? c->off_tcptr3 : c->off_tcptr);
+        const uint32_t n_seg = range_list ? c->n_seg_ranges : chain_list ? c->n_seg_chain : c->n_seg;
         const uint32_t late_parts = late ? kLateMergeParts : UINT32_MAX;
         if (variant == 2) {
             KRIYA_CUDA_TRY(c, kriya_launch_decode_tcp(a, segs, seg_ptr, grid, c->tmap_kp, c->tmap_vp, layer * c->cfg.num_kv_blocks,
@@ -568,6 +569,8 @@ int32_t kriya_cuda_ctx_create(const kriya_cuda_config* cfg_in, kriya_cuda_ctx** 
     {
         const char* e = getenv("KRIYA_TC_VARIANT");  // 128 or 64: force one kernel variant (default: by plan)
         c->tc_force = e ? atoi(e) : 0;  // 128 / 64: one KV head per copy, 128- or 64-token tiles; default: by shape and plan
+        const char* cm = getenv("KRIYA_TC_CHAIN_MIN_TILES");  // tiles per CTA for overlapping launches of a step (0: as for any launch)
+        if (cm) c->tc_chain_min_tiles = uint32_t(std::max(0, atoi(cm)));
         const char* m = getenv("KRIYA_TC64_MIN_TILES");
         c->tc64_min_tiles = m ? uint32_t(std::max(1, atoi(m))) : 96u;
     }
@@ -684,6 +687,8 @@ int32_t kriya_cuda_ctx_create(const kriya_cuda_config* cfg_in, kriya_cuda_ctx** 
     off = align_up(off + size_t(c->cap_work) * sizeof(KriyaDecodeWork), 256);      // work list
     off = align_up(off + (size_t(c->tc_ctas) + 1) * 4 * kTcpHdrWords, 256);        // per-CTA segment ranges / records
     off = align_up(off + size_t(c->cap_seg) * sizeof(KriyaTcSeg), 256);            // segments
+    off = align_up(off + (size_t(c->tc_ctas) + 1) * 4 * kTcpHdrWords, 256);        // the same two for the list of overlapping launches
+    off = align_up(off + size_t(c->cap_seg) * sizeof(KriyaTcSeg), 256);
     off = align_up(off + size_t(c->cap_tiles) * sizeof(kriya_cta_work_tile), 256); // caller tiles
     off = align_up(off + size_t(c->cap_indices) * 4, 256);                         // page indices
     c->plan_bytes = off;
@@ -909,6 +914,21 @@ int32_t kriya_cuda_plan_upload(kriya_cuda_ctx* c, const int32_t* indptr, size_t 
         expand_tcp_headers(reinterpret_cast<uint32_t*>(h + o_ptr), plan_ctas, reinterpret_cast<const KriyaTcSeg*>(h + o_seg), indices,
                            geo.pages_per_tile, c->cfg.block_size_tokens, positions, uint32_t(n_positions));
     place(size_t(n_seg) * sizeof(KriyaTcSeg));
+    // the list for the overlapping launches of a whole-step call: the same rows, more tiles per CTA
+    size_t o_ptr3 = 0, o_seg3 = 0;
+    uint32_t n_seg3 = 0;
+    const bool chain_list = variant == 2 && c->tc_chain_min_tiles > geo.min_tiles;
+    if (chain_list) {
+        o_ptr3 = place((size_t(plan_ctas) + 1) * 4 * kTcpHdrWords);
+        o_seg3 = off;
+        n_seg3 = build_tc_segments(indptr, last_len, c->cfg.block_size_tokens, uint32_t(rows), geo.runs_per_row, nullptr, nullptr, plan_ctas,
+                                   geo.pages_per_tile, reinterpret_cast<KriyaTcSeg*>(h + o_seg3), c->cap_seg,
+                                   reinterpret_cast<uint32_t*>(h + o_ptr3), c->tc_chain_min_tiles, c->attention_window);
+        if (n_seg3 == UINT32_MAX) return invalid("plan needs more decode segments than the context holds");
+        expand_tcp_headers(reinterpret_cast<uint32_t*>(h + o_ptr3), plan_ctas, reinterpret_cast<const KriyaTcSeg*>(h + o_seg3), indices,
+                           geo.pages_per_tile, c->cfg.block_size_tokens, positions, uint32_t(n_positions));
+        place(size_t(n_seg3) * sizeof(KriyaTcSeg));
+    }
     const size_t o_tiles = place(std::max<size_t>(tiles_len, 1) * sizeof(kriya_cta_work_tile));
     if (tiles_len) memcpy(h + o_tiles, tiles, tiles_len * sizeof(kriya_cta_work_tile));
     const size_t o_indices = place(std::max<size_t>(indices_len, 1) * 4);
@@ -926,6 +946,11 @@ int32_t kriya_cuda_plan_upload(kriya_cuda_ctx* c, const int32_t* indptr, size_t 
     c->tc_variant = variant;
     c->n_seg = n_seg;
     c->tc_max_parts = max_parts_of(reinterpret_cast<const KriyaTcSeg*>(h + o_seg), n_seg);
+    c->chain_list_valid = chain_list;
+    c->off_tcptr3 = o_ptr3;
+    c->off_tcseg3 = o_seg3;
+    c->n_seg_chain = n_seg3;
+    c->tc_max_parts_chain = chain_list ? max_parts_of(reinterpret_cast<const KriyaTcSeg*>(h + o_seg3), n_seg3) : 0u;
 
     c->n_rows = uint32_t(rows);
     c->n_indices = uint32_t(indices_len);
@@ -1520,6 +1545,12 @@ static int32_t decode_layers(kriya_cuda_ctx* c, uint32_t l0, uint32_t l1, bool f
                              const kriya_bsr_gqa_params* gqa) {
     const size_t qb = size_t(rows) * c->cfg.num_q_heads * c->cfg.head_dim * 2;
     const size_t kb = size_t(rows) * c->cfg.num_kv_heads * c->cfg.head_dim * 2;
+    // launches that are declared independent overlap: they take the work list with the longer streams (see chain_list_valid)
+    struct ChainScope {
+        kriya_cuda_ctx* c;
+        ~ChainScope() { c->use_chain_list = false; }
+    } chain_scope{c};
+    c->use_chain_list = c->layer_chain_mode == 2u && !c->timing && c->fuse_append && use_tc_decode(c) && !rope->apply_qk_norm;
     for (uint32_t layer = l0; layer < l1; ++layer) {
         uint8_t* ql = static_cast<uint8_t*>(q) + layer * qb;
         const uint8_t* kl = static_cast<const uint8_t*>(k) + layer * kb;

@@ -112,6 +112,12 @@ struct kriya_cuda_ctx {
            off_range = 0, off_tcseg = 0, off_tcptr = 0, off_tcseg2 = 0, off_tcptr2 = 0, dyn_base = 0;
     uint32_t cap_seg = 0, n_seg = 0, n_seg_ranges = 0;
     uint32_t tc_max_parts = 0, tc_max_parts_ranges = 0;  // most pieces any run of the current (range) lists is cut into
+    // Third work list of the whole-page decode kernel, for the launches of a whole-step call whose layers are declared
+    // independent (layer_chain_mode 2): those launches overlap, so a CTA is given more tiles before another one is
+    // brought in (fewer, longer streams per launch; a launch alone takes longer).  Built with every plan upload.
+    size_t off_tcptr3 = 0, off_tcseg3 = 0;
+    uint32_t n_seg_chain = 0, tc_max_parts_chain = 0, tc_chain_min_tiles = 14;
+    bool chain_list_valid = false, use_chain_list = false;
     uint32_t layer_chain_mode = 2;  // KriyaFusedAppend::overlap_previous for the second and later layers of a whole-step call
     bool fuse_append = true;  // whole-step calls use the fused append + decode launch where it applies
     uint64_t wait_ns = 2000000000ull;  // limit of the bounded waits inside kernels (kriya_cuda_set_wait_limit_us)
