@@ -339,6 +339,19 @@ int32_t kriya_cuda_set_wait_limit_us(kriya_cuda_ctx* ctx, uint32_t limit_us);
  * exercised on purpose and without any fault.  The next kriya_cuda_sync() must return KRIYA_CUDA_EXECUTION_ERROR. */
 int32_t kriya_cuda_selftest_wait_expiry(kriya_cuda_ctx* ctx);
 
+/* Host only, no device needed: how a plan's rows are cut into pieces for the persistent tensor-core decode kernels (the
+ * stream-K counterpart of the reference's split-K tile list, bsr_paged.rs:285-297, build_cta_work_tiles
+ * kv_manager.rs:716-757).  `runs_per_row` is 1 for the whole-page kernel (a run = a plan row, both KV heads) and the number
+ * of KV heads for the one-head-per-copy kernels; a tile is `pages_per_tile` blocks; a CTA is given at least `min_tiles`
+ * tiles before another one is brought in; `window` as in kriya_cuda_set_attention_window (0 = none).  Writes one record of
+ * 12 words per piece - row, KV head, first block, end block, scratch slot, the run's first slot, the run's piece count,
+ * the row's offset in the page indices, its tokens, its first attended token, two zero words - in the order the CTAs
+ * take them, and ctas + 1 offsets into that list.  Returns the number of records, or -1 when `cap` records do not suffice. */
+int64_t kriya_cuda_debug_work_split(const int32_t* page_indptr, const int32_t* last_page_len, uint32_t rows,
+                                    uint32_t block_size_tokens, uint32_t runs_per_row, uint32_t ctas, uint32_t pages_per_tile,
+                                    uint32_t min_tiles, uint32_t window, uint32_t* out_records, uint32_t cap,
+                                    uint32_t* out_cta_offsets);
+
 /* AttentionMaskVariant::SlidingWindowCausal { window_size } (crates/kriya-core/src/descriptor.rs:63-70; declared by the
  * reference, read by none of its kernels).  With window_size > 0 a query at position p attends keys p + 1 - window_size
  * ..= p (itself included) in every following decode and prefill call; 0 (the default) is the plain causal mask.  Decode

@@ -149,6 +149,8 @@ CUDA_SYMBOLS = {
     "kriya_cuda_set_attention_window": (C.c_int32, [_VP, C.c_uint32]),
     "kriya_cuda_set_wait_limit_us": (C.c_int32, [_VP, C.c_uint32]),
     "kriya_cuda_selftest_wait_expiry": (C.c_int32, [_VP]),
+    "kriya_cuda_debug_work_split": (C.c_int64, [_VP, _VP, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32,
+                                    C.c_uint32, _VP, C.c_uint32, _VP]),
     "kriya_cuda_timing_enable": (C.c_int32, [_VP, C.c_int32]),
     "kriya_cuda_timing_read": (C.c_int32, [_VP, C.c_uint32, C.POINTER(C.c_uint64), C.POINTER(C.c_double)]),
     "kriya_cuda_paged_gqa_decode_static": (C.c_int32, [C.c_int32, _VP, C.c_uint32, _VP, _VP, _VP, C.c_uint32, _VP, _VP,

@@ -1697,6 +1697,19 @@ int32_t kriya_cuda_set_attention_window(kriya_cuda_ctx* c, uint32_t window_size)
     return KRIYA_CUDA_OK;
 }
 
+int64_t kriya_cuda_debug_work_split(const int32_t* page_indptr, const int32_t* last_page_len, uint32_t rows,
+                                    uint32_t block_size_tokens, uint32_t runs_per_row, uint32_t ctas, uint32_t pages_per_tile,
+                                    uint32_t min_tiles, uint32_t window, uint32_t* out_records, uint32_t cap,
+                                    uint32_t* out_cta_offsets) {
+    if (!page_indptr || !last_page_len || !out_records || !out_cta_offsets || block_size_tokens == 0 || runs_per_row == 0 ||
+        ctas == 0 || pages_per_tile == 0 || min_tiles == 0)
+        return -1;
+    static_assert(sizeof(KriyaTcSeg) == 12 * sizeof(uint32_t), "a record is twelve words");
+    const uint32_t n = build_tc_segments(page_indptr, last_page_len, block_size_tokens, rows, runs_per_row, nullptr, nullptr, ctas,
+                                         pages_per_tile, reinterpret_cast<KriyaTcSeg*>(out_records), cap, out_cta_offsets, min_tiles, window);
+    return n == UINT32_MAX ? -1 : int64_t(n);
+}
+
 int32_t kriya_cuda_set_fused_append(kriya_cuda_ctx* c, int32_t enable) {
     if (!c) return KRIYA_CUDA_INVALID_INPUT;
     c->fuse_append = (enable & 1) != 0;
