@@ -917,17 +917,21 @@ int32_t kriya_cuda_plan_upload(kriya_cuda_ctx* c, const int32_t* indptr, size_t 
     // the list for the overlapping launches of a whole-step call: the same rows, more tiles per CTA
     size_t o_ptr3 = 0, o_seg3 = 0;
     uint32_t n_seg3 = 0;
-    const bool chain_list = variant == 2 && c->tc_chain_min_tiles > geo.min_tiles;
+    bool chain_list = variant == 2 && c->tc_chain_min_tiles > geo.min_tiles;
     if (chain_list) {
         o_ptr3 = place((size_t(plan_ctas) + 1) * 4 * kTcpHdrWords);
         o_seg3 = off;
         n_seg3 = build_tc_segments(indptr, last_len, c->cfg.block_size_tokens, uint32_t(rows), geo.runs_per_row, nullptr, nullptr, plan_ctas,
                                    geo.pages_per_tile, reinterpret_cast<KriyaTcSeg*>(h + o_seg3), c->cap_seg,
                                    reinterpret_cast<uint32_t*>(h + o_ptr3), c->tc_chain_min_tiles, c->attention_window);
-        if (n_seg3 == UINT32_MAX) return invalid("plan needs more decode segments than the context holds");
-        expand_tcp_headers(reinterpret_cast<uint32_t*>(h + o_ptr3), plan_ctas, reinterpret_cast<const KriyaTcSeg*>(h + o_seg3), indices,
-                           geo.pages_per_tile, c->cfg.block_size_tokens, positions, uint32_t(n_positions));
-        place(size_t(n_seg3) * sizeof(KriyaTcSeg));
+        if (n_seg3 == UINT32_MAX) {  // (it has no more pieces than the ordinary list; should it not fit, that list serves)
+            chain_list = false;
+            n_seg3 = 0;
+        } else {
+            expand_tcp_headers(reinterpret_cast<uint32_t*>(h + o_ptr3), plan_ctas, reinterpret_cast<const KriyaTcSeg*>(h + o_seg3), indices,
+                               geo.pages_per_tile, c->cfg.block_size_tokens, positions, uint32_t(n_positions));
+            place(size_t(n_seg3) * sizeof(KriyaTcSeg));
+        }
     }
     const size_t o_tiles = place(std::max<size_t>(tiles_len, 1) * sizeof(kriya_cta_work_tile));
     if (tiles_len) memcpy(h + o_tiles, tiles, tiles_len * sizeof(kriya_cta_work_tile));
