@@ -468,8 +468,9 @@ def run_gpu_arm(args):
                          "launch_us_isolated": dec_us, "achieved_isolated": gbs(dec_us) if n_dec else None,
                          "frac_isolated": (gbs(dec_us) / peak) if n_dec else None,
                          "how": "achieved = algorithmic bytes per launch / (device time of the timed region / launches in it), CUDA events on "
-                                "the launching stream.  in_stream: the 36 launches of a step have independent inputs and may overlap at their "
-                                "edges (programmatic dependent launch); dependent: every layer's queries and new K/V wait for the previous "
+                                "the launching stream.  in_stream: the 36 launches of a step have independent inputs and may overlap (programmatic "
+                                "dependent launch; such launches take the plan's work list with at least 14 tiles per CTA, so about two "
+                                "launches are in flight; the other legs take the list of a single launch, at least 8 tiles); dependent: every layer's queries and new K/V wait for the previous "
                                 "layer's launch, only its cached K/V streams early; serial: nothing of a launch but its set-up precedes the "
                                 "previous launch's completion; isolated: every launch between two events of its own (includes the idle time "
                                 "the events cost)",
